@@ -1,0 +1,178 @@
+/*
+ * libsparsetriton_b200 -- C ABI of the B200 (sm_100a) sparse-convolution hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*,
+ * i.e. a cudaStream_t; NULL = legacy default stream) and returns an int status:
+ *     0  ST_OK
+ *    <0  argument / support error detected on the host before any launch (table below)
+ * Conditions detected on the device (hash table full, output buffer too small) are written to a
+ * caller-supplied int32 status word in device memory; the bits are listed at ST_DEV_*.
+ * No entry point allocates or frees memory: scratch is passed in by the caller, sized by the
+ * matching *_workspace_bytes() call.  All work is enqueued on the given stream; nothing here
+ * synchronises.
+ *
+ * Each declaration names the function of ptj0225/SparseTriton it stands in for
+ * (path:line inside that project).  The reference has no FFI of its own -- its kernels are
+ * Triton programs called from Python -- so "replaces" means: the Python callable of the same
+ * role calls this entry point instead of launching the Triton kernel.
+ *
+ * Layouts
+ *   coordinates  (N,4) row-major, columns (batch, x, y, z); int16 (ST_I16) or int32 (ST_I32);
+ *                every value must lie in [0, 65535] to be representable in a key
+ *   hash table   keys  int64[capacity], -1 = empty, else batch<<48 | x<<32 | y<<16 | z
+ *                vals  int32[capacity], row index of the key, -1 = empty
+ *   offsets      (K,3) int32 in HOST memory (copied into the launch parameters), K <= 343
+ *   neighbour map  int32 (N_out, K) row-major, -1 = no neighbour  (the reference's layout)
+ *   features     (N, C) row-major, fp32 / fp16 / bf16; weights (K, Cin, Cout) row-major, same dtype
+ */
+#ifndef SPARSETRITON_B200_H
+#define SPARSETRITON_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ST_OK 0
+#define ST_ERR_ARG (-1)         /* null pointer, negative size, K out of range ... */
+#define ST_ERR_DTYPE (-2)       /* unknown dtype code */
+#define ST_ERR_WORKSPACE (-3)   /* workspace too small or misaligned */
+#define ST_ERR_CUDA (-4)        /* a launch was rejected; st_last_error_string() has the text */
+#define ST_ERR_UNSUPPORTED (-5) /* shape outside what the kernels handle */
+
+#define ST_DEV_TABLE_FULL 1     /* an insert ran out of probes: capacity too small */
+#define ST_DEV_OUT_OVERFLOW 2   /* more output rows than the caller's buffer holds */
+#define ST_DEV_BAD_INDEX 4      /* a map entry pointed outside the feature matrix (debug checks) */
+
+#define ST_I16 0
+#define ST_I32 1
+
+#define ST_F32 0                /* fp32 storage; tensor-core kernels multiply in tf32 */
+#define ST_F16 1
+#define ST_BF16 2
+
+#define ST_MAX_KVOL 343
+
+/* Library revision (monotonic integer). */
+int st_version(void);
+/* Text of the last host-side error of the calling thread. */
+const char* st_last_error_string(void);
+/* 1 if the tcgen05 (tensor-core) kernels can serve this conv shape, else 0 (SIMT kernels used). */
+int st_conv_uses_tensor_cores(int dtype, int cin, int cout);
+
+/* ---------------------------------------------------------------- hash table ------------- */
+
+/* Fill keys and vals with -1.
+ * Replaces the two torch.full(-1) fills of HashTable.__init__, sparsetriton/utils/hash.py:428-429. */
+int st_hash_clear(int64_t* keys, int32_t* vals, int64_t capacity, void* stream);
+
+/* Insert n coordinates; value = row index; a repeated coordinate keeps its largest row.
+ * Replaces HashTable.insert -> build_hash_table_kernel, sparsetriton/utils/hash.py:516-544, 193-258.
+ * status: device int32, ST_DEV_TABLE_FULL is OR-ed in if some key found no slot. */
+int st_hash_build(const void* coords, int64_t n, int coord_dtype, int64_t* keys, int32_t* vals,
+                  int64_t capacity, int32_t* status, void* stream);
+
+/* out[i] = row of coords[i] or -1.
+ * Replaces HashTable.query -> query_hash_table_kernel, sparsetriton/utils/hash.py:546-580, 261-366. */
+int st_hash_query(const void* coords, int64_t m, int coord_dtype, const int64_t* keys, const int32_t* vals,
+                  int64_t capacity, int32_t* out, void* stream);
+
+/* ---------------------------------------------------------------- output coordinates ----- */
+
+/* Scratch needed by st_outcoords_count/_write for n inputs and K offsets. */
+int64_t st_outcoords_workspace_bytes(int64_t n, int K, int stride, int transposed);
+
+/* Pass 1 of the output-coordinate build of a strided (transposed = 0) or transposed conv:
+ * enumerate candidates  in+off (kept if divisible by stride on every axis, then divided)  or
+ * in*stride+off (transposed; batch column unscaled), drop those outside [0,new_shape), dedupe
+ * keeping the candidate with the smallest flat index n*K+k, and write the number of survivors
+ * to *n_out (device or pinned-host int64).
+ * Replaces _build_out_coords_normal / _build_out_coords_transposed with expand_coords_kernel,
+ * mask_spatial_range and filter_unique_kernel: nn/functional/conv/kmap.py:213-444, 11-97,
+ * utils/spatial/tile.py:6-84. */
+int st_outcoords_count(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K,
+                       int stride, int transposed, const int32_t* new_shape_host, void* workspace,
+                       int64_t workspace_bytes, int64_t* n_out, int32_t* status, void* stream);
+
+/* Pass 2: write the surviving coordinates, ordered by first occurrence (n-major, k-minor), into
+ * out_coords (same integer type as coords, out_capacity rows).  Must follow st_outcoords_count on
+ * the same stream with the same arguments and workspace. */
+int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K,
+                       int stride, int transposed, const int32_t* new_shape_host, void* workspace,
+                       int64_t workspace_bytes, void* out_coords, int64_t out_capacity, int32_t* status,
+                       void* stream);
+
+/* ---------------------------------------------------------------- neighbour map ---------- */
+
+/* nbr[o,k] = row of (batch, out*lookup_stride - off[k]) if inside [0,lookup_shape) and present.
+ * Replaces compute_neighbor_indices, nn/functional/conv/conv.py:12-75. */
+int st_map_build(const void* out_coords, int64_t n_out, int coord_dtype, const int32_t* offsets_host, int K,
+                 int lookup_stride, const int32_t* lookup_shape_host, const int64_t* keys, const int32_t* vals,
+                 int64_t capacity, int32_t* nbr, void* stream);
+
+/* inv[i,k] = o for every nbr[o,k] = i >= 0, -1 elsewhere (inv is (n_in,K) and is fully written).
+ * No counterpart in the reference, whose dgrad scatters with atomics
+ * (funcs/implicit_precomputed_gemm.py:129-177); this is the map its gather-form dgrad reads. */
+int st_map_invert(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, int32_t* inv, void* stream);
+
+/* Scratch for st_map_pairs_count/_write. */
+int64_t st_map_pairs_workspace_bytes(int64_t n_out, int K);
+/* Number of valid entries of a neighbour map -> *n_pairs (device or pinned-host int64). */
+int st_map_pairs_count(const int32_t* nbr, int64_t n_out, int K, void* workspace, int64_t workspace_bytes,
+                       int64_t* n_pairs, void* stream);
+/* The map as (in_idx, out_idx, offset) int32 triples in (out_idx, offset) order; follows _count.
+ * No counterpart in the reference (its map stays dense); used for pair statistics and parity. */
+int st_map_pairs_write(const int32_t* nbr, int64_t n_out, int K, void* workspace, int64_t workspace_bytes,
+                       int32_t* triples, int64_t capacity, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------- convolution ------------ */
+
+/* Scratch for the three products with a stored map (max over fwd/dgrad/wgrad). */
+int64_t st_conv_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout);
+
+/* Y[o,:] = sum_k X[nbr[o,k],:] . W[k]      fp32 accumulation, Y in the feature dtype.
+ * Replaces ConvPrecomputedNeighborGEMM.forward -> precomputed_fwd_kernel,
+ * funcs/implicit_precomputed_gemm.py:237-276, 64-126. */
+int st_conv_fwd(int dtype, const void* X, const void* W, const int32_t* nbr, void* Y, int64_t n_in,
+                int64_t n_out, int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* dX[i,:] = sum_k dY[inv[i,k],:] . W[k]^T  (gather form over the inverse map; deterministic).
+ * Replaces precomputed_bwd_feat_kernel, funcs/implicit_precomputed_gemm.py:278-304, 129-177. */
+int st_conv_dgrad(int dtype, const void* dY, const void* W, const int32_t* inv, void* dX, int64_t n_in,
+                  int64_t n_out, int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* dW[k] = sum_o X[nbr[o,k],:]^T . dY[o,:]  split over (offset, row chunk) into fp32 partials that
+ * a second kernel reduces in a fixed order.
+ * Replaces precomputed_bwd_weight_kernel, funcs/implicit_precomputed_gemm.py:306-324, 180-230. */
+int st_conv_wgrad(int dtype, const void* X, const void* dY, const int32_t* nbr, void* dW, int64_t n_in,
+                  int64_t n_out, int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Hash-on-the-fly forms: no stored map; every tile recomputes
+ *   curr = out*lookup_stride - off[k], bounds-checks it against lookup_shape and probes the table.
+ * Replace ConvHashOnTheFlyImplicitGEMM forward / backward,
+ * funcs/implicit_hashfly_gemm.py:330-452 with kernels :45-148, :151-237, :239-328. */
+int64_t st_conv_hashfly_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout);
+
+int st_conv_fwd_hashfly(int dtype, const void* X, const void* W, const void* out_coords, int coord_dtype,
+                        const int32_t* offsets_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
+                        const int32_t* lookup_shape_host, int lookup_stride, void* Y, int64_t n_in, int64_t n_out,
+                        int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* dX[row(curr),:] += dY[o,:] . W[k]^T, scatter-accumulated in fp32 and then cast to the dtype. */
+int st_conv_dgrad_hashfly(int dtype, const void* dY, const void* W, const void* out_coords, int coord_dtype,
+                          const int32_t* offsets_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
+                          const int32_t* lookup_shape_host, int lookup_stride, void* dX, int64_t n_in,
+                          int64_t n_out, int K, int cin, int cout, void* workspace, int64_t workspace_bytes,
+                          void* stream);
+
+int st_conv_wgrad_hashfly(int dtype, const void* X, const void* dY, const void* out_coords, int coord_dtype,
+                          const int32_t* offsets_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
+                          const int32_t* lookup_shape_host, int lookup_stride, void* dW, int64_t n_in,
+                          int64_t n_out, int K, int cin, int cout, void* workspace, int64_t workspace_bytes,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSETRITON_B200_H */

@@ -1,0 +1,114 @@
+"""Loader and thin ctypes binding of libsparsetriton_b200.so.
+
+The product has no CPU fallback: if the library is missing, or a tensor that reaches a
+kernel is not a CUDA tensor, the call raises.  Pointers are taken from torch tensors; the
+library itself knows nothing about torch.
+"""
+import ctypes
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "_native", "libsparsetriton_b200.so")
+
+ST_I16, ST_I32 = 0, 1
+ST_F32, ST_F16, ST_BF16 = 0, 1, 2
+DEV_TABLE_FULL, DEV_OUT_OVERFLOW, DEV_BAD_INDEX = 1, 2, 4
+
+_COORD_CODES = {torch.int16: ST_I16, torch.int32: ST_I32}
+_FEAT_CODES = {torch.float32: ST_F32, torch.float16: ST_F16, torch.bfloat16: ST_BF16}
+
+_lib = None
+
+_I64, _INT, _PTR = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+
+_SIGNATURES = {
+    "st_version": ([], _INT),
+    "st_last_error_string": ([], ctypes.c_char_p),
+    "st_conv_uses_tensor_cores": ([_INT, _INT, _INT], _INT),
+    "st_hash_clear": ([_PTR, _PTR, _I64, _PTR], _INT),
+    "st_hash_build": ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
+    "st_hash_query": ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
+    "st_outcoords_workspace_bytes": ([_I64, _INT, _INT, _INT], _I64),
+    "st_outcoords_count": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _I64, _PTR, _PTR, _PTR], _INT),
+    "st_outcoords_write": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _I64, _PTR, _I64, _PTR, _PTR], _INT),
+    "st_map_build": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
+    "st_map_invert": ([_PTR, _I64, _INT, _I64, _PTR, _PTR], _INT),
+    "st_map_pairs_workspace_bytes": ([_I64, _INT], _I64),
+    "st_map_pairs_count": ([_PTR, _I64, _INT, _PTR, _I64, _PTR, _PTR], _INT),
+    "st_map_pairs_write": ([_PTR, _I64, _INT, _PTR, _I64, _PTR, _I64, _PTR, _PTR], _INT),
+    "st_conv_workspace_bytes": ([_INT, _I64, _I64, _INT, _INT, _INT], _I64),
+    "st_conv_hashfly_workspace_bytes": ([_INT, _I64, _I64, _INT, _INT, _INT], _I64),
+    "st_conv_fwd": ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),
+    "st_conv_dgrad": ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),
+    "st_conv_wgrad": ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),
+}
+_HASHFLY_SIG = ([_INT, _PTR, _PTR, _PTR, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _INT, _PTR, _I64, _I64, _INT, _INT, _INT,
+                 _PTR, _I64, _PTR], _INT)
+for _n in ("st_conv_fwd_hashfly", "st_conv_dgrad_hashfly", "st_conv_wgrad_hashfly"):
+    _SIGNATURES[_n] = _HASHFLY_SIG
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+
+def lib():
+    """The loaded library; raises RuntimeError if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m sparsetriton_b200.build` "
+                "(needs nvcc; there is no CPU fallback)")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (argtypes, restype) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = restype
+        _lib = handle
+    return _lib
+
+
+def check(rc, what):
+    if rc != 0:
+        msg = lib().st_last_error_string().decode()
+        raise RuntimeError(f"{what} failed with status {rc}: {msg}")
+
+
+def require_cuda(t, what):
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: expected a CUDA tensor, got device '{t.device}' "
+                           "(sparsetriton_b200 has no CPU path)")
+
+
+def coord_code(t):
+    try:
+        return _COORD_CODES[t.dtype]
+    except KeyError:
+        raise TypeError(f"coordinates must be int16 or int32 for the CUDA kernels, got {t.dtype}") from None
+
+
+def feat_code(t):
+    try:
+        return _FEAT_CODES[t.dtype]
+    except KeyError:
+        raise TypeError(f"features must be float32, float16 or bfloat16, got {t.dtype}") from None
+
+
+def ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() > 0 else ctypes.c_void_p(0)
+
+
+def stream_ptr(device=None):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def host_i32(values):
+    """A ctypes int32 array (host) from a flat python sequence."""
+    vals = [int(v) for v in values]
+    return (ctypes.c_int32 * len(vals))(*vals)
+
+
+def workspace(nbytes, device):
+    """256-byte aligned scratch from torch's caching allocator."""
+    return torch.empty((max(int(nbytes), 256),), dtype=torch.uint8, device=device)

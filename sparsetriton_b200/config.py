@@ -1,0 +1,73 @@
+"""Process-wide switches of the sparse-convolution path.
+
+Mirrors sparsetriton/config.py:21-201 of the reference: same names, defaults, accepted
+inputs and error types.  `_STATE` is a plain dict because callers snapshot and restore it.
+"""
+from enum import Enum
+
+import torch
+
+__all__ = [
+    "ConvAlgo", "set_coords_dtype", "get_coords_dtype", "set_conv_algo", "get_conv_algo",
+    "set_h_table_f", "get_h_table_f", "set_h_table_max_p", "get_h_table_max_p",
+]
+
+
+class ConvAlgo(Enum):
+    """Which form of the gather-GEMM-scatter convolution runs (config.py:21-35)."""
+    ImplicitHashFlyGEMM = "Implicit_hashfly_gemm"          # probe the hash table inside the GEMM
+    PrecomputedNeighborGEMM = "Precomputed_neighbor_gemm"  # stored (N_out, K) neighbour map
+
+
+_STATE = {
+    "coords_dtype": torch.int16,
+    "algo": ConvAlgo.PrecomputedNeighborGEMM,
+    "h_tbl_factor": 1.5,       # minimum slots per key; tables are rounded up to a power of two
+    "h_tbl_max_probe_n": 16,   # kept for API parity; probing here is bounded by the capacity
+}
+
+
+def set_coords_dtype(dtype):
+    if not isinstance(dtype, torch.dtype):
+        raise TypeError(f"Expected torch.dtype, got {type(dtype)}")
+    _STATE["coords_dtype"] = dtype
+
+
+def get_coords_dtype():
+    return _STATE["coords_dtype"]
+
+
+def set_conv_algo(algo):
+    if not isinstance(algo, ConvAlgo):
+        raise TypeError(f"Expected ConvAlgo, got {type(algo)}")
+    _STATE["algo"] = algo
+
+
+def get_conv_algo():
+    return _STATE["algo"]
+
+
+def set_h_table_f(factor):
+    try:
+        value = float(factor)
+    except (TypeError, ValueError):
+        raise TypeError("factor must be a number")
+    assert value >= 1, "factor must be >= 1"
+    _STATE["h_tbl_factor"] = value
+
+
+def get_h_table_f():
+    return _STATE["h_tbl_factor"]
+
+
+def set_h_table_max_p(probe_n):
+    try:
+        value = int(probe_n)
+    except (TypeError, ValueError):
+        raise TypeError("probe_n must be an integer")
+    assert value > 0, "probe_n must be positive"
+    _STATE["h_tbl_max_probe_n"] = value
+
+
+def get_h_table_max_p():
+    return _STATE["h_tbl_max_probe_n"]

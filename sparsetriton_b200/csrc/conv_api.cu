@@ -1,0 +1,276 @@
+// C entry points of the convolution products: argument checks, dtype dispatch, choice between the
+// tensor-core (tcgen05) kernels and the general CUDA-core kernels.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "conv_maps.cuh"
+#include "conv_tc.cuh"
+
+namespace st {
+
+int wgrad_chunks(int64_t n_out);
+
+template <typename T, typename Map>
+int simt_gather(const T* in, const T* w, const Map& map, T* out, int64_t n_rows, int64_t n_src, int K, int c_red,
+                int c_acc, bool w_transposed, cudaStream_t s);
+template <typename T, typename Map>
+int simt_scatter(const T* in, const T* w, const Map& map, T* out, float* out32, int64_t n_rows, int64_t n_dst, int K,
+                 int c_red, int c_acc, cudaStream_t s);
+template <typename T, typename Map>
+int simt_wgrad(const T* x, const T* dy, const Map& map, T* dw, float* partial, int64_t n_rows, int64_t n_src, int K,
+               int cin, int cout, cudaStream_t s);
+
+static int64_t elem_size(int dtype) { return dtype == ST_F32 ? 4 : 2; }
+
+static int check_conv_args(const char* who, int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout) {
+  if (dtype != ST_F32 && dtype != ST_F16 && dtype != ST_BF16) {
+    set_error("%s: unknown feature dtype %d", who, dtype);
+    return ST_ERR_DTYPE;
+  }
+  if (n_in < 0 || n_out < 0 || K < 1 || K > ST_MAX_KVOL || cin < 1 || cout < 1 || n_in > 0x7FFFFFFFll ||
+      n_out > 0x7FFFFFFFll) {
+    set_error("%s: bad sizes n_in=%lld n_out=%lld K=%d cin=%d cout=%d", who, (long long)n_in, (long long)n_out, K,
+              cin, cout);
+    return ST_ERR_ARG;
+  }
+  return ST_OK;
+}
+
+static int64_t wgrad_partial_bytes(int64_t n_out, int K, int cin, int cout) {
+  return align_up((int64_t)wgrad_chunks(n_out) * K * cin * cout * 4, 256);
+}
+
+// Dispatch a callable over the feature dtype.
+template <typename F>
+static int by_dtype(int dtype, F&& f) {
+  switch (dtype) {
+    case ST_F32: return f(static_cast<float*>(nullptr));
+    case ST_F16: return f(static_cast<__half*>(nullptr));
+    default: return f(static_cast<__nv_bfloat16*>(nullptr));
+  }
+}
+
+template <typename CT>
+static HashFlyMap<CT> make_hashfly(const void* coords, const Offsets& off, const int64_t* keys, const int32_t* vals,
+                                   int64_t capacity, const int32_t* shape, int stride) {
+  HashFlyMap<CT> m;
+  m.coords = static_cast<const CT*>(coords);
+  m.off = off;
+  m.table = make_table(keys, vals, capacity);
+  m.shape = Int3{shape[0], shape[1], shape[2]};
+  m.stride = stride;
+  return m;
+}
+
+static int check_hashfly_args(const char* who, const void* coords, int coord_dtype, const int32_t* offsets_host,
+                              const int64_t* keys, const int32_t* vals, int64_t capacity, const int32_t* shape,
+                              int stride, int K, int64_t n_out, Offsets* off) {
+  if (coord_dtype != ST_I16 && coord_dtype != ST_I32) {
+    set_error("%s: unknown coordinate dtype %d", who, coord_dtype);
+    return ST_ERR_DTYPE;
+  }
+  if (!offsets_host || !shape || stride < 1 || capacity < 0 || capacity > 0x7FFFFFFFll ||
+      (capacity > 0 && (!keys || !vals)) || (n_out > 0 && !coords)) {
+    set_error("%s: bad map arguments", who);
+    return ST_ERR_ARG;
+  }
+  if (!pack_offsets(offsets_host, K, off)) {
+    set_error("%s: offset outside int16", who);
+    return ST_ERR_UNSUPPORTED;
+  }
+  return ST_OK;
+}
+
+}  // namespace st
+
+using namespace st;
+
+extern "C" {
+
+int st_conv_uses_tensor_cores(int dtype, int cin, int cout) { return tc_supported(dtype, cin, cout) ? 1 : 0; }
+
+int64_t st_conv_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout) {
+  (void)dtype;
+  (void)n_in;
+  if (n_out < 0 || K < 1 || cin < 1 || cout < 1) return 256;
+  return wgrad_partial_bytes(n_out, K, cin, cout) + 256;
+}
+
+int64_t st_conv_hashfly_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout) {
+  if (n_in < 0 || n_out < 0 || K < 1 || cin < 1 || cout < 1) return 256;
+  int64_t scatter = dtype == ST_F32 ? 0 : align_up(n_in * cin * 4, 256);
+  int64_t wg = wgrad_partial_bytes(n_out, K, cin, cout);
+  return (scatter > wg ? scatter : wg) + 256;
+}
+
+int st_conv_fwd(int dtype, const void* X, const void* W, const int32_t* nbr, void* Y, int64_t n_in, int64_t n_out,
+                int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  int rc = check_conv_args("st_conv_fwd", dtype, n_in, n_out, K, cin, cout);
+  if (rc != ST_OK) return rc;
+  if (n_out == 0) return ST_OK;
+  if (!X && n_in > 0 || !W || !nbr || !Y) {
+    set_error("st_conv_fwd: null pointer");
+    return ST_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (tc_supported(dtype, cin, cout))
+    return tc_conv_gather(dtype, X, W, nbr, Y, n_out, n_in, K, cin, cout, /*w_transposed=*/false, s);
+  StoredMap map{nbr, K};
+  return by_dtype(dtype, [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    return simt_gather<T, StoredMap>(static_cast<const T*>(X), static_cast<const T*>(W), map, static_cast<T*>(Y),
+                                     n_out, n_in, K, cin, cout, false, s);
+  });
+}
+
+int st_conv_dgrad(int dtype, const void* dY, const void* W, const int32_t* inv, void* dX, int64_t n_in, int64_t n_out,
+                  int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  int rc = check_conv_args("st_conv_dgrad", dtype, n_in, n_out, K, cin, cout);
+  if (rc != ST_OK) return rc;
+  if (n_in == 0) return ST_OK;
+  if (!dY && n_out > 0 || !W || !inv || !dX) {
+    set_error("st_conv_dgrad: null pointer");
+    return ST_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (tc_supported(dtype, cout, cin))
+    return tc_conv_gather(dtype, dY, W, inv, dX, n_in, n_out, K, cout, cin, /*w_transposed=*/true, s);
+  StoredMap map{inv, K};
+  return by_dtype(dtype, [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    return simt_gather<T, StoredMap>(static_cast<const T*>(dY), static_cast<const T*>(W), map, static_cast<T*>(dX),
+                                     n_in, n_out, K, cout, cin, true, s);
+  });
+}
+
+int st_conv_wgrad(int dtype, const void* X, const void* dY, const int32_t* nbr, void* dW, int64_t n_in, int64_t n_out,
+                  int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
+  int rc = check_conv_args("st_conv_wgrad", dtype, n_in, n_out, K, cin, cout);
+  if (rc != ST_OK) return rc;
+  if (!dW || (n_out > 0 && (!X || !dY || !nbr))) {
+    set_error("st_conv_wgrad: null pointer");
+    return ST_ERR_ARG;
+  }
+  if (n_out > 0 && (!workspace || workspace_bytes < wgrad_partial_bytes(n_out, K, cin, cout) ||
+                    (reinterpret_cast<uintptr_t>(workspace) & 255))) {
+    set_error("st_conv_wgrad: workspace too small or misaligned");
+    return ST_ERR_WORKSPACE;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  StoredMap map{nbr, K};
+  return by_dtype(dtype, [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    return simt_wgrad<T, StoredMap>(static_cast<const T*>(X), static_cast<const T*>(dY), map, static_cast<T*>(dW),
+                                    static_cast<float*>(workspace), n_out, n_in, K, cin, cout, s);
+  });
+}
+
+int st_conv_fwd_hashfly(int dtype, const void* X, const void* W, const void* out_coords, int coord_dtype,
+                        const int32_t* offsets_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
+                        const int32_t* lookup_shape_host, int lookup_stride, void* Y, int64_t n_in, int64_t n_out,
+                        int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  int rc = check_conv_args("st_conv_fwd_hashfly", dtype, n_in, n_out, K, cin, cout);
+  if (rc != ST_OK) return rc;
+  Offsets off;
+  rc = check_hashfly_args("st_conv_fwd_hashfly", out_coords, coord_dtype, offsets_host, keys, vals, capacity,
+                          lookup_shape_host, lookup_stride, K, n_out, &off);
+  if (rc != ST_OK) return rc;
+  if (n_out == 0) return ST_OK;
+  if (!X && n_in > 0 || !W || !Y) {
+    set_error("st_conv_fwd_hashfly: null pointer");
+    return ST_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  return by_dtype(dtype, [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    if (coord_dtype == ST_I32) {
+      auto map = make_hashfly<int32_t>(out_coords, off, keys, vals, capacity, lookup_shape_host, lookup_stride);
+      return simt_gather<T, HashFlyMap<int32_t>>(static_cast<const T*>(X), static_cast<const T*>(W), map,
+                                                 static_cast<T*>(Y), n_out, n_in, K, cin, cout, false, s);
+    }
+    auto map = make_hashfly<int16_t>(out_coords, off, keys, vals, capacity, lookup_shape_host, lookup_stride);
+    return simt_gather<T, HashFlyMap<int16_t>>(static_cast<const T*>(X), static_cast<const T*>(W), map,
+                                               static_cast<T*>(Y), n_out, n_in, K, cin, cout, false, s);
+  });
+}
+
+int st_conv_dgrad_hashfly(int dtype, const void* dY, const void* W, const void* out_coords, int coord_dtype,
+                          const int32_t* offsets_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
+                          const int32_t* lookup_shape_host, int lookup_stride, void* dX, int64_t n_in, int64_t n_out,
+                          int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
+  int rc = check_conv_args("st_conv_dgrad_hashfly", dtype, n_in, n_out, K, cin, cout);
+  if (rc != ST_OK) return rc;
+  Offsets off;
+  rc = check_hashfly_args("st_conv_dgrad_hashfly", out_coords, coord_dtype, offsets_host, keys, vals, capacity,
+                          lookup_shape_host, lookup_stride, K, n_out, &off);
+  if (rc != ST_OK) return rc;
+  if (n_in == 0) return ST_OK;
+  if (!dY && n_out > 0 || !W || !dX) {
+    set_error("st_conv_dgrad_hashfly: null pointer");
+    return ST_ERR_ARG;
+  }
+  float* out32 = static_cast<float*>(dX);
+  if (dtype != ST_F32) {
+    if (!workspace || workspace_bytes < align_up(n_in * cin * 4, 256) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255)) {
+      set_error("st_conv_dgrad_hashfly: workspace too small or misaligned");
+      return ST_ERR_WORKSPACE;
+    }
+    out32 = static_cast<float*>(workspace);
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  return by_dtype(dtype, [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    if (coord_dtype == ST_I32) {
+      auto map = make_hashfly<int32_t>(out_coords, off, keys, vals, capacity, lookup_shape_host, lookup_stride);
+      return simt_scatter<T, HashFlyMap<int32_t>>(static_cast<const T*>(dY), static_cast<const T*>(W), map,
+                                                  static_cast<T*>(dX), out32, n_out, n_in, K, cout, cin, s);
+    }
+    auto map = make_hashfly<int16_t>(out_coords, off, keys, vals, capacity, lookup_shape_host, lookup_stride);
+    return simt_scatter<T, HashFlyMap<int16_t>>(static_cast<const T*>(dY), static_cast<const T*>(W), map,
+                                                static_cast<T*>(dX), out32, n_out, n_in, K, cout, cin, s);
+  });
+}
+
+int st_conv_wgrad_hashfly(int dtype, const void* X, const void* dY, const void* out_coords, int coord_dtype,
+                          const int32_t* offsets_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
+                          const int32_t* lookup_shape_host, int lookup_stride, void* dW, int64_t n_in, int64_t n_out,
+                          int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
+  int rc = check_conv_args("st_conv_wgrad_hashfly", dtype, n_in, n_out, K, cin, cout);
+  if (rc != ST_OK) return rc;
+  Offsets off;
+  rc = check_hashfly_args("st_conv_wgrad_hashfly", out_coords, coord_dtype, offsets_host, keys, vals, capacity,
+                          lookup_shape_host, lookup_stride, K, n_out, &off);
+  if (rc != ST_OK) return rc;
+  if (!dW || (n_out > 0 && (!X || !dY))) {
+    set_error("st_conv_wgrad_hashfly: null pointer");
+    return ST_ERR_ARG;
+  }
+  if (n_out > 0 && (!workspace || workspace_bytes < wgrad_partial_bytes(n_out, K, cin, cout) ||
+                    (reinterpret_cast<uintptr_t>(workspace) & 255))) {
+    set_error("st_conv_wgrad_hashfly: workspace too small or misaligned");
+    return ST_ERR_WORKSPACE;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  return by_dtype(dtype, [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    if (coord_dtype == ST_I32) {
+      auto map = make_hashfly<int32_t>(out_coords, off, keys, vals, capacity, lookup_shape_host, lookup_stride);
+      return simt_wgrad<T, HashFlyMap<int32_t>>(static_cast<const T*>(X), static_cast<const T*>(dY), map,
+                                                static_cast<T*>(dW), static_cast<float*>(workspace), n_out, n_in, K,
+                                                cin, cout, s);
+    }
+    auto map = make_hashfly<int16_t>(out_coords, off, keys, vals, capacity, lookup_shape_host, lookup_stride);
+    return simt_wgrad<T, HashFlyMap<int16_t>>(static_cast<const T*>(X), static_cast<const T*>(dY), map,
+                                              static_cast<T*>(dW), static_cast<float*>(workspace), n_out, n_in, K, cin,
+                                              cout, s);
+  });
+}
+
+}  // extern "C"

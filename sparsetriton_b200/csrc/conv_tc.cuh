@@ -1,0 +1,19 @@
+// Tensor-core (tcgen05 / TMEM) implicit-GEMM convolution kernels: host-side interface.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace st {
+
+// True if the tcgen05 gather kernel handles a product with c_red reduction channels and c_acc
+// accumulator (output) channels in this dtype.
+bool tc_supported(int dtype, int c_red, int c_acc);
+
+// OUT[r,:] = sum_k IN[map[r,k],:] . B_k over a stored (n_rows, K) map.
+//   w_transposed = false: B_k = W[k]   with W (K, c_red, c_acc)   (forward)
+//   w_transposed = true : B_k = W[k]^T with W (K, c_acc, c_red)   (dgrad over the inverse map)
+int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
+                   int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream);
+
+}  // namespace st

@@ -1,0 +1,131 @@
+// Coordinate hash table: clear, build (insert) and query.
+//
+// Open addressing with linear probing over two arrays (keys int64, vals int32).  The key is the
+// exact packed coordinate, so two different coordinates never alias.  One thread serves one
+// coordinate; its probe sequence walks consecutive slots, i.e. stays inside one or two 32-byte
+// sectors of the key array for the load factors used (<= 0.67).
+#include "common.cuh"
+
+namespace st {
+
+constexpr int kThreads = 256;
+
+__global__ void __launch_bounds__(kThreads)
+hash_clear_kernel(unsigned long long* keys, int32_t* vals, int64_t capacity) {
+  // two slots per thread so that key stores are 16 bytes wide
+  int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) * 2;
+  if (i + 1 < capacity && (reinterpret_cast<uintptr_t>(keys) & 15) == 0) {
+    reinterpret_cast<ulonglong2*>(keys)[i >> 1] = make_ulonglong2(kEmptyKey, kEmptyKey);
+    vals[i] = -1;
+    vals[i + 1] = -1;
+  } else {
+    for (int64_t j = i; j < capacity && j < i + 2; ++j) {
+      keys[j] = kEmptyKey;
+      vals[j] = -1;
+    }
+  }
+}
+
+template <typename CT>
+__global__ void __launch_bounds__(kThreads)
+hash_build_kernel(const CT* __restrict__ coords, int64_t n, unsigned long long* keys, int32_t* vals,
+                  uint32_t capacity, uint32_t mask, int32_t* status) {
+  int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i >= n) return;
+  int4 c = load_coord<CT>(coords, i);
+  unsigned long long key = pack_key(c.x, c.y, c.z, c.w);
+  uint32_t slot = home_slot(key, capacity, mask);
+  for (uint32_t step = 0; step < capacity; ++step) {
+    unsigned long long seen = keys[slot];
+    if (seen == kEmptyKey) seen = atomicCAS(keys + slot, kEmptyKey, key);
+    if (seen == kEmptyKey || seen == key) {
+      atomicMax(vals + slot, (int32_t)i);  // repeated coordinate: largest row stays
+      return;
+    }
+    slot = next_slot(slot, capacity);
+  }
+  atomicOr(status, ST_DEV_TABLE_FULL);
+}
+
+template <typename CT>
+__global__ void __launch_bounds__(kThreads)
+hash_query_kernel(const CT* __restrict__ coords, int64_t m, Table table, int32_t* __restrict__ out) {
+  int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i >= m) return;
+  int4 c = load_coord<CT>(coords, i);
+  int32_t r = -1;
+  if (table.capacity != 0 && key_representable(c.x, c.y, c.z, c.w))
+    r = table_find(table, pack_key(c.x, c.y, c.z, c.w));
+  out[i] = r;
+}
+
+}  // namespace st
+
+using namespace st;
+
+extern "C" {
+
+int st_hash_clear(int64_t* keys, int32_t* vals, int64_t capacity, void* stream) {
+  if (capacity < 0 || (capacity > 0 && (!keys || !vals))) {
+    set_error("st_hash_clear: bad arguments");
+    return ST_ERR_ARG;
+  }
+  if (capacity == 0) return ST_OK;
+  int64_t threads = (capacity + 1) / 2;
+  hash_clear_kernel<<<(unsigned)((threads + kThreads - 1) / kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<unsigned long long*>(keys), vals, capacity);
+  return check_launch("st_hash_clear");
+}
+
+int st_hash_build(const void* coords, int64_t n, int coord_dtype, int64_t* keys, int32_t* vals, int64_t capacity,
+                  int32_t* status, void* stream) {
+  if (n < 0 || capacity < 0 || capacity > 0x7FFFFFFFll || n > 0x7FFFFFFFll || !status ||
+      (n > 0 && (!coords || !keys || !vals))) {
+    set_error("st_hash_build: bad arguments");
+    return ST_ERR_ARG;
+  }
+  if (n == 0) return ST_OK;
+  if (capacity < n) {
+    set_error("st_hash_build: capacity %lld < number of keys %lld", (long long)capacity, (long long)n);
+    return ST_ERR_ARG;
+  }
+  Table t = make_table(keys, vals, capacity);
+  unsigned grid = (unsigned)((n + kThreads - 1) / kThreads);
+  auto* k = reinterpret_cast<unsigned long long*>(keys);
+  if (coord_dtype == ST_I32)
+    hash_build_kernel<int32_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+        static_cast<const int32_t*>(coords), n, k, vals, t.capacity, t.mask, status);
+  else if (coord_dtype == ST_I16)
+    hash_build_kernel<int16_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+        static_cast<const int16_t*>(coords), n, k, vals, t.capacity, t.mask, status);
+  else {
+    set_error("st_hash_build: unknown coordinate dtype %d", coord_dtype);
+    return ST_ERR_DTYPE;
+  }
+  return check_launch("st_hash_build");
+}
+
+int st_hash_query(const void* coords, int64_t m, int coord_dtype, const int64_t* keys, const int32_t* vals,
+                  int64_t capacity, int32_t* out, void* stream) {
+  if (m < 0 || capacity < 0 || capacity > 0x7FFFFFFFll || (m > 0 && (!coords || !out)) ||
+      (capacity > 0 && (!keys || !vals))) {
+    set_error("st_hash_query: bad arguments");
+    return ST_ERR_ARG;
+  }
+  if (m == 0) return ST_OK;
+  Table t = make_table(keys, vals, capacity);
+  unsigned grid = (unsigned)((m + kThreads - 1) / kThreads);
+  if (coord_dtype == ST_I32)
+    hash_query_kernel<int32_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(static_cast<const int32_t*>(coords), m,
+                                                                           t, out);
+  else if (coord_dtype == ST_I16)
+    hash_query_kernel<int16_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(static_cast<const int16_t*>(coords), m,
+                                                                           t, out);
+  else {
+    set_error("st_hash_query: unknown coordinate dtype %d", coord_dtype);
+    return ST_ERR_DTYPE;
+  }
+  return check_launch("st_hash_query");
+}
+
+}  // extern "C"

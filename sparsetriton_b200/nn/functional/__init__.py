@@ -1,0 +1,6 @@
+"""Functional API (reference: sparsetriton/nn/functional/__init__.py)."""
+from . import conv
+from .conv import sparse_conv3d
+from .norm import sparse_batch_norm
+
+__all__ = ["conv", "sparse_conv3d", "sparse_batch_norm"]

@@ -1,0 +1,92 @@
+"""Hash-on-the-fly form of the convolution: autograd Function over the C ABI.
+
+Reference: nn/functional/conv/funcs/implicit_hashfly_gemm.py:330-452
+(ConvHashOnTheFlyImplicitGEMM).  Same call signature and return values:
+
+    out = ConvHashOnTheFlyImplicitGEMM.apply(features, weights, coords, kernel_offsets,
+                                             hash_table_keys, hash_table_vals,
+                                             spatial_shape, lookup_stride)
+    backward -> (d_features, d_weights, None, None, None, None, None, None)
+
+No neighbour map is stored: every tile of every kernel recomputes
+    curr = out * lookup_stride - kernel_offsets[k],
+drops it when outside [0, spatial_shape) and probes the hash table (int64 exact keys, int32 rows).
+dgrad scatter-accumulates into an fp32 buffer; wgrad reduces fp32 partials in a fixed order.
+The weight-gradient kernel of the reference omits the upper bound check (:308); the full check is
+applied here in all three products.
+"""
+import torch
+
+from sparsetriton_b200 import _lib
+
+__all__ = ["ConvHashOnTheFlyImplicitGEMM"]
+
+
+def _host_offsets(kernel_offsets):
+    host = getattr(kernel_offsets, "_st_host", None)
+    if host is None:
+        host = [int(v) for v in kernel_offsets.reshape(-1).tolist()]
+    return _lib.host_i32(host)
+
+
+class ConvHashOnTheFlyImplicitGEMM(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, features, weights, coords, kernel_offsets, hash_table_keys, hash_table_vals, spatial_shape,
+                lookup_stride):
+        _lib.require_cuda(features, "ConvHashOnTheFlyImplicitGEMM")
+        n_in, c_in = features.shape
+        K, w_cin, c_out = weights.shape
+        assert w_cin == c_in, f"weights expect {w_cin} input channels, features have {c_in}"
+        assert kernel_offsets.shape[0] == K, "kernel_offsets must be (K, 3)"
+        if hash_table_keys.dtype != torch.int64 or hash_table_vals.dtype != torch.int32:
+            raise TypeError("hash table must hold int64 keys and int32 values")
+        n_out = coords.shape[0]
+        x = features.contiguous()
+        w = weights.to(x.dtype).contiguous()
+        c = coords.contiguous()
+        keys, vals = hash_table_keys.contiguous(), hash_table_vals.contiguous()
+        ctx.offsets_h = _host_offsets(kernel_offsets)
+        ctx.shape_h = _lib.host_i32(int(v) for v in spatial_shape)
+        ctx.lookup_stride = int(lookup_stride)
+        ctx.w_dtype = weights.dtype
+        code = _lib.feat_code(x)
+        y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
+        if n_out > 0:
+            with torch.cuda.device(x.device):
+                rc = _lib.lib().st_conv_fwd_hashfly(
+                    code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(c), _lib.coord_code(c), ctx.offsets_h, _lib.ptr(keys),
+                    _lib.ptr(vals), keys.shape[0], ctx.shape_h, ctx.lookup_stride, _lib.ptr(y), n_in, n_out, K, c_in,
+                    c_out, None, 0, _lib.stream_ptr())
+            _lib.check(rc, "st_conv_fwd_hashfly")
+        ctx.save_for_backward(x, w, c, keys, vals)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, w, c, keys, vals = ctx.saved_tensors
+        n_in, c_in = x.shape
+        K, _, c_out = w.shape
+        n_out = c.shape[0]
+        dy = grad_output.to(x.dtype).contiguous()
+        code, ccode = _lib.feat_code(x), _lib.coord_code(c)
+        L = _lib.lib()
+        dx = dw = None
+        with torch.cuda.device(x.device):
+            stream = _lib.stream_ptr()
+            ws = _lib.workspace(L.st_conv_hashfly_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
+            if ctx.needs_input_grad[0]:
+                dx = torch.empty_like(x)
+                rc = L.st_conv_dgrad_hashfly(
+                    code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(c), ccode, ctx.offsets_h, _lib.ptr(keys), _lib.ptr(vals),
+                    keys.shape[0], ctx.shape_h, ctx.lookup_stride, _lib.ptr(dx), n_in, n_out, K, c_in, c_out,
+                    _lib.ptr(ws), ws.numel(), stream)
+                _lib.check(rc, "st_conv_dgrad_hashfly")
+            if ctx.needs_input_grad[1]:
+                dw = torch.empty_like(w)
+                rc = L.st_conv_wgrad_hashfly(
+                    code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(c), ccode, ctx.offsets_h, _lib.ptr(keys), _lib.ptr(vals),
+                    keys.shape[0], ctx.shape_h, ctx.lookup_stride, _lib.ptr(dw), n_in, n_out, K, c_in, c_out,
+                    _lib.ptr(ws), ws.numel(), stream)
+                _lib.check(rc, "st_conv_wgrad_hashfly")
+                dw = dw.to(ctx.w_dtype)
+        return dx, dw, None, None, None, None, None, None

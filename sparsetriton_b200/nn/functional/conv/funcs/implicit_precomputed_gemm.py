@@ -1,0 +1,88 @@
+"""Stored-map form of the convolution: autograd Function over the C ABI.
+
+Reference: nn/functional/conv/funcs/implicit_precomputed_gemm.py:233-324
+(ConvPrecomputedNeighborGEMM).  Same call signature and return values:
+
+    out = ConvPrecomputedNeighborGEMM.apply(features, weights, neighbor_indices)
+    backward -> (d_features, d_weights, None)
+
+Forward   Y[o]  = sum_k X[nbr[o,k]] . W[k]                 st_conv_fwd
+dgrad     dX[i] = sum_k dY[inv[i,k]] . W[k]^T              st_map_invert + st_conv_dgrad
+wgrad     dW[k] = sum_o X[nbr[o,k]]^T . dY[o]              st_conv_wgrad
+All three accumulate in fp32 and run without atomics, so results are reproducible run to run
+(the reference scatters dX and dW with atomic adds in the storage dtype).
+"""
+import torch
+
+from sparsetriton_b200 import _lib
+
+__all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map"]
+
+
+def inverse_map(neighbor_indices, n_in):
+    """inv (n_in, K) with inv[nbr[o,k], k] = o.  Memoised on the map tensor: layers that share a
+    neighbour map share its inverse."""
+    cached = getattr(neighbor_indices, "_st_inverse", None)
+    if cached is not None and cached.shape[0] == n_in:
+        return cached
+    n_out, K = neighbor_indices.shape
+    inv = torch.empty((n_in, K), dtype=torch.int32, device=neighbor_indices.device)
+    with torch.cuda.device(neighbor_indices.device):
+        rc = _lib.lib().st_map_invert(_lib.ptr(neighbor_indices), n_out, K, n_in, _lib.ptr(inv), _lib.stream_ptr())
+    _lib.check(rc, "st_map_invert")
+    neighbor_indices._st_inverse = inv
+    return inv
+
+
+class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, features, weights, neighbor_indices):
+        _lib.require_cuda(features, "ConvPrecomputedNeighborGEMM")
+        n_in, c_in = features.shape
+        K, w_cin, c_out = weights.shape
+        assert w_cin == c_in, f"weights expect {w_cin} input channels, features have {c_in}"
+        n_out = neighbor_indices.shape[0]
+        assert neighbor_indices.shape[1] == K, "neighbor_indices must be (N_out, K)"
+
+        x = features.contiguous()
+        w = weights.to(x.dtype).contiguous()
+        nbr = neighbor_indices if neighbor_indices.is_contiguous() else neighbor_indices.contiguous()
+        assert nbr.dtype == torch.int32, "neighbor_indices must be int32"
+        code = _lib.feat_code(x)
+        y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
+        if n_out > 0:
+            with torch.cuda.device(x.device):
+                rc = _lib.lib().st_conv_fwd(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), _lib.ptr(y), n_in, n_out,
+                                            K, c_in, c_out, None, 0, _lib.stream_ptr())
+            _lib.check(rc, "st_conv_fwd")
+        ctx.save_for_backward(x, w, nbr)
+        ctx.w_dtype = weights.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, w, nbr = ctx.saved_tensors
+        n_in, c_in = x.shape
+        K, _, c_out = w.shape
+        n_out = nbr.shape[0]
+        dy = grad_output.to(x.dtype).contiguous()
+        code = _lib.feat_code(x)
+        L = _lib.lib()
+        dx = dw = None
+        with torch.cuda.device(x.device):
+            stream = _lib.stream_ptr()
+            if ctx.needs_input_grad[0]:
+                dx = torch.empty_like(x)
+                if n_in > 0:
+                    inv = inverse_map(nbr, n_in)
+                    rc = L.st_conv_dgrad(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv), _lib.ptr(dx), n_in, n_out, K,
+                                         c_in, c_out, None, 0, stream)
+                    _lib.check(rc, "st_conv_dgrad")
+            if ctx.needs_input_grad[1]:
+                dw = torch.empty_like(w)
+                ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
+                rc = L.st_conv_wgrad(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), _lib.ptr(dw), n_in, n_out, K,
+                                     c_in, c_out, _lib.ptr(ws), ws.numel(), stream)
+                _lib.check(rc, "st_conv_wgrad")
+                dw = dw.to(ctx.w_dtype)
+        return dx, dw, None

@@ -58,6 +58,8 @@ extern "C" {
 int st_version(void);
 /* Text of the last host-side error of the calling thread. */
 const char* st_last_error_string(void);
+/* Number of kernels this library has enqueued in this process so far. */
+long long st_launch_count(void);
 /* 1 if the tcgen05 (tensor-core) kernels can serve this conv shape, else 0 (SIMT kernels used). */
 int st_conv_uses_tensor_cores(int dtype, int cin, int cout);
 

@@ -22,7 +22,7 @@ _lib = None
 def build(force=False):
     """Compile oracle.c with gcc + OpenMP into liboracle.so next to it."""
     if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(_SRC):
-        subprocess.check_call(["gcc", "-O3", "-march=native", "-fopenmp", "-shared", "-fPIC", _SRC, "-o", _SO])
+        subprocess.check_call(["gcc", "-O3", "-march=x86-64-v3", "-fopenmp", "-shared", "-fPIC", _SRC, "-o", _SO])
     return _SO
 
 

@@ -26,6 +26,7 @@ _I64, _INT, _PTR = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
 _SIGNATURES = {
     "st_version": ([], _INT),
     "st_last_error_string": ([], ctypes.c_char_p),
+    "st_launch_count": ([], ctypes.c_longlong),
     "st_conv_uses_tensor_cores": ([_INT, _INT, _INT], _INT),
     "st_hash_clear": ([_PTR, _PTR, _I64, _PTR], _INT),
     "st_hash_build": ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR, _PTR], _INT),

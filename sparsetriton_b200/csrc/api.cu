@@ -1,4 +1,5 @@
 // Library-wide plumbing: version, error text, offset packing and a block-hierarchical prefix sum.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -7,6 +8,9 @@
 namespace st {
 
 static thread_local char g_error[512] = "";
+static std::atomic<long long> g_launches{0};
+
+void note_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -95,7 +99,7 @@ int64_t scan_tmp_bytes(int64_t n) {
 int exclusive_scan_u32(const uint32_t* in, uint32_t* out, int64_t n, void* tmp, int64_t* total,
                        cudaStream_t stream) {
   if (n <= 0) {
-    if (total) scan_zero_total_kernel<<<1, 1, 0, stream>>>(total);
+    if (total) { scan_zero_total_kernel<<<1, 1, 0, stream>>>(total); note_launches(1); }
     return check_launch("scan(empty)");
   }
   const int64_t b1 = (n + kScanBlock - 1) / kScanBlock;
@@ -113,16 +117,16 @@ int exclusive_scan_u32(const uint32_t* in, uint32_t* out, int64_t n, void* tmp, 
 
   // in may alias out: keep the last input value for the total
   if (total) cudaMemcpyAsync(last_in, in + (n - 1), 4, cudaMemcpyDeviceToDevice, stream);
-  scan_blocks_kernel<<<(unsigned)b1, kScanBlock, 0, stream>>>(in, out, n, sums1);
+  { scan_blocks_kernel<<<(unsigned)b1, kScanBlock, 0, stream>>>(in, out, n, sums1); note_launches(1); }
   if (b1 > 1) {
-    scan_blocks_kernel<<<(unsigned)b2, kScanBlock, 0, stream>>>(sums1, sums1, b1, sums2);
+    { scan_blocks_kernel<<<(unsigned)b2, kScanBlock, 0, stream>>>(sums1, sums1, b1, sums2); note_launches(1); }
     if (b2 > 1) {
-      scan_blocks_kernel<<<1, kScanBlock, 0, stream>>>(sums2, sums2, b2, nullptr);
-      scan_add_kernel<<<(unsigned)b2, kScanBlock, 0, stream>>>(sums1, b1, sums2);
+      { scan_blocks_kernel<<<1, kScanBlock, 0, stream>>>(sums2, sums2, b2, nullptr); note_launches(1); }
+      { scan_add_kernel<<<(unsigned)b2, kScanBlock, 0, stream>>>(sums1, b1, sums2); note_launches(1); }
     }
-    scan_add_kernel<<<(unsigned)b1, kScanBlock, 0, stream>>>(out, n, sums1);
+    { scan_add_kernel<<<(unsigned)b1, kScanBlock, 0, stream>>>(out, n, sums1); note_launches(1); }
   }
-  if (total) scan_total_kernel<<<1, 1, 0, stream>>>(last_in, out + (n - 1), total);
+  if (total) { scan_total_kernel<<<1, 1, 0, stream>>>(last_in, out + (n - 1), total); note_launches(1); }
   return check_launch("scan");
 }
 
@@ -133,5 +137,7 @@ extern "C" {
 int st_version(void) { return 1; }
 
 const char* st_last_error_string(void) { return st::g_error; }
+
+long long st_launch_count(void) { return st::g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

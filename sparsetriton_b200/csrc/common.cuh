@@ -14,6 +14,8 @@ constexpr unsigned long long kEmptyKey = 0xFFFFFFFFFFFFFFFFull;
 void set_error(const char* fmt, ...);
 // Returns ST_OK or records the pending launch error and returns ST_ERR_CUDA.
 int check_launch(const char* what);
+// Adds n to the process-wide count of kernels this library has enqueued (st_launch_count()).
+void note_launches(int n);
 
 // Kernel offsets travel inside the launch parameters.
 struct Offsets {

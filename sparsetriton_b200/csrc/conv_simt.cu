@@ -245,7 +245,7 @@ int simt_gather(const T* in, const T* w, const Map& map, T* out, int64_t n_rows,
   dim3 grid((unsigned)((n_rows + BM - 1) / BM), (unsigned)((c_acc + BN - 1) / BN));
   // forward: B_k = W[k] (c_red=cin rows, c_acc=cout cols).  dgrad: B_k = W[k]^T, W[k] is (c_acc, c_red).
   int64_t sr = w_transposed ? 1 : c_acc, sa = w_transposed ? c_red : 1;
-  conv_gather_kernel<T, Map><<<grid, kConvThreads, 0, s>>>(in, w, map, out, n_rows, n_src, K, c_red, c_acc, sr, sa);
+  { conv_gather_kernel<T, Map><<<grid, kConvThreads, 0, s>>>(in, w, map, out, n_rows, n_src, K, c_red, c_acc, sr, sa); note_launches(1); }
   return check_launch("conv_gather_kernel");
 }
 
@@ -257,11 +257,11 @@ int simt_scatter(const T* in, const T* w, const Map& map, T* out, float* out32, 
   cudaMemsetAsync(out32, 0, n * sizeof(float), s);
   if (n_rows > 0) {
     dim3 grid((unsigned)((n_rows + BM - 1) / BM), (unsigned)((c_acc + BN - 1) / BN));
-    conv_scatter_kernel<T, Map><<<grid, kConvThreads, 0, s>>>(in, w, map, out32, n_rows, n_dst, K, c_red, c_acc, 1,
-                                                              c_red);
+    { conv_scatter_kernel<T, Map><<<grid, kConvThreads, 0, s>>>(in, w, map, out32, n_rows, n_dst, K, c_red, c_acc, 1,
+                                                              c_red); note_launches(1); }
   }
   if (reinterpret_cast<void*>(out) != reinterpret_cast<void*>(out32))
-    cast_from_f32_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(out32, n, out);
+    { cast_from_f32_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(out32, n, out); note_launches(1); }
   return check_launch("conv_scatter_kernel");
 }
 
@@ -278,9 +278,9 @@ int simt_wgrad(const T* x, const T* dy, const Map& map, T* dw, float* partial, i
   int64_t rows_per_chunk = (n_rows + chunks - 1) / chunks;
   rows_per_chunk = (rows_per_chunk + BK - 1) / BK * BK;
   dim3 grid((unsigned)chunks, (unsigned)K, (unsigned)(((cin + BM - 1) / BM) * ((cout + BN - 1) / BN)));
-  conv_wgrad_kernel<T, Map><<<grid, kConvThreads, 0, s>>>(x, dy, map, partial, n_rows, n_src, K, cin, cout,
-                                                          rows_per_chunk);
-  reduce_partials_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(partial, chunks, n, dw);
+  { conv_wgrad_kernel<T, Map><<<grid, kConvThreads, 0, s>>>(x, dy, map, partial, n_rows, n_src, K, cin, cout,
+                                                          rows_per_chunk); note_launches(1); }
+  { reduce_partials_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(partial, chunks, n, dw); note_launches(1); }
   return check_launch("conv_wgrad_kernel");
 }
 

@@ -72,8 +72,8 @@ int st_hash_clear(int64_t* keys, int32_t* vals, int64_t capacity, void* stream) 
   }
   if (capacity == 0) return ST_OK;
   int64_t threads = (capacity + 1) / 2;
-  hash_clear_kernel<<<(unsigned)((threads + kThreads - 1) / kThreads), kThreads, 0, (cudaStream_t)stream>>>(
-      reinterpret_cast<unsigned long long*>(keys), vals, capacity);
+  { hash_clear_kernel<<<(unsigned)((threads + kThreads - 1) / kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<unsigned long long*>(keys), vals, capacity); note_launches(1); }
   return check_launch("st_hash_clear");
 }
 
@@ -93,11 +93,11 @@ int st_hash_build(const void* coords, int64_t n, int coord_dtype, int64_t* keys,
   unsigned grid = (unsigned)((n + kThreads - 1) / kThreads);
   auto* k = reinterpret_cast<unsigned long long*>(keys);
   if (coord_dtype == ST_I32)
-    hash_build_kernel<int32_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(
-        static_cast<const int32_t*>(coords), n, k, vals, t.capacity, t.mask, status);
+    { hash_build_kernel<int32_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+        static_cast<const int32_t*>(coords), n, k, vals, t.capacity, t.mask, status); note_launches(1); }
   else if (coord_dtype == ST_I16)
-    hash_build_kernel<int16_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(
-        static_cast<const int16_t*>(coords), n, k, vals, t.capacity, t.mask, status);
+    { hash_build_kernel<int16_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(
+        static_cast<const int16_t*>(coords), n, k, vals, t.capacity, t.mask, status); note_launches(1); }
   else {
     set_error("st_hash_build: unknown coordinate dtype %d", coord_dtype);
     return ST_ERR_DTYPE;
@@ -116,11 +116,11 @@ int st_hash_query(const void* coords, int64_t m, int coord_dtype, const int64_t*
   Table t = make_table(keys, vals, capacity);
   unsigned grid = (unsigned)((m + kThreads - 1) / kThreads);
   if (coord_dtype == ST_I32)
-    hash_query_kernel<int32_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(static_cast<const int32_t*>(coords), m,
-                                                                           t, out);
+    { hash_query_kernel<int32_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(static_cast<const int32_t*>(coords), m,
+                                                                           t, out); note_launches(1); }
   else if (coord_dtype == ST_I16)
-    hash_query_kernel<int16_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(static_cast<const int16_t*>(coords), m,
-                                                                           t, out);
+    { hash_query_kernel<int16_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(static_cast<const int16_t*>(coords), m,
+                                                                           t, out); note_launches(1); }
   else {
     set_error("st_hash_query: unknown coordinate dtype %d", coord_dtype);
     return ST_ERR_DTYPE;

@@ -281,12 +281,12 @@ pairs_write_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, const
 template <typename CT>
 static int outcoords_count_impl(const CT* coords, int64_t n, const Offsets& off, int K, int stride, bool transposed,
                                 Int3 ns, OutCoordsWorkspace& w, int64_t* n_out, int32_t* status, cudaStream_t s) {
-  scratch_clear_kernel<<<(w.capacity + 255) / 256, 256, 0, s>>>(w.keys, w.min_flat, w.capacity);
-  outcoords_insert_kernel<CT><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(coords, w.n_flat, K, off, stride, transposed,
-                                                                      ns, w.keys, w.min_flat, w.capacity, status);
-  outcoords_mark_kernel<CT><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(coords, w.n_flat, K, off, stride, transposed, ns,
+  { scratch_clear_kernel<<<(w.capacity + 255) / 256, 256, 0, s>>>(w.keys, w.min_flat, w.capacity); note_launches(1); }
+  { outcoords_insert_kernel<CT><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(coords, w.n_flat, K, off, stride, transposed,
+                                                                      ns, w.keys, w.min_flat, w.capacity, status); note_launches(1); }
+  { outcoords_mark_kernel<CT><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(coords, w.n_flat, K, off, stride, transposed, ns,
                                                                     w.keys, w.min_flat, w.capacity, w.win_bits,
-                                                                    w.block_counts);
+                                                                    w.block_counts); note_launches(1); }
   int rc = check_launch("st_outcoords_count");
   if (rc != ST_OK) return rc;
   return exclusive_scan_u32(w.block_counts, w.block_counts, w.n_blocks, w.scan_tmp, n_out, s);
@@ -374,13 +374,13 @@ int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int
   if (n == 0) return ST_OK;
   cudaStream_t s = (cudaStream_t)stream;
   if (coord_dtype == ST_I32)
-    outcoords_write_kernel<int32_t><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(
+    { outcoords_write_kernel<int32_t><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(
         static_cast<const int32_t*>(coords), w.n_flat, K, off, stride, transposed != 0, ns, w.win_bits,
-        w.block_counts, static_cast<int32_t*>(out_coords), out_capacity, status);
+        w.block_counts, static_cast<int32_t*>(out_coords), out_capacity, status); note_launches(1); }
   else
-    outcoords_write_kernel<int16_t><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(
+    { outcoords_write_kernel<int16_t><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(
         static_cast<const int16_t*>(coords), w.n_flat, K, off, stride, transposed != 0, ns, w.win_bits,
-        w.block_counts, static_cast<int16_t*>(out_coords), out_capacity, status);
+        w.block_counts, static_cast<int16_t*>(out_coords), out_capacity, status); note_launches(1); }
   return check_launch("st_outcoords_write");
 }
 
@@ -405,11 +405,11 @@ int st_map_build(const void* out_coords, int64_t n_out, int coord_dtype, const i
   unsigned grid = (unsigned)((n_flat + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
   if (coord_dtype == ST_I32)
-    map_build_kernel<int32_t><<<grid, 256, 0, s>>>(static_cast<const int32_t*>(out_coords), n_flat, K, off,
-                                                   lookup_stride, shape, t, nbr);
+    { map_build_kernel<int32_t><<<grid, 256, 0, s>>>(static_cast<const int32_t*>(out_coords), n_flat, K, off,
+                                                   lookup_stride, shape, t, nbr); note_launches(1); }
   else if (coord_dtype == ST_I16)
-    map_build_kernel<int16_t><<<grid, 256, 0, s>>>(static_cast<const int16_t*>(out_coords), n_flat, K, off,
-                                                   lookup_stride, shape, t, nbr);
+    { map_build_kernel<int16_t><<<grid, 256, 0, s>>>(static_cast<const int16_t*>(out_coords), n_flat, K, off,
+                                                   lookup_stride, shape, t, nbr); note_launches(1); }
   else {
     set_error("st_map_build: unknown coordinate dtype %d", coord_dtype);
     return ST_ERR_DTYPE;
@@ -424,10 +424,10 @@ int st_map_invert(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, int32_
   }
   cudaStream_t s = (cudaStream_t)stream;
   int64_t n_inv = n_in * K;
-  if (n_inv > 0) fill_i32_kernel<<<(unsigned)((n_inv + 255) / 256), 256, 0, s>>>(inv, n_inv, -1);
+  if (n_inv > 0) { fill_i32_kernel<<<(unsigned)((n_inv + 255) / 256), 256, 0, s>>>(inv, n_inv, -1); note_launches(1); }
   int64_t n_flat = n_out * K;
   if (n_flat > 0 && n_in > 0)
-    map_invert_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, s>>>(nbr, n_flat, K, n_in, inv);
+    { map_invert_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, s>>>(nbr, n_flat, K, n_in, inv); note_launches(1); }
   return check_launch("st_map_invert");
 }
 
@@ -453,7 +453,7 @@ int st_map_pairs_count(const int32_t* nbr, int64_t n_out, int K, void* workspace
   int64_t n_blocks = (n_flat + kBlock - 1) / kBlock;
   uint32_t* counts = static_cast<uint32_t*>(workspace);
   void* tmp = static_cast<char*>(workspace) + align_up(n_blocks * 4, 256);
-  pairs_count_kernel<<<(unsigned)n_blocks, kBlock, 0, s>>>(nbr, n_flat, counts);
+  { pairs_count_kernel<<<(unsigned)n_blocks, kBlock, 0, s>>>(nbr, n_flat, counts); note_launches(1); }
   int rc = check_launch("st_map_pairs_count");
   if (rc != ST_OK) return rc;
   return exclusive_scan_u32(counts, counts, n_blocks, tmp, n_pairs, s);
@@ -473,8 +473,8 @@ int st_map_pairs_write(const int32_t* nbr, int64_t n_out, int K, void* workspace
     return ST_ERR_WORKSPACE;
   }
   int64_t n_blocks = (n_flat + kBlock - 1) / kBlock;
-  pairs_write_kernel<<<(unsigned)n_blocks, kBlock, 0, (cudaStream_t)stream>>>(
-      nbr, n_flat, K, static_cast<const uint32_t*>(workspace), triples, capacity, status);
+  { pairs_write_kernel<<<(unsigned)n_blocks, kBlock, 0, (cudaStream_t)stream>>>(
+      nbr, n_flat, K, static_cast<const uint32_t*>(workspace), triples, capacity, status); note_launches(1); }
   return check_launch("st_map_pairs_write");
 }
 

@@ -8,7 +8,7 @@ from typing import Tuple, Union
 
 import torch
 
-from sparsetriton_b200 import _lib
+from sparsetriton_b200 import _lib, trace
 from sparsetriton_b200.config import ConvAlgo, get_conv_algo, get_h_table_f
 from sparsetriton_b200.tensor import SparseTensor
 from sparsetriton_b200.utils.hash import HashTable, round_up_capacity
@@ -48,7 +48,7 @@ def compute_neighbor_indices(
     host = getattr(kernel_offsets, "_st_host", None)
     if host is None:
         host = kernel_offsets.reshape(-1).tolist()
-    with torch.cuda.device(device):
+    with torch.cuda.device(device), trace.stage("map_build", 1):
         rc = _lib.lib().st_map_build(_lib.ptr(coords), n_out, _lib.coord_code(coords), _lib.host_i32(host), K,
                                      int(stride), _lib.host_i32(int(v) for v in spatial_shape), _lib.ptr(keys),
                                      _lib.ptr(vals), keys.shape[0], _lib.ptr(nbr), _lib.stream_ptr())

@@ -17,7 +17,7 @@ applied here in all three products.
 """
 import torch
 
-from sparsetriton_b200 import _lib
+from sparsetriton_b200 import _lib, trace
 
 __all__ = ["ConvHashOnTheFlyImplicitGEMM"]
 
@@ -52,7 +52,7 @@ class ConvHashOnTheFlyImplicitGEMM(torch.autograd.Function):
         code = _lib.feat_code(x)
         y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
         if n_out > 0:
-            with torch.cuda.device(x.device):
+            with torch.cuda.device(x.device), trace.stage("conv_fwd_hashfly", 1):
                 rc = _lib.lib().st_conv_fwd_hashfly(
                     code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(c), _lib.coord_code(c), ctx.offsets_h, _lib.ptr(keys),
                     _lib.ptr(vals), keys.shape[0], ctx.shape_h, ctx.lookup_stride, _lib.ptr(y), n_in, n_out, K, c_in,
@@ -76,17 +76,19 @@ class ConvHashOnTheFlyImplicitGEMM(torch.autograd.Function):
             ws = _lib.workspace(L.st_conv_hashfly_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
             if ctx.needs_input_grad[0]:
                 dx = torch.empty_like(x)
-                rc = L.st_conv_dgrad_hashfly(
-                    code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(c), ccode, ctx.offsets_h, _lib.ptr(keys), _lib.ptr(vals),
-                    keys.shape[0], ctx.shape_h, ctx.lookup_stride, _lib.ptr(dx), n_in, n_out, K, c_in, c_out,
-                    _lib.ptr(ws), ws.numel(), stream)
+                with trace.stage("conv_dgrad_hashfly", 3):
+                    rc = L.st_conv_dgrad_hashfly(
+                        code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(c), ccode, ctx.offsets_h, _lib.ptr(keys),
+                        _lib.ptr(vals), keys.shape[0], ctx.shape_h, ctx.lookup_stride, _lib.ptr(dx), n_in, n_out, K,
+                        c_in, c_out, _lib.ptr(ws), ws.numel(), stream)
                 _lib.check(rc, "st_conv_dgrad_hashfly")
             if ctx.needs_input_grad[1]:
                 dw = torch.empty_like(w)
-                rc = L.st_conv_wgrad_hashfly(
-                    code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(c), ccode, ctx.offsets_h, _lib.ptr(keys), _lib.ptr(vals),
-                    keys.shape[0], ctx.shape_h, ctx.lookup_stride, _lib.ptr(dw), n_in, n_out, K, c_in, c_out,
-                    _lib.ptr(ws), ws.numel(), stream)
+                with trace.stage("conv_wgrad_hashfly", 2):
+                    rc = L.st_conv_wgrad_hashfly(
+                        code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(c), ccode, ctx.offsets_h, _lib.ptr(keys),
+                        _lib.ptr(vals), keys.shape[0], ctx.shape_h, ctx.lookup_stride, _lib.ptr(dw), n_in, n_out, K,
+                        c_in, c_out, _lib.ptr(ws), ws.numel(), stream)
                 _lib.check(rc, "st_conv_wgrad_hashfly")
                 dw = dw.to(ctx.w_dtype)
         return dx, dw, None, None, None, None, None, None

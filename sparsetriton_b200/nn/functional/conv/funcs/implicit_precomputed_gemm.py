@@ -14,7 +14,7 @@ All three accumulate in fp32 and run without atomics, so results are reproducibl
 """
 import torch
 
-from sparsetriton_b200 import _lib
+from sparsetriton_b200 import _lib, trace
 
 __all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map"]
 
@@ -27,7 +27,7 @@ def inverse_map(neighbor_indices, n_in):
         return cached
     n_out, K = neighbor_indices.shape
     inv = torch.empty((n_in, K), dtype=torch.int32, device=neighbor_indices.device)
-    with torch.cuda.device(neighbor_indices.device):
+    with torch.cuda.device(neighbor_indices.device), trace.stage("map_invert", 2):
         rc = _lib.lib().st_map_invert(_lib.ptr(neighbor_indices), n_out, K, n_in, _lib.ptr(inv), _lib.stream_ptr())
     _lib.check(rc, "st_map_invert")
     neighbor_indices._st_inverse = inv
@@ -51,7 +51,7 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         code = _lib.feat_code(x)
         y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
         if n_out > 0:
-            with torch.cuda.device(x.device):
+            with torch.cuda.device(x.device), trace.stage("conv_fwd", 1):
                 rc = _lib.lib().st_conv_fwd(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), _lib.ptr(y), n_in, n_out,
                                             K, c_in, c_out, None, 0, _lib.stream_ptr())
             _lib.check(rc, "st_conv_fwd")
@@ -75,14 +75,16 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
                 dx = torch.empty_like(x)
                 if n_in > 0:
                     inv = inverse_map(nbr, n_in)
-                    rc = L.st_conv_dgrad(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv), _lib.ptr(dx), n_in, n_out, K,
-                                         c_in, c_out, None, 0, stream)
+                    with trace.stage("conv_dgrad", 1):
+                        rc = L.st_conv_dgrad(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv), _lib.ptr(dx), n_in, n_out,
+                                             K, c_in, c_out, None, 0, stream)
                     _lib.check(rc, "st_conv_dgrad")
             if ctx.needs_input_grad[1]:
                 dw = torch.empty_like(w)
                 ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
-                rc = L.st_conv_wgrad(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), _lib.ptr(dw), n_in, n_out, K,
-                                     c_in, c_out, _lib.ptr(ws), ws.numel(), stream)
+                with trace.stage("conv_wgrad", 2):
+                    rc = L.st_conv_wgrad(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), _lib.ptr(dw), n_in, n_out, K,
+                                         c_in, c_out, _lib.ptr(ws), ws.numel(), stream)
                 _lib.check(rc, "st_conv_wgrad")
                 dw = dw.to(ctx.w_dtype)
         return dx, dw, None

@@ -18,7 +18,7 @@ from typing import Tuple
 
 import torch
 
-from sparsetriton_b200 import _lib
+from sparsetriton_b200 import _lib, trace
 
 __all__ = ["build_out_coords", "kernel_offsets", "output_shape"]
 
@@ -91,7 +91,8 @@ def build_out_coords(
     ws = _lib.workspace(ws_bytes, device)
     counters = torch.zeros(2, dtype=torch.int64, device=device)      # [n_out, status]
     status = counters[1:].view(torch.int32)
-    with torch.cuda.device(device):
+    # clear + insert + mark + (<= 6) scan kernels, then the write kernel
+    with torch.cuda.device(device), trace.stage("out_coords", 10):
         stream = _lib.stream_ptr()
         rc = L.st_outcoords_count(_lib.ptr(coords), n, code, off_h, K, stride, int(transposed), shape_h,
                                   _lib.ptr(ws), ws.numel(), _lib.ptr(counters), _lib.ptr(status), stream)

@@ -1,0 +1,64 @@
+"""Per-stage device timing of the hot path.
+
+    with trace.recording() as rec:
+        ... run convolutions ...
+    rec.summary()  -> {stage: {"calls": n, "ms": total, "launches": n_kernels}}
+
+Each C-ABI call site is wrapped in `trace.stage(name)`.  When no recording is active the wrapper
+does nothing; when one is, it brackets the call with CUDA events on the current stream (the stream
+the kernels are launched on) and reads the library's own launch counter before and after, so
+"launches" is the number of kernels the library really enqueued.
+"""
+import contextlib
+
+import torch
+
+from sparsetriton_b200 import _lib
+
+_active = None
+
+
+class Recording:
+    def __init__(self):
+        self.spans = []          # (name, start_event, end_event, launches)
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b, launches in self.spans:
+            e = out.setdefault(name, {"calls": 0, "ms": 0.0, "launches": 0})
+            e["calls"] += 1
+            e["ms"] += a.elapsed_time(b)
+            e["launches"] += launches
+        return out
+
+    def total_launches(self):
+        return sum(s[3] for s in self.spans)
+
+
+@contextlib.contextmanager
+def recording():
+    global _active
+    prev, _active = _active, Recording()
+    try:
+        yield _active
+    finally:
+        _active = prev
+
+
+@contextlib.contextmanager
+def stage(name, launches=None):
+    rec = _active
+    if rec is None:
+        yield
+        return
+    counter = _lib.lib().st_launch_count
+    a = torch.cuda.Event(enable_timing=True)
+    b = torch.cuda.Event(enable_timing=True)
+    before = counter()
+    a.record()
+    try:
+        yield
+    finally:
+        b.record()
+        rec.spans.append((name, a, b, counter() - before))

@@ -13,7 +13,7 @@ keeps its largest row index.
 """
 import torch
 
-from sparsetriton_b200 import _lib
+from sparsetriton_b200 import _lib, trace
 from sparsetriton_b200.config import get_coords_dtype
 
 __all__ = ["HashTable", "flatten_coord", "hash_coords", "unflatten_coord"]
@@ -58,7 +58,7 @@ class HashTable:
         if dev.type == "cuda" and capacity > 0:
             self.table_keys = torch.empty((capacity,), dtype=torch.int64, device=dev)
             self.table_values = torch.empty((capacity,), dtype=torch.int32, device=dev)
-            with torch.cuda.device(self.table_keys.device):
+            with torch.cuda.device(self.table_keys.device), trace.stage("hash_clear", 1):
                 rc = _lib.lib().st_hash_clear(_lib.ptr(self.table_keys), _lib.ptr(self.table_values), capacity,
                                               _lib.stream_ptr())
             _lib.check(rc, "st_hash_clear")
@@ -105,7 +105,7 @@ class HashTable:
             return
         coords = self._kernel_ready(keys, "HashTable.insert")
         status = torch.zeros(1, dtype=torch.int32, device=coords.device)
-        with torch.cuda.device(coords.device):
+        with torch.cuda.device(coords.device), trace.stage("hash_build", 1):
             rc = _lib.lib().st_hash_build(_lib.ptr(coords), coords.shape[0], _lib.coord_code(coords),
                                           _lib.ptr(self.table_keys), _lib.ptr(self.table_values), self.capacity,
                                           _lib.ptr(status), _lib.stream_ptr())
@@ -118,7 +118,7 @@ class HashTable:
             return torch.empty((0,), dtype=torch.int32, device=self.device)
         coords = self._kernel_ready(keys, "HashTable.query")
         out = torch.empty((n,), dtype=torch.int32, device=coords.device)
-        with torch.cuda.device(coords.device):
+        with torch.cuda.device(coords.device), trace.stage("hash_query", 1):
             rc = _lib.lib().st_hash_query(_lib.ptr(coords), n, _lib.coord_code(coords), _lib.ptr(self.table_keys),
                                           _lib.ptr(self.table_values), self.capacity, _lib.ptr(out),
                                           _lib.stream_ptr())

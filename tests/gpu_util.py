@@ -1,0 +1,63 @@
+"""Helpers shared by the GPU parity tests."""
+import numpy as np
+import torch
+
+import sparsetriton_b200 as st
+from sparsetriton_b200 import _lib
+from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype
+from sparsetriton_b200.nn.functional import sparse_conv3d
+
+TOL = {torch.float32: 2e-3, torch.float16: 1e-2, torch.bfloat16: 1e-2}
+
+
+def rel_err(got, want):
+    """max |got - want| / max |want|  (max-norm relative error)."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    denom = max(float(np.abs(want).max()) if want.size else 0.0, 1e-30)
+    return float(np.abs(got - want).max()) / denom if want.size else 0.0
+
+
+def t2n(t):
+    return t.detach().float().cpu().numpy() if t.is_floating_point() else t.detach().cpu().numpy()
+
+
+def run_conv(dev, coords, shape, batch, feats, weight, bias, dy, k, s, p, d, transposed, subm, algo,
+             coord_dtype=torch.int32, dtype=torch.float32):
+    """sparse_conv3d forward + backward through the public API.  Returns numpy
+    (out_coords, new_shape, y, dx, dw, db)."""
+    set_coords_dtype(coord_dtype)
+    set_conv_algo(algo)
+    x = torch.as_tensor(feats).to(dev, dtype).requires_grad_(True)
+    w = torch.as_tensor(weight).to(dev, dtype).requires_grad_(True)
+    b = None
+    if bias is not None and np.size(bias):
+        b = torch.as_tensor(bias).to(dev, dtype).requires_grad_(True)
+    sp = st.SparseTensor(x, torch.as_tensor(coords).to(dev), spatial_shape=tuple(int(v) for v in shape),
+                         batch_size=int(batch))
+    out = sparse_conv3d(sp, w, kernel_size=k, bias=b, stride=s, dilation=d, padding=p, transposed=transposed,
+                        submanifold=subm)
+    g = torch.as_tensor(dy).to(dev, dtype)
+    (out.F.float() * g.float()).sum().backward()
+    return (t2n(out.C).astype(np.int32), np.array(out.spatial_shape), t2n(out.F), t2n(x.grad), t2n(w.grad),
+            None if b is None else t2n(b.grad))
+
+
+def map_triples(nbr):
+    """(in, out, offset) triples of a device neighbour map via st_map_pairs_* (C ABI)."""
+    L = _lib.lib()
+    n_out, K = nbr.shape
+    dev = nbr.device
+    ws = _lib.workspace(L.st_map_pairs_workspace_bytes(n_out, K), dev)
+    counters = torch.zeros(2, dtype=torch.int64, device=dev)
+    status = counters[1:].view(torch.int32)
+    with torch.cuda.device(dev):
+        s = _lib.stream_ptr()
+        _lib.check(L.st_map_pairs_count(_lib.ptr(nbr), n_out, K, _lib.ptr(ws), ws.numel(), _lib.ptr(counters), s),
+                   "st_map_pairs_count")
+        n_pairs = int(counters[0].item())
+        tri = torch.empty((n_pairs, 3), dtype=torch.int32, device=dev)
+        _lib.check(L.st_map_pairs_write(_lib.ptr(nbr), n_out, K, _lib.ptr(ws), ws.numel(), _lib.ptr(tri), n_pairs,
+                                        _lib.ptr(status), s), "st_map_pairs_write")
+    assert int(counters[1].item()) == 0
+    return tri.cpu().numpy()

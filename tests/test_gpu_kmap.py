@@ -1,0 +1,124 @@
+"""Kernel-map construction on the GPU: ordered output coordinates and (in, out, offset) triples
+must be bit-identical to the reference's golden vectors and to the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import case_id, golden_files, load_golden
+from gpu_util import map_triples
+from sparsetriton_b200 import synthetic
+from sparsetriton_b200.config import set_coords_dtype
+from sparsetriton_b200.nn.functional.conv.conv import compute_neighbor_indices
+from sparsetriton_b200.nn.functional.conv.funcs.implicit_precomputed_gemm import inverse_map
+from sparsetriton_b200.nn.functional.conv.kmap import build_out_coords
+from sparsetriton_b200.utils.hash import HashTable
+
+pytestmark = pytest.mark.gpu
+
+
+def gpu_kernel_map(dev, coords, shape, k, s, d, p, transposed, subm, dtype=torch.int32, factor=2.0):
+    """Same call sequence as sparse_conv3d up to the neighbour map."""
+    set_coords_dtype(dtype)
+    c = torch.as_tensor(coords).to(dev, dtype)
+    if subm:
+        p = ((k - 1) * d) // 2
+    keyc = c.clone()
+    if transposed and s > 1:
+        keyc[:, 1:] *= s
+    table = HashTable(capacity=max(int(c.shape[0] * factor), 1), device=dev)
+    table.insert(keyc)
+    oc, ns, ko = build_out_coords(c, tuple(int(v) for v in shape), k, s, d, p, transposed=transposed,
+                                  submanifold=subm)
+    look = tuple(int(v) * s for v in shape) if (transposed and s > 1) else tuple(int(v) for v in shape)
+    nbr = compute_neighbor_indices(table, oc, ko, look, 1 if transposed else s, p, d)
+    ns = [int(v) for v in (ns.tolist() if isinstance(ns, torch.Tensor) else ns)]
+    return oc, ns, ko, nbr
+
+
+@pytest.mark.parametrize("path", golden_files("kmap_"), ids=case_id)
+def test_golden(cuda_device, oracle, path):
+    g = load_golden(path)
+    dtype = getattr(torch, str(g["coord_dtype"]))
+    oc, ns, ko, nbr = gpu_kernel_map(cuda_device, g["coords"], g["shape"], int(g["k"]), int(g["s"]), int(g["d"]),
+                                     int(g["p"]), bool(g["transposed"]), bool(g["subm"]), dtype)
+    assert oc.dtype == dtype
+    assert np.array_equal(ko.cpu().numpy().astype(np.int32), g["kernel_offsets"])
+    assert ns == g["new_shape"].tolist()
+    assert np.array_equal(oc.cpu().numpy().astype(np.int32), g["out_coords"]), "ordered output coordinates differ"
+    assert np.array_equal(nbr.cpu().numpy(), g["nbr"])
+    assert np.array_equal(map_triples(nbr), oracle.pairs(g["nbr"]))
+
+
+CASES = [
+    # k, s, p, d, transposed, subm
+    (3, 1, 1, 1, False, True),
+    (5, 1, 2, 1, False, True),
+    (3, 1, 2, 2, False, True),
+    (3, 2, 1, 1, False, False),
+    (2, 2, 0, 1, False, False),
+    (3, 1, 1, 1, False, False),
+    (5, 2, 2, 1, False, False),
+    (2, 2, 0, 1, True, False),
+    (3, 2, 1, 1, True, False),
+]
+
+
+@pytest.mark.parametrize("k,s,p,d,transposed,subm", CASES)
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int16])
+def test_random_vs_oracle(cuda_device, oracle, k, s, p, d, transposed, subm, dtype):
+    n = 20_000 if (transposed or (k == 3 and s == 1 and not subm)) else 60_000
+    coords = synthetic.random_cells(n, 3, 40, seed=100 + k + s)
+    if transposed:                                   # batched transposed: rows grouped by sample or not,
+        coords = coords[torch.argsort(coords[:, 0], stable=True)]   # the exact rule is order-independent
+    shape = (40, 40, 40)
+    oc, ns, ko, nbr = gpu_kernel_map(cuda_device, coords, shape, k, s, d, p, transposed, subm, dtype)
+    woc, wns, woff, wnbr = oracle.kernel_map(coords.numpy(), shape, k, s, d, p, transposed, subm)
+    assert ns == wns.tolist()
+    assert np.array_equal(oc.cpu().numpy().astype(np.int32), woc)
+    assert np.array_equal(nbr.cpu().numpy(), wnbr)
+    assert np.array_equal(map_triples(nbr), oracle.pairs(wnbr))
+
+
+def test_surface_scene_downsample_and_back(cuda_device, oracle):
+    """A contiguous surface (duplicate-heavy candidates): k3 s2 p1 map, then the transposed map
+    built from its output coordinates."""
+    cells = synthetic.surface_scene(3000, grid=128, target=40_000, n_spheres=3, n_boxes=4)
+    coords = synthetic.batch_of([cells, synthetic.surface_scene(3001, grid=128, target=30_000, n_spheres=2, n_boxes=2)])
+    shape = (128, 128, 128)
+    oc, ns, ko, nbr = gpu_kernel_map(cuda_device, coords, shape, 3, 2, 1, 1, False, False)
+    woc, wns, _, wnbr = oracle.kernel_map(coords.numpy(), shape, 3, 2, 1, 1, False, False)
+    assert np.array_equal(oc.cpu().numpy(), woc) and np.array_equal(nbr.cpu().numpy(), wnbr)
+    oc2, ns2, _, nbr2 = gpu_kernel_map(cuda_device, oc, ns, 3, 2, 1, 1, True, False)
+    woc2, wns2, _, wnbr2 = oracle.kernel_map(woc, tuple(wns), 3, 2, 1, 1, True, False)
+    assert ns2 == wns2.tolist()
+    assert np.array_equal(oc2.cpu().numpy(), woc2) and np.array_equal(nbr2.cpu().numpy(), wnbr2)
+
+
+def test_edge_cases(cuda_device, oracle):
+    set_coords_dtype(torch.int32)
+    empty = torch.empty((0, 4), dtype=torch.int32, device=cuda_device)
+    oc, ns, ko = build_out_coords(empty, (8, 8, 8), 3, 2, 1, 1, submanifold=False)
+    assert oc.shape == (0, 4) and ns.tolist() == [4, 4, 4] and ko.shape == (27, 3)
+    # single voxel in the far corner, every kind of map
+    one = np.array([[1, 7, 7, 7]], np.int32)
+    for (k, s, p, d, tr, subm) in CASES:
+        oc, ns, _, nbr = gpu_kernel_map(cuda_device, one, (8, 8, 8), k, s, d, p, tr, subm)
+        woc, wns, _, wnbr = oracle.kernel_map(one, (8, 8, 8), k, s, d, p, tr, subm)
+        assert np.array_equal(oc.cpu().numpy(), woc) and np.array_equal(nbr.cpu().numpy(), wnbr), (k, s, p, d, tr)
+    # fully occupied small grid: every candidate is duplicated up to 27 times
+    xs = torch.arange(6)
+    full = torch.stack(torch.meshgrid(torch.zeros(1, dtype=torch.long), xs, xs, xs, indexing="ij"), -1).reshape(-1, 4)
+    oc, ns, _, nbr = gpu_kernel_map(cuda_device, full.numpy().astype(np.int32), (6, 6, 6), 3, 2, 1, 1, False, False)
+    woc, wns, _, wnbr = oracle.kernel_map(full.numpy(), (6, 6, 6), 3, 2, 1, 1, False, False)
+    assert np.array_equal(oc.cpu().numpy(), woc) and np.array_equal(nbr.cpu().numpy(), wnbr)
+
+
+def test_inverse_map(cuda_device):
+    coords = synthetic.random_cells(5000, 2, 24, seed=5)
+    oc, ns, ko, nbr = gpu_kernel_map(cuda_device, coords, (24, 24, 24), 3, 2, 1, 1, False, False)
+    inv = inverse_map(nbr, coords.shape[0]).cpu().numpy()
+    want = np.full((coords.shape[0], 27), -1, np.int32)
+    n = nbr.cpu().numpy()
+    o, k = np.nonzero(n >= 0)
+    want[n[o, k], k] = o
+    assert np.array_equal(inv, want)

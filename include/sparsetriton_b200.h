@@ -44,6 +44,7 @@ extern "C" {
 #define ST_DEV_TABLE_FULL 1     /* an insert ran out of probes: capacity too small */
 #define ST_DEV_OUT_OVERFLOW 2   /* more output rows than the caller's buffer holds */
 #define ST_DEV_BAD_INDEX 4      /* a map entry pointed outside the feature matrix (debug checks) */
+#define ST_DEV_TIMEOUT 8        /* a bounded wait inside a tensor-core kernel expired; the kernel unwound */
 
 #define ST_I16 0
 #define ST_I32 1
@@ -60,6 +61,9 @@ int st_version(void);
 const char* st_last_error_string(void);
 /* Number of kernels this library has enqueued in this process so far. */
 long long st_launch_count(void);
+/* Sticky status of the tensor-core kernels on the current device: out4 (HOST memory, 4 x int32) =
+ * {ST_DEV_* flags, id of the wait that expired, block index, reserved}.  Synchronises the stream. */
+int st_device_status(int32_t* out4, void* stream);
 /* 1 if the tcgen05 (tensor-core) kernels can serve this conv shape, else 0 (SIMT kernels used). */
 int st_conv_uses_tensor_cores(int dtype, int cin, int cout);
 

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_PKG, "_native", "libsparsetriton_b200.so")
 
 ST_I16, ST_I32 = 0, 1
 ST_F32, ST_F16, ST_BF16 = 0, 1, 2
-DEV_TABLE_FULL, DEV_OUT_OVERFLOW, DEV_BAD_INDEX = 1, 2, 4
+DEV_TABLE_FULL, DEV_OUT_OVERFLOW, DEV_BAD_INDEX, DEV_TIMEOUT = 1, 2, 4, 8
 
 _COORD_CODES = {torch.int16: ST_I16, torch.int32: ST_I32}
 _FEAT_CODES = {torch.float32: ST_F32, torch.float16: ST_F16, torch.bfloat16: ST_BF16}
@@ -28,6 +28,7 @@ _SIGNATURES = {
     "st_last_error_string": ([], ctypes.c_char_p),
     "st_launch_count": ([], ctypes.c_longlong),
     "st_conv_uses_tensor_cores": ([_INT, _INT, _INT], _INT),
+    "st_device_status": ([_PTR, _PTR], _INT),
     "st_hash_clear": ([_PTR, _PTR, _I64, _PTR], _INT),
     "st_hash_build": ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
     "st_hash_query": ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
@@ -113,3 +114,11 @@ def host_i32(values):
 def workspace(nbytes, device):
     """256-byte aligned scratch from torch's caching allocator."""
     return torch.empty((max(int(nbytes), 256),), dtype=torch.uint8, device=device)
+
+
+def device_status(device=None):
+    """[flags, wait site, block, reserved] of the tensor-core kernels on `device` (synchronises)."""
+    out = (ctypes.c_int32 * 4)()
+    with torch.cuda.device(device):
+        check(lib().st_device_status(out, stream_ptr()), "st_device_status")
+    return list(out)

@@ -89,6 +89,14 @@ extern "C" {
 
 int st_conv_uses_tensor_cores(int dtype, int cin, int cout) { return tc_supported(dtype, cin, cout) ? 1 : 0; }
 
+int st_device_status(int32_t* out4, void* stream) {
+  if (!out4) {
+    set_error("st_device_status: null output");
+    return ST_ERR_ARG;
+  }
+  return tc_read_status(out4, (cudaStream_t)stream);
+}
+
 int64_t st_conv_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout) {
   (void)dtype;
   (void)n_in;

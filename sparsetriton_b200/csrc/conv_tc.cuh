@@ -16,4 +16,8 @@ bool tc_supported(int dtype, int c_red, int c_acc);
 int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
                    int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream);
 
+// Copies the sticky device status words of the tensor-core kernels (flags, wait site, block, extra)
+// to host memory and synchronises the stream.
+int tc_read_status(int32_t* host_out4, cudaStream_t stream);
+
 }  // namespace st

@@ -66,6 +66,9 @@ long long st_launch_count(void);
 int st_device_status(int32_t* out4, void* stream);
 /* 1 if the tcgen05 (tensor-core) kernels can serve this conv shape, else 0 (SIMT kernels used). */
 int st_conv_uses_tensor_cores(int dtype, int cin, int cout);
+/* Process-wide switch (default on).  With 0 every product runs on the CUDA-core kernels; used to
+ * cross-check the tensor-core kernels and to get exact-fp32 arithmetic for fp32 features. */
+int st_set_tensor_cores(int enable);
 
 /* ---------------------------------------------------------------- hash table ------------- */
 

@@ -89,6 +89,11 @@ extern "C" {
 
 int st_conv_uses_tensor_cores(int dtype, int cin, int cout) { return tc_supported(dtype, cin, cout) ? 1 : 0; }
 
+int st_set_tensor_cores(int enable) {
+  tc_set_enabled(enable != 0);
+  return ST_OK;
+}
+
 int st_device_status(int32_t* out4, void* stream) {
   if (!out4) {
     set_error("st_device_status: null output");

@@ -156,17 +156,27 @@ __device__ __forceinline__ void producer_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
 }
 
-// Shared-memory operand descriptor, 128-byte swizzle, 8-row groups 1024 B apart.
-//   lbo_bytes: distance between 128-byte column blocks (MN-major operands); ignored for K-major.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes) {
+// Shared-memory operand descriptor for rows of 128 bytes.
+//   lbo_bytes  distance between 128-byte column blocks (MN-major operands); ignored for K-major
+//   sbo_bytes  distance between row groups: 1024 (8 rows) for the 128-byte swizzle, 512 (4 rows) for
+//              the 128-byte swizzle with 32-byte atoms
+//   layout     2 = SWIZZLE_128B (16-byte chunk index ^= row % 8)
+//              1 = SWIZZLE_128B_BASE32B (32-byte chunk index ^= row % 4): the only swizzled layout
+//                  the tensor core accepts for an MN-major operand of 32-bit elements (tf32)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout) {
   uint64_t d = 0;
   d |= (uint64_t)((addr >> 4) & 0x3FFF);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((1024 >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= 1ull << 46;   // descriptor version of sm_100
-  d |= 2ull << 61;   // SWIZZLE_128B
+  d |= (uint64_t)layout << 61;
   return d;
 }
+
+// Position (in 16-byte units) at which logical chunk c of row r is stored inside its 128-byte row.
+__device__ __forceinline__ int swz16(int c, int r) { return c ^ (r & 7); }
+__device__ __forceinline__ int swz32(int c, int r) { return c ^ ((r & 3) << 1); }
 
 struct __align__(8) Control {
   unsigned long long full[kMaxStages];
@@ -284,7 +294,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_kernel(const Params p, con
             for (int e = t; e < R * 8; e += kProducerThreads) {
               const int c = e & 7, r = e >> 3;
               if (c < cb_chunks)
-                cp_async16(blk + (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)),
+                cp_async16(blk + (uint32_t)(r * 128 + ((p.esize == 4 ? swz32(c, r) : swz16(c, r)) << 4)),
                            wrow0 + (size_t)r * w_col_bytes + cb * 128 + c * 16, 16u);
             }
           }
@@ -354,6 +364,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_kernel(const Params p, con
       // MN-major B: one K-step covers 32 B of reduction = (32/esize) rows of 128 B
       const int b_kstep_bytes = p.b_mn_major ? (32 / p.esize) * 128 : 32;
       const uint32_t b_lbo = p.b_mn_major ? (uint32_t)(128 / p.esize) * 128u : 16u;
+      const bool b_base32 = p.b_mn_major && p.esize == 4;
+      const uint32_t b_sbo = b_base32 ? 512u : 1024u, b_layout = b_base32 ? 1u : 2u;
       for (int64_t tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
         ok = mbar_wait(smem_u32(&ctl->acc_empty[buf]), acc_phase[buf] ^ 1u, abort_flag, 2);
         if (!ok) break;
@@ -369,8 +381,8 @@ __global__ void __launch_bounds__(kThreads, 1) gather_kernel(const Params p, con
           const uint32_t a_base = ring + (uint32_t)stage * p.stage_bytes;
           const uint32_t w_base = a_base + p.a_stage_bytes;
           for (int ks = 0; ks < ksteps; ++ks) {
-            const uint64_t da = smem_desc(a_base + ks * a_kstep_bytes, 16u);
-            const uint64_t db = smem_desc(w_base + ks * b_kstep_bytes, b_lbo);
+            const uint64_t da = smem_desc(a_base + ks * a_kstep_bytes, 16u, 1024u, 2u);
+            const uint64_t db = smem_desc(w_base + ks * b_kstep_bytes, b_lbo, b_sbo, b_layout);
             const uint32_t accumulate = ((info & 1u) && ks == 0) ? 0u : 1u;
             if (p.esize == 2)
               mma_f16(d_addr, da, db, p.idesc, accumulate);
@@ -457,7 +469,12 @@ static int sm_count() {
   return g_sm_count;
 }
 
+static bool g_tc_enabled = true;
+
+void tc_set_enabled(bool on) { g_tc_enabled = on; }
+
 bool tc_supported(int dtype, int c_red, int c_acc) {
+  if (!g_tc_enabled) return false;
   if (dtype != ST_F32 && dtype != ST_F16 && dtype != ST_BF16) return false;
   const int es = dtype == ST_F32 ? 4 : 2;
   const int kstep = 32 / es;                       // reduction elements per MMA

@@ -9,6 +9,8 @@ namespace st {
 // True if the tcgen05 gather kernel handles a product with c_red reduction channels and c_acc
 // accumulator (output) channels in this dtype.
 bool tc_supported(int dtype, int c_red, int c_acc);
+// Process-wide switch: when off, tc_supported() answers false and the CUDA-core kernels run.
+void tc_set_enabled(bool on);
 
 // OUT[r,:] = sum_k IN[map[r,k],:] . B_k over a stored (n_rows, K) map.
 //   w_transposed = false: B_k = W[k]   with W (K, c_red, c_acc)   (forward)

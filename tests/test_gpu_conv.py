@@ -21,6 +21,15 @@ pytestmark = pytest.mark.gpu
 ALGOS = [ConvAlgo.PrecomputedNeighborGEMM, ConvAlgo.ImplicitHashFlyGEMM]
 
 
+@pytest.fixture(autouse=True)
+def _no_device_side_errors(cuda_device):
+    """No bounded wait of a tensor-core kernel may have expired during a test."""
+    from sparsetriton_b200 import _lib
+    yield
+    status = _lib.device_status(cuda_device)
+    assert status[0] == 0, f"device status after test: {status}"
+
+
 @pytest.mark.parametrize("algo", ALGOS, ids=lambda a: a.name)
 @pytest.mark.parametrize("path", golden_files("conv_"), ids=case_id)
 def test_golden_fp32(cuda_device, path, algo):

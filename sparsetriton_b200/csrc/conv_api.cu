@@ -9,6 +9,7 @@
 namespace st {
 
 int wgrad_chunks(int64_t n_out);
+int reduce_partials(int dtype, const float* partial, int chunks, int64_t n, void* out, cudaStream_t s);
 
 template <typename T, typename Map>
 int simt_gather(const T* in, const T* w, const Map& map, T* out, int64_t n_rows, int64_t n_src, int K, int c_red,
@@ -38,6 +39,13 @@ static int check_conv_args(const char* who, int dtype, int64_t n_in, int64_t n_o
 
 static int64_t wgrad_partial_bytes(int64_t n_out, int K, int cin, int cout) {
   return align_up((int64_t)wgrad_chunks(n_out) * K * cin * cout * 4, 256);
+}
+
+// Partials of whichever weight-gradient kernel would run, so one workspace serves both.
+static int64_t wgrad_workspace_bytes(int dtype, int64_t n_out, int K, int cin, int cout) {
+  int64_t simt = wgrad_partial_bytes(n_out, K, cin, cout);
+  int64_t tcb = align_up(tc_wgrad_partial_bytes(dtype, n_out, K, cin, cout), 256);
+  return simt > tcb ? simt : tcb;
 }
 
 // Dispatch a callable over the feature dtype.
@@ -103,10 +111,9 @@ int st_device_status(int32_t* out4, void* stream) {
 }
 
 int64_t st_conv_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout) {
-  (void)dtype;
   (void)n_in;
   if (n_out < 0 || K < 1 || cin < 1 || cout < 1) return 256;
-  return wgrad_partial_bytes(n_out, K, cin, cout) + 256;
+  return wgrad_workspace_bytes(dtype, n_out, K, cin, cout) + 256;
 }
 
 int64_t st_conv_hashfly_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout) {
@@ -168,12 +175,18 @@ int st_conv_wgrad(int dtype, const void* X, const void* dY, const int32_t* nbr, 
     set_error("st_conv_wgrad: null pointer");
     return ST_ERR_ARG;
   }
-  if (n_out > 0 && (!workspace || workspace_bytes < wgrad_partial_bytes(n_out, K, cin, cout) ||
+  if (n_out > 0 && (!workspace || workspace_bytes < wgrad_workspace_bytes(dtype, n_out, K, cin, cout) ||
                     (reinterpret_cast<uintptr_t>(workspace) & 255))) {
     set_error("st_conv_wgrad: workspace too small or misaligned");
     return ST_ERR_WORKSPACE;
   }
   cudaStream_t s = (cudaStream_t)stream;
+  if (n_out > 0 && tc_wgrad_supported(dtype, n_out, K, cin, cout)) {
+    int chunks = 0;
+    rc = tc_conv_wgrad(dtype, X, dY, nbr, static_cast<float*>(workspace), &chunks, n_out, n_in, K, cin, cout, s);
+    if (rc != ST_OK) return rc;
+    return reduce_partials(dtype, static_cast<const float*>(workspace), chunks, (int64_t)K * cin * cout, dW, s);
+  }
   StoredMap map{nbr, K};
   return by_dtype(dtype, [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;

@@ -284,6 +284,21 @@ int simt_wgrad(const T* x, const T* dy, const Map& map, T* dw, float* partial, i
   return check_launch("conv_wgrad_kernel");
 }
 
+// out[i] = sum over chunks of partial[chunk][i], cast to the feature dtype (fixed summation order).
+int reduce_partials(int dtype, const float* partial, int chunks, int64_t n, void* out, cudaStream_t s) {
+  if (n <= 0) return ST_OK;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (dtype == ST_F32) {
+    reduce_partials_kernel<float><<<grid, 256, 0, s>>>(partial, chunks, n, static_cast<float*>(out));
+  } else if (dtype == ST_F16) {
+    reduce_partials_kernel<__half><<<grid, 256, 0, s>>>(partial, chunks, n, static_cast<__half*>(out));
+  } else {
+    reduce_partials_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(partial, chunks, n, static_cast<__nv_bfloat16*>(out));
+  }
+  note_launches(1);
+  return check_launch("reduce_partials");
+}
+
 #define ST_INSTANTIATE(T, MAP)                                                                                     \
   template int simt_gather<T, MAP>(const T*, const T*, const MAP&, T*, int64_t, int64_t, int, int, int, bool,     \
                                    cudaStream_t);                                                                  \

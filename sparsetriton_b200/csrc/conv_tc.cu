@@ -19,6 +19,7 @@
 
 #include "conv_maps.cuh"
 #include "conv_tc.cuh"
+#include "tc_ptx.cuh"
 
 namespace st {
 
@@ -32,9 +33,7 @@ constexpr int kThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32;
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kABlockBytes = kTileM * 128;                     // 128 rows x 128 B
 constexpr int kMaxStages = 8;
-constexpr long long kWaitCycles = 4000000000ll;                // ~2 s at 2 GHz
 
-__device__ int32_t g_status[4];                                // [0] flags, [1] where, [2] block, [3] extra
 
 struct Params {
   const void* in;          // (n_src, c_red)
@@ -55,128 +54,6 @@ struct Params {
   int out_kind;            // ST_F32 / ST_F16 / ST_BF16
   int64_t n_tiles;
 };
-
-// ------------------------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.shared::cta.b64 t, [%0];\n\t}" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false if the limit expired or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-    if (mbar_try(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
-      *abort_flag = 1;
-      if (atomicOr(&g_status[0], ST_DEV_TIMEOUT) == 0) {
-        g_status[1] = where;
-        g_status[2] = blockIdx.x;
-      }
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void mma_f16(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
-      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_tf32(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
-      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void producer_bar_sync() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory");
-}
-
-// Shared-memory operand descriptor for rows of 128 bytes.
-//   lbo_bytes  distance between 128-byte column blocks (MN-major operands); ignored for K-major
-//   sbo_bytes  distance between row groups: 1024 (8 rows) for the 128-byte swizzle, 512 (4 rows) for
-//              the 128-byte swizzle with 32-byte atoms
-//   layout     2 = SWIZZLE_128B (16-byte chunk index ^= row % 8)
-//              1 = SWIZZLE_128B_BASE32B (32-byte chunk index ^= row % 4): the only swizzled layout
-//                  the tensor core accepts for an MN-major operand of 32-bit elements (tf32)
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                              uint32_t layout) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr >> 4) & 0x3FFF);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= 1ull << 46;   // descriptor version of sm_100
-  d |= (uint64_t)layout << 61;
-  return d;
-}
-
-// Position (in 16-byte units) at which logical chunk c of row r is stored inside its 128-byte row.
-__device__ __forceinline__ int swz16(int c, int r) { return c ^ (r & 7); }
-__device__ __forceinline__ int swz32(int c, int r) { return c ^ ((r & 3) << 1); }
 
 struct __align__(8) Control {
   unsigned long long full[kMaxStages];
@@ -334,9 +211,9 @@ __global__ void __launch_bounds__(kThreads, 1) gather_kernel(const Params p, con
           if (i >= 0 && i < p.n_src) mine |= 1u << j;
         }
         const uint32_t warp_mask = __reduce_or_sync(0xFFFFFFFFu, mine);
-        producer_bar_sync();                                 // the previous group's masks have been read
+        producer_bar_sync<kProducerThreads>();                                 // the previous group's masks have been read
         if (lane == 0) ctl->group_mask[pwarp] = warp_mask;
-        producer_bar_sync();
+        producer_bar_sync<kProducerThreads>();
         uint32_t m = ctl->group_mask[0] | ctl->group_mask[1] | ctl->group_mask[2] | ctl->group_mask[3];
         while (m && ok) {
           const int j = __ffs(m) - 1;
@@ -455,6 +332,272 @@ struct StoredRows {
   }
 };
 
+
+// =================================================================================================
+// Weight gradient on the tensor cores.
+//
+//   dW[k][ci][co] = sum_r  X[map(r,k)][ci] * dY[r][co]
+//
+// The reduction runs over rows, so both operands enter the MMA "MN-major" (channels contiguous,
+// one 128-byte line per row): A = dY tile (M = 128 output channels), B = gathered X rows
+// (N = up to 128 input channels), K = the 128 rows of a tile.  A CTA owns a chunk of row tiles, a
+// group of G kernel offsets (G accumulators of N columns fill TMEM), one 128-wide block of output
+// channels and one block of input channels; it keeps its G accumulators in TMEM across all of its
+// tiles and finally writes them as fp32 partials  partial[chunk][k][ci][co]  that a second kernel
+// sums in chunk order ("split by offset", deterministic).  The dY tile is loaded once per tile and
+// reused by every offset of the group.
+// =================================================================================================
+constexpr int kWgradBSlotsMax = 6;
+
+struct WgradParams {
+  const void* x;         // (n_src, cin)
+  const void* dy;        // (n_rows, cout)
+  float* partial;        // (n_chunks, K, cin, cout)
+  int64_t n_rows, n_src, n_tiles, tiles_per_chunk;
+  int K, cin, cout, esize;
+  int group;             // offsets per CTA (accumulators in TMEM)
+  int n_kgroups;
+  int ci_blk;            // input channels per CTA (MMA N)
+  int n_ciblk, n_coblk;
+  int a_slot_bytes, b_slot_bytes, b_slots;
+  int tmem_cols;
+  uint32_t idesc_base;   // everything but N
+};
+
+struct __align__(8) WgradControl {
+  unsigned long long a_full[2], a_empty[2];
+  unsigned long long b_full[kWgradBSlotsMax], b_empty[kWgradBSlotsMax];
+  unsigned long long acc_full;
+  uint32_t b_info[kWgradBSlotsMax];    // bits 0-7 accumulator index, bit 8 end-of-tile marker
+  uint32_t group_mask[kProducerWarps];
+  uint32_t touched;                    // accumulators that received at least one MMA
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename Map>
+__global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p, const Map map) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - raw);
+  const uint32_t a_ring = base;
+  const uint32_t b_ring = base + 2u * (uint32_t)p.a_slot_bytes;
+  WgradControl* ctl =
+      reinterpret_cast<WgradControl*>(base_ptr + 2 * (size_t)p.a_slot_bytes + (size_t)p.b_slots * p.b_slot_bytes);
+  volatile int* abort_flag = &ctl->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // work item of this CTA
+  const int chunk = blockIdx.x;
+  const int kgroup = blockIdx.y;
+  const int coblk = blockIdx.z / p.n_ciblk, ciblk = blockIdx.z % p.n_ciblk;
+  const int k_first = kgroup * p.group;
+  const int g_count = min(p.group, p.K - k_first);
+  const int co0 = coblk * 128, co_cnt = min(128, p.cout - co0);
+  const int ci0 = ciblk * p.ci_blk, ci_cnt = min(p.ci_blk, p.cin - ci0);
+  const int64_t tile_begin = (int64_t)chunk * p.tiles_per_chunk;
+  const int64_t tile_end = min(p.n_tiles, tile_begin + p.tiles_per_chunk);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&ctl->a_full[s]), kProducerThreads);
+      mbar_init(smem_u32(&ctl->a_empty[s]), 1);
+    }
+    for (int s = 0; s < p.b_slots; ++s) {
+      mbar_init(smem_u32(&ctl->b_full[s]), kProducerThreads + 1);
+      mbar_init(smem_u32(&ctl->b_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctl->acc_full), 2);
+    ctl->abort_flag = 0;
+    ctl->touched = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), (uint32_t)p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const bool base32 = p.esize == 4;                 // 32-bit elements: 128-byte swizzle with 32-byte atoms
+
+  if (warp >= kFirstProducerWarp) {
+    // =============================================================== producers
+    const int t = threadIdx.x - kFirstProducerWarp * 32;
+    const int pwarp = t >> 5;
+    int a_slot = 0, b_slot = 0;
+    uint32_t a_phase = 0, b_phase = 0;
+    bool ok = true;
+    const int x_row_bytes = p.cin * p.esize, dy_row_bytes = p.cout * p.esize;
+    const int a_bytes = co_cnt * p.esize, b_bytes = ci_cnt * p.esize;      // bytes of this CTA's channel blocks
+
+    // Copy `bytes` of one row into the 128-byte-line blocks of a slot (line t of every block).
+    auto copy_row = [&](uint32_t slot_base, const char* src, int bytes, bool valid) {
+      const int n_chunks = bytes >> 4;
+      for (int c = 0; c < n_chunks; ++c) {
+        const int blk = c >> 3, cc = c & 7;
+        const uint32_t dst = slot_base + (uint32_t)(blk * kABlockBytes + t * 128 + ((base32 ? swz32(cc, t) : swz16(cc, t)) << 4));
+        cp_async16(dst, valid ? src + c * 16 : static_cast<const char*>(p.dy), valid ? 16u : 0u);
+      }
+    };
+    auto send_b = [&](int acc, bool marker, bool has, int32_t src_row) {
+      ok = mbar_wait(smem_u32(&ctl->b_empty[b_slot]), b_phase ^ 1u, abort_flag, 11);
+      if (!ok) return;
+      if (!marker)
+        copy_row(b_ring + (uint32_t)b_slot * p.b_slot_bytes,
+                 static_cast<const char*>(p.x) + (size_t)(has ? src_row : 0) * x_row_bytes + (size_t)ci0 * p.esize,
+                 b_bytes, has);
+      cp_async_arrive_noinc(smem_u32(&ctl->b_full[b_slot]));
+      if (t == 0) {
+        ctl->b_info[b_slot] = (uint32_t)acc | (marker ? 0x100u : 0u);
+        mbar_arrive(smem_u32(&ctl->b_full[b_slot]));
+      }
+      if (++b_slot == p.b_slots) {
+        b_slot = 0;
+        b_phase ^= 1u;
+      }
+    };
+
+    for (int64_t tile = tile_begin; tile < tile_end && ok; ++tile) {
+      const int64_t row = tile * kTileM + t;
+      const bool row_ok = row < p.n_rows;
+      typename Map::RowState rs = map.row_state(row, row_ok);
+      // neighbours of this row for the offsets of the group (independent loads, then a bit mask)
+      int32_t idx[32];
+      uint32_t mine = 0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        int32_t i = (j < g_count && row_ok) ? map.get(rs, row, k_first + j) : -1;
+        if (i >= p.n_src) i = -1;
+        idx[j] = i;
+        if (i >= 0) mine |= 1u << j;
+      }
+      const uint32_t warp_mask = __reduce_or_sync(0xFFFFFFFFu, mine);
+      producer_bar_sync<kProducerThreads>();
+      if (lane == 0) ctl->group_mask[pwarp] = warp_mask;
+      producer_bar_sync<kProducerThreads>();
+      uint32_t m = ctl->group_mask[0] | ctl->group_mask[1] | ctl->group_mask[2] | ctl->group_mask[3];
+      if (m) {
+        // dY tile: once per tile, shared by all offsets of the group
+        ok = mbar_wait(smem_u32(&ctl->a_empty[a_slot]), a_phase ^ 1u, abort_flag, 10);
+        if (!ok) break;
+        copy_row(a_ring + (uint32_t)a_slot * p.a_slot_bytes,
+                 static_cast<const char*>(p.dy) + (size_t)(row_ok ? row : 0) * dy_row_bytes + (size_t)co0 * p.esize,
+                 a_bytes, row_ok);
+        cp_async_arrive_noinc(smem_u32(&ctl->a_full[a_slot]));
+        if (++a_slot == 2) {
+          a_slot = 0;
+          a_phase ^= 1u;
+        }
+        while (m && ok) {
+          const int j = __ffs(m) - 1;
+          m &= m - 1;
+          send_b(j, false, (mine >> j) & 1u, idx[j]);
+        }
+        if (ok) send_b(0, true, false, 0);                   // end of tile: lets the MMA warp free the dY slot
+      }
+    }
+    if (ok) send_b(0xFF, true, false, 0);                     // end of work
+    cp_async_wait_all();
+  } else if (warp == kMmaWarp) {
+    // =============================================================== MMA issuer
+    if (lane == 0) {
+      int a_slot = 0, b_slot = 0;
+      uint32_t a_phase = 0, b_phase = 0;
+      uint32_t touched = 0;
+      bool ok = true, have_a = false;
+      const int rows_per_step = 32 / p.esize;                  // reduction rows per MMA (16 or 8)
+      const int ksteps = kTileM / rows_per_step;
+      const uint32_t step_bytes = (uint32_t)rows_per_step * 128u;
+      const uint32_t sbo = base32 ? 512u : 1024u, layout = base32 ? 1u : 2u;
+      const uint32_t idesc = p.idesc_base | ((uint32_t)(p.ci_blk >> 3) << 17);
+      for (;;) {
+        ok = mbar_wait(smem_u32(&ctl->b_full[b_slot]), b_phase, abort_flag, 12);
+        if (!ok) break;
+        const uint32_t info = ctl->b_info[b_slot];
+        const bool marker = (info & 0x100u) != 0;
+        const int acc = (int)(info & 0xFFu);
+        if (!marker) {
+          if (!have_a) {
+            ok = mbar_wait(smem_u32(&ctl->a_full[a_slot]), a_phase, abort_flag, 13);
+            if (!ok) break;
+            have_a = true;
+          }
+          fence_proxy_async();
+          tc_fence_after();
+          const uint32_t a_base = a_ring + (uint32_t)a_slot * p.a_slot_bytes;
+          const uint32_t b_base = b_ring + (uint32_t)b_slot * p.b_slot_bytes;
+          const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.ci_blk);
+          for (int ks = 0; ks < ksteps; ++ks) {
+            const uint64_t da = smem_desc(a_base + ks * step_bytes, kABlockBytes, sbo, layout);
+            const uint64_t db = smem_desc(b_base + ks * step_bytes, kABlockBytes, sbo, layout);
+            const uint32_t accumulate = (((touched >> acc) & 1u) || ks > 0) ? 1u : 0u;
+            if (p.esize == 2)
+              mma_f16(d_addr, da, db, idesc, accumulate);
+            else
+              mma_tf32(d_addr, da, db, idesc, accumulate);
+          }
+          touched |= 1u << acc;
+        }
+        mma_commit(smem_u32(&ctl->b_empty[b_slot]));
+        if (++b_slot == p.b_slots) {
+          b_slot = 0;
+          b_phase ^= 1u;
+        }
+        if (marker) {
+          if (acc == 0xFF) break;                               // end of work
+          if (have_a) {                                         // end of tile: the dY slot may be refilled
+            mma_commit(smem_u32(&ctl->a_empty[a_slot]));
+            if (++a_slot == 2) {
+              a_slot = 0;
+              a_phase ^= 1u;
+            }
+            have_a = false;
+          }
+        }
+      }
+      if (ok) {
+        ctl->touched = touched;
+        mma_commit(smem_u32(&ctl->acc_full));
+        mbar_arrive(smem_u32(&ctl->acc_full));
+      }
+    }
+    __syncwarp();
+  } else {
+    // =============================================================== epilogue (warps 0..3)
+    bool ok = mbar_wait(smem_u32(&ctl->acc_full), 0u, abort_flag, 14);
+    ok = __all_sync(0xFFFFFFFFu, ok);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t touched = ctl->touched;
+      const int co = warp * 32 + lane;                           // accumulator row = output channel
+      for (int j = 0; j < g_count; ++j) {
+        float* dst = p.partial + (((size_t)chunk * p.K + (k_first + j)) * p.cin + ci0) * p.cout + co0 + co;
+        const bool live = (touched >> j) & 1u;
+        for (int c0 = 0; c0 < ci_cnt; c0 += 16) {
+          uint32_t v[32];
+          tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(j * p.ci_blk + c0), v);
+          tmem_ld_wait();
+          if (co < co_cnt) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) dst[(size_t)(c0 + c) * p.cout] = live ? __uint_as_float(v[c]) : 0.f;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
 }  // namespace tc
 
 static int g_sm_count = 0;
@@ -548,6 +691,98 @@ int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map,
   kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, rows);
   note_launches(1);
   return check_launch("tc_conv_gather");
+}
+
+
+// ------------------------------------------------------------------------------------------- wgrad
+struct WgradPlan {
+  tc::WgradParams p;
+  int n_chunks;
+  size_t smem;
+};
+
+static bool plan_wgrad(WgradPlan* plan, int dtype, int64_t n_rows, int K, int cin, int cout) {
+  if (!g_tc_enabled) return false;
+  if (dtype != ST_F32 && dtype != ST_F16 && dtype != ST_BF16) return false;
+  const int es = dtype == ST_F32 ? 4 : 2;
+  if (cin % 16 != 0 || cin < 16 || cout % 8 != 0 || cout < 8 || n_rows <= 0) return false;
+  tc::WgradParams& p = plan->p;
+  p.esize = es;
+  p.K = K;
+  p.cin = cin;
+  p.cout = cout;
+  p.n_rows = n_rows;
+  p.n_tiles = (n_rows + tc::kTileM - 1) / tc::kTileM;
+  // input-channel block: at most 256 bytes per row (two 128-byte lines), i.e. 128 (16-bit) or 64 (32-bit) channels
+  const int ci_max = 256 / es;
+  p.n_ciblk = (cin + ci_max - 1) / ci_max;
+  p.ci_blk = ((cin + p.n_ciblk - 1) / p.n_ciblk + 15) / 16 * 16;
+  p.n_ciblk = (cin + p.ci_blk - 1) / p.ci_blk;
+  p.n_coblk = (cout + 127) / 128;
+  p.group = 512 / p.ci_blk;
+  if (p.group > 32) p.group = 32;
+  if (p.group > K) p.group = K;
+  p.n_kgroups = (K + p.group - 1) / p.group;
+  int cols = 32;
+  while (cols < p.group * p.ci_blk) cols <<= 1;
+  p.tmem_cols = cols;
+  p.a_slot_bytes = (128 * es / 128) * tc::kABlockBytes;                 // 128 output channels
+  p.b_slot_bytes = ((p.ci_blk * es + 127) / 128) * tc::kABlockBytes;
+  int b_slots = (200 * 1024 - 2 * p.a_slot_bytes) / p.b_slot_bytes;
+  if (b_slots > tc::kWgradBSlotsMax) b_slots = tc::kWgradBSlotsMax;
+  if (b_slots < 2) return false;
+  p.b_slots = b_slots;
+  const uint32_t fmt = dtype == ST_F16 ? 0u : (dtype == ST_BF16 ? 1u : 2u);
+  p.idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(tc::kTileM >> 4) << 24);
+  const int64_t ctas_per_chunk = (int64_t)p.n_kgroups * p.n_coblk * p.n_ciblk;
+  int64_t chunks = (2 * sm_count() + ctas_per_chunk - 1) / ctas_per_chunk;
+  if (chunks > p.n_tiles) chunks = p.n_tiles;
+  if (chunks > 64) chunks = 64;
+  if (chunks < 1) chunks = 1;
+  p.tiles_per_chunk = (p.n_tiles + chunks - 1) / chunks;
+  plan->n_chunks = (int)((p.n_tiles + p.tiles_per_chunk - 1) / p.tiles_per_chunk);
+  plan->smem = 2 * (size_t)p.a_slot_bytes + (size_t)p.b_slots * p.b_slot_bytes + sizeof(tc::WgradControl) + 1024;
+  return true;
+}
+
+bool tc_wgrad_supported(int dtype, int64_t n_rows, int K, int cin, int cout) {
+  WgradPlan plan;
+  return plan_wgrad(&plan, dtype, n_rows, K, cin, cout);
+}
+
+int64_t tc_wgrad_partial_bytes(int dtype, int64_t n_rows, int K, int cin, int cout) {
+  WgradPlan plan;
+  if (!plan_wgrad(&plan, dtype, n_rows, K, cin, cout)) return 0;
+  return (int64_t)plan.n_chunks * K * cin * cout * 4;
+}
+
+int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, float* partial, int* n_chunks_out,
+                  int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream) {
+  WgradPlan plan;
+  if (!plan_wgrad(&plan, dtype, n_rows, K, cin, cout)) {
+    set_error("tc_conv_wgrad: unsupported shape");
+    return ST_ERR_UNSUPPORTED;
+  }
+  plan.p.x = x;
+  plan.p.dy = dy;
+  plan.p.partial = partial;
+  plan.p.n_src = n_src;
+  auto kernel = tc::wgrad_kernel<tc::StoredRows>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) {
+      set_error("tc_conv_wgrad: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
+      return ST_ERR_CUDA;
+    }
+    configured = true;
+  }
+  dim3 grid((unsigned)plan.n_chunks, (unsigned)plan.p.n_kgroups, (unsigned)(plan.p.n_coblk * plan.p.n_ciblk));
+  tc::StoredRows rows{map, K};
+  kernel<<<grid, tc::kThreads, plan.smem, stream>>>(plan.p, rows);
+  note_launches(1);
+  *n_chunks_out = plan.n_chunks;
+  return check_launch("tc_conv_wgrad");
 }
 
 int tc_read_status(int32_t* host_out4, cudaStream_t stream) {

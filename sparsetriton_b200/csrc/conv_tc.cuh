@@ -18,6 +18,12 @@ void tc_set_enabled(bool on);
 int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
                    int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream);
 
+// Tensor-core weight gradient: fills fp32 partials (n_chunks, K, cin, cout) that the caller reduces.
+bool tc_wgrad_supported(int dtype, int64_t n_rows, int K, int cin, int cout);
+int64_t tc_wgrad_partial_bytes(int dtype, int64_t n_rows, int K, int cin, int cout);
+int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, float* partial, int* n_chunks_out,
+                  int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream);
+
 // Copies the sticky device status words of the tensor-core kernels (flags, wait site, block, extra)
 // to host memory and synchronises the stream.
 int tc_read_status(int32_t* host_out4, cudaStream_t stream);

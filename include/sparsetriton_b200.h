@@ -157,6 +157,26 @@ int st_conv_dgrad(int dtype, const void* dY, const void* W, const int32_t* inv, 
 int st_conv_wgrad(int dtype, const void* X, const void* dY, const int32_t* nbr, void* dW, int64_t n_in,
                   int64_t n_out, int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Weight gradient without any caller-side memory.  No counterpart in the reference: it exists for
+ * hosts that may not allocate device memory around the call -- an inference or training plugin whose
+ * memory pool is owned and sized by another runtime, a real-time loop that forbids cudaMalloc after
+ * start-up, code running inside a region where allocation would synchronise the device.  The fp32
+ * partial sums that st_conv_wgrad() keeps in the caller's workspace are kept here in a fixed array
+ * inside the library: st_conv_wgrad_static_max_bytes() bytes (64 MiB) of every GPU that has loaded
+ * the library, held until the process exits.  Same arguments and result as st_conv_wgrad(), minus
+ * the workspace.  A layer whose partial sums do not fit is refused with ST_ERR_WORKSPACE and a
+ * message naming both sizes; nothing is launched in that case.  The call itself allocates nothing
+ * and frees nothing.
+ *   - The first call on each GPU looks up the device address of the array (with that GPU current);
+ *     make that first call outside of any stream capture.
+ *   - All calls on one GPU share the array.  It keeps whatever the last call left in it; each call
+ *     overwrites every partial it later reads, so no clearing is needed, but two calls that run on
+ *     the GPU at the same time (different streams) would overwrite each other's partials: keep
+ *     calls on one GPU ordered. */
+int64_t st_conv_wgrad_static_max_bytes(void);
+int st_conv_wgrad_static(int dtype, const void* X, const void* dY, const int32_t* nbr, void* dW, int64_t n_in,
+                         int64_t n_out, int K, int cin, int cout, void* stream);
+
 /* Hash-on-the-fly forms: no stored map; every tile recomputes
  *   curr = out*lookup_stride - off[k], bounds-checks it against lookup_shape and probes the table.
  * Replace ConvHashOnTheFlyImplicitGEMM forward / backward,

@@ -47,6 +47,8 @@ _SIGNATURES = {
     "st_conv_dgrad": ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),
     "st_conv_wgrad": ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),
 }
+_SIGNATURES["st_conv_wgrad_static_max_bytes"] = ([], _I64)
+_SIGNATURES["st_conv_wgrad_static"] = ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR], _INT)
 _HASHFLY_SIG = ([_INT, _PTR, _PTR, _PTR, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _INT, _PTR, _I64, _I64, _INT, _INT, _INT,
                  _PTR, _I64, _PTR], _INT)
 for _n in ("st_conv_fwd_hashfly", "st_conv_dgrad_hashfly", "st_conv_wgrad_hashfly"):

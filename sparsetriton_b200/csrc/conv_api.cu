@@ -97,8 +97,11 @@ extern "C" {
 
 int st_conv_uses_tensor_cores(int dtype, int cin, int cout) { return tc_supported(dtype, cin, cout) ? 1 : 0; }
 
+int st_debug_prof(long long* out, int n) { return st::tc_read_prof(out, n); }
+
 int st_set_tensor_cores(int enable) {
   tc_set_enabled(enable != 0);
+  if (enable == 1 || enable == 2) tc_set_gather_version(enable == 1 ? 2 : 1);
   return ST_OK;
 }
 

@@ -17,6 +17,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "conv_maps.cuh"
 #include "conv_tc.cuh"
 #include "tc_ptx.cuh"
@@ -287,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather_kernel(const Params p, con
     bool ok = true;
     const int out_es = p.out_kind == ST_F32 ? 4 : 2;
     for (int64_t tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
-      ok = mbar_wait(smem_u32(&ctl->acc_full[buf]), acc_phase[buf], abort_flag, 4);
+      ok = mbar_wait(smem_u32(&ctl->acc_full[buf]), acc_phase[buf], abort_flag, 4, 256);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -332,6 +334,410 @@ struct StoredRows {
   }
 };
 
+
+// =================================================================================================
+// Gather kernel, second form: one copy of a W[k] slice serves several row tiles.
+//
+// A CTA works on a "super tile" of S consecutive 128-row tiles whose S accumulators sit side by side
+// in TMEM (S * C_out columns; two such sets when they fit, so that the epilogue overlaps the next
+// super tile).  The loop order is offset-major: for each kernel offset that has a neighbour anywhere
+// in the super tile the W[k] slice is copied once into its own ring, then one gathered-row stage per
+// sub tile that needs it goes through the row ring.  With the 20 %-filled maps of surface data the
+// W copies were 5/6 of the shared-memory fill traffic of the first form; here they are divided by S.
+// Each producer thread first fetches the map entries of its S rows for 32 offsets at a time
+// (independent loads into a local array), so no stage waits for an index load.
+// =================================================================================================
+// Cycle counters for timing experiments: compiled in only with -DST_TC_PROFILE (and read when dbg bit
+// 256 is set); otherwise PROF_CLOCK() is a constant and the bookkeeping disappears.
+__device__ long long g_prof[160 * 16];
+#ifdef ST_TC_PROFILE
+#define PROF_CLOCK() clock64()
+#else
+#define PROF_CLOCK() 0ll
+#endif
+
+constexpr int kMaxSub = 4;
+constexpr int kMaxWSlots = 4;
+constexpr int kMaxAStages = 12;
+constexpr int kGroup = 16;                                   // kernel offsets whose map entries are staged at a time
+constexpr int kIdxTileBytes = kGroup * kMaxSub * kTileM * 4;  // 32 KB
+
+struct Params2 {
+  const void* in;
+  const void* w;
+  void* out;
+  int64_t n_rows, n_src, n_super;
+  int K, c_red, c_acc, esize;
+  int w_rows, w_cols, b_mn_major, k_blocks;
+  int w_slot_bytes, w_slots, a_stages;
+  int sub;                 // row tiles per super tile (S)
+  int acc_bufs;            // 1 or 2 accumulator sets
+  int tmem_cols;
+  uint32_t idesc;
+  int out_kind;
+  int dbg;                 // timing experiments only (wrong results): 1 no proxy fence, 2 no MMA, 4 no row copies, 8 no zero-fill copies
+};
+
+struct __align__(8) Control2 {
+  unsigned long long a_full[kMaxAStages], a_empty[kMaxAStages];
+  unsigned long long w_full[kMaxWSlots], w_empty[kMaxWSlots];
+  unsigned long long acc_full[2], acc_empty[2];
+  // bits 0-1 sub tile, bit 2 first MMA into that accumulator, bit 3 takes the next W slot,
+  // bit 4 frees the W slot afterwards, bit 5 end of super tile (no data), bits 8.. K-steps
+  uint32_t a_info[kMaxAStages];
+  uint32_t group_mask[kProducerWarps][kMaxSub];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename Map, int ESIZE>
+__global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, const Map map) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - raw);
+  const uint32_t w_ring = base;
+  const uint32_t a_ring = base + (uint32_t)(p.w_slots * p.w_slot_bytes);
+  // map entries of the current offset group: idx_tile[(j * kMaxSub + s) * 128 + row]
+  int32_t* idx_tile = reinterpret_cast<int32_t*>(base_ptr + (size_t)p.w_slots * p.w_slot_bytes +
+                                                 (size_t)p.a_stages * kABlockBytes);
+  Control2* ctl = reinterpret_cast<Control2*>(reinterpret_cast<unsigned char*>(idx_tile) + kIdxTileBytes);
+  volatile int* abort_flag = &ctl->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.a_stages; ++s) {
+      mbar_init(smem_u32(&ctl->a_full[s]), kProducerWarps);
+      mbar_init(smem_u32(&ctl->a_empty[s]), 1);
+    }
+    for (int s = 0; s < p.w_slots; ++s) {
+      mbar_init(smem_u32(&ctl->w_full[s]), kProducerWarps);
+      mbar_init(smem_u32(&ctl->w_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl->acc_full[b]), 1);
+      mbar_init(smem_u32(&ctl->acc_empty[b]), kEpilogueWarps * 32);
+    }
+    ctl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), (uint32_t)p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const int red_bytes = p.c_red * ESIZE;
+  const int set_cols = p.sub * p.c_acc;                      // TMEM columns of one accumulator set
+
+  if (warp >= kFirstProducerWarp) {
+    // =============================================================== producers
+    const int t = threadIdx.x - kFirstProducerWarp * 32;
+    const int pwarp = t >> 5;
+    int a_stage = 0, w_slot = 0;
+    uint32_t a_phase = 0, w_phase = 0;
+    bool ok = true;
+    const int kr = 128 / ESIZE;
+    const int w_col_bytes = p.w_cols * ESIZE;
+    StageQueue queue;
+    queue.clear();
+    long long t_pref = 0, t_acq_a = 0, t_acq_w = 0, t_total0 = PROF_CLOCK(), t_push = 0, t_copy = 0;
+    long long n_flush = 0;
+    // Wait until the consumer has released a slot.  If it has not yet, first hand over every stage
+    // still held back in the queue, so that the consumer can never be waiting for this warp.
+    auto acquire = [&](uint32_t bar, uint32_t parity, int where) {
+      int ready = 0;
+      if (lane == 0) ready = mbar_try(bar, parity) ? 1 : 0;
+      ready = __shfl_sync(0xFFFFFFFFu, ready, 0);
+      if (ready) return true;
+      const long long c0 = PROF_CLOCK();
+      queue.flush(lane);
+      ++n_flush;
+      const bool r = mbar_wait_warp(bar, parity, abort_flag, where, lane);
+      if (where == 21) t_acq_w += PROF_CLOCK() - c0; else t_acq_a += PROF_CLOCK() - c0;
+      return r;
+    };
+
+    auto send_w = [&](int k, int kb) {
+      ok = acquire(smem_u32(&ctl->w_empty[w_slot]), w_phase ^ 1u, 21);
+      if (!ok) return;
+      const uint32_t w_base = w_ring + (uint32_t)w_slot * p.w_slot_bytes;
+      const char* wk = static_cast<const char*>(p.w) + (size_t)k * p.w_rows * w_col_bytes;
+      if (p.dbg & 16) {
+      } else if (p.b_mn_major) {
+        const int R = min(kr, p.w_rows - kb * kr);
+        const int n_cb = (w_col_bytes + 127) >> 7;
+        const char* wrow0 = wk + (size_t)kb * kr * w_col_bytes;
+        for (int cb = 0; cb < n_cb; ++cb) {
+          const int cb_chunks = min(128, w_col_bytes - cb * 128) >> 4;
+          const uint32_t blk = w_base + (uint32_t)(cb * kr * 128);
+          for (int e = t; e < R * 8; e += kProducerThreads) {
+            const int c = e & 7, r = e >> 3;
+            if (c < cb_chunks)
+              cp_async16(blk + (uint32_t)(r * 128 + ((ESIZE == 4 ? swz32(c, r) : swz16(c, r)) << 4)),
+                         wrow0 + (size_t)r * w_col_bytes + cb * 128 + c * 16, 16u);
+          }
+        }
+      } else {
+        const int wchunks = min(128, w_col_bytes - kb * 128) >> 4;
+        for (int e = t; e < p.w_rows * 8; e += kProducerThreads) {
+          const int c = e & 7, r = e >> 3;
+          if (c < wchunks)
+            cp_async16(w_base + (uint32_t)(r * 128 + (swz16(c, r) << 4)), wk + (size_t)r * w_col_bytes + kb * 128 + c * 16,
+                       16u);
+        }
+      }
+      cp_async_commit();
+      queue.push(smem_u32(&ctl->w_full[w_slot]), lane);
+      if (++w_slot == p.w_slots) {
+        w_slot = 0;
+        w_phase ^= 1u;
+      }
+    };
+    // flags: see Control2::a_info
+    auto send_a = [&](int kb, bool has, int32_t src_row, uint32_t flags) {
+      ok = acquire(smem_u32(&ctl->a_empty[a_stage]), a_phase ^ 1u, 22);
+      if (!ok) return;
+      const long long cc = PROF_CLOCK();
+      int valid_bytes = 0;
+      if (!(flags & 32u)) {
+        valid_bytes = min(128, red_bytes - kb * 128);
+        const int chunks = valid_bytes >> 4;
+        const char* src = has ? static_cast<const char*>(p.in) + (size_t)src_row * red_bytes + kb * 128
+                              : static_cast<const char*>(p.w);
+        const uint32_t a_row = a_ring + (uint32_t)a_stage * kABlockBytes + (uint32_t)t * 128u;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (c < chunks && !(p.dbg & 4) && (has || !(p.dbg & 8)))
+            cp_async16(a_row + (uint32_t)(swz16(c, t) << 4), src + (has ? c * 16 : 0), has ? 16u : 0u);
+      }
+      if (t == 0) ctl->a_info[a_stage] = flags | ((uint32_t)(valid_bytes >> 5) << 8);
+      cp_async_commit();
+      const long long cq = PROF_CLOCK();
+      t_copy += cq - cc;
+      queue.push(smem_u32(&ctl->a_full[a_stage]), lane);
+      t_push += PROF_CLOCK() - cq;
+      if (++a_stage == p.a_stages) {
+        a_stage = 0;
+        a_phase ^= 1u;
+      }
+    };
+
+    for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
+      const int64_t row0 = st_i * p.sub * kTileM + t;          // this thread's row in sub tile 0
+      typename Map::RowState rs[kMaxSub];
+      bool row_ok[kMaxSub];
+#pragma unroll
+      for (int s = 0; s < kMaxSub; ++s) {
+        row_ok[s] = s < p.sub && row0 + (int64_t)s * kTileM < p.n_rows;
+        rs[s] = map.row_state(row0 + (int64_t)s * kTileM, row_ok[s]);
+      }
+      uint32_t touched = 0;                                     // sub tiles whose accumulator has been started
+      for (int k0 = 0; k0 < p.K && ok; k0 += kGroup) {
+        const long long cpf = PROF_CLOCK();
+        const int kn = min(kGroup, p.K - k0);
+        uint32_t mine[kMaxSub];
+        int32_t got[kMaxSub][kGroup];
+#pragma unroll
+        for (int s = 0; s < kMaxSub; ++s) {
+#pragma unroll
+          for (int j = 0; j < kGroup; ++j)
+            got[s][j] = (row_ok[s] && j < kn && !(p.dbg & 32)) ? map.get(rs[s], row0 + (int64_t)s * kTileM, k0 + j) : -1;
+        }
+        // every stage of the previous group has been issued by every producer thread: the tile can be rewritten
+        producer_bar_sync<kProducerThreads>();
+#pragma unroll
+        for (int s = 0; s < kMaxSub; ++s) {
+          mine[s] = 0;
+#pragma unroll
+          for (int j = 0; j < kGroup; ++j) {
+            int32_t i = got[s][j];
+            if (i >= p.n_src) i = -1;
+            idx_tile[(j * kMaxSub + s) * kTileM + t] = i;
+            if (i >= 0) mine[s] |= 1u << j;
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < kMaxSub; ++s) {
+          const uint32_t wm = __reduce_or_sync(0xFFFFFFFFu, mine[s]);
+          if (lane == 0) ctl->group_mask[pwarp][s] = wm;
+        }
+        producer_bar_sync<kProducerThreads>();
+        uint32_t m[kMaxSub], m_any = 0;
+#pragma unroll
+        for (int s = 0; s < kMaxSub; ++s) {
+          m[s] = ctl->group_mask[0][s] | ctl->group_mask[1][s] | ctl->group_mask[2][s] | ctl->group_mask[3][s];
+          m_any |= m[s];
+        }
+        t_pref += PROF_CLOCK() - cpf;
+        while (m_any && ok) {
+          const int j = __ffs(m_any) - 1;
+          m_any &= m_any - 1;
+          uint32_t users = 0;                                   // sub tiles that need this offset
+#pragma unroll
+          for (int s = 0; s < kMaxSub; ++s) users |= ((m[s] >> j) & 1u) << s;
+          const int last_user = 31 - __clz(users);
+          for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
+            send_w(k0 + j, kb);
+            bool first_of_w = true;
+#pragma unroll
+            for (int s = 0; s < kMaxSub; ++s) {
+              if (!((users >> s) & 1u) || !ok) continue;
+              const bool has = (mine[s] >> j) & 1u;
+              uint32_t flags = (uint32_t)s;
+              if (kb == 0 && !((touched >> s) & 1u)) flags |= 4u;
+              if (first_of_w) flags |= 8u;
+              if (s == last_user) flags |= 16u;
+              send_a(kb, has, idx_tile[(j * kMaxSub + s) * kTileM + t], flags);
+              first_of_w = false;
+            }
+          }
+          touched |= users;
+        }
+      }
+      // sub tiles that exist but never got a neighbour still have to write zeros
+      for (int s = 0; s < p.sub && ok; ++s) {
+        const bool exists = (st_i * p.sub + s) * (int64_t)kTileM < p.n_rows;
+        if (exists && !((touched >> s) & 1u)) {
+          send_w(0, 0);
+          if (ok) send_a(0, false, 0, (uint32_t)s | 4u | 8u | 16u);
+        }
+      }
+      if (ok) send_a(0, false, 0, 32u);                          // end of super tile
+      queue.flush(lane);                                          // let the epilogue of this super tile start
+    }
+    queue.flush(lane);
+    if ((p.dbg & 256) && t == 0) {
+      long long* o = g_prof + (size_t)blockIdx.x * 16;
+      o[0] = PROF_CLOCK() - t_total0; o[1] = t_pref; o[2] = t_acq_a; o[3] = t_acq_w; o[4] = n_flush; o[5] = t_push; o[6] = t_copy;
+    }
+  } else if (warp == kMmaWarp) {
+    // =============================================================== MMA issuer
+    if (lane == 0) {
+      int a_stage = 0, w_slot = 0;
+      uint32_t a_phase = 0, w_phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int buf = 0;
+      bool ok = true;
+      const uint32_t b_kstep16 = (p.b_mn_major ? (32 / ESIZE) * 128 : 32) >> 4;   // K-step advance, 16-byte units
+      const uint32_t b_lbo = p.b_mn_major ? (uint32_t)(128 / ESIZE) * 128u : 16u;
+      const bool b_base32 = p.b_mn_major && ESIZE == 4;
+      // descriptors without their 14-bit start address (the address stays below 2^18, so a plain OR works)
+      const uint64_t a_desc_hi = smem_desc(0u, 16u, 1024u, 2u);
+      const uint64_t b_desc_hi = smem_desc(0u, b_lbo, b_base32 ? 512u : 1024u, b_base32 ? 1u : 2u);
+      const uint32_t idesc = p.idesc;
+      uint32_t w_lo = 0;
+      long long m_acc = 0, m_a = 0, m_w = 0, m_t0 = PROF_CLOCK(), m_n = 0, m_issue = 0, m_commit = 0;
+      for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
+        long long c0 = PROF_CLOCK();
+        ok = mbar_wait(smem_u32(&ctl->acc_empty[buf]), acc_phase[buf] ^ 1u, abort_flag, 23);
+        m_acc += PROF_CLOCK() - c0;
+        if (!ok) break;
+        tc_fence_after();
+        for (;;) {
+          c0 = PROF_CLOCK();
+          ok = mbar_wait(smem_u32(&ctl->a_full[a_stage]), a_phase, abort_flag, 24);
+          m_a += PROF_CLOCK() - c0;
+          ++m_n;
+          if (!ok) break;
+          const uint32_t info = ctl->a_info[a_stage];
+          if (info & 8u) {                                      // this stage starts a new W slice
+            c0 = PROF_CLOCK();
+            ok = mbar_wait(smem_u32(&ctl->w_full[w_slot]), w_phase, abort_flag, 25);
+            m_w += PROF_CLOCK() - c0;
+            if (!ok) break;
+            w_lo = (w_ring + (uint32_t)w_slot * p.w_slot_bytes) >> 4;
+          }
+          tc_fence_after();
+          const long long ci0 = PROF_CLOCK();
+          const int ksteps = (p.dbg & 2) ? 0 : (int)(info >> 8);
+          const uint32_t a_lo = (a_ring + (uint32_t)a_stage * kABlockBytes) >> 4;
+          const uint32_t d_addr = tmem_base + (uint32_t)(buf * set_cols + (int)(info & 3u) * p.c_acc);
+          const uint32_t fresh = (info & 4u) ? 0u : 1u;          // 0: the first MMA overwrites the accumulator
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            if (ks < ksteps) {
+              const uint64_t da = a_desc_hi | (uint64_t)(a_lo + ks * 2);
+              const uint64_t db = b_desc_hi | (uint64_t)(w_lo + ks * b_kstep16);
+              if (ESIZE == 2)
+                mma_f16(d_addr, da, db, idesc, ks == 0 ? fresh : 1u);
+              else
+                mma_tf32(d_addr, da, db, idesc, ks == 0 ? fresh : 1u);
+            }
+          }
+          const long long ci1 = PROF_CLOCK();
+          mma_commit(smem_u32(&ctl->a_empty[a_stage]));
+          if (++a_stage == p.a_stages) {
+            a_stage = 0;
+            a_phase ^= 1u;
+          }
+          if (info & 16u) {                                     // last user of the W slice
+            mma_commit(smem_u32(&ctl->w_empty[w_slot]));
+            if (++w_slot == p.w_slots) {
+              w_slot = 0;
+              w_phase ^= 1u;
+            }
+          }
+          m_issue += ci1 - ci0;
+          m_commit += PROF_CLOCK() - ci1;
+          if (info & 32u) break;
+        }
+        if (!ok) break;
+        mma_commit(smem_u32(&ctl->acc_full[buf]));
+        acc_phase[buf] ^= 1u;
+        if (p.acc_bufs == 2) buf ^= 1;
+      }
+      if (p.dbg & 256) {
+        long long* o = g_prof + (size_t)blockIdx.x * 16;
+        o[8] = PROF_CLOCK() - m_t0; o[9] = m_acc; o[10] = m_a; o[11] = m_w; o[12] = m_n; o[13] = m_issue; o[14] = m_commit;
+      }
+    }
+    __syncwarp();
+  } else {
+    // =============================================================== epilogue (warps 0..3)
+    uint32_t acc_phase[2] = {0, 0};
+    int buf = 0;
+    bool ok = true;
+    const int out_es = p.out_kind == ST_F32 ? 4 : 2;
+    for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
+      ok = mbar_wait(smem_u32(&ctl->acc_full[buf]), acc_phase[buf], abort_flag, 26, 256);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      for (int s = 0; s < p.sub; ++s) {
+        const int64_t row = (st_i * p.sub + s) * (int64_t)kTileM + warp * 32 + lane;
+        if ((st_i * p.sub + s) * (int64_t)kTileM >= p.n_rows) break;         // whole sub tile past the end
+        char* out_row = static_cast<char*>(p.out) + (size_t)row * p.c_acc * out_es;
+        const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * set_cols + s * p.c_acc);
+        for (int c0 = 0; c0 < p.c_acc; c0 += 32) {
+          uint32_t v[32];
+          if (p.c_acc - c0 >= 32) {
+            tmem_ld32(t_row + c0, v);
+            tmem_ld_wait();
+            if (row < p.n_rows && !(p.dbg & 64)) store_cols<32>(out_row, c0, p.out_kind, v);
+          } else {
+            tmem_ld16(t_row + c0, v);
+            tmem_ld_wait();
+            if (row < p.n_rows) store_cols<16>(out_row, c0, p.out_kind, v);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctl->acc_empty[buf]));
+      acc_phase[buf] ^= 1u;
+      if (p.acc_bufs == 2) buf ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
 
 // =================================================================================================
 // Weight gradient on the tensor cores.
@@ -567,7 +973,7 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p,
     __syncwarp();
   } else {
     // =============================================================== epilogue (warps 0..3)
-    bool ok = mbar_wait(smem_u32(&ctl->acc_full), 0u, abort_flag, 14);
+    bool ok = mbar_wait(smem_u32(&ctl->acc_full), 0u, abort_flag, 14, 512);
     ok = __all_sync(0xFFFFFFFFu, ok);
     if (ok) {
       tc_fence_after();
@@ -667,8 +1073,98 @@ static bool fill_params(tc::Params* p, int dtype, const void* in, const void* w,
   return true;
 }
 
+
+static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* w, void* out, int64_t n_rows,
+                         int64_t n_src, int K, int c_red, int c_acc, bool w_transposed) {
+  const int es = dtype == ST_F32 ? 4 : 2;
+  p->in = in;
+  p->w = w;
+  p->out = out;
+  p->n_rows = n_rows;
+  p->n_src = n_src;
+  p->K = K;
+  p->c_red = c_red;
+  p->c_acc = c_acc;
+  p->esize = es;
+  p->b_mn_major = w_transposed ? 0 : 1;
+  p->w_rows = w_transposed ? c_acc : c_red;
+  p->w_cols = w_transposed ? c_red : c_acc;
+  p->k_blocks = (c_red * es + 127) / 128;
+  int w_bytes = p->b_mn_major ? ((c_acc * es + 127) / 128) * (128 / es) * 128 : c_acc * 128;
+  p->w_slot_bytes = (w_bytes + 1023) / 1024 * 1024;
+  // accumulators: as many row tiles per W copy as TMEM allows (<= 4); a second set only when it is free
+  int sub = 512 / c_acc;
+  if (sub > tc::kMaxSub) sub = tc::kMaxSub;
+  p->acc_bufs = (2 * sub * c_acc <= 512) ? 2 : 1;
+  const int64_t n_tiles = (n_rows + tc::kTileM - 1) / tc::kTileM;
+  // small problems: do not leave SMs idle for the sake of sharing
+  while (sub > 1 && (n_tiles + sub - 1) / sub < sm_count()) --sub;
+  p->sub = sub;
+  p->n_super = (n_tiles + sub - 1) / sub;
+  int cols = 32;
+  while (cols < p->acc_bufs * sub * c_acc) cols <<= 1;
+  p->tmem_cols = cols;
+  p->w_slots = 3;
+  const int budget = 222 * 1024 - tc::kIdxTileBytes;
+  int a_stages = (budget - p->w_slots * p->w_slot_bytes) / tc::kABlockBytes;
+  if (a_stages > tc::kMaxAStages) a_stages = tc::kMaxAStages;
+  if (a_stages < 4) {
+    p->w_slots = 2;
+    a_stages = (budget - p->w_slots * p->w_slot_bytes) / tc::kABlockBytes;
+    if (a_stages > tc::kMaxAStages) a_stages = tc::kMaxAStages;
+  }
+  if (a_stages < 2) return false;
+  p->a_stages = a_stages;
+  const uint32_t fmt = dtype == ST_F16 ? 0u : (dtype == ST_BF16 ? 1u : 2u);
+  p->idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p->b_mn_major << 16) | ((uint32_t)(c_acc >> 3) << 17) |
+             ((uint32_t)(tc::kTileM >> 4) << 24);
+  p->out_kind = dtype;
+  {
+    const char* e = getenv("ST_TC_DEBUG");
+    p->dbg = e ? atoi(e) : 0;
+    const char* f = getenv("ST_TC_SUB");
+    if (f && atoi(f) >= 1 && atoi(f) <= sub) {
+      p->sub = atoi(f);
+      p->n_super = (n_tiles + p->sub - 1) / p->sub;
+    }
+  }
+  return true;
+}
+
+static int g_gather_version = 2;
+void tc_set_gather_version(int v) { g_gather_version = v; }
+
+static int tc_conv_gather2(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
+                           int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream) {
+  tc::Params2 p;
+  if (!fill_params2(&p, dtype, in, w, out, n_rows, n_src, K, c_red, c_acc, w_transposed)) {
+    set_error("tc_conv_gather: shape does not fit shared memory");
+    return ST_ERR_UNSUPPORTED;
+  }
+  if (n_rows == 0) return ST_OK;
+  const size_t smem = (size_t)p.w_slots * p.w_slot_bytes + (size_t)p.a_stages * tc::kABlockBytes +
+                      tc::kIdxTileBytes + sizeof(tc::Control2) + 1024;
+  auto kernel = p.esize == 2 ? tc::gather2_kernel<tc::StoredRows, 2> : tc::gather2_kernel<tc::StoredRows, 4>;
+  static bool configured[2] = {false, false};
+  if (!configured[p.esize == 4]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) {
+      set_error("tc_conv_gather: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
+      return ST_ERR_CUDA;
+    }
+    configured[p.esize == 4] = true;
+  }
+  int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
+  tc::StoredRows rows{map, K};
+  kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, rows);
+  note_launches(1);
+  return check_launch("tc_conv_gather");
+}
+
 int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
                    int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream) {
+  if (g_gather_version == 2)
+    return tc_conv_gather2(dtype, in, w, map, out, n_rows, n_src, K, c_red, c_acc, w_transposed, stream);
   tc::Params p;
   if (!fill_params(&p, dtype, in, w, out, n_rows, n_src, K, c_red, c_acc, w_transposed)) {
     set_error("tc_conv_gather: shape does not fit the shared-memory ring");
@@ -783,6 +1279,11 @@ int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, 
   note_launches(1);
   *n_chunks_out = plan.n_chunks;
   return check_launch("tc_conv_wgrad");
+}
+
+int tc_read_prof(long long* host_out, int n) {
+  cudaDeviceSynchronize();
+  return cudaMemcpyFromSymbol(host_out, tc::g_prof, sizeof(long long) * n) == cudaSuccess ? ST_OK : ST_ERR_CUDA;
 }
 
 int tc_read_status(int32_t* host_out4, cudaStream_t stream) {

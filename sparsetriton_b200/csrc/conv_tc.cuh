@@ -11,6 +11,8 @@ namespace st {
 bool tc_supported(int dtype, int c_red, int c_acc);
 // Process-wide switch: when off, tc_supported() answers false and the CUDA-core kernels run.
 void tc_set_enabled(bool on);
+// Which form of the gather kernel runs (1: W copied per row tile, 2: W shared by several row tiles).
+void tc_set_gather_version(int v);
 
 // OUT[r,:] = sum_k IN[map[r,k],:] . B_k over a stored (n_rows, K) map.
 //   w_transposed = false: B_k = W[k]   with W (K, c_red, c_acc)   (forward)
@@ -23,6 +25,9 @@ bool tc_wgrad_supported(int dtype, int64_t n_rows, int K, int cin, int cout);
 int64_t tc_wgrad_partial_bytes(int dtype, int64_t n_rows, int K, int cin, int cout);
 int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, float* partial, int* n_chunks_out,
                   int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream);
+
+// Cycle counters of timing experiments (see Params2::dbg).
+int tc_read_prof(long long* host_out, int n);
 
 // Copies the sticky device status words of the tensor-core kernels (flags, wait site, block, extra)
 // to host memory and synchronises the stream.

@@ -36,10 +36,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false if the limit expired or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
+// `sleep_ns` > 0 backs off between polls: waiting warps must not take issue slots from the MMA
+// and producer warps that share their scheduler.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where,
+                                          unsigned sleep_ns = 0) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
+    if (sleep_ns) __nanosleep(sleep_ns);
     if (mbar_try(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitCycles) {
@@ -57,6 +61,11 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
 }
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -111,6 +120,52 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Lagged, warp-aggregated hand-over of cp.async stages.
+//
+// Having every producer thread arrive on a stage's mbarrier costs ~130 serialised shared-memory
+// atomics per stage.  Instead each thread closes a stage with cp.async.commit_group, remembers the
+// stage's mbarrier in a 4-deep queue, and once three newer groups have been committed
+// (cp.async.wait_group 3: the oldest one has landed) the warp syncs and one lane arrives for it.
+struct StageQueue {
+  uint32_t bar[4];          // 0 = empty slot; bar[3] is the oldest
+  __device__ __forceinline__ void clear() { bar[0] = bar[1] = bar[2] = bar[3] = 0; }
+  // Call after commit_group of the stage whose barrier is `b`.
+  __device__ __forceinline__ void push(uint32_t b, int lane) {
+    cp_async_wait_group<3>();
+    const uint32_t oldest = bar[3];
+    bar[3] = bar[2];
+    bar[2] = bar[1];
+    bar[1] = bar[0];
+    bar[0] = b;
+    if (oldest) {
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(oldest);
+    }
+  }
+  // Hand over everything still queued (end of the kernel's work).
+  __device__ __forceinline__ void flush(int lane) {
+    cp_async_wait_all();
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      if (bar[3]) mbar_arrive(bar[3]);
+      if (bar[2]) mbar_arrive(bar[2]);
+      if (bar[1]) mbar_arrive(bar[1]);
+      if (bar[0]) mbar_arrive(bar[0]);
+    }
+    clear();
+  }
+};
+
+// Whole-warp bounded wait: lane 0 polls, the result is broadcast.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where,
+                                               int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, where) ? 1 : 0;
+  return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+}
+
 // Named barrier 1 among the `Threads` producer threads.
 template <int Threads>
 __device__ __forceinline__ void producer_bar_sync() {

@@ -111,6 +111,10 @@ inline Table make_table(const int64_t* keys, const int32_t* vals, int64_t capaci
   return t;
 }
 
+// q (n,4) int32 <- coordinates stored in the table, by row; absent rows get batch -1.
+int unpack_table_coords(const int64_t* keys, const int32_t* vals, int64_t capacity, int32_t* q, int64_t n,
+                        cudaStream_t stream);
+
 inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 // Exclusive prefix sum of n uint32 values (in != out allowed, in == out allowed); *total (device

@@ -48,6 +48,19 @@ static int64_t wgrad_workspace_bytes(int dtype, int64_t n_out, int K, int cin, i
   return simt > tcb ? simt : tcb;
 }
 
+// Scratch of the gather-form feature gradient of the hash-on-the-fly algorithm: a status word, a
+// table over the output coordinates (power-of-two capacity >= 2 n_out) and one int32x4 coordinate
+// per input row.
+static int64_t out_table_capacity(int64_t n_out) {
+  int64_t cap = 1024;
+  while (cap < 2 * n_out) cap <<= 1;
+  return cap;
+}
+static int64_t inverse_dgrad_bytes(int64_t n_in, int64_t n_out) {
+  const int64_t cap = out_table_capacity(n_out);
+  return 256 + align_up(cap * 8, 256) + align_up(cap * 4, 256) + align_up(n_in * 16, 256);
+}
+
 // Dispatch a callable over the feature dtype.
 template <typename F>
 static int by_dtype(int dtype, F&& f) {
@@ -101,7 +114,6 @@ int st_debug_prof(long long* out, int n) { return st::tc_read_prof(out, n); }
 
 int st_set_tensor_cores(int enable) {
   tc_set_enabled(enable != 0);
-  if (enable == 1 || enable == 2) tc_set_gather_version(enable == 1 ? 2 : 1);
   return ST_OK;
 }
 
@@ -122,8 +134,10 @@ int64_t st_conv_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, i
 int64_t st_conv_hashfly_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout) {
   if (n_in < 0 || n_out < 0 || K < 1 || cin < 1 || cout < 1) return 256;
   int64_t scatter = dtype == ST_F32 ? 0 : align_up(n_in * cin * 4, 256);
-  int64_t wg = wgrad_partial_bytes(n_out, K, cin, cout);
-  return (scatter > wg ? scatter : wg) + 256;
+  int64_t wg = wgrad_workspace_bytes(dtype, n_out, K, cin, cout);
+  int64_t inv = inverse_dgrad_bytes(n_in, n_out);
+  int64_t m = scatter > wg ? scatter : wg;
+  return (m > inv ? m : inv) + 256;
 }
 
 int st_conv_fwd(int dtype, const void* X, const void* W, const int32_t* nbr, void* Y, int64_t n_in, int64_t n_out,
@@ -216,6 +230,10 @@ int st_conv_fwd_hashfly(int dtype, const void* X, const void* W, const void* out
     return ST_ERR_ARG;
   }
   cudaStream_t s = (cudaStream_t)stream;
+  if (tc_supported(dtype, cin, cout)) {
+    HashFlyArgs h{out_coords, coord_dtype, &off, keys, vals, capacity, lookup_shape_host, lookup_stride};
+    return tc_conv_gather_hashfly(dtype, X, W, h, Y, n_out, n_in, K, cin, cout, s);
+  }
   return by_dtype(dtype, [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
     if (coord_dtype == ST_I32) {
@@ -243,6 +261,33 @@ int st_conv_dgrad_hashfly(int dtype, const void* dY, const void* W, const void* 
   if (!dY && n_out > 0 || !W || !dX) {
     set_error("st_conv_dgrad_hashfly: null pointer");
     return ST_ERR_ARG;
+  }
+  if (tc_supported(dtype, cout, cin) && n_out > 0 && capacity > 0) {
+    // Gather form: dX[i] = sum_k dY[o(i,k)] . W[k]^T with o found in a table over the output coordinates.
+    if (!workspace || workspace_bytes < inverse_dgrad_bytes(n_in, n_out) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255)) {
+      set_error("st_conv_dgrad_hashfly: workspace too small or misaligned");
+      return ST_ERR_WORKSPACE;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t cap = out_table_capacity(n_out);
+    char* p = static_cast<char*>(workspace);
+    int32_t* status = reinterpret_cast<int32_t*>(p);
+    p += 256;
+    int64_t* okeys = reinterpret_cast<int64_t*>(p);
+    p += align_up(cap * 8, 256);
+    int32_t* ovals = reinterpret_cast<int32_t*>(p);
+    p += align_up(cap * 4, 256);
+    int32_t* q = reinterpret_cast<int32_t*>(p);
+    cudaMemsetAsync(status, 0, 4, s);
+    rc = st_hash_clear(okeys, ovals, cap, stream);
+    if (rc != ST_OK) return rc;
+    rc = st_hash_build(out_coords, n_out, coord_dtype, okeys, ovals, cap, status, stream);
+    if (rc != ST_OK) return rc;
+    rc = unpack_table_coords(keys, vals, capacity, q, n_in, s);
+    if (rc != ST_OK) return rc;
+    return tc_conv_dgrad_inverse(dtype, dY, W, q, off, okeys, ovals, cap, lookup_stride, dX, n_in, n_out, K, cin,
+                                 cout, s);
   }
   float* out32 = static_cast<float*>(dX);
   if (dtype != ST_F32) {
@@ -281,12 +326,19 @@ int st_conv_wgrad_hashfly(int dtype, const void* X, const void* dY, const void* 
     set_error("st_conv_wgrad_hashfly: null pointer");
     return ST_ERR_ARG;
   }
-  if (n_out > 0 && (!workspace || workspace_bytes < wgrad_partial_bytes(n_out, K, cin, cout) ||
+  if (n_out > 0 && (!workspace || workspace_bytes < wgrad_workspace_bytes(dtype, n_out, K, cin, cout) ||
                     (reinterpret_cast<uintptr_t>(workspace) & 255))) {
     set_error("st_conv_wgrad_hashfly: workspace too small or misaligned");
     return ST_ERR_WORKSPACE;
   }
   cudaStream_t s = (cudaStream_t)stream;
+  if (n_out > 0 && tc_wgrad_supported(dtype, n_out, K, cin, cout)) {
+    HashFlyArgs h{out_coords, coord_dtype, &off, keys, vals, capacity, lookup_shape_host, lookup_stride};
+    int chunks = 0;
+    rc = tc_conv_wgrad_hashfly(dtype, X, dY, h, static_cast<float*>(workspace), &chunks, n_out, n_in, K, cin, cout, s);
+    if (rc != ST_OK) return rc;
+    return reduce_partials(dtype, static_cast<const float*>(workspace), chunks, (int64_t)K * cin * cout, dW, s);
+  }
   return by_dtype(dtype, [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
     if (coord_dtype == ST_I32) {

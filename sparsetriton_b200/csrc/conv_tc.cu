@@ -2,18 +2,15 @@
 //
 //   OUT[r, :] = sum_k  IN[map(r,k), :] . B_k            r = output row, k = kernel offset
 //
-// One persistent CTA per SM walks 128-row output tiles.  The fp32 accumulator of a tile lives in
-// TMEM for all of its kernel offsets (two buffers, so the epilogue of tile i overlaps the MMAs of
-// tile i+1).  Warp roles:
-//   warps 0-3  epilogue : tcgen05.ld the accumulator, convert, store rows of OUT
+// Persistent CTAs (one per SM) of 288 threads with fixed warp roles:
+//   warps 0-3  epilogue : tcgen05.ld the accumulators, convert, store rows of OUT
 //   warp  4    MMA      : one elected lane issues tcgen05.mma / tcgen05.commit
-//   warps 5-8  producer : per non-empty (tile, offset) and per 128-byte slice of the reduction
-//                         dimension, gather the 128 input rows (cp.async, 16 B, zero-fill for "no
-//                         neighbour") and the matching slice of W[k] into a ring of shared-memory
-//                         stages laid out in the 128-byte-swizzled canonical operand format
-// Stages are handed over with mbarriers: cp.async completion arrives on `full`, tcgen05.commit on
-// `empty`.  (tile, offset) pairs in which no row has a neighbour are skipped altogether.
-// Every wait is bounded: on expiry the kernel records ST_DEV_TIMEOUT and unwinds.
+//   warps 5-8  producer : gather the input rows (cp.async, 16 B, zero-fill for "no neighbour") and
+//                         the slices of W[k] into shared-memory rings laid out in the
+//                         128-byte-swizzled canonical operand format
+// Rings are handed over with mbarriers; every wait is bounded: on expiry the kernel records
+// ST_DEV_TIMEOUT in a sticky device word and unwinds.  The same producer code serves a stored
+// neighbour map or the coordinate hash table probed on the fly (the Map template argument).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -34,39 +31,7 @@ constexpr int kFirstProducerWarp = kMmaWarp + 1;               // warps 5..8
 constexpr int kThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32;
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kABlockBytes = kTileM * 128;                     // 128 rows x 128 B
-constexpr int kMaxStages = 8;
 
-
-struct Params {
-  const void* in;          // (n_src, c_red)
-  const void* w;           // (K, rows_w, cols_w)
-  void* out;               // (n_rows, c_acc)
-  int64_t n_rows, n_src;
-  int K, c_red, c_acc;
-  int esize;               // bytes per element (2 or 4)
-  int w_rows, w_cols;      // W[k] is (w_rows, w_cols) row-major in memory
-  int b_mn_major;          // 1: B_k = W[k] (rows = reduction), 0: B_k = W[k]^T (cols = reduction)
-  int k_blocks;            // 128-byte slices of the reduction dimension
-  int a_stage_bytes;       // kABlockBytes
-  int w_stage_bytes;       // bytes of one W slice
-  int stage_bytes;
-  int stages;
-  int tmem_cols;           // power of two >= 2 * c_acc
-  uint32_t idesc;
-  int out_kind;            // ST_F32 / ST_F16 / ST_BF16
-  int64_t n_tiles;
-};
-
-struct __align__(8) Control {
-  unsigned long long full[kMaxStages];
-  unsigned long long empty[kMaxStages];
-  unsigned long long acc_full[2];
-  unsigned long long acc_empty[2];
-  uint32_t stage_info[kMaxStages];     // bit0 first stage of its tile, bit1 last stage, bits 8.. MMA K-steps
-  uint32_t group_mask[kProducerWarps]; // per-warp "some row has a neighbour" bits of the current offset group
-  uint32_t tmem_base;
-  int abort_flag;
-};
 
 // Store 32 fp32 accumulator columns of one row.
 template <int N>
@@ -98,232 +63,7 @@ __device__ __forceinline__ void store_cols(void* out_row, int col0, int out_kind
   }
 }
 
-template <typename Map>
-__global__ void __launch_bounds__(kThreads, 1) gather_kernel(const Params p, const Map map) {
-  extern __shared__ unsigned char smem_raw[];
-  // stage ring first (1024-byte aligned for the swizzle pattern), control block after it
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t ring = (raw + 1023u) & ~1023u;
-  unsigned char* ring_ptr = smem_raw + (ring - raw);
-  Control* ctl = reinterpret_cast<Control*>(ring_ptr + (size_t)p.stages * p.stage_bytes);
-  volatile int* abort_flag = &ctl->abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&ctl->full[s]), kProducerThreads + 1);
-      mbar_init(smem_u32(&ctl->empty[s]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&ctl->acc_full[b]), 1);
-      mbar_init(smem_u32(&ctl->acc_empty[b]), kEpilogueWarps * 32);
-    }
-    ctl->abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), (uint32_t)p.tmem_cols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = ctl->tmem_base;
-
-  const int red_bytes = p.c_red * p.esize;
-
-  if (warp >= kFirstProducerWarp) {
-    // =============================================================== producers
-    const int t = threadIdx.x - kFirstProducerWarp * 32;    // 0..127 = row inside the tile
-    const int pwarp = t >> 5;
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    const int kr = 128 / p.esize;                            // reduction elements per 128-byte slice
-    const int w_col_bytes = p.w_cols * p.esize;
-
-    // Fill one stage: slice kb of the gathered rows and of W[k]; kb < 0 sends the end-of-tile marker.
-    auto emit = [&](int k, int kb, bool has, int32_t src_row, bool first) {
-      ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abort_flag, 1);
-      if (!ok) return;
-      int valid_bytes = 0;
-      if (kb >= 0) {
-        const uint32_t a_base = ring + (uint32_t)stage * p.stage_bytes;
-        const uint32_t w_base = a_base + p.a_stage_bytes;
-        // ---- A: this thread's row, up to 8 chunks of 16 B; chunk c is stored at position c ^ (row % 8)
-        valid_bytes = min(128, red_bytes - kb * 128);
-        const int chunks = valid_bytes >> 4;
-        const char* src = has ? static_cast<const char*>(p.in) + (size_t)src_row * red_bytes + kb * 128
-                              : static_cast<const char*>(p.w);
-        const uint32_t a_row = a_base + (uint32_t)t * 128u;
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          if (c < chunks) cp_async16(a_row + (uint32_t)((c ^ (t & 7)) << 4), src + (has ? c * 16 : 0), has ? 16u : 0u);
-        // ---- slice of W[k]
-        const char* wk = static_cast<const char*>(p.w) + (size_t)k * p.w_rows * w_col_bytes;
-        if (p.b_mn_major) {
-          // rows [kb*kr, kb*kr + R) of W[k], all 128-byte column blocks; block cb sits kr*128 B after block cb-1
-          const int R = min(kr, p.w_rows - kb * kr);
-          const int n_cb = (w_col_bytes + 127) >> 7;
-          const char* wrow0 = wk + (size_t)kb * kr * w_col_bytes;
-          for (int cb = 0; cb < n_cb; ++cb) {
-            const int cb_chunks = min(128, w_col_bytes - cb * 128) >> 4;
-            const uint32_t blk = w_base + (uint32_t)(cb * kr * 128);
-            for (int e = t; e < R * 8; e += kProducerThreads) {
-              const int c = e & 7, r = e >> 3;
-              if (c < cb_chunks)
-                cp_async16(blk + (uint32_t)(r * 128 + ((p.esize == 4 ? swz32(c, r) : swz16(c, r)) << 4)),
-                           wrow0 + (size_t)r * w_col_bytes + cb * 128 + c * 16, 16u);
-            }
-          }
-        } else {
-          // column block kb of W[k] (columns = reduction), all w_rows rows
-          const int wchunks = min(128, w_col_bytes - kb * 128) >> 4;
-          for (int e = t; e < p.w_rows * 8; e += kProducerThreads) {
-            const int c = e & 7, r = e >> 3;
-            if (c < wchunks)
-              cp_async16(w_base + (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)),
-                         wk + (size_t)r * w_col_bytes + kb * 128 + c * 16, 16u);
-          }
-        }
-      }
-      cp_async_arrive_noinc(smem_u32(&ctl->full[stage]));
-      if (t == 0) {
-        ctl->stage_info[stage] = (first ? 1u : 0u) | (kb < 0 ? 2u : 0u) | ((uint32_t)(valid_bytes >> 5) << 8);
-        mbar_arrive(smem_u32(&ctl->full[stage]));
-      }
-      if (++stage == p.stages) {
-        stage = 0;
-        phase ^= 1u;
-      }
-    };
-
-    for (int64_t tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
-      const int64_t row = tile * kTileM + t;
-      const bool row_ok = row < p.n_rows;
-      typename Map::RowState rs = map.row_state(row, row_ok);
-      int done = 0;                                          // offsets of this tile sent so far
-      for (int k0 = 0; k0 < p.K && ok; k0 += 32) {
-        // which of the offsets k0..k0+31 have a neighbour in this row / in any row of the tile
-        uint32_t mine = 0;
-        const int kn = min(32, p.K - k0);
-        for (int j = 0; j < kn; ++j) {
-          const int32_t i = row_ok ? map.get(rs, row, k0 + j) : -1;
-          if (i >= 0 && i < p.n_src) mine |= 1u << j;
-        }
-        const uint32_t warp_mask = __reduce_or_sync(0xFFFFFFFFu, mine);
-        producer_bar_sync<kProducerThreads>();                                 // the previous group's masks have been read
-        if (lane == 0) ctl->group_mask[pwarp] = warp_mask;
-        producer_bar_sync<kProducerThreads>();
-        uint32_t m = ctl->group_mask[0] | ctl->group_mask[1] | ctl->group_mask[2] | ctl->group_mask[3];
-        while (m && ok) {
-          const int j = __ffs(m) - 1;
-          m &= m - 1;
-          const bool has = (mine >> j) & 1u;
-          const int32_t src_row = has ? map.get(rs, row, k0 + j) : 0;
-          for (int kb = 0; kb < p.k_blocks && ok; ++kb) emit(k0 + j, kb, has, src_row, done == 0 && kb == 0);
-          ++done;
-        }
-      }
-      // a tile without any neighbour still has to produce zeros: one all-zero slice against W[0]
-      if (ok && done == 0) emit(0, 0, false, 0, true);
-      if (ok) emit(0, -1, false, 0, false);                  // end-of-tile marker
-    }
-    cp_async_wait_all();
-  } else if (warp == kMmaWarp) {
-    // =============================================================== MMA issuer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t acc_phase[2] = {0, 0};
-      int buf = 0;
-      bool ok = true;
-      const int a_kstep_bytes = 32;
-      // MN-major B: one K-step covers 32 B of reduction = (32/esize) rows of 128 B
-      const int b_kstep_bytes = p.b_mn_major ? (32 / p.esize) * 128 : 32;
-      const uint32_t b_lbo = p.b_mn_major ? (uint32_t)(128 / p.esize) * 128u : 16u;
-      const bool b_base32 = p.b_mn_major && p.esize == 4;
-      const uint32_t b_sbo = b_base32 ? 512u : 1024u, b_layout = b_base32 ? 1u : 2u;
-      for (int64_t tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
-        ok = mbar_wait(smem_u32(&ctl->acc_empty[buf]), acc_phase[buf] ^ 1u, abort_flag, 2);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t d_addr = tmem_base + (uint32_t)(buf * p.c_acc);
-        for (;;) {
-          ok = mbar_wait(smem_u32(&ctl->full[stage]), phase, abort_flag, 3);
-          if (!ok) break;
-          fence_proxy_async();
-          tc_fence_after();
-          const uint32_t info = ctl->stage_info[stage];
-          const int ksteps = (int)(info >> 8);
-          const uint32_t a_base = ring + (uint32_t)stage * p.stage_bytes;
-          const uint32_t w_base = a_base + p.a_stage_bytes;
-          for (int ks = 0; ks < ksteps; ++ks) {
-            const uint64_t da = smem_desc(a_base + ks * a_kstep_bytes, 16u, 1024u, 2u);
-            const uint64_t db = smem_desc(w_base + ks * b_kstep_bytes, b_lbo, b_sbo, b_layout);
-            const uint32_t accumulate = ((info & 1u) && ks == 0) ? 0u : 1u;
-            if (p.esize == 2)
-              mma_f16(d_addr, da, db, p.idesc, accumulate);
-            else
-              mma_tf32(d_addr, da, db, p.idesc, accumulate);
-          }
-          mma_commit(smem_u32(&ctl->empty[stage]));
-          if (++stage == p.stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-          if (info & 2u) break;                             // end-of-tile marker (carries no MMA)
-        }
-        if (!ok) break;
-        mma_commit(smem_u32(&ctl->acc_full[buf]));
-        acc_phase[buf] ^= 1u;
-        buf ^= 1;
-      }
-    }
-    __syncwarp();
-  } else {
-    // =============================================================== epilogue (warps 0..3)
-    uint32_t acc_phase[2] = {0, 0};
-    int buf = 0;
-    bool ok = true;
-    const int out_es = p.out_kind == ST_F32 ? 4 : 2;
-    for (int64_t tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
-      ok = mbar_wait(smem_u32(&ctl->acc_full[buf]), acc_phase[buf], abort_flag, 4, 256);
-      ok = __all_sync(0xFFFFFFFFu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const int64_t row = tile * kTileM + warp * 32 + lane;
-      char* out_row = static_cast<char*>(p.out) + (size_t)row * p.c_acc * out_es;
-      const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * p.c_acc);
-      for (int c0 = 0; c0 < p.c_acc; c0 += 32) {
-        uint32_t v[32];
-        if (p.c_acc - c0 >= 32) {
-          tmem_ld32(t_row + c0, v);
-          tmem_ld_wait();
-          if (row < p.n_rows) store_cols<32>(out_row, c0, p.out_kind, v);
-        } else {
-          tmem_ld16(t_row + c0, v);
-          tmem_ld_wait();
-          if (row < p.n_rows) store_cols<16>(out_row, c0, p.out_kind, v);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&ctl->acc_empty[buf]));
-      acc_phase[buf] ^= 1u;
-      buf ^= 1;
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == kMmaWarp) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
-  }
-}
-
-// Map adapters: what a producer thread keeps per row.
+// Map adapters: what a producer thread keeps per row, and how it finds the source row of offset k.
 struct StoredRows {
   const int32_t* nbr;
   int K;
@@ -331,6 +71,57 @@ struct StoredRows {
   __device__ __forceinline__ RowState row_state(int64_t, bool) const { return RowState{}; }
   __device__ __forceinline__ int32_t get(const RowState&, int64_t row, int k) const {
     return __ldg(nbr + row * K + k);
+  }
+};
+
+// Forward rule of the hash-on-the-fly form: source = table[(b, out * stride - off_k)] if inside the shape.
+template <typename CT>
+struct HashRows {
+  const CT* coords;
+  Offsets off;
+  Table table;
+  Int3 shape;
+  int stride;
+  using RowState = int4;
+  __device__ __forceinline__ RowState row_state(int64_t row, bool valid) const {
+    return valid ? load_coord<CT>(coords, row) : make_int4(0, 0, 0, 0);
+  }
+  __device__ __forceinline__ int32_t get(const RowState& c, int64_t, int k) const {
+    const int x = c.y * stride - off.v[k * 3 + 0];
+    const int y = c.z * stride - off.v[k * 3 + 1];
+    const int z = c.w * stride - off.v[k * 3 + 2];
+    if (x < 0 || x >= shape.x || y < 0 || y >= shape.y || z < 0 || z >= shape.z || table.capacity == 0 ||
+        !key_representable(c.x, x, y, z))
+      return -1;
+    return table_find(table, pack_key(c.x, x, y, z));
+  }
+};
+
+// Inverse rule (feature gradient): rows are inputs with table-space coordinate q; the source is the
+// output row at (q + off_k) / stride when the division is exact on every axis and that output exists.
+struct InverseRows {
+  const int32_t* q;        // (n_in, 4) int32, batch = -1 for rows that are not in the input table
+  Offsets off;
+  Table table;             // over the OUTPUT coordinates
+  int stride;
+  using RowState = int4;
+  __device__ __forceinline__ RowState row_state(int64_t row, bool valid) const {
+    return valid ? __ldg(reinterpret_cast<const int4*>(q) + row) : make_int4(-1, 0, 0, 0);
+  }
+  __device__ __forceinline__ int32_t get(const RowState& c, int64_t, int k) const {
+    if (c.x < 0 || table.capacity == 0) return -1;
+    int v[3] = {c.y + off.v[k * 3 + 0], c.z + off.v[k * 3 + 1], c.w + off.v[k * 3 + 2]};
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+      if (v[a] < 0) return -1;
+      if (stride > 1) {
+        const int qt = v[a] / stride;
+        if (qt * stride != v[a]) return -1;
+        v[a] = qt;
+      }
+    }
+    if (!key_representable(c.x, v[0], v[1], v[2])) return -1;
+    return table_find(table, pack_key(c.x, v[0], v[1], v[2]));
   }
 };
 
@@ -1032,48 +823,6 @@ bool tc_supported(int dtype, int c_red, int c_acc) {
   return true;
 }
 
-static bool fill_params(tc::Params* p, int dtype, const void* in, const void* w, void* out, int64_t n_rows,
-                        int64_t n_src, int K, int c_red, int c_acc, bool w_transposed) {
-  const int es = dtype == ST_F32 ? 4 : 2;
-  p->in = in;
-  p->w = w;
-  p->out = out;
-  p->n_rows = n_rows;
-  p->n_src = n_src;
-  p->K = K;
-  p->c_red = c_red;
-  p->c_acc = c_acc;
-  p->esize = es;
-  p->b_mn_major = w_transposed ? 0 : 1;
-  p->w_rows = w_transposed ? c_acc : c_red;
-  p->w_cols = w_transposed ? c_red : c_acc;
-  p->k_blocks = (c_red * es + 127) / 128;
-  p->a_stage_bytes = tc::kABlockBytes;
-  if (p->b_mn_major) {
-    const int n_cb = (c_acc * es + 127) / 128;
-    p->w_stage_bytes = n_cb * (128 / es) * 128;
-  } else {
-    p->w_stage_bytes = c_acc * 128;
-  }
-  p->w_stage_bytes = (p->w_stage_bytes + 1023) / 1024 * 1024;
-  p->stage_bytes = p->a_stage_bytes + p->w_stage_bytes;
-  const int budget = 200 * 1024;
-  int stages = budget / p->stage_bytes;
-  if (stages > tc::kMaxStages) stages = tc::kMaxStages;
-  if (stages < 2) return false;
-  p->stages = stages;
-  int cols = 32;
-  while (cols < 2 * c_acc) cols <<= 1;
-  p->tmem_cols = cols;
-  const uint32_t fmt = dtype == ST_F16 ? 0u : (dtype == ST_BF16 ? 1u : 2u);
-  p->idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p->b_mn_major << 16) | ((uint32_t)(c_acc >> 3) << 17) |
-             ((uint32_t)(tc::kTileM >> 4) << 24);
-  p->out_kind = dtype;
-  p->n_tiles = (n_rows + tc::kTileM - 1) / tc::kTileM;
-  return true;
-}
-
-
 static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* w, void* out, int64_t n_rows,
                          int64_t n_src, int K, int c_red, int c_acc, bool w_transposed) {
   const int es = dtype == ST_F32 ? 4 : 2;
@@ -1131,64 +880,78 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   return true;
 }
 
-static int g_gather_version = 2;
-void tc_set_gather_version(int v) { g_gather_version = v; }
+template <typename Map>
+static int launch_gather(const tc::Params2& p, const Map& map, cudaStream_t stream) {
+  const size_t smem = (size_t)p.w_slots * p.w_slot_bytes + (size_t)p.a_stages * tc::kABlockBytes +
+                      tc::kIdxTileBytes + sizeof(tc::Control2) + 1024;
+  auto kernel = p.esize == 2 ? tc::gather2_kernel<Map, 2> : tc::gather2_kernel<Map, 4>;
+  static bool configured[2] = {false, false};            // one pair per Map instantiation
+  if (!configured[p.esize == 4]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) {
+      set_error("tc gather: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
+      return ST_ERR_CUDA;
+    }
+    configured[p.esize == 4] = true;
+  }
+  int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
+  kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, map);
+  note_launches(1);
+  return check_launch("tc gather");
+}
 
-static int tc_conv_gather2(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
-                           int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream) {
+int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
+                   int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream) {
   tc::Params2 p;
   if (!fill_params2(&p, dtype, in, w, out, n_rows, n_src, K, c_red, c_acc, w_transposed)) {
     set_error("tc_conv_gather: shape does not fit shared memory");
     return ST_ERR_UNSUPPORTED;
   }
   if (n_rows == 0) return ST_OK;
-  const size_t smem = (size_t)p.w_slots * p.w_slot_bytes + (size_t)p.a_stages * tc::kABlockBytes +
-                      tc::kIdxTileBytes + sizeof(tc::Control2) + 1024;
-  auto kernel = p.esize == 2 ? tc::gather2_kernel<tc::StoredRows, 2> : tc::gather2_kernel<tc::StoredRows, 4>;
-  static bool configured[2] = {false, false};
-  if (!configured[p.esize == 4]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) {
-      set_error("tc_conv_gather: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
-      return ST_ERR_CUDA;
-    }
-    configured[p.esize == 4] = true;
-  }
-  int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
-  tc::StoredRows rows{map, K};
-  kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, rows);
-  note_launches(1);
-  return check_launch("tc_conv_gather");
+  return launch_gather(p, tc::StoredRows{map, K}, stream);
 }
 
-int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
-                   int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream) {
-  if (g_gather_version == 2)
-    return tc_conv_gather2(dtype, in, w, map, out, n_rows, n_src, K, c_red, c_acc, w_transposed, stream);
-  tc::Params p;
-  if (!fill_params(&p, dtype, in, w, out, n_rows, n_src, K, c_red, c_acc, w_transposed)) {
-    set_error("tc_conv_gather: shape does not fit the shared-memory ring");
+template <typename CT>
+static tc::HashRows<CT> make_hash_rows(const HashFlyArgs& h) {
+  tc::HashRows<CT> m;
+  m.coords = static_cast<const CT*>(h.coords);
+  m.off = *h.offsets;
+  m.table = make_table(h.keys, h.vals, h.capacity);
+  m.shape = Int3{h.shape[0], h.shape[1], h.shape[2]};
+  m.stride = h.stride;
+  return m;
+}
+
+int tc_conv_gather_hashfly(int dtype, const void* in, const void* w, const HashFlyArgs& h, void* out, int64_t n_rows,
+                           int64_t n_src, int K, int c_red, int c_acc, cudaStream_t stream) {
+  tc::Params2 p;
+  if (!fill_params2(&p, dtype, in, w, out, n_rows, n_src, K, c_red, c_acc, /*w_transposed=*/false)) {
+    set_error("tc_conv_gather_hashfly: shape does not fit shared memory");
     return ST_ERR_UNSUPPORTED;
   }
   if (n_rows == 0) return ST_OK;
-  const size_t smem = (size_t)p.stages * p.stage_bytes + sizeof(tc::Control) + 1024;
-  auto kernel = tc::gather_kernel<tc::StoredRows>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) {
-      set_error("tc_conv_gather: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
-      return ST_ERR_CUDA;
-    }
-    configured = true;
-  }
-  int64_t grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
-  tc::StoredRows rows{map, K};
-  kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, rows);
-  note_launches(1);
-  return check_launch("tc_conv_gather");
+  if (h.coord_dtype == ST_I32) return launch_gather(p, make_hash_rows<int32_t>(h), stream);
+  return launch_gather(p, make_hash_rows<int16_t>(h), stream);
 }
 
+// Inverse rule for the feature gradient without a stored map: input row i (table-space coordinate
+// q_i) receives from output o = (q_i + off_k) / stride when that division is exact and o exists.
+int tc_conv_dgrad_inverse(int dtype, const void* dy, const void* w, const int32_t* q_coords, const Offsets& off,
+                          const int64_t* out_keys, const int32_t* out_vals, int64_t out_capacity, int stride, void* dx,
+                          int64_t n_in, int64_t n_out, int K, int cin, int cout, cudaStream_t stream) {
+  tc::Params2 p;
+  if (!fill_params2(&p, dtype, dy, w, dx, n_in, n_out, K, cout, cin, /*w_transposed=*/true)) {
+    set_error("tc_conv_dgrad_inverse: shape does not fit shared memory");
+    return ST_ERR_UNSUPPORTED;
+  }
+  if (n_in == 0) return ST_OK;
+  tc::InverseRows m;
+  m.q = q_coords;
+  m.off = off;
+  m.table = make_table(out_keys, out_vals, out_capacity);
+  m.stride = stride;
+  return launch_gather(p, m, stream);
+}
 
 // ------------------------------------------------------------------------------------------- wgrad
 struct WgradPlan {
@@ -1252,33 +1015,53 @@ int64_t tc_wgrad_partial_bytes(int dtype, int64_t n_rows, int K, int cin, int co
   return (int64_t)plan.n_chunks * K * cin * cout * 4;
 }
 
-int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, float* partial, int* n_chunks_out,
-                  int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream) {
-  WgradPlan plan;
-  if (!plan_wgrad(&plan, dtype, n_rows, K, cin, cout)) {
-    set_error("tc_conv_wgrad: unsupported shape");
-    return ST_ERR_UNSUPPORTED;
-  }
-  plan.p.x = x;
-  plan.p.dy = dy;
-  plan.p.partial = partial;
-  plan.p.n_src = n_src;
-  auto kernel = tc::wgrad_kernel<tc::StoredRows>;
-  static bool configured = false;
+template <typename Map>
+static int launch_wgrad(WgradPlan& plan, const Map& map, cudaStream_t stream) {
+  auto kernel = tc::wgrad_kernel<Map>;
+  static bool configured = false;                        // one per Map instantiation
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) {
-      set_error("tc_conv_wgrad: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
+      set_error("tc wgrad: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
       return ST_ERR_CUDA;
     }
     configured = true;
   }
   dim3 grid((unsigned)plan.n_chunks, (unsigned)plan.p.n_kgroups, (unsigned)(plan.p.n_coblk * plan.p.n_ciblk));
-  tc::StoredRows rows{map, K};
-  kernel<<<grid, tc::kThreads, plan.smem, stream>>>(plan.p, rows);
+  kernel<<<grid, tc::kThreads, plan.smem, stream>>>(plan.p, map);
   note_launches(1);
+  return check_launch("tc wgrad");
+}
+
+static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void* dy, float* partial, int64_t n_rows,
+                          int64_t n_src, int K, int cin, int cout) {
+  if (!plan_wgrad(plan, dtype, n_rows, K, cin, cout)) {
+    set_error("tc wgrad: unsupported shape");
+    return false;
+  }
+  plan->p.x = x;
+  plan->p.dy = dy;
+  plan->p.partial = partial;
+  plan->p.n_src = n_src;
+  return true;
+}
+
+int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, float* partial, int* n_chunks_out,
+                  int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream) {
+  WgradPlan plan;
+  if (!prepare_wgrad(&plan, dtype, x, dy, partial, n_rows, n_src, K, cin, cout)) return ST_ERR_UNSUPPORTED;
   *n_chunks_out = plan.n_chunks;
-  return check_launch("tc_conv_wgrad");
+  return launch_wgrad(plan, tc::StoredRows{map, K}, stream);
+}
+
+int tc_conv_wgrad_hashfly(int dtype, const void* x, const void* dy, const HashFlyArgs& h, float* partial,
+                          int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout,
+                          cudaStream_t stream) {
+  WgradPlan plan;
+  if (!prepare_wgrad(&plan, dtype, x, dy, partial, n_rows, n_src, K, cin, cout)) return ST_ERR_UNSUPPORTED;
+  *n_chunks_out = plan.n_chunks;
+  if (h.coord_dtype == ST_I32) return launch_wgrad(plan, make_hash_rows<int32_t>(h), stream);
+  return launch_wgrad(plan, make_hash_rows<int16_t>(h), stream);
 }
 
 int tc_read_prof(long long* host_out, int n) {

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "common.cuh"
+
 namespace st {
 
 // True if the tcgen05 gather kernel handles a product with c_red reduction channels and c_acc
@@ -11,14 +13,35 @@ namespace st {
 bool tc_supported(int dtype, int c_red, int c_acc);
 // Process-wide switch: when off, tc_supported() answers false and the CUDA-core kernels run.
 void tc_set_enabled(bool on);
-// Which form of the gather kernel runs (1: W copied per row tile, 2: W shared by several row tiles).
-void tc_set_gather_version(int v);
 
 // OUT[r,:] = sum_k IN[map[r,k],:] . B_k over a stored (n_rows, K) map.
 //   w_transposed = false: B_k = W[k]   with W (K, c_red, c_acc)   (forward)
 //   w_transposed = true : B_k = W[k]^T with W (K, c_acc, c_red)   (dgrad over the inverse map)
 int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
                    int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream);
+
+// Arguments of the hash-on-the-fly forms.
+struct HashFlyArgs {
+  const void* coords;      // (n_rows, 4) output coordinates
+  int coord_dtype;         // ST_I16 / ST_I32
+  const Offsets* offsets;
+  const int64_t* keys;     // table over the (possibly scaled) input coordinates
+  const int32_t* vals;
+  int64_t capacity;
+  const int32_t* shape;    // host, 3 values
+  int stride;
+};
+
+// Forward over the table probed on the fly.
+int tc_conv_gather_hashfly(int dtype, const void* in, const void* w, const HashFlyArgs& h, void* out, int64_t n_rows,
+                           int64_t n_src, int K, int c_red, int c_acc, cudaStream_t stream);
+// Feature gradient without a stored map, gather form over a table of the OUTPUT coordinates.
+int tc_conv_dgrad_inverse(int dtype, const void* dy, const void* w, const int32_t* q_coords, const Offsets& off,
+                          const int64_t* out_keys, const int32_t* out_vals, int64_t out_capacity, int stride, void* dx,
+                          int64_t n_in, int64_t n_out, int K, int cin, int cout, cudaStream_t stream);
+int tc_conv_wgrad_hashfly(int dtype, const void* x, const void* dy, const HashFlyArgs& h, float* partial,
+                          int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout,
+                          cudaStream_t stream);
 
 // Tensor-core weight gradient: fills fp32 partials (n_chunks, K, cin, cout) that the caller reduces.
 bool tc_wgrad_supported(int dtype, int64_t n_rows, int K, int cin, int cout);

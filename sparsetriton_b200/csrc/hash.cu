@@ -59,6 +59,40 @@ hash_query_kernel(const CT* __restrict__ coords, int64_t m, Table table, int32_t
   out[i] = r;
 }
 
+// q[row] = coordinate stored in the table for that row (int32 x 4); rows absent from the table keep
+// batch = -1.  Recovers per-row coordinates from a table when only the table is at hand.
+__global__ void __launch_bounds__(kThreads)
+table_rows_init_kernel(int4* q, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i < n) q[i] = make_int4(-1, 0, 0, 0);
+}
+
+__global__ void __launch_bounds__(kThreads)
+table_unpack_kernel(const unsigned long long* __restrict__ keys, const int32_t* __restrict__ vals, int64_t capacity,
+                    int4* q, int64_t n) {
+  int64_t s = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (s >= capacity) return;
+  const unsigned long long k = keys[s];
+  const int32_t v = vals[s];
+  if (k == kEmptyKey || v < 0 || v >= n) return;
+  q[v] = make_int4((int)(k >> 48), (int)((k >> 32) & 0xFFFF), (int)((k >> 16) & 0xFFFF), (int)(k & 0xFFFF));
+}
+
+int unpack_table_coords(const int64_t* keys, const int32_t* vals, int64_t capacity, int32_t* q, int64_t n,
+                        cudaStream_t stream) {
+  if (n > 0) {
+    table_rows_init_kernel<<<(unsigned)((n + kThreads - 1) / kThreads), kThreads, 0, stream>>>(
+        reinterpret_cast<int4*>(q), n);
+    note_launches(1);
+  }
+  if (n > 0 && capacity > 0) {
+    table_unpack_kernel<<<(unsigned)((capacity + kThreads - 1) / kThreads), kThreads, 0, stream>>>(
+        reinterpret_cast<const unsigned long long*>(keys), vals, capacity, reinterpret_cast<int4*>(q), n);
+    note_launches(1);
+  }
+  return check_launch("unpack_table_coords");
+}
+
 }  // namespace st
 
 using namespace st;

@@ -112,6 +112,16 @@ int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int
                        int64_t workspace_bytes, void* out_coords, int64_t out_capacity, int32_t* status,
                        void* stream);
 
+/* Pass 3 (optional): the neighbour map of the same convolution, nbr (n_out, K) int32, produced by a
+ * scatter over the surviving candidates -- candidate (n, k) lands on output row o, so nbr[o,k] = n --
+ * instead of n_out*K probes of the input table.  Equals st_map_build on the written coordinates.
+ * in_shape_host: the input grid (inputs outside it get no map entry, as with the probing form).
+ * Must follow st_outcoords_write on the same stream with the same arguments and workspace.
+ * Replaces compute_neighbor_indices for strided / transposed layers, nn/functional/conv/conv.py:12-75. */
+int st_outcoords_map(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K, int stride,
+                     int transposed, const int32_t* new_shape_host, const int32_t* in_shape_host, void* workspace,
+                     int64_t workspace_bytes, int32_t* nbr, int64_t n_out, void* stream);
+
 /* ---------------------------------------------------------------- neighbour map ---------- */
 
 /* nbr[o,k] = row of (batch, out*lookup_stride - off[k]) if inside [0,lookup_shape) and present.

@@ -36,6 +36,7 @@ _SIGNATURES = {
     "st_outcoords_workspace_bytes": ([_I64, _INT, _INT, _INT], _I64),
     "st_outcoords_count": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _I64, _PTR, _PTR, _PTR], _INT),
     "st_outcoords_write": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _I64, _PTR, _I64, _PTR, _PTR], _INT),
+    "st_outcoords_map": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _I64, _PTR], _INT),
     "st_map_build": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
     "st_map_invert": ([_PTR, _I64, _INT, _I64, _PTR, _PTR], _INT),
     "st_map_pairs_workspace_bytes": ([_I64, _INT], _I64),

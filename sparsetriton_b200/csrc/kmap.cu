@@ -1,10 +1,11 @@
 // Kernel-map construction: output coordinates of strided / transposed convolutions, the dense
 // output-stationary neighbour map, its inverse, and its compaction into (in, out, offset) triples.
 //
-// All kernels enumerate the flat index t = row * K + k with one thread per t, so a warp sweeps the
-// offsets of one or two voxels, coordinate loads are warp-wide broadcasts and every write of the
-// (rows, K) tables is coalesced.  Order-defining steps (which duplicate survives, where a row
-// lands) are functions of t only, so results do not depend on scheduling.
+// The map kernels enumerate the flat index t = row * K + k with one thread per t, so a warp sweeps
+// the offsets of one or two voxels, coordinate loads are warp-wide broadcasts and every write of the
+// (rows, K) tables is coalesced; the output-coordinate kernels give each input row one thread that
+// loops over its K offsets.  Order-defining steps (which duplicate survives, where a row lands) are
+// functions of t only, so results do not depend on scheduling.
 #include "common.cuh"
 
 namespace st {
@@ -43,19 +44,39 @@ __device__ __forceinline__ bool candidate(const int4& c, const Offsets& off, int
   return true;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Output coordinates.  One thread per input row sweeps the K offsets of its row.
+//
+//   count   candidates that survive the stride / range filters -> scratch-table capacity, chosen ON
+//           THE DEVICE as the power of two >= 1.5 x candidates (the host only reserves the worst case)
+//   insert  exact-key open addressing; atomicMin keeps the smallest flat index n*K+k per coordinate
+//   mark    a candidate wins if it holds that smallest index; K win bits and a win count per row
+//   scan    exclusive prefix sum of the per-row counts = first output row of each input row
+//   write   winners store their coordinate (ordered by flat index) and leave their output row in the
+//           table slot, so that the neighbour map can be produced by a scatter over the same
+//           candidates instead of N_out*K probes of the input table (st_outcoords_map)
+// ---------------------------------------------------------------------------------------------
+constexpr int kRowThreads = 256;
+
+struct OutCoordsHeader {                 // first 256 bytes of the workspace
+  unsigned long long n_candidates;
+  uint32_t capacity;                     // power of two
+  uint32_t pad;
+};
+
 struct OutCoordsWorkspace {
-  unsigned long long* keys;  // scratch table keys
-  uint32_t* min_flat;        // smallest flat candidate index per key
-  uint32_t* win_bits;        // one ballot word per warp of candidates
-  uint32_t* block_counts;    // winners per block, then exclusive offsets
+  OutCoordsHeader* header;
+  unsigned long long* keys;              // scratch table keys
+  uint32_t* slot_value;                  // smallest flat candidate index per key; after `write`: output row
+  uint32_t* win_words;                   // (n, words) win bits of each input row
+  uint32_t* row_counts;                  // wins per input row, then their exclusive prefix sum
   void* scan_tmp;
-  uint32_t capacity;         // power of two
-  int64_t n_flat;
-  int64_t n_blocks;
+  int64_t capacity_max;                  // slots reserved (worst case)
+  int words;                             // ceil(K / 32)
 };
 
 static int64_t scratch_capacity(int64_t n, int K, int stride, int transposed) {
-  // candidates that can pass the stride filter per input: ceil(ks/stride)^3 <= K; use K when unknown
+  // candidates that can pass the stride filter per input: ceil(ks/stride)^3 <= K
   int64_t per_input = K;
   if (!transposed && stride > 1) {
     int ks = 1;
@@ -63,141 +84,205 @@ static int64_t scratch_capacity(int64_t n, int K, int stride, int transposed) {
     int64_t c = (ks + stride - 1) / stride;
     per_input = c * c * c;
   }
-  int64_t want = 2 * n * per_input;
+  int64_t want = (3 * n * per_input + 1) / 2;
   int64_t cap = 1024;
   while (cap < want) cap <<= 1;
   return cap;
 }
 
+static int64_t outcoords_bytes(int64_t n, int K, int stride, int transposed) {
+  const int64_t cap = scratch_capacity(n, K, stride, transposed);
+  const int words = (K + 31) / 32;
+  return 256 + align_up(cap * 8, 256) + align_up(cap * 4, 256) + align_up(n * words * 4, 256) +
+         align_up(n * 4, 256) + scan_tmp_bytes(n) + 256;
+}
+
 static bool carve(void* workspace, int64_t bytes, int64_t n, int K, int stride, int transposed,
                   OutCoordsWorkspace* w) {
-  int64_t cap = scratch_capacity(n, K, stride, transposed);
-  int64_t n_flat = n * K;
-  int64_t n_blocks = (n_flat + kBlock - 1) / kBlock;
+  const int64_t cap = scratch_capacity(n, K, stride, transposed);
+  w->words = (K + 31) / 32;
   char* p = static_cast<char*>(workspace);
   char* end = p + bytes;
+  w->header = reinterpret_cast<OutCoordsHeader*>(p);
+  p += 256;
   w->keys = reinterpret_cast<unsigned long long*>(p);
   p += align_up(cap * 8, 256);
-  w->min_flat = reinterpret_cast<uint32_t*>(p);
+  w->slot_value = reinterpret_cast<uint32_t*>(p);
   p += align_up(cap * 4, 256);
-  w->win_bits = reinterpret_cast<uint32_t*>(p);
-  p += align_up(n_blocks * (kBlock / 32) * 4, 256);
-  w->block_counts = reinterpret_cast<uint32_t*>(p);
-  p += align_up(n_blocks * 4, 256);
+  w->win_words = reinterpret_cast<uint32_t*>(p);
+  p += align_up(n * w->words * 4, 256);
+  w->row_counts = reinterpret_cast<uint32_t*>(p);
+  p += align_up(n * 4, 256);
   w->scan_tmp = p;
-  p += scan_tmp_bytes(n_blocks);
-  w->capacity = (uint32_t)cap;
-  w->n_flat = n_flat;
-  w->n_blocks = n_blocks;
+  p += scan_tmp_bytes(n);
+  w->capacity_max = cap;
   return p <= end && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0;
 }
 
-__global__ void __launch_bounds__(256)
-scratch_clear_kernel(unsigned long long* keys, uint32_t* min_flat, uint32_t capacity) {
-  uint32_t i = blockIdx.x * 256u + threadIdx.x;
-  if (i < capacity) {
-    keys[i] = kEmptyKey;
-    min_flat[i] = 0xFFFFFFFFu;
+template <typename CT>
+__global__ void __launch_bounds__(kRowThreads)
+outcoords_count_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
+                       Int3 new_shape, OutCoordsHeader* header) {
+  const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  int cnt = 0;
+  if (row < n) {
+    const int4 c = load_coord<CT>(coords, row);
+    Int3 v;
+    for (int k = 0; k < K; ++k) cnt += candidate(c, off, k, stride, transposed, new_shape, &v) ? 1 : 0;
+  }
+  // block sum -> one atomic per block
+  __shared__ int warp_sum[kRowThreads / 32];
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) cnt += __shfl_down_sync(0xFFFFFFFFu, cnt, d);
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int total = 0;
+    for (int i = 0; i < kRowThreads / 32; ++i) total += warp_sum[i];
+    if (total) atomicAdd(&header->n_candidates, (unsigned long long)total);
   }
 }
 
-// Pass A: insert every surviving candidate, keep the smallest flat index per coordinate.
-template <typename CT>
-__global__ void __launch_bounds__(kBlock)
-outcoords_insert_kernel(const CT* __restrict__ coords, int64_t n_flat, int K, Offsets off, int stride,
-                        bool transposed, Int3 new_shape, unsigned long long* keys, uint32_t* min_flat,
-                        uint32_t capacity, int32_t* status) {
-  int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x;
-  if (t >= n_flat) return;
-  uint32_t row = (uint32_t)(t / K);
-  int k = (int)(t - (int64_t)row * K);
-  int4 c = load_coord<CT>(coords, row);
-  Int3 v;
-  if (!candidate(c, off, k, stride, transposed, new_shape, &v)) return;
-  unsigned long long key = pack_key(c.x, v.x, v.y, v.z);
-  uint32_t mask = capacity - 1;
+__global__ void outcoords_capacity_kernel(OutCoordsHeader* header, unsigned long long capacity_max) {
+  unsigned long long want = (3 * header->n_candidates + 1) / 2;
+  unsigned long long cap = 1024;
+  while (cap < want && cap < capacity_max) cap <<= 1;
+  header->capacity = (uint32_t)cap;
+}
+
+__global__ void __launch_bounds__(256)
+scratch_clear_kernel(const OutCoordsHeader* header, unsigned long long* keys, uint32_t* slot_value) {
+  const uint32_t capacity = header->capacity;
+  for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < capacity; i += gridDim.x * 256u) {
+    keys[i] = kEmptyKey;
+    slot_value[i] = 0xFFFFFFFFu;
+  }
+}
+
+// Slot of `key`, inserting it if absent; capacity is a power of two.  Returns 0xFFFFFFFF when full.
+__device__ __forceinline__ uint32_t scratch_insert(unsigned long long* keys, uint32_t capacity, unsigned long long key) {
+  const uint32_t mask = capacity - 1;
   uint32_t slot = mix_key(key) & mask;
   for (uint32_t step = 0; step < capacity; ++step) {
     unsigned long long seen = keys[slot];
     if (seen == kEmptyKey) seen = atomicCAS(keys + slot, kEmptyKey, key);
-    if (seen == kEmptyKey || seen == key) {
-      atomicMin(min_flat + slot, (uint32_t)t);
-      return;
-    }
+    if (seen == kEmptyKey || seen == key) return slot;
     slot = (slot + 1) & mask;
   }
-  atomicOr(status, ST_DEV_TABLE_FULL);
+  return 0xFFFFFFFFu;
 }
 
-// Pass B: a candidate wins if it holds the smallest flat index of its coordinate.
+__device__ __forceinline__ uint32_t scratch_find(const unsigned long long* keys, uint32_t capacity,
+                                                 unsigned long long key) {
+  const uint32_t mask = capacity - 1;
+  uint32_t slot = mix_key(key) & mask;
+  for (uint32_t step = 0; step < capacity; ++step) {
+    const unsigned long long seen = keys[slot];
+    if (seen == key) return slot;
+    if (seen == kEmptyKey) return 0xFFFFFFFFu;
+    slot = (slot + 1) & mask;
+  }
+  return 0xFFFFFFFFu;
+}
+
 template <typename CT>
-__global__ void __launch_bounds__(kBlock)
-outcoords_mark_kernel(const CT* __restrict__ coords, int64_t n_flat, int K, Offsets off, int stride,
-                      bool transposed, Int3 new_shape, const unsigned long long* __restrict__ keys,
-                      const uint32_t* __restrict__ min_flat, uint32_t capacity, uint32_t* win_bits,
-                      uint32_t* block_counts) {
-  int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x;
-  bool win = false;
-  if (t < n_flat) {
-    uint32_t row = (uint32_t)(t / K);
-    int k = (int)(t - (int64_t)row * K);
-    int4 c = load_coord<CT>(coords, row);
+__global__ void __launch_bounds__(kRowThreads)
+outcoords_insert_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
+                        Int3 new_shape, const OutCoordsHeader* header, unsigned long long* keys,
+                        uint32_t* slot_value, int32_t* status) {
+  const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if (row >= n) return;
+  const uint32_t capacity = header->capacity;
+  const int4 c = load_coord<CT>(coords, row);
+  const uint32_t flat0 = (uint32_t)row * (uint32_t)K;
+  for (int k = 0; k < K; ++k) {
     Int3 v;
-    if (candidate(c, off, k, stride, transposed, new_shape, &v)) {
-      unsigned long long key = pack_key(c.x, v.x, v.y, v.z);
-      uint32_t mask = capacity - 1;
-      uint32_t slot = mix_key(key) & mask;
-      for (uint32_t step = 0; step < capacity; ++step) {
-        unsigned long long seen = keys[slot];
-        if (seen == key) {
-          win = (min_flat[slot] == (uint32_t)t);
-          break;
-        }
-        if (seen == kEmptyKey) break;  // cannot happen after pass A unless the table overflowed
-        slot = (slot + 1) & mask;
-      }
+    if (!candidate(c, off, k, stride, transposed, new_shape, &v)) continue;
+    const uint32_t slot = scratch_insert(keys, capacity, pack_key(c.x, v.x, v.y, v.z));
+    if (slot == 0xFFFFFFFFu) {
+      atomicOr(status, ST_DEV_TABLE_FULL);
+      return;
     }
+    atomicMin(slot_value + slot, flat0 + (uint32_t)k);
   }
-  uint32_t bits = __ballot_sync(0xFFFFFFFFu, win);
-  if ((threadIdx.x & 31) == 0) win_bits[(int64_t)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5)] = bits;
-  int total = __syncthreads_count(win);
-  if (threadIdx.x == 0) block_counts[blockIdx.x] = (uint32_t)total;
 }
 
-// Pass C: winners write their coordinate at (block offset + rank inside the block).
 template <typename CT>
-__global__ void __launch_bounds__(kBlock)
-outcoords_write_kernel(const CT* __restrict__ coords, int64_t n_flat, int K, Offsets off, int stride,
-                       bool transposed, Int3 new_shape, const uint32_t* __restrict__ win_bits,
-                       const uint32_t* __restrict__ block_offsets, CT* out, int64_t out_capacity,
-                       int32_t* status) {
-  __shared__ uint32_t warp_offset[kBlock / 32];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t bits = win_bits[(int64_t)blockIdx.x * (kBlock / 32) + warp];
-  if (warp == 0) {
-    uint32_t cnt = __popc(win_bits[(int64_t)blockIdx.x * (kBlock / 32) + lane]);
-    uint32_t incl = cnt;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      uint32_t x = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-      if (lane >= d) incl += x;
+__global__ void __launch_bounds__(kRowThreads)
+outcoords_mark_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
+                      Int3 new_shape, const OutCoordsHeader* header, const unsigned long long* keys,
+                      const uint32_t* slot_value, uint32_t* win_words, int words, uint32_t* row_counts) {
+  const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if (row >= n) return;
+  const uint32_t capacity = header->capacity;
+  const int4 c = load_coord<CT>(coords, row);
+  const uint32_t flat0 = (uint32_t)row * (uint32_t)K;
+  uint32_t count = 0;
+  for (int w = 0; w < words; ++w) {
+    uint32_t bits = 0;
+    const int k_end = min(K, (w + 1) * 32);
+    for (int k = w * 32; k < k_end; ++k) {
+      Int3 v;
+      if (!candidate(c, off, k, stride, transposed, new_shape, &v)) continue;
+      const uint32_t slot = scratch_find(keys, capacity, pack_key(c.x, v.x, v.y, v.z));
+      if (slot != 0xFFFFFFFFu && slot_value[slot] == flat0 + (uint32_t)k) bits |= 1u << (k & 31);
     }
-    warp_offset[lane] = incl - cnt;
+    win_words[row * words + w] = bits;
+    count += __popc(bits);
   }
-  __syncthreads();
-  if (!((bits >> lane) & 1u)) return;
-  int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x;
-  int64_t dst = (int64_t)block_offsets[blockIdx.x] + warp_offset[warp] + __popc(bits & ((1u << lane) - 1u));
-  if (dst >= out_capacity) {
-    atomicOr(status, ST_DEV_OUT_OVERFLOW);
-    return;
+  row_counts[row] = count;
+}
+
+template <typename CT>
+__global__ void __launch_bounds__(kRowThreads)
+outcoords_write_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
+                       Int3 new_shape, const OutCoordsHeader* header, const unsigned long long* keys,
+                       uint32_t* slot_value, const uint32_t* __restrict__ win_words, int words,
+                       const uint32_t* __restrict__ row_offsets, CT* out, int64_t out_capacity, int32_t* status) {
+  const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if (row >= n) return;
+  const uint32_t capacity = header->capacity;
+  const int4 c = load_coord<CT>(coords, row);
+  int64_t dst = row_offsets[row];
+  for (int w = 0; w < words; ++w) {
+    uint32_t bits = win_words[row * words + w];
+    while (bits) {
+      const int k = w * 32 + __ffs(bits) - 1;
+      bits &= bits - 1;
+      Int3 v;
+      candidate(c, off, k, stride, transposed, new_shape, &v);
+      if (dst >= out_capacity) {
+        atomicOr(status, ST_DEV_OUT_OVERFLOW);
+        return;
+      }
+      store_coord<CT>(out, dst, c.x, v.x, v.y, v.z);
+      const uint32_t slot = scratch_find(keys, capacity, pack_key(c.x, v.x, v.y, v.z));
+      if (slot != 0xFFFFFFFFu) slot_value[slot] = (uint32_t)dst;      // the coordinate's output row
+      ++dst;
+    }
   }
-  uint32_t row = (uint32_t)(t / K);
-  int k = (int)(t - (int64_t)row * K);
-  int4 c = load_coord<CT>(coords, row);
-  Int3 v;
-  candidate(c, off, k, stride, transposed, new_shape, &v);
-  store_coord<CT>(out, dst, c.x, v.x, v.y, v.z);
+}
+
+// nbr[out_row(candidate), k] = max(input row): the neighbour map by scatter.  nbr must hold -1.
+template <typename CT>
+__global__ void __launch_bounds__(kRowThreads)
+outcoords_map_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
+                     Int3 new_shape, Int3 in_shape, const OutCoordsHeader* header, const unsigned long long* keys,
+                     const uint32_t* slot_value, int32_t* nbr, int64_t n_out) {
+  const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if (row >= n) return;
+  const uint32_t capacity = header->capacity;
+  const int4 c = load_coord<CT>(coords, row);
+  // an input outside its own grid is never found by the bounds-checked lookup of the probing form
+  if (c.y < 0 || c.y >= in_shape.x || c.z < 0 || c.z >= in_shape.y || c.w < 0 || c.w >= in_shape.z) return;
+  for (int k = 0; k < K; ++k) {
+    Int3 v;
+    if (!candidate(c, off, k, stride, transposed, new_shape, &v)) continue;
+    const uint32_t slot = scratch_find(keys, capacity, pack_key(c.x, v.x, v.y, v.z));
+    if (slot == 0xFFFFFFFFu) continue;
+    const uint32_t o = slot_value[slot];
+    if (o < (uint32_t)n_out) atomicMax(nbr + (int64_t)o * K + k, (int32_t)row);   // duplicate coordinates: largest row
+  }
 }
 
 // nbr[o,k] = row of (b, out*stride - off[k]) or -1.
@@ -281,15 +366,18 @@ pairs_write_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, const
 template <typename CT>
 static int outcoords_count_impl(const CT* coords, int64_t n, const Offsets& off, int K, int stride, bool transposed,
                                 Int3 ns, OutCoordsWorkspace& w, int64_t* n_out, int32_t* status, cudaStream_t s) {
-  { scratch_clear_kernel<<<(w.capacity + 255) / 256, 256, 0, s>>>(w.keys, w.min_flat, w.capacity); note_launches(1); }
-  { outcoords_insert_kernel<CT><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(coords, w.n_flat, K, off, stride, transposed,
-                                                                      ns, w.keys, w.min_flat, w.capacity, status); note_launches(1); }
-  { outcoords_mark_kernel<CT><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(coords, w.n_flat, K, off, stride, transposed, ns,
-                                                                    w.keys, w.min_flat, w.capacity, w.win_bits,
-                                                                    w.block_counts); note_launches(1); }
+  const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
+  cudaMemsetAsync(w.header, 0, sizeof(OutCoordsHeader), s);
+  { outcoords_count_kernel<CT><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, w.header); note_launches(1); }
+  { outcoords_capacity_kernel<<<1, 1, 0, s>>>(w.header, (unsigned long long)w.capacity_max); note_launches(1); }
+  { scratch_clear_kernel<<<1184, 256, 0, s>>>(w.header, w.keys, w.slot_value); note_launches(1); }
+  { outcoords_insert_kernel<CT><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, w.header, w.keys,
+                                                             w.slot_value, status); note_launches(1); }
+  { outcoords_mark_kernel<CT><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, w.header, w.keys,
+                                                           w.slot_value, w.win_words, w.words, w.row_counts); note_launches(1); }
   int rc = check_launch("st_outcoords_count");
   if (rc != ST_OK) return rc;
-  return exclusive_scan_u32(w.block_counts, w.block_counts, w.n_blocks, w.scan_tmp, n_out, s);
+  return exclusive_scan_u32(w.row_counts, w.row_counts, n, w.scan_tmp, n_out, s);
 }
 
 }  // namespace st
@@ -330,10 +418,7 @@ extern "C" {
 
 int64_t st_outcoords_workspace_bytes(int64_t n, int K, int stride, int transposed) {
   if (n <= 0 || K < 1) return 256;
-  int64_t cap = scratch_capacity(n, K, stride, transposed);
-  int64_t n_blocks = (n * K + kBlock - 1) / kBlock;
-  return align_up(cap * 8, 256) + align_up(cap * 4, 256) + align_up(n_blocks * (kBlock / 32) * 4, 256) +
-         align_up(n_blocks * 4, 256) + scan_tmp_bytes(n_blocks) + 256;
+  return outcoords_bytes(n, K, stride, transposed);
 }
 
 int st_outcoords_count(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K, int stride,
@@ -373,15 +458,50 @@ int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int
   if (rc != ST_OK) return rc;
   if (n == 0) return ST_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  if (coord_dtype == ST_I32)
-    { outcoords_write_kernel<int32_t><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(
-        static_cast<const int32_t*>(coords), w.n_flat, K, off, stride, transposed != 0, ns, w.win_bits,
-        w.block_counts, static_cast<int32_t*>(out_coords), out_capacity, status); note_launches(1); }
-  else
-    { outcoords_write_kernel<int16_t><<<(unsigned)w.n_blocks, kBlock, 0, s>>>(
-        static_cast<const int16_t*>(coords), w.n_flat, K, off, stride, transposed != 0, ns, w.win_bits,
-        w.block_counts, static_cast<int16_t*>(out_coords), out_capacity, status); note_launches(1); }
+  const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
+  if (coord_dtype == ST_I32) {
+    outcoords_write_kernel<int32_t><<<grid, kRowThreads, 0, s>>>(
+        static_cast<const int32_t*>(coords), n, K, off, stride, transposed != 0, ns, w.header, w.keys, w.slot_value,
+        w.win_words, w.words, w.row_counts, static_cast<int32_t*>(out_coords), out_capacity, status);
+  } else {
+    outcoords_write_kernel<int16_t><<<grid, kRowThreads, 0, s>>>(
+        static_cast<const int16_t*>(coords), n, K, off, stride, transposed != 0, ns, w.header, w.keys, w.slot_value,
+        w.win_words, w.words, w.row_counts, static_cast<int16_t*>(out_coords), out_capacity, status);
+  }
+  note_launches(1);
   return check_launch("st_outcoords_write");
+}
+
+int st_outcoords_map(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K, int stride,
+                     int transposed, const int32_t* new_shape_host, const int32_t* in_shape_host, void* workspace,
+                     int64_t workspace_bytes, int32_t* nbr, int64_t n_out, void* stream) {
+  Offsets off;
+  Int3 ns;
+  OutCoordsWorkspace w;
+  if (n_out < 0 || (n_out > 0 && !nbr) || !in_shape_host) {
+    set_error("st_outcoords_map: bad output arguments");
+    return ST_ERR_ARG;
+  }
+  int rc = outcoords_args(coords, n, coord_dtype, offsets_host, K, stride, new_shape_host, workspace,
+                          workspace_bytes, transposed, &off, &ns, &w, "st_outcoords_map");
+  if (rc != ST_OK) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t n_map = n_out * K;
+  if (n_map > 0) { fill_i32_kernel<<<(unsigned)((n_map + 255) / 256), 256, 0, s>>>(nbr, n_map, -1); note_launches(1); }
+  if (n == 0 || n_out == 0) return check_launch("st_outcoords_map");
+  const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
+  const Int3 in_shape = {in_shape_host[0], in_shape_host[1], in_shape_host[2]};
+  if (coord_dtype == ST_I32) {
+    outcoords_map_kernel<int32_t><<<grid, kRowThreads, 0, s>>>(static_cast<const int32_t*>(coords), n, K, off, stride,
+                                                               transposed != 0, ns, in_shape, w.header, w.keys,
+                                                               w.slot_value, nbr, n_out);
+  } else {
+    outcoords_map_kernel<int16_t><<<grid, kRowThreads, 0, s>>>(static_cast<const int16_t*>(coords), n, K, off, stride,
+                                                               transposed != 0, ns, in_shape, w.header, w.keys,
+                                                               w.slot_value, nbr, n_out);
+  }
+  note_launches(1);
+  return check_launch("st_outcoords_map");
 }
 
 int st_map_build(const void* out_coords, int64_t n_out, int coord_dtype, const int32_t* offsets_host, int K,

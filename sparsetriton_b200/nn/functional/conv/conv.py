@@ -14,7 +14,7 @@ from sparsetriton_b200.tensor import SparseTensor
 from sparsetriton_b200.utils.hash import HashTable, round_up_capacity
 
 from .funcs import ConvHashOnTheFlyImplicitGEMM, ConvPrecomputedNeighborGEMM
-from .kmap import build_out_coords, kernel_offsets
+from .kmap import build_out_coords, kernel_offsets, out_coords_and_map
 
 __all__ = ["compute_neighbor_indices", "sparse_conv3d"]
 
@@ -107,9 +107,17 @@ def sparse_conv3d(
     upsample = transposed and s > 1
 
     cached = cache.neighbor_indices.get(cache_key) if algo == ConvAlgo.PrecomputedNeighborGEMM else None
+    shortcut = submanifold and s == 1                       # output coordinates are the input coordinates
+    neighbor_indices = table = koff = None
     if cached is not None:
         out_coords, neighbor_indices, new_shape = cached
-        table = None
+    elif algo == ConvAlgo.PrecomputedNeighborGEMM and not shortcut:
+        # strided / transposed layer with a stored map: coordinates and map come out of one pass over
+        # the candidates; no table over the inputs is needed
+        out_coords, new_shape, koff, neighbor_indices = out_coords_and_map(coords, tensor.spatial_shape, k, s, d, p,
+                                                                           transposed)
+        if out_coords.shape[0] > 0:
+            cache.neighbor_indices[cache_key] = (out_coords, neighbor_indices, new_shape)
     else:
         # Table over the coordinates the lookup is made in: the inputs themselves, or, for an
         # upsampling transposed conv, the inputs with their spatial columns scaled (conv.py:138-142).
@@ -135,7 +143,7 @@ def sparse_conv3d(
     lookup_stride = 1 if transposed else s
 
     if algo == ConvAlgo.PrecomputedNeighborGEMM:
-        if cached is None:
+        if neighbor_indices is None:
             neighbor_indices = compute_neighbor_indices(table, out_coords, koff, lookup_shape, lookup_stride, p, d)
             cache.neighbor_indices[cache_key] = (out_coords, neighbor_indices, new_shape)
         out_feats = ConvPrecomputedNeighborGEMM.apply(feats, weight, neighbor_indices)

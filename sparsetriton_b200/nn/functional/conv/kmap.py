@@ -20,7 +20,7 @@ import torch
 
 from sparsetriton_b200 import _lib, trace
 
-__all__ = ["build_out_coords", "kernel_offsets", "output_shape"]
+__all__ = ["build_out_coords", "out_coords_and_map", "kernel_offsets", "output_shape"]
 
 
 def kernel_offsets(kernel_size: int, dilation: int, padding: int, transposed: bool):
@@ -76,11 +76,30 @@ def build_out_coords(
 
     new_shape_t = torch.tensor(new_shape, device=device)
     new_shape_t._st_host = new_shape      # spares callers in this package a device->host read
-    n = in_coords.shape[0]
-    K = len(offsets)
-    if n == 0:
-        return torch.empty((0, 4), dtype=in_coords.dtype, device=device), new_shape_t, koff
+    out, _ = _run_out_coords(in_coords, offsets, new_shape, stride, transposed, with_map=False)
+    return out, new_shape_t, koff
 
+
+def out_coords_and_map(in_coords, spatial_shape, kernel_size, stride, dilation, padding, transposed):
+    """Output coordinates AND the (N_out, K) neighbour map of a strided / transposed convolution in
+    one pass over the candidates (the map is scattered from the same dedupe table instead of probing
+    the input table N_out*K times).  Returns (out_coords, new_shape tuple, kernel_offsets tensor, nbr).
+    Same results as build_out_coords followed by compute_neighbor_indices."""
+    offsets = kernel_offsets(kernel_size, dilation, padding, transposed)
+    koff = _offsets_tensor(offsets, in_coords)
+    koff._st_host = [v for o in offsets for v in o]
+    new_shape = output_shape(spatial_shape, kernel_size, stride, dilation, padding, transposed)
+    out, nbr = _run_out_coords(in_coords, offsets, new_shape, stride, transposed, with_map=True,
+                               in_shape=tuple(int(v) for v in spatial_shape))
+    return out, new_shape, koff, nbr
+
+
+def _run_out_coords(in_coords, offsets, new_shape, stride, transposed, with_map, in_shape=None):
+    device = in_coords.device
+    n, K = in_coords.shape[0], len(offsets)
+    if n == 0:
+        return (torch.empty((0, 4), dtype=in_coords.dtype, device=device),
+                torch.empty((0, K), dtype=torch.int32, device=device) if with_map else None)
     _lib.require_cuda(in_coords, "build_out_coords")
     coords = in_coords.contiguous()
     code = _lib.coord_code(coords)
@@ -91,8 +110,8 @@ def build_out_coords(
     ws = _lib.workspace(ws_bytes, device)
     counters = torch.zeros(2, dtype=torch.int64, device=device)      # [n_out, status]
     status = counters[1:].view(torch.int32)
-    # clear + insert + mark + (<= 6) scan kernels, then the write kernel
-    with torch.cuda.device(device), trace.stage("out_coords", 10):
+    nbr = None
+    with torch.cuda.device(device), trace.stage("out_coords"):
         stream = _lib.stream_ptr()
         rc = L.st_outcoords_count(_lib.ptr(coords), n, code, off_h, K, stride, int(transposed), shape_h,
                                   _lib.ptr(ws), ws.numel(), _lib.ptr(counters), _lib.ptr(status), stream)
@@ -105,4 +124,12 @@ def build_out_coords(
             rc = L.st_outcoords_write(_lib.ptr(coords), n, code, off_h, K, stride, int(transposed), shape_h,
                                       _lib.ptr(ws), ws.numel(), _lib.ptr(out), n_out, _lib.ptr(status), stream)
             _lib.check(rc, "st_outcoords_write")
-    return out, new_shape_t, koff
+    if with_map:
+        nbr = torch.empty((n_out, K), dtype=torch.int32, device=device)
+        if n_out > 0:
+            with torch.cuda.device(device), trace.stage("map_scatter"):
+                rc = L.st_outcoords_map(_lib.ptr(coords), n, code, off_h, K, stride, int(transposed), shape_h,
+                                        _lib.host_i32(in_shape), _lib.ptr(ws), ws.numel(), _lib.ptr(nbr), n_out,
+                                        _lib.stream_ptr())
+                _lib.check(rc, "st_outcoords_map")
+    return out, nbr

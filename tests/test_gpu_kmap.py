@@ -10,7 +10,7 @@ from sparsetriton_b200 import synthetic
 from sparsetriton_b200.config import set_coords_dtype
 from sparsetriton_b200.nn.functional.conv.conv import compute_neighbor_indices
 from sparsetriton_b200.nn.functional.conv.funcs.implicit_precomputed_gemm import inverse_map
-from sparsetriton_b200.nn.functional.conv.kmap import build_out_coords
+from sparsetriton_b200.nn.functional.conv.kmap import build_out_coords, out_coords_and_map
 from sparsetriton_b200.utils.hash import HashTable
 
 pytestmark = pytest.mark.gpu
@@ -49,6 +49,27 @@ def test_golden(cuda_device, oracle, path):
     assert np.array_equal(map_triples(nbr), oracle.pairs(g["nbr"]))
 
 
+def gpu_fused_map(dev, coords, shape, k, s, d, p, transposed, dtype=torch.int32):
+    """Coordinates and map from the single-pass form used by sparse_conv3d for strided / transposed layers."""
+    set_coords_dtype(dtype)
+    c = torch.as_tensor(coords).to(dev, dtype)
+    oc, ns, ko, nbr = out_coords_and_map(c, tuple(int(v) for v in shape), k, s, d, p, transposed)
+    return oc, list(ns), ko, nbr
+
+
+@pytest.mark.parametrize("path", [p for p in golden_files("kmap_") if "subm_k" not in p or "_s2" in p], ids=case_id)
+def test_golden_single_pass_map(cuda_device, oracle, path):
+    g = load_golden(path)
+    dtype = getattr(torch, str(g["coord_dtype"]))
+    k, s, d, subm = int(g["k"]), int(g["s"]), int(g["d"]), bool(g["subm"])
+    p = ((k - 1) * d) // 2 if subm else int(g["p"])
+    oc, ns, ko, nbr = gpu_fused_map(cuda_device, g["coords"], g["shape"], k, s, d, p, bool(g["transposed"]), dtype)
+    assert ns == g["new_shape"].tolist()
+    assert np.array_equal(oc.cpu().numpy().astype(np.int32), g["out_coords"])
+    assert np.array_equal(nbr.cpu().numpy(), g["nbr"])
+    assert np.array_equal(map_triples(nbr), oracle.pairs(g["nbr"]))
+
+
 CASES = [
     # k, s, p, d, transposed, subm
     (3, 1, 1, 1, False, True),
@@ -77,6 +98,20 @@ def test_random_vs_oracle(cuda_device, oracle, k, s, p, d, transposed, subm, dty
     assert np.array_equal(oc.cpu().numpy().astype(np.int32), woc)
     assert np.array_equal(nbr.cpu().numpy(), wnbr)
     assert np.array_equal(map_triples(nbr), oracle.pairs(wnbr))
+    if not (subm and s == 1):
+        oc2, ns2, _, nbr2 = gpu_fused_map(cuda_device, coords, shape, k, s, d, p, transposed, dtype)
+        assert np.array_equal(oc2.cpu().numpy().astype(np.int32), woc) and np.array_equal(nbr2.cpu().numpy(), wnbr)
+
+
+def test_single_pass_map_duplicates_and_out_of_grid(cuda_device, oracle):
+    """Rows with equal coordinates keep the largest row (as the table does); inputs outside the
+    declared grid produce output coordinates but no map entry (as the bounds-checked lookup does)."""
+    base = synthetic.random_cells(3000, 2, 20, seed=9).numpy()
+    coords = np.concatenate([base, base[:500], np.array([[0, 25, 3, 3], [1, 3, 30, 3]], np.int32)])
+    shape = (20, 20, 20)
+    oc, ns, _, nbr = gpu_fused_map(cuda_device, coords, shape, 3, 2, 1, 1, False)
+    woc, wns, _, wnbr = oracle.kernel_map(coords, shape, 3, 2, 1, 1, False, False)
+    assert np.array_equal(oc.cpu().numpy(), woc) and np.array_equal(nbr.cpu().numpy(), wnbr)
 
 
 def test_surface_scene_downsample_and_back(cuda_device, oracle):

@@ -2,6 +2,10 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
+Other workloads: `hash_map_c2` (hash table + kernel-map microbenchmark, 2M or 8M random cells in a
+2048^3 grid), `unet_infer` / `unet_train` (the lidar-like sparse U-Net, batch 8 / 16 sharded by sample
+over the ranks; training all-reduces one flat gradient bucket over NCCL and applies SGD with momentum).
+
 Workload (default `conv_layer_c3`): one SparseConv3D downsample layer, batch 4, grid 512^3,
 300 000 surface voxels per sample, 64 -> 128 channels, kernel 3, stride 2, padding 1, bf16,
 PrecomputedNeighborGEMM.  One step is one pass of the whole hot path over one batch:
@@ -344,6 +348,258 @@ def run_reference(args):
     }))
 
 
+# --------------------------------------------------------------------------------- other workloads
+def _dist_setup(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    return dist, world, rank, local, dev
+
+
+def run_hash_map(args):
+    """BASELINE config 2: table build at load factor 0.5, submanifold maps for k3 (27) and k5 (125),
+    a k3 s2 p1 downsample (output coordinates + map) and the transposed map from its output."""
+    from sparsetriton_b200 import synthetic, trace
+    from sparsetriton_b200.config import set_coords_dtype
+    from sparsetriton_b200.nn.functional.conv.conv import compute_neighbor_indices
+    from sparsetriton_b200.nn.functional.conv.kmap import build_out_coords, out_coords_and_map
+    from sparsetriton_b200.utils.hash import HashTable
+
+    dist, world, rank, local, dev = _dist_setup(args)
+    set_coords_dtype(torch.int32)
+    n, grid = args.cells, 2048
+    coords = synthetic.random_cells(n, 4, grid, seed=2001 + rank).to(dev)
+    shape = (grid,) * 3
+    cap = 1 << (2 * n - 1).bit_length()
+
+    def step():
+        t = HashTable(cap, device=dev)
+        t.insert(coords)
+        res = {}
+        for k in (3, 5):
+            _, _, ko = build_out_coords(coords, shape, k, 1, 1, (k - 1) // 2, submanifold=True)
+            with trace.stage(f"subm_map_k{k}"):
+                res[k] = compute_neighbor_indices(t, coords, ko, shape, 1)
+        oc, ns, ko, nbr = out_coords_and_map(coords, shape, 3, 2, 1, 1, False)
+        oc2, ns2, ko2, nbr2 = out_coords_and_map(oc, ns, 3, 2, 1, 1, True)
+        return res, nbr, nbr2, oc, oc2
+
+    res, nbr, nbr2, oc, oc2 = step()
+    pairs = {"k3": int((res[3] >= 0).sum()), "k5": int((res[5] >= 0).sum()), "down": int((nbr >= 0).sum()),
+             "up": int((nbr2 >= 0).sum())}
+    n_down, n_up = oc.shape[0], oc2.shape[0]
+    del res, nbr, nbr2, oc, oc2
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with trace.recording() as rec:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        stages = rec.summary()
+        launches = rec.total_launches()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        pk = peaks()
+        per = {k: v["ms"] / args.steps for k, v in stages.items()}
+        # algorithmic bytes (coords 16 B, one 8 B key probe + 4 B map entry per (voxel, offset), 4 B value per hit)
+        algo = {
+            "hash_build": 52.0 * n,
+            "subm_map_k3": n * (16 + 12 * 27) + 4.0 * pairs["k3"],
+            "subm_map_k5": n * (16 + 12 * 125) + 4.0 * pairs["k5"],
+        }
+        roof = {}
+        for name, nbytes in algo.items():
+            if name in per and per[name] > 0:
+                gbs = nbytes / (per[name] * 1e-3) / 1e9
+                roof[name] = {"ms": per[name], "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"]}
+        top = max(roof, key=lambda k: roof[k]["ms"])
+        ms_step = t.item() / args.steps
+        print(json.dumps({
+            "metric": "hash_and_kernel_map_voxels_per_s", "value": world * n / (ms_step * 1e-3), "unit": "voxels/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64 keys / int32 coords",
+            "data": "synthetic",
+            "config": {"workload": "hash_map_c2: %d random cells, batch 4, grid 2048^3, table capacity %d; build + subm k3 + "
+                                   "subm k5 + k3s2p1 down (coords+map) + transposed map" % (n, cap),
+                       "pairs": pairs, "n_out_down": n_down, "n_out_up": n_up, "l2_policy": "tables and maps larger than L2"},
+            "gpu_launches": launches, "stages": per, "stage_rooflines": roof,
+            "roofline": {"kernel": top, "bound": "hbm", "achieved": roof[top]["achieved_gbs"], "peak": pk["hbm_gbs"],
+                         "unit": "GB/s", "frac": roof[top]["frac"], "traffic": None, "peak_source": pk["source"]},
+            "clocks": clocks,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def make_lidar_batch(samples):
+    """(coords (N,4) int32 with batch relabelled from 0, feats (N,4) fp32) of the given scene seeds."""
+    from sparsetriton_b200 import synthetic
+    scenes = [synthetic.lidar_scene(seed) for seed in samples]
+    coords = synthetic.batch_of(scenes, dtype=torch.int32)
+    g = torch.Generator().manual_seed(samples[0] + 17)
+    xyz = coords[:, 1:].float() / torch.tensor([1440.0, 1440.0, 41.0])
+    feats = torch.cat([xyz, torch.rand(coords.shape[0], 1, generator=g)], dim=1)
+    return coords, feats
+
+
+def run_unet(args, train):
+    """BASELINE configs 4 / 5: lidar-like sparse U-Net, bf16 features, fp32 master weights."""
+    from sparsetriton_b200 import trace
+    from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype, set_h_table_f
+    from sparsetriton_b200.distributed import GradientBucket, global_mean_scale, shard_samples
+    from sparsetriton_b200.tensor import SparseTensor
+    from sparsetriton_b200.unet import SparseUNet
+
+    dist, world, rank, local, dev = _dist_setup(args)
+    set_coords_dtype(torch.int32)
+    set_h_table_f(2.0)
+    set_conv_algo(ConvAlgo.ImplicitHashFlyGEMM if args.algo == "hashfly" else ConvAlgo.PrecomputedNeighborGEMM)
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    total_batch = 16 if train else 8
+    base_seed = 5000 if train else 4000
+    mine = shard_samples(total_batch, rank, world)
+    coords_h, feats_h = make_lidar_batch([base_seed + i for i in mine])
+    coords_h, feats_h = coords_h.pin_memory(), feats_h.to(dtype).pin_memory()
+    shape = (1440, 1440, 41)
+    torch.manual_seed(5100 if train else 4100)
+    model = SparseUNet().to(dev)
+    model.train(train)
+    n_in = coords_h.shape[0]
+    opt = bucket = None
+    if train:
+        bucket = GradientBucket(model.parameters())
+        opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+
+    state = {"labels": None, "scale": None, "n_out": None}
+
+    def step(coords, feats):
+        x = SparseTensor._trusted(feats, coords, shape, len(mine))
+        if not train:
+            with torch.no_grad():
+                out = model(x)
+            return out.F
+        out = model(x)
+        if state["labels"] is None:
+            g = torch.Generator().manual_seed(base_seed + 99 + rank)
+            state["labels"] = torch.randint(0, 20, (out.F.shape[0],), generator=g).to(dev)
+            state["scale"] = global_mean_scale(out.F.shape[0], dev)
+            state["n_out"] = out.F.shape[0]
+        loss = torch.nn.functional.cross_entropy(out.F, state["labels"], reduction="sum") * state["scale"]
+        bucket.zero()
+        loss.backward()
+        bucket.all_reduce()
+        opt.step()
+        return loss.detach()
+
+    coords_d, feats_d = coords_h.to(dev), feats_h.to(dev)
+    for _ in range(args.warmup):
+        step(coords_d, feats_d)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sync_all()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with trace.recording() as rec:
+        sync_all()
+        e0.record()
+        for _ in range(args.steps):
+            step(coords_d, feats_d)
+        e1.record()
+        sync_all()
+        stages = rec.summary()
+        launches = rec.total_launches()
+    dev_ms = e0.elapsed_time(e1)
+
+    result_h = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        c = coords_h.to(dev, non_blocking=True)
+        f = feats_h.to(dev, non_blocking=True)
+        r = step(c, f)
+        result_h.copy_(r.float().sum().reshape(1), non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    sync_all()
+    e2e_ms = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([dev_ms, e2e_ms, float(n_in)], dtype=torch.float64, device=dev)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum)
+        dev_ms, e2e_ms, total_voxels = tmax[0].item(), tmax[1].item(), tsum[2].item()
+    else:
+        total_voxels = float(n_in)
+    if rank == 0:
+        pk = peaks()
+        ms_step = dev_ms / args.steps
+        per = {k: {"ms_per_step": v["ms"] / args.steps, "launches_per_step": v["launches"] / args.steps,
+                   "calls_per_step": v["calls"] / args.steps,
+                   "tflops": (v["work"] / (v["ms"] * 1e-3) / 1e12) if v["work"] and v["ms"] > 0 else None}
+               for k, v in stages.items()}
+        conv = [k for k in per if k.startswith("conv_")]
+        top = max(conv, key=lambda k: per[k]["ms_per_step"]) if conv else None
+        roof = None
+        if top and per[top]["tflops"]:
+            peak = pk["bf16_tflops_sustained"] * (0.5 if dtype == torch.float32 else 1.0)
+            roof = {"kernel": top + " (all layers)", "bound": "tensor", "achieved": per[top]["tflops"], "peak": peak,
+                    "unit": "TFLOP/s", "frac": per[top]["tflops"] / peak, "traffic": None, "peak_source": pk["source"],
+                    "share_of_step": per[top]["ms_per_step"] / ms_step}
+        print(json.dumps({
+            "metric": "sparse_unet_%s_voxels_per_s" % ("train_step" if train else "inference"),
+            "value": total_voxels / (ms_step * 1e-3), "unit": "voxels/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+            "config": {"workload": "%s: lidar-like U-Net 4->32/64/128/256->...->32->20, grid 1440x1440x41, batch %d "
+                                   "(%d samples on this rank, %d voxels)" % (args.workload, total_batch, len(mine), n_in),
+                       "algo": args.algo, "parallelism": "dp%d by sample%s" % (world, ", NCCL all-reduce of one flat gradient bucket" if train else ""),
+                       "l2_policy": "activations of every level exceed L2"},
+            "e2e": {"value": total_voxels / (e2e_ms / args.steps * 1e-3), "unit": "voxels/s",
+                    "h2d_bytes_per_step": coords_h.numel() * 4 + feats_h.numel() * feats_h.element_size(),
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches, "stages": per, "roofline": roof, "clocks": clocks,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -356,10 +612,17 @@ def main():
     ap.add_argument("--per-sample", type=int, default=PER_SAMPLE, dest="per_sample")
     ap.add_argument("--grid", type=int, default=GRID)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="conv_layer_c3",
+                    choices=["conv_layer_c3", "hash_map_c2", "unet_infer", "unet_train"])
+    ap.add_argument("--cells", type=int, default=8_000_000, help="hash_map_c2: number of coordinates")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "hash_map_c2":
+        run_hash_map(args)
+    elif args.workload in ("unet_infer", "unet_train"):
+        run_unet(args, train=args.workload == "unet_train")
     else:
         run_ours(args)
 

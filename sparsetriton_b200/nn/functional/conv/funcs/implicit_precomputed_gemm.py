@@ -50,8 +50,9 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         assert nbr.dtype == torch.int32, "neighbor_indices must be int32"
         code = _lib.feat_code(x)
         y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
+        ctx.flops = 2.0 * trace.map_pairs(nbr) * c_in * c_out if trace.active() else 0.0
         if n_out > 0:
-            with torch.cuda.device(x.device), trace.stage("conv_fwd", 1):
+            with torch.cuda.device(x.device), trace.stage("conv_fwd", work=ctx.flops):
                 rc = _lib.lib().st_conv_fwd(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), _lib.ptr(y), n_in, n_out,
                                             K, c_in, c_out, None, 0, _lib.stream_ptr())
             _lib.check(rc, "st_conv_fwd")
@@ -75,14 +76,14 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
                 dx = torch.empty_like(x)
                 if n_in > 0:
                     inv = inverse_map(nbr, n_in)
-                    with trace.stage("conv_dgrad", 1):
+                    with trace.stage("conv_dgrad", work=ctx.flops):
                         rc = L.st_conv_dgrad(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv), _lib.ptr(dx), n_in, n_out,
                                              K, c_in, c_out, None, 0, stream)
                     _lib.check(rc, "st_conv_dgrad")
             if ctx.needs_input_grad[1]:
                 dw = torch.empty_like(w)
                 ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
-                with trace.stage("conv_wgrad", 2):
+                with trace.stage("conv_wgrad", work=ctx.flops):
                     rc = L.st_conv_wgrad(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), _lib.ptr(dw), n_in, n_out, K,
                                          c_in, c_out, _lib.ptr(ws), ws.numel(), stream)
                 _lib.check(rc, "st_conv_wgrad")

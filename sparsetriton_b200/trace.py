@@ -2,7 +2,7 @@
 
     with trace.recording() as rec:
         ... run convolutions ...
-    rec.summary()  -> {stage: {"calls": n, "ms": total, "launches": n_kernels}}
+    rec.summary()  -> {stage: {"calls": n, "ms": total, "launches": n_kernels, "work": flops or bytes}}
 
 Each C-ABI call site is wrapped in `trace.stage(name)`.  When no recording is active the wrapper
 does nothing; when one is, it brackets the call with CUDA events on the current stream (the stream
@@ -20,16 +20,17 @@ _active = None
 
 class Recording:
     def __init__(self):
-        self.spans = []          # (name, start_event, end_event, launches)
+        self.spans = []          # (name, start_event, end_event, launches, algorithmic work)
 
     def summary(self):
         torch.cuda.synchronize()
         out = {}
-        for name, a, b, launches in self.spans:
-            e = out.setdefault(name, {"calls": 0, "ms": 0.0, "launches": 0})
+        for name, a, b, launches, work in self.spans:
+            e = out.setdefault(name, {"calls": 0, "ms": 0.0, "launches": 0, "work": 0.0})
             e["calls"] += 1
             e["ms"] += a.elapsed_time(b)
             e["launches"] += launches
+            e["work"] += work
         return out
 
     def total_launches(self):
@@ -47,7 +48,21 @@ def recording():
 
 
 @contextlib.contextmanager
-def stage(name, launches=None):
+def active():
+    """True while a recording is open (call sites use it to skip bookkeeping that costs a sync)."""
+    return _active is not None
+
+
+def map_pairs(neighbor_indices):
+    """Number of valid entries of a neighbour map, memoised on the tensor (one device->host read)."""
+    n = getattr(neighbor_indices, "_st_pairs", None)
+    if n is None:
+        n = int((neighbor_indices >= 0).sum().item())
+        neighbor_indices._st_pairs = n
+    return n
+
+
+def stage(name, launches=None, work=0.0):
     rec = _active
     if rec is None:
         yield
@@ -61,4 +76,4 @@ def stage(name, launches=None):
         yield
     finally:
         b.record()
-        rec.spans.append((name, a, b, counter() - before))
+        rec.spans.append((name, a, b, counter() - before, float(work)))

@@ -1,0 +1,95 @@
+"""The benchmark U-Net on small lidar-like scenes: both convolution algorithms, tensor-core and
+CUDA-core kernels, must give the same network output and gradients within the feature tolerances."""
+import numpy as np
+import pytest
+import torch
+
+import sparsetriton_b200 as st
+from gpu_util import rel_err
+from sparsetriton_b200 import _lib, synthetic
+from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype
+from sparsetriton_b200.unet import SparseUNet, skip_concat
+
+pytestmark = pytest.mark.gpu
+
+
+SHAPE = (64, 64, 41)                      # odd z extent: the k2 s2 layers drop the last slab, as in the benchmark grid
+
+
+def _scene(dev, batch=2):
+    samples = []
+    for b in range(batch):
+        c = synthetic.surface_scene(70 + b, grid=64, target=7000, n_spheres=3, n_boxes=3)
+        samples.append(c[c[:, 2] < SHAPE[2]])
+    coords = synthetic.batch_of(samples)
+    g = torch.Generator().manual_seed(5)
+    feats = torch.cat([coords[:, 1:].float() / torch.tensor([64.0, 64.0, 41.0]), torch.rand(coords.shape[0], 1, generator=g)], 1)
+    return coords.to(dev), feats.to(dev)
+
+
+def _run(model, coords, feats, labels_seed, dtype, algo, tensor_cores):
+    set_conv_algo(algo)
+    _lib.lib().st_set_tensor_cores(int(tensor_cores))
+    model.zero_grad(set_to_none=True)
+    x = st.SparseTensor(feats.to(dtype), coords, spatial_shape=SHAPE, batch_size=2)
+    out = model(x)
+    g = torch.Generator().manual_seed(labels_seed)
+    labels = torch.randint(0, 20, (out.F.shape[0],), generator=g).to(out.F.device)
+    loss = torch.nn.functional.cross_entropy(out.F.float(), labels)
+    loss.backward()
+    grads = torch.cat([p.grad.reshape(-1).float() for p in model.parameters()])
+    _lib.lib().st_set_tensor_cores(1)
+    return out.C.cpu().numpy(), out.F.detach().float().cpu().numpy(), float(loss.detach()), grads.cpu().numpy()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_unet_algorithms_and_kernels_agree(cuda_device, dtype):
+    set_coords_dtype(torch.int32)
+    torch.manual_seed(4100)
+    model = SparseUNet(widths=(16, 32, 64, 128)).to(cuda_device)
+    coords, feats = _scene(cuda_device)
+    ref = _run(model, coords, feats, 1, dtype, ConvAlgo.PrecomputedNeighborGEMM, tensor_cores=False)
+    assert ref[0].shape[0] >= coords.shape[0] and np.isfinite(ref[1]).all() and np.isfinite(ref[3]).all()
+    assert (np.abs(ref[3]) > 0).mean() > 0.5
+    tol_out, tol_grad = (5e-3, 2e-2) if dtype == torch.float32 else (5e-2, 1.5e-1)
+    for algo, tcores in [(ConvAlgo.PrecomputedNeighborGEMM, True), (ConvAlgo.ImplicitHashFlyGEMM, True),
+                         (ConvAlgo.ImplicitHashFlyGEMM, False)]:
+        got = _run(model, coords, feats, 1, dtype, algo, tcores)
+        assert np.array_equal(got[0], ref[0]), "output coordinates differ between algorithms"
+        assert rel_err(got[1], ref[1]) < tol_out, (algo, tcores, rel_err(got[1], ref[1]))
+        assert abs(got[2] - ref[2]) < tol_out * max(1.0, abs(ref[2]))
+        assert rel_err(got[3], ref[3]) < tol_grad, (algo, tcores, rel_err(got[3], ref[3]))
+    assert _lib.device_status(cuda_device)[0] == 0
+
+
+def test_conv_stack_is_reproducible(cuda_device):
+    """Stored-map convolutions use no atomics anywhere (forward, dgrad over the inverse map, wgrad with a
+    fixed-order reduction): running the same layers twice gives bit-identical outputs and gradients.
+    (The U-Net as a whole is not bit-reproducible because torch's index_add_ in batch norm is atomic.)"""
+    from sparsetriton_b200.nn import SparseConv3D, SparseConvTransposed3D, SubMConv3D
+    set_coords_dtype(torch.int32)
+    set_conv_algo(ConvAlgo.PrecomputedNeighborGEMM)
+    torch.manual_seed(1)
+    layers = torch.nn.Sequential(SubMConv3D(16, 32, 3), SparseConv3D(32, 64, 2, stride=2),
+                                 SubMConv3D(64, 64, 3), SparseConvTransposed3D(64, 32, 2, stride=2)).to(cuda_device)
+    coords, _ = _scene(cuda_device)
+    feats = torch.randn(coords.shape[0], 16, device=cuda_device).bfloat16()
+    results = []
+    for _ in range(2):
+        layers.zero_grad(set_to_none=True)
+        x = feats.clone().requires_grad_(True)
+        out = layers(st.SparseTensor(x, coords, spatial_shape=SHAPE, batch_size=2))
+        out.F.float().square().mean().backward()
+        results.append((out.F.detach().clone(), x.grad.clone(), torch.cat([p.grad.reshape(-1) for p in layers.parameters()])))
+    for a, b in zip(*results):
+        assert torch.equal(a, b), "reruns must be bit-identical"
+
+
+def test_skip_concat(cuda_device):
+    set_coords_dtype(torch.int32)
+    enc = st.SparseTensor(torch.arange(6.0, device=cuda_device).view(3, 2),
+                          torch.tensor([[0, 1, 1, 1], [0, 2, 2, 2], [1, 1, 1, 1]], device=cuda_device))
+    dec = st.SparseTensor(torch.ones(4, 1, device=cuda_device),
+                          torch.tensor([[1, 1, 1, 1], [0, 9, 9, 9], [0, 2, 2, 2], [0, 1, 1, 1]], device=cuda_device))
+    out = skip_concat(dec, enc)
+    assert out.F.tolist() == [[1, 4, 5], [1, 0, 0], [1, 2, 3], [1, 0, 1]]

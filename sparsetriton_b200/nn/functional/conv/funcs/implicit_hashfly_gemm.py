@@ -19,6 +19,8 @@ import torch
 
 from sparsetriton_b200 import _lib, trace
 
+from ._channels import pad_cols, pad_weight, padded_widths
+
 __all__ = ["ConvHashOnTheFlyImplicitGEMM"]
 
 
@@ -41,8 +43,10 @@ class ConvHashOnTheFlyImplicitGEMM(torch.autograd.Function):
         if hash_table_keys.dtype != torch.int64 or hash_table_vals.dtype != torch.int32:
             raise TypeError("hash table must hold int64 keys and int32 values")
         n_out = coords.shape[0]
-        x = features.contiguous()
-        w = weights.to(x.dtype).contiguous()
+        ctx.true_widths = (c_in, c_out)
+        c_in, c_out = padded_widths(features.dtype, c_in, c_out)          # narrow layers: zero-padded operands
+        x = pad_cols(features, c_in).contiguous()
+        w = pad_weight(weights.to(x.dtype), c_in, c_out).contiguous()
         c = coords.contiguous()
         keys, vals = hash_table_keys.contiguous(), hash_table_vals.contiguous()
         ctx.offsets_h = _host_offsets(kernel_offsets)
@@ -59,7 +63,7 @@ class ConvHashOnTheFlyImplicitGEMM(torch.autograd.Function):
                     c_out, None, 0, _lib.stream_ptr())
             _lib.check(rc, "st_conv_fwd_hashfly")
         ctx.save_for_backward(x, w, c, keys, vals)
-        return y
+        return y if c_out == ctx.true_widths[1] else y[:, :ctx.true_widths[1]].contiguous()
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -67,7 +71,8 @@ class ConvHashOnTheFlyImplicitGEMM(torch.autograd.Function):
         n_in, c_in = x.shape
         K, _, c_out = w.shape
         n_out = c.shape[0]
-        dy = grad_output.to(x.dtype).contiguous()
+        t_in, t_out = ctx.true_widths
+        dy = pad_cols(grad_output.to(x.dtype), c_out).contiguous()
         code, ccode = _lib.feat_code(x), _lib.coord_code(c)
         L = _lib.lib()
         dx = dw = None
@@ -91,4 +96,8 @@ class ConvHashOnTheFlyImplicitGEMM(torch.autograd.Function):
                         c_in, c_out, _lib.ptr(ws), ws.numel(), stream)
                 _lib.check(rc, "st_conv_wgrad_hashfly")
                 dw = dw.to(ctx.w_dtype)
+        if dx is not None and t_in != c_in:
+            dx = dx[:, :t_in].contiguous()
+        if dw is not None and (t_in != c_in or t_out != c_out):
+            dw = dw[:, :t_in, :t_out].contiguous()
         return dx, dw, None, None, None, None, None, None

@@ -16,6 +16,8 @@ import torch
 
 from sparsetriton_b200 import _lib, trace
 
+from ._channels import pad_cols, pad_weight, padded_widths
+
 __all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map"]
 
 
@@ -44,8 +46,10 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         n_out = neighbor_indices.shape[0]
         assert neighbor_indices.shape[1] == K, "neighbor_indices must be (N_out, K)"
 
-        x = features.contiguous()
-        w = weights.to(x.dtype).contiguous()
+        ctx.true_widths = (c_in, c_out)
+        c_in, c_out = padded_widths(features.dtype, c_in, c_out)          # narrow layers: zero-padded operands
+        x = pad_cols(features, c_in).contiguous()
+        w = pad_weight(weights.to(x.dtype), c_in, c_out).contiguous()
         nbr = neighbor_indices if neighbor_indices.is_contiguous() else neighbor_indices.contiguous()
         assert nbr.dtype == torch.int32, "neighbor_indices must be int32"
         code = _lib.feat_code(x)
@@ -58,7 +62,7 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
             _lib.check(rc, "st_conv_fwd")
         ctx.save_for_backward(x, w, nbr)
         ctx.w_dtype = weights.dtype
-        return y
+        return y if c_out == ctx.true_widths[1] else y[:, :ctx.true_widths[1]].contiguous()
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -66,7 +70,8 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         n_in, c_in = x.shape
         K, _, c_out = w.shape
         n_out = nbr.shape[0]
-        dy = grad_output.to(x.dtype).contiguous()
+        t_in, t_out = ctx.true_widths
+        dy = pad_cols(grad_output.to(x.dtype), c_out).contiguous()
         code = _lib.feat_code(x)
         L = _lib.lib()
         dx = dw = None
@@ -88,4 +93,8 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
                                          c_in, c_out, _lib.ptr(ws), ws.numel(), stream)
                 _lib.check(rc, "st_conv_wgrad")
                 dw = dw.to(ctx.w_dtype)
+        if dx is not None and t_in != c_in:
+            dx = dx[:, :t_in].contiguous()
+        if dw is not None and (t_in != c_in or t_out != c_out):
+            dw = dw[:, :t_in, :t_out].contiguous()
         return dx, dw, None

@@ -47,7 +47,6 @@ def recording():
         _active = prev
 
 
-@contextlib.contextmanager
 def active():
     """True while a recording is open (call sites use it to skip bookkeeping that costs a sync)."""
     return _active is not None
@@ -62,6 +61,7 @@ def map_pairs(neighbor_indices):
     return n
 
 
+@contextlib.contextmanager
 def stage(name, launches=None, work=0.0):
     rec = _active
     if rec is None:

@@ -6,9 +6,19 @@ features of the same level concatenated as skip, two SubMConv3D(k3) + BN + ReLU 
 32 channels; a SparseLinear head gives 20 classes.
 
 Even kernels follow the reference's rule (kmap.py:135-180): the k2 s2 down-conv maps inputs
-{2o-1, 2o} to output o and the k2 s2 transposed conv emits {2i-1, 2i}, so the decoder's coordinate
-set at a level is a superset of the encoder's.  The skip is therefore a lookup: every decoder
-coordinate takes the encoder row with the same coordinate, or zeros.
+{2o-1, 2o} to output o and the k2 s2 transposed conv emits {2i-1, 2i}, so what a transposed conv
+produces at a level is a superset of the encoder's coordinates of that level (up to 8 children per
+voxel, of which the encoder had only some).  Two decoder modes:
+
+  prune=True (default, the usual U-Net)  the up-conv is evaluated only at the encoder's coordinates
+      of the level, so decoder and encoder tensors share coordinates, hash table and neighbour maps
+      and the skip is a plain channel concatenation.  Evaluating a transposed convolution at the
+      children the down-conv came from needs no new map: child = parent*s + off_t[k] is the very
+      relation the down-conv's map stores, so the up-conv is a gather over that map's inverse.
+  prune=False (the literal composition of the reference's layers)  every child is materialised and
+      the skip is a lookup (encoder row of the same coordinate, or zeros).  The active set then grows
+      up to 8x per level: on the 1440x1440x41 benchmark scenes a batch-16 training step does not fit
+      180 GB, which is why the benchmarks run the pruned form.
 
 Precision: parameters stay fp32 (master weights); features run in `feature_dtype` (bf16 in the
 benchmarks); the conv Functions cast the weights per call and return fp32 weight gradients;
@@ -17,11 +27,40 @@ batch norm computes in fp32 per sample and casts back.
 import torch
 from torch import nn
 
+from sparsetriton_b200.config import ConvAlgo, get_conv_algo
+from sparsetriton_b200.nn.functional.conv.funcs import ConvPrecomputedNeighborGEMM
+from sparsetriton_b200.nn.functional.conv.funcs.implicit_precomputed_gemm import inverse_map
 from sparsetriton_b200.nn.modules import ReLU, SparseBatchNorm, SparseConv3D, SparseConvTransposed3D, SparseLinear, SubMConv3D
 from sparsetriton_b200.tensor import SparseTensor
 from sparsetriton_b200.utils.hash import HashTable, round_up_capacity
 
-__all__ = ["SparseUNet", "skip_concat"]
+__all__ = ["SparseUNet", "skip_concat", "up_conv_onto"]
+
+
+def up_conv_onto(x: SparseTensor, up: SparseConvTransposed3D, target: SparseTensor) -> SparseTensor:
+    """`up(x)` evaluated only at the coordinates of `target`, the tensor that `x`'s coordinates were
+    downsampled from by a SparseConv3D with the same kernel size / stride / padding / dilation.
+
+    With the stored-map algorithm and the down-conv's map still cached on `target`, this is one gather
+    GEMM over the inverse of that map (no coordinate or map building).  Otherwise it falls back to the
+    full transposed convolution followed by a lookup of the target's coordinates in its output."""
+    k, s, p, d = up.kernel_size[0], up.stride[0], up.padding[0], up.dilation[0]
+    cached = target._cache.neighbor_indices.get((k, s, p, d, False, False))
+    if get_conv_algo() == ConvAlgo.PrecomputedNeighborGEMM and cached is not None and cached[1].shape[0] == x.F.shape[0]:
+        inv = inverse_map(cached[1], target.C.shape[0])         # (N_target, K): parent row per child and offset
+        feats = ConvPrecomputedNeighborGEMM.apply(x.F, up.weight, inv)
+        if up.bias is not None:
+            feats = feats + up.bias.to(feats.dtype)
+        return target.replace(feats)
+    full = up(x)
+    table = HashTable(round_up_capacity(full.C.shape[0], 2.0), device=full.C.device)
+    table.insert(full.C)
+    idx = table.query(target.C).long()
+    found = (idx >= 0).unsqueeze(1)
+    rows = full.F.index_select(0, idx.clamp(min=0)) * found.to(full.F.dtype)
+    if up.bias is not None:                                   # a child without any parent gets the bias alone
+        rows = rows + up.bias.to(rows.dtype) * (~found).to(rows.dtype)
+    return target.replace(rows)
 
 
 def skip_concat(decoder: SparseTensor, encoder: SparseTensor) -> SparseTensor:
@@ -52,8 +91,9 @@ class _Block(nn.Module):
 
 
 class SparseUNet(nn.Module):
-    def __init__(self, in_channels=4, widths=(32, 64, 128, 256), num_classes=20):
+    def __init__(self, in_channels=4, widths=(32, 64, 128, 256), num_classes=20, prune=True):
         super().__init__()
+        self.prune = prune
         self.enc = nn.ModuleList()
         self.down = nn.ModuleList()
         c = in_channels
@@ -77,7 +117,11 @@ class SparseUNet(nn.Module):
             x = block(x)
             skips.append(x)
         for j, (up, block) in enumerate(zip(self.up, self.dec)):
-            x = up(x)
-            x = skip_concat(x, skips[len(skips) - 2 - j])
+            skip = skips[len(skips) - 2 - j]
+            if self.prune:
+                x = up_conv_onto(x, up, skip)
+                x = x.replace(torch.cat([x.F, skip.F], dim=1))
+            else:
+                x = skip_concat(up(x), skip)
             x = block(x)
         return x.replace(self.head(x.F.float()))

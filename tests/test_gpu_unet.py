@@ -8,7 +8,7 @@ import sparsetriton_b200 as st
 from gpu_util import rel_err
 from sparsetriton_b200 import _lib, synthetic
 from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype
-from sparsetriton_b200.unet import SparseUNet, skip_concat
+from sparsetriton_b200.unet import SparseUNet, skip_concat, up_conv_onto
 
 pytestmark = pytest.mark.gpu
 
@@ -83,6 +83,39 @@ def test_conv_stack_is_reproducible(cuda_device):
         results.append((out.F.detach().clone(), x.grad.clone(), torch.cat([p.grad.reshape(-1) for p in layers.parameters()])))
     for a, b in zip(*results):
         assert torch.equal(a, b), "reruns must be bit-identical"
+
+
+@pytest.mark.parametrize("algo", [ConvAlgo.PrecomputedNeighborGEMM, ConvAlgo.ImplicitHashFlyGEMM], ids=lambda a: a.name)
+def test_up_conv_onto_equals_transposed_conv_then_lookup(cuda_device, algo):
+    """The pruned decoder's up-conv (gather over the inverse of the down-conv's map) against the literal
+    SparseConvTransposed3D followed by picking the rows at the encoder's coordinates."""
+    from sparsetriton_b200.nn import SparseConv3D, SparseConvTransposed3D
+    from sparsetriton_b200.utils.hash import HashTable
+    set_coords_dtype(torch.int32)
+    set_conv_algo(algo)
+    torch.manual_seed(3)
+    coords, _ = _scene(cuda_device)
+    enc = st.SparseTensor(torch.randn(coords.shape[0], 32, device=cuda_device).bfloat16(), coords,
+                          spatial_shape=SHAPE, batch_size=2)
+    down = SparseConv3D(32, 64, 2, stride=2, bias=False).to(cuda_device)
+    up = SparseConvTransposed3D(64, 32, 2, stride=2, bias=True).to(cuda_device)
+    low = down(enc)
+    got = up_conv_onto(low, up, enc)
+    assert torch.equal(got.C, enc.C) and got._cache is enc._cache
+    full = up(low)
+    table = HashTable(2 * full.C.shape[0], device=cuda_device)
+    table.insert(full.C)
+    idx = table.query(enc.C).long()
+    found = idx >= 0
+    # under the even-kernel rule child c has parent ceil(c/2), which must lie inside the coarse grid
+    # (S-2)//2+1: the last slab(s) of each axis (x, y = 63; z = 39, 40) are orphans.  The literal
+    # transposed conv never produces them, the restricted one gives them the bias alone.
+    coarse = torch.tensor([(v - 2) // 2 + 1 for v in SHAPE], device=cuda_device)
+    orphan = (((enc.C[:, 1:].long() + 1) // 2) >= coarse).any(dim=1)
+    assert torch.equal(orphan, ~found) and found.float().mean() > 0.9
+    want = full.F[idx[found]]
+    assert rel_err(got.F[found].detach().float().cpu().numpy(), want.detach().float().cpu().numpy()) < 1e-2
+    assert torch.equal(got.F[~found], up.bias.to(got.F.dtype).expand_as(got.F[~found]))
 
 
 def test_skip_concat(cuda_device):

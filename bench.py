@@ -306,6 +306,7 @@ def cpu_inputs(per_sample, grid):
 def cpu_baseline_leg(args, seconds_budget):
     from oracle import cpu_oracle as O
     O.build()
+    O.set_threads(os.cpu_count() or 1)            # launchers such as torchrun export OMP_NUM_THREADS=1
     coords, feats, weight = cpu_inputs(args.per_sample, args.grid)
     secs, n_in, n_out = cpu_step(O, coords, feats, weight, None)
     reps = 1
@@ -327,6 +328,7 @@ def run_reference(args):
         return
     from oracle import cpu_oracle as O
     O.build()
+    O.set_threads(os.cpu_count() or 1)            # launchers such as torchrun export OMP_NUM_THREADS=1
     coords, feats, weight = cpu_inputs(args.per_sample, args.grid)
     for _ in range(min(args.warmup, 1)):
         cpu_step(O, coords, feats, weight, None)

@@ -150,7 +150,7 @@ __device__ long long g_prof[160 * 16];
 constexpr int kMaxSub = 4;
 constexpr int kMaxWSlots = 4;
 constexpr int kMaxAStages = 12;
-constexpr int kGroup = 16;                                   // kernel offsets whose map entries are staged at a time
+constexpr int kGroup = 8;                                    // kernel offsets whose map entries are staged at a time
 constexpr int kIdxTileBytes = kGroup * kMaxSub * kTileM * 4;  // 32 KB
 
 struct Params2 {
@@ -182,7 +182,7 @@ struct __align__(8) Control2 {
 };
 
 template <typename Map, int ESIZE>
-__global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, const Map map) {
+__global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, const Map map) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -854,7 +854,18 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   while (cols < p->acc_bufs * sub * c_acc) cols <<= 1;
   p->tmem_cols = cols;
   p->w_slots = 3;
-  const int budget = 222 * 1024 - tc::kIdxTileBytes;
+  const bool two_ctas = getenv("ST_TC_OCC2") != nullptr;       // experiment: two CTAs per SM
+  if (two_ctas) {
+    if (sub > 2) sub = 2;
+    p->sub = sub;
+    p->n_super = (n_tiles + sub - 1) / sub;
+    p->acc_bufs = 1;
+    int c2 = 32;
+    while (c2 < sub * c_acc) c2 <<= 1;
+    p->tmem_cols = c2;
+    p->w_slots = 2;
+  }
+  const int budget = (two_ctas ? 110 : 222) * 1024 - tc::kIdxTileBytes;
   int a_stages = (budget - p->w_slots * p->w_slot_bytes) / tc::kABlockBytes;
   if (a_stages > tc::kMaxAStages) a_stages = tc::kMaxAStages;
   if (a_stages < 4) {
@@ -894,7 +905,8 @@ static int launch_gather(const tc::Params2& p, const Map& map, cudaStream_t stre
     }
     configured[p.esize == 4] = true;
   }
-  int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
+  const int64_t ctas = (int64_t)sm_count() * (getenv("ST_TC_OCC2") ? 2 : 1);
+  int64_t grid = p.n_super < ctas ? p.n_super : ctas;
   kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, map);
   note_launches(1);
   return check_launch("tc gather");

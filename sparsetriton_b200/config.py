@@ -10,6 +10,7 @@ import torch
 __all__ = [
     "ConvAlgo", "set_coords_dtype", "get_coords_dtype", "set_conv_algo", "get_conv_algo",
     "set_h_table_f", "get_h_table_f", "set_h_table_max_p", "get_h_table_max_p",
+    "set_row_order", "get_row_order",
 ]
 
 
@@ -24,6 +25,7 @@ _STATE = {
     "algo": ConvAlgo.PrecomputedNeighborGEMM,
     "h_tbl_factor": 1.5,       # minimum slots per key; tables are rounded up to a power of two
     "h_tbl_max_probe_n": 16,   # kept for API parity; probing here is bounded by the capacity
+    "row_order": True,         # stored-map products walk rows sorted by occupied offsets (no reference counterpart)
 }
 
 
@@ -71,3 +73,16 @@ def set_h_table_max_p(probe_n):
 
 def get_h_table_max_p():
     return _STATE["h_tbl_max_probe_n"]
+
+
+def set_row_order(enabled):
+    """Whether the stored-map products walk the rows of their map sorted by occupied offsets
+    (fewer, denser 128-row tile steps).  Results of forward and feature gradient are the same
+    either way.  No counterpart in the reference."""
+    if not isinstance(enabled, bool):
+        raise TypeError(f"Expected bool, got {type(enabled)}")
+    _STATE["row_order"] = enabled
+
+
+def get_row_order():
+    return _STATE["row_order"]

@@ -14,7 +14,10 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cuda.h>
+
 #include <cstdlib>
+#include <cstring>
 
 #include "conv_maps.cuh"
 #include "conv_tc.cuh"
@@ -147,16 +150,24 @@ __device__ long long g_prof[160 * 16];
 #define PROF_CLOCK() 0ll
 #endif
 
+// Producers that fetch rows with TMA tile::gather4 and weight slices with tiled TMA copies.  The form
+// passes every small case it was given (up to 40000 rows, two row tiles per super tile), but a launch
+// over 834k output rows / 1.2M source rows with four row tiles per super tile ended in a launch
+// failure whose cause has not been found; until it is, the form is compiled out and the cp.async
+// producers are the only ones that run.
+constexpr bool kTmaProducers = false;
+
 constexpr int kMaxSub = 4;
 constexpr int kMaxWSlots = 4;
 constexpr int kMaxAStages = 12;
-constexpr int kGroup = 8;                                    // kernel offsets whose map entries are staged at a time
+constexpr int kGroup = 16;                                   // kernel offsets whose map entries are staged at a time
 constexpr int kIdxTileBytes = kGroup * kMaxSub * kTileM * 4;  // 32 KB
 
 struct Params2 {
   const void* in;
   const void* w;
   void* out;
+  const int32_t* order;    // optional: tile row r stands for row order[r] of the map and of OUT
   int64_t n_rows, n_src, n_super;
   int K, c_red, c_acc, esize;
   int w_rows, w_cols, b_mn_major, k_blocks;
@@ -166,6 +177,7 @@ struct Params2 {
   int tmem_cols;
   uint32_t idesc;
   int out_kind;
+  int use_tma;             // 1: gathered rows come by TMA tile::gather4, 0: by cp.async
   int dbg;                 // timing experiments only (wrong results): 1 no proxy fence, 2 no MMA, 4 no row copies, 8 no zero-fill copies
 };
 
@@ -177,12 +189,15 @@ struct __align__(8) Control2 {
   // bit 4 frees the W slot afterwards, bit 5 end of super tile (no data), bits 8.. K-steps
   uint32_t a_info[kMaxAStages];
   uint32_t group_mask[kProducerWarps][kMaxSub];
+  unsigned long long group_bar;        // barrier among the producer warps
   uint32_t tmem_base;
   int abort_flag;
 };
 
 template <typename Map, int ESIZE>
-__global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, const Map map) {
+__global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, const Map map,
+                                                              const __grid_constant__ CUtensorMap in_desc,
+                                                              const __grid_constant__ CUtensorMap w_desc) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -195,20 +210,22 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
   Control2* ctl = reinterpret_cast<Control2*>(reinterpret_cast<unsigned char*>(idx_tile) + kIdxTileBytes);
   volatile int* abort_flag = &ctl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool use_tma = kTmaProducers && p.use_tma;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.a_stages; ++s) {
-      mbar_init(smem_u32(&ctl->a_full[s]), kProducerWarps);
+      mbar_init(smem_u32(&ctl->a_full[s]), use_tma ? 1 : kProducerWarps);
       mbar_init(smem_u32(&ctl->a_empty[s]), 1);
     }
     for (int s = 0; s < p.w_slots; ++s) {
-      mbar_init(smem_u32(&ctl->w_full[s]), kProducerWarps);
+      mbar_init(smem_u32(&ctl->w_full[s]), use_tma ? 1 : kProducerWarps);
       mbar_init(smem_u32(&ctl->w_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl->acc_full[b]), 1);
       mbar_init(smem_u32(&ctl->acc_empty[b]), kEpilogueWarps * 32);
     }
+    mbar_init(smem_u32(&ctl->group_bar), kProducerWarps);
     ctl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -234,6 +251,15 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
     const int w_col_bytes = p.w_cols * ESIZE;
     StageQueue queue;
     queue.clear();
+    // Barrier among the four producer warps with a bounded wait (a plain bar.sync could hang if one warp
+    // had given up after an expired wait).
+    uint32_t group_phase = 0;
+    auto producer_sync = [&]() {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->group_bar));
+      ok = mbar_wait_warp(smem_u32(&ctl->group_bar), group_phase, abort_flag, 28, lane) && ok;
+      group_phase ^= 1u;
+    };
     long long t_pref = 0, t_acq_a = 0, t_acq_w = 0, t_total0 = PROF_CLOCK(), t_push = 0, t_copy = 0;
     long long n_flush = 0;
     // Wait until the consumer has released a slot.  If it has not yet, first hand over every stage
@@ -316,14 +342,72 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
       }
     };
 
+    // TMA form of send_w: one lane of producer warp 0 fetches the slice with tiled copies (the
+    // descriptor's box is one 128-byte column block of the slice); the other warps only keep count.
+    auto send_w_tma = [&](int k, int kb) {
+      if (pwarp == 0) {
+        ok = acquire(smem_u32(&ctl->w_empty[w_slot]), w_phase ^ 1u, 29);
+        if (ok && lane == 0) {
+          const uint32_t bar = smem_u32(&ctl->w_full[w_slot]);
+          const uint32_t w_base = w_ring + (uint32_t)w_slot * p.w_slot_bytes;
+          if (p.b_mn_major) {
+            const int n_cb = (w_col_bytes + 127) >> 7;
+            mbar_arrive_expect_tx(bar, (uint32_t)(n_cb * kr * 128));
+            for (int cb = 0; cb < n_cb; ++cb)
+              tma_load_2d(w_base + (uint32_t)(cb * kr * 128), &w_desc, bar, cb * kr, k * p.w_rows + kb * kr);
+          } else {
+            mbar_arrive_expect_tx(bar, (uint32_t)(p.w_rows * 128));
+            tma_load_2d(w_base, &w_desc, bar, kb * kr, k * p.w_rows);
+          }
+        }
+        __syncwarp();
+      }
+      if (++w_slot == p.w_slots) {
+        w_slot = 0;
+        w_phase ^= 1u;
+      }
+    };
+
+    // TMA form of send_a, executed by ONE warp per stage (the warp that owns the sub tile): lane l
+    // fetches rows 4l..4l+3 of the stage with one tile::gather4; "no neighbour" (-1) and indices past
+    // the end of the source are out-of-bounds rows, which the copy engine fills with zeros.  The
+    // stage's mbarrier counts one arrival (lane 0, together with the expected byte count).
+    auto send_a_tma = [&](int kb, const int32_t* idx4, uint32_t flags, bool mine_to_send) {
+      if (mine_to_send) {
+        ok = acquire(smem_u32(&ctl->a_empty[a_stage]), a_phase ^ 1u, 27);
+        if (ok) {
+          const uint32_t bar = smem_u32(&ctl->a_full[a_stage]);
+          const bool marker = (flags & 32u) != 0;
+          const int valid_bytes = marker ? 0 : min(128, red_bytes - kb * 128);
+          if (lane == 0) {
+            ctl->a_info[a_stage] = flags | ((uint32_t)(valid_bytes >> 5) << 8);
+            if (marker) mbar_arrive(bar); else mbar_arrive_expect_tx(bar, (uint32_t)kABlockBytes);
+          }
+          __syncwarp();
+          if (!marker) {
+            const int4 r = *reinterpret_cast<const int4*>(idx4 + 4 * lane);
+            tma_gather4(a_ring + (uint32_t)a_stage * kABlockBytes + (uint32_t)lane * 512u, &in_desc, bar,
+                        kb * (128 / ESIZE), r.x, r.y, r.z, r.w);
+          }
+        }
+      }
+      if (++a_stage == p.a_stages) {
+        a_stage = 0;
+        a_phase ^= 1u;
+      }
+    };
+
     for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
-      const int64_t row0 = st_i * p.sub * kTileM + t;          // this thread's row in sub tile 0
+      const int64_t row0 = st_i * p.sub * kTileM + t;          // this thread's position in sub tile 0
       typename Map::RowState rs[kMaxSub];
+      int64_t arow[kMaxSub];                                    // the rows these positions stand for
       bool row_ok[kMaxSub];
 #pragma unroll
       for (int s = 0; s < kMaxSub; ++s) {
-        row_ok[s] = s < p.sub && row0 + (int64_t)s * kTileM < p.n_rows;
-        rs[s] = map.row_state(row0 + (int64_t)s * kTileM, row_ok[s]);
+        const int64_t pos = row0 + (int64_t)s * kTileM;
+        row_ok[s] = s < p.sub && pos < p.n_rows;
+        arow[s] = (row_ok[s] && p.order) ? (int64_t)__ldg(p.order + pos) : pos;
+        rs[s] = map.row_state(arow[s], row_ok[s]);
       }
       uint32_t touched = 0;                                     // sub tiles whose accumulator has been started
       for (int k0 = 0; k0 < p.K && ok; k0 += kGroup) {
@@ -335,10 +419,10 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
         for (int s = 0; s < kMaxSub; ++s) {
 #pragma unroll
           for (int j = 0; j < kGroup; ++j)
-            got[s][j] = (row_ok[s] && j < kn && !(p.dbg & 32)) ? map.get(rs[s], row0 + (int64_t)s * kTileM, k0 + j) : -1;
+            got[s][j] = (row_ok[s] && j < kn && !(p.dbg & 32)) ? map.get(rs[s], arow[s], k0 + j) : -1;
         }
         // every stage of the previous group has been issued by every producer thread: the tile can be rewritten
-        producer_bar_sync<kProducerThreads>();
+        producer_sync();
 #pragma unroll
         for (int s = 0; s < kMaxSub; ++s) {
           mine[s] = 0;
@@ -355,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
           const uint32_t wm = __reduce_or_sync(0xFFFFFFFFu, mine[s]);
           if (lane == 0) ctl->group_mask[pwarp][s] = wm;
         }
-        producer_bar_sync<kProducerThreads>();
+        producer_sync();
         uint32_t m[kMaxSub], m_any = 0;
 #pragma unroll
         for (int s = 0; s < kMaxSub; ++s) {
@@ -371,7 +455,7 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
           for (int s = 0; s < kMaxSub; ++s) users |= ((m[s] >> j) & 1u) << s;
           const int last_user = 31 - __clz(users);
           for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
-            send_w(k0 + j, kb);
+            if (use_tma) send_w_tma(k0 + j, kb); else send_w(k0 + j, kb);
             bool first_of_w = true;
 #pragma unroll
             for (int s = 0; s < kMaxSub; ++s) {
@@ -381,7 +465,10 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
               if (kb == 0 && !((touched >> s) & 1u)) flags |= 4u;
               if (first_of_w) flags |= 8u;
               if (s == last_user) flags |= 16u;
-              send_a(kb, has, idx_tile[(j * kMaxSub + s) * kTileM + t], flags);
+              if (use_tma)
+                send_a_tma(kb, idx_tile + (j * kMaxSub + s) * kTileM, flags, pwarp == s);
+              else
+                send_a(kb, has, idx_tile[(j * kMaxSub + s) * kTileM + t], flags);
               first_of_w = false;
             }
           }
@@ -392,11 +479,23 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
       for (int s = 0; s < p.sub && ok; ++s) {
         const bool exists = (st_i * p.sub + s) * (int64_t)kTileM < p.n_rows;
         if (exists && !((touched >> s) & 1u)) {
-          send_w(0, 0);
-          if (ok) send_a(0, false, 0, (uint32_t)s | 4u | 8u | 16u);
+          if (use_tma) send_w_tma(0, 0); else send_w(0, 0);
+          if (ok) {
+            if (use_tma) {
+              // an all "-1" index line: every row of the stage is zero-filled
+              producer_sync();
+              idx_tile[t] = -1;
+              producer_sync();
+              send_a_tma(0, idx_tile, (uint32_t)s | 4u | 8u | 16u, pwarp == 0);
+            } else {
+              send_a(0, false, 0, (uint32_t)s | 4u | 8u | 16u);
+            }
+          }
         }
       }
-      if (ok) send_a(0, false, 0, 32u);                          // end of super tile
+      if (ok) {                                                   // end of super tile
+        if (use_tma) send_a_tma(0, idx_tile, 32u, pwarp == 0); else send_a(0, false, 0, 32u);
+      }
       queue.flush(lane);                                          // let the epilogue of this super tile start
     }
     queue.flush(lane);
@@ -500,7 +599,8 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
       for (int s = 0; s < p.sub; ++s) {
         const int64_t row = (st_i * p.sub + s) * (int64_t)kTileM + warp * 32 + lane;
         if ((st_i * p.sub + s) * (int64_t)kTileM >= p.n_rows) break;         // whole sub tile past the end
-        char* out_row = static_cast<char*>(p.out) + (size_t)row * p.c_acc * out_es;
+        const int64_t dst_row = (p.order && row < p.n_rows) ? (int64_t)__ldg(p.order + row) : row;
+        char* out_row = static_cast<char*>(p.out) + (size_t)dst_row * p.c_acc * out_es;
         const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * set_cols + s * p.c_acc);
         for (int c0 = 0; c0 < p.c_acc; c0 += 32) {
           uint32_t v[32];
@@ -522,6 +622,11 @@ __global__ void __launch_bounds__(kThreads, 2) gather2_kernel(const Params2 p, c
     }
   }
 
+  // After an expired wait, bulk copies of this CTA may still be in flight: give them time to land
+  // before the CTA's shared memory and mbarriers go away (they complete within microseconds).
+  if (*abort_flag) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) {
@@ -549,6 +654,7 @@ constexpr int kWgradBSlotsMax = 6;
 struct WgradParams {
   const void* x;         // (n_src, cin)
   const void* dy;        // (n_rows, cout)
+  const int32_t* order;  // optional: tile row r stands for row order[r] of the map and of dY
   float* partial;        // (n_chunks, K, cin, cout)
   int64_t n_rows, n_src, n_tiles, tiles_per_chunk;
   int K, cin, cout, esize;
@@ -658,8 +764,9 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p,
     };
 
     for (int64_t tile = tile_begin; tile < tile_end && ok; ++tile) {
-      const int64_t row = tile * kTileM + t;
-      const bool row_ok = row < p.n_rows;
+      const int64_t pos = tile * kTileM + t;
+      const bool row_ok = pos < p.n_rows;
+      const int64_t row = (row_ok && p.order) ? (int64_t)__ldg(p.order + pos) : pos;
       typename Map::RowState rs = map.row_state(row, row_ok);
       // neighbours of this row for the offsets of the group (independent loads, then a bit mask)
       int32_t idx[32];
@@ -829,6 +936,7 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   p->in = in;
   p->w = w;
   p->out = out;
+  p->order = nullptr;
   p->n_rows = n_rows;
   p->n_src = n_src;
   p->K = K;
@@ -854,18 +962,7 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   while (cols < p->acc_bufs * sub * c_acc) cols <<= 1;
   p->tmem_cols = cols;
   p->w_slots = 3;
-  const bool two_ctas = getenv("ST_TC_OCC2") != nullptr;       // experiment: two CTAs per SM
-  if (two_ctas) {
-    if (sub > 2) sub = 2;
-    p->sub = sub;
-    p->n_super = (n_tiles + sub - 1) / sub;
-    p->acc_bufs = 1;
-    int c2 = 32;
-    while (c2 < sub * c_acc) c2 <<= 1;
-    p->tmem_cols = c2;
-    p->w_slots = 2;
-  }
-  const int budget = (two_ctas ? 110 : 222) * 1024 - tc::kIdxTileBytes;
+  const int budget = 222 * 1024 - tc::kIdxTileBytes;
   int a_stages = (budget - p->w_slots * p->w_slot_bytes) / tc::kABlockBytes;
   if (a_stages > tc::kMaxAStages) a_stages = tc::kMaxAStages;
   if (a_stages < 4) {
@@ -891,8 +988,72 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   return true;
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    cudaGetLastError();
+  }
+  return fn;
+}
+
+// Descriptor of a row-major (rows, cols) matrix for tile::gather4: box = one 128-byte line, 128-byte swizzle.
+static bool make_gather_desc(CUtensorMap* desc, const void* base, int64_t rows, int cols, int esize, int dtype) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || !base || rows < 1 || (reinterpret_cast<uintptr_t>(base) & 15) || (cols * esize) % 16) return false;
+  const CUtensorMapDataType dt = dtype == ST_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == ST_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                   : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)cols * esize};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / esize), 1};
+  const cuuint32_t estride[2] = {1, 1};
+  return fn(desc, dt, 2, const_cast<void*>(base), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Descriptor of the weights seen as a (K * w_rows, w_cols) matrix; the box is one 128-byte column block
+// of a W[k] slice: `box_rows` rows.  `atom32` selects the 128-byte swizzle with 32-byte atoms (MN-major
+// operands of 32-bit elements), else the plain 128-byte swizzle.
+static bool make_weight_desc(CUtensorMap* desc, const void* base, int64_t rows, int cols, int esize, int dtype,
+                             int box_rows, bool atom32) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || !base || rows < 1 || box_rows < 1 || box_rows > 256 || (reinterpret_cast<uintptr_t>(base) & 15) ||
+      (cols * esize) % 16)
+    return false;
+  const CUtensorMapDataType dt = dtype == ST_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == ST_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                   : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t gstride[1] = {(cuuint64_t)cols * esize};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / esize), (cuuint32_t)box_rows};
+  const cuuint32_t estride[2] = {1, 1};
+  return fn(desc, dt, 2, const_cast<void*>(base), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <typename Map>
-static int launch_gather(const tc::Params2& p, const Map& map, cudaStream_t stream) {
+static int launch_gather(tc::Params2 p, const Map& map, cudaStream_t stream) {
+  CUtensorMap in_desc, w_desc;
+  memset(&in_desc, 0, sizeof(in_desc));
+  memset(&w_desc, 0, sizeof(w_desc));
+  p.use_tma = tc::kTmaProducers && p.n_src > 0 &&
+              make_gather_desc(&in_desc, p.in, p.n_src, p.c_red, p.esize, p.out_kind) &&
+              make_weight_desc(&w_desc, p.w, (int64_t)p.K * p.w_rows, p.w_cols, p.esize, p.out_kind,
+                               p.b_mn_major ? 128 / p.esize : p.w_rows, p.b_mn_major && p.esize == 4) ? 1 : 0;
   const size_t smem = (size_t)p.w_slots * p.w_slot_bytes + (size_t)p.a_stages * tc::kABlockBytes +
                       tc::kIdxTileBytes + sizeof(tc::Control2) + 1024;
   auto kernel = p.esize == 2 ? tc::gather2_kernel<Map, 2> : tc::gather2_kernel<Map, 4>;
@@ -905,21 +1066,21 @@ static int launch_gather(const tc::Params2& p, const Map& map, cudaStream_t stre
     }
     configured[p.esize == 4] = true;
   }
-  const int64_t ctas = (int64_t)sm_count() * (getenv("ST_TC_OCC2") ? 2 : 1);
-  int64_t grid = p.n_super < ctas ? p.n_super : ctas;
-  kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, map);
+  int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
+  kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, map, in_desc, w_desc);
   note_launches(1);
   return check_launch("tc gather");
 }
 
-int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, void* out, int64_t n_rows,
-                   int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream) {
+int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, const int32_t* order, void* out,
+                   int64_t n_rows, int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream) {
   tc::Params2 p;
   if (!fill_params2(&p, dtype, in, w, out, n_rows, n_src, K, c_red, c_acc, w_transposed)) {
     set_error("tc_conv_gather: shape does not fit shared memory");
     return ST_ERR_UNSUPPORTED;
   }
   if (n_rows == 0) return ST_OK;
+  p.order = order;
   return launch_gather(p, tc::StoredRows{map, K}, stream);
 }
 
@@ -1053,15 +1214,17 @@ static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void*
   }
   plan->p.x = x;
   plan->p.dy = dy;
+  plan->p.order = nullptr;
   plan->p.partial = partial;
   plan->p.n_src = n_src;
   return true;
 }
 
-int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, float* partial, int* n_chunks_out,
-                  int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream) {
+int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const int32_t* order, float* partial,
+                  int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream) {
   WgradPlan plan;
   if (!prepare_wgrad(&plan, dtype, x, dy, partial, n_rows, n_src, K, cin, cout)) return ST_ERR_UNSUPPORTED;
+  plan.p.order = order;
   *n_chunks_out = plan.n_chunks;
   return launch_wgrad(plan, tc::StoredRows{map, K}, stream);
 }

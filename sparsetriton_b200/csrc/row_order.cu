@@ -1,0 +1,196 @@
+// Row order of a neighbour map for the tensor-core kernels.
+//
+// The implicit-GEMM kernels work on tiles of 128 rows and skip a kernel offset for a tile only when
+// none of its 128 rows has a neighbour there.  In the natural row order nearly every tile touches
+// nearly every offset, and 70-80 % of what the tensor cores multiply is zero fill.  Rows with the
+// same set of occupied offsets behave alike, so the kernels may walk the rows in the order of their
+// K-bit occupancy mask instead: tiles then share masks, far fewer (tile, offset) stages remain and
+// those are denser.  The order only decides which rows share a tile; every row's own sum still
+// runs over the offsets in ascending k, so forward and feature-gradient results do not depend on it.
+//
+// order = stable LSD radix sort of the rows by mask (9-bit digits).  Each warp owns a contiguous
+// chunk of the sequence and ranks its elements 32 at a time with match.any, which keeps equal digits
+// in their original order: the result is deterministic (no atomics between warps).
+#include "common.cuh"
+
+namespace st {
+
+namespace {
+
+constexpr int kSortChunk = 1024;        // elements per warp
+constexpr int kSortWarps = 4;           // warps per block
+constexpr int kDigitBitsMax = 9;
+constexpr int kBucketsMax = 1 << kDigitBitsMax;
+
+// key[r] = occupancy mask of row r (bit k: nbr[r,k] >= 0) for K <= 32, a 32-bit hash of the whole
+// pattern beyond (equal patterns still get equal keys); val[r] = r.
+__global__ void __launch_bounds__(128) row_keys_kernel(const int32_t* __restrict__ nbr, int64_t n, int K,
+                                                      uint32_t* __restrict__ keys, int32_t* __restrict__ vals) {
+  extern __shared__ int32_t stage[];                     // 128 rows x K entries when K <= 64
+  const int64_t row0 = (int64_t)blockIdx.x * 128;
+  const int rows = (int)min((int64_t)128, n - row0);
+  const int64_t row = row0 + threadIdx.x;
+  uint32_t key = 0;
+  if (K <= 64) {
+    const int32_t* src = nbr + row0 * K;
+    for (int e = threadIdx.x; e < rows * K; e += 128) stage[e] = __ldg(src + e);
+    __syncthreads();
+    if (threadIdx.x < rows) {
+      const int32_t* mine = stage + threadIdx.x * K;
+      if (K <= 32) {
+        for (int k = 0; k < K; ++k) key |= (mine[k] >= 0 ? 1u : 0u) << k;
+      } else {
+        for (int k = 0; k < K; ++k) key = key * 0x9E3779B1u + (mine[k] >= 0 ? (uint32_t)(k + 1) : 0u);
+      }
+    }
+  } else if (threadIdx.x < rows) {
+    for (int k = 0; k < K; ++k) key = key * 0x9E3779B1u + (__ldg(nbr + row * K + k) >= 0 ? (uint32_t)(k + 1) : 0u);
+  }
+  if (threadIdx.x < rows) {
+    keys[row] = key;
+    vals[row] = (int32_t)row;
+  }
+}
+
+// hist[d * n_chunks + chunk] = number of elements of the chunk whose digit is d
+__global__ void __launch_bounds__(kSortWarps * 32) sort_hist_kernel(const uint32_t* __restrict__ keys, int64_t n,
+                                                                   int shift, int bits, int64_t n_chunks,
+                                                                   uint32_t* __restrict__ hist) {
+  __shared__ uint32_t count[kSortWarps][kBucketsMax];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t chunk = (int64_t)blockIdx.x * kSortWarps + warp;
+  const int buckets = 1 << bits;
+  for (int d = lane; d < buckets; d += 32) count[warp][d] = 0;
+  __syncwarp();
+  if (chunk < n_chunks) {
+    const int64_t begin = chunk * kSortChunk, end = min(n, begin + kSortChunk);
+    for (int64_t i = begin + lane; i < end; i += 32)
+      atomicAdd(&count[warp][(keys[i] >> shift) & (buckets - 1)], 1u);
+    __syncwarp();
+    for (int d = lane; d < buckets; d += 32) hist[(int64_t)d * n_chunks + chunk] = count[warp][d];
+  }
+}
+
+// Stable scatter of one digit pass: `first` is the exclusive scan of hist.
+__global__ void __launch_bounds__(kSortWarps * 32)
+    sort_scatter_kernel(const uint32_t* __restrict__ keys, const int32_t* __restrict__ vals, int64_t n, int shift,
+                        int bits, int64_t n_chunks, const uint32_t* __restrict__ first, uint32_t* __restrict__ keys_out,
+                        int32_t* __restrict__ vals_out) {
+  __shared__ uint32_t next[kSortWarps][kBucketsMax];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t chunk = (int64_t)blockIdx.x * kSortWarps + warp;
+  if (chunk >= n_chunks) return;
+  const int buckets = 1 << bits;
+  for (int d = lane; d < buckets; d += 32) next[warp][d] = first[(int64_t)d * n_chunks + chunk];
+  __syncwarp();
+  const int64_t begin = chunk * kSortChunk, end = min(n, begin + kSortChunk);
+  const uint32_t lower = (1u << lane) - 1u;
+  for (int64_t i0 = begin; i0 < end; i0 += 32) {
+    const int64_t i = i0 + lane;
+    const bool live = i < end;
+    const uint32_t key = live ? keys[i] : 0u;
+    const int32_t val = live ? vals[i] : 0;
+    // lanes past the end get a digit of their own so that they never share a bucket with live ones
+    const uint32_t d = live ? ((key >> shift) & (uint32_t)(buckets - 1)) : 0xFFFFFFFFu;
+    const uint32_t peers = __match_any_sync(0xFFFFFFFFu, d);
+    uint32_t base = 0;
+    if (live) base = next[warp][d];
+    __syncwarp();
+    if (live && (peers & lower) == 0) next[warp][d] = base + (uint32_t)__popc(peers);
+    __syncwarp();
+    if (live) {
+      const uint32_t dst = base + (uint32_t)__popc(peers & lower);
+      keys_out[dst] = key;
+      vals_out[dst] = val;
+    }
+  }
+}
+
+struct OrderScratch {
+  uint32_t *keys_a, *keys_b, *hist;
+  int32_t* vals_b;
+  void* scan_tmp;
+  int64_t n_chunks;
+};
+
+int64_t carve(OrderScratch* s, void* ws, int64_t n, int K) {
+  (void)K;
+  const int64_t n_chunks = n > 0 ? (n + kSortChunk - 1) / kSortChunk : 1;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) {
+    char* p = ws ? static_cast<char*>(ws) + off : nullptr;
+    off += align_up(bytes > 0 ? bytes : 1, 256);
+    return p;
+  };
+  const int64_t nn = n > 0 ? n : 1;
+  s->keys_a = reinterpret_cast<uint32_t*>(take(nn * 4));
+  s->keys_b = reinterpret_cast<uint32_t*>(take(nn * 4));
+  s->vals_b = reinterpret_cast<int32_t*>(take(nn * 4));
+  s->hist = reinterpret_cast<uint32_t*>(take(n_chunks * kBucketsMax * 4));
+  s->scan_tmp = take(scan_tmp_bytes(n_chunks * kBucketsMax));
+  s->n_chunks = n_chunks;
+  return off;
+}
+
+}  // namespace
+
+}  // namespace st
+
+using namespace st;
+
+extern "C" {
+
+int64_t st_map_row_order_workspace_bytes(int64_t n_rows, int K) {
+  OrderScratch s;
+  return carve(&s, nullptr, n_rows, K);
+}
+
+int st_map_row_order(const int32_t* nbr, int64_t n_rows, int K, int32_t* order, void* workspace,
+                     int64_t workspace_bytes, void* stream) {
+  if (n_rows < 0 || K < 1 || n_rows > 0x7FFFFFFFll || (n_rows > 0 && (!nbr || !order || !workspace))) {
+    set_error("st_map_row_order: bad arguments");
+    return ST_ERR_ARG;
+  }
+  if (n_rows == 0) return ST_OK;
+  OrderScratch s;
+  if (workspace_bytes < carve(&s, workspace, n_rows, K)) {
+    set_error("st_map_row_order: workspace of %lld bytes is too small", (long long)workspace_bytes);
+    return ST_ERR_WORKSPACE;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int key_bits = K < 32 ? K : 32;
+  const int passes = (key_bits + kDigitBitsMax - 1) / kDigitBitsMax;
+  const int bits = (key_bits + passes - 1) / passes;
+  // ping-pong so that the last pass lands in `order`: values start in `order` when the number of
+  // passes is even, in the scratch copy when it is odd
+  uint32_t* keys_in = s.keys_a;
+  uint32_t* keys_out = s.keys_b;
+  int32_t* vals_in = (passes % 2 == 0) ? order : s.vals_b;
+  int32_t* vals_out = (passes % 2 == 0) ? s.vals_b : order;
+  const size_t stage_bytes = K <= 64 ? (size_t)128 * K * 4 : 0;
+  {
+    row_keys_kernel<<<(unsigned)((n_rows + 127) / 128), 128, stage_bytes, st>>>(nbr, n_rows, K, keys_in, vals_in);
+    note_launches(1);
+  }
+  const unsigned blocks = (unsigned)((s.n_chunks + kSortWarps - 1) / kSortWarps);
+  const int64_t n_hist = s.n_chunks << bits;
+  for (int pass = 0; pass < passes; ++pass) {
+    const int shift = pass * bits;
+    {
+      sort_hist_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, n_rows, shift, bits, s.n_chunks, s.hist);
+      note_launches(1);
+    }
+    int rc = exclusive_scan_u32(s.hist, s.hist, n_hist, s.scan_tmp, nullptr, st);
+    if (rc != ST_OK) return rc;
+    {
+      sort_scatter_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, vals_in, n_rows, shift, bits, s.n_chunks, s.hist,
+                                                              keys_out, vals_out);
+      note_launches(1);
+    }
+    uint32_t* tk = keys_in; keys_in = keys_out; keys_out = tk;
+    int32_t* tv = vals_in; vals_in = vals_out; vals_out = tv;
+  }
+  return check_launch("st_map_row_order");
+}
+
+}  // extern "C"

@@ -120,6 +120,31 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// ---- TMA (bulk tensor copies).  The descriptor lives in kernel parameter space (__grid_constant__).
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+// Four rows of a 2-D tensor (row coordinates r0..r3, first column `col`) -> four consecutive 128-byte
+// lines at `dst`, written with the descriptor's swizzle; rows outside the tensor (e.g. -1) arrive as
+// zeros.  Completion is counted in bytes on `bar`.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* desc, uint32_t bar, int col, int r0, int r1,
+                                            int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+      "l"(desc), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
+// A (cols x rows) box of a 2-D tensor starting at (col, row) -> dense lines at `dst`.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* desc, uint32_t bar, int col, int row) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(desc), "r"(bar), "r"(col), "r"(row)
+      : "memory");
+}
+
 // Lagged, warp-aggregated hand-over of cp.async stages.
 //
 // Having every producer thread arrive on a stage's mbarrier costs ~130 serialised shared-memory

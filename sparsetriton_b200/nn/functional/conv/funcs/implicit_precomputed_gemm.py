@@ -18,7 +18,10 @@ from sparsetriton_b200 import _lib, trace
 
 from ._channels import pad_cols, pad_weight, padded_widths
 
-__all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map"]
+__all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map", "row_order"]
+
+# below this many rows the sort costs more than the denser tiles save
+_MIN_ROWS_FOR_ORDER = 16384
 
 
 def inverse_map(neighbor_indices, n_in):
@@ -34,6 +37,27 @@ def inverse_map(neighbor_indices, n_in):
     _lib.check(rc, "st_map_invert")
     neighbor_indices._st_inverse = inv
     return inv
+
+
+def row_order(map_tensor):
+    """Rows of a (forward or inverse) map sorted by which offsets they occupy, or None when the
+    switch is off or the map is small.  Memoised on the map tensor like the inverse."""
+    from sparsetriton_b200.config import get_row_order
+    n_rows, K = map_tensor.shape
+    if not get_row_order() or n_rows < _MIN_ROWS_FOR_ORDER:
+        return None
+    cached = getattr(map_tensor, "_st_order", None)
+    if cached is not None:
+        return cached
+    L = _lib.lib()
+    order = torch.empty((n_rows,), dtype=torch.int32, device=map_tensor.device)
+    ws = _lib.workspace(L.st_map_row_order_workspace_bytes(n_rows, K), map_tensor.device)
+    with torch.cuda.device(map_tensor.device), trace.stage("row_order"):
+        rc = L.st_map_row_order(_lib.ptr(map_tensor), n_rows, K, _lib.ptr(order), _lib.ptr(ws), ws.numel(),
+                                _lib.stream_ptr())
+    _lib.check(rc, "st_map_row_order")
+    map_tensor._st_order = order
+    return order
 
 
 class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
@@ -56,10 +80,12 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
         ctx.flops = 2.0 * trace.map_pairs(nbr) * c_in * c_out if trace.active() else 0.0
         if n_out > 0:
+            order = row_order(nbr)
             with torch.cuda.device(x.device), trace.stage("conv_fwd", work=ctx.flops):
-                rc = _lib.lib().st_conv_fwd(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), _lib.ptr(y), n_in, n_out,
-                                            K, c_in, c_out, None, 0, _lib.stream_ptr())
-            _lib.check(rc, "st_conv_fwd")
+                rc = _lib.lib().st_conv_fwd_ordered(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), _lib.ptr(order),
+                                                    _lib.ptr(y), n_in, n_out, K, c_in, c_out, None, 0,
+                                                    _lib.stream_ptr())
+            _lib.check(rc, "st_conv_fwd_ordered")
         ctx.save_for_backward(x, w, nbr)
         ctx.w_dtype = weights.dtype
         return y if c_out == ctx.true_widths[1] else y[:, :ctx.true_widths[1]].contiguous()
@@ -81,17 +107,21 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
                 dx = torch.empty_like(x)
                 if n_in > 0:
                     inv = inverse_map(nbr, n_in)
+                    inv_order = row_order(inv)
                     with trace.stage("conv_dgrad", work=ctx.flops):
-                        rc = L.st_conv_dgrad(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv), _lib.ptr(dx), n_in, n_out,
-                                             K, c_in, c_out, None, 0, stream)
-                    _lib.check(rc, "st_conv_dgrad")
+                        rc = L.st_conv_dgrad_ordered(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv),
+                                                     _lib.ptr(inv_order), _lib.ptr(dx), n_in, n_out, K, c_in, c_out,
+                                                     None, 0, stream)
+                    _lib.check(rc, "st_conv_dgrad_ordered")
             if ctx.needs_input_grad[1]:
                 dw = torch.empty_like(w)
                 ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
+                order = row_order(nbr)
                 with trace.stage("conv_wgrad", work=ctx.flops):
-                    rc = L.st_conv_wgrad(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), _lib.ptr(dw), n_in, n_out, K,
-                                         c_in, c_out, _lib.ptr(ws), ws.numel(), stream)
-                _lib.check(rc, "st_conv_wgrad")
+                    rc = L.st_conv_wgrad_ordered(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), _lib.ptr(order),
+                                                 _lib.ptr(dw), n_in, n_out, K, c_in, c_out, _lib.ptr(ws), ws.numel(),
+                                                 stream)
+                _lib.check(rc, "st_conv_wgrad_ordered")
                 dw = dw.to(ctx.w_dtype)
         if dx is not None and t_in != c_in:
             dx = dx[:, :t_in].contiguous()

@@ -1,0 +1,117 @@
+"""Row order of a neighbour map (st_map_row_order) and the products that walk the rows in it.
+
+The order must be the stable sort of the rows by their occupancy mask; forward and feature
+gradient must give bit-identical results with and without it (a row's own sum never changes), the
+weight gradient the same result within the storage tolerance (its row sum is reordered).
+"""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import TOL, rel_err, t2n
+from sparsetriton_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def _random_map(n_rows, n_src, K, density, seed, dev, patterns=None):
+    """A map like a convolution's: within one offset no source row is used twice (so the inverse
+    map exists); rows optionally draw their occupied offsets from a few masks."""
+    g = torch.Generator().manual_seed(seed)
+    if patterns:
+        masks = torch.rand(patterns, K, generator=g) < density
+        keep = masks[torch.randint(0, patterns, (n_rows,), generator=g)]
+    else:
+        keep = torch.rand(n_rows, K, generator=g) < density
+    nbr = torch.full((n_rows, K), -1, dtype=torch.int32)
+    for k in range(K):
+        rows = torch.nonzero(keep[:, k]).flatten()
+        rows = rows[:n_src]
+        nbr[rows, k] = torch.randperm(n_src, generator=g)[:rows.numel()].to(torch.int32)
+    return nbr.to(dev)
+
+
+def _order(nbr):
+    L = _lib.lib()
+    n, K = nbr.shape
+    order = torch.full((n,), -7, dtype=torch.int32, device=nbr.device)
+    ws = _lib.workspace(L.st_map_row_order_workspace_bytes(n, K), nbr.device)
+    with torch.cuda.device(nbr.device):
+        _lib.check(L.st_map_row_order(_lib.ptr(nbr), n, K, _lib.ptr(order), _lib.ptr(ws), ws.numel(),
+                                      _lib.stream_ptr()), "st_map_row_order")
+    return order
+
+
+@pytest.mark.parametrize("n_rows,K,density,patterns", [
+    (1, 27, 0.5, None), (127, 27, 0.3, None), (5000, 27, 0.3, 40), (70001, 27, 0.2, None), (3000, 8, 0.5, None),
+    (4097, 1, 0.5, None), (2500, 32, 0.4, 9), (1500, 125, 0.1, 12), (900, 343, 0.05, 5)])
+def test_order_is_the_stable_sort_by_mask(cuda_device, n_rows, K, density, patterns):
+    nbr = _random_map(n_rows, 1000, K, density, 11 + n_rows + K, cuda_device, patterns)
+    order = _order(nbr).cpu().numpy().astype(np.int64)
+    assert np.array_equal(np.sort(order), np.arange(n_rows))                  # a permutation
+    occ = (nbr.cpu().numpy() >= 0)
+    if K <= 32:
+        key = (occ.astype(np.uint64) << np.arange(K, dtype=np.uint64)).sum(1)
+        assert np.array_equal(order, np.argsort(key, kind="stable"))
+    else:
+        # beyond 32 offsets the key is a hash of the pattern: equal patterns stay together, in row order
+        packed = np.packbits(occ, axis=1)
+        sorted_patterns = packed[order]
+        change = np.any(sorted_patterns[1:] != sorted_patterns[:-1], axis=1)
+        n_groups = 1 + int(change.sum())
+        assert n_groups == len(np.unique(packed, axis=0))
+        same = ~change
+        assert np.all(order[1:][same] > order[:-1][same])
+    again = _order(nbr).cpu().numpy()
+    assert np.array_equal(again, order)                                        # run-to-run identical
+
+
+def test_empty_map(cuda_device):
+    L = _lib.lib()
+    assert L.st_map_row_order(None, 0, 27, None, None, 0, _lib.stream_ptr()) == 0
+    assert L.st_map_row_order(None, 5, 27, None, None, 0, _lib.stream_ptr()) == -1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16], ids=["fp32", "bf16", "fp16"])
+@pytest.mark.parametrize("n_rows,n_src,K,cin,cout,patterns", [
+    (3000, 2000, 27, 32, 64, 20), (70001, 40000, 27, 64, 128, None), (5000, 5000, 8, 16, 16, None),
+    (20000, 9000, 27, 128, 64, 30)])
+def test_products_with_order(cuda_device, oracle, dtype, n_rows, n_src, K, cin, cout, patterns):
+    dev = cuda_device
+    L = _lib.lib()
+    nbr = _random_map(n_rows, n_src, K, 0.25, 5, dev, patterns)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(n_src, cin, generator=g).to(dev, dtype)
+    w = (torch.randn(K, cin, cout, generator=g) / (cin * K * 0.25) ** 0.5).to(dev, dtype)
+    dy = torch.randn(n_rows, cout, generator=g).to(dev, dtype)
+    code = _lib.feat_code(x)
+    inv = torch.empty((n_src, K), dtype=torch.int32, device=dev)
+    y0, y1 = torch.empty(n_rows, cout, device=dev, dtype=dtype), torch.full((n_rows, cout), 7.0, device=dev, dtype=dtype)
+    dx0, dx1 = torch.empty_like(x), torch.full_like(x, 7.0)
+    dw0, dw1 = torch.empty_like(w), torch.full_like(w, 7.0)
+    ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_src, n_rows, K, cin, cout), dev)
+    with torch.cuda.device(dev):
+        s = _lib.stream_ptr()
+        _lib.check(L.st_map_invert(_lib.ptr(nbr), n_rows, K, n_src, _lib.ptr(inv), s), "st_map_invert")
+        order, inv_order = _order(nbr), _order(inv)
+        p = _lib.ptr
+        _lib.check(L.st_conv_fwd(code, p(x), p(w), p(nbr), p(y0), n_src, n_rows, K, cin, cout, None, 0, s), "fwd")
+        _lib.check(L.st_conv_fwd_ordered(code, p(x), p(w), p(nbr), p(order), p(y1), n_src, n_rows, K, cin, cout, None,
+                                         0, s), "fwd ordered")
+        _lib.check(L.st_conv_dgrad(code, p(dy), p(w), p(inv), p(dx0), n_src, n_rows, K, cin, cout, None, 0, s), "dgrad")
+        _lib.check(L.st_conv_dgrad_ordered(code, p(dy), p(w), p(inv), p(inv_order), p(dx1), n_src, n_rows, K, cin, cout,
+                                           None, 0, s), "dgrad ordered")
+        _lib.check(L.st_conv_wgrad(code, p(x), p(dy), p(nbr), p(dw0), n_src, n_rows, K, cin, cout, p(ws), ws.numel(), s),
+                   "wgrad")
+        _lib.check(L.st_conv_wgrad_ordered(code, p(x), p(dy), p(nbr), p(order), p(dw1), n_src, n_rows, K, cin, cout,
+                                           p(ws), ws.numel(), s), "wgrad ordered")
+        torch.cuda.synchronize()
+    assert torch.equal(y0, y1)
+    assert torch.equal(dx0, dx1)
+    tol = TOL[dtype]
+    assert rel_err(t2n(dw1), t2n(dw0)) < tol
+    xf, wf, dyf, m = t2n(x), t2n(w), t2n(dy), nbr.cpu().numpy()
+    assert rel_err(t2n(y1), oracle.conv_fwd(xf, wf, m)) < tol
+    assert rel_err(t2n(dx1), oracle.conv_dgrad(dyf, wf, m, n_src)) < tol
+    assert rel_err(t2n(dw1), oracle.conv_wgrad(xf, dyf, m, K, cin, cout)) < tol
+    assert _lib.device_status(dev)[0] == 0

@@ -145,6 +145,18 @@ int64_t st_map_row_order_workspace_bytes(int64_t n_rows, int K);
 int st_map_row_order(const int32_t* nbr, int64_t n_rows, int K, int32_t* order, void* workspace,
                      int64_t workspace_bytes, void* stream);
 
+/* Tile plan of a neighbour map for the tensor-core kernels: the map re-laid tile by tile (128 rows
+ * in the walking order) and offset by offset, so that the 128 source rows of one tile x offset step
+ * are one 512-byte line, plus one bit per tile and offset saying whether the step has any neighbour:
+ *   tmap [(tile*K + k)*128 + r] = nbr[order[tile*128 + r], k]   (ceil(n_rows/128)*K*128 int32)
+ *   tmask[tile*ceil(K/32) + k/32] bit k%32                      (ceil(n_rows/128)*ceil(K/32) uint32)
+ * sort_rows != 0 first computes `order` as st_map_row_order() does (workspace as for that call);
+ * sort_rows == 0 plans the natural order (order, workspace unused).
+ * No counterpart in the reference. */
+int64_t st_map_plan_workspace_bytes(int64_t n_rows, int K);
+int st_map_plan(const int32_t* nbr, int64_t n_rows, int K, int sort_rows, int32_t* order, int32_t* tmap,
+                uint32_t* tmask, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Scratch for st_map_pairs_count/_write. */
 int64_t st_map_pairs_workspace_bytes(int64_t n_out, int K);
 /* Number of valid entries of a neighbour map -> *n_pairs (device or pinned-host int64). */
@@ -177,18 +189,20 @@ int st_conv_dgrad(int dtype, const void* dY, const void* W, const int32_t* inv, 
 int st_conv_wgrad(int dtype, const void* X, const void* dY, const int32_t* nbr, void* dW, int64_t n_in,
                   int64_t n_out, int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
 
-/* The three products with a row order from st_map_row_order() of the map they are given
- * (row_order may be NULL: natural order).  Forward and feature-gradient results do not depend on
- * the order; the weight gradient adds its rows in that order (still the same from run to run). */
-int st_conv_fwd_ordered(int dtype, const void* X, const void* W, const int32_t* nbr, const int32_t* row_order, void* Y,
-                        int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
-                        int64_t workspace_bytes, void* stream);
-int st_conv_dgrad_ordered(int dtype, const void* dY, const void* W, const int32_t* inv, const int32_t* row_order,
-                          void* dX, int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
-                          int64_t workspace_bytes, void* stream);
-int st_conv_wgrad_ordered(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
-                          void* dW, int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
-                          int64_t workspace_bytes, void* stream);
+/* The three products over a map that comes with a tile plan from st_map_plan() (of the map they are
+ * given: the forward map for fwd and wgrad, the inverse map for dgrad).  row_order, tmap and tmask
+ * may each be NULL: without tmap/tmask the kernels read `nbr` itself, without row_order they walk
+ * the rows in natural order.  Forward and feature-gradient results do not depend on the order; the
+ * weight gradient adds its rows in that order (still the same from run to run). */
+int st_conv_fwd_planned(int dtype, const void* X, const void* W, const int32_t* nbr, const int32_t* row_order,
+                        const int32_t* tmap, const uint32_t* tmask, void* Y, int64_t n_in, int64_t n_out, int K,
+                        int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
+int st_conv_dgrad_planned(int dtype, const void* dY, const void* W, const int32_t* inv, const int32_t* row_order,
+                          const int32_t* tmap, const uint32_t* tmask, void* dX, int64_t n_in, int64_t n_out, int K,
+                          int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
+int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
+                          const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K,
+                          int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Weight gradient without any caller-side memory.  No counterpart in the reference: it exists for
  * hosts that may not allocate device memory around the call -- an inference or training plugin whose

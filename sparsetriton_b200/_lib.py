@@ -48,9 +48,11 @@ _SIGNATURES = {
     "st_conv_dgrad": ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),
     "st_conv_wgrad": ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),
 }
-_ORDERED_SIG = ([_INT, _PTR, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT)
-for _n in ("st_conv_fwd_ordered", "st_conv_dgrad_ordered", "st_conv_wgrad_ordered"):
-    _SIGNATURES[_n] = _ORDERED_SIG
+_PLANNED_SIG = ([_INT, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT)
+for _n in ("st_conv_fwd_planned", "st_conv_dgrad_planned", "st_conv_wgrad_planned"):
+    _SIGNATURES[_n] = _PLANNED_SIG
+_SIGNATURES["st_map_plan_workspace_bytes"] = ([_I64, _INT], _I64)
+_SIGNATURES["st_map_plan"] = ([_PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _I64, _PTR], _INT)
 _SIGNATURES["st_map_row_order_workspace_bytes"] = ([_I64, _INT], _I64)
 _SIGNATURES["st_map_row_order"] = ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR], _INT)
 _SIGNATURES["st_conv_wgrad_static_max_bytes"] = ([], _I64)

@@ -140,7 +140,8 @@ int64_t st_conv_hashfly_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, 
   return (m > inv ? m : inv) + 256;
 }
 
-int st_conv_fwd_ordered(int dtype, const void* X, const void* W, const int32_t* nbr, const int32_t* row_order, void* Y,
+int st_conv_fwd_planned(int dtype, const void* X, const void* W, const int32_t* nbr, const int32_t* row_order,
+                        const int32_t* tmap, const uint32_t* tmask, void* Y,
                         int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
                         int64_t workspace_bytes, void* stream) {
   (void)workspace;
@@ -154,7 +155,7 @@ int st_conv_fwd_ordered(int dtype, const void* X, const void* W, const int32_t* 
   }
   cudaStream_t s = (cudaStream_t)stream;
   if (tc_supported(dtype, cin, cout))
-    return tc_conv_gather(dtype, X, W, nbr, row_order, Y, n_out, n_in, K, cin, cout, /*w_transposed=*/false, s);
+    return tc_conv_gather(dtype, X, W, nbr, MapPlan{row_order, tmap, tmask}, Y, n_out, n_in, K, cin, cout, /*w_transposed=*/false, s);
   StoredMap map{nbr, K};
   return by_dtype(dtype, [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
@@ -165,11 +166,11 @@ int st_conv_fwd_ordered(int dtype, const void* X, const void* W, const int32_t* 
 
 int st_conv_fwd(int dtype, const void* X, const void* W, const int32_t* nbr, void* Y, int64_t n_in, int64_t n_out,
                 int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
-  return st_conv_fwd_ordered(dtype, X, W, nbr, nullptr, Y, n_in, n_out, K, cin, cout, workspace, workspace_bytes, stream);
+  return st_conv_fwd_planned(dtype, X, W, nbr, nullptr, nullptr, nullptr, Y, n_in, n_out, K, cin, cout, workspace, workspace_bytes, stream);
 }
 
-int st_conv_dgrad_ordered(int dtype, const void* dY, const void* W, const int32_t* inv, const int32_t* row_order,
-                          void* dX, int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
+int st_conv_dgrad_planned(int dtype, const void* dY, const void* W, const int32_t* inv, const int32_t* row_order,
+                          const int32_t* tmap, const uint32_t* tmask, void* dX, int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
                           int64_t workspace_bytes, void* stream) {
   (void)workspace;
   (void)workspace_bytes;
@@ -182,7 +183,7 @@ int st_conv_dgrad_ordered(int dtype, const void* dY, const void* W, const int32_
   }
   cudaStream_t s = (cudaStream_t)stream;
   if (tc_supported(dtype, cout, cin))
-    return tc_conv_gather(dtype, dY, W, inv, row_order, dX, n_in, n_out, K, cout, cin, /*w_transposed=*/true, s);
+    return tc_conv_gather(dtype, dY, W, inv, MapPlan{row_order, tmap, tmask}, dX, n_in, n_out, K, cout, cin, /*w_transposed=*/true, s);
   StoredMap map{inv, K};
   return by_dtype(dtype, [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
@@ -193,12 +194,12 @@ int st_conv_dgrad_ordered(int dtype, const void* dY, const void* W, const int32_
 
 int st_conv_dgrad(int dtype, const void* dY, const void* W, const int32_t* inv, void* dX, int64_t n_in, int64_t n_out,
                   int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
-  return st_conv_dgrad_ordered(dtype, dY, W, inv, nullptr, dX, n_in, n_out, K, cin, cout, workspace, workspace_bytes,
+  return st_conv_dgrad_planned(dtype, dY, W, inv, nullptr, nullptr, nullptr, dX, n_in, n_out, K, cin, cout, workspace, workspace_bytes,
                                stream);
 }
 
-int st_conv_wgrad_ordered(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
-                          void* dW, int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
+int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
+                          const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
                           int64_t workspace_bytes, void* stream) {
   int rc = check_conv_args("st_conv_wgrad", dtype, n_in, n_out, K, cin, cout);
   if (rc != ST_OK) return rc;
@@ -214,7 +215,7 @@ int st_conv_wgrad_ordered(int dtype, const void* X, const void* dY, const int32_
   cudaStream_t s = (cudaStream_t)stream;
   if (n_out > 0 && tc_wgrad_supported(dtype, n_out, K, cin, cout)) {
     int chunks = 0;
-    rc = tc_conv_wgrad(dtype, X, dY, nbr, row_order, static_cast<float*>(workspace), &chunks, n_out, n_in, K, cin, cout, s);
+    rc = tc_conv_wgrad(dtype, X, dY, nbr, MapPlan{row_order, tmap, tmask}, static_cast<float*>(workspace), &chunks, n_out, n_in, K, cin, cout, s);
     if (rc != ST_OK) return rc;
     return reduce_partials(dtype, static_cast<const float*>(workspace), chunks, (int64_t)K * cin * cout, dW, s);
   }
@@ -228,7 +229,7 @@ int st_conv_wgrad_ordered(int dtype, const void* X, const void* dY, const int32_
 
 int st_conv_wgrad(int dtype, const void* X, const void* dY, const int32_t* nbr, void* dW, int64_t n_in, int64_t n_out,
                   int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
-  return st_conv_wgrad_ordered(dtype, X, dY, nbr, nullptr, dW, n_in, n_out, K, cin, cout, workspace, workspace_bytes,
+  return st_conv_wgrad_planned(dtype, X, dY, nbr, nullptr, nullptr, nullptr, dW, n_in, n_out, K, cin, cout, workspace, workspace_bytes,
                                stream);
 }
 

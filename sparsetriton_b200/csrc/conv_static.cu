@@ -90,7 +90,7 @@ int st_conv_wgrad_static(int dtype, const void* X, const void* dY, const int32_t
   // store their whole (chunk, K, cin, cout) block, zeros included), so nothing has to be cleared.
   if (use_tc) {
     int chunks = 0;
-    rc = tc_conv_wgrad(dtype, X, dY, nbr, nullptr, partial, &chunks, n_out, n_in, K, cin, cout, s);
+    rc = tc_conv_wgrad(dtype, X, dY, nbr, MapPlan{}, partial, &chunks, n_out, n_in, K, cin, cout, s);
     if (rc != ST_OK) return rc;
     return reduce_partials(dtype, partial, chunks, n_w, dW, s);
   }

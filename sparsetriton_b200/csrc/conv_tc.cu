@@ -33,6 +33,10 @@ constexpr int kMmaWarp = kEpilogueWarps;                       // warp 4
 constexpr int kFirstProducerWarp = kMmaWarp + 1;               // warps 5..8
 constexpr int kThreads = (kEpilogueWarps + 1 + kProducerWarps) * 32;
 constexpr int kProducerThreads = kProducerWarps * 32;
+// The gather kernel runs several producer groups of kProducerWarps warps each (see gather2_kernel).
+constexpr int kGatherGroups = 1;
+constexpr int kPlannedLag = 1;          // stages a planned producer group keeps in flight behind the newest
+constexpr int kGatherThreads = (kEpilogueWarps + 1 + kGatherGroups * kProducerWarps) * 32;
 constexpr int kABlockBytes = kTileM * 128;                     // 128 rows x 128 B
 
 
@@ -68,6 +72,7 @@ __device__ __forceinline__ void store_cols(void* out_row, int col0, int out_kind
 
 // Map adapters: what a producer thread keeps per row, and how it finds the source row of offset k.
 struct StoredRows {
+  static constexpr bool kPlanned = false;
   const int32_t* nbr;
   int K;
   struct RowState {};
@@ -75,6 +80,19 @@ struct StoredRows {
   __device__ __forceinline__ int32_t get(const RowState&, int64_t row, int k) const {
     return __ldg(nbr + row * K + k);
   }
+};
+
+// A stored map in tile-plan form: tmap[(tile * K + k) * 128 + r] is the source row of tile row r for
+// offset k, tmask[tile * MW + k / 32] bit (k % 32) says whether the tile has any neighbour at k.
+// The producers then need no staging of map entries at all: a step's 128 indices are one line.
+struct PlannedRows {
+  static constexpr bool kPlanned = true;
+  const int32_t* tmap;
+  const uint32_t* tmask;
+  int K, MW;
+  struct RowState {};
+  __device__ __forceinline__ RowState row_state(int64_t, bool) const { return RowState{}; }
+  __device__ __forceinline__ int32_t get(const RowState&, int64_t, int) const { return -1; }
 };
 
 // Forward rule of the hash-on-the-fly form: source = table[(b, out * stride - off_k)] if inside the shape.
@@ -85,6 +103,7 @@ struct HashRows {
   Table table;
   Int3 shape;
   int stride;
+  static constexpr bool kPlanned = false;
   using RowState = int4;
   __device__ __forceinline__ RowState row_state(int64_t row, bool valid) const {
     return valid ? load_coord<CT>(coords, row) : make_int4(0, 0, 0, 0);
@@ -107,6 +126,7 @@ struct InverseRows {
   Offsets off;
   Table table;             // over the OUTPUT coordinates
   int stride;
+  static constexpr bool kPlanned = false;
   using RowState = int4;
   __device__ __forceinline__ RowState row_state(int64_t row, bool valid) const {
     return valid ? __ldg(reinterpret_cast<const int4*>(q) + row) : make_int4(-1, 0, 0, 0);
@@ -150,12 +170,14 @@ __device__ long long g_prof[160 * 16];
 #define PROF_CLOCK() 0ll
 #endif
 
-// Producers that fetch rows with TMA tile::gather4 and weight slices with tiled TMA copies.  The form
-// passes every small case it was given (up to 40000 rows, two row tiles per super tile), but a launch
-// over 834k output rows / 1.2M source rows with four row tiles per super tile ended in a launch
-// failure whose cause has not been found; until it is, the form is compiled out and the cp.async
-// producers are the only ones that run.
-constexpr bool kTmaProducers = false;
+// Producers that fetch rows with TMA tile::gather4 and weight slices with tiled TMA copies (stored
+// maps in tile-plan form only).  An earlier form dealt the stages of a sub tile to "its" warp; a
+// launch over 834k output rows with four row tiles per super tile then ended in a launch failure.
+// The likely cause: such a warp waited for a slot's release by mbarrier parity without having taken
+// part in the slot's previous laps, so a warp with few stages could be two laps ahead of the
+// consumer, take an old phase for the release it needed, and re-arm the barrier and overwrite the
+// slot while both were in use.  Ownership now follows the slot index (see the planned producers).
+constexpr bool kTmaProducers = true;
 
 constexpr int kMaxSub = 4;
 constexpr int kMaxWSlots = 4;
@@ -177,6 +199,7 @@ struct Params2 {
   int tmem_cols;
   uint32_t idesc;
   int out_kind;
+  int idx_bytes;           // shared memory for staged map entries (0 with a tile plan)
   int use_tma;             // 1: gathered rows come by TMA tile::gather4, 0: by cp.async
   int dbg;                 // timing experiments only (wrong results): 1 no proxy fence, 2 no MMA, 4 no row copies, 8 no zero-fill copies
 };
@@ -195,7 +218,7 @@ struct __align__(8) Control2 {
 };
 
 template <typename Map, int ESIZE>
-__global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, const Map map,
+__global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params2 p, const Map map,
                                                               const __grid_constant__ CUtensorMap in_desc,
                                                               const __grid_constant__ CUtensorMap w_desc) {
   extern __shared__ unsigned char smem_raw[];
@@ -207,7 +230,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, c
   // map entries of the current offset group: idx_tile[(j * kMaxSub + s) * 128 + row]
   int32_t* idx_tile = reinterpret_cast<int32_t*>(base_ptr + (size_t)p.w_slots * p.w_slot_bytes +
                                                  (size_t)p.a_stages * kABlockBytes);
-  Control2* ctl = reinterpret_cast<Control2*>(reinterpret_cast<unsigned char*>(idx_tile) + kIdxTileBytes);
+  Control2* ctl = reinterpret_cast<Control2*>(reinterpret_cast<unsigned char*>(idx_tile) + p.idx_bytes);
   volatile int* abort_flag = &ctl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool use_tma = kTmaProducers && p.use_tma;
@@ -242,14 +265,20 @@ __global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, c
 
   if (warp >= kFirstProducerWarp) {
     // =============================================================== producers
-    const int t = threadIdx.x - kFirstProducerWarp * 32;
+    // Producer groups: a single warp runs its (mostly dependent) instruction stream at a fraction of
+    // the issue rate, so with one producer warp per scheduler the copies were bound by instruction
+    // latency.  With a stored tile plan the steps are dealt round-robin to kGatherGroups groups of four
+    // warps, each of which copies whole steps on its own; the forms that stage map entries in shared
+    // memory (hash on the fly, plain stored map) run on group 0 alone.
+    const int group = (threadIdx.x - kFirstProducerWarp * 32) / kProducerThreads;
+    const int t = (threadIdx.x - kFirstProducerWarp * 32) % kProducerThreads;
     const int pwarp = t >> 5;
     int a_stage = 0, w_slot = 0;
     uint32_t a_phase = 0, w_phase = 0;
     bool ok = true;
     const int kr = 128 / ESIZE;
     const int w_col_bytes = p.w_cols * ESIZE;
-    StageQueue queue;
+    StageQueue<Map::kPlanned ? kPlannedLag : 3> queue;
     queue.clear();
     // Barrier among the four producer warps with a bounded wait (a plain bar.sync could hang if one warp
     // had given up after an expired wait).
@@ -261,7 +290,7 @@ __global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, c
       group_phase ^= 1u;
     };
     long long t_pref = 0, t_acq_a = 0, t_acq_w = 0, t_total0 = PROF_CLOCK(), t_push = 0, t_copy = 0;
-    long long n_flush = 0;
+    long long n_flush = 0, t_w = 0, t_idx = 0;
     // Wait until the consumer has released a slot.  If it has not yet, first hand over every stage
     // still held back in the queue, so that the consumer can never be waiting for this warp.
     auto acquire = [&](uint32_t bar, uint32_t parity, int where) {
@@ -277,10 +306,10 @@ __global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, c
       return r;
     };
 
-    auto send_w = [&](int k, int kb) {
-      ok = acquire(smem_u32(&ctl->w_empty[w_slot]), w_phase ^ 1u, 21);
+    auto send_w_at = [&](int k, int kb, int slot, uint32_t parity) {
+      ok = acquire(smem_u32(&ctl->w_empty[slot]), parity ^ 1u, 21);
       if (!ok) return;
-      const uint32_t w_base = w_ring + (uint32_t)w_slot * p.w_slot_bytes;
+      const uint32_t w_base = w_ring + (uint32_t)slot * p.w_slot_bytes;
       const char* wk = static_cast<const char*>(p.w) + (size_t)k * p.w_rows * w_col_bytes;
       if (p.dbg & 16) {
       } else if (p.b_mn_major) {
@@ -307,28 +336,56 @@ __global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, c
         }
       }
       cp_async_commit();
-      queue.push(smem_u32(&ctl->w_full[w_slot]), lane);
+      queue.push(smem_u32(&ctl->w_full[slot]), lane);
+    };
+    auto next_w = [&]() {
       if (++w_slot == p.w_slots) {
         w_slot = 0;
         w_phase ^= 1u;
       }
     };
-    // flags: see Control2::a_info
-    auto send_a = [&](int kb, bool has, int32_t src_row, uint32_t flags) {
+    auto next_a = [&]() {
+      if (++a_stage == p.a_stages) {
+        a_stage = 0;
+        a_phase ^= 1u;
+      }
+    };
+    auto send_w = [&](int k, int kb) {
+      send_w_at(k, kb, w_slot, w_phase);
+      if (ok) next_w();
+    };
+    // flags: see Control2::a_info.  `idx_line` holds the 128 source rows of the stage (shared memory;
+    // null: a stage of zeros).  Eight consecutive lanes fetch the eight 16-byte pieces of one row, so a
+    // warp-wide cp.async touches 4 whole 128-byte lines (a lane-per-row split touches 32 lines per
+    // instruction and is bound by L1 wavefronts); thread t serves rows 8*(t/8) .. 8*(t/8)+7.
+    auto send_a = [&](int kb, const int32_t* idx_line, uint32_t flags) {
       ok = acquire(smem_u32(&ctl->a_empty[a_stage]), a_phase ^ 1u, 22);
       if (!ok) return;
       const long long cc = PROF_CLOCK();
       int valid_bytes = 0;
       if (!(flags & 32u)) {
         valid_bytes = min(128, red_bytes - kb * 128);
-        const int chunks = valid_bytes >> 4;
-        const char* src = has ? static_cast<const char*>(p.in) + (size_t)src_row * red_bytes + kb * 128
-                              : static_cast<const char*>(p.w);
-        const uint32_t a_row = a_ring + (uint32_t)a_stage * kABlockBytes + (uint32_t)t * 128u;
+        const int c = t & 7, g = t >> 3;
+        if (c < (valid_bytes >> 4) && !(p.dbg & 4)) {
+          int32_t r[8];
+          if (idx_line) {
+            const int4 lo = *reinterpret_cast<const int4*>(idx_line + g * 8);
+            const int4 hi = *reinterpret_cast<const int4*>(idx_line + g * 8 + 4);
+            r[0] = lo.x; r[1] = lo.y; r[2] = lo.z; r[3] = lo.w;
+            r[4] = hi.x; r[5] = hi.y; r[6] = hi.z; r[7] = hi.w;
+          } else {
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
-          if (c < chunks && !(p.dbg & 4) && (has || !(p.dbg & 8)))
-            cp_async16(a_row + (uint32_t)(swz16(c, t) << 4), src + (has ? c * 16 : 0), has ? 16u : 0u);
+            for (int i = 0; i < 8; ++i) r[i] = -1;
+          }
+          const char* src0 = static_cast<const char*>(p.in) + kb * 128 + c * 16;
+          const uint32_t dst0 = a_ring + (uint32_t)a_stage * kABlockBytes + (uint32_t)(g * 8 * 128);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const bool has = r[i] >= 0;
+            cp_async16(dst0 + (uint32_t)(i * 128 + ((c ^ i) << 4)),
+                       has ? src0 + (size_t)r[i] * red_bytes : static_cast<const char*>(p.w), has ? 16u : 0u);
+          }
+        }
       }
       if (t == 0) ctl->a_info[a_stage] = flags | ((uint32_t)(valid_bytes >> 5) << 8);
       cp_async_commit();
@@ -342,166 +399,305 @@ __global__ void __launch_bounds__(kThreads, 1) gather2_kernel(const Params2 p, c
       }
     };
 
-    // TMA form of send_w: one lane of producer warp 0 fetches the slice with tiled copies (the
-    // descriptor's box is one 128-byte column block of the slice); the other warps only keep count.
-    auto send_w_tma = [&](int k, int kb) {
-      if (pwarp == 0) {
-        ok = acquire(smem_u32(&ctl->w_empty[w_slot]), w_phase ^ 1u, 29);
-        if (ok && lane == 0) {
-          const uint32_t bar = smem_u32(&ctl->w_full[w_slot]);
-          const uint32_t w_base = w_ring + (uint32_t)w_slot * p.w_slot_bytes;
-          if (p.b_mn_major) {
-            const int n_cb = (w_col_bytes + 127) >> 7;
-            mbar_arrive_expect_tx(bar, (uint32_t)(n_cb * kr * 128));
-            for (int cb = 0; cb < n_cb; ++cb)
-              tma_load_2d(w_base + (uint32_t)(cb * kr * 128), &w_desc, bar, cb * kr, k * p.w_rows + kb * kr);
-          } else {
-            mbar_arrive_expect_tx(bar, (uint32_t)(p.w_rows * 128));
-            tma_load_2d(w_base, &w_desc, bar, kb * kr, k * p.w_rows);
+    if constexpr (Map::kPlanned) {
+      // ----- stored map in tile-plan form: no staging, no barrier among the producer warps -----
+      const int64_t n_tiles = (p.n_rows + kTileM - 1) / kTileM;
+      const int piece = t & 7, line8 = (t >> 3) * 8;
+      // A ring slot always belongs to the same group (slot index modulo the groups; the row ring has a
+      // multiple of kGatherGroups slots), so the group that waits for a slot to be released has itself
+      // filled it on every earlier lap.  This matters: an mbarrier wait names a phase only by its
+      // parity, and a group that did not take part in a slot's previous lap could be two laps ahead
+      // of the consumer and mistake an old phase for the one it needs.
+      struct Step {
+        const int32_t* line;     // row step: its 128 source rows (null: zeros / no data)
+        int k, kb;
+        uint32_t flags;          // row step: see Control2::a_info
+        int slot;
+        uint32_t parity;
+        bool is_w, valid;
+      };
+      Step cur{nullptr, 0, 0, 0u, 0, 0u, false, false};
+      int4 cur_lo = make_int4(-1, -1, -1, -1), cur_hi = cur_lo;
+      auto run = [&](const Step& d, const int4& lo, const int4& hi) {
+        if (d.is_w) {
+          const long long cw = PROF_CLOCK();
+          send_w_at(d.k, d.kb, d.slot, d.parity);
+          t_w += PROF_CLOCK() - cw;
+          return;
+        }
+        ok = acquire(smem_u32(&ctl->a_empty[d.slot]), d.parity ^ 1u, 22);
+        if (!ok) return;
+        const long long cc = PROF_CLOCK();
+        int valid_bytes = 0;
+        if (!(d.flags & 32u)) {
+          valid_bytes = min(128, red_bytes - d.kb * 128);
+          if (piece < (valid_bytes >> 4) && !(p.dbg & 4)) {
+            const int32_t r[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            const char* src0 = static_cast<const char*>(p.in) + d.kb * 128 + piece * 16;
+            const uint32_t dst0 = a_ring + (uint32_t)d.slot * kABlockBytes + (uint32_t)(line8 * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const bool has = (uint32_t)r[i] < (uint32_t)p.n_src;
+              cp_async16(dst0 + (uint32_t)(i * 128 + ((piece ^ i) << 4)),
+                         has ? src0 + (size_t)r[i] * red_bytes : static_cast<const char*>(p.w), has ? 16u : 0u);
+            }
           }
+        }
+        if (t == 0) ctl->a_info[d.slot] = d.flags | ((uint32_t)(valid_bytes >> 5) << 8);
+        cp_async_commit();
+        const long long cq = PROF_CLOCK();
+        t_copy += cq - cc;
+        queue.push(smem_u32(&ctl->a_full[d.slot]), lane);
+        t_push += PROF_CLOCK() - cq;
+      };
+      // Deal one step.  Every group keeps count of the ring slots; the owner of the step's slot loads
+      // the step's indices now and issues the step it had pending (one step of distance hides the load).
+      auto deal = [&](const Step& d) {
+        if (d.slot % kGatherGroups != group) return;
+        int4 lo = make_int4(-1, -1, -1, -1), hi = lo;
+        if (d.line) {
+          lo = __ldg(reinterpret_cast<const int4*>(d.line + line8));
+          hi = __ldg(reinterpret_cast<const int4*>(d.line + line8 + 4));
+        }
+        if (cur.valid && ok) run(cur, cur_lo, cur_hi);
+        cur = d;
+        cur_lo = lo;
+        cur_hi = hi;
+      };
+      auto cp_emit = [&](const int32_t* line, int k, int kb, uint32_t flags, bool w_first) {
+        if (w_first) {
+          deal(Step{nullptr, k, kb, 0u, w_slot, w_phase, true, true});
+          next_w();
+        }
+        deal(Step{line, k, kb, flags, a_stage, a_phase, false, true});
+        next_a();
+      };
+
+      // ----- the same steps issued as TMA copies (group 0's four warps) -----
+      // A row step is 32 tile::gather4 copies, one per lane (rows 4l .. 4l+3 of the step; "-1" and rows
+      // past the end of the source are out of bounds and arrive as zeros), a W slice one or two tiled
+      // copies by one lane; both complete on the slot's mbarrier by byte count, so there is no
+      // hand-over lag and no proxy fence.  Warp w issues the row steps whose ring slot is w modulo 4
+      // (the ring has a multiple of 4 slots: same ownership rule as above), warp 0 all W slices;
+      // every warp issues its own items in sequence order.
+      struct RowStep {
+        int kb;
+        uint32_t flags;
+        int slot;
+        uint32_t parity;
+        bool valid;
+      };
+      RowStep pend{0, 0u, 0, 0u, false};
+      int4 pend_idx = make_int4(-1, -1, -1, -1);
+      auto tma_run = [&](const RowStep& d, const int4& idx) {
+        ok = mbar_wait_warp(smem_u32(&ctl->a_empty[d.slot]), d.parity ^ 1u, abort_flag, 27, lane);
+        if (!ok) return;
+        const uint32_t bar = smem_u32(&ctl->a_full[d.slot]);
+        const bool marker = (d.flags & 32u) != 0;
+        const bool copy = !marker && !(p.dbg & 4);
+        if (lane == 0) {
+          const int valid_bytes = marker ? 0 : min(128, red_bytes - d.kb * 128);
+          ctl->a_info[d.slot] = d.flags | ((uint32_t)(valid_bytes >> 5) << 8);
+          if (copy) mbar_arrive_expect_tx(bar, (uint32_t)kABlockBytes); else mbar_arrive(bar);
         }
         __syncwarp();
-      }
-      if (++w_slot == p.w_slots) {
-        w_slot = 0;
-        w_phase ^= 1u;
-      }
-    };
-
-    // TMA form of send_a, executed by ONE warp per stage (the warp that owns the sub tile): lane l
-    // fetches rows 4l..4l+3 of the stage with one tile::gather4; "no neighbour" (-1) and indices past
-    // the end of the source are out-of-bounds rows, which the copy engine fills with zeros.  The
-    // stage's mbarrier counts one arrival (lane 0, together with the expected byte count).
-    auto send_a_tma = [&](int kb, const int32_t* idx4, uint32_t flags, bool mine_to_send) {
-      if (mine_to_send) {
-        ok = acquire(smem_u32(&ctl->a_empty[a_stage]), a_phase ^ 1u, 27);
-        if (ok) {
-          const uint32_t bar = smem_u32(&ctl->a_full[a_stage]);
-          const bool marker = (flags & 32u) != 0;
-          const int valid_bytes = marker ? 0 : min(128, red_bytes - kb * 128);
-          if (lane == 0) {
-            ctl->a_info[a_stage] = flags | ((uint32_t)(valid_bytes >> 5) << 8);
-            if (marker) mbar_arrive(bar); else mbar_arrive_expect_tx(bar, (uint32_t)kABlockBytes);
-          }
-          __syncwarp();
-          if (!marker) {
-            const int4 r = *reinterpret_cast<const int4*>(idx4 + 4 * lane);
-            tma_gather4(a_ring + (uint32_t)a_stage * kABlockBytes + (uint32_t)lane * 512u, &in_desc, bar,
-                        kb * (128 / ESIZE), r.x, r.y, r.z, r.w);
+        if (copy)
+          tma_gather4(a_ring + (uint32_t)d.slot * kABlockBytes + (uint32_t)lane * 512u, &in_desc, bar,
+                      d.kb * (128 / ESIZE), idx.x, idx.y, idx.z, idx.w);
+      };
+      auto tma_emit = [&](const int32_t* line, int k, int kb, uint32_t flags, bool w_first) {
+        if (w_first) {
+          const int slot = w_slot;
+          const uint32_t parity = w_phase;
+          next_w();
+          if (pwarp == 0) {
+            if (pend.valid && ok) tma_run(pend, pend_idx);
+            pend.valid = false;
+            if (ok) ok = mbar_wait_warp(smem_u32(&ctl->w_empty[slot]), parity ^ 1u, abort_flag, 29, lane);
+            if (ok && lane == 0) {
+              const uint32_t bar = smem_u32(&ctl->w_full[slot]);
+              const uint32_t w_base = w_ring + (uint32_t)slot * p.w_slot_bytes;
+              if (p.dbg & 16) {
+                mbar_arrive(bar);
+              } else if (p.b_mn_major) {
+                const int n_cb = (w_col_bytes + 127) >> 7;
+                mbar_arrive_expect_tx(bar, (uint32_t)(n_cb * kr * 128));
+                for (int cb = 0; cb < n_cb; ++cb)
+                  tma_load_2d(w_base + (uint32_t)(cb * kr * 128), &w_desc, bar, cb * kr, k * p.w_rows + kb * kr);
+              } else {
+                mbar_arrive_expect_tx(bar, (uint32_t)(p.w_rows * 128));
+                tma_load_2d(w_base, &w_desc, bar, kb * kr, k * p.w_rows);
+              }
+            }
+            __syncwarp();
           }
         }
-      }
-      if (++a_stage == p.a_stages) {
-        a_stage = 0;
-        a_phase ^= 1u;
-      }
-    };
-
-    for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
-      const int64_t row0 = st_i * p.sub * kTileM + t;          // this thread's position in sub tile 0
-      typename Map::RowState rs[kMaxSub];
-      int64_t arow[kMaxSub];                                    // the rows these positions stand for
-      bool row_ok[kMaxSub];
+        const int slot = a_stage;
+        const uint32_t parity = a_phase;
+        next_a();
+        if (slot % kProducerWarps != pwarp) return;
+        int4 idx = make_int4(-1, -1, -1, -1);
+        if (line) idx = __ldg(reinterpret_cast<const int4*>(line) + lane);
+        if (pend.valid && ok) tma_run(pend, pend_idx);
+        pend = RowStep{kb, flags, slot, parity, true};
+        pend_idx = idx;
+      };
+      auto emit = [&](const int32_t* line, int k, int kb, uint32_t flags, bool w_first) {
+        if (use_tma) tma_emit(line, k, kb, flags, w_first); else cp_emit(line, k, kb, flags, w_first);
+      };
+      auto load_masks = [&](int64_t tile0, int word, uint32_t* m) {
 #pragma unroll
-      for (int s = 0; s < kMaxSub; ++s) {
-        const int64_t pos = row0 + (int64_t)s * kTileM;
-        row_ok[s] = s < p.sub && pos < p.n_rows;
-        arow[s] = (row_ok[s] && p.order) ? (int64_t)__ldg(p.order + pos) : pos;
-        rs[s] = map.row_state(arow[s], row_ok[s]);
-      }
-      uint32_t touched = 0;                                     // sub tiles whose accumulator has been started
-      for (int k0 = 0; k0 < p.K && ok; k0 += kGroup) {
+        for (int s = 0; s < kMaxSub; ++s)
+          m[s] = (s < p.sub && tile0 + s < n_tiles) ? __ldg(map.tmask + (tile0 + s) * map.MW + word) : 0u;
+      };
+      uint32_t next_m[kMaxSub];
+      load_masks((int64_t)blockIdx.x * p.sub, 0, next_m);
+      const bool takes_part = !use_tma || group == 0;
+      for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok && takes_part; st_i += gridDim.x) {
         const long long cpf = PROF_CLOCK();
-        const int kn = min(kGroup, p.K - k0);
-        uint32_t mine[kMaxSub];
-        int32_t got[kMaxSub][kGroup];
+        const int64_t tile0 = st_i * p.sub;
+        uint32_t m0[kMaxSub];
 #pragma unroll
-        for (int s = 0; s < kMaxSub; ++s) {
-#pragma unroll
-          for (int j = 0; j < kGroup; ++j)
-            got[s][j] = (row_ok[s] && j < kn && !(p.dbg & 32)) ? map.get(rs[s], arow[s], k0 + j) : -1;
-        }
-        // every stage of the previous group has been issued by every producer thread: the tile can be rewritten
-        producer_sync();
-#pragma unroll
-        for (int s = 0; s < kMaxSub; ++s) {
-          mine[s] = 0;
-#pragma unroll
-          for (int j = 0; j < kGroup; ++j) {
-            int32_t i = got[s][j];
-            if (i >= p.n_src) i = -1;
-            idx_tile[(j * kMaxSub + s) * kTileM + t] = i;
-            if (i >= 0) mine[s] |= 1u << j;
-          }
-        }
-#pragma unroll
-        for (int s = 0; s < kMaxSub; ++s) {
-          const uint32_t wm = __reduce_or_sync(0xFFFFFFFFu, mine[s]);
-          if (lane == 0) ctl->group_mask[pwarp][s] = wm;
-        }
-        producer_sync();
-        uint32_t m[kMaxSub], m_any = 0;
-#pragma unroll
-        for (int s = 0; s < kMaxSub; ++s) {
-          m[s] = ctl->group_mask[0][s] | ctl->group_mask[1][s] | ctl->group_mask[2][s] | ctl->group_mask[3][s];
-          m_any |= m[s];
-        }
+        for (int s = 0; s < kMaxSub; ++s) m0[s] = next_m[s];
+        if (st_i + gridDim.x < p.n_super) load_masks((st_i + gridDim.x) * p.sub, 0, next_m);
         t_pref += PROF_CLOCK() - cpf;
-        while (m_any && ok) {
-          const int j = __ffs(m_any) - 1;
-          m_any &= m_any - 1;
-          uint32_t users = 0;                                   // sub tiles that need this offset
+        uint32_t touched = 0;
+        for (int word = 0; word < map.MW && ok; ++word) {
+          uint32_t m[kMaxSub], m_any = 0;
+          if (word == 0) {
 #pragma unroll
-          for (int s = 0; s < kMaxSub; ++s) users |= ((m[s] >> j) & 1u) << s;
-          const int last_user = 31 - __clz(users);
-          for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
-            if (use_tma) send_w_tma(k0 + j, kb); else send_w(k0 + j, kb);
-            bool first_of_w = true;
-#pragma unroll
-            for (int s = 0; s < kMaxSub; ++s) {
-              if (!((users >> s) & 1u) || !ok) continue;
-              const bool has = (mine[s] >> j) & 1u;
-              uint32_t flags = (uint32_t)s;
-              if (kb == 0 && !((touched >> s) & 1u)) flags |= 4u;
-              if (first_of_w) flags |= 8u;
-              if (s == last_user) flags |= 16u;
-              if (use_tma)
-                send_a_tma(kb, idx_tile + (j * kMaxSub + s) * kTileM, flags, pwarp == s);
-              else
-                send_a(kb, has, idx_tile[(j * kMaxSub + s) * kTileM + t], flags);
-              first_of_w = false;
-            }
+            for (int s = 0; s < kMaxSub; ++s) m[s] = m0[s];
+          } else {
+            load_masks(tile0, word, m);
           }
-          touched |= users;
-        }
-      }
-      // sub tiles that exist but never got a neighbour still have to write zeros
-      for (int s = 0; s < p.sub && ok; ++s) {
-        const bool exists = (st_i * p.sub + s) * (int64_t)kTileM < p.n_rows;
-        if (exists && !((touched >> s) & 1u)) {
-          if (use_tma) send_w_tma(0, 0); else send_w(0, 0);
-          if (ok) {
-            if (use_tma) {
-              // an all "-1" index line: every row of the stage is zero-filled
-              producer_sync();
-              idx_tile[t] = -1;
-              producer_sync();
-              send_a_tma(0, idx_tile, (uint32_t)s | 4u | 8u | 16u, pwarp == 0);
-            } else {
-              send_a(0, false, 0, (uint32_t)s | 4u | 8u | 16u);
+#pragma unroll
+          for (int s = 0; s < kMaxSub; ++s) m_any |= m[s];
+          while (m_any && ok) {
+            const int j = __ffs(m_any) - 1;
+            m_any &= m_any - 1;
+            const int k = word * 32 + j;
+            uint32_t users = 0;
+#pragma unroll
+            for (int s = 0; s < kMaxSub; ++s) users |= ((m[s] >> j) & 1u) << s;
+            const int last_user = 31 - __clz(users);
+            for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
+              bool first_of_w = true;
+#pragma unroll
+              for (int s = 0; s < kMaxSub; ++s) {
+                if (!((users >> s) & 1u) || !ok) continue;
+                uint32_t flags = (uint32_t)s;
+                if (kb == 0 && !((touched >> s) & 1u)) flags |= 4u;
+                if (first_of_w) flags |= 8u;
+                if (s == last_user) flags |= 16u;
+                emit(map.tmap + ((tile0 + s) * map.K + k) * (int64_t)kTileM, k, kb, flags, first_of_w);
+                first_of_w = false;
+              }
             }
+            touched |= users;
           }
         }
+        // sub tiles that exist but never got a neighbour still have to write zeros
+        for (int s = 0; s < p.sub && ok; ++s) {
+          if (tile0 + s < n_tiles && !((touched >> s) & 1u))
+            emit(nullptr, 0, 0, (uint32_t)s | 4u | 8u | 16u, true);
+        }
+        if (ok) emit(nullptr, 0, 0, 32u, false);                       // end of super tile
       }
-      if (ok) {                                                   // end of super tile
-        if (use_tma) send_a_tma(0, idx_tile, 32u, pwarp == 0); else send_a(0, false, 0, 32u);
+      if (cur.valid && ok) run(cur, cur_lo, cur_hi);
+      if (pend.valid && ok) tma_run(pend, pend_idx);
+    } else if (group == 0) {
+      for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
+        const int64_t row0 = st_i * p.sub * kTileM + t;          // this thread's position in sub tile 0
+        typename Map::RowState rs[kMaxSub];
+        int64_t arow[kMaxSub];                                    // the rows these positions stand for
+        bool row_ok[kMaxSub];
+  #pragma unroll
+        for (int s = 0; s < kMaxSub; ++s) {
+          const int64_t pos = row0 + (int64_t)s * kTileM;
+          row_ok[s] = s < p.sub && pos < p.n_rows;
+          arow[s] = (row_ok[s] && p.order) ? (int64_t)__ldg(p.order + pos) : pos;
+          rs[s] = map.row_state(arow[s], row_ok[s]);
+        }
+        uint32_t touched = 0;                                     // sub tiles whose accumulator has been started
+        for (int k0 = 0; k0 < p.K && ok; k0 += kGroup) {
+          const long long cpf = PROF_CLOCK();
+          const int kn = min(kGroup, p.K - k0);
+          uint32_t mine[kMaxSub];
+          int32_t got[kMaxSub][kGroup];
+  #pragma unroll
+          for (int s = 0; s < kMaxSub; ++s) {
+  #pragma unroll
+            for (int j = 0; j < kGroup; ++j)
+              got[s][j] = (row_ok[s] && j < kn && !(p.dbg & 32)) ? map.get(rs[s], arow[s], k0 + j) : -1;
+          }
+          // every stage of the previous group has been issued by every producer thread: the tile can be rewritten
+          producer_sync();
+  #pragma unroll
+          for (int s = 0; s < kMaxSub; ++s) {
+            mine[s] = 0;
+  #pragma unroll
+            for (int j = 0; j < kGroup; ++j) {
+              int32_t i = got[s][j];
+              if (i >= p.n_src) i = -1;
+              idx_tile[(j * kMaxSub + s) * kTileM + t] = i;
+              if (i >= 0) mine[s] |= 1u << j;
+            }
+          }
+  #pragma unroll
+          for (int s = 0; s < kMaxSub; ++s) {
+            const uint32_t wm = __reduce_or_sync(0xFFFFFFFFu, mine[s]);
+            if (lane == 0) ctl->group_mask[pwarp][s] = wm;
+          }
+          producer_sync();
+          uint32_t m[kMaxSub], m_any = 0;
+  #pragma unroll
+          for (int s = 0; s < kMaxSub; ++s) {
+            m[s] = ctl->group_mask[0][s] | ctl->group_mask[1][s] | ctl->group_mask[2][s] | ctl->group_mask[3][s];
+            m_any |= m[s];
+          }
+          t_pref += PROF_CLOCK() - cpf;
+          while (m_any && ok) {
+            const int j = __ffs(m_any) - 1;
+            m_any &= m_any - 1;
+            uint32_t users = 0;                                   // sub tiles that need this offset
+  #pragma unroll
+            for (int s = 0; s < kMaxSub; ++s) users |= ((m[s] >> j) & 1u) << s;
+            const int last_user = 31 - __clz(users);
+            for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
+              send_w(k0 + j, kb);
+              bool first_of_w = true;
+  #pragma unroll
+              for (int s = 0; s < kMaxSub; ++s) {
+                if (!((users >> s) & 1u) || !ok) continue;
+                uint32_t flags = (uint32_t)s;
+                if (kb == 0 && !((touched >> s) & 1u)) flags |= 4u;
+                if (first_of_w) flags |= 8u;
+                if (s == last_user) flags |= 16u;
+                send_a(kb, idx_tile + (j * kMaxSub + s) * kTileM, flags);
+                first_of_w = false;
+              }
+            }
+            touched |= users;
+          }
+        }
+        // sub tiles that exist but never got a neighbour still have to write zeros
+        for (int s = 0; s < p.sub && ok; ++s) {
+          const bool exists = (st_i * p.sub + s) * (int64_t)kTileM < p.n_rows;
+          if (exists && !((touched >> s) & 1u)) {
+            send_w(0, 0);
+            if (ok) send_a(0, nullptr, (uint32_t)s | 4u | 8u | 16u);
+          }
+        }
+        if (ok) {                                                   // end of super tile
+          send_a(0, nullptr, 32u);
+        }
+        queue.flush(lane);                                          // let the epilogue of this super tile start
       }
-      queue.flush(lane);                                          // let the epilogue of this super tile start
     }
     queue.flush(lane);
-    if ((p.dbg & 256) && t == 0) {
+    if ((p.dbg & 256) && t == 0 && group == 0) {
       long long* o = g_prof + (size_t)blockIdx.x * 16;
-      o[0] = PROF_CLOCK() - t_total0; o[1] = t_pref; o[2] = t_acq_a; o[3] = t_acq_w; o[4] = n_flush; o[5] = t_push; o[6] = t_copy;
+      o[0] = PROF_CLOCK() - t_total0; o[1] = t_pref; o[2] = t_acq_a; o[3] = t_acq_w; o[4] = n_flush; o[5] = t_push; o[6] = t_copy; o[7] = t_w; o[15] = t_idx;
     }
   } else if (warp == kMmaWarp) {
     // =============================================================== MMA issuer
@@ -737,6 +933,8 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p,
     const int a_bytes = co_cnt * p.esize, b_bytes = ci_cnt * p.esize;      // bytes of this CTA's channel blocks
 
     // Copy `bytes` of one row into the 128-byte-line blocks of a slot (line t of every block).
+    // (Letting eight lanes share a row, so that a warp-wide cp.async touches whole lines, was measured
+    // slower here: the producers are bound by instruction issue and the row exchange costs shuffles.)
     auto copy_row = [&](uint32_t slot_base, const char* src, int bytes, bool valid) {
       const int n_chunks = bytes >> 4;
       for (int c = 0; c < n_chunks; ++c) {
@@ -763,28 +961,21 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p,
       }
     };
 
-    for (int64_t tile = tile_begin; tile < tile_end && ok; ++tile) {
-      const int64_t pos = tile * kTileM + t;
-      const bool row_ok = pos < p.n_rows;
-      const int64_t row = (row_ok && p.order) ? (int64_t)__ldg(p.order + pos) : pos;
-      typename Map::RowState rs = map.row_state(row, row_ok);
-      // neighbours of this row for the offsets of the group (independent loads, then a bit mask)
-      int32_t idx[32];
-      uint32_t mine = 0;
+    if constexpr (Map::kPlanned) {
+      // stored map in tile-plan form: the tile's mask says which offsets to visit, a step's source rows
+      // are one coalesced line; no barrier among the producer warps
+      const int word = k_first >> 5, shift = k_first & 31;
+      const uint32_t group_bits = g_count >= 32 ? 0xFFFFFFFFu : ((1u << g_count) - 1u);
+      for (int64_t tile = tile_begin; tile < tile_end && ok; ++tile) {
+        uint32_t m = (__ldg(map.tmask + tile * map.MW + word) >> shift) & group_bits;
+        if (!m) continue;
+        const int64_t pos = tile * kTileM + t;
+        const bool row_ok = pos < p.n_rows;
+        const int64_t row = (row_ok && p.order) ? (int64_t)__ldg(p.order + pos) : pos;
+        int32_t idx[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        int32_t i = (j < g_count && row_ok) ? map.get(rs, row, k_first + j) : -1;
-        if (i >= p.n_src) i = -1;
-        idx[j] = i;
-        if (i >= 0) mine |= 1u << j;
-      }
-      const uint32_t warp_mask = __reduce_or_sync(0xFFFFFFFFu, mine);
-      producer_bar_sync<kProducerThreads>();
-      if (lane == 0) ctl->group_mask[pwarp] = warp_mask;
-      producer_bar_sync<kProducerThreads>();
-      uint32_t m = ctl->group_mask[0] | ctl->group_mask[1] | ctl->group_mask[2] | ctl->group_mask[3];
-      if (m) {
-        // dY tile: once per tile, shared by all offsets of the group
+        for (int j = 0; j < 32; ++j)
+          idx[j] = ((m >> j) & 1u) ? __ldg(map.tmap + ((tile * map.K + k_first + j) * (int64_t)kTileM + t)) : -1;
         ok = mbar_wait(smem_u32(&ctl->a_empty[a_slot]), a_phase ^ 1u, abort_flag, 10);
         if (!ok) break;
         copy_row(a_ring + (uint32_t)a_slot * p.a_slot_bytes,
@@ -795,12 +986,52 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p,
           a_slot = 0;
           a_phase ^= 1u;
         }
-        while (m && ok) {
-          const int j = __ffs(m) - 1;
-          m &= m - 1;
-          send_b(j, false, (mine >> j) & 1u, idx[j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (((m >> j) & 1u) && ok) send_b(j, false, (uint32_t)idx[j] < (uint32_t)p.n_src, idx[j]);
         }
-        if (ok) send_b(0, true, false, 0);                   // end of tile: lets the MMA warp free the dY slot
+        if (ok) send_b(0, true, false, 0);                     // end of tile: lets the MMA warp free the dY slot
+      }
+    } else {
+      for (int64_t tile = tile_begin; tile < tile_end && ok; ++tile) {
+        const int64_t pos = tile * kTileM + t;
+        const bool row_ok = pos < p.n_rows;
+        const int64_t row = (row_ok && p.order) ? (int64_t)__ldg(p.order + pos) : pos;
+        typename Map::RowState rs = map.row_state(row, row_ok);
+        // neighbours of this row for the offsets of the group (independent loads, then a bit mask)
+        int32_t idx[32];
+        uint32_t mine = 0;
+  #pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          int32_t i = (j < g_count && row_ok) ? map.get(rs, row, k_first + j) : -1;
+          if (i >= p.n_src) i = -1;
+          idx[j] = i;
+          if (i >= 0) mine |= 1u << j;
+        }
+        const uint32_t warp_mask = __reduce_or_sync(0xFFFFFFFFu, mine);
+        producer_bar_sync<kProducerThreads>();
+        if (lane == 0) ctl->group_mask[pwarp] = warp_mask;
+        producer_bar_sync<kProducerThreads>();
+        uint32_t m = ctl->group_mask[0] | ctl->group_mask[1] | ctl->group_mask[2] | ctl->group_mask[3];
+        if (m) {
+          // dY tile: once per tile, shared by all offsets of the group
+          ok = mbar_wait(smem_u32(&ctl->a_empty[a_slot]), a_phase ^ 1u, abort_flag, 10);
+          if (!ok) break;
+          copy_row(a_ring + (uint32_t)a_slot * p.a_slot_bytes,
+                   static_cast<const char*>(p.dy) + (size_t)(row_ok ? row : 0) * dy_row_bytes + (size_t)co0 * p.esize,
+                   a_bytes, row_ok);
+          cp_async_arrive_noinc(smem_u32(&ctl->a_full[a_slot]));
+          if (++a_slot == 2) {
+            a_slot = 0;
+            a_phase ^= 1u;
+          }
+          while (m && ok) {
+            const int j = __ffs(m) - 1;
+            m &= m - 1;
+            send_b(j, false, (mine >> j) & 1u, idx[j]);
+          }
+          if (ok) send_b(0, true, false, 0);                   // end of tile: lets the MMA warp free the dY slot
+        }
       }
     }
     if (ok) send_b(0xFF, true, false, 0);                     // end of work
@@ -931,7 +1162,7 @@ bool tc_supported(int dtype, int c_red, int c_acc) {
 }
 
 static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* w, void* out, int64_t n_rows,
-                         int64_t n_src, int K, int c_red, int c_acc, bool w_transposed) {
+                         int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, bool planned = false) {
   const int es = dtype == ST_F32 ? 4 : 2;
   p->in = in;
   p->w = w;
@@ -952,6 +1183,11 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   // accumulators: as many row tiles per W copy as TMEM allows (<= 4); a second set only when it is free
   int sub = 512 / c_acc;
   if (sub > tc::kMaxSub) sub = tc::kMaxSub;
+  {
+    // experiment: prefer two accumulator sets (epilogue overlaps the next super tile) over sharing W
+    const char* e = getenv("ST_TC_ACC2");
+    if (e && atoi(e) && sub >= 2 && 2 * sub * c_acc > 512) sub /= 2;
+  }
   p->acc_bufs = (2 * sub * c_acc <= 512) ? 2 : 1;
   const int64_t n_tiles = (n_rows + tc::kTileM - 1) / tc::kTileM;
   // small problems: do not leave SMs idle for the sake of sharing
@@ -962,7 +1198,8 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   while (cols < p->acc_bufs * sub * c_acc) cols <<= 1;
   p->tmem_cols = cols;
   p->w_slots = 3;
-  const int budget = 222 * 1024 - tc::kIdxTileBytes;
+  p->idx_bytes = planned ? 0 : tc::kIdxTileBytes;
+  const int budget = 222 * 1024 - p->idx_bytes;
   int a_stages = (budget - p->w_slots * p->w_slot_bytes) / tc::kABlockBytes;
   if (a_stages > tc::kMaxAStages) a_stages = tc::kMaxAStages;
   if (a_stages < 4) {
@@ -970,7 +1207,9 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
     a_stages = (budget - p->w_slots * p->w_slot_bytes) / tc::kABlockBytes;
     if (a_stages > tc::kMaxAStages) a_stages = tc::kMaxAStages;
   }
-  if (a_stages < 2) return false;
+  if (a_stages < (planned ? tc::kProducerWarps : 2)) return false;
+  // slot ownership by index needs whole rounds: of the four TMA-issuing warps or of the cp.async groups
+  a_stages -= a_stages % (planned ? tc::kProducerWarps : tc::kGatherGroups);
   p->a_stages = a_stages;
   const uint32_t fmt = dtype == ST_F16 ? 0u : (dtype == ST_BF16 ? 1u : 2u);
   p->idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p->b_mn_major << 16) | ((uint32_t)(c_acc >> 3) << 17) |
@@ -1050,12 +1289,12 @@ static int launch_gather(tc::Params2 p, const Map& map, cudaStream_t stream) {
   CUtensorMap in_desc, w_desc;
   memset(&in_desc, 0, sizeof(in_desc));
   memset(&w_desc, 0, sizeof(w_desc));
-  p.use_tma = tc::kTmaProducers && p.n_src > 0 &&
+  p.use_tma = tc::kTmaProducers && Map::kPlanned && !getenv("ST_TC_NO_TMA") && p.n_src > 0 &&
               make_gather_desc(&in_desc, p.in, p.n_src, p.c_red, p.esize, p.out_kind) &&
               make_weight_desc(&w_desc, p.w, (int64_t)p.K * p.w_rows, p.w_cols, p.esize, p.out_kind,
                                p.b_mn_major ? 128 / p.esize : p.w_rows, p.b_mn_major && p.esize == 4) ? 1 : 0;
   const size_t smem = (size_t)p.w_slots * p.w_slot_bytes + (size_t)p.a_stages * tc::kABlockBytes +
-                      tc::kIdxTileBytes + sizeof(tc::Control2) + 1024;
+                      p.idx_bytes + sizeof(tc::Control2) + 1024;
   auto kernel = p.esize == 2 ? tc::gather2_kernel<Map, 2> : tc::gather2_kernel<Map, 4>;
   static bool configured[2] = {false, false};            // one pair per Map instantiation
   if (!configured[p.esize == 4]) {
@@ -1067,20 +1306,22 @@ static int launch_gather(tc::Params2 p, const Map& map, cudaStream_t stream) {
     configured[p.esize == 4] = true;
   }
   int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
-  kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, map, in_desc, w_desc);
+  kernel<<<(unsigned)grid, tc::kGatherThreads, smem, stream>>>(p, map, in_desc, w_desc);
   note_launches(1);
   return check_launch("tc gather");
 }
 
-int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, const int32_t* order, void* out,
+int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, const MapPlan& plan, void* out,
                    int64_t n_rows, int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream) {
   tc::Params2 p;
-  if (!fill_params2(&p, dtype, in, w, out, n_rows, n_src, K, c_red, c_acc, w_transposed)) {
+  const bool planned = plan.tmap && plan.tmask;
+  if (!fill_params2(&p, dtype, in, w, out, n_rows, n_src, K, c_red, c_acc, w_transposed, planned)) {
     set_error("tc_conv_gather: shape does not fit shared memory");
     return ST_ERR_UNSUPPORTED;
   }
   if (n_rows == 0) return ST_OK;
-  p.order = order;
+  p.order = plan.order;
+  if (planned) return launch_gather(p, tc::PlannedRows{plan.tmap, plan.tmask, K, (K + 31) / 32}, stream);
   return launch_gather(p, tc::StoredRows{map, K}, stream);
 }
 
@@ -1220,12 +1461,13 @@ static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void*
   return true;
 }
 
-int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const int32_t* order, float* partial,
+int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const MapPlan& rows, float* partial,
                   int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream) {
   WgradPlan plan;
   if (!prepare_wgrad(&plan, dtype, x, dy, partial, n_rows, n_src, K, cin, cout)) return ST_ERR_UNSUPPORTED;
-  plan.p.order = order;
+  plan.p.order = rows.order;
   *n_chunks_out = plan.n_chunks;
+  if (rows.tmap && rows.tmask) return launch_wgrad(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream);
   return launch_wgrad(plan, tc::StoredRows{map, K}, stream);
 }
 

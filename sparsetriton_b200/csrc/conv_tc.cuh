@@ -17,9 +17,17 @@ void tc_set_enabled(bool on);
 // OUT[r,:] = sum_k IN[map[r,k],:] . B_k over a stored (n_rows, K) map.
 //   w_transposed = false: B_k = W[k]   with W (K, c_red, c_acc)   (forward)
 //   w_transposed = true : B_k = W[k]^T with W (K, c_acc, c_red)   (dgrad over the inverse map)
-// `order` (may be null) is a permutation of the rows: tiles are formed from rows order[0..127],
-// order[128..255], ...; the result does not depend on it.
-int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, const int32_t* order, void* out,
+// `plan` (all members may be null) describes how the rows are walked:
+//   order : a permutation of the rows; tiles are formed from rows order[0..127], order[128..255], ...
+//           (the result does not depend on it)
+//   tmap, tmask : the map in tile-plan form for that order (see row_order.cu); when given, `map`
+//           itself is not read.
+struct MapPlan {
+  const int32_t* order = nullptr;
+  const int32_t* tmap = nullptr;
+  const uint32_t* tmask = nullptr;
+};
+int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, const MapPlan& plan, void* out,
                    int64_t n_rows, int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream);
 
 // Arguments of the hash-on-the-fly forms.
@@ -48,7 +56,7 @@ int tc_conv_wgrad_hashfly(int dtype, const void* x, const void* dy, const HashFl
 // Tensor-core weight gradient: fills fp32 partials (n_chunks, K, cin, cout) that the caller reduces.
 bool tc_wgrad_supported(int dtype, int64_t n_rows, int K, int cin, int cout);
 int64_t tc_wgrad_partial_bytes(int dtype, int64_t n_rows, int K, int cin, int cout);
-int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const int32_t* order, float* partial,
+int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const MapPlan& plan, float* partial,
                   int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream);
 
 // Cycle counters of timing experiments (see Params2::dbg).

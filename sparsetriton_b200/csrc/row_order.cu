@@ -17,7 +17,7 @@ namespace st {
 
 namespace {
 
-constexpr int kSortChunk = 1024;        // elements per warp
+constexpr int kSortChunk = 512;         // elements per warp
 constexpr int kSortWarps = 4;           // warps per block
 constexpr int kDigitBitsMax = 9;
 constexpr int kBucketsMax = 1 << kDigitBitsMax;
@@ -71,17 +71,76 @@ __global__ void __launch_bounds__(kSortWarps * 32) sort_hist_kernel(const uint32
   }
 }
 
-// Stable scatter of one digit pass: `first` is the exclusive scan of hist.
+// One block per digit value d: hist[d * n_chunks + *] <- its exclusive prefix over the chunks,
+// totals[d] <- the number of elements with that digit.
+__global__ void __launch_bounds__(256) sort_bucket_scan_kernel(uint32_t* __restrict__ hist, int64_t n_chunks,
+                                                              uint32_t* __restrict__ totals) {
+  __shared__ uint32_t warp_sum[8];
+  __shared__ uint32_t carry_s;
+  uint32_t* row = hist + (int64_t)blockIdx.x * n_chunks;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < n_chunks; base += 256) {
+    const int64_t i = base + threadIdx.x;
+    const uint32_t v = i < n_chunks ? row[i] : 0u;
+    uint32_t inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t u = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += u;
+    }
+    if (lane == 31) warp_sum[warp] = inc;
+    __syncthreads();
+    uint32_t before = carry_s;
+    for (int w = 0; w < warp; ++w) before += warp_sum[w];
+    if (i < n_chunks) row[i] = before + inc - v;
+    __syncthreads();
+    if (threadIdx.x == 255) carry_s = before + inc;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) totals[blockIdx.x] = carry_s;
+}
+
+// Stable scatter of one digit pass: `prefix` is hist after sort_bucket_scan_kernel; the first output
+// position of digit d is the sum of totals[0..d), which every block works out for itself.
 __global__ void __launch_bounds__(kSortWarps * 32)
     sort_scatter_kernel(const uint32_t* __restrict__ keys, const int32_t* __restrict__ vals, int64_t n, int shift,
-                        int bits, int64_t n_chunks, const uint32_t* __restrict__ first, uint32_t* __restrict__ keys_out,
+                        int bits, int64_t n_chunks, const uint32_t* __restrict__ prefix,
+                        const uint32_t* __restrict__ totals, uint32_t* __restrict__ keys_out,
                         int32_t* __restrict__ vals_out) {
   __shared__ uint32_t next[kSortWarps][kBucketsMax];
+  __shared__ uint32_t base[kBucketsMax];
+  __shared__ uint32_t part[kSortWarps * 32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t chunk = (int64_t)blockIdx.x * kSortWarps + warp;
-  if (chunk >= n_chunks) return;
   const int buckets = 1 << bits;
-  for (int d = lane; d < buckets; d += 32) next[warp][d] = first[(int64_t)d * n_chunks + chunk];
+  {
+    // exclusive scan of totals[0..buckets) by the whole block: each thread owns a run of `per` digits
+    constexpr int T = kSortWarps * 32;
+    const int per = (buckets + T - 1) / T;
+    uint32_t mine[(kBucketsMax + T - 1) / T];
+    uint32_t sum = 0;
+#pragma unroll
+    for (int i = 0; i < (kBucketsMax + T - 1) / T; ++i) {
+      const int d = threadIdx.x * per + i;
+      mine[i] = (i < per && d < buckets) ? totals[d] : 0u;
+      sum += mine[i];
+    }
+    part[threadIdx.x] = sum;
+    __syncthreads();
+    uint32_t before = 0;
+    for (int j = 0; j < (int)threadIdx.x; ++j) before += part[j];
+#pragma unroll
+    for (int i = 0; i < (kBucketsMax + T - 1) / T; ++i) {
+      const int d = threadIdx.x * per + i;
+      if (i < per && d < buckets) base[d] = before;
+      before += mine[i];
+    }
+    __syncthreads();
+  }
+  if (chunk >= n_chunks) return;
+  for (int d = lane; d < buckets; d += 32) next[warp][d] = base[d] + prefix[(int64_t)d * n_chunks + chunk];
   __syncwarp();
   const int64_t begin = chunk * kSortChunk, end = min(n, begin + kSortChunk);
   const uint32_t lower = (1u << lane) - 1u;
@@ -106,10 +165,54 @@ __global__ void __launch_bounds__(kSortWarps * 32)
   }
 }
 
+// Tile plan: the map re-laid so that the 128 source rows of one (tile, offset) step are one
+// contiguous 512-byte line, in the row order the kernels walk, plus a per-tile bit mask of the
+// offsets that have a neighbour anywhere in the tile.
+//   tmap [(tile * K + k) * 128 + r] = nbr[order[tile * 128 + r], k]      (-1 past the last row)
+//   tmask[tile * MW + k / 32] bit (k % 32)                                 MW = ceil(K / 32)
+// One block per tile.  The tile's rows are read as runs of consecutive entries (a warp-wide load
+// touches 2-3 lines, not 32) into shared memory, `kPlanChunk` offsets at a time, and written back
+// transposed.
+constexpr int kPlanChunk = 64;
+
+__global__ void __launch_bounds__(128) plan_tiles_kernel(const int32_t* __restrict__ nbr,
+                                                        const int32_t* __restrict__ order, int64_t n_rows, int K,
+                                                        int MW, int32_t* __restrict__ tmap,
+                                                        uint32_t* __restrict__ tmask) {
+  extern __shared__ int32_t stage[];                      // 128 x (min(K, kPlanChunk) | 1) entries
+  __shared__ int64_t src_row[128];
+  __shared__ uint32_t mask_word[2];                       // the (at most two) mask words of a chunk
+  const int64_t tile = blockIdx.x;
+  const int r = threadIdx.x, warp = r >> 5, lane = r & 31;
+  const int64_t pos = tile * 128 + r;
+  src_row[r] = pos < n_rows ? (order ? (int64_t)__ldg(order + pos) : pos) : -1;
+  for (int k0 = 0; k0 < K; k0 += kPlanChunk) {
+    const int kc = min(kPlanChunk, K - k0);
+    const int pitch = kc | 1;                              // odd: conflict-free column reads
+    if (r < 2) mask_word[r] = 0;
+    __syncthreads();
+    for (int e = r; e < 128 * kc; e += 128) {
+      const int row = e / kc, k = e - row * kc;
+      const int64_t src = src_row[row];
+      stage[row * pitch + k] = src >= 0 ? __ldg(nbr + src * K + k0 + k) : -1;
+    }
+    __syncthreads();
+    for (int k = 0; k < kc; ++k) {
+      const int32_t v = stage[r * pitch + k];
+      tmap[(tile * K + k0 + k) * 128 + r] = v;
+      const uint32_t any = __ballot_sync(0xFFFFFFFFu, v >= 0);
+      if (any && lane == 0) atomicOr(&mask_word[k >> 5], 1u << (k & 31));
+    }
+    __syncthreads();
+    if (r < (kc + 31) / 32) tmask[tile * MW + (k0 >> 5) + r] = mask_word[r];
+    __syncthreads();
+  }
+  (void)warp;
+}
+
 struct OrderScratch {
-  uint32_t *keys_a, *keys_b, *hist;
+  uint32_t *keys_a, *keys_b, *hist, *totals;
   int32_t* vals_b;
-  void* scan_tmp;
   int64_t n_chunks;
 };
 
@@ -127,7 +230,7 @@ int64_t carve(OrderScratch* s, void* ws, int64_t n, int K) {
   s->keys_b = reinterpret_cast<uint32_t*>(take(nn * 4));
   s->vals_b = reinterpret_cast<int32_t*>(take(nn * 4));
   s->hist = reinterpret_cast<uint32_t*>(take(n_chunks * kBucketsMax * 4));
-  s->scan_tmp = take(scan_tmp_bytes(n_chunks * kBucketsMax));
+  s->totals = reinterpret_cast<uint32_t*>(take(kBucketsMax * 4));
   s->n_chunks = n_chunks;
   return off;
 }
@@ -173,24 +276,49 @@ int st_map_row_order(const int32_t* nbr, int64_t n_rows, int K, int32_t* order, 
     note_launches(1);
   }
   const unsigned blocks = (unsigned)((s.n_chunks + kSortWarps - 1) / kSortWarps);
-  const int64_t n_hist = s.n_chunks << bits;
   for (int pass = 0; pass < passes; ++pass) {
     const int shift = pass * bits;
     {
       sort_hist_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, n_rows, shift, bits, s.n_chunks, s.hist);
       note_launches(1);
     }
-    int rc = exclusive_scan_u32(s.hist, s.hist, n_hist, s.scan_tmp, nullptr, st);
-    if (rc != ST_OK) return rc;
+    {
+      sort_bucket_scan_kernel<<<1u << bits, 256, 0, st>>>(s.hist, s.n_chunks, s.totals);
+      note_launches(1);
+    }
     {
       sort_scatter_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, vals_in, n_rows, shift, bits, s.n_chunks, s.hist,
-                                                              keys_out, vals_out);
+                                                              s.totals, keys_out, vals_out);
       note_launches(1);
     }
     uint32_t* tk = keys_in; keys_in = keys_out; keys_out = tk;
     int32_t* tv = vals_in; vals_in = vals_out; vals_out = tv;
   }
   return check_launch("st_map_row_order");
+}
+
+int64_t st_map_plan_workspace_bytes(int64_t n_rows, int K) { return st_map_row_order_workspace_bytes(n_rows, K); }
+
+int st_map_plan(const int32_t* nbr, int64_t n_rows, int K, int sort_rows, int32_t* order, int32_t* tmap,
+                uint32_t* tmask, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (n_rows < 0 || K < 1 || n_rows > 0x7FFFFFFFll ||
+      (n_rows > 0 && (!nbr || !tmap || !tmask || (sort_rows && (!order || !workspace))))) {
+    set_error("st_map_plan: bad arguments");
+    return ST_ERR_ARG;
+  }
+  if (n_rows == 0) return ST_OK;
+  if (sort_rows) {
+    int rc = st_map_row_order(nbr, n_rows, K, order, workspace, workspace_bytes, stream);
+    if (rc != ST_OK) return rc;
+  }
+  const int64_t n_tiles = (n_rows + 127) / 128;
+  {
+    const size_t stage_bytes = (size_t)128 * ((K < kPlanChunk ? K : kPlanChunk) | 1) * 4;
+    plan_tiles_kernel<<<(unsigned)n_tiles, 128, stage_bytes, (cudaStream_t)stream>>>(
+        nbr, sort_rows ? order : nullptr, n_rows, K, (K + 31) / 32, tmap, tmask);
+    note_launches(1);
+  }
+  return check_launch("st_map_plan");
 }
 
 }  // extern "C"

@@ -149,18 +149,22 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* desc, uint
 //
 // Having every producer thread arrive on a stage's mbarrier costs ~130 serialised shared-memory
 // atomics per stage.  Instead each thread closes a stage with cp.async.commit_group, remembers the
-// stage's mbarrier in a 4-deep queue, and once three newer groups have been committed
-// (cp.async.wait_group 3: the oldest one has landed) the warp syncs and one lane arrives for it.
+// stage's mbarrier in a short queue, and once LAG newer groups have been committed
+// (cp.async.wait_group LAG: the oldest one has landed) the warp syncs and one lane arrives for it.
+// A longer lag keeps more copies in flight per thread but holds ring slots back from the consumer.
+template <int LAG>
 struct StageQueue {
-  uint32_t bar[4];          // 0 = empty slot; bar[3] is the oldest
-  __device__ __forceinline__ void clear() { bar[0] = bar[1] = bar[2] = bar[3] = 0; }
+  uint32_t bar[LAG + 1];    // 0 = empty slot; bar[LAG] is the oldest
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int i = 0; i <= LAG; ++i) bar[i] = 0;
+  }
   // Call after commit_group of the stage whose barrier is `b`.
   __device__ __forceinline__ void push(uint32_t b, int lane) {
-    cp_async_wait_group<3>();
-    const uint32_t oldest = bar[3];
-    bar[3] = bar[2];
-    bar[2] = bar[1];
-    bar[1] = bar[0];
+    cp_async_wait_group<LAG>();
+    const uint32_t oldest = bar[LAG];
+#pragma unroll
+    for (int i = LAG; i > 0; --i) bar[i] = bar[i - 1];
     bar[0] = b;
     if (oldest) {
       fence_proxy_async();
@@ -174,10 +178,9 @@ struct StageQueue {
     fence_proxy_async();
     __syncwarp();
     if (lane == 0) {
-      if (bar[3]) mbar_arrive(bar[3]);
-      if (bar[2]) mbar_arrive(bar[2]);
-      if (bar[1]) mbar_arrive(bar[1]);
-      if (bar[0]) mbar_arrive(bar[0]);
+#pragma unroll
+      for (int i = LAG; i >= 0; --i)
+        if (bar[i]) mbar_arrive(bar[i]);
     }
     clear();
   }

@@ -18,7 +18,7 @@ from sparsetriton_b200 import _lib, trace
 
 from ._channels import pad_cols, pad_weight, padded_widths
 
-__all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map", "row_order"]
+__all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map", "map_plan", "MapPlan"]
 
 # below this many rows the sort costs more than the denser tiles save
 _MIN_ROWS_FOR_ORDER = 16384
@@ -39,25 +39,47 @@ def inverse_map(neighbor_indices, n_in):
     return inv
 
 
-def row_order(map_tensor):
-    """Rows of a (forward or inverse) map sorted by which offsets they occupy, or None when the
-    switch is off or the map is small.  Memoised on the map tensor like the inverse."""
+class MapPlan:
+    """Tile plan of a (forward or inverse) neighbour map: row order, re-laid map, tile masks
+    (st_map_plan).  `ptrs()` are the three pointers the *_planned entry points take."""
+    __slots__ = ("order", "tmap", "tmask")
+
+    def __init__(self, order, tmap, tmask):
+        self.order, self.tmap, self.tmask = order, tmap, tmask
+
+    def ptrs(self):
+        return _lib.ptr(self.order), _lib.ptr(self.tmap), _lib.ptr(self.tmask)
+
+
+_NO_PLAN = MapPlan(None, None, None)
+
+
+def map_plan(map_tensor):
+    """The tile plan of a map, memoised on the map tensor like the inverse (layers that share a
+    map share its plan).  Rows are sorted by occupied offsets unless config.set_row_order(False)
+    or the map is small."""
     from sparsetriton_b200.config import get_row_order
     n_rows, K = map_tensor.shape
-    if not get_row_order() or n_rows < _MIN_ROWS_FOR_ORDER:
-        return None
-    cached = getattr(map_tensor, "_st_order", None)
-    if cached is not None:
-        return cached
+    if n_rows == 0:
+        return _NO_PLAN
+    sort_rows = bool(get_row_order()) and n_rows >= _MIN_ROWS_FOR_ORDER
+    cached = getattr(map_tensor, "_st_plan", None)
+    if cached is not None and cached[0] == sort_rows:
+        return cached[1]
     L = _lib.lib()
-    order = torch.empty((n_rows,), dtype=torch.int32, device=map_tensor.device)
-    ws = _lib.workspace(L.st_map_row_order_workspace_bytes(n_rows, K), map_tensor.device)
-    with torch.cuda.device(map_tensor.device), trace.stage("row_order"):
-        rc = L.st_map_row_order(_lib.ptr(map_tensor), n_rows, K, _lib.ptr(order), _lib.ptr(ws), ws.numel(),
-                                _lib.stream_ptr())
-    _lib.check(rc, "st_map_row_order")
-    map_tensor._st_order = order
-    return order
+    dev = map_tensor.device
+    n_tiles = (n_rows + 127) // 128
+    order = torch.empty((n_rows,), dtype=torch.int32, device=dev) if sort_rows else None
+    tmap = torch.empty((n_tiles * K * 128,), dtype=torch.int32, device=dev)
+    tmask = torch.empty((n_tiles * ((K + 31) // 32),), dtype=torch.int32, device=dev)
+    ws = _lib.workspace(L.st_map_plan_workspace_bytes(n_rows, K), dev) if sort_rows else None
+    with torch.cuda.device(dev), trace.stage("map_plan"):
+        rc = L.st_map_plan(_lib.ptr(map_tensor), n_rows, K, 1 if sort_rows else 0, _lib.ptr(order), _lib.ptr(tmap),
+                           _lib.ptr(tmask), _lib.ptr(ws), ws.numel() if ws is not None else 0, _lib.stream_ptr())
+    _lib.check(rc, "st_map_plan")
+    plan = MapPlan(order, tmap, tmask)
+    map_tensor._st_plan = (sort_rows, plan)
+    return plan
 
 
 class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
@@ -79,13 +101,15 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         code = _lib.feat_code(x)
         y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
         ctx.flops = 2.0 * trace.map_pairs(nbr) * c_in * c_out if trace.active() else 0.0
+        # the plan only serves the tensor-core kernels
+        use_plan = ctx.use_plan = bool(_lib.lib().st_conv_uses_tensor_cores(code, c_in, c_out))
         if n_out > 0:
-            order = row_order(nbr)
+            plan = map_plan(nbr) if use_plan else _NO_PLAN
             with torch.cuda.device(x.device), trace.stage("conv_fwd", work=ctx.flops):
-                rc = _lib.lib().st_conv_fwd_ordered(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), _lib.ptr(order),
+                rc = _lib.lib().st_conv_fwd_planned(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
                                                     _lib.ptr(y), n_in, n_out, K, c_in, c_out, None, 0,
                                                     _lib.stream_ptr())
-            _lib.check(rc, "st_conv_fwd_ordered")
+            _lib.check(rc, "st_conv_fwd_planned")
         ctx.save_for_backward(x, w, nbr)
         ctx.w_dtype = weights.dtype
         return y if c_out == ctx.true_widths[1] else y[:, :ctx.true_widths[1]].contiguous()
@@ -107,21 +131,20 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
                 dx = torch.empty_like(x)
                 if n_in > 0:
                     inv = inverse_map(nbr, n_in)
-                    inv_order = row_order(inv)
+                    plan = map_plan(inv) if L.st_conv_uses_tensor_cores(code, c_out, c_in) else _NO_PLAN
                     with trace.stage("conv_dgrad", work=ctx.flops):
-                        rc = L.st_conv_dgrad_ordered(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv),
-                                                     _lib.ptr(inv_order), _lib.ptr(dx), n_in, n_out, K, c_in, c_out,
-                                                     None, 0, stream)
-                    _lib.check(rc, "st_conv_dgrad_ordered")
+                        rc = L.st_conv_dgrad_planned(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv), *plan.ptrs(),
+                                                     _lib.ptr(dx), n_in, n_out, K, c_in, c_out, None, 0, stream)
+                    _lib.check(rc, "st_conv_dgrad_planned")
             if ctx.needs_input_grad[1]:
                 dw = torch.empty_like(w)
                 ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
-                order = row_order(nbr)
+                plan = map_plan(nbr) if ctx.use_plan else _NO_PLAN
                 with trace.stage("conv_wgrad", work=ctx.flops):
-                    rc = L.st_conv_wgrad_ordered(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), _lib.ptr(order),
+                    rc = L.st_conv_wgrad_planned(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), *plan.ptrs(),
                                                  _lib.ptr(dw), n_in, n_out, K, c_in, c_out, _lib.ptr(ws), ws.numel(),
                                                  stream)
-                _lib.check(rc, "st_conv_wgrad_ordered")
+                _lib.check(rc, "st_conv_wgrad_planned")
                 dw = dw.to(ctx.w_dtype)
         if dx is not None and t_in != c_in:
             dx = dx[:, :t_in].contiguous()

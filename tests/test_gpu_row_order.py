@@ -1,8 +1,10 @@
-"""Row order of a neighbour map (st_map_row_order) and the products that walk the rows in it.
+"""Row order and tile plan of a neighbour map (st_map_row_order, st_map_plan) and the products
+that walk the map through them.
 
-The order must be the stable sort of the rows by their occupancy mask; forward and feature
-gradient must give bit-identical results with and without it (a row's own sum never changes), the
-weight gradient the same result within the storage tolerance (its row sum is reordered).
+The order must be the stable sort of the rows by their occupancy mask; the plan must be the map
+re-laid tile by tile in that order with exact tile masks; forward and feature gradient must give
+bit-identical results with and without a plan (a row's own sum never changes), the weight gradient
+the same result within the storage tolerance (its row sum is reordered).
 """
 import numpy as np
 import pytest
@@ -66,17 +68,59 @@ def test_order_is_the_stable_sort_by_mask(cuda_device, n_rows, K, density, patte
     assert np.array_equal(again, order)                                        # run-to-run identical
 
 
+def _plan(nbr, sort_rows):
+    L = _lib.lib()
+    n, K = nbr.shape
+    dev = nbr.device
+    n_tiles, MW = (n + 127) // 128, (K + 31) // 32
+    order = torch.full((n,), -7, dtype=torch.int32, device=dev) if sort_rows else None
+    tmap = torch.full((n_tiles * K * 128,), -9, dtype=torch.int32, device=dev)
+    tmask = torch.full((n_tiles * MW,), -9, dtype=torch.int32, device=dev)
+    ws = _lib.workspace(L.st_map_plan_workspace_bytes(n, K), dev)
+    with torch.cuda.device(dev):
+        _lib.check(L.st_map_plan(_lib.ptr(nbr), n, K, 1 if sort_rows else 0, _lib.ptr(order), _lib.ptr(tmap),
+                                 _lib.ptr(tmask), _lib.ptr(ws), ws.numel(), _lib.stream_ptr()), "st_map_plan")
+    return order, tmap, tmask
+
+
+@pytest.mark.parametrize("sort_rows", [False, True], ids=["natural", "sorted"])
+@pytest.mark.parametrize("n_rows,K,density", [(1, 27, 0.5), (128, 27, 0.3), (129, 8, 0.4), (5000, 27, 0.2),
+                                              (1000, 64, 0.1), (700, 125, 0.05), (300, 343, 0.02)])
+def test_plan_is_the_relaid_map(cuda_device, n_rows, K, density, sort_rows):
+    nbr = _random_map(n_rows, 3000, K, density, 7 + n_rows, cuda_device, patterns=15)
+    order, tmap, tmask = _plan(nbr, sort_rows)
+    m = nbr.cpu().numpy()
+    n_tiles, MW = (n_rows + 127) // 128, (K + 31) // 32
+    if sort_rows:
+        o = order.cpu().numpy().astype(np.int64)
+        assert np.array_equal(o, _order(nbr).cpu().numpy())
+    else:
+        o = np.arange(n_rows)
+    padded = np.full((n_tiles * 128, K), -1, np.int32)
+    padded[:n_rows] = m[o]
+    want = padded.reshape(n_tiles, 128, K).transpose(0, 2, 1)                  # (tile, k, r)
+    assert np.array_equal(tmap.cpu().numpy().reshape(n_tiles, K, 128), want)
+    bits = (want >= 0).any(axis=2)                                             # (tile, k)
+    want_mask = np.zeros((n_tiles, MW), np.uint32)
+    for k in range(K):
+        want_mask[:, k // 32] |= bits[:, k].astype(np.uint32) << np.uint32(k % 32)
+    assert np.array_equal(tmask.cpu().numpy().view(np.uint32).reshape(n_tiles, MW), want_mask)
+
+
 def test_empty_map(cuda_device):
     L = _lib.lib()
     assert L.st_map_row_order(None, 0, 27, None, None, 0, _lib.stream_ptr()) == 0
     assert L.st_map_row_order(None, 5, 27, None, None, 0, _lib.stream_ptr()) == -1
+    assert L.st_map_plan(None, 0, 27, 1, None, None, None, None, 0, _lib.stream_ptr()) == 0
+    assert L.st_map_plan(None, 5, 27, 1, None, None, None, None, 0, _lib.stream_ptr()) == -1
 
 
+@pytest.mark.parametrize("form", ["order_only", "plan_natural", "plan_sorted"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16], ids=["fp32", "bf16", "fp16"])
 @pytest.mark.parametrize("n_rows,n_src,K,cin,cout,patterns", [
     (3000, 2000, 27, 32, 64, 20), (70001, 40000, 27, 64, 128, None), (5000, 5000, 8, 16, 16, None),
-    (20000, 9000, 27, 128, 64, 30)])
-def test_products_with_order(cuda_device, oracle, dtype, n_rows, n_src, K, cin, cout, patterns):
+    (20000, 9000, 27, 128, 64, 30), (9000, 9000, 125, 32, 32, 25), (2000, 2500, 27, 256, 256, 6)])
+def test_products_with_plan(cuda_device, oracle, dtype, form, n_rows, n_src, K, cin, cout, patterns):
     dev = cuda_device
     L = _lib.lib()
     nbr = _random_map(n_rows, n_src, K, 0.25, 5, dev, patterns)
@@ -93,19 +137,24 @@ def test_products_with_order(cuda_device, oracle, dtype, n_rows, n_src, K, cin, 
     with torch.cuda.device(dev):
         s = _lib.stream_ptr()
         _lib.check(L.st_map_invert(_lib.ptr(nbr), n_rows, K, n_src, _lib.ptr(inv), s), "st_map_invert")
-        order, inv_order = _order(nbr), _order(inv)
+        if form == "order_only":
+            fp, ip = (_order(nbr), None, None), (_order(inv), None, None)
+        else:
+            fp, ip = _plan(nbr, form == "plan_sorted"), _plan(inv, form == "plan_sorted")
         p = _lib.ptr
+        fpp, ipp = [p(v) for v in fp], [p(v) for v in ip]
         _lib.check(L.st_conv_fwd(code, p(x), p(w), p(nbr), p(y0), n_src, n_rows, K, cin, cout, None, 0, s), "fwd")
-        _lib.check(L.st_conv_fwd_ordered(code, p(x), p(w), p(nbr), p(order), p(y1), n_src, n_rows, K, cin, cout, None,
-                                         0, s), "fwd ordered")
+        _lib.check(L.st_conv_fwd_planned(code, p(x), p(w), p(nbr), *fpp, p(y1), n_src, n_rows, K, cin, cout, None,
+                                         0, s), "fwd planned")
         _lib.check(L.st_conv_dgrad(code, p(dy), p(w), p(inv), p(dx0), n_src, n_rows, K, cin, cout, None, 0, s), "dgrad")
-        _lib.check(L.st_conv_dgrad_ordered(code, p(dy), p(w), p(inv), p(inv_order), p(dx1), n_src, n_rows, K, cin, cout,
-                                           None, 0, s), "dgrad ordered")
+        _lib.check(L.st_conv_dgrad_planned(code, p(dy), p(w), p(inv), *ipp, p(dx1), n_src, n_rows, K, cin, cout,
+                                           None, 0, s), "dgrad planned")
         _lib.check(L.st_conv_wgrad(code, p(x), p(dy), p(nbr), p(dw0), n_src, n_rows, K, cin, cout, p(ws), ws.numel(), s),
                    "wgrad")
-        _lib.check(L.st_conv_wgrad_ordered(code, p(x), p(dy), p(nbr), p(order), p(dw1), n_src, n_rows, K, cin, cout,
-                                           p(ws), ws.numel(), s), "wgrad ordered")
+        _lib.check(L.st_conv_wgrad_planned(code, p(x), p(dy), p(nbr), *fpp, p(dw1), n_src, n_rows, K, cin, cout,
+                                           p(ws), ws.numel(), s), "wgrad planned")
         torch.cuda.synchronize()
+    assert _lib.device_status(dev)[0] == 0
     assert torch.equal(y0, y1)
     assert torch.equal(dx0, dx1)
     tol = TOL[dtype]
@@ -114,4 +163,3 @@ def test_products_with_order(cuda_device, oracle, dtype, n_rows, n_src, K, cin, 
     assert rel_err(t2n(y1), oracle.conv_fwd(xf, wf, m)) < tol
     assert rel_err(t2n(dx1), oracle.conv_dgrad(dyf, wf, m, n_src)) < tol
     assert rel_err(t2n(dw1), oracle.conv_wgrad(xf, dyf, m, K, cin, cout)) < tol
-    assert _lib.device_status(dev)[0] == 0

@@ -170,14 +170,6 @@ __device__ long long g_prof[160 * 16];
 #define PROF_CLOCK() 0ll
 #endif
 
-// Producers that fetch rows with TMA tile::gather4 and weight slices with tiled TMA copies (stored
-// maps in tile-plan form only).  An earlier form dealt the stages of a sub tile to "its" warp; a
-// launch over 834k output rows with four row tiles per super tile then ended in a launch failure.
-// The likely cause: such a warp waited for a slot's release by mbarrier parity without having taken
-// part in the slot's previous laps, so a warp with few stages could be two laps ahead of the
-// consumer, take an old phase for the release it needed, and re-arm the barrier and overwrite the
-// slot while both were in use.  Ownership now follows the slot index (see the planned producers).
-constexpr bool kTmaProducers = true;
 
 constexpr int kMaxSub = 4;
 constexpr int kMaxWSlots = 4;
@@ -200,7 +192,7 @@ struct Params2 {
   uint32_t idesc;
   int out_kind;
   int idx_bytes;           // shared memory for staged map entries (0 with a tile plan)
-  int use_tma;             // 1: gathered rows come by TMA tile::gather4, 0: by cp.async
+  int n_slots, slot_bytes; // planned_gather_kernel: ring of whole-offset slots
   int dbg;                 // timing experiments only (wrong results): 1 no proxy fence, 2 no MMA, 4 no row copies, 8 no zero-fill copies
 };
 
@@ -218,9 +210,7 @@ struct __align__(8) Control2 {
 };
 
 template <typename Map, int ESIZE>
-__global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params2 p, const Map map,
-                                                              const __grid_constant__ CUtensorMap in_desc,
-                                                              const __grid_constant__ CUtensorMap w_desc) {
+__global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params2 p, const Map map) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -233,15 +223,14 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
   Control2* ctl = reinterpret_cast<Control2*>(reinterpret_cast<unsigned char*>(idx_tile) + p.idx_bytes);
   volatile int* abort_flag = &ctl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool use_tma = kTmaProducers && p.use_tma;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.a_stages; ++s) {
-      mbar_init(smem_u32(&ctl->a_full[s]), use_tma ? 1 : kProducerWarps);
+      mbar_init(smem_u32(&ctl->a_full[s]), kProducerWarps);
       mbar_init(smem_u32(&ctl->a_empty[s]), 1);
     }
     for (int s = 0; s < p.w_slots; ++s) {
-      mbar_init(smem_u32(&ctl->w_full[s]), use_tma ? 1 : kProducerWarps);
+      mbar_init(smem_u32(&ctl->w_full[s]), kProducerWarps);
       mbar_init(smem_u32(&ctl->w_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -473,77 +462,8 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
         next_a();
       };
 
-      // ----- the same steps issued as TMA copies (group 0's four warps) -----
-      // A row step is 32 tile::gather4 copies, one per lane (rows 4l .. 4l+3 of the step; "-1" and rows
-      // past the end of the source are out of bounds and arrive as zeros), a W slice one or two tiled
-      // copies by one lane; both complete on the slot's mbarrier by byte count, so there is no
-      // hand-over lag and no proxy fence.  Warp w issues the row steps whose ring slot is w modulo 4
-      // (the ring has a multiple of 4 slots: same ownership rule as above), warp 0 all W slices;
-      // every warp issues its own items in sequence order.
-      struct RowStep {
-        int kb;
-        uint32_t flags;
-        int slot;
-        uint32_t parity;
-        bool valid;
-      };
-      RowStep pend{0, 0u, 0, 0u, false};
-      int4 pend_idx = make_int4(-1, -1, -1, -1);
-      auto tma_run = [&](const RowStep& d, const int4& idx) {
-        ok = mbar_wait_warp(smem_u32(&ctl->a_empty[d.slot]), d.parity ^ 1u, abort_flag, 27, lane);
-        if (!ok) return;
-        const uint32_t bar = smem_u32(&ctl->a_full[d.slot]);
-        const bool marker = (d.flags & 32u) != 0;
-        const bool copy = !marker && !(p.dbg & 4);
-        if (lane == 0) {
-          const int valid_bytes = marker ? 0 : min(128, red_bytes - d.kb * 128);
-          ctl->a_info[d.slot] = d.flags | ((uint32_t)(valid_bytes >> 5) << 8);
-          if (copy) mbar_arrive_expect_tx(bar, (uint32_t)kABlockBytes); else mbar_arrive(bar);
-        }
-        __syncwarp();
-        if (copy)
-          tma_gather4(a_ring + (uint32_t)d.slot * kABlockBytes + (uint32_t)lane * 512u, &in_desc, bar,
-                      d.kb * (128 / ESIZE), idx.x, idx.y, idx.z, idx.w);
-      };
-      auto tma_emit = [&](const int32_t* line, int k, int kb, uint32_t flags, bool w_first) {
-        if (w_first) {
-          const int slot = w_slot;
-          const uint32_t parity = w_phase;
-          next_w();
-          if (pwarp == 0) {
-            if (pend.valid && ok) tma_run(pend, pend_idx);
-            pend.valid = false;
-            if (ok) ok = mbar_wait_warp(smem_u32(&ctl->w_empty[slot]), parity ^ 1u, abort_flag, 29, lane);
-            if (ok && lane == 0) {
-              const uint32_t bar = smem_u32(&ctl->w_full[slot]);
-              const uint32_t w_base = w_ring + (uint32_t)slot * p.w_slot_bytes;
-              if (p.dbg & 16) {
-                mbar_arrive(bar);
-              } else if (p.b_mn_major) {
-                const int n_cb = (w_col_bytes + 127) >> 7;
-                mbar_arrive_expect_tx(bar, (uint32_t)(n_cb * kr * 128));
-                for (int cb = 0; cb < n_cb; ++cb)
-                  tma_load_2d(w_base + (uint32_t)(cb * kr * 128), &w_desc, bar, cb * kr, k * p.w_rows + kb * kr);
-              } else {
-                mbar_arrive_expect_tx(bar, (uint32_t)(p.w_rows * 128));
-                tma_load_2d(w_base, &w_desc, bar, kb * kr, k * p.w_rows);
-              }
-            }
-            __syncwarp();
-          }
-        }
-        const int slot = a_stage;
-        const uint32_t parity = a_phase;
-        next_a();
-        if (slot % kProducerWarps != pwarp) return;
-        int4 idx = make_int4(-1, -1, -1, -1);
-        if (line) idx = __ldg(reinterpret_cast<const int4*>(line) + lane);
-        if (pend.valid && ok) tma_run(pend, pend_idx);
-        pend = RowStep{kb, flags, slot, parity, true};
-        pend_idx = idx;
-      };
       auto emit = [&](const int32_t* line, int k, int kb, uint32_t flags, bool w_first) {
-        if (use_tma) tma_emit(line, k, kb, flags, w_first); else cp_emit(line, k, kb, flags, w_first);
+        cp_emit(line, k, kb, flags, w_first);
       };
       auto load_masks = [&](int64_t tile0, int word, uint32_t* m) {
 #pragma unroll
@@ -552,14 +472,23 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
       };
       uint32_t next_m[kMaxSub];
       load_masks((int64_t)blockIdx.x * p.sub, 0, next_m);
-      const bool takes_part = !use_tma || group == 0;
-      for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok && takes_part; st_i += gridDim.x) {
+      for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
         const long long cpf = PROF_CLOCK();
         const int64_t tile0 = st_i * p.sub;
         uint32_t m0[kMaxSub];
 #pragma unroll
         for (int s = 0; s < kMaxSub; ++s) m0[s] = next_m[s];
-        if (st_i + gridDim.x < p.n_super) load_masks((st_i + gridDim.x) * p.sub, 0, next_m);
+        if (st_i + gridDim.x < p.n_super) {
+          const int64_t next_tile0 = (st_i + gridDim.x) * p.sub;
+          load_masks(next_tile0, 0, next_m);
+          // The index lines of a super tile are one contiguous block of the plan.  A step's indices are
+          // loaded only one step ahead, so a miss to DRAM there would cost a full memory latency per
+          // step and warp: bring the next super tile's block into L2 now.
+          const int64_t tiles = min((int64_t)p.sub, n_tiles - next_tile0);
+          const char* block = reinterpret_cast<const char*>(map.tmap + next_tile0 * map.K * (int64_t)kTileM);
+          const int64_t lines = min(tiles * map.K * 4, (int64_t)1024);           // 128-byte lines
+          for (int64_t l = t; l < lines; l += kProducerThreads) prefetch_l2(block + l * 128);
+        }
         t_pref += PROF_CLOCK() - cpf;
         uint32_t touched = 0;
         for (int word = 0; word < map.MW && ok; ++word) {
@@ -598,13 +527,11 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
         }
         // sub tiles that exist but never got a neighbour still have to write zeros
         for (int s = 0; s < p.sub && ok; ++s) {
-          if (tile0 + s < n_tiles && !((touched >> s) & 1u))
-            emit(nullptr, 0, 0, (uint32_t)s | 4u | 8u | 16u, true);
+          if (tile0 + s < n_tiles && !((touched >> s) & 1u)) emit(nullptr, 0, 0, (uint32_t)s | 4u | 8u | 16u, true);
         }
         if (ok) emit(nullptr, 0, 0, 32u, false);                       // end of super tile
       }
       if (cur.valid && ok) run(cur, cur_lo, cur_hi);
-      if (pend.valid && ok) tma_run(pend, pend_idx);
     } else if (group == 0) {
       for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
         const int64_t row0 = st_i * p.sub * kTileM + t;          // this thread's position in sub tile 0
@@ -754,12 +681,14 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
             }
           }
           const long long ci1 = PROF_CLOCK();
+          if (p.dbg & 512) mbar_arrive(smem_u32(&ctl->a_empty[a_stage])); else
           mma_commit(smem_u32(&ctl->a_empty[a_stage]));
           if (++a_stage == p.a_stages) {
             a_stage = 0;
             a_phase ^= 1u;
           }
           if (info & 16u) {                                     // last user of the W slice
+            if (p.dbg & 512) mbar_arrive(smem_u32(&ctl->w_empty[w_slot])); else
             mma_commit(smem_u32(&ctl->w_empty[w_slot]));
             if (++w_slot == p.w_slots) {
               w_slot = 0;
@@ -788,17 +717,26 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
     bool ok = true;
     const int out_es = p.out_kind == ST_F32 ? 4 : 2;
     for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
+      // where this lane's rows go: known before the accumulators are ready, so fetched before the wait
+      int64_t dst_rows[kMaxSub];
+#pragma unroll
+      for (int s = 0; s < kMaxSub; ++s) {
+        const int64_t row = (st_i * p.sub + s) * (int64_t)kTileM + warp * 32 + lane;
+        dst_rows[s] = (s < p.sub && p.order && row < p.n_rows) ? (int64_t)__ldg(p.order + row) : row;
+      }
       ok = mbar_wait(smem_u32(&ctl->acc_full[buf]), acc_phase[buf], abort_flag, 26, 256);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
-      for (int s = 0; s < p.sub; ++s) {
+#pragma unroll
+      for (int s = 0; s < kMaxSub; ++s) {
+        if (s >= p.sub) break;
         const int64_t row = (st_i * p.sub + s) * (int64_t)kTileM + warp * 32 + lane;
         if ((st_i * p.sub + s) * (int64_t)kTileM >= p.n_rows) break;         // whole sub tile past the end
-        const int64_t dst_row = (p.order && row < p.n_rows) ? (int64_t)__ldg(p.order + row) : row;
+        const int64_t dst_row = dst_rows[s];
         char* out_row = static_cast<char*>(p.out) + (size_t)dst_row * p.c_acc * out_es;
         const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * set_cols + s * p.c_acc);
-        for (int c0 = 0; c0 < p.c_acc; c0 += 32) {
+        for (int c0 = 0; c0 < p.c_acc && !(p.dbg & 128); c0 += 32) {
           uint32_t v[32];
           if (p.c_acc - c0 >= 32) {
             tmem_ld32(t_row + c0, v);
@@ -1135,6 +1073,12 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p,
 
 }  // namespace tc
 
+}  // namespace st
+
+#include "conv_tc_plan.cuh"
+
+namespace st {
+
 static int g_sm_count = 0;
 
 static int sm_count() {
@@ -1199,6 +1143,8 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   p->tmem_cols = cols;
   p->w_slots = 3;
   p->idx_bytes = planned ? 0 : tc::kIdxTileBytes;
+  p->n_slots = 0;
+  p->slot_bytes = 0;
   const int budget = 222 * 1024 - p->idx_bytes;
   int a_stages = (budget - p->w_slots * p->w_slot_bytes) / tc::kABlockBytes;
   if (a_stages > tc::kMaxAStages) a_stages = tc::kMaxAStages;
@@ -1218,6 +1164,8 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   {
     const char* e = getenv("ST_TC_DEBUG");
     p->dbg = e ? atoi(e) : 0;
+    const char* g = getenv("ST_TC_ASTAGES");
+    if (g && atoi(g) >= 4 && atoi(g) <= p->a_stages) p->a_stages = atoi(g) / 4 * 4;
     const char* f = getenv("ST_TC_SUB");
     if (f && atoi(f) >= 1 && atoi(f) <= sub) {
       p->sub = atoi(f);
@@ -1286,13 +1234,6 @@ static bool make_weight_desc(CUtensorMap* desc, const void* base, int64_t rows, 
 
 template <typename Map>
 static int launch_gather(tc::Params2 p, const Map& map, cudaStream_t stream) {
-  CUtensorMap in_desc, w_desc;
-  memset(&in_desc, 0, sizeof(in_desc));
-  memset(&w_desc, 0, sizeof(w_desc));
-  p.use_tma = tc::kTmaProducers && Map::kPlanned && !getenv("ST_TC_NO_TMA") && p.n_src > 0 &&
-              make_gather_desc(&in_desc, p.in, p.n_src, p.c_red, p.esize, p.out_kind) &&
-              make_weight_desc(&w_desc, p.w, (int64_t)p.K * p.w_rows, p.w_cols, p.esize, p.out_kind,
-                               p.b_mn_major ? 128 / p.esize : p.w_rows, p.b_mn_major && p.esize == 4) ? 1 : 0;
   const size_t smem = (size_t)p.w_slots * p.w_slot_bytes + (size_t)p.a_stages * tc::kABlockBytes +
                       p.idx_bytes + sizeof(tc::Control2) + 1024;
   auto kernel = p.esize == 2 ? tc::gather2_kernel<Map, 2> : tc::gather2_kernel<Map, 4>;
@@ -1306,9 +1247,42 @@ static int launch_gather(tc::Params2 p, const Map& map, cudaStream_t stream) {
     configured[p.esize == 4] = true;
   }
   int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
-  kernel<<<(unsigned)grid, tc::kGatherThreads, smem, stream>>>(p, map, in_desc, w_desc);
+  kernel<<<(unsigned)grid, tc::kGatherThreads, smem, stream>>>(p, map);
   note_launches(1);
   return check_launch("tc gather");
+}
+
+// A stored map in tile-plan form: the TMA-fed kernel when the tensors can be described to the copy
+// engine (16-byte aligned bases and row pitches) and two whole-offset slots fit in shared memory,
+// else the cp.async producers of gather2_kernel over the same plan.
+static int launch_planned(tc::Params2 p, const tc::PlannedRows& map, cudaStream_t stream) {
+  CUtensorMap in_desc, w_desc;
+  memset(&in_desc, 0, sizeof(in_desc));
+  memset(&w_desc, 0, sizeof(w_desc));
+  p.slot_bytes = p.w_slot_bytes + p.sub * tc::kABlockBytes;
+  int n_slots = (int)((222 * 1024 - (int)sizeof(tc::Control3)) / p.slot_bytes);
+  if (n_slots > tc::kMaxSlots3) n_slots = tc::kMaxSlots3;
+  p.n_slots = n_slots;
+  const bool tma = !getenv("ST_TC_NO_TMA") && n_slots >= 2 && p.n_src > 0 &&
+                   make_gather_desc(&in_desc, p.in, p.n_src, p.c_red, p.esize, p.out_kind) &&
+                   make_weight_desc(&w_desc, p.w, (int64_t)p.K * p.w_rows, p.w_cols, p.esize, p.out_kind,
+                                    p.b_mn_major ? 128 / p.esize : p.w_rows, p.b_mn_major && p.esize == 4);
+  if (!tma) return launch_gather(p, map, stream);
+  const size_t smem = (size_t)p.n_slots * p.slot_bytes + sizeof(tc::Control3) + 1024;
+  auto kernel = p.esize == 2 ? tc::planned_gather_kernel<2> : tc::planned_gather_kernel<4>;
+  static bool configured[2] = {false, false};
+  if (!configured[p.esize == 4]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) {
+      set_error("tc planned gather: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
+      return ST_ERR_CUDA;
+    }
+    configured[p.esize == 4] = true;
+  }
+  int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
+  kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, map, in_desc, w_desc);
+  note_launches(1);
+  return check_launch("tc planned gather");
 }
 
 int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, const MapPlan& plan, void* out,
@@ -1321,7 +1295,7 @@ int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map,
   }
   if (n_rows == 0) return ST_OK;
   p.order = plan.order;
-  if (planned) return launch_gather(p, tc::PlannedRows{plan.tmap, plan.tmask, K, (K + 31) / 32}, stream);
+  if (planned) return launch_planned(p, tc::PlannedRows{plan.tmap, plan.tmask, K, (K + 31) / 32}, stream);
   return launch_gather(p, tc::StoredRows{map, K}, stream);
 }
 

@@ -797,6 +797,7 @@ struct WgradParams {
   int ci_blk;            // input channels per CTA (MMA N)
   int n_ciblk, n_coblk;
   int a_slot_bytes, b_slot_bytes, b_slots;
+  int quad;              // planned_wgrad_kernel: offsets per shared-memory slot (b_slots counts such slots)
   int tmem_cols;
   uint32_t idesc_base;   // everything but N
 };
@@ -1196,7 +1197,8 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // Descriptor of a row-major (rows, cols) matrix for tile::gather4: box = one 128-byte line, 128-byte swizzle.
-static bool make_gather_desc(CUtensorMap* desc, const void* base, int64_t rows, int cols, int esize, int dtype) {
+static bool make_gather_desc(CUtensorMap* desc, const void* base, int64_t rows, int cols, int esize, int dtype,
+                             bool atom32 = false) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn || !base || rows < 1 || (reinterpret_cast<uintptr_t>(base) & 15) || (cols * esize) % 16) return false;
   const CUtensorMapDataType dt = dtype == ST_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -1207,8 +1209,8 @@ static bool make_gather_desc(CUtensorMap* desc, const void* base, int64_t rows, 
   const cuuint32_t box[2] = {(cuuint32_t)(128 / esize), 1};
   const cuuint32_t estride[2] = {1, 1};
   return fn(desc, dt, 2, const_cast<void*>(base), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // Descriptor of the weights seen as a (K * w_rows, w_cols) matrix; the box is one 128-byte column block
@@ -1421,6 +1423,42 @@ static int launch_wgrad(WgradPlan& plan, const Map& map, cudaStream_t stream) {
   return check_launch("tc wgrad");
 }
 
+// Tile-plan form: the TMA-fed kernel when both tensors can be described to the copy engine and two
+// slots fit, else the cp.async producers of wgrad_kernel over the same plan.
+static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cudaStream_t stream) {
+  tc::WgradParams& p = plan.p;
+  const int budget = 222 * 1024 - 2 * p.a_slot_bytes - (int)sizeof(tc::WgradControl3);
+  int quad = budget / (2 * p.b_slot_bytes);
+  if (quad > tc::kProducerWarps) quad = tc::kProducerWarps;
+  if (quad > p.group) quad = p.group;
+  CUtensorMap x_desc, dy_desc;
+  memset(&x_desc, 0, sizeof(x_desc));
+  memset(&dy_desc, 0, sizeof(dy_desc));
+  const int dtype = p.esize == 4 ? ST_F32 : ST_BF16;      // element size is all the copy engine needs to know
+  const bool tma = !getenv("ST_TC_NO_TMA") && quad >= 1 && p.n_src > 0 &&
+                   make_gather_desc(&x_desc, p.x, p.n_src, p.cin, p.esize, dtype, p.esize == 4) &&
+                   make_gather_desc(&dy_desc, p.dy, p.n_rows, p.cout, p.esize, dtype, p.esize == 4);
+  if (!tma) return launch_wgrad(plan, map, stream);
+  p.quad = quad;
+  int slots = budget / (quad * p.b_slot_bytes);
+  p.b_slots = slots > 4 ? 4 : slots;
+  const size_t smem = 2 * (size_t)p.a_slot_bytes + (size_t)p.b_slots * quad * p.b_slot_bytes + sizeof(tc::WgradControl3) + 1024;
+  auto kernel = tc::planned_wgrad_kernel;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) {
+      set_error("tc planned wgrad: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
+      return ST_ERR_CUDA;
+    }
+    configured = true;
+  }
+  dim3 grid((unsigned)plan.n_chunks, (unsigned)p.n_kgroups, (unsigned)(p.n_coblk * p.n_ciblk));
+  kernel<<<grid, tc::kThreads, smem, stream>>>(p, map, x_desc, dy_desc);
+  note_launches(1);
+  return check_launch("tc planned wgrad");
+}
+
 static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void* dy, float* partial, int64_t n_rows,
                           int64_t n_src, int K, int cin, int cout) {
   if (!plan_wgrad(plan, dtype, n_rows, K, cin, cout)) {
@@ -1430,6 +1468,7 @@ static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void*
   plan->p.x = x;
   plan->p.dy = dy;
   plan->p.order = nullptr;
+  plan->p.quad = 1;
   plan->p.partial = partial;
   plan->p.n_src = n_src;
   return true;
@@ -1441,7 +1480,8 @@ int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, 
   if (!prepare_wgrad(&plan, dtype, x, dy, partial, n_rows, n_src, K, cin, cout)) return ST_ERR_UNSUPPORTED;
   plan.p.order = rows.order;
   *n_chunks_out = plan.n_chunks;
-  if (rows.tmap && rows.tmask) return launch_wgrad(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream);
+  if (rows.tmap && rows.tmask)
+    return launch_wgrad_planned(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream);
   return launch_wgrad(plan, tc::StoredRows{map, K}, stream);
 }
 

@@ -307,5 +307,260 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
   }
 }
 
+
+// =================================================================================================
+// Weight gradient over a stored map in tile-plan form, fed by TMA.
+//
+//   dW[k][ci][co] = sum_r  X[tmap(r, k)][ci] * dY[order[r]][co]
+//
+// Same decomposition as wgrad_kernel (a CTA owns a chunk of row tiles, a group of G offsets whose G
+// accumulators fill TMEM, a block of output channels and one of input channels; fp32 partials per
+// chunk), but:
+//   - the tile's mask says which offsets of the group have any neighbour in the tile; both the
+//     producers and the MMA thread read it, so no step descriptors travel through shared memory;
+//   - the dY tile and the gathered X rows arrive by tile::gather4 (rows of dY through `order`, rows
+//     of X through the tile's index lines);
+//   - up to Q offsets share one shared-memory slot and one mbarrier (producer warp q fetches the
+//     rows of the q-th of them), so the MMA thread waits and commits once per Q x 8 (16) MMAs.
+// Every producer warp arrives on every barrier (see planned_gather_kernel).
+// =================================================================================================
+struct __align__(8) WgradControl3 {
+  unsigned long long a_full[2], a_empty[2];
+  unsigned long long b_full[4], b_empty[4];
+  unsigned long long acc_full;
+  uint32_t touched;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradParams p, const PlannedRows map,
+                                                                    const __grid_constant__ CUtensorMap x_desc,
+                                                                    const __grid_constant__ CUtensorMap dy_desc) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - raw);
+  const uint32_t a_ring = base;
+  const uint32_t b_ring = base + 2u * (uint32_t)p.a_slot_bytes;
+  const uint32_t quad_bytes = (uint32_t)p.quad * (uint32_t)p.b_slot_bytes;
+  WgradControl3* ctl = reinterpret_cast<WgradControl3*>(base_ptr + 2 * (size_t)p.a_slot_bytes + (size_t)p.b_slots * quad_bytes);
+  volatile int* abort_flag = &ctl->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // work item of this CTA
+  const int chunk = blockIdx.x;
+  const int kgroup = blockIdx.y;
+  const int coblk = blockIdx.z / p.n_ciblk, ciblk = blockIdx.z % p.n_ciblk;
+  const int k_first = kgroup * p.group;
+  const int g_count = min(p.group, p.K - k_first);
+  const int co0 = coblk * 128, co_cnt = min(128, p.cout - co0);
+  const int ci0 = ciblk * p.ci_blk, ci_cnt = min(p.ci_blk, p.cin - ci0);
+  const int64_t tile_begin = (int64_t)chunk * p.tiles_per_chunk;
+  const int64_t tile_end = min(p.n_tiles, tile_begin + p.tiles_per_chunk);
+  const int word = k_first >> 5, shift = k_first & 31;
+  const uint32_t group_bits = g_count >= 32 ? 0xFFFFFFFFu : ((1u << g_count) - 1u);
+  const int per_line = 128 / p.esize;                       // elements of one 128-byte line
+  const int a_blocks = (co_cnt * p.esize + 127) >> 7;       // 128-byte column blocks of the dY tile
+  const int b_blocks = (ci_cnt * p.esize + 127) >> 7;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&ctl->a_full[s]), kProducerWarps);
+      mbar_init(smem_u32(&ctl->a_empty[s]), 1);
+    }
+    for (int s = 0; s < p.b_slots; ++s) {
+      mbar_init(smem_u32(&ctl->b_full[s]), kProducerWarps);
+      mbar_init(smem_u32(&ctl->b_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctl->acc_full), 2);
+    ctl->abort_flag = 0;
+    ctl->touched = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), (uint32_t)p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const bool base32 = p.esize == 4;                 // 32-bit elements: 128-byte swizzle with 32-byte atoms
+
+  auto tile_mask = [&](int64_t tile) { return (__ldg(map.tmask + tile * map.MW + word) >> shift) & group_bits; };
+
+  if (warp >= kFirstProducerWarp) {
+    // =============================================================== producers
+    const int pw = warp - kFirstProducerWarp;
+    int a_slot = 0, b_slot = 0;
+    uint32_t a_phase = 0, b_phase = 0;
+    bool ok = true;
+    uint32_t m_next = tile_begin < tile_end ? tile_mask(tile_begin) : 0u;
+    for (int64_t tile = tile_begin; tile < tile_end && ok; ++tile) {
+      uint32_t m = m_next;
+      if (tile + 1 < tile_end) m_next = tile_mask(tile + 1);
+      if (!m) continue;
+      // ---- the dY tile: rows order[tile * 128 + r]
+      {
+        const int64_t pos = tile * kTileM + 4 * lane;
+        int4 rows;
+        if (p.order) {
+          // the last tile's line may run past the end of `order`: read only what exists
+          rows.x = pos + 0 < p.n_rows ? __ldg(p.order + pos + 0) : -1;
+          rows.y = pos + 1 < p.n_rows ? __ldg(p.order + pos + 1) : -1;
+          rows.z = pos + 2 < p.n_rows ? __ldg(p.order + pos + 2) : -1;
+          rows.w = pos + 3 < p.n_rows ? __ldg(p.order + pos + 3) : -1;
+        } else {
+          rows = make_int4((int)pos, (int)pos + 1, (int)pos + 2, (int)pos + 3);
+        }
+        if (pos + 0 >= p.n_rows) rows.x = -1;
+        if (pos + 1 >= p.n_rows) rows.y = -1;
+        if (pos + 2 >= p.n_rows) rows.z = -1;
+        if (pos + 3 >= p.n_rows) rows.w = -1;
+        ok = mbar_wait_warp(smem_u32(&ctl->a_empty[a_slot]), a_phase ^ 1u, abort_flag, 35, lane);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&ctl->a_full[a_slot]);
+        const uint32_t slot_base = a_ring + (uint32_t)a_slot * (uint32_t)p.a_slot_bytes;
+        // column block b is fetched by warp b % 4
+        int mine = 0;
+        for (int b = pw; b < a_blocks; b += kProducerWarps) ++mine;
+        if (lane == 0) {
+          if (mine) mbar_arrive_expect_tx(bar, (uint32_t)mine * kABlockBytes); else mbar_arrive(bar);
+        }
+        __syncwarp();
+        for (int b = pw; b < a_blocks; b += kProducerWarps)
+          tma_gather4(slot_base + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &dy_desc, bar, co0 + b * per_line,
+                      rows.x, rows.y, rows.z, rows.w);
+        if (++a_slot == 2) {
+          a_slot = 0;
+          a_phase ^= 1u;
+        }
+      }
+      // ---- the gathered X rows, `quad` offsets per slot: warp q fetches the q-th of them
+      while (m && ok) {
+        int my_j = -1;
+        for (int q = 0; q < p.quad && m; ++q) {
+          const int j = __ffs(m) - 1;
+          m &= m - 1;
+          if (q == pw) my_j = j;
+        }
+        int4 idx = make_int4(-1, -1, -1, -1);
+        if (my_j >= 0)
+          idx = __ldg(reinterpret_cast<const int4*>(map.tmap + (tile * map.K + k_first + my_j) * (int64_t)kTileM) + lane);
+        ok = mbar_wait_warp(smem_u32(&ctl->b_empty[b_slot]), b_phase ^ 1u, abort_flag, 36, lane);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&ctl->b_full[b_slot]);
+        const uint32_t stage = b_ring + (uint32_t)b_slot * quad_bytes + (uint32_t)pw * (uint32_t)p.b_slot_bytes;
+        if (lane == 0) {
+          if (my_j >= 0) mbar_arrive_expect_tx(bar, (uint32_t)b_blocks * kABlockBytes); else mbar_arrive(bar);
+        }
+        __syncwarp();
+        if (my_j >= 0) {
+          for (int b = 0; b < b_blocks; ++b)
+            tma_gather4(stage + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &x_desc, bar, ci0 + b * per_line, idx.x,
+                        idx.y, idx.z, idx.w);
+        }
+        if (++b_slot == p.b_slots) {
+          b_slot = 0;
+          b_phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // =============================================================== MMA issuer
+    if (lane == 0) {
+      int a_slot = 0, b_slot = 0;
+      uint32_t a_phase = 0, b_phase = 0;
+      uint32_t touched = 0;
+      bool ok = true;
+      const int rows_per_step = 32 / p.esize;                  // reduction rows per MMA (16 or 8)
+      const int ksteps = kTileM / rows_per_step;
+      const uint32_t step_bytes = (uint32_t)rows_per_step * 128u;
+      const uint32_t sbo = base32 ? 512u : 1024u, layout = base32 ? 1u : 2u;
+      const uint32_t idesc = p.idesc_base | ((uint32_t)(p.ci_blk >> 3) << 17);
+      const uint64_t desc_hi = smem_desc(0u, kABlockBytes, sbo, layout);
+      uint32_t m_next = tile_begin < tile_end ? tile_mask(tile_begin) : 0u;
+      for (int64_t tile = tile_begin; tile < tile_end && ok; ++tile) {
+        uint32_t m = m_next;
+        if (tile + 1 < tile_end) m_next = tile_mask(tile + 1);
+        if (!m) continue;
+        ok = mbar_wait(smem_u32(&ctl->a_full[a_slot]), a_phase, abort_flag, 37);
+        if (!ok) break;
+        const uint32_t a_lo = (a_ring + (uint32_t)a_slot * (uint32_t)p.a_slot_bytes) >> 4;
+        while (m && ok) {
+          ok = mbar_wait(smem_u32(&ctl->b_full[b_slot]), b_phase, abort_flag, 38);
+          if (!ok) break;
+          tc_fence_after();
+          for (int q = 0; q < p.quad && m; ++q) {
+            const int j = __ffs(m) - 1;
+            m &= m - 1;
+            const uint32_t b_lo = (b_ring + (uint32_t)b_slot * quad_bytes + (uint32_t)q * (uint32_t)p.b_slot_bytes) >> 4;
+            const uint32_t d_addr = tmem_base + (uint32_t)(j * p.ci_blk);
+            const uint32_t first = ((touched >> j) & 1u) ? 1u : 0u;
+            for (int ks = 0; ks < ksteps; ++ks) {
+              const uint64_t da = desc_hi | (uint64_t)(a_lo + ks * (step_bytes >> 4));
+              const uint64_t db = desc_hi | (uint64_t)(b_lo + ks * (step_bytes >> 4));
+              if (p.esize == 2)
+                mma_f16(d_addr, da, db, idesc, ks == 0 ? first : 1u);
+              else
+                mma_tf32(d_addr, da, db, idesc, ks == 0 ? first : 1u);
+            }
+            touched |= 1u << j;
+          }
+          mma_commit(smem_u32(&ctl->b_empty[b_slot]));
+          if (++b_slot == p.b_slots) {
+            b_slot = 0;
+            b_phase ^= 1u;
+          }
+        }
+        mma_commit(smem_u32(&ctl->a_empty[a_slot]));
+        if (++a_slot == 2) {
+          a_slot = 0;
+          a_phase ^= 1u;
+        }
+      }
+      if (ok) {
+        ctl->touched = touched;
+        mma_commit(smem_u32(&ctl->acc_full));
+        mbar_arrive(smem_u32(&ctl->acc_full));
+      }
+    }
+    __syncwarp();
+  } else {
+    // =============================================================== epilogue (warps 0..3)
+    bool ok = mbar_wait(smem_u32(&ctl->acc_full), 0u, abort_flag, 39, 512);
+    ok = __all_sync(0xFFFFFFFFu, ok);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t touched = ctl->touched;
+      const int co = warp * 32 + lane;                           // accumulator row = output channel
+      for (int j = 0; j < g_count; ++j) {
+        float* dst = p.partial + (((size_t)chunk * p.K + (k_first + j)) * p.cin + ci0) * p.cout + co0 + co;
+        const bool live = (touched >> j) & 1u;
+        for (int c0 = 0; c0 < ci_cnt; c0 += 16) {
+          uint32_t v[32];
+          tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(j * p.ci_blk + c0), v);
+          tmem_ld_wait();
+          if (co < co_cnt) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) dst[(size_t)(c0 + c) * p.cout] = live ? __uint_as_float(v[c]) : 0.f;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  if (*abort_flag) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
 }  // namespace tc
 }  // namespace st

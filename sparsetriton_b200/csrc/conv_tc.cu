@@ -192,7 +192,8 @@ struct Params2 {
   uint32_t idesc;
   int out_kind;
   int idx_bytes;           // shared memory for staged map entries (0 with a tile plan)
-  int n_slots, slot_bytes; // planned_gather_kernel: ring of whole-offset slots
+  int n_slots, slot_bytes; // planned_gather_kernel: ring of slots
+  int part;                // planned_gather_kernel: sub tiles per slot
   int dbg;                 // timing experiments only (wrong results): 1 no proxy fence, 2 no MMA, 4 no row copies, 8 no zero-fill copies
 };
 
@@ -1146,6 +1147,7 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   p->idx_bytes = planned ? 0 : tc::kIdxTileBytes;
   p->n_slots = 0;
   p->slot_bytes = 0;
+  p->part = 1;
   const int budget = 222 * 1024 - p->idx_bytes;
   int a_stages = (budget - p->w_slots * p->w_slot_bytes) / tc::kABlockBytes;
   if (a_stages > tc::kMaxAStages) a_stages = tc::kMaxAStages;
@@ -1261,9 +1263,21 @@ static int launch_planned(tc::Params2 p, const tc::PlannedRows& map, cudaStream_
   CUtensorMap in_desc, w_desc;
   memset(&in_desc, 0, sizeof(in_desc));
   memset(&w_desc, 0, sizeof(w_desc));
-  p.slot_bytes = p.w_slot_bytes + p.sub * tc::kABlockBytes;
-  int n_slots = (int)((222 * 1024 - (int)sizeof(tc::Control3)) / p.slot_bytes);
-  if (n_slots > tc::kMaxSlots3) n_slots = tc::kMaxSlots3;
+  p.part = p.sub;                        // smaller parts (more slots in flight) were measured slower
+  {
+    const char* e = getenv("ST_TC_PART");
+    if (e && atoi(e) >= 1 && atoi(e) <= p.sub) p.part = atoi(e);
+  }
+  int n_slots = 0;
+  for (;;) {
+    p.slot_bytes = p.w_slot_bytes + p.part * tc::kABlockBytes;
+    n_slots = (int)((222 * 1024 - (int)sizeof(tc::Control3)) / p.slot_bytes);
+    if (n_slots > tc::kMaxSlots3) n_slots = tc::kMaxSlots3;
+    // the slot that carries an offset's W slice is held until the offset's last item: the ring must
+    // have room for all of an offset's items
+    if (n_slots >= (p.sub + p.part - 1) / p.part || p.part >= p.sub) break;
+    ++p.part;
+  }
   p.n_slots = n_slots;
   const bool tma = !getenv("ST_TC_NO_TMA") && n_slots >= 2 && p.n_src > 0 &&
                    make_gather_desc(&in_desc, p.in, p.n_src, p.c_red, p.esize, p.out_kind) &&
@@ -1439,6 +1453,10 @@ static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cud
                    make_gather_desc(&x_desc, p.x, p.n_src, p.cin, p.esize, dtype, p.esize == 4) &&
                    make_gather_desc(&dy_desc, p.dy, p.n_rows, p.cout, p.esize, dtype, p.esize == 4);
   if (!tma) return launch_wgrad(plan, map, stream);
+  {
+    const char* e = getenv("ST_TC_QUAD");
+    if (e && atoi(e) >= 1 && atoi(e) <= quad) quad = atoi(e);
+  }
   p.quad = quad;
   int slots = budget / (quad * p.b_slot_bytes);
   p.b_slots = slots > 4 ? 4 : slots;
@@ -1479,10 +1497,13 @@ int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, 
   WgradPlan plan;
   if (!prepare_wgrad(&plan, dtype, x, dy, partial, n_rows, n_src, K, cin, cout)) return ST_ERR_UNSUPPORTED;
   plan.p.order = rows.order;
-  *n_chunks_out = plan.n_chunks;
+  int rc;
   if (rows.tmap && rows.tmask)
-    return launch_wgrad_planned(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream);
-  return launch_wgrad(plan, tc::StoredRows{map, K}, stream);
+    rc = launch_wgrad_planned(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream);
+  else
+    rc = launch_wgrad(plan, tc::StoredRows{map, K}, stream);
+  *n_chunks_out = plan.n_chunks;
+  return rc;
 }
 
 int tc_conv_wgrad_hashfly(int dtype, const void* x, const void* dy, const HashFlyArgs& h, float* partial,

@@ -9,6 +9,10 @@
 //
 //   slot = [ W slice of (k, kb) | rows of sub tile 0 | ... | rows of sub tile S-1 ]      one mbarrier
 //
+// or, to have more and smaller slots in flight, a part of it: the super tile's S sub tiles are dealt
+// in parts of P; the offset's first item carries the W slice and its slot is held back until the
+// offset's last item has been multiplied.
+//
 // Producer warp w fetches the rows of sub tile w with 32 tile::gather4 copies (lane l: rows 4l..4l+3;
 // "-1" and rows past the end of the source are out of bounds and arrive as zeros); warp 0 also
 // fetches the W slice with one or two tiled copies; each warp announces its own bytes on the slot's
@@ -31,7 +35,8 @@ struct __align__(8) Control3 {
   unsigned long long full[kMaxSlots3], empty[kMaxSlots3];
   unsigned long long acc_full[2], acc_empty[2];
   // bits 0-3 sub tiles that take part, bits 4-7 those whose accumulator starts here, bits 8-11 K-steps,
-  // bit 12 end of super tile (no data)
+  // bit 12 end of super tile (no data), bit 13 the slot carries the offset's W slice, bit 14 last item
+  // of the offset, bits 16-17 which part of the super tile the slot's rows belong to
   uint32_t info[kMaxSlots3];
   uint32_t tmem_base;
   int abort_flag;
@@ -84,12 +89,14 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
     bool ok = true;
     struct Item {
       int k, kb;
-      uint32_t users, fresh;
+      uint32_t users, fresh;   // sub tiles of this item (absolute bits)
+      int part;                // which group of p.part sub tiles
+      bool has_w, last;        // carries the W slice / is the offset's last item
       int slot;
       uint32_t parity;
       bool marker, valid;
     };
-    Item pend{0, 0, 0u, 0u, 0, 0u, false, false};
+    Item pend{0, 0, 0u, 0u, 0, false, false, 0, 0u, false, false};
     int4 pend_idx = make_int4(-1, -1, -1, -1);
 
     auto run = [&](const Item& d, const int4& idx) {
@@ -101,10 +108,11 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
       if (lane == 0) {
         // Every producer warp arrives on every slot, announcing the bytes of its own copies first (a
         // copy that completed before its bytes were announced would drive the count negative).
-        const bool copy_w = pw == 0 && !d.marker && !(p.dbg & 16);
+        const bool copy_w = pw == 0 && d.has_w && !d.marker && !(p.dbg & 16);
         if (pw == 0) {
           const int valid_bytes = d.marker ? 0 : min(128, red_bytes - d.kb * 128);
-          ctl->info[d.slot] = d.users | (d.fresh << 4) | ((uint32_t)(valid_bytes >> 5) << 8) | (d.marker ? 0x1000u : 0u);
+          ctl->info[d.slot] = d.users | (d.fresh << 4) | ((uint32_t)(valid_bytes >> 5) << 8) | (d.marker ? 0x1000u : 0u) |
+                              (d.has_w ? 0x2000u : 0u) | (d.last ? 0x4000u : 0u) | ((uint32_t)d.part << 16);
         }
         const uint32_t bytes = (copy_w ? w_bytes : 0u) + (copy_rows ? (uint32_t)kABlockBytes : 0u);
         if (bytes) mbar_arrive_expect_tx(bar, bytes); else mbar_arrive(bar);
@@ -120,21 +128,42 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
       }
       __syncwarp();
       if (copy_rows)
-        tma_gather4(slot_base + (uint32_t)p.w_slot_bytes + (uint32_t)pw * kABlockBytes + (uint32_t)lane * 512u, &in_desc,
-                    bar, d.kb * kr, idx.x, idx.y, idx.z, idx.w);
+        tma_gather4(slot_base + (uint32_t)p.w_slot_bytes + (uint32_t)(pw - d.part * p.part) * kABlockBytes +
+                        (uint32_t)lane * 512u,
+                    &in_desc, bar, d.kb * kr, idx.x, idx.y, idx.z, idx.w);
     };
     // Queue one item: its indices are loaded now and it is issued when the next one is queued, so the
     // load overlaps the previous item's wait and copies.
-    auto emit = [&](int64_t tile0, int k, int kb, uint32_t users, uint32_t fresh, bool marker, bool zeros) {
+    auto emit_item = [&](int64_t tile0, const Item& d, bool zeros) {
       int4 idx = make_int4(-1, -1, -1, -1);
-      if (!marker && !zeros && ((users >> pw) & 1u))
-        idx = __ldg(reinterpret_cast<const int4*>(map.tmap + ((tile0 + pw) * map.K + k) * (int64_t)kTileM) + lane);
+      if (!d.marker && !zeros && ((d.users >> pw) & 1u))
+        idx = __ldg(reinterpret_cast<const int4*>(map.tmap + ((tile0 + pw) * map.K + d.k) * (int64_t)kTileM) + lane);
       if (pend.valid && ok) run(pend, pend_idx);
-      pend = Item{k, kb, users, fresh, slot, phase, marker, true};
+      pend = d;
+      pend.slot = slot;
+      pend.parity = phase;
+      pend.valid = true;
       pend_idx = idx;
       if (++slot == p.n_slots) {
         slot = 0;
         phase ^= 1u;
+      }
+    };
+    // One offset of the super tile: an item per part (p.part sub tiles) that has a user; the first one
+    // carries the W slice, which the later ones read from its slot.
+    auto emit = [&](int64_t tile0, int k, int kb, uint32_t users, uint32_t fresh, bool marker, bool zeros) {
+      if (marker) {
+        emit_item(tile0, Item{0, 0, 0u, 0u, 0, false, false, 0, 0u, true, true}, false);
+        return;
+      }
+      const uint32_t part_bits = (1u << p.part) - 1u;
+      bool first = true;
+      for (int q = 0; q * p.part < p.sub; ++q) {
+        const uint32_t u = users & (part_bits << (q * p.part));
+        if (!u) continue;
+        const bool last = (users >> ((q + 1) * p.part)) == 0u;
+        emit_item(tile0, Item{k, kb, u, fresh & u, q, first, last, 0, 0u, false, true}, zeros);
+        first = false;
       }
     };
     auto load_masks = [&](int64_t tile0, int word, uint32_t* m) {
@@ -203,6 +232,8 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
       const uint64_t a_desc_hi = smem_desc(0u, 16u, 1024u, 2u);
       const uint64_t b_desc_hi = smem_desc(0u, b_lbo, b_base32 ? 512u : 1024u, b_base32 ? 1u : 2u);
       const uint32_t idesc = p.idesc;
+      uint32_t w_lo = 0;
+      int held = -1;                                          // slot kept for its W slice
       for (int64_t st_i = blockIdx.x; st_i < p.n_super && ok; st_i += gridDim.x) {
         ok = mbar_wait(smem_u32(&ctl->acc_empty[buf]), acc_phase[buf] ^ 1u, abort_flag, 32);
         if (!ok) break;
@@ -212,14 +243,18 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
           if (!ok) break;
           const uint32_t info = ctl->info[slot];
           tc_fence_after();
+          const uint32_t slot_base = base + (uint32_t)slot * (uint32_t)p.slot_bytes;
+          if (info & 0x2000u) {                                  // the offset's W slice lives in this slot
+            w_lo = slot_base >> 4;
+            held = slot;
+          }
           if (!(info & 0x1000u) && !(p.dbg & 2)) {
-            const uint32_t slot_base = base + (uint32_t)slot * (uint32_t)p.slot_bytes;
-            const uint32_t w_lo = slot_base >> 4;
             const int ksteps = (int)((info >> 8) & 15u);
+            const int part0 = (int)((info >> 16) & 3u) * p.part;
 #pragma unroll
             for (int s = 0; s < kMaxSub; ++s) {
               if (!((info >> s) & 1u)) continue;
-              const uint32_t a_lo = (slot_base + (uint32_t)p.w_slot_bytes + (uint32_t)s * kABlockBytes) >> 4;
+              const uint32_t a_lo = (slot_base + (uint32_t)p.w_slot_bytes + (uint32_t)(s - part0) * kABlockBytes) >> 4;
               const uint32_t d_addr = tmem_base + (uint32_t)(buf * set_cols + s * p.c_acc);
               const uint32_t fresh = ((info >> (4 + s)) & 1u) ? 0u : 1u;        // 0: the first MMA overwrites
 #pragma unroll
@@ -235,7 +270,16 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
               }
             }
           }
-          mma_commit(smem_u32(&ctl->empty[slot]));
+          // A slot that holds the W slice stays with the consumer until the offset's last item is done.
+          if (info & 0x1000u) {
+            mma_commit(smem_u32(&ctl->empty[slot]));
+          } else if (info & 0x4000u) {
+            if (held >= 0 && held != slot) mma_commit(smem_u32(&ctl->empty[held]));
+            mma_commit(smem_u32(&ctl->empty[slot]));
+            held = -1;
+          } else if (held != slot) {
+            mma_commit(smem_u32(&ctl->empty[slot]));
+          }
           if (++slot == p.n_slots) {
             slot = 0;
             phase ^= 1u;

@@ -1399,8 +1399,12 @@ static bool plan_wgrad(WgradPlan* plan, int dtype, int64_t n_rows, int K, int ci
   p.idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(tc::kTileM >> 4) << 24);
   const int64_t ctas_per_chunk = (int64_t)p.n_kgroups * p.n_coblk * p.n_ciblk;
   int64_t chunks = (2 * sm_count() + ctas_per_chunk - 1) / ctas_per_chunk;
+  {
+    const char* e = getenv("ST_TC_WCHUNKS");
+    if (e && atoi(e) >= 1) chunks = atoi(e);
+  }
   if (chunks > p.n_tiles) chunks = p.n_tiles;
-  if (chunks > 64) chunks = 64;
+  if (chunks > 256) chunks = 256;
   if (chunks < 1) chunks = 1;
   p.tiles_per_chunk = (p.n_tiles + chunks - 1) / chunks;
   plan->n_chunks = (int)((p.n_tiles + p.tiles_per_chunk - 1) / p.tiles_per_chunk);

@@ -399,8 +399,9 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
   const int g_count = min(p.group, p.K - k_first);
   const int co0 = coblk * 128, co_cnt = min(128, p.cout - co0);
   const int ci0 = ciblk * p.ci_blk, ci_cnt = min(p.ci_blk, p.cin - ci0);
-  const int64_t tile_begin = (int64_t)chunk * p.tiles_per_chunk;
-  const int64_t tile_end = min(p.n_tiles, tile_begin + p.tiles_per_chunk);
+  // The chunk takes every gridDim.x-th tile: in sorted row order the number of occupied offsets grows
+  // along the rows, so contiguous ranges of tiles would be very unequal pieces of work.
+  const int64_t tile_begin = chunk, tile_end = p.n_tiles, tile_step = gridDim.x;
   const int word = k_first >> 5, shift = k_first & 31;
   const uint32_t group_bits = g_count >= 32 ? 0xFFFFFFFFu : ((1u << g_count) - 1u);
   const int per_line = 128 / p.esize;                       // elements of one 128-byte line
@@ -440,9 +441,9 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
     uint32_t a_phase = 0, b_phase = 0;
     bool ok = true;
     uint32_t m_next = tile_begin < tile_end ? tile_mask(tile_begin) : 0u;
-    for (int64_t tile = tile_begin; tile < tile_end && ok; ++tile) {
+    for (int64_t tile = tile_begin; tile < tile_end && ok; tile += tile_step) {
       uint32_t m = m_next;
-      if (tile + 1 < tile_end) m_next = tile_mask(tile + 1);
+      if (tile + tile_step < tile_end) m_next = tile_mask(tile + tile_step);
       if (!m) continue;
       // ---- the dY tile: rows order[tile * 128 + r]
       {
@@ -524,9 +525,9 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
       const uint32_t idesc = p.idesc_base | ((uint32_t)(p.ci_blk >> 3) << 17);
       const uint64_t desc_hi = smem_desc(0u, kABlockBytes, sbo, layout);
       uint32_t m_next = tile_begin < tile_end ? tile_mask(tile_begin) : 0u;
-      for (int64_t tile = tile_begin; tile < tile_end && ok; ++tile) {
+      for (int64_t tile = tile_begin; tile < tile_end && ok; tile += tile_step) {
         uint32_t m = m_next;
-        if (tile + 1 < tile_end) m_next = tile_mask(tile + 1);
+        if (tile + tile_step < tile_end) m_next = tile_mask(tile + tile_step);
         if (!m) continue;
         ok = mbar_wait(smem_u32(&ctl->a_full[a_slot]), a_phase, abort_flag, 37);
         if (!ok) break;

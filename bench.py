@@ -164,16 +164,21 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    ev0.record()
+    for _ in range(args.steps):
+        step(coords_d, feats_d, dy_d, weight)
+    ev1.record()
+    sync_all()
+    dev_ms = ev0.elapsed_time(ev1)
+    # the per-stage breakdown and the launch count come from a second pass over the same steps with the
+    # stage recorder on (its event pairs cost host time, so it stays out of the timed pass)
     with trace.recording() as rec:
-        sync_all()
-        ev0.record()
         for _ in range(args.steps):
             step(coords_d, feats_d, dy_d, weight)
-        ev1.record()
         sync_all()
         stages = rec.summary()
         launches = rec.total_launches()
-    dev_ms = ev0.elapsed_time(ev1)
 
     # end to end: host buffers in, host results out, through the same public API
     y_h = torch.empty((n_out, COUT), dtype=dtype).pin_memory()
@@ -574,16 +579,20 @@ def run_unet(args, train):
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for _ in range(args.steps):
+        step(coords_d, feats_d)
+    e1.record()
+    sync_all()
+    dev_ms = e0.elapsed_time(e1)
+    # stage breakdown and launch count: a second pass with the stage recorder on (kept out of the timed pass)
     with trace.recording() as rec:
-        sync_all()
-        e0.record()
         for _ in range(args.steps):
             step(coords_d, feats_d)
-        e1.record()
         sync_all()
         stages = rec.summary()
         launches = rec.total_launches()
-    dev_ms = e0.elapsed_time(e1)
 
     result_h = torch.zeros(1, dtype=torch.float32).pin_memory()
 

@@ -224,6 +224,28 @@ int64_t st_conv_wgrad_static_max_bytes(void);
 int st_conv_wgrad_static(int dtype, const void* X, const void* dY, const int32_t* nbr, void* dW, int64_t n_in,
                          int64_t n_out, int K, int cin, int cout, void* stream);
 
+/* ---------------------------------------------------------------- normalisation ---------- */
+
+/* Per-sample batch normalisation of sparse features with an optional fused ReLU, as four streaming
+ * passes.  Replaces sparse_batch_norm, nn/functional/norm.py:20-112 (statistics per (batch index,
+ * channel), biased variance) and the ReLU module that follows it in the reference's networks.
+ * `batch` is the int32 batch index of every row (NULL: a single sample); mean, rstd, shift are
+ * (B, C) fp32, sums is (B, C, 2) fp32 and is cleared by the call, weight / bias (C) may be NULL.
+ *   st_bn_sums            sums[b,c] = ( sum (x - shift), sum (x - shift)^2 ) over the rows of sample b
+ *   st_bn_apply           y = relu?((x - mean) * rstd * weight + bias)
+ *   st_bn_backward_sums   dz = dy * [relu: output > 0];  sums[b,c] = ( sum dz, sum dz * xhat )
+ *   st_bn_backward_apply  dx = rstd * weight * (dz - inv_count[b] * (sums0 + xhat * sums1)) */
+int st_bn_sums(int dtype, const void* X, const int32_t* batch, int64_t n, int C, int B, const float* shift, float* sums,
+               void* stream);
+int st_bn_apply(int dtype, const void* X, const int32_t* batch, int64_t n, int C, int B, const float* mean,
+                const float* rstd, const float* weight, const float* bias, int relu, void* Y, void* stream);
+int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B,
+                        const float* mean, const float* rstd, const float* weight, const float* bias, int relu,
+                        float* sums, void* stream);
+int st_bn_backward_apply(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B,
+                         const float* mean, const float* rstd, const float* weight, const float* bias, int relu,
+                         const float* sums, const float* inv_count, void* dX, void* stream);
+
 /* Hash-on-the-fly forms: no stored map; every tile recomputes
  *   curr = out*lookup_stride - off[k], bounds-checks it against lookup_shape and probes the table.
  * Replace ConvHashOnTheFlyImplicitGEMM forward / backward,

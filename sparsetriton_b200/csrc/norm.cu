@@ -1,0 +1,269 @@
+// Per-sample batch normalisation of sparse features, with the ReLU that follows it folded in.
+//
+// Reference: nn/functional/norm.py:20-112 (statistics per (batch index, channel) over the rows of that
+// sample, biased variance, eps inside the square root) and the ReLU module applied to its output.
+// The layer is pure streaming work over an (N, C) matrix, so it is written as four passes that each
+// read the features once:
+//   forward   sums (twice: mean, then centred second moment) -> normalise + scale + shift (+ ReLU)
+//   backward  the two per-(sample, channel) sums of the gradient -> dX
+// instead of the dozen elementwise launches and one-hot matrix products an op-by-op formulation
+// costs.  Per-(sample, channel) sums are reduced per thread over a strip of rows and then added with
+// one fp32 atomic per strip, sample and channel.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace st {
+
+namespace {
+
+constexpr int kBnThreads = 256;
+constexpr int kBnRowsPerBlock = 512;
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Thread layout of the two reduction kernels: the block's threads form (row lanes) x (channel lanes);
+// a thread walks its channel down a strip of rows and flushes its two sums whenever the sample
+// changes (rows of a sample are contiguous in every tensor the convolutions produce, so normally
+// once or twice per strip).
+struct Lanes {
+  int c_lanes, r_lanes;
+};
+__host__ __device__ inline Lanes lanes_for(int C) {
+  int c = 1;
+  while (c * 2 <= C && c * 2 <= kBnThreads) c *= 2;
+  return Lanes{c, kBnThreads / c};
+}
+
+// sums[(b*C + c)*2 + 0] += sum (x - shift),  [.. + 1] += sum (x - shift)^2      shift (B, C) or null
+template <typename T>
+__global__ void __launch_bounds__(kBnThreads) bn_sums_kernel(const T* __restrict__ x, const int32_t* __restrict__ batch,
+                                                            int64_t n, int C, const float* __restrict__ shift,
+                                                            float* __restrict__ sums) {
+  const Lanes L = lanes_for(C);
+  const int cl = threadIdx.x % L.c_lanes, rl = threadIdx.x / L.c_lanes;
+  const int64_t row0 = (int64_t)blockIdx.x * kBnRowsPerBlock;
+  const int64_t row_end = min(n, row0 + kBnRowsPerBlock);
+  for (int c = cl; c < C; c += L.c_lanes) {
+    float s0 = 0.f, s1 = 0.f, sh = 0.f;
+    int cur = -1;
+    for (int64_t r = row0 + rl; r < row_end; r += L.r_lanes) {
+      const int b = batch ? __ldg(batch + r) : 0;
+      if (b != cur) {
+        if (cur >= 0) {
+          atomicAdd(sums + ((int64_t)cur * C + c) * 2, s0);
+          atomicAdd(sums + ((int64_t)cur * C + c) * 2 + 1, s1);
+        }
+        cur = b;
+        s0 = s1 = 0.f;
+        sh = shift ? __ldg(shift + (int64_t)b * C + c) : 0.f;
+      }
+      const float v = to_f(x[r * C + c]) - sh;
+      s0 += v;
+      s1 += v * v;
+    }
+    if (cur >= 0) {
+      atomicAdd(sums + ((int64_t)cur * C + c) * 2, s0);
+      atomicAdd(sums + ((int64_t)cur * C + c) * 2 + 1, s1);
+    }
+  }
+}
+
+// y = relu?((x - mean) * rstd * w + bias)
+template <typename T>
+__global__ void __launch_bounds__(kBnThreads) bn_apply_kernel(const T* __restrict__ x, const int32_t* __restrict__ batch,
+                                                             int64_t n, int C, const float* __restrict__ mean,
+                                                             const float* __restrict__ rstd, const float* __restrict__ w,
+                                                             const float* __restrict__ bias, int relu, T* __restrict__ y) {
+  const int64_t total = n * C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / C;
+    const int c = (int)(i - r * C);
+    const int b = batch ? __ldg(batch + r) : 0;
+    const int64_t s = (int64_t)b * C + c;
+    float v = (to_f(x[i]) - __ldg(mean + s)) * __ldg(rstd + s);
+    if (w) v *= __ldg(w + c);
+    if (bias) v += __ldg(bias + c);
+    if (relu) v = fmaxf(v, 0.f);
+    y[i] = from_f<T>(v);
+  }
+}
+
+// dz = dy * [z > 0 if relu];  sums[..0] += sum dz,  sums[..1] += sum dz * xhat
+template <typename T>
+__global__ void __launch_bounds__(kBnThreads)
+    bn_bwd_sums_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
+                       const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
+                       const float* __restrict__ bias, int relu, float* __restrict__ sums) {
+  const Lanes L = lanes_for(C);
+  const int cl = threadIdx.x % L.c_lanes, rl = threadIdx.x / L.c_lanes;
+  const int64_t row0 = (int64_t)blockIdx.x * kBnRowsPerBlock;
+  const int64_t row_end = min(n, row0 + kBnRowsPerBlock);
+  for (int c = cl; c < C; c += L.c_lanes) {
+    const float wc = w ? __ldg(w + c) : 1.f, bc = bias ? __ldg(bias + c) : 0.f;
+    float s0 = 0.f, s1 = 0.f, m = 0.f, rs = 0.f;
+    int cur = -1;
+    for (int64_t r = row0 + rl; r < row_end; r += L.r_lanes) {
+      const int b = batch ? __ldg(batch + r) : 0;
+      if (b != cur) {
+        if (cur >= 0) {
+          atomicAdd(sums + ((int64_t)cur * C + c) * 2, s0);
+          atomicAdd(sums + ((int64_t)cur * C + c) * 2 + 1, s1);
+        }
+        cur = b;
+        s0 = s1 = 0.f;
+        m = __ldg(mean + (int64_t)b * C + c);
+        rs = __ldg(rstd + (int64_t)b * C + c);
+      }
+      const float xhat = (to_f(x[r * C + c]) - m) * rs;
+      float dz = to_f(dy[r * C + c]);
+      if (relu && !(xhat * wc + bc > 0.f)) dz = 0.f;
+      s0 += dz;
+      s1 += dz * xhat;
+    }
+    if (cur >= 0) {
+      atomicAdd(sums + ((int64_t)cur * C + c) * 2, s0);
+      atomicAdd(sums + ((int64_t)cur * C + c) * 2 + 1, s1);
+    }
+  }
+}
+
+// dx = rstd * w / n_b * (n_b * dz - sum dz - xhat * sum dz*xhat)
+template <typename T>
+__global__ void __launch_bounds__(kBnThreads)
+    bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
+                        const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
+                        const float* __restrict__ bias, int relu, const float* __restrict__ sums,
+                        const float* __restrict__ inv_count, T* __restrict__ dx) {
+  const int64_t total = n * C;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / C;
+    const int c = (int)(i - r * C);
+    const int b = batch ? __ldg(batch + r) : 0;
+    const int64_t s = (int64_t)b * C + c;
+    const float wc = w ? __ldg(w + c) : 1.f, bc = bias ? __ldg(bias + c) : 0.f;
+    const float rs = __ldg(rstd + s);
+    const float xhat = (to_f(x[i]) - __ldg(mean + s)) * rs;
+    float dz = to_f(dy[i]);
+    if (relu && !(xhat * wc + bc > 0.f)) dz = 0.f;
+    const float ic = __ldg(inv_count + b);
+    const float v = rs * wc * (dz - ic * (__ldg(sums + s * 2) + xhat * __ldg(sums + s * 2 + 1)));
+    dx[i] = from_f<T>(v);
+  }
+}
+
+int check_bn(const char* who, int dtype, int64_t n, int C, int B) {
+  if (dtype != ST_F32 && dtype != ST_F16 && dtype != ST_BF16) {
+    set_error("%s: unsupported feature dtype %d", who, dtype);
+    return ST_ERR_DTYPE;
+  }
+  if (n < 0 || C < 1 || B < 1) {
+    set_error("%s: bad sizes (n=%lld, C=%d, B=%d)", who, (long long)n, C, B);
+    return ST_ERR_ARG;
+  }
+  return ST_OK;
+}
+
+unsigned strip_blocks(int64_t n) { return (unsigned)((n + kBnRowsPerBlock - 1) / kBnRowsPerBlock); }
+unsigned flat_blocks(int64_t total) {
+  int64_t b = (total + kBnThreads * 4 - 1) / (kBnThreads * 4);
+  return (unsigned)(b < 1 ? 1 : (b > 148 * 32 ? 148 * 32 : b));
+}
+
+}  // namespace
+
+}  // namespace st
+
+using namespace st;
+
+#define ST_BN_DISPATCH(dtype, CALL)                                  \
+  do {                                                               \
+    if ((dtype) == ST_F32) { using T = float; CALL; }                \
+    else if ((dtype) == ST_F16) { using T = __half; CALL; }          \
+    else { using T = __nv_bfloat16; CALL; }                          \
+  } while (0)
+
+extern "C" {
+
+int st_bn_sums(int dtype, const void* X, const int32_t* batch, int64_t n, int C, int B, const float* shift, float* sums,
+               void* stream) {
+  int rc = check_bn("st_bn_sums", dtype, n, C, B);
+  if (rc != ST_OK) return rc;
+  if (!sums || (n > 0 && !X)) {
+    set_error("st_bn_sums: null pointer");
+    return ST_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)B * C, s) != cudaSuccess) return check_launch("st_bn_sums");
+  if (n > 0) {
+    ST_BN_DISPATCH(dtype, (bn_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C,
+                                                                                   shift, sums)));
+    note_launches(1);
+  }
+  return check_launch("st_bn_sums");
+}
+
+int st_bn_apply(int dtype, const void* X, const int32_t* batch, int64_t n, int C, int B, const float* mean,
+                const float* rstd, const float* weight, const float* bias, int relu, void* Y, void* stream) {
+  int rc = check_bn("st_bn_apply", dtype, n, C, B);
+  if (rc != ST_OK) return rc;
+  if (n == 0) return ST_OK;
+  if (!X || !Y || !mean || !rstd) {
+    set_error("st_bn_apply: null pointer");
+    return ST_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  ST_BN_DISPATCH(dtype, (bn_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(
+                            static_cast<const T*>(X), batch, n, C, mean, rstd, weight, bias, relu, static_cast<T*>(Y))));
+  note_launches(1);
+  return check_launch("st_bn_apply");
+}
+
+int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B,
+                        const float* mean, const float* rstd, const float* weight, const float* bias, int relu,
+                        float* sums, void* stream) {
+  int rc = check_bn("st_bn_backward_sums", dtype, n, C, B);
+  if (rc != ST_OK) return rc;
+  if (!sums || !mean || !rstd || (n > 0 && (!X || !dY))) {
+    set_error("st_bn_backward_sums: null pointer");
+    return ST_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)B * C, s) != cudaSuccess)
+    return check_launch("st_bn_backward_sums");
+  if (n > 0) {
+    ST_BN_DISPATCH(dtype, (bn_bwd_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(
+                              static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, mean, rstd, weight, bias, relu,
+                              sums)));
+    note_launches(1);
+  }
+  return check_launch("st_bn_backward_sums");
+}
+
+int st_bn_backward_apply(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B,
+                         const float* mean, const float* rstd, const float* weight, const float* bias, int relu,
+                         const float* sums, const float* inv_count, void* dX, void* stream) {
+  int rc = check_bn("st_bn_backward_apply", dtype, n, C, B);
+  if (rc != ST_OK) return rc;
+  if (n == 0) return ST_OK;
+  if (!X || !dY || !dX || !mean || !rstd || !sums || !inv_count) {
+    set_error("st_bn_backward_apply: null pointer");
+    return ST_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  ST_BN_DISPATCH(dtype, (bn_bwd_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(
+                            static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, mean, rstd, weight, bias, relu,
+                            sums, inv_count, static_cast<T*>(dX))));
+  note_launches(1);
+  return check_launch("st_bn_backward_apply");
+}
+
+}  // extern "C"

@@ -28,11 +28,13 @@ class SparseBatchNorm(nn.Module):
             self.register_buffer("running_var", None)
             self.register_buffer("num_batches_tracked", None)
 
-    def forward(self, input: SparseTensor) -> SparseTensor:
+    def forward(self, input: SparseTensor, relu: bool = False) -> SparseTensor:
+        """`relu=True` folds the ReLU that follows the layer into its kernels (no reference counterpart:
+        there the activation is a separate module)."""
         if input.F.shape[1] != self.num_features:
             raise ValueError(f"expected {self.num_features} channels, got {input.F.shape[1]}")
         out = sparse_batch_norm(input, self.weight, self.bias, self.running_mean, self.running_var,
-                                training=self.training, eps=self.eps, momentum=self.momentum)
+                                training=self.training, eps=self.eps, momentum=self.momentum, relu=relu)
         if self.training and self.track_running_stats:
             self.num_batches_tracked += 1
         return out

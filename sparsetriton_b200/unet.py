@@ -86,8 +86,9 @@ class _Block(nn.Module):
         self.act = ReLU()
 
     def forward(self, x):
-        x = self.act(self.bn1(self.conv1(x)))
-        return self.act(self.bn2(self.conv2(x)))
+        # the activation is folded into the normalisation kernels; self.act stays for state_dict / module parity
+        x = self.bn1(self.conv1(x), relu=True)
+        return self.bn2(self.conv2(x), relu=True)
 
 
 class SparseUNet(nn.Module):

@@ -160,6 +160,165 @@ __global__ void __launch_bounds__(kBnThreads)
   }
 }
 
+// ---- 16-byte vector forms (C a multiple of 16 / sizeof(T)): a thread owns V consecutive channels, a
+// warp reads whole 128-byte lines.
+template <typename T> struct Vec { static constexpr int V = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float (&out)[Vec<T>::V]) {
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec<T>::V; ++i) out[i] = to_f(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float (&in)[Vec<T>::V]) {
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec<T>::V; ++i) e[i] = from_f<T>(in[i]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// Reduction kernels: the block's threads form (row lanes) x (C / V channel lanes); MODE 0: sums of
+// (x - shift) and its square; MODE 1: sums of dz and dz * xhat.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kBnThreads)
+    bn_sums_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
+                       const float* __restrict__ p0 /* shift | mean */, const float* __restrict__ rstd,
+                       const float* __restrict__ w, const float* __restrict__ bias, int relu, float* __restrict__ sums) {
+  constexpr int V = Vec<T>::V;
+  const int c_lanes = C / V;                      // <= kBnThreads is checked by the caller
+  const int r_lanes = kBnThreads / c_lanes;
+  const int cl = threadIdx.x % c_lanes, rl = threadIdx.x / c_lanes;
+  const int c0 = cl * V;
+  const int64_t row0 = (int64_t)blockIdx.x * kBnRowsPerBlock;
+  const int64_t row_end = min(n, row0 + kBnRowsPerBlock);
+  float s0[V], s1[V], a[V], b[V], wc[V], bc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    s0[i] = s1[i] = a[i] = 0.f;
+    b[i] = 1.f;
+    wc[i] = (MODE == 1 && w) ? __ldg(w + c0 + i) : 1.f;
+    bc[i] = (MODE == 1 && bias) ? __ldg(bias + c0 + i) : 0.f;
+  }
+  int cur = -1;
+  auto flush = [&]() {
+    if (cur < 0) return;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      atomicAdd(sums + ((int64_t)cur * C + c0 + i) * 2, s0[i]);
+      atomicAdd(sums + ((int64_t)cur * C + c0 + i) * 2 + 1, s1[i]);
+      s0[i] = s1[i] = 0.f;
+    }
+  };
+  // Sums that belong to the sample of the block's first row (normally all of them: rows of a sample are
+  // contiguous) are added up across the row lanes in shared memory first, so that the block issues one
+  // atomic per channel and component instead of one per thread.
+  __shared__ float red[kBnThreads * 2 * V];
+  const int b_common = (batch && row0 < n) ? __ldg(batch + row0) : 0;
+  for (int64_t r = row0 + rl; r < row_end; r += r_lanes) {
+    const int bt = batch ? __ldg(batch + r) : 0;
+    if (bt != cur) {
+      flush();
+      cur = bt;
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        a[i] = p0 ? __ldg(p0 + (int64_t)bt * C + c0 + i) : 0.f;
+        if (MODE == 1) b[i] = __ldg(rstd + (int64_t)bt * C + c0 + i);
+      }
+    }
+    float xv[V];
+    load_vec(x + r * C + c0, xv);
+    if (MODE == 0) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float v = xv[i] - a[i];
+        s0[i] += v;
+        s1[i] += v * v;
+      }
+    } else {
+      float dv[V];
+      load_vec(dy + r * C + c0, dv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float xhat = (xv[i] - a[i]) * b[i];
+        float dz = dv[i];
+        if (relu && !(xhat * wc[i] + bc[i] > 0.f)) dz = 0.f;
+        s0[i] += dz;
+        s1[i] += dz * xhat;
+      }
+    }
+  }
+  if (cur != b_common) flush();                               // leftovers of another sample: added directly
+  float* mine = red + (size_t)threadIdx.x * 2 * V;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    mine[2 * i] = cur == b_common ? s0[i] : 0.f;
+    mine[2 * i + 1] = cur == b_common ? s1[i] : 0.f;
+  }
+  __syncthreads();
+  // thread t < 2*C adds up entry e = t of every row lane:  red[(rl * c_lanes + cl) * 2V + j],  e = cl * 2V + j
+  for (int e = threadIdx.x; e < 2 * C; e += kBnThreads) {
+    float acc = 0.f;
+    for (int q = 0; q < r_lanes; ++q) acc += red[(size_t)q * c_lanes * 2 * V + e];
+    const int c = (e / (2 * V)) * V + (e % (2 * V)) / 2;
+    atomicAdd(sums + ((int64_t)b_common * C + c) * 2 + (e & 1), acc);
+  }
+}
+
+// Elementwise kernels: MODE 0 forward, MODE 1 backward.  One thread per 16-byte vector.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kBnThreads)
+    bn_apply_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
+                        const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
+                        const float* __restrict__ bias, int relu, const float* __restrict__ sums,
+                        const float* __restrict__ inv_count, T* __restrict__ out) {
+  constexpr int V = Vec<T>::V;
+  const int vec_per_row = C / V;
+  const int64_t total = n * vec_per_row;
+  for (int64_t iv = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; iv < total; iv += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = iv / vec_per_row;
+    const int c0 = (int)(iv - r * vec_per_row) * V;
+    const int bt = batch ? __ldg(batch + r) : 0;
+    const int64_t s = (int64_t)bt * C + c0;
+    float xv[V], res[V];
+    load_vec(x + r * C + c0, xv);
+    if (MODE == 0) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float v = (xv[i] - __ldg(mean + s + i)) * __ldg(rstd + s + i);
+        if (w) v *= __ldg(w + c0 + i);
+        if (bias) v += __ldg(bias + c0 + i);
+        if (relu) v = fmaxf(v, 0.f);
+        res[i] = v;
+      }
+    } else {
+      float dv[V];
+      load_vec(dy + r * C + c0, dv);
+      const float ic = __ldg(inv_count + bt);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float wc = w ? __ldg(w + c0 + i) : 1.f, bc = bias ? __ldg(bias + c0 + i) : 0.f;
+        const float rs = __ldg(rstd + s + i);
+        const float xhat = (xv[i] - __ldg(mean + s + i)) * rs;
+        float dz = dv[i];
+        if (relu && !(xhat * wc + bc > 0.f)) dz = 0.f;
+        res[i] = rs * wc * (dz - ic * (__ldg(sums + (s + i) * 2) + xhat * __ldg(sums + (s + i) * 2 + 1)));
+      }
+    }
+    store_vec(out + r * C + c0, res);
+  }
+}
+
+// The vector forms need whole 16-byte vectors per row, aligned rows, and at most kBnThreads channel lanes.
+template <typename T>
+bool vec_ok(int C, const void* a, const void* b, const void* c) {
+  constexpr int V = Vec<T>::V;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return C % V == 0 && C / V <= kBnThreads && kBnThreads % (C / V) == 0 && al(a) && al(b) && al(c);
+}
+
 int check_bn(const char* who, int dtype, int64_t n, int C, int B) {
   if (dtype != ST_F32 && dtype != ST_F16 && dtype != ST_BF16) {
     set_error("%s: unsupported feature dtype %d", who, dtype);
@@ -184,11 +343,11 @@ unsigned flat_blocks(int64_t total) {
 
 using namespace st;
 
-#define ST_BN_DISPATCH(dtype, CALL)                                  \
+#define ST_BN_DISPATCH(dtype, ...)                                   \
   do {                                                               \
-    if ((dtype) == ST_F32) { using T = float; CALL; }                \
-    else if ((dtype) == ST_F16) { using T = __half; CALL; }          \
-    else { using T = __nv_bfloat16; CALL; }                          \
+    if ((dtype) == ST_F32) { using T = float; __VA_ARGS__; }         \
+    else if ((dtype) == ST_F16) { using T = __half; __VA_ARGS__; }   \
+    else { using T = __nv_bfloat16; __VA_ARGS__; }                   \
   } while (0)
 
 extern "C" {
@@ -204,8 +363,13 @@ int st_bn_sums(int dtype, const void* X, const int32_t* batch, int64_t n, int C,
   cudaStream_t s = (cudaStream_t)stream;
   if (cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)B * C, s) != cudaSuccess) return check_launch("st_bn_sums");
   if (n > 0) {
-    ST_BN_DISPATCH(dtype, (bn_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C,
-                                                                                   shift, sums)));
+    ST_BN_DISPATCH(dtype, {
+      if (vec_ok<T>(C, X, nullptr, nullptr))
+        bn_sums_vec_kernel<T, 0><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C, shift,
+                                                                        nullptr, nullptr, nullptr, 0, sums);
+      else
+        bn_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, shift, sums);
+    });
     note_launches(1);
   }
   return check_launch("st_bn_sums");
@@ -221,8 +385,14 @@ int st_bn_apply(int dtype, const void* X, const int32_t* batch, int64_t n, int C
     return ST_ERR_ARG;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  ST_BN_DISPATCH(dtype, (bn_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(
-                            static_cast<const T*>(X), batch, n, C, mean, rstd, weight, bias, relu, static_cast<T*>(Y))));
+  ST_BN_DISPATCH(dtype, {
+    if (vec_ok<T>(C, X, Y, nullptr))
+      bn_apply_vec_kernel<T, 0><<<flat_blocks(n * C / Vec<T>::V), kBnThreads, 0, s>>>(
+          static_cast<const T*>(X), nullptr, batch, n, C, mean, rstd, weight, bias, relu, nullptr, nullptr, static_cast<T*>(Y));
+    else
+      bn_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, mean, rstd, weight,
+                                                                   bias, relu, static_cast<T*>(Y));
+  });
   note_launches(1);
   return check_launch("st_bn_apply");
 }
@@ -240,9 +410,14 @@ int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t*
   if (cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)B * C, s) != cudaSuccess)
     return check_launch("st_bn_backward_sums");
   if (n > 0) {
-    ST_BN_DISPATCH(dtype, (bn_bwd_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(
-                              static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, mean, rstd, weight, bias, relu,
-                              sums)));
+    ST_BN_DISPATCH(dtype, {
+      if (vec_ok<T>(C, X, dY, nullptr))
+        bn_sums_vec_kernel<T, 1><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), static_cast<const T*>(dY),
+                                                                        batch, n, C, mean, rstd, weight, bias, relu, sums);
+      else
+        bn_bwd_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), static_cast<const T*>(dY), batch,
+                                                                     n, C, mean, rstd, weight, bias, relu, sums);
+    });
     note_launches(1);
   }
   return check_launch("st_bn_backward_sums");
@@ -259,9 +434,16 @@ int st_bn_backward_apply(int dtype, const void* X, const void* dY, const int32_t
     return ST_ERR_ARG;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  ST_BN_DISPATCH(dtype, (bn_bwd_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(
-                            static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, mean, rstd, weight, bias, relu,
-                            sums, inv_count, static_cast<T*>(dX))));
+  ST_BN_DISPATCH(dtype, {
+    if (vec_ok<T>(C, X, dY, dX))
+      bn_apply_vec_kernel<T, 1><<<flat_blocks(n * C / Vec<T>::V), kBnThreads, 0, s>>>(
+          static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, mean, rstd, weight, bias, relu, sums, inv_count,
+          static_cast<T*>(dX));
+    else
+      bn_bwd_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(static_cast<const T*>(X), static_cast<const T*>(dY), batch,
+                                                                       n, C, mean, rstd, weight, bias, relu, sums, inv_count,
+                                                                       static_cast<T*>(dX));
+  });
   note_launches(1);
   return check_launch("st_bn_backward_apply");
 }

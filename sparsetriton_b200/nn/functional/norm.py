@@ -9,7 +9,7 @@ accepted: statistics are fp32 and the result is cast back to the feature dtype.
 """
 import torch
 
-from sparsetriton_b200 import _lib
+from sparsetriton_b200 import _lib, trace
 from sparsetriton_b200.tensor import SparseTensor
 
 __all__ = ["sparse_batch_norm"]
@@ -40,7 +40,7 @@ class _BatchNormFn(torch.autograd.Function):
         dev = x.device
         w = weight.detach().float().contiguous() if weight is not None else None
         b = bias.detach().float().contiguous() if bias is not None else None
-        with torch.cuda.device(dev):
+        with torch.cuda.device(dev), trace.stage("bn_fwd"):
             s = _lib.stream_ptr()
             if mean_in is None:
                 sums = torch.empty((n_samples, C, 2), dtype=torch.float32, device=dev)
@@ -73,7 +73,7 @@ class _BatchNormFn(torch.autograd.Function):
         code = _lib.feat_code(x)
         dy = dy.to(x.dtype).contiguous()
         dev = x.device
-        with torch.cuda.device(dev):
+        with torch.cuda.device(dev), trace.stage("bn_bwd"):
             s = _lib.stream_ptr()
             sums = torch.empty((n_samples, C, 2), dtype=torch.float32, device=dev)
             _lib.check(L.st_bn_backward_sums(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(batch), n, C, n_samples,

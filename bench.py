@@ -301,9 +301,10 @@ def roofline(per_stage, n_in, n_out, pairs, pk, dtype):
         # Both ceilings of the product; the one that takes longer at its measured peak is the bound.
         flops = 2.0 * pairs * CIN * COUT
         es = 4 if dtype == torch.float32 else 2
-        gathered = {"conv_fwd": pairs * CIN, "conv_dgrad": pairs * COUT, "conv_wgrad": pairs * CIN}[top]
-        streamed = {"conv_fwd": n_out * COUT, "conv_dgrad": n_in * CIN, "conv_wgrad": n_out * COUT}[top]
-        map_rows = n_in if top == "conv_dgrad" else n_out
+        kind = top.replace("_hashfly", "")
+        gathered = {"conv_fwd": pairs * CIN, "conv_dgrad": pairs * COUT, "conv_wgrad": pairs * CIN}[kind]
+        streamed = {"conv_fwd": n_out * COUT, "conv_dgrad": n_in * CIN, "conv_wgrad": n_out * COUT}[kind]
+        map_rows = n_in if kind == "conv_dgrad" else n_out
         nbytes = (gathered + streamed + K * CIN * COUT) * es + map_rows * K * 4
         tc_peak = pk["bf16_tflops"] * (0.5 if dtype == torch.float32 else 1.0)
         t_tc = flops / (tc_peak * 1e12)
@@ -443,8 +444,11 @@ def run_hash_map(args):
         return res, nbr, nbr2, oc, oc2
 
     res, nbr, nbr2, oc, oc2 = step()
-    pairs = {"k3": int((res[3] >= 0).sum()), "k5": int((res[5] >= 0).sum()), "down": int((nbr >= 0).sum()),
-             "up": int((nbr2 >= 0).sum())}
+    def count_pairs(m, rows=1 << 22):
+        """Valid entries of a map, a few million rows at a time (the transposed map has > 3e9 entries)."""
+        return sum(int((m[i:i + rows] >= 0).sum()) for i in range(0, m.shape[0], rows))
+
+    pairs = {"k3": count_pairs(res[3]), "k5": count_pairs(res[5]), "down": count_pairs(nbr), "up": count_pairs(nbr2)}
     n_down, n_up = oc.shape[0], oc2.shape[0]
     del res, nbr, nbr2, oc, oc2
     for _ in range(args.warmup):

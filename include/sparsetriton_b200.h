@@ -69,6 +69,10 @@ int st_conv_uses_tensor_cores(int dtype, int cin, int cout);
 /* Process-wide switch (default on).  With 0 every product runs on the CUDA-core kernels; used to
  * cross-check the tensor-core kernels and to get exact-fp32 arithmetic for fp32 features. */
 int st_set_tensor_cores(int enable);
+/* Process-wide switch (default on): products over a tile plan use the kernels fed by TMA (tile::gather4);
+ * when off, or when a tensor's base or row pitch is not 16-byte aligned, their cp.async forms run over
+ * the same plan.  Results are identical. */
+int st_set_tma(int enable);
 
 /* ---------------------------------------------------------------- hash table ------------- */
 

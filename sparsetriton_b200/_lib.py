@@ -30,6 +30,7 @@ _SIGNATURES = {
     "st_conv_uses_tensor_cores": ([_INT, _INT, _INT], _INT),
     "st_device_status": ([_PTR, _PTR], _INT),
     "st_set_tensor_cores": ([_INT], _INT),
+    "st_set_tma": ([_INT], _INT),
     "st_hash_clear": ([_PTR, _PTR, _I64, _PTR], _INT),
     "st_hash_build": ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
     "st_hash_query": ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR, _PTR], _INT),

@@ -117,6 +117,11 @@ int st_set_tensor_cores(int enable) {
   return ST_OK;
 }
 
+int st_set_tma(int enable) {
+  tc_set_tma(enable != 0);
+  return ST_OK;
+}
+
 int st_device_status(int32_t* out4, void* stream) {
   if (!out4) {
     set_error("st_device_status: null output");

@@ -1097,6 +1097,11 @@ static bool g_tc_enabled = true;
 
 void tc_set_enabled(bool on) { g_tc_enabled = on; }
 
+// Whether the planned products may use the TMA-fed kernels (else their cp.async forms over the same plan).
+static bool g_tma_enabled = true;
+
+void tc_set_tma(bool on) { g_tma_enabled = on; }
+
 bool tc_supported(int dtype, int c_red, int c_acc) {
   if (!g_tc_enabled) return false;
   if (dtype != ST_F32 && dtype != ST_F16 && dtype != ST_BF16) return false;
@@ -1129,11 +1134,13 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   // accumulators: as many row tiles per W copy as TMEM allows (<= 4); a second set only when it is free
   int sub = 512 / c_acc;
   if (sub > tc::kMaxSub) sub = tc::kMaxSub;
+#ifdef ST_TC_PROFILE
   {
     // experiment: prefer two accumulator sets (epilogue overlaps the next super tile) over sharing W
     const char* e = getenv("ST_TC_ACC2");
     if (e && atoi(e) && sub >= 2 && 2 * sub * c_acc > 512) sub /= 2;
   }
+#endif
   p->acc_bufs = (2 * sub * c_acc <= 512) ? 2 : 1;
   const int64_t n_tiles = (n_rows + tc::kTileM - 1) / tc::kTileM;
   // small problems: do not leave SMs idle for the sake of sharing
@@ -1164,7 +1171,10 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   p->idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p->b_mn_major << 16) | ((uint32_t)(c_acc >> 3) << 17) |
              ((uint32_t)(tc::kTileM >> 4) << 24);
   p->out_kind = dtype;
+  p->dbg = 0;
+#ifdef ST_TC_PROFILE
   {
+    // timing experiments of instrumented builds only (see Params2::dbg)
     const char* e = getenv("ST_TC_DEBUG");
     p->dbg = e ? atoi(e) : 0;
     const char* g = getenv("ST_TC_ASTAGES");
@@ -1175,6 +1185,7 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
       p->n_super = (n_tiles + p->sub - 1) / p->sub;
     }
   }
+#endif
   return true;
 }
 
@@ -1264,10 +1275,12 @@ static int launch_planned(tc::Params2 p, const tc::PlannedRows& map, cudaStream_
   memset(&in_desc, 0, sizeof(in_desc));
   memset(&w_desc, 0, sizeof(w_desc));
   p.part = p.sub;                        // smaller parts (more slots in flight) were measured slower
+#ifdef ST_TC_PROFILE
   {
     const char* e = getenv("ST_TC_PART");
     if (e && atoi(e) >= 1 && atoi(e) <= p.sub) p.part = atoi(e);
   }
+#endif
   int n_slots = 0;
   for (;;) {
     p.slot_bytes = p.w_slot_bytes + p.part * tc::kABlockBytes;
@@ -1279,7 +1292,7 @@ static int launch_planned(tc::Params2 p, const tc::PlannedRows& map, cudaStream_
     ++p.part;
   }
   p.n_slots = n_slots;
-  const bool tma = !getenv("ST_TC_NO_TMA") && n_slots >= 2 && p.n_src > 0 &&
+  const bool tma = g_tma_enabled && n_slots >= 2 && p.n_src > 0 &&
                    make_gather_desc(&in_desc, p.in, p.n_src, p.c_red, p.esize, p.out_kind) &&
                    make_weight_desc(&w_desc, p.w, (int64_t)p.K * p.w_rows, p.w_cols, p.esize, p.out_kind,
                                     p.b_mn_major ? 128 / p.esize : p.w_rows, p.b_mn_major && p.esize == 4);
@@ -1399,10 +1412,12 @@ static bool plan_wgrad(WgradPlan* plan, int dtype, int64_t n_rows, int K, int ci
   p.idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(tc::kTileM >> 4) << 24);
   const int64_t ctas_per_chunk = (int64_t)p.n_kgroups * p.n_coblk * p.n_ciblk;
   int64_t chunks = (2 * sm_count() + ctas_per_chunk - 1) / ctas_per_chunk;
+#ifdef ST_TC_PROFILE
   {
     const char* e = getenv("ST_TC_WCHUNKS");
     if (e && atoi(e) >= 1) chunks = atoi(e);
   }
+#endif
   if (chunks > p.n_tiles) chunks = p.n_tiles;
   if (chunks > 256) chunks = 256;
   if (chunks < 1) chunks = 1;
@@ -1453,14 +1468,16 @@ static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cud
   memset(&x_desc, 0, sizeof(x_desc));
   memset(&dy_desc, 0, sizeof(dy_desc));
   const int dtype = p.esize == 4 ? ST_F32 : ST_BF16;      // element size is all the copy engine needs to know
-  const bool tma = !getenv("ST_TC_NO_TMA") && quad >= 1 && p.n_src > 0 &&
+  const bool tma = g_tma_enabled && quad >= 1 && p.n_src > 0 &&
                    make_gather_desc(&x_desc, p.x, p.n_src, p.cin, p.esize, dtype, p.esize == 4) &&
                    make_gather_desc(&dy_desc, p.dy, p.n_rows, p.cout, p.esize, dtype, p.esize == 4);
   if (!tma) return launch_wgrad(plan, map, stream);
+#ifdef ST_TC_PROFILE
   {
     const char* e = getenv("ST_TC_QUAD");
     if (e && atoi(e) >= 1 && atoi(e) <= quad) quad = atoi(e);
   }
+#endif
   p.quad = quad;
   int slots = budget / (quad * p.b_slot_bytes);
   p.b_slots = slots > 4 ? 4 : slots;

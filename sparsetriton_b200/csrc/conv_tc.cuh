@@ -13,6 +13,8 @@ namespace st {
 bool tc_supported(int dtype, int c_red, int c_acc);
 // Process-wide switch: when off, tc_supported() answers false and the CUDA-core kernels run.
 void tc_set_enabled(bool on);
+// Process-wide switch: when off, products over a tile plan run their cp.async forms instead of the TMA-fed ones.
+void tc_set_tma(bool on);
 
 // OUT[r,:] = sum_k IN[map[r,k],:] . B_k over a stored (n_rows, K) map.
 //   w_transposed = false: B_k = W[k]   with W (K, c_red, c_acc)   (forward)

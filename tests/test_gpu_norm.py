@@ -38,7 +38,7 @@ def _reference(feats, batch_idx, batch_size, weight, bias, running_mean, running
 
 def _rel(a, b):
     a, b = a.double(), b.double()
-    return float((a - b).abs().max() / b.abs().max().clamp(min=1e-30))
+    return float(((a - b).abs().max() / b.abs().max().clamp(min=1e-30)).detach())
 
 
 def _scene(n, C, B, dtype, dev, seed, sorted_batches=True):

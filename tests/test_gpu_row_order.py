@@ -115,7 +115,7 @@ def test_empty_map(cuda_device):
     assert L.st_map_plan(None, 5, 27, 1, None, None, None, None, 0, _lib.stream_ptr()) == -1
 
 
-@pytest.mark.parametrize("form", ["order_only", "plan_natural", "plan_sorted"])
+@pytest.mark.parametrize("form", ["order_only", "plan_natural", "plan_sorted", "plan_sorted_cp_async"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16], ids=["fp32", "bf16", "fp16"])
 @pytest.mark.parametrize("n_rows,n_src,K,cin,cout,patterns", [
     (3000, 2000, 27, 32, 64, 20), (70001, 40000, 27, 64, 128, None), (5000, 5000, 8, 16, 16, None),
@@ -140,7 +140,9 @@ def test_products_with_plan(cuda_device, oracle, dtype, form, n_rows, n_src, K, 
         if form == "order_only":
             fp, ip = (_order(nbr), None, None), (_order(inv), None, None)
         else:
-            fp, ip = _plan(nbr, form == "plan_sorted"), _plan(inv, form == "plan_sorted")
+            fp, ip = _plan(nbr, form != "plan_natural"), _plan(inv, form != "plan_natural")
+        # the cp.async forms of the planned kernels (what runs when TMA cannot describe a tensor)
+        L.st_set_tma(0 if form == "plan_sorted_cp_async" else 1)
         p = _lib.ptr
         fpp, ipp = [p(v) for v in fp], [p(v) for v in ip]
         _lib.check(L.st_conv_fwd(code, p(x), p(w), p(nbr), p(y0), n_src, n_rows, K, cin, cout, None, 0, s), "fwd")
@@ -154,6 +156,7 @@ def test_products_with_plan(cuda_device, oracle, dtype, form, n_rows, n_src, K, 
         _lib.check(L.st_conv_wgrad_planned(code, p(x), p(dy), p(nbr), *fpp, p(dw1), n_src, n_rows, K, cin, cout,
                                            p(ws), ws.numel(), s), "wgrad planned")
         torch.cuda.synchronize()
+        L.st_set_tma(1)
     assert _lib.device_status(dev)[0] == 0
     assert torch.equal(y0, y1)
     assert torch.equal(dx0, dx1)

@@ -250,6 +250,8 @@ def run_ours(args):
         per_stage = {k: {"ms_per_step": v["ms"] / args.steps, "launches_per_step": v["launches"] / args.steps}
                      for k, v in stages.items()}
         roof = roofline(per_stage, n_in, n_out, pairs, pk, dtype)
+        if roof is not None:
+            roof["traffic"], roof["traffic_source"] = ncu_traffic(roof["kernel"], args, algo, n_in)
         h2d = coords_h.numel() * 4 + feats_h.numel() * feats_h.element_size() + dy_h.numel() * dy_h.element_size()
         d2h = (y_h.numel() + dx_h.numel() + dw_h.numel()) * y_h.element_size()
         line = {
@@ -277,6 +279,26 @@ def run_ours(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernels, from the ncu
+# captures summarised under profiles/ (default workload: 4 x 300 k voxels, bf16, stored-map algorithm).
+NCU_TRAFFIC_C3 = {
+    "conv_fwd": (466.4e6 + 187.8e6, "profiles/planned_gather_kernel_c3.md"),
+    "conv_dgrad": (820.9e6 + 143.0e6, "profiles/planned_gather_kernel_c3.md"),
+    "conv_wgrad": (899.5e6 + 43.6e6, "profiles/planned_wgrad_kernel_c3.md"),
+}
+
+
+def ncu_traffic(kernel, args, algo, n_in):
+    """Measured DRAM traffic per launch when this run is the configuration the capture was taken on, scaled
+    by the voxel count of this rank otherwise (traffic of these kernels grows with the rows); None where no
+    capture exists."""
+    from sparsetriton_b200.config import ConvAlgo
+    if kernel not in NCU_TRAFFIC_C3 or algo != ConvAlgo.PrecomputedNeighborGEMM or args.dtype == "fp32":
+        return None, None
+    nbytes, src = NCU_TRAFFIC_C3[kernel]
+    return nbytes * n_in / 1.2e6, src
 
 
 def roofline(per_stage, n_in, n_out, pairs, pk, dtype):

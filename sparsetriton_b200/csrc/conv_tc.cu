@@ -11,6 +11,8 @@
 // Rings are handed over with mbarriers; every wait is bounded: on expiry the kernel records
 // ST_DEV_TIMEOUT in a sticky device word and unwinds.  The same producer code serves a stored
 // neighbour map or the coordinate hash table probed on the fly (the Map template argument).
+// Stored maps that come with a tile plan run on the TMA-fed kernels of conv_tc_plan.cuh; the kernels in
+// this file are their cp.async counterparts (hash on the fly, maps without a plan, unaligned tensors).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 

@@ -460,7 +460,7 @@ def run_hash_map(args):
         for k in (3, 5):
             _, _, ko = build_out_coords(coords, shape, k, 1, 1, (k - 1) // 2, submanifold=True)
             with trace.stage(f"subm_map_k{k}"):
-                res[k] = compute_neighbor_indices(t, coords, ko, shape, 1)
+                res[k] = compute_neighbor_indices(t, coords, ko, shape, 1, queries_are_table_rows=True)
         oc, ns, ko, nbr = out_coords_and_map(coords, shape, 3, 2, 1, 1, False)
         oc2, ns2, ko2, nbr2 = out_coords_and_map(oc, ns, 3, 2, 1, 1, True)
         return res, nbr, nbr2, oc, oc2

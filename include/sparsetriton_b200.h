@@ -134,6 +134,15 @@ int st_map_build(const void* out_coords, int64_t n_out, int coord_dtype, const i
                  int lookup_stride, const int32_t* lookup_shape_host, const int64_t* keys, const int32_t* vals,
                  int64_t capacity, int32_t* nbr, void* stream);
 
+/* The same map for a submanifold layer, where the queried coordinates are the rows the table was built
+ * from (row r has value r, or a larger row with the same coordinate), the stride is 1 and the offsets come
+ * in opposite pairs (off[K-1-k] = -off[k], K odd; checked): only offsets 0..K/2 are probed, the rest follows
+ * from "i is o's neighbour at k  <=>  o is i's neighbour at K-1-k".  Same result as st_map_build, entry for
+ * entry, including duplicate and out-of-grid coordinates. */
+int st_map_build_symmetric(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K,
+                           const int32_t* lookup_shape_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
+                           int32_t* nbr, void* stream);
+
 /* inv[i,k] = o for every nbr[o,k] = i >= 0, -1 elsewhere (inv is (n_in,K) and is fully written).
  * No counterpart in the reference, whose dgrad scatters with atomics
  * (funcs/implicit_precomputed_gemm.py:129-177); this is the map its gather-form dgrad reads. */

@@ -384,6 +384,53 @@ map_build_kernel(const CT* __restrict__ out_coords, int64_t n_flat, int K, Offse
   nbr[t] = r;
 }
 
+// Submanifold map over the table's own coordinates, probing only half of the offsets.  With offsets that
+// come in opposite pairs (off[K-1-k] = -off[k]) and queries that are the table's rows, "i is the
+// neighbour of o at k" means "o is the neighbour of i at K-1-k": a thread probes offset k <= K/2 of its
+// row, stores the hit, and mirrors it with atomicMax (the table's own rule for duplicate coordinates:
+// the largest row wins).  nbr must hold -1 in its upper half.
+template <typename CT>
+__global__ void __launch_bounds__(256)
+map_build_half_kernel(const CT* __restrict__ coords, int64_t n_half, int K, Offsets off, Int3 shape, Table table,
+                      int32_t* __restrict__ nbr) {
+  const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (t >= n_half) return;
+  const int half = K / 2 + 1;
+  const int64_t row = t / half;
+  const int k = (int)(t - row * half);
+  const int4 c = load_coord<CT>(coords, row);
+  const int x = c.y - off.v[k * 3 + 0], y = c.z - off.v[k * 3 + 1], z = c.w - off.v[k * 3 + 2];
+  int32_t r = -1;
+  if (x >= 0 && x < shape.x && y >= 0 && y < shape.y && z >= 0 && z < shape.z && table.capacity != 0 &&
+      key_representable(c.x, x, y, z))
+    r = table_find(table, pack_key(c.x, x, y, z));
+  nbr[row * K + k] = r;
+  if (k == K / 2 || r < 0) return;
+  // the mirrored entry looks this row's own coordinate up, which the probing form bounds-checks
+  if (c.y < 0 || c.y >= shape.x || c.z < 0 || c.z >= shape.y || c.w < 0 || c.w >= shape.z) return;
+  atomicMax(nbr + (int64_t)r * K + (K - 1 - k), (int32_t)row);
+}
+
+// Rows that the table does not return for their own coordinate (smaller duplicates, coordinates outside
+// the grid) are nobody's mirror image: their upper half is probed directly.
+template <typename CT>
+__global__ void __launch_bounds__(256)
+map_build_rest_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, Int3 shape, Table table,
+                      int32_t* __restrict__ nbr) {
+  const int64_t row = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (row >= n) return;
+  if (nbr[row * K + K / 2] == (int32_t)row) return;
+  const int4 c = load_coord<CT>(coords, row);
+  for (int k = K / 2 + 1; k < K; ++k) {
+    const int x = c.y - off.v[k * 3 + 0], y = c.z - off.v[k * 3 + 1], z = c.w - off.v[k * 3 + 2];
+    int32_t r = -1;
+    if (x >= 0 && x < shape.x && y >= 0 && y < shape.y && z >= 0 && z < shape.z && table.capacity != 0 &&
+        key_representable(c.x, x, y, z))
+      r = table_find(table, pack_key(c.x, x, y, z));
+    nbr[row * K + k] = r;
+  }
+}
+
 __global__ void __launch_bounds__(256) fill_i32_kernel(int32_t* p, int64_t n, int32_t v) {
   int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (i < n) p[i] = v;
@@ -624,6 +671,50 @@ int st_map_build(const void* out_coords, int64_t n_out, int coord_dtype, const i
     return ST_ERR_DTYPE;
   }
   return check_launch("st_map_build");
+}
+
+int st_map_build_symmetric(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K,
+                           const int32_t* lookup_shape_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
+                           int32_t* nbr, void* stream) {
+  if (n < 0 || K < 1 || K > ST_MAX_KVOL || (K & 1) == 0 || !offsets_host || !lookup_shape_host || capacity < 0 ||
+      capacity > 0x7FFFFFFFll || (n > 0 && (!coords || !nbr)) || (capacity > 0 && (!keys || !vals))) {
+    set_error("st_map_build_symmetric: bad arguments (K must be odd)");
+    return ST_ERR_ARG;
+  }
+  for (int k = 0; k < K; ++k)
+    for (int a = 0; a < 3; ++a)
+      if (offsets_host[k * 3 + a] != -offsets_host[(K - 1 - k) * 3 + a]) {
+        set_error("st_map_build_symmetric: offsets %d and %d are not opposite", k, K - 1 - k);
+        return ST_ERR_ARG;
+      }
+  Offsets off;
+  if (!pack_offsets(offsets_host, K, &off)) {
+    set_error("st_map_build_symmetric: offset outside int16");
+    return ST_ERR_UNSUPPORTED;
+  }
+  if (coord_dtype != ST_I32 && coord_dtype != ST_I16) {
+    set_error("st_map_build_symmetric: unknown coordinate dtype %d", coord_dtype);
+    return ST_ERR_DTYPE;
+  }
+  if (n == 0) return ST_OK;
+  const Int3 shape = {lookup_shape_host[0], lookup_shape_host[1], lookup_shape_host[2]};
+  const Table t = make_table(keys, vals, capacity);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t n_flat = n * K, n_half = n * (K / 2 + 1);
+  fill_i32_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, s>>>(nbr, n_flat, -1);
+  if (coord_dtype == ST_I32) {
+    map_build_half_kernel<int32_t><<<(unsigned)((n_half + 255) / 256), 256, 0, s>>>(static_cast<const int32_t*>(coords),
+                                                                                   n_half, K, off, shape, t, nbr);
+    map_build_rest_kernel<int32_t><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const int32_t*>(coords), n, K,
+                                                                              off, shape, t, nbr);
+  } else {
+    map_build_half_kernel<int16_t><<<(unsigned)((n_half + 255) / 256), 256, 0, s>>>(static_cast<const int16_t*>(coords),
+                                                                                   n_half, K, off, shape, t, nbr);
+    map_build_rest_kernel<int16_t><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const int16_t*>(coords), n, K,
+                                                                              off, shape, t, nbr);
+  }
+  note_launches(3);
+  return check_launch("st_map_build_symmetric");
 }
 
 int st_map_invert(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, int32_t* inv, void* stream) {

@@ -27,11 +27,14 @@ def compute_neighbor_indices(
     stride: int,
     padding: int = 0,
     dilation: int = 1,
+    queries_are_table_rows: bool = False,
 ) -> torch.Tensor:
     """(N_out, K) int32 map: row of (batch, out*stride - kernel_offsets[k]) in the table, or -1
     when that coordinate is outside [0, spatial_shape) or absent (conv.py:12-75).
 
     `padding` and `dilation` are unused: they are already folded into `kernel_offsets`.
+    `queries_are_table_rows` (no reference counterpart) says that `out_coords` are the very rows the table
+    was built from, as in a submanifold layer; the map is then built from half of the probes.
     One kernel launch; the (N_out*K, 4) candidate rows of the reference are never materialised.
     """
     n_out, K = out_coords.shape[0], kernel_offsets.shape[0]
@@ -48,6 +51,16 @@ def compute_neighbor_indices(
     host = getattr(kernel_offsets, "_st_host", None)
     if host is None:
         host = kernel_offsets.reshape(-1).tolist()
+    # Submanifold layer (the queries are the rows the table was built from, stride 1, odd kernel): offsets
+    # come in opposite pairs, so half of the probes give the whole map (no reference counterpart).
+    if queries_are_table_rows and int(stride) == 1 and K % 2 == 1 and \
+            all(host[i] == -host[3 * (K - 1) - 3 * (i // 3) + i % 3] for i in range(3 * K)):
+        with torch.cuda.device(device), trace.stage("map_build", 3):
+            rc = _lib.lib().st_map_build_symmetric(_lib.ptr(coords), n_out, _lib.coord_code(coords), _lib.host_i32(host),
+                                                   K, _lib.host_i32(int(v) for v in spatial_shape), _lib.ptr(keys),
+                                                   _lib.ptr(vals), keys.shape[0], _lib.ptr(nbr), _lib.stream_ptr())
+        _lib.check(rc, "st_map_build_symmetric")
+        return nbr
     with torch.cuda.device(device), trace.stage("map_build", 1):
         rc = _lib.lib().st_map_build(_lib.ptr(coords), n_out, _lib.coord_code(coords), _lib.host_i32(host), K,
                                      int(stride), _lib.host_i32(int(v) for v in spatial_shape), _lib.ptr(keys),
@@ -144,7 +157,8 @@ def sparse_conv3d(
 
     if algo == ConvAlgo.PrecomputedNeighborGEMM:
         if neighbor_indices is None:
-            neighbor_indices = compute_neighbor_indices(table, out_coords, koff, lookup_shape, lookup_stride, p, d)
+            neighbor_indices = compute_neighbor_indices(table, out_coords, koff, lookup_shape, lookup_stride, p, d,
+                                                        queries_are_table_rows=shortcut and out_coords is coords)
             cache.neighbor_indices[cache_key] = (out_coords, neighbor_indices, new_shape)
         out_feats = ConvPrecomputedNeighborGEMM.apply(feats, weight, neighbor_indices)
     elif algo == ConvAlgo.ImplicitHashFlyGEMM:

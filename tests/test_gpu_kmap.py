@@ -157,3 +157,27 @@ def test_inverse_map(cuda_device):
     o, k = np.nonzero(n >= 0)
     want[n[o, k], k] = o
     assert np.array_equal(inv, want)
+
+
+@pytest.mark.parametrize("k,d", [(3, 1), (3, 2), (5, 1), (1, 1)])
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int16], ids=["i32", "i16"])
+def test_submanifold_map_by_symmetry_equals_full_probing(cuda_device, oracle, k, d, dtype):
+    """st_map_build_symmetric probes half of the offsets and mirrors the hits; the result must equal the
+    fully probed map entry for entry, also for rows with duplicate coordinates (the largest row wins, the
+    smaller ones still get their own entries) and for rows outside the declared grid."""
+    base = synthetic.random_cells(6000, 2, 24, seed=31).numpy()
+    coords = np.concatenate([base, base[:700], base[100:300],
+                             np.array([[0, 30, 3, 3], [1, 3, 40, 3], [0, 23, 23, 24]], np.int32)])
+    shape = (24, 24, 24)
+    set_coords_dtype(dtype)
+    c = torch.as_tensor(coords).to(cuda_device, dtype)
+    p = ((k - 1) * d) // 2
+    table = HashTable(capacity=2 * c.shape[0], device=cuda_device)
+    table.insert(c)
+    oc, _, ko = build_out_coords(c, shape, k, 1, d, p, transposed=False, submanifold=True)
+    assert oc is c
+    full = compute_neighbor_indices(table, c, ko, shape, 1, p, d)
+    half = compute_neighbor_indices(table, c, ko, shape, 1, p, d, queries_are_table_rows=True)
+    assert torch.equal(full, half)
+    want = oracle.kernel_map(coords, shape, k, 1, d, p, False, True)[3]
+    assert np.array_equal(half.cpu().numpy(), want)

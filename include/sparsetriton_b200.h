@@ -138,10 +138,12 @@ int st_map_build(const void* out_coords, int64_t n_out, int coord_dtype, const i
  * from (row r has value r, or a larger row with the same coordinate), the stride is 1 and the offsets come
  * in opposite pairs (off[K-1-k] = -off[k], K odd; checked): only offsets 0..K/2 are probed, the rest follows
  * from "i is o's neighbour at k  <=>  o is i's neighbour at K-1-k".  Same result as st_map_build, entry for
- * entry, including duplicate and out-of-grid coordinates. */
+ * entry, including duplicate and out-of-grid coordinates.  *asymmetric_rows (device int32, may be NULL)
+ * receives the number of rows the table does not return for their own coordinate; when it is 0 the map
+ * is symmetric and st_conv_dgrad_mirrored may be used. */
 int st_map_build_symmetric(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K,
                            const int32_t* lookup_shape_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
-                           int32_t* nbr, void* stream);
+                           int32_t* nbr, int32_t* asymmetric_rows, void* stream);
 
 /* inv[i,k] = o for every nbr[o,k] = i >= 0, -1 elsewhere (inv is (n_in,K) and is fully written).
  * No counterpart in the reference, whose dgrad scatters with atomics
@@ -216,6 +218,16 @@ int st_conv_dgrad_planned(int dtype, const void* dY, const void* W, const int32_
 int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
                           const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K,
                           int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Feature gradient of a submanifold layer over its OWN map (no inverse map, no second plan):
+ *   dX[i,:] = sum_k dY[nbr[i,k],:] . W[K-1-k]^T
+ * Valid when the map is symmetric, nbr[o,k] = i <=> nbr[i,K-1-k] = o: offsets in opposite pairs and every
+ * row returned by the table for its own coordinate (no duplicate or out-of-grid coordinates;
+ * st_map_build_symmetric reports that).  Tensor-core shapes only (ST_ERR_UNSUPPORTED otherwise).
+ * No counterpart in the reference. */
+int st_conv_dgrad_mirrored(int dtype, const void* dY, const void* W, const int32_t* nbr, const int32_t* row_order,
+                           const int32_t* tmap, const uint32_t* tmask, void* dX, int64_t n, int K, int cin, int cout,
+                           void* workspace, int64_t workspace_bytes, void* stream);
 
 /* Weight gradient without any caller-side memory.  No counterpart in the reference: it exists for
  * hosts that may not allocate device memory around the call -- an inference or training plugin whose

@@ -39,7 +39,8 @@ _SIGNATURES = {
     "st_outcoords_write": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _I64, _PTR, _I64, _PTR, _PTR], _INT),
     "st_outcoords_map": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _I64, _PTR], _INT),
     "st_map_build": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
-    "st_map_build_symmetric": ([_PTR, _I64, _INT, _PTR, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
+    "st_map_build_symmetric": ([_PTR, _I64, _INT, _PTR, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _PTR, _PTR], _INT),
+    "st_conv_dgrad_mirrored": ([_INT, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),
     "st_map_invert": ([_PTR, _I64, _INT, _I64, _PTR, _PTR], _INT),
     "st_map_pairs_workspace_bytes": ([_I64, _INT], _I64),
     "st_map_pairs_count": ([_PTR, _I64, _INT, _PTR, _I64, _PTR, _PTR], _INT),

@@ -203,6 +203,26 @@ int st_conv_dgrad(int dtype, const void* dY, const void* W, const int32_t* inv, 
                                stream);
 }
 
+int st_conv_dgrad_mirrored(int dtype, const void* dY, const void* W, const int32_t* nbr, const int32_t* row_order,
+                           const int32_t* tmap, const uint32_t* tmask, void* dX, int64_t n, int K, int cin, int cout,
+                           void* workspace, int64_t workspace_bytes, void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  int rc = check_conv_args("st_conv_dgrad_mirrored", dtype, n, n, K, cin, cout);
+  if (rc != ST_OK) return rc;
+  if (n == 0) return ST_OK;
+  if (!dY || !W || !nbr || !dX) {
+    set_error("st_conv_dgrad_mirrored: null pointer");
+    return ST_ERR_ARG;
+  }
+  if (!tc_supported(dtype, cout, cin)) {
+    set_error("st_conv_dgrad_mirrored: shape outside the tensor-core kernels; use st_conv_dgrad over the inverse map");
+    return ST_ERR_UNSUPPORTED;
+  }
+  return tc_conv_gather(dtype, dY, W, nbr, MapPlan{row_order, tmap, tmask}, dX, n, n, K, cout, cin, /*w_transposed=*/true,
+                        (cudaStream_t)stream, /*w_flip=*/true);
+}
+
 int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
                           const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
                           int64_t workspace_bytes, void* stream) {

@@ -196,6 +196,7 @@ struct Params2 {
   int idx_bytes;           // shared memory for staged map entries (0 with a tile plan)
   int n_slots, slot_bytes; // planned_gather_kernel: ring of slots
   int part;                // planned_gather_kernel: sub tiles per slot
+  int w_flip;              // 1: offset k multiplies with W[K-1-k] (feature gradient of a submanifold layer over its own map)
   int dbg;                 // timing experiments only (wrong results): 1 no proxy fence, 2 no MMA, 4 no row copies, 8 no zero-fill copies
 };
 
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
       ok = acquire(smem_u32(&ctl->w_empty[slot]), parity ^ 1u, 21);
       if (!ok) return;
       const uint32_t w_base = w_ring + (uint32_t)slot * p.w_slot_bytes;
-      const char* wk = static_cast<const char*>(p.w) + (size_t)k * p.w_rows * w_col_bytes;
+      const char* wk = static_cast<const char*>(p.w) + (size_t)(p.w_flip ? p.K - 1 - k : k) * p.w_rows * w_col_bytes;
       if (p.dbg & 16) {
       } else if (p.b_mn_major) {
         const int R = min(kr, p.w_rows - kb * kr);
@@ -1157,6 +1158,7 @@ static bool fill_params2(tc::Params2* p, int dtype, const void* in, const void* 
   p->n_slots = 0;
   p->slot_bytes = 0;
   p->part = 1;
+  p->w_flip = 0;
   const int budget = 222 * 1024 - p->idx_bytes;
   int a_stages = (budget - p->w_slots * p->w_slot_bytes) / tc::kABlockBytes;
   if (a_stages > tc::kMaxAStages) a_stages = tc::kMaxAStages;
@@ -1317,7 +1319,8 @@ static int launch_planned(tc::Params2 p, const tc::PlannedRows& map, cudaStream_
 }
 
 int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, const MapPlan& plan, void* out,
-                   int64_t n_rows, int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream) {
+                   int64_t n_rows, int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream,
+                   bool w_flip) {
   tc::Params2 p;
   const bool planned = plan.tmap && plan.tmask;
   if (!fill_params2(&p, dtype, in, w, out, n_rows, n_src, K, c_red, c_acc, w_transposed, planned)) {
@@ -1326,6 +1329,7 @@ int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map,
   }
   if (n_rows == 0) return ST_OK;
   p.order = plan.order;
+  p.w_flip = w_flip ? 1 : 0;
   if (planned) return launch_planned(p, tc::PlannedRows{plan.tmap, plan.tmask, K, (K + 31) / 32}, stream);
   return launch_gather(p, tc::StoredRows{map, K}, stream);
 }

@@ -30,7 +30,8 @@ struct MapPlan {
   const uint32_t* tmask = nullptr;
 };
 int tc_conv_gather(int dtype, const void* in, const void* w, const int32_t* map, const MapPlan& plan, void* out,
-                   int64_t n_rows, int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream);
+                   int64_t n_rows, int64_t n_src, int K, int c_red, int c_acc, bool w_transposed, cudaStream_t stream,
+                   bool w_flip = false);   // w_flip: offset k multiplies with slice K-1-k
 
 // Arguments of the hash-on-the-fly forms.
 struct HashFlyArgs {

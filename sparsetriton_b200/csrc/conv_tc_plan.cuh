@@ -117,12 +117,13 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
         const uint32_t bytes = (copy_w ? w_bytes : 0u) + (copy_rows ? (uint32_t)kABlockBytes : 0u);
         if (bytes) mbar_arrive_expect_tx(bar, bytes); else mbar_arrive(bar);
         if (copy_w) {
+          const int kw = p.w_flip ? p.K - 1 - d.k : d.k;     // which W slice this offset multiplies with
           if (p.b_mn_major) {
             const int n_cb = (w_col_bytes + 127) >> 7;
             for (int cb = 0; cb < n_cb; ++cb)
-              tma_load_2d(slot_base + (uint32_t)(cb * kr * 128), &w_desc, bar, cb * kr, d.k * p.w_rows + d.kb * kr);
+              tma_load_2d(slot_base + (uint32_t)(cb * kr * 128), &w_desc, bar, cb * kr, kw * p.w_rows + d.kb * kr);
           } else {
-            tma_load_2d(slot_base, &w_desc, bar, d.kb * kr, d.k * p.w_rows);
+            tma_load_2d(slot_base, &w_desc, bar, d.kb * kr, kw * p.w_rows);
           }
         }
       }

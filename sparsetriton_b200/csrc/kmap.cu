@@ -416,10 +416,11 @@ map_build_half_kernel(const CT* __restrict__ coords, int64_t n_half, int K, Offs
 template <typename CT>
 __global__ void __launch_bounds__(256)
 map_build_rest_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, Int3 shape, Table table,
-                      int32_t* __restrict__ nbr) {
+                      int32_t* __restrict__ nbr, int32_t* __restrict__ asymmetric_rows) {
   const int64_t row = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (row >= n) return;
   if (nbr[row * K + K / 2] == (int32_t)row) return;
+  if (asymmetric_rows) atomicAdd(asymmetric_rows, 1);
   const int4 c = load_coord<CT>(coords, row);
   for (int k = K / 2 + 1; k < K; ++k) {
     const int x = c.y - off.v[k * 3 + 0], y = c.z - off.v[k * 3 + 1], z = c.w - off.v[k * 3 + 2];
@@ -675,7 +676,7 @@ int st_map_build(const void* out_coords, int64_t n_out, int coord_dtype, const i
 
 int st_map_build_symmetric(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K,
                            const int32_t* lookup_shape_host, const int64_t* keys, const int32_t* vals, int64_t capacity,
-                           int32_t* nbr, void* stream) {
+                           int32_t* nbr, int32_t* asymmetric_rows, void* stream) {
   if (n < 0 || K < 1 || K > ST_MAX_KVOL || (K & 1) == 0 || !offsets_host || !lookup_shape_host || capacity < 0 ||
       capacity > 0x7FFFFFFFll || (n > 0 && (!coords || !nbr)) || (capacity > 0 && (!keys || !vals))) {
     set_error("st_map_build_symmetric: bad arguments (K must be odd)");
@@ -696,22 +697,23 @@ int st_map_build_symmetric(const void* coords, int64_t n, int coord_dtype, const
     set_error("st_map_build_symmetric: unknown coordinate dtype %d", coord_dtype);
     return ST_ERR_DTYPE;
   }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (asymmetric_rows) cudaMemsetAsync(asymmetric_rows, 0, sizeof(int32_t), s);
   if (n == 0) return ST_OK;
   const Int3 shape = {lookup_shape_host[0], lookup_shape_host[1], lookup_shape_host[2]};
   const Table t = make_table(keys, vals, capacity);
-  cudaStream_t s = (cudaStream_t)stream;
   const int64_t n_flat = n * K, n_half = n * (K / 2 + 1);
   fill_i32_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, s>>>(nbr, n_flat, -1);
   if (coord_dtype == ST_I32) {
     map_build_half_kernel<int32_t><<<(unsigned)((n_half + 255) / 256), 256, 0, s>>>(static_cast<const int32_t*>(coords),
                                                                                    n_half, K, off, shape, t, nbr);
     map_build_rest_kernel<int32_t><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const int32_t*>(coords), n, K,
-                                                                              off, shape, t, nbr);
+                                                                              off, shape, t, nbr, asymmetric_rows);
   } else {
     map_build_half_kernel<int16_t><<<(unsigned)((n_half + 255) / 256), 256, 0, s>>>(static_cast<const int16_t*>(coords),
                                                                                    n_half, K, off, shape, t, nbr);
     map_build_rest_kernel<int16_t><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const int16_t*>(coords), n, K,
-                                                                              off, shape, t, nbr);
+                                                                              off, shape, t, nbr, asymmetric_rows);
   }
   note_launches(3);
   return check_launch("st_map_build_symmetric");

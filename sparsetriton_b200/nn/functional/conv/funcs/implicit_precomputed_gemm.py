@@ -82,6 +82,18 @@ def map_plan(map_tensor):
     return plan
 
 
+def _is_symmetric(map_tensor, n_in):
+    """True for a submanifold map whose builder found every row under its own coordinate
+    (st_map_build_symmetric): then nbr[o,k] = i <=> nbr[i,K-1-k] = o.  One 4-byte read, memoised."""
+    flag = getattr(map_tensor, "_st_asymmetric_rows", None)
+    if flag is None or map_tensor.shape[0] != n_in:
+        return False
+    if not isinstance(flag, bool):
+        flag = int(flag.item()) == 0
+        map_tensor._st_asymmetric_rows = flag
+    return flag
+
+
 class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, features, weights, neighbor_indices):
@@ -129,7 +141,14 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
             stream = _lib.stream_ptr()
             if ctx.needs_input_grad[0]:
                 dx = torch.empty_like(x)
-                if n_in > 0:
+                if n_in > 0 and _is_symmetric(nbr, n_in) and L.st_conv_uses_tensor_cores(code, c_out, c_in):
+                    # submanifold layer: the map is its own inverse with the offsets reversed
+                    plan = map_plan(nbr)
+                    with trace.stage("conv_dgrad", work=ctx.flops):
+                        rc = L.st_conv_dgrad_mirrored(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
+                                                      _lib.ptr(dx), n_in, K, c_in, c_out, None, 0, stream)
+                    _lib.check(rc, "st_conv_dgrad_mirrored")
+                elif n_in > 0:
                     inv = inverse_map(nbr, n_in)
                     plan = map_plan(inv) if L.st_conv_uses_tensor_cores(code, c_out, c_in) else _NO_PLAN
                     with trace.stage("conv_dgrad", work=ctx.flops):

@@ -172,6 +172,13 @@ int64_t st_map_plan_workspace_bytes(int64_t n_rows, int K);
 int st_map_plan(const int32_t* nbr, int64_t n_rows, int K, int sort_rows, int32_t* order, int32_t* tmap,
                 uint32_t* tmask, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* The tile plan of the INVERSE of a map, straight from the forward map: what st_map_invert followed by
+ * st_map_plan(sort_rows = 1) gives (identical arrays), without writing or re-reading the (N_in, K) inverse.
+ * K <= 32.  Used by the feature gradient of strided / transposed layers. */
+int64_t st_map_plan_inverse_workspace_bytes(int64_t n_in, int K);
+int st_map_plan_inverse(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, int32_t* order, int32_t* tmap,
+                        uint32_t* tmask, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Scratch for st_map_pairs_count/_write. */
 int64_t st_map_pairs_workspace_bytes(int64_t n_out, int K);
 /* Number of valid entries of a neighbour map -> *n_pairs (device or pinned-host int64). */
@@ -207,7 +214,8 @@ int st_conv_wgrad(int dtype, const void* X, const void* dY, const int32_t* nbr, 
 /* The three products over a map that comes with a tile plan from st_map_plan() (of the map they are
  * given: the forward map for fwd and wgrad, the inverse map for dgrad).  row_order, tmap and tmask
  * may each be NULL: without tmap/tmask the kernels read `nbr` itself, without row_order they walk
- * the rows in natural order.  Forward and feature-gradient results do not depend on the order; the
+ * the rows in natural order.  st_conv_dgrad_planned also accepts inv = NULL when the plan is given and
+ * st_conv_uses_tensor_cores(dtype, cout, cin) holds (the plan from st_map_plan_inverse).  Forward and feature-gradient results do not depend on the order; the
  * weight gradient adds its rows in that order (still the same from run to run). */
 int st_conv_fwd_planned(int dtype, const void* X, const void* W, const int32_t* nbr, const int32_t* row_order,
                         const int32_t* tmap, const uint32_t* tmask, void* Y, int64_t n_in, int64_t n_out, int K,

@@ -55,6 +55,8 @@ _PLANNED_SIG = ([_INT, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _IN
 for _n in ("st_conv_fwd_planned", "st_conv_dgrad_planned", "st_conv_wgrad_planned"):
     _SIGNATURES[_n] = _PLANNED_SIG
 _SIGNATURES["st_map_plan_workspace_bytes"] = ([_I64, _INT], _I64)
+_SIGNATURES["st_map_plan_inverse_workspace_bytes"] = ([_I64, _INT], _I64)
+_SIGNATURES["st_map_plan_inverse"] = ([_PTR, _I64, _INT, _I64, _PTR, _PTR, _PTR, _PTR, _I64, _PTR], _INT)
 _SIGNATURES["st_map_plan"] = ([_PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _I64, _PTR], _INT)
 _SIGNATURES["st_map_row_order_workspace_bytes"] = ([_I64, _INT], _I64)
 _SIGNATURES["st_map_row_order"] = ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR], _INT)

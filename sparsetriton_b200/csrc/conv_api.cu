@@ -182,12 +182,16 @@ int st_conv_dgrad_planned(int dtype, const void* dY, const void* W, const int32_
   int rc = check_conv_args("st_conv_dgrad", dtype, n_in, n_out, K, cin, cout);
   if (rc != ST_OK) return rc;
   if (n_in == 0) return ST_OK;
-  if (!dY && n_out > 0 || !W || !inv || !dX) {
+  // the inverse map itself may be absent when its plan is given (st_map_plan_inverse) and the tensor-core
+  // kernels take the shape: they read the map only through the plan
+  const bool planned = tmap && tmask;
+  const bool tc = tc_supported(dtype, cout, cin);
+  if (!dY && n_out > 0 || !W || !dX || (!inv && !(planned && tc))) {
     set_error("st_conv_dgrad: null pointer");
     return ST_ERR_ARG;
   }
   cudaStream_t s = (cudaStream_t)stream;
-  if (tc_supported(dtype, cout, cin))
+  if (tc)
     return tc_conv_gather(dtype, dY, W, inv, MapPlan{row_order, tmap, tmask}, dX, n_in, n_out, K, cout, cin, /*w_transposed=*/true, s);
   StoredMap map{inv, K};
   return by_dtype(dtype, [&](auto* tag) {

@@ -235,6 +235,87 @@ int64_t carve(OrderScratch* s, void* ws, int64_t n, int K) {
   return off;
 }
 
+// The radix passes over (keys, row ids) already placed in (s.keys_a, start of the value ping-pong);
+// the sorted row ids land in `order`, the sorted keys in *sorted_keys.
+int passes_for(int K) { return ((K < 32 ? K : 32) + kDigitBitsMax - 1) / kDigitBitsMax; }
+int32_t* first_vals(const OrderScratch& s, int K, int32_t* order) { return passes_for(K) % 2 == 0 ? order : s.vals_b; }
+
+void sort_passes(const OrderScratch& s, int64_t n_rows, int K, int32_t* order, uint32_t** sorted_keys, cudaStream_t st) {
+  const int key_bits = K < 32 ? K : 32;
+  const int passes = passes_for(K);
+  const int bits = (key_bits + passes - 1) / passes;
+  // ping-pong so that the last pass lands in `order`
+  uint32_t* keys_in = s.keys_a;
+  uint32_t* keys_out = s.keys_b;
+  int32_t* vals_in = first_vals(s, K, order);
+  int32_t* vals_out = (passes % 2 == 0) ? s.vals_b : order;
+  const unsigned blocks = (unsigned)((s.n_chunks + kSortWarps - 1) / kSortWarps);
+  for (int pass = 0; pass < passes; ++pass) {
+    const int shift = pass * bits;
+    sort_hist_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, n_rows, shift, bits, s.n_chunks, s.hist);
+    sort_bucket_scan_kernel<<<1u << bits, 256, 0, st>>>(s.hist, s.n_chunks, s.totals);
+    sort_scatter_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, vals_in, n_rows, shift, bits, s.n_chunks, s.hist,
+                                                            s.totals, keys_out, vals_out);
+    note_launches(3);
+    uint32_t* tk = keys_in; keys_in = keys_out; keys_out = tk;
+    int32_t* tv = vals_in; vals_in = vals_out; vals_out = tv;
+  }
+  if (sorted_keys) *sorted_keys = keys_in;
+}
+
+// ---- plan of the INVERSE map straight from the forward map (K <= 32), without writing the inverse ----
+__global__ void __launch_bounds__(256) iota_clear_kernel(uint32_t* keys, int32_t* vals, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i < n) {
+    keys[i] = 0u;
+    vals[i] = (int32_t)i;
+  }
+}
+
+// keys[i] |= 1 << k for every nbr[o,k] = i: the occupancy mask of row i of the inverse map
+__global__ void __launch_bounds__(256)
+inverse_keys_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int64_t n_in, uint32_t* keys) {
+  const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (t >= n_flat) return;
+  const int32_t i = __ldg(nbr + t);
+  if (i >= 0 && i < n_in) atomicOr(keys + i, 1u << (int)(t % K));
+}
+
+__global__ void __launch_bounds__(256) rank_kernel(const int32_t* __restrict__ order, int64_t n, int32_t* rank) {
+  const int64_t p = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (p < n) rank[order[p]] = (int32_t)p;
+}
+
+// tmask[tile] = OR of the tile's 128 sorted keys (K <= 32: one word per tile)
+__global__ void __launch_bounds__(128) tile_mask_kernel(const uint32_t* __restrict__ sorted_keys, int64_t n,
+                                                       uint32_t* __restrict__ tmask) {
+  __shared__ uint32_t part[4];
+  const int64_t p = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  const uint32_t m = __reduce_or_sync(0xFFFFFFFFu, p < n ? sorted_keys[p] : 0u);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) tmask[blockIdx.x] = part[0] | part[1] | part[2] | part[3];
+}
+
+// tmap_inv[(tile(pos) * K + k) * 128 + pos % 128] = o for nbr[o,k] = i, pos = rank[i]; tmap_inv holds -1
+__global__ void __launch_bounds__(256)
+inverse_plan_scatter_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int64_t n_in,
+                            const int32_t* __restrict__ rank, int32_t* __restrict__ tmap) {
+  const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (t >= n_flat) return;
+  const int32_t i = __ldg(nbr + t);
+  if (i < 0 || i >= n_in) return;
+  const int64_t o = t / K;
+  const int k = (int)(t - o * K);
+  const int64_t pos = __ldg(rank + i);
+  tmap[((pos >> 7) * K + k) * 128 + (pos & 127)] = (int32_t)o;
+}
+
+__global__ void __launch_bounds__(256) fill_kernel(int32_t* p, int64_t n, int32_t v) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i < n) p[i] = v;
+}
+
 }  // namespace
 
 }  // namespace st
@@ -261,43 +342,53 @@ int st_map_row_order(const int32_t* nbr, int64_t n_rows, int K, int32_t* order, 
     return ST_ERR_WORKSPACE;
   }
   cudaStream_t st = (cudaStream_t)stream;
-  const int key_bits = K < 32 ? K : 32;
-  const int passes = (key_bits + kDigitBitsMax - 1) / kDigitBitsMax;
-  const int bits = (key_bits + passes - 1) / passes;
-  // ping-pong so that the last pass lands in `order`: values start in `order` when the number of
-  // passes is even, in the scratch copy when it is odd
-  uint32_t* keys_in = s.keys_a;
-  uint32_t* keys_out = s.keys_b;
-  int32_t* vals_in = (passes % 2 == 0) ? order : s.vals_b;
-  int32_t* vals_out = (passes % 2 == 0) ? s.vals_b : order;
   const size_t stage_bytes = K <= 64 ? (size_t)128 * K * 4 : 0;
   {
-    row_keys_kernel<<<(unsigned)((n_rows + 127) / 128), 128, stage_bytes, st>>>(nbr, n_rows, K, keys_in, vals_in);
+    row_keys_kernel<<<(unsigned)((n_rows + 127) / 128), 128, stage_bytes, st>>>(nbr, n_rows, K, s.keys_a,
+                                                                                first_vals(s, K, order));
     note_launches(1);
   }
-  const unsigned blocks = (unsigned)((s.n_chunks + kSortWarps - 1) / kSortWarps);
-  for (int pass = 0; pass < passes; ++pass) {
-    const int shift = pass * bits;
-    {
-      sort_hist_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, n_rows, shift, bits, s.n_chunks, s.hist);
-      note_launches(1);
-    }
-    {
-      sort_bucket_scan_kernel<<<1u << bits, 256, 0, st>>>(s.hist, s.n_chunks, s.totals);
-      note_launches(1);
-    }
-    {
-      sort_scatter_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, vals_in, n_rows, shift, bits, s.n_chunks, s.hist,
-                                                              s.totals, keys_out, vals_out);
-      note_launches(1);
-    }
-    uint32_t* tk = keys_in; keys_in = keys_out; keys_out = tk;
-    int32_t* tv = vals_in; vals_in = vals_out; vals_out = tv;
-  }
+  sort_passes(s, n_rows, K, order, nullptr, st);
   return check_launch("st_map_row_order");
 }
 
 int64_t st_map_plan_workspace_bytes(int64_t n_rows, int K) { return st_map_row_order_workspace_bytes(n_rows, K); }
+
+int64_t st_map_plan_inverse_workspace_bytes(int64_t n_in, int K) {
+  return st_map_row_order_workspace_bytes(n_in, K) + align_up((n_in > 0 ? n_in : 1) * 4, 256);
+}
+
+int st_map_plan_inverse(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, int32_t* order, int32_t* tmap,
+                        uint32_t* tmask, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (n_out < 0 || n_in < 0 || K < 1 || K > 32 || n_in > 0x7FFFFFFFll || (n_out > 0 && !nbr) ||
+      (n_in > 0 && (!order || !tmap || !tmask || !workspace))) {
+    set_error("st_map_plan_inverse: bad arguments (K must be <= 32)");
+    return ST_ERR_ARG;
+  }
+  if (n_in == 0) return ST_OK;
+  OrderScratch s;
+  const int64_t sort_bytes = carve(&s, workspace, n_in, K);
+  if (workspace_bytes < st_map_plan_inverse_workspace_bytes(n_in, K)) {
+    set_error("st_map_plan_inverse: workspace of %lld bytes is too small", (long long)workspace_bytes);
+    return ST_ERR_WORKSPACE;
+  }
+  int32_t* rank = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + sort_bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t n_flat = n_out * K, n_tiles = (n_in + 127) / 128, n_tmap = n_tiles * K * 128;
+  const unsigned rows_grid = (unsigned)((n_in + 255) / 256);
+  iota_clear_kernel<<<rows_grid, 256, 0, st>>>(s.keys_a, first_vals(s, K, order), n_in);
+  if (n_flat > 0) inverse_keys_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, st>>>(nbr, n_flat, K, n_in, s.keys_a);
+  note_launches(2);
+  uint32_t* sorted_keys = nullptr;
+  sort_passes(s, n_in, K, order, &sorted_keys, st);
+  rank_kernel<<<rows_grid, 256, 0, st>>>(order, n_in, rank);
+  tile_mask_kernel<<<(unsigned)n_tiles, 128, 0, st>>>(sorted_keys, n_in, tmask);
+  fill_kernel<<<(unsigned)((n_tmap + 255) / 256), 256, 0, st>>>(tmap, n_tmap, -1);
+  if (n_flat > 0)
+    inverse_plan_scatter_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, st>>>(nbr, n_flat, K, n_in, rank, tmap);
+  note_launches(4);
+  return check_launch("st_map_plan_inverse");
+}
 
 int st_map_plan(const int32_t* nbr, int64_t n_rows, int K, int sort_rows, int32_t* order, int32_t* tmap,
                 uint32_t* tmask, void* workspace, int64_t workspace_bytes, void* stream) {

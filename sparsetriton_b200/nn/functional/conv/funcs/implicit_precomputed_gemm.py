@@ -82,6 +82,33 @@ def map_plan(map_tensor):
     return plan
 
 
+def inverse_plan(neighbor_indices, n_in):
+    """Tile plan of the inverse map built straight from the forward map (st_map_plan_inverse), or None
+    when that form does not apply (more than 32 offsets, row order switched off, small maps).  Memoised
+    on the map tensor."""
+    from sparsetriton_b200.config import get_row_order
+    n_out, K = neighbor_indices.shape
+    if K > 32 or not get_row_order() or n_in < _MIN_ROWS_FOR_ORDER:
+        return None
+    cached = getattr(neighbor_indices, "_st_inverse_plan", None)
+    if cached is not None and cached.order.shape[0] == n_in:
+        return cached
+    L = _lib.lib()
+    dev = neighbor_indices.device
+    n_tiles = (n_in + 127) // 128
+    order = torch.empty((n_in,), dtype=torch.int32, device=dev)
+    tmap = torch.empty((n_tiles * K * 128,), dtype=torch.int32, device=dev)
+    tmask = torch.empty((n_tiles,), dtype=torch.int32, device=dev)
+    ws = _lib.workspace(L.st_map_plan_inverse_workspace_bytes(n_in, K), dev)
+    with torch.cuda.device(dev), trace.stage("map_plan"):
+        rc = L.st_map_plan_inverse(_lib.ptr(neighbor_indices), n_out, K, n_in, _lib.ptr(order), _lib.ptr(tmap),
+                                   _lib.ptr(tmask), _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
+    _lib.check(rc, "st_map_plan_inverse")
+    plan = MapPlan(order, tmap, tmask)
+    neighbor_indices._st_inverse_plan = plan
+    return plan
+
+
 def _is_symmetric(map_tensor, n_in):
     """True for a submanifold map whose builder found every row under its own coordinate
     (st_map_build_symmetric): then nbr[o,k] = i <=> nbr[i,K-1-k] = o.  One 4-byte read, memoised."""
@@ -148,6 +175,13 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
                         rc = L.st_conv_dgrad_mirrored(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
                                                       _lib.ptr(dx), n_in, K, c_in, c_out, None, 0, stream)
                     _lib.check(rc, "st_conv_dgrad_mirrored")
+                elif n_in > 0 and L.st_conv_uses_tensor_cores(code, c_out, c_in) and inverse_plan(nbr, n_in) is not None:
+                    # the kernels read the inverse map only through its plan, which comes straight from nbr
+                    plan = inverse_plan(nbr, n_in)
+                    with trace.stage("conv_dgrad", work=ctx.flops):
+                        rc = L.st_conv_dgrad_planned(code, _lib.ptr(dy), _lib.ptr(w), None, *plan.ptrs(),
+                                                     _lib.ptr(dx), n_in, n_out, K, c_in, c_out, None, 0, stream)
+                    _lib.check(rc, "st_conv_dgrad_planned")
                 elif n_in > 0:
                     inv = inverse_map(nbr, n_in)
                     plan = map_plan(inv) if L.st_conv_uses_tensor_cores(code, c_out, c_in) else _NO_PLAN

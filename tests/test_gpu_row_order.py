@@ -166,3 +166,29 @@ def test_products_with_plan(cuda_device, oracle, dtype, form, n_rows, n_src, K, 
     assert rel_err(t2n(y1), oracle.conv_fwd(xf, wf, m)) < tol
     assert rel_err(t2n(dx1), oracle.conv_dgrad(dyf, wf, m, n_src)) < tol
     assert rel_err(t2n(dw1), oracle.conv_wgrad(xf, dyf, m, K, cin, cout)) < tol
+
+
+@pytest.mark.parametrize("n_rows,n_src,K,density,patterns", [(5000, 4000, 27, 0.25, 20), (70001, 50000, 27, 0.2, None),
+                                                              (3000, 9000, 8, 0.5, None), (900, 700, 1, 0.6, None),
+                                                              (40000, 30000, 32, 0.1, 50)])
+def test_inverse_plan_from_the_forward_map(cuda_device, n_rows, n_src, K, density, patterns):
+    """st_map_plan_inverse must give exactly the arrays of st_map_invert + st_map_plan(sorted)."""
+    dev = cuda_device
+    L = _lib.lib()
+    nbr = _random_map(n_rows, n_src, K, density, 77 + K, dev, patterns)
+    inv = torch.empty((n_src, K), dtype=torch.int32, device=dev)
+    n_tiles = (n_src + 127) // 128
+    order = torch.full((n_src,), -7, dtype=torch.int32, device=dev)
+    tmap = torch.full((n_tiles * K * 128,), -9, dtype=torch.int32, device=dev)
+    tmask = torch.full((n_tiles,), -9, dtype=torch.int32, device=dev)
+    ws = _lib.workspace(L.st_map_plan_inverse_workspace_bytes(n_src, K), dev)
+    with torch.cuda.device(dev):
+        s = _lib.stream_ptr()
+        _lib.check(L.st_map_invert(_lib.ptr(nbr), n_rows, K, n_src, _lib.ptr(inv), s), "st_map_invert")
+        want = _plan(inv, True)
+        _lib.check(L.st_map_plan_inverse(_lib.ptr(nbr), n_rows, K, n_src, _lib.ptr(order), _lib.ptr(tmap), _lib.ptr(tmask),
+                                         _lib.ptr(ws), ws.numel(), s), "st_map_plan_inverse")
+        torch.cuda.synchronize()
+    assert torch.equal(order, want[0])
+    assert torch.equal(tmap, want[1])
+    assert torch.equal(tmask, want[2])

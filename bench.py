@@ -309,6 +309,7 @@ def roofline(per_stage, n_in, n_out, pairs, pk, dtype):
                   (gathered rows + streamed rows + weights) * element size + map rows * 4 K bytes against the
                   copy bandwidth: the ceiling that takes longer is reported as the bound
       map_build   N_out * (16 + 12 K) + 4 * pairs bytes             (coords + key probe + map write + value)
+      map_plan    8 K rows bytes (read the map, write its plan); the inverse plan also reads the forward map
       out_coords  N * (16 + 12 c) + 16 N_out bytes, c = 27/8        (candidates inserted + coords written)
       hash_build  52 N bytes at capacity 2N
     """
@@ -345,6 +346,10 @@ def roofline(per_stage, n_in, n_out, pairs, pk, dtype):
     else:
         if top == "map_build":
             nbytes = n_out * (16 + 12 * K) + 4 * (pairs or 0)
+        elif top in ("map_plan", "map_plan_inverse"):
+            nbytes = 8 * K * (n_out if top == "map_plan" else n_in) + (4 * K * n_out if top == "map_plan_inverse" else 0)
+        elif top == "map_scatter":
+            nbytes = 4 * (pairs or 0) + 4 * n_out * K
         elif top == "out_coords":
             nbytes = n_in * (16 + 12 * K / 8.0) + 16 * n_out
         else:

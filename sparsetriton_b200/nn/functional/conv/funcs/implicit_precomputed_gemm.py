@@ -100,7 +100,7 @@ def inverse_plan(neighbor_indices, n_in):
     tmap = torch.empty((n_tiles * K * 128,), dtype=torch.int32, device=dev)
     tmask = torch.empty((n_tiles,), dtype=torch.int32, device=dev)
     ws = _lib.workspace(L.st_map_plan_inverse_workspace_bytes(n_in, K), dev)
-    with torch.cuda.device(dev), trace.stage("map_plan"):
+    with torch.cuda.device(dev), trace.stage("map_plan_inverse"):
         rc = L.st_map_plan_inverse(_lib.ptr(neighbor_indices), n_out, K, n_in, _lib.ptr(order), _lib.ptr(tmap),
                                    _lib.ptr(tmask), _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
     _lib.check(rc, "st_map_plan_inverse")

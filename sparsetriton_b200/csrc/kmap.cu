@@ -432,11 +432,6 @@ map_build_rest_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets o
   }
 }
 
-__global__ void __launch_bounds__(256) fill_i32_kernel(int32_t* p, int64_t n, int32_t v) {
-  int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (i < n) p[i] = v;
-}
-
 __global__ void __launch_bounds__(256)
 map_invert_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int64_t n_in, int32_t* inv) {
   int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
@@ -622,7 +617,7 @@ int st_outcoords_map(const void* coords, int64_t n, int coord_dtype, const int32
   if (rc != ST_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t n_map = n_out * K;
-  if (n_map > 0) { fill_i32_kernel<<<(unsigned)((n_map + 255) / 256), 256, 0, s>>>(nbr, n_map, -1); note_launches(1); }
+  if (n_map > 0) cudaMemsetAsync(nbr, 0xFF, (size_t)n_map * sizeof(int32_t), s);            // every entry -1
   if (n == 0 || n_out == 0) return check_launch("st_outcoords_map");
   const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
   const Int3 in_shape = {in_shape_host[0], in_shape_host[1], in_shape_host[2]};
@@ -703,7 +698,7 @@ int st_map_build_symmetric(const void* coords, int64_t n, int coord_dtype, const
   const Int3 shape = {lookup_shape_host[0], lookup_shape_host[1], lookup_shape_host[2]};
   const Table t = make_table(keys, vals, capacity);
   const int64_t n_flat = n * K, n_half = n * (K / 2 + 1);
-  fill_i32_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, s>>>(nbr, n_flat, -1);
+  cudaMemsetAsync(nbr, 0xFF, (size_t)n_flat * sizeof(int32_t), s);                             // every entry -1
   if (coord_dtype == ST_I32) {
     map_build_half_kernel<int32_t><<<(unsigned)((n_half + 255) / 256), 256, 0, s>>>(static_cast<const int32_t*>(coords),
                                                                                    n_half, K, off, shape, t, nbr);
@@ -715,7 +710,7 @@ int st_map_build_symmetric(const void* coords, int64_t n, int coord_dtype, const
     map_build_rest_kernel<int16_t><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(static_cast<const int16_t*>(coords), n, K,
                                                                               off, shape, t, nbr, asymmetric_rows);
   }
-  note_launches(3);
+  note_launches(2);
   return check_launch("st_map_build_symmetric");
 }
 
@@ -726,7 +721,7 @@ int st_map_invert(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, int32_
   }
   cudaStream_t s = (cudaStream_t)stream;
   int64_t n_inv = n_in * K;
-  if (n_inv > 0) { fill_i32_kernel<<<(unsigned)((n_inv + 255) / 256), 256, 0, s>>>(inv, n_inv, -1); note_launches(1); }
+  if (n_inv > 0) cudaMemsetAsync(inv, 0xFF, (size_t)n_inv * sizeof(int32_t), s);           // every entry -1
   int64_t n_flat = n_out * K;
   if (n_flat > 0 && n_in > 0)
     { map_invert_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, s>>>(nbr, n_flat, K, n_in, inv); note_launches(1); }

@@ -272,13 +272,25 @@ __global__ void __launch_bounds__(256) iota_clear_kernel(uint32_t* keys, int32_t
   }
 }
 
-// keys[i] |= 1 << k for every nbr[o,k] = i: the occupancy mask of row i of the inverse map
+// keys[i] |= 1 << k for every nbr[o,k] = i: the occupancy mask of row i of the inverse map.
+// Four consecutive entries per thread (one 16-byte load, one division).
 __global__ void __launch_bounds__(256)
 inverse_keys_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int64_t n_in, uint32_t* keys) {
-  const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (t >= n_flat) return;
-  const int32_t i = __ldg(nbr + t);
-  if (i >= 0 && i < n_in) atomicOr(keys + i, 1u << (int)(t % K));
+  const int64_t t0 = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
+  if (t0 >= n_flat) return;
+  int32_t v[4] = {-1, -1, -1, -1};
+  if (t0 + 3 < n_flat && (reinterpret_cast<uintptr_t>(nbr) & 15) == 0) {
+    const int4 q = __ldg(reinterpret_cast<const int4*>(nbr + t0));
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  } else {
+    for (int j = 0; j < 4 && t0 + j < n_flat; ++j) v[j] = __ldg(nbr + t0 + j);
+  }
+  int k = (int)(t0 % K);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (v[j] >= 0 && v[j] < n_in) atomicOr(keys + v[j], 1u << k);
+    if (++k == K) k = 0;
+  }
 }
 
 __global__ void __launch_bounds__(256) rank_kernel(const int32_t* __restrict__ order, int64_t n, int32_t* rank) {
@@ -301,19 +313,28 @@ __global__ void __launch_bounds__(128) tile_mask_kernel(const uint32_t* __restri
 __global__ void __launch_bounds__(256)
 inverse_plan_scatter_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int64_t n_in,
                             const int32_t* __restrict__ rank, int32_t* __restrict__ tmap) {
-  const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (t >= n_flat) return;
-  const int32_t i = __ldg(nbr + t);
-  if (i < 0 || i >= n_in) return;
-  const int64_t o = t / K;
-  const int k = (int)(t - o * K);
-  const int64_t pos = __ldg(rank + i);
-  tmap[((pos >> 7) * K + k) * 128 + (pos & 127)] = (int32_t)o;
-}
-
-__global__ void __launch_bounds__(256) fill_kernel(int32_t* p, int64_t n, int32_t v) {
-  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (i < n) p[i] = v;
+  const int64_t t0 = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;          // four entries per thread
+  if (t0 >= n_flat) return;
+  int32_t v[4] = {-1, -1, -1, -1};
+  if (t0 + 3 < n_flat && (reinterpret_cast<uintptr_t>(nbr) & 15) == 0) {
+    const int4 q = __ldg(reinterpret_cast<const int4*>(nbr + t0));
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  } else {
+    for (int j = 0; j < 4 && t0 + j < n_flat; ++j) v[j] = __ldg(nbr + t0 + j);
+  }
+  int64_t o = t0 / K;
+  int k = (int)(t0 - o * K);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (v[j] >= 0 && v[j] < n_in) {
+      const int64_t pos = __ldg(rank + v[j]);
+      tmap[((pos >> 7) * K + k) * 128 + (pos & 127)] = (int32_t)o;
+    }
+    if (++k == K) {
+      k = 0;
+      ++o;
+    }
+  }
 }
 
 }  // namespace
@@ -377,16 +398,17 @@ int st_map_plan_inverse(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, 
   const int64_t n_flat = n_out * K, n_tiles = (n_in + 127) / 128, n_tmap = n_tiles * K * 128;
   const unsigned rows_grid = (unsigned)((n_in + 255) / 256);
   iota_clear_kernel<<<rows_grid, 256, 0, st>>>(s.keys_a, first_vals(s, K, order), n_in);
-  if (n_flat > 0) inverse_keys_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, st>>>(nbr, n_flat, K, n_in, s.keys_a);
+  if (n_flat > 0)
+    inverse_keys_kernel<<<(unsigned)((n_flat / 4 + 256) / 256), 256, 0, st>>>(nbr, n_flat, K, n_in, s.keys_a);
   note_launches(2);
   uint32_t* sorted_keys = nullptr;
   sort_passes(s, n_in, K, order, &sorted_keys, st);
   rank_kernel<<<rows_grid, 256, 0, st>>>(order, n_in, rank);
   tile_mask_kernel<<<(unsigned)n_tiles, 128, 0, st>>>(sorted_keys, n_in, tmask);
-  fill_kernel<<<(unsigned)((n_tmap + 255) / 256), 256, 0, st>>>(tmap, n_tmap, -1);
+  cudaMemsetAsync(tmap, 0xFF, (size_t)n_tmap * sizeof(int32_t), st);                  // every entry -1
   if (n_flat > 0)
-    inverse_plan_scatter_kernel<<<(unsigned)((n_flat + 255) / 256), 256, 0, st>>>(nbr, n_flat, K, n_in, rank, tmap);
-  note_launches(4);
+    inverse_plan_scatter_kernel<<<(unsigned)((n_flat / 4 + 256) / 256), 256, 0, st>>>(nbr, n_flat, K, n_in, rank, tmap);
+  note_launches(3);
   return check_launch("st_map_plan_inverse");
 }
 

@@ -589,7 +589,8 @@ def run_unet(args, train):
             state["labels"] = torch.randint(0, 20, (out.F.shape[0],), generator=g).to(dev)
             state["scale"] = global_mean_scale(out.F.shape[0], dev)
             state["n_out"] = out.F.shape[0]
-        loss = torch.nn.functional.cross_entropy(out.F, state["labels"], reduction="sum") * state["scale"]
+        # per-row losses summed by a parallel reduction: torch's fused "sum" reduction of nll_loss runs in one block
+        loss = torch.nn.functional.cross_entropy(out.F.float(), state["labels"], reduction="none").sum() * state["scale"]
         bucket.zero()
         loss.backward()
         bucket.all_reduce()

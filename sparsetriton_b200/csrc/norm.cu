@@ -165,8 +165,9 @@ __global__ void __launch_bounds__(kBnThreads)
 template <typename T> struct Vec { static constexpr int V = 16 / sizeof(T); };
 
 template <typename T>
-__device__ __forceinline__ void load_vec(const T* p, float (&out)[Vec<T>::V]) {
-  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+__device__ __forceinline__ uint4 load_raw(const T* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+template <typename T>
+__device__ __forceinline__ void unpack_vec(const uint4& raw, float (&out)[Vec<T>::V]) {
   const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
   for (int i = 0; i < Vec<T>::V; ++i) out[i] = to_f(e[i]);
@@ -180,14 +181,21 @@ __device__ __forceinline__ void store_vec(T* p, const float (&in)[Vec<T>::V]) {
   *reinterpret_cast<uint4*>(p) = raw;
 }
 
-// Reduction kernels: the block's threads form (row lanes) x (C / V channel lanes); MODE 0: sums of
-// (x - shift) and its square; MODE 1: sums of dz and dz * xhat.
+// Both vector kernels give a block a strip of rows and lay its threads out as (row lanes) x (C / V
+// channel lanes), so a thread keeps its V channels for the whole strip and holds the per-(sample,
+// channel) coefficients in registers, reloading them only when the sample changes (rows of a sample
+// are contiguous in every tensor the convolutions produce).  Each pass of the row loop issues the loads
+// of kBnUnroll rows before it uses any of them, which is what keeps enough bytes in flight per SM.
+constexpr int kBnUnroll = 4;
+
+// Reduction kernels.  MODE 0: sums of (x - shift) and its square; MODE 1: sums of dz and dz * xhat.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kBnThreads)
     bn_sums_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
                        const float* __restrict__ p0 /* shift | mean */, const float* __restrict__ rstd,
                        const float* __restrict__ w, const float* __restrict__ bias, int relu, float* __restrict__ sums) {
   constexpr int V = Vec<T>::V;
+  constexpr int U = kBnUnroll;
   const int c_lanes = C / V;                      // <= kBnThreads is checked by the caller
   const int r_lanes = kBnThreads / c_lanes;
   const int cl = threadIdx.x % c_lanes, rl = threadIdx.x / c_lanes;
@@ -212,41 +220,56 @@ __global__ void __launch_bounds__(kBnThreads)
       s0[i] = s1[i] = 0.f;
     }
   };
-  // Sums that belong to the sample of the block's first row (normally all of them: rows of a sample are
-  // contiguous) are added up across the row lanes in shared memory first, so that the block issues one
-  // atomic per channel and component instead of one per thread.
+  // Sums that belong to the sample of the block's first row (normally all of them) are added up across
+  // the row lanes in shared memory first, so that the block issues one atomic per channel and component
+  // instead of one per thread.
   __shared__ float red[kBnThreads * 2 * V];
   const int b_common = (batch && row0 < n) ? __ldg(batch + row0) : 0;
-  for (int64_t r = row0 + rl; r < row_end; r += r_lanes) {
-    const int bt = batch ? __ldg(batch + r) : 0;
-    if (bt != cur) {
-      flush();
-      cur = bt;
+  for (int64_t r = row0 + rl; r < row_end; r += (int64_t)U * r_lanes) {
+    uint4 xr[U], dr[U];
+    int bt[U];
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        a[i] = p0 ? __ldg(p0 + (int64_t)bt * C + c0 + i) : 0.f;
-        if (MODE == 1) b[i] = __ldg(rstd + (int64_t)bt * C + c0 + i);
+    for (int j = 0; j < U; ++j) {
+      const int64_t rr = r + (int64_t)j * r_lanes;
+      bt[j] = -1;
+      if (rr < row_end) {
+        bt[j] = batch ? __ldg(batch + rr) : 0;
+        xr[j] = load_raw(x + rr * C + c0);
+        if (MODE == 1) dr[j] = load_raw(dy + rr * C + c0);
       }
     }
-    float xv[V];
-    load_vec(x + r * C + c0, xv);
-    if (MODE == 0) {
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        const float v = xv[i] - a[i];
-        s0[i] += v;
-        s1[i] += v * v;
+    for (int j = 0; j < U; ++j) {
+      if (r + (int64_t)j * r_lanes >= row_end) break;
+      if (bt[j] != cur) {
+        flush();
+        cur = bt[j];
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          a[i] = p0 ? __ldg(p0 + (int64_t)cur * C + c0 + i) : 0.f;
+          if (MODE == 1) b[i] = __ldg(rstd + (int64_t)cur * C + c0 + i);
+        }
       }
-    } else {
-      float dv[V];
-      load_vec(dy + r * C + c0, dv);
+      float xv[V];
+      unpack_vec<T>(xr[j], xv);
+      if (MODE == 0) {
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        const float xhat = (xv[i] - a[i]) * b[i];
-        float dz = dv[i];
-        if (relu && !(xhat * wc[i] + bc[i] > 0.f)) dz = 0.f;
-        s0[i] += dz;
-        s1[i] += dz * xhat;
+        for (int i = 0; i < V; ++i) {
+          const float v = xv[i] - a[i];
+          s0[i] += v;
+          s1[i] += v * v;
+        }
+      } else {
+        float dv[V];
+        unpack_vec<T>(dr[j], dv);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const float xhat = (xv[i] - a[i]) * b[i];
+          float dz = dv[i];
+          if (relu && !(xhat * wc[i] + bc[i] > 0.f)) dz = 0.f;
+          s0[i] += dz;
+          s1[i] += dz * xhat;
+        }
       }
     }
   }
@@ -267,47 +290,86 @@ __global__ void __launch_bounds__(kBnThreads)
   }
 }
 
-// Elementwise kernels: MODE 0 forward, MODE 1 backward.  One thread per 16-byte vector.
+// Elementwise kernels: MODE 0 forward, MODE 1 backward.  A block covers rows_per_block rows.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kBnThreads)
     bn_apply_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
                         const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
                         const float* __restrict__ bias, int relu, const float* __restrict__ sums,
-                        const float* __restrict__ inv_count, T* __restrict__ out) {
+                        const float* __restrict__ inv_count, T* __restrict__ out, int rows_per_block) {
   constexpr int V = Vec<T>::V;
-  const int vec_per_row = C / V;
-  const int64_t total = n * vec_per_row;
-  for (int64_t iv = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; iv < total; iv += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = iv / vec_per_row;
-    const int c0 = (int)(iv - r * vec_per_row) * V;
-    const int bt = batch ? __ldg(batch + r) : 0;
-    const int64_t s = (int64_t)bt * C + c0;
-    float xv[V], res[V];
-    load_vec(x + r * C + c0, xv);
-    if (MODE == 0) {
+  constexpr int U = kBnUnroll;
+  const int c_lanes = C / V;
+  const int r_lanes = kBnThreads / c_lanes;
+  const int cl = threadIdx.x % c_lanes, rl = threadIdx.x / c_lanes;
+  const int c0 = cl * V;
+  const int64_t row0 = (int64_t)blockIdx.x * rows_per_block;
+  const int64_t row_end = min(n, row0 + rows_per_block);
+  float m[V], rs[V], wc[V], bc[V], q0[V], q1[V];
+  float ic = 0.f;
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        float v = (xv[i] - __ldg(mean + s + i)) * __ldg(rstd + s + i);
-        if (w) v *= __ldg(w + c0 + i);
-        if (bias) v += __ldg(bias + c0 + i);
-        if (relu) v = fmaxf(v, 0.f);
-        res[i] = v;
-      }
-    } else {
-      float dv[V];
-      load_vec(dy + r * C + c0, dv);
-      const float ic = __ldg(inv_count + bt);
+  for (int i = 0; i < V; ++i) {
+    m[i] = q0[i] = q1[i] = 0.f;
+    rs[i] = 1.f;
+    wc[i] = w ? __ldg(w + c0 + i) : 1.f;
+    bc[i] = bias ? __ldg(bias + c0 + i) : 0.f;
+  }
+  int cur = -1;
+  for (int64_t r = row0 + rl; r < row_end; r += (int64_t)U * r_lanes) {
+    uint4 xr[U], dr[U];
+    int bt[U];
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        const float wc = w ? __ldg(w + c0 + i) : 1.f, bc = bias ? __ldg(bias + c0 + i) : 0.f;
-        const float rs = __ldg(rstd + s + i);
-        const float xhat = (xv[i] - __ldg(mean + s + i)) * rs;
-        float dz = dv[i];
-        if (relu && !(xhat * wc + bc > 0.f)) dz = 0.f;
-        res[i] = rs * wc * (dz - ic * (__ldg(sums + (s + i) * 2) + xhat * __ldg(sums + (s + i) * 2 + 1)));
+    for (int j = 0; j < U; ++j) {
+      const int64_t rr = r + (int64_t)j * r_lanes;
+      bt[j] = -1;
+      if (rr < row_end) {
+        bt[j] = batch ? __ldg(batch + rr) : 0;
+        xr[j] = load_raw(x + rr * C + c0);
+        if (MODE == 1) dr[j] = load_raw(dy + rr * C + c0);
       }
     }
-    store_vec(out + r * C + c0, res);
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const int64_t rr = r + (int64_t)j * r_lanes;
+      if (rr >= row_end) break;
+      if (bt[j] != cur) {
+        cur = bt[j];
+        const int64_t s = (int64_t)cur * C + c0;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          m[i] = __ldg(mean + s + i);
+          rs[i] = __ldg(rstd + s + i);
+          if (MODE == 1) {
+            q0[i] = __ldg(sums + (s + i) * 2);
+            q1[i] = __ldg(sums + (s + i) * 2 + 1);
+          }
+        }
+        if (MODE == 1) ic = __ldg(inv_count + cur);
+      }
+      float xv[V], res[V];
+      unpack_vec<T>(xr[j], xv);
+      if (MODE == 0) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float v = (xv[i] - m[i]) * rs[i];
+          if (w) v *= wc[i];
+          if (bias) v += bc[i];
+          if (relu) v = fmaxf(v, 0.f);
+          res[i] = v;
+        }
+      } else {
+        float dv[V];
+        unpack_vec<T>(dr[j], dv);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const float xhat = (xv[i] - m[i]) * rs[i];
+          float dz = dv[i];
+          if (relu && !(xhat * wc[i] + bc[i] > 0.f)) dz = 0.f;
+          res[i] = rs[i] * wc[i] * (dz - ic * (q0[i] + xhat * q1[i]));
+        }
+      }
+      store_vec(out + rr * C + c0, res);
+    }
   }
 }
 
@@ -332,6 +394,9 @@ int check_bn(const char* who, int dtype, int64_t n, int C, int B) {
 }
 
 unsigned strip_blocks(int64_t n) { return (unsigned)((n + kBnRowsPerBlock - 1) / kBnRowsPerBlock); }
+// Rows per block of the vector apply kernels: four passes of the unrolled row loop per thread.
+int apply_rows(int C, int V) { return 4 * kBnUnroll * (kBnThreads / (C / V)); }
+unsigned apply_blocks(int64_t n, int rows) { return (unsigned)((n + rows - 1) / rows); }
 unsigned flat_blocks(int64_t total) {
   int64_t b = (total + kBnThreads * 4 - 1) / (kBnThreads * 4);
   return (unsigned)(b < 1 ? 1 : (b > 148 * 32 ? 148 * 32 : b));
@@ -387,8 +452,12 @@ int st_bn_apply(int dtype, const void* X, const int32_t* batch, int64_t n, int C
   cudaStream_t s = (cudaStream_t)stream;
   ST_BN_DISPATCH(dtype, {
     if (vec_ok<T>(C, X, Y, nullptr))
-      bn_apply_vec_kernel<T, 0><<<flat_blocks(n * C / Vec<T>::V), kBnThreads, 0, s>>>(
-          static_cast<const T*>(X), nullptr, batch, n, C, mean, rstd, weight, bias, relu, nullptr, nullptr, static_cast<T*>(Y));
+    {
+      const int rows = apply_rows(C, Vec<T>::V);
+      bn_apply_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C,
+                                                                             mean, rstd, weight, bias, relu, nullptr,
+                                                                             nullptr, static_cast<T*>(Y), rows);
+    }
     else
       bn_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, mean, rstd, weight,
                                                                    bias, relu, static_cast<T*>(Y));
@@ -436,9 +505,12 @@ int st_bn_backward_apply(int dtype, const void* X, const void* dY, const int32_t
   cudaStream_t s = (cudaStream_t)stream;
   ST_BN_DISPATCH(dtype, {
     if (vec_ok<T>(C, X, dY, dX))
-      bn_apply_vec_kernel<T, 1><<<flat_blocks(n * C / Vec<T>::V), kBnThreads, 0, s>>>(
+    {
+      const int rows = apply_rows(C, Vec<T>::V);
+      bn_apply_vec_kernel<T, 1><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(
           static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, mean, rstd, weight, bias, relu, sums, inv_count,
-          static_cast<T*>(dX));
+          static_cast<T*>(dX), rows);
+    }
     else
       bn_bwd_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(static_cast<const T*>(X), static_cast<const T*>(dY), batch,
                                                                        n, C, mean, rstd, weight, bias, relu, sums, inv_count,

@@ -21,7 +21,13 @@ def _batch_info(tensor: SparseTensor):
     hit = cache.get("batch_info")
     if hit is None or hit[0].shape[0] != tensor.C.shape[0]:
         ids = tensor.C[:, 0].to(torch.int32).contiguous()
-        counts = torch.bincount(ids.long(), minlength=tensor.batch_size).clamp(min=1).to(torch.float32)
+        if tensor.batch_size <= 64:
+            # compare-and-sum: a plain reduction, where bincount's atomics all land on a handful of addresses
+            samples = torch.arange(tensor.batch_size, dtype=torch.int32, device=ids.device)
+            counts = (ids.view(-1, 1) == samples.view(1, -1)).sum(0)
+        else:
+            counts = torch.bincount(ids.long(), minlength=tensor.batch_size)
+        counts = counts.clamp(min=1).to(torch.float32)
         hit = (ids, (1.0 / counts).contiguous())
         cache["batch_info"] = hit
     return hit

@@ -193,15 +193,16 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(kBnThreads)
     bn_sums_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
                        const float* __restrict__ p0 /* shift | mean */, const float* __restrict__ rstd,
-                       const float* __restrict__ w, const float* __restrict__ bias, int relu, float* __restrict__ sums) {
+                       const float* __restrict__ w, const float* __restrict__ bias, int relu, float* __restrict__ sums,
+                       int rows_per_block) {
   constexpr int V = Vec<T>::V;
   constexpr int U = kBnUnroll;
   const int c_lanes = C / V;                      // <= kBnThreads is checked by the caller
   const int r_lanes = kBnThreads / c_lanes;
   const int cl = threadIdx.x % c_lanes, rl = threadIdx.x / c_lanes;
   const int c0 = cl * V;
-  const int64_t row0 = (int64_t)blockIdx.x * kBnRowsPerBlock;
-  const int64_t row_end = min(n, row0 + kBnRowsPerBlock);
+  const int64_t row0 = (int64_t)blockIdx.x * rows_per_block;
+  const int64_t row_end = min(n, row0 + rows_per_block);
   float s0[V], s1[V], a[V], b[V], wc[V], bc[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) {
@@ -273,18 +274,32 @@ __global__ void __launch_bounds__(kBnThreads)
       }
     }
   }
-  if (cur != b_common) flush();                               // leftovers of another sample: added directly
-  float* mine = red + (size_t)threadIdx.x * 2 * V;
+  if (cur != b_common) flush();              // leftovers of another sample: added directly (flush zeroes the sums)
+  // Row lanes that share a warp (fewer than 32 channel lanes) are added up by shuffles; what is left
+  // is one partial per warp, or per row lane when a warp spans a single row.
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int d = c_lanes; d < 32; d <<= 1) {
 #pragma unroll
-  for (int i = 0; i < V; ++i) {
-    mine[2 * i] = cur == b_common ? s0[i] : 0.f;
-    mine[2 * i + 1] = cur == b_common ? s1[i] : 0.f;
+    for (int i = 0; i < V; ++i) {
+      s0[i] += __shfl_xor_sync(0xFFFFFFFFu, s0[i], d);
+      s1[i] += __shfl_xor_sync(0xFFFFFFFFu, s1[i], d);
+    }
+  }
+  const bool warp_shared = c_lanes < 32;
+  const int groups = warp_shared ? kBnThreads / 32 : r_lanes;
+  if (!warp_shared || lane < c_lanes) {
+    float* mine = red + ((size_t)(warp_shared ? warp : rl) * c_lanes + cl) * 2 * V;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      mine[2 * i] = s0[i];
+      mine[2 * i + 1] = s1[i];
+    }
   }
   __syncthreads();
-  // thread t < 2*C adds up entry e = t of every row lane:  red[(rl * c_lanes + cl) * 2V + j],  e = cl * 2V + j
+  // thread t < 2*C adds up entry e = t of every group:  red[(g * c_lanes + cl) * 2V + j],  e = cl * 2V + j
   for (int e = threadIdx.x; e < 2 * C; e += kBnThreads) {
     float acc = 0.f;
-    for (int q = 0; q < r_lanes; ++q) acc += red[(size_t)q * c_lanes * 2 * V + e];
+    for (int q = 0; q < groups; ++q) acc += red[(size_t)q * c_lanes * 2 * V + e];
     const int c = (e / (2 * V)) * V + (e % (2 * V)) / 2;
     atomicAdd(sums + ((int64_t)b_common * C + c) * 2 + (e & 1), acc);
   }
@@ -394,7 +409,7 @@ int check_bn(const char* who, int dtype, int64_t n, int C, int B) {
 }
 
 unsigned strip_blocks(int64_t n) { return (unsigned)((n + kBnRowsPerBlock - 1) / kBnRowsPerBlock); }
-// Rows per block of the vector apply kernels: four passes of the unrolled row loop per thread.
+// Rows per block of the vector kernels: four passes of the unrolled row loop per thread.
 int apply_rows(int C, int V) { return 4 * kBnUnroll * (kBnThreads / (C / V)); }
 unsigned apply_blocks(int64_t n, int rows) { return (unsigned)((n + rows - 1) / rows); }
 unsigned flat_blocks(int64_t total) {
@@ -430,8 +445,11 @@ int st_bn_sums(int dtype, const void* X, const int32_t* batch, int64_t n, int C,
   if (n > 0) {
     ST_BN_DISPATCH(dtype, {
       if (vec_ok<T>(C, X, nullptr, nullptr))
-        bn_sums_vec_kernel<T, 0><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C, shift,
-                                                                        nullptr, nullptr, nullptr, 0, sums);
+      {
+        const int rows = apply_rows(C, Vec<T>::V);
+        bn_sums_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C,
+                                                                              shift, nullptr, nullptr, nullptr, 0, sums, rows);
+      }
       else
         bn_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, shift, sums);
     });
@@ -481,8 +499,12 @@ int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t*
   if (n > 0) {
     ST_BN_DISPATCH(dtype, {
       if (vec_ok<T>(C, X, dY, nullptr))
-        bn_sums_vec_kernel<T, 1><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), static_cast<const T*>(dY),
-                                                                        batch, n, C, mean, rstd, weight, bias, relu, sums);
+      {
+        const int rows = apply_rows(C, Vec<T>::V);
+        bn_sums_vec_kernel<T, 1><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X),
+                                                                              static_cast<const T*>(dY), batch, n, C, mean, rstd,
+                                                                              weight, bias, relu, sums, rows);
+      }
       else
         bn_bwd_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), static_cast<const T*>(dY), batch,
                                                                      n, C, mean, rstd, weight, bias, relu, sums);

@@ -1417,7 +1417,16 @@ static bool plan_wgrad(WgradPlan* plan, int dtype, int64_t n_rows, int K, int ci
   const uint32_t fmt = dtype == ST_F16 ? 0u : (dtype == ST_BF16 ? 1u : 2u);
   p.idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(tc::kTileM >> 4) << 24);
   const int64_t ctas_per_chunk = (int64_t)p.n_kgroups * p.n_coblk * p.n_ciblk;
-  int64_t chunks = (2 * sm_count() + ctas_per_chunk - 1) / ctas_per_chunk;
+  // CTAs per launch.  Two per SM by default; one per SM when a chunk is a single CTA (a second wave would
+  // only add partial sums to write and reduce); four per SM when the offsets are split over more than
+  // four groups (wide input blocks, four offsets per group): with an odd kernel the group that holds the
+  // centre offset then carries about half of all pairs on a small share of the CTAs, and smaller CTAs
+  // are what lets the other SMs share that load.  (With four groups or fewer, two per SM measured best.)
+  int64_t target = 2 * (int64_t)sm_count();
+  if (ctas_per_chunk == 1) target = sm_count();
+  else if (p.n_kgroups > 4) target = 4 * (int64_t)sm_count();
+  int64_t chunks = (target + ctas_per_chunk - 1) / ctas_per_chunk;
+  if (chunks > sm_count()) chunks = sm_count();
 #ifdef ST_TC_PROFILE
   {
     const char* e = getenv("ST_TC_WCHUNKS");

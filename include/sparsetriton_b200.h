@@ -82,7 +82,8 @@ int st_hash_clear(int64_t* keys, int32_t* vals, int64_t capacity, void* stream);
 
 /* Insert n coordinates; value = row index; a repeated coordinate keeps its largest row.
  * Replaces HashTable.insert -> build_hash_table_kernel, sparsetriton/utils/hash.py:516-544, 193-258.
- * status: device int32, ST_DEV_TABLE_FULL is OR-ed in if some key found no slot. */
+ * status: device int32, ST_DEV_TABLE_FULL is OR-ed in if some key found no slot, ST_DEV_BAD_INDEX if a
+ * coordinate has a value outside [0, 65535] (that row is left out of the table). */
 int st_hash_build(const void* coords, int64_t n, int coord_dtype, int64_t* keys, int32_t* vals,
                   int64_t capacity, int32_t* status, void* stream);
 
@@ -248,7 +249,9 @@ int st_conv_dgrad_mirrored(int dtype, const void* dY, const void* W, const int32
  * message naming both sizes; nothing is launched in that case.  The call itself allocates nothing
  * and frees nothing.
  *   - The first call on each GPU looks up the device address of the array (with that GPU current);
- *     make that first call outside of any stream capture.
+ *     make that first call outside of any stream capture.  The address is remembered for the life of
+ *     the process: it does not survive cudaDeviceReset() or the tear-down of the device's primary
+ *     context, after which this entry point must not be called again in the same process.
  *   - All calls on one GPU share the array.  It keeps whatever the last call left in it; each call
  *     overwrites every partial it later reads, so no clearing is needed, but two calls that run on
  *     the GPU at the same time (different streams) would overwrite each other's partials: keep
@@ -267,17 +270,76 @@ int st_conv_wgrad_static(int dtype, const void* X, const void* dY, const int32_t
  *   st_bn_sums            sums[b,c] = ( sum (x - shift), sum (x - shift)^2 ) over the rows of sample b
  *   st_bn_apply           y = relu?((x - mean) * rstd * weight + bias)
  *   st_bn_backward_sums   dz = dy * [relu: output > 0];  sums[b,c] = ( sum dz, sum dz * xhat )
- *   st_bn_backward_apply  dx = rstd * weight * (dz - inv_count[b] * (sums0 + xhat * sums1)) */
+ *   st_bn_backward_apply  dx = rstd * weight * (dz - inv_count[b] * (sums0 + xhat * sums1))
+ * A row whose batch index is not in [0, B) takes part in no sum and gets a zero output row; the (B, C)
+ * arrays are never touched for it and ST_DEV_BAD_INDEX is OR-ed into *status (device int32, may be NULL). */
 int st_bn_sums(int dtype, const void* X, const int32_t* batch, int64_t n, int C, int B, const float* shift, float* sums,
-               void* stream);
+               int32_t* status, void* stream);
 int st_bn_apply(int dtype, const void* X, const int32_t* batch, int64_t n, int C, int B, const float* mean,
-                const float* rstd, const float* weight, const float* bias, int relu, void* Y, void* stream);
+                const float* rstd, const float* weight, const float* bias, int relu, void* Y, int32_t* status, void* stream);
 int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B,
                         const float* mean, const float* rstd, const float* weight, const float* bias, int relu,
-                        float* sums, void* stream);
+                        float* sums, int32_t* status, void* stream);
 int st_bn_backward_apply(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B,
                          const float* mean, const float* rstd, const float* weight, const float* bias, int relu,
-                         const float* sums, const float* inv_count, void* dX, void* stream);
+                         const float* sums, const float* inv_count, void* dX, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------- dense conversion ------- */
+
+/* dense (batch, X, Y, Z, C) <- 0, then dense[b, x, y, z, :] = feats[i, :] for every row i with coordinates
+ * (b, x, y, z).  The call clears the whole volume itself.  Rows outside the volume (batch >= `batch`, a
+ * spatial column outside shape_host) are skipped and ST_DEV_BAD_INDEX is OR-ed into *status (device
+ * int32, may be NULL).  Repeated coordinates: one of the rows stays, which one is unspecified (as in the
+ * reference, whose stores race).
+ * Replaces ToDenseFunction.forward -> _to_dense_fwd_kernel, sparsetriton/utils/to_dense.py:143-203, 30-84. */
+int st_to_dense_fwd(int dtype, const void* feats, const void* coords, int coord_dtype, int64_t n, int C, int batch,
+                    const int32_t* shape_host, void* dense, int32_t* status, void* stream);
+
+/* grad_feats[i, :] = grad_dense[b, x, y, z, :] (zeros for rows outside the volume).
+ * Replaces ToDenseFunction.backward -> _to_dense_bwd_kernel, sparsetriton/utils/to_dense.py:205-240, 87-140. */
+int st_to_dense_bwd(int dtype, const void* grad_dense, const void* coords, int coord_dtype, int64_t n, int C, int batch,
+                    const int32_t* shape_host, void* grad_feats, void* stream);
+
+/* ---------------------------------------------------------------- pooling / upsampling --- */
+
+/* Pooling of a sparse tensor: input voxel `in` belongs to the output cell
+ *     out = floor((in + padding - kernel_size/2) / stride)            (per spatial axis; batch kept)
+ * and the output rows are the distinct cells in ascending (batch, x, y, z) order, each holding the mean
+ * or the maximum of its inputs.  Replaces SparsePoolingFunction, sparsetriton/nn/functional/spatial.py:
+ * 26-262 (cells and their order :123-129, reduction kernel :37-88, backward :175-262).  Differences:
+ * cells are exact (the reference packs them into 16-bit fields and aliases negative cells), the
+ * reduction runs over each row's own segment of a sorted list instead of float atomics (same result
+ * from run to run), and the maximum works (the reference's atomic-max form does not compile).
+ *
+ *   st_pool_count   sort the inputs by cell; *n_out (device or pinned-host int64) <- number of cells.
+ *                   Inputs outside [0, shape_host) or with batch >= `batch` join no cell and raise
+ *                   ST_DEV_BAD_INDEX in *status.
+ *   st_pool_write   (same arguments and workspace, same stream, after _count)
+ *                   out_coords (n_out, 4)  the cells, in the coordinate dtype
+ *                   in_to_out  (n)         output row of every input (-1: none)
+ *                   members    (n)         input rows grouped by output row
+ *                   seg_start  (n_out + 1) members[seg_start[o] .. seg_start[o+1]) are the inputs of row o
+ *   st_pool_fwd     out[o, :] = mean or max (mode_max != 0) over the members of o, fp32 accumulation
+ *   st_pool_bwd     grad_in[i, :] = grad_out[o, :] / count(o)   (mean)
+ *                                 = grad_out[o, :] where feats[i, :] == out[o, :], else 0   (max), o = in_to_out[i] */
+int64_t st_pool_workspace_bytes(int64_t n);
+int st_pool_count(const void* coords, int64_t n, int coord_dtype, int kernel_size, int padding, int stride,
+                  const int32_t* shape_host, int batch, void* workspace, int64_t workspace_bytes, int64_t* n_out,
+                  int32_t* status, void* stream);
+int st_pool_write(const void* coords, int64_t n, int coord_dtype, int kernel_size, int padding, int stride,
+                  const int32_t* shape_host, int batch, void* workspace, int64_t workspace_bytes, void* out_coords,
+                  int64_t n_out, int32_t* in_to_out, int32_t* members, int32_t* seg_start, void* stream);
+int st_pool_fwd(int dtype, const void* feats, int C, const int32_t* members, const int32_t* seg_start, int64_t n_out,
+                int mode_max, void* out, void* stream);
+int st_pool_bwd(int dtype, const void* grad_out, const void* feats, const void* out, int C, const int32_t* in_to_out,
+                const int32_t* seg_start, int64_t n, int mode_max, void* grad_in, void* stream);
+
+/* Nearest-neighbour upsampling: input row i -> output rows i*scale^3 + (dx*scale + dy)*scale + dz with
+ * coordinates in*scale + (dx, dy, dz) and the features of row i; backward sums the scale^3 rows in fp32.
+ * Replaces SparseUpsampleFunction, sparsetriton/nn/functional/spatial.py:294-505 (kernels :305-396, :446-480). */
+int st_upsample_fwd(int dtype, const void* feats, const void* coords, int coord_dtype, int64_t n, int C, int scale,
+                    void* out_feats, void* out_coords, void* stream);
+int st_upsample_bwd(int dtype, const void* grad_out, int64_t n, int C, int scale, void* grad_in, void* stream);
 
 /* Hash-on-the-fly forms: no stored map; every tile recomputes
  *   curr = out*lookup_stride - off[k], bounds-checks it against lookup_shape and probes the table.

@@ -178,3 +178,125 @@ def pairs(nbr):
     """The (in_idx, out_idx, offset) triples of a neighbour map, in (out_idx, offset) order."""
     o, k = np.nonzero(nbr >= 0)
     return np.stack([nbr[o, k], o.astype(np.int32), k.astype(np.int32)], axis=1)
+
+
+# ------------------------------------------------------------------------------------------------
+# Adjacent operators (numpy restatements; same "checker only" rule as above)
+# ------------------------------------------------------------------------------------------------
+def to_dense(feats, coords, shape, batch=None):
+    """utils/to_dense.py:143-203: dense (B, X, Y, Z, C), zeros except dense[b,x,y,z,:] = feats[i,:];
+    B = largest batch index + 1 (:275-278) unless given."""
+    feats = np.asarray(feats)
+    coords = _i32(coords).reshape(-1, 4)
+    if batch is None:
+        batch = int(coords[:, 0].max()) + 1 if coords.shape[0] else 1
+    dense = np.zeros((batch, *[int(v) for v in shape], feats.shape[1]), feats.dtype)
+    dense[coords[:, 0], coords[:, 1], coords[:, 2], coords[:, 3]] = feats
+    return dense
+
+
+def to_dense_bwd(grad_dense, coords):
+    """utils/to_dense.py:205-240: grad_feats[i,:] = grad_dense[b,x,y,z,:]."""
+    coords = _i32(coords).reshape(-1, 4)
+    return np.asarray(grad_dense)[coords[:, 0], coords[:, 1], coords[:, 2], coords[:, 3]]
+
+
+def pool_map(coords, kernel_size, padding, stride):
+    """nn/functional/spatial.py:121-129: cell of every input = floor((in + padding - ks//2) / stride) per
+    spatial axis; output rows = distinct cells in ascending (batch, x, y, z) order.
+    Returns (out_coords int32 (n_out,4), in_to_out int64 (n,))."""
+    coords = _i32(coords).reshape(-1, 4)
+    cells = coords.copy()
+    cells[:, 1:] = np.floor_divide(coords[:, 1:] + padding - kernel_size // 2, stride)
+    if coords.shape[0] == 0:
+        return cells, np.zeros(0, np.int64)
+    uniq, inverse = np.unique(cells, axis=0, return_inverse=True)
+    return uniq.astype(np.int32), inverse.reshape(-1)
+
+
+def pool_new_shape(shape, kernel_size, padding, stride):
+    """nn/functional/spatial.py:116."""
+    return tuple((int(s) - kernel_size + padding * 2) // stride + 1 for s in shape)
+
+
+def pool_fwd(feats, in_to_out, n_out, mode):
+    """nn/functional/spatial.py:37-88 + :156-157: mean ("avg") or maximum ("max") of the inputs of every cell."""
+    feats = np.asarray(feats, np.float64)
+    if mode == "avg":
+        out = np.zeros((n_out, feats.shape[1]))
+        np.add.at(out, in_to_out, feats)
+        return out / np.bincount(in_to_out, minlength=n_out).reshape(-1, 1)
+    out = np.full((n_out, feats.shape[1]), -np.inf)
+    np.maximum.at(out, in_to_out, feats)
+    return out
+
+
+def pool_bwd(grad_out, feats, out, in_to_out, mode):
+    """nn/functional/spatial.py:175-262: avg: grad / count; max: grad where the input equals the maximum."""
+    g = np.asarray(grad_out, np.float64)[in_to_out]
+    if mode == "avg":
+        return g / np.bincount(in_to_out, minlength=np.asarray(grad_out).shape[0])[in_to_out].reshape(-1, 1)
+    return np.where(np.asarray(feats, np.float64) == np.asarray(out, np.float64)[in_to_out], g, 0.0)
+
+
+def upsample(feats, coords, scale):
+    """nn/functional/spatial.py:305-396: row i -> rows i*s^3 + (dx*s + dy)*s + dz at in*s + (dx,dy,dz)."""
+    coords = _i32(coords).reshape(-1, 4)
+    s3 = scale ** 3
+    step = np.arange(s3)
+    d = np.stack([np.zeros(s3, np.int64), step // (scale * scale), (step // scale) % scale, step % scale], axis=1)
+    base = coords.astype(np.int64) * np.array([1, scale, scale, scale])
+    out_coords = (base[:, None, :] + d[None, :, :]).reshape(-1, 4).astype(np.int32)
+    return np.repeat(np.asarray(feats), s3, axis=0), out_coords
+
+
+def upsample_bwd(grad_out, scale):
+    """nn/functional/spatial.py:446-480: sum of the scale^3 output rows of every input row."""
+    g = np.asarray(grad_out, np.float64)
+    return g.reshape(-1, scale ** 3, g.shape[1]).sum(axis=1)
+
+
+def batch_norm(feats, batch_idx, n_samples, weight, bias, eps, relu=False, upstream=None, running=None, momentum=0.1):
+    """nn/functional/norm.py:73-112 in float64: statistics per (sample, channel), biased variance, counts
+    clamped to 1; optional ReLU on top (the reference applies it as a separate module).
+    Returns dict(y, mean, var[, dx, dw, db][, running_mean, running_var])."""
+    x = np.asarray(feats, np.float64)
+    b = np.asarray(batch_idx, np.int64)
+    C = x.shape[1]
+    counts = np.maximum(np.bincount(b, minlength=n_samples), 1).astype(np.float64).reshape(-1, 1)
+    mean = np.zeros((n_samples, C))
+    np.add.at(mean, b, x)
+    mean /= counts
+    var = np.zeros((n_samples, C))
+    np.add.at(var, b, (x - mean[b]) ** 2)
+    var /= counts
+    rstd = 1.0 / np.sqrt(var + eps)
+    xhat = (x - mean[b]) * rstd[b]
+    w = np.ones(C) if weight is None else np.asarray(weight, np.float64)
+    bb = np.zeros(C) if bias is None else np.asarray(bias, np.float64)
+    z = xhat * w + bb
+    res = {"y": np.maximum(z, 0.0) if relu else z, "mean": mean, "var": var}
+    if running is not None:                                      # norm.py:91-94
+        res["running_mean"] = (1 - momentum) * np.asarray(running[0], np.float64) + momentum * mean.mean(0)
+        res["running_var"] = (1 - momentum) * np.asarray(running[1], np.float64) + momentum * var.mean(0)
+    if upstream is not None:
+        dz = np.asarray(upstream, np.float64) * ((z > 0) if relu else 1.0)
+        res["dw"], res["db"] = (dz * xhat).sum(0), dz.sum(0)
+        dxhat = dz * w
+        s0 = np.zeros((n_samples, C))
+        s1 = np.zeros((n_samples, C))
+        np.add.at(s0, b, dxhat)
+        np.add.at(s1, b, dxhat * xhat)
+        res["dx"] = rstd[b] * (dxhat - (s0[b] + xhat * s1[b]) / counts[b])
+    return res
+
+
+def batch_norm_eval(feats, running_mean, running_var, weight, bias, eps):
+    """nn/functional/norm.py:95-110, inference form."""
+    x = np.asarray(feats, np.float64)
+    y = (x - np.asarray(running_mean, np.float64)) / np.sqrt(np.asarray(running_var, np.float64) + eps)
+    if weight is not None:
+        y = y * np.asarray(weight, np.float64)
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64)
+    return y

@@ -60,14 +60,24 @@ _SIGNATURES["st_map_plan_inverse"] = ([_PTR, _I64, _INT, _I64, _PTR, _PTR, _PTR,
 _SIGNATURES["st_map_plan"] = ([_PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _I64, _PTR], _INT)
 _SIGNATURES["st_map_row_order_workspace_bytes"] = ([_I64, _INT], _I64)
 _SIGNATURES["st_map_row_order"] = ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR], _INT)
-_SIGNATURES["st_bn_sums"] = ([_INT, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR], _INT)
-_SIGNATURES["st_bn_apply"] = ([_INT, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _INT, _PTR, _PTR], _INT)
-_SIGNATURES["st_bn_backward_sums"] = ([_INT, _PTR, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _INT, _PTR, _PTR],
-                                      _INT)
+_SIGNATURES["st_bn_sums"] = ([_INT, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR], _INT)
+_SIGNATURES["st_bn_apply"] = ([_INT, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _INT, _PTR, _PTR, _PTR], _INT)
+_SIGNATURES["st_bn_backward_sums"] = ([_INT, _PTR, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _INT, _PTR, _PTR,
+                                       _PTR], _INT)
 _SIGNATURES["st_bn_backward_apply"] = ([_INT, _PTR, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _INT, _PTR, _PTR,
-                                        _PTR, _PTR], _INT)
+                                        _PTR, _PTR, _PTR], _INT)
 _SIGNATURES["st_conv_wgrad_static_max_bytes"] = ([], _I64)
 _SIGNATURES["st_conv_wgrad_static"] = ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR], _INT)
+_SIGNATURES["st_to_dense_fwd"] = ([_INT, _PTR, _PTR, _INT, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR], _INT)
+_SIGNATURES["st_to_dense_bwd"] = ([_INT, _PTR, _PTR, _INT, _I64, _INT, _INT, _PTR, _PTR, _PTR], _INT)
+_SIGNATURES["st_pool_workspace_bytes"] = ([_I64], _I64)
+_SIGNATURES["st_pool_count"] = ([_PTR, _I64, _INT, _INT, _INT, _INT, _PTR, _INT, _PTR, _I64, _PTR, _PTR, _PTR], _INT)
+_SIGNATURES["st_pool_write"] = ([_PTR, _I64, _INT, _INT, _INT, _INT, _PTR, _INT, _PTR, _I64, _PTR, _I64, _PTR, _PTR, _PTR,
+                                 _PTR], _INT)
+_SIGNATURES["st_pool_fwd"] = ([_INT, _PTR, _INT, _PTR, _PTR, _I64, _INT, _PTR, _PTR], _INT)
+_SIGNATURES["st_pool_bwd"] = ([_INT, _PTR, _PTR, _PTR, _INT, _PTR, _PTR, _I64, _INT, _PTR, _PTR], _INT)
+_SIGNATURES["st_upsample_fwd"] = ([_INT, _PTR, _PTR, _INT, _I64, _INT, _INT, _PTR, _PTR, _PTR], _INT)
+_SIGNATURES["st_upsample_bwd"] = ([_INT, _PTR, _I64, _INT, _INT, _PTR, _PTR], _INT)
 _HASHFLY_SIG = ([_INT, _PTR, _PTR, _PTR, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _INT, _PTR, _I64, _I64, _INT, _INT, _INT,
                  _PTR, _I64, _PTR], _INT)
 for _n in ("st_conv_fwd_hashfly", "st_conv_dgrad_hashfly", "st_conv_wgrad_hashfly"):

@@ -70,7 +70,11 @@ int st_conv_wgrad_static(int dtype, const void* X, const void* dY, const int32_t
   cudaStream_t s = (cudaStream_t)stream;
   const int64_t n_w = (int64_t)K * cin * cout;
   if (n_out == 0) {
-    cudaMemsetAsync(dW, 0, (size_t)n_w * (dtype == ST_F32 ? 4 : 2), s);
+    const cudaError_t e = cudaMemsetAsync(dW, 0, (size_t)n_w * (dtype == ST_F32 ? 4 : 2), s);
+    if (e != cudaSuccess) {
+      set_error("st_conv_wgrad_static(empty): %s", cudaGetErrorString(e));
+      return ST_ERR_CUDA;
+    }
     return check_launch("st_conv_wgrad_static(empty)");
   }
   // Which kernel would run, and how many partial bytes it writes.

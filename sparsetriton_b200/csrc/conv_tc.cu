@@ -168,8 +168,10 @@ struct InverseRows {
 __device__ long long g_prof[160 * 16];
 #ifdef ST_TC_PROFILE
 #define PROF_CLOCK() clock64()
+#define ST_DBG(p, bit) ((p).dbg & (bit))
 #else
 #define PROF_CLOCK() 0ll
+#define ST_DBG(p, bit) 0          // the experiment switches of Params2::dbg exist in instrumented builds only
 #endif
 
 
@@ -304,7 +306,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
       if (!ok) return;
       const uint32_t w_base = w_ring + (uint32_t)slot * p.w_slot_bytes;
       const char* wk = static_cast<const char*>(p.w) + (size_t)(p.w_flip ? p.K - 1 - k : k) * p.w_rows * w_col_bytes;
-      if (p.dbg & 16) {
+      if (ST_DBG(p, 16)) {
       } else if (p.b_mn_major) {
         const int R = min(kr, p.w_rows - kb * kr);
         const int n_cb = (w_col_bytes + 127) >> 7;
@@ -359,7 +361,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
       if (!(flags & 32u)) {
         valid_bytes = min(128, red_bytes - kb * 128);
         const int c = t & 7, g = t >> 3;
-        if (c < (valid_bytes >> 4) && !(p.dbg & 4)) {
+        if (c < (valid_bytes >> 4) && !ST_DBG(p, 4)) {
           int32_t r[8];
           if (idx_line) {
             const int4 lo = *reinterpret_cast<const int4*>(idx_line + g * 8);
@@ -424,7 +426,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
         int valid_bytes = 0;
         if (!(d.flags & 32u)) {
           valid_bytes = min(128, red_bytes - d.kb * 128);
-          if (piece < (valid_bytes >> 4) && !(p.dbg & 4)) {
+          if (piece < (valid_bytes >> 4) && !ST_DBG(p, 4)) {
             const int32_t r[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
             const char* src0 = static_cast<const char*>(p.in) + d.kb * 128 + piece * 16;
             const uint32_t dst0 = a_ring + (uint32_t)d.slot * kABlockBytes + (uint32_t)(line8 * 128);
@@ -559,7 +561,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
           for (int s = 0; s < kMaxSub; ++s) {
   #pragma unroll
             for (int j = 0; j < kGroup; ++j)
-              got[s][j] = (row_ok[s] && j < kn && !(p.dbg & 32)) ? map.get(rs[s], arow[s], k0 + j) : -1;
+              got[s][j] = (row_ok[s] && j < kn && !ST_DBG(p, 32)) ? map.get(rs[s], arow[s], k0 + j) : -1;
           }
           // every stage of the previous group has been issued by every producer thread: the tile can be rewritten
           producer_sync();
@@ -626,7 +628,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
       }
     }
     queue.flush(lane);
-    if ((p.dbg & 256) && t == 0 && group == 0) {
+    if (ST_DBG(p, 256) && t == 0 && group == 0) {
       long long* o = g_prof + (size_t)blockIdx.x * 16;
       o[0] = PROF_CLOCK() - t_total0; o[1] = t_pref; o[2] = t_acq_a; o[3] = t_acq_w; o[4] = n_flush; o[5] = t_push; o[6] = t_copy; o[7] = t_w; o[15] = t_idx;
     }
@@ -669,7 +671,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
           }
           tc_fence_after();
           const long long ci0 = PROF_CLOCK();
-          const int ksteps = (p.dbg & 2) ? 0 : (int)(info >> 8);
+          const int ksteps = ST_DBG(p, 2) ? 0 : (int)(info >> 8);
           const uint32_t a_lo = (a_ring + (uint32_t)a_stage * kABlockBytes) >> 4;
           const uint32_t d_addr = tmem_base + (uint32_t)(buf * set_cols + (int)(info & 3u) * p.c_acc);
           const uint32_t fresh = (info & 4u) ? 0u : 1u;          // 0: the first MMA overwrites the accumulator
@@ -685,14 +687,14 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
             }
           }
           const long long ci1 = PROF_CLOCK();
-          if (p.dbg & 512) mbar_arrive(smem_u32(&ctl->a_empty[a_stage])); else
+          if (ST_DBG(p, 512)) mbar_arrive(smem_u32(&ctl->a_empty[a_stage])); else
           mma_commit(smem_u32(&ctl->a_empty[a_stage]));
           if (++a_stage == p.a_stages) {
             a_stage = 0;
             a_phase ^= 1u;
           }
           if (info & 16u) {                                     // last user of the W slice
-            if (p.dbg & 512) mbar_arrive(smem_u32(&ctl->w_empty[w_slot])); else
+            if (ST_DBG(p, 512)) mbar_arrive(smem_u32(&ctl->w_empty[w_slot])); else
             mma_commit(smem_u32(&ctl->w_empty[w_slot]));
             if (++w_slot == p.w_slots) {
               w_slot = 0;
@@ -708,7 +710,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
         acc_phase[buf] ^= 1u;
         if (p.acc_bufs == 2) buf ^= 1;
       }
-      if (p.dbg & 256) {
+      if (ST_DBG(p, 256)) {
         long long* o = g_prof + (size_t)blockIdx.x * 16;
         o[8] = PROF_CLOCK() - m_t0; o[9] = m_acc; o[10] = m_a; o[11] = m_w; o[12] = m_n; o[13] = m_issue; o[14] = m_commit;
       }
@@ -740,12 +742,12 @@ __global__ void __launch_bounds__(kGatherThreads, 1) gather2_kernel(const Params
         const int64_t dst_row = dst_rows[s];
         char* out_row = static_cast<char*>(p.out) + (size_t)dst_row * p.c_acc * out_es;
         const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * set_cols + s * p.c_acc);
-        for (int c0 = 0; c0 < p.c_acc && !(p.dbg & 128); c0 += 32) {
+        for (int c0 = 0; c0 < p.c_acc && !ST_DBG(p, 128); c0 += 32) {
           uint32_t v[32];
           if (p.c_acc - c0 >= 32) {
             tmem_ld32(t_row + c0, v);
             tmem_ld_wait();
-            if (row < p.n_rows && !(p.dbg & 64)) store_cols<32>(out_row, c0, p.out_kind, v);
+            if (row < p.n_rows && !ST_DBG(p, 64)) store_cols<32>(out_row, c0, p.out_kind, v);
           } else {
             tmem_ld16(t_row + c0, v);
             tmem_ld_wait();
@@ -1084,16 +1086,25 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const WgradParams p,
 
 namespace st {
 
-static int g_sm_count = 0;
+// Per-device state: the SM count and whether a kernel's dynamic shared memory limit has been raised are
+// properties of the device the launch goes to, so both are remembered by device ordinal.
+constexpr int kMaxDevices = 64;
+
+static int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
+}
 
 static int sm_count() {
-  if (g_sm_count == 0) {
-    int dev = 0, n = 0;
-    cudaGetDevice(&dev);
+  static int count[kMaxDevices] = {0};
+  const int dev = current_device();
+  if (count[dev] == 0) {
+    int n = 0;
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    g_sm_count = n > 0 ? n : 148;
+    count[dev] = n > 0 ? n : 148;
   }
-  return g_sm_count;
+  return count[dev];
 }
 
 static bool g_tc_enabled = true;
@@ -1256,14 +1267,14 @@ static int launch_gather(tc::Params2 p, const Map& map, cudaStream_t stream) {
   const size_t smem = (size_t)p.w_slots * p.w_slot_bytes + (size_t)p.a_stages * tc::kABlockBytes +
                       p.idx_bytes + sizeof(tc::Control2) + 1024;
   auto kernel = p.esize == 2 ? tc::gather2_kernel<Map, 2> : tc::gather2_kernel<Map, 4>;
-  static bool configured[2] = {false, false};            // one pair per Map instantiation
-  if (!configured[p.esize == 4]) {
+  static bool configured[2][kMaxDevices] = {};             // per element size and device (one set per Map instantiation)
+  if (!configured[p.esize == 4][current_device()]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) {
       set_error("tc gather: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
       return ST_ERR_CUDA;
     }
-    configured[p.esize == 4] = true;
+    configured[p.esize == 4][current_device()] = true;
   }
   int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
   kernel<<<(unsigned)grid, tc::kGatherThreads, smem, stream>>>(p, map);
@@ -1303,14 +1314,14 @@ static int launch_planned(tc::Params2 p, const tc::PlannedRows& map, cudaStream_
   if (!tma) return launch_gather(p, map, stream);
   const size_t smem = (size_t)p.n_slots * p.slot_bytes + sizeof(tc::Control3) + 1024;
   auto kernel = p.esize == 2 ? tc::planned_gather_kernel<2> : tc::planned_gather_kernel<4>;
-  static bool configured[2] = {false, false};
-  if (!configured[p.esize == 4]) {
+  static bool configured[2][kMaxDevices] = {};
+  if (!configured[p.esize == 4][current_device()]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) {
       set_error("tc planned gather: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
       return ST_ERR_CUDA;
     }
-    configured[p.esize == 4] = true;
+    configured[p.esize == 4][current_device()] = true;
   }
   int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
   kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, map, in_desc, w_desc);
@@ -1456,14 +1467,14 @@ int64_t tc_wgrad_partial_bytes(int dtype, int64_t n_rows, int K, int cin, int co
 template <typename Map>
 static int launch_wgrad(WgradPlan& plan, const Map& map, cudaStream_t stream) {
   auto kernel = tc::wgrad_kernel<Map>;
-  static bool configured = false;                        // one per Map instantiation
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};               // per device (one set per Map instantiation)
+  if (!configured[current_device()]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) {
       set_error("tc wgrad: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
       return ST_ERR_CUDA;
     }
-    configured = true;
+    configured[current_device()] = true;
   }
   dim3 grid((unsigned)plan.n_chunks, (unsigned)plan.p.n_kgroups, (unsigned)(plan.p.n_coblk * plan.p.n_ciblk));
   kernel<<<grid, tc::kThreads, plan.smem, stream>>>(plan.p, map);
@@ -1498,14 +1509,14 @@ static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cud
   p.b_slots = slots > 4 ? 4 : slots;
   const size_t smem = 2 * (size_t)p.a_slot_bytes + (size_t)p.b_slots * quad * p.b_slot_bytes + sizeof(tc::WgradControl3) + 1024;
   auto kernel = tc::planned_wgrad_kernel;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};
+  if (!configured[current_device()]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) {
       set_error("tc planned wgrad: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
       return ST_ERR_CUDA;
     }
-    configured = true;
+    configured[current_device()] = true;
   }
   dim3 grid((unsigned)plan.n_chunks, (unsigned)p.n_kgroups, (unsigned)(p.n_coblk * p.n_ciblk));
   kernel<<<grid, tc::kThreads, smem, stream>>>(p, map, x_desc, dy_desc);

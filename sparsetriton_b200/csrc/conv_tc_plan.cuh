@@ -104,11 +104,11 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
       if (!ok) return;
       const uint32_t bar = smem_u32(&ctl->full[d.slot]);
       const uint32_t slot_base = base + (uint32_t)d.slot * (uint32_t)p.slot_bytes;
-      const bool copy_rows = !d.marker && !(p.dbg & 4) && ((d.users >> pw) & 1u);
+      const bool copy_rows = !d.marker && !ST_DBG(p, 4) && ((d.users >> pw) & 1u);
       if (lane == 0) {
         // Every producer warp arrives on every slot, announcing the bytes of its own copies first (a
         // copy that completed before its bytes were announced would drive the count negative).
-        const bool copy_w = pw == 0 && d.has_w && !d.marker && !(p.dbg & 16);
+        const bool copy_w = pw == 0 && d.has_w && !d.marker && !ST_DBG(p, 16);
         if (pw == 0) {
           const int valid_bytes = d.marker ? 0 : min(128, red_bytes - d.kb * 128);
           ctl->info[d.slot] = d.users | (d.fresh << 4) | ((uint32_t)(valid_bytes >> 5) << 8) | (d.marker ? 0x1000u : 0u) |
@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
             w_lo = slot_base >> 4;
             held = slot;
           }
-          if (!(info & 0x1000u) && !(p.dbg & 2)) {
+          if (!(info & 0x1000u) && !ST_DBG(p, 2)) {
             const int ksteps = (int)((info >> 8) & 15u);
             const int part0 = (int)((info >> 16) & 3u) * p.part;
 #pragma unroll
@@ -319,12 +319,12 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
         if ((st_i * p.sub + s) * (int64_t)kTileM >= p.n_rows) break;         // whole sub tile past the end
         char* out_row = static_cast<char*>(p.out) + (size_t)dst_rows[s] * p.c_acc * out_es;
         const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * set_cols + s * p.c_acc);
-        for (int c0 = 0; c0 < p.c_acc && !(p.dbg & 128); c0 += 32) {
+        for (int c0 = 0; c0 < p.c_acc && !ST_DBG(p, 128); c0 += 32) {
           uint32_t v[32];
           if (p.c_acc - c0 >= 32) {
             tmem_ld32(t_row + c0, v);
             tmem_ld_wait();
-            if (row < p.n_rows && !(p.dbg & 64)) store_cols<32>(out_row, c0, p.out_kind, v);
+            if (row < p.n_rows && !ST_DBG(p, 64)) store_cols<32>(out_row, c0, p.out_kind, v);
           } else {
             tmem_ld16(t_row + c0, v);
             tmem_ld_wait();

@@ -33,6 +33,12 @@ hash_build_kernel(const CT* __restrict__ coords, int64_t n, unsigned long long* 
   int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   if (i >= n) return;
   int4 c = load_coord<CT>(coords, i);
+  if (!key_representable(c.x, c.y, c.z, c.w)) {
+    // a negative value or one above 65535 has no key of its own (it would alias another cell's): the
+    // row is left out of the table, where st_hash_query could never return it anyway
+    atomicOr(status, ST_DEV_BAD_INDEX);
+    return;
+  }
   unsigned long long key = pack_key(c.x, c.y, c.z, c.w);
   uint32_t slot = home_slot(key, capacity, mask);
   for (uint32_t step = 0; step < capacity; ++step) {

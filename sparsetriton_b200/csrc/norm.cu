@@ -43,11 +43,20 @@ __host__ __device__ inline Lanes lanes_for(int C) {
   return Lanes{c, kBnThreads / c};
 }
 
+// Sample of row r, or -1 (and ST_DEV_BAD_INDEX in *status) when the stored index is not in [0, B): such a
+// row takes part in no sum and its output is zero, so a bad index never reaches the (B, C) arrays.
+__device__ __forceinline__ int sample_of(const int32_t* __restrict__ batch, int64_t r, int B, int32_t* status) {
+  const int b = batch ? __ldg(batch + r) : 0;
+  if ((unsigned)b < (unsigned)B) return b;
+  if (status) atomicOr(status, ST_DEV_BAD_INDEX);
+  return -1;
+}
+
 // sums[(b*C + c)*2 + 0] += sum (x - shift),  [.. + 1] += sum (x - shift)^2      shift (B, C) or null
 template <typename T>
 __global__ void __launch_bounds__(kBnThreads) bn_sums_kernel(const T* __restrict__ x, const int32_t* __restrict__ batch,
-                                                            int64_t n, int C, const float* __restrict__ shift,
-                                                            float* __restrict__ sums) {
+                                                            int64_t n, int C, int B, const float* __restrict__ shift,
+                                                            float* __restrict__ sums, int32_t* status) {
   const Lanes L = lanes_for(C);
   const int cl = threadIdx.x % L.c_lanes, rl = threadIdx.x / L.c_lanes;
   const int64_t row0 = (int64_t)blockIdx.x * kBnRowsPerBlock;
@@ -56,7 +65,7 @@ __global__ void __launch_bounds__(kBnThreads) bn_sums_kernel(const T* __restrict
     float s0 = 0.f, s1 = 0.f, sh = 0.f;
     int cur = -1;
     for (int64_t r = row0 + rl; r < row_end; r += L.r_lanes) {
-      const int b = batch ? __ldg(batch + r) : 0;
+      const int b = sample_of(batch, r, B, status);
       if (b != cur) {
         if (cur >= 0) {
           atomicAdd(sums + ((int64_t)cur * C + c) * 2, s0);
@@ -64,8 +73,9 @@ __global__ void __launch_bounds__(kBnThreads) bn_sums_kernel(const T* __restrict
         }
         cur = b;
         s0 = s1 = 0.f;
-        sh = shift ? __ldg(shift + (int64_t)b * C + c) : 0.f;
+        if (b >= 0) sh = shift ? __ldg(shift + (int64_t)b * C + c) : 0.f;
       }
+      if (b < 0) continue;
       const float v = to_f(x[r * C + c]) - sh;
       s0 += v;
       s1 += v * v;
@@ -80,14 +90,19 @@ __global__ void __launch_bounds__(kBnThreads) bn_sums_kernel(const T* __restrict
 // y = relu?((x - mean) * rstd * w + bias)
 template <typename T>
 __global__ void __launch_bounds__(kBnThreads) bn_apply_kernel(const T* __restrict__ x, const int32_t* __restrict__ batch,
-                                                             int64_t n, int C, const float* __restrict__ mean,
+                                                             int64_t n, int C, int B, const float* __restrict__ mean,
                                                              const float* __restrict__ rstd, const float* __restrict__ w,
-                                                             const float* __restrict__ bias, int relu, T* __restrict__ y) {
+                                                             const float* __restrict__ bias, int relu, T* __restrict__ y,
+                                                             int32_t* status) {
   const int64_t total = n * C;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / C;
     const int c = (int)(i - r * C);
-    const int b = batch ? __ldg(batch + r) : 0;
+    const int b = sample_of(batch, r, B, status);
+    if (b < 0) {
+      y[i] = from_f<T>(0.f);
+      continue;
+    }
     const int64_t s = (int64_t)b * C + c;
     float v = (to_f(x[i]) - __ldg(mean + s)) * __ldg(rstd + s);
     if (w) v *= __ldg(w + c);
@@ -101,8 +116,8 @@ __global__ void __launch_bounds__(kBnThreads) bn_apply_kernel(const T* __restric
 template <typename T>
 __global__ void __launch_bounds__(kBnThreads)
     bn_bwd_sums_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
-                       const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
-                       const float* __restrict__ bias, int relu, float* __restrict__ sums) {
+                       int B, const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
+                       const float* __restrict__ bias, int relu, float* __restrict__ sums, int32_t* status) {
   const Lanes L = lanes_for(C);
   const int cl = threadIdx.x % L.c_lanes, rl = threadIdx.x / L.c_lanes;
   const int64_t row0 = (int64_t)blockIdx.x * kBnRowsPerBlock;
@@ -112,7 +127,7 @@ __global__ void __launch_bounds__(kBnThreads)
     float s0 = 0.f, s1 = 0.f, m = 0.f, rs = 0.f;
     int cur = -1;
     for (int64_t r = row0 + rl; r < row_end; r += L.r_lanes) {
-      const int b = batch ? __ldg(batch + r) : 0;
+      const int b = sample_of(batch, r, B, status);
       if (b != cur) {
         if (cur >= 0) {
           atomicAdd(sums + ((int64_t)cur * C + c) * 2, s0);
@@ -120,9 +135,12 @@ __global__ void __launch_bounds__(kBnThreads)
         }
         cur = b;
         s0 = s1 = 0.f;
-        m = __ldg(mean + (int64_t)b * C + c);
-        rs = __ldg(rstd + (int64_t)b * C + c);
+        if (b >= 0) {
+          m = __ldg(mean + (int64_t)b * C + c);
+          rs = __ldg(rstd + (int64_t)b * C + c);
+        }
       }
+      if (b < 0) continue;
       const float xhat = (to_f(x[r * C + c]) - m) * rs;
       float dz = to_f(dy[r * C + c]);
       if (relu && !(xhat * wc + bc > 0.f)) dz = 0.f;
@@ -140,14 +158,18 @@ __global__ void __launch_bounds__(kBnThreads)
 template <typename T>
 __global__ void __launch_bounds__(kBnThreads)
     bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
-                        const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
+                        int B, const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
                         const float* __restrict__ bias, int relu, const float* __restrict__ sums,
-                        const float* __restrict__ inv_count, T* __restrict__ dx) {
+                        const float* __restrict__ inv_count, T* __restrict__ dx, int32_t* status) {
   const int64_t total = n * C;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / C;
     const int c = (int)(i - r * C);
-    const int b = batch ? __ldg(batch + r) : 0;
+    const int b = sample_of(batch, r, B, status);
+    if (b < 0) {
+      dx[i] = from_f<T>(0.f);
+      continue;
+    }
     const int64_t s = (int64_t)b * C + c;
     const float wc = w ? __ldg(w + c) : 1.f, bc = bias ? __ldg(bias + c) : 0.f;
     const float rs = __ldg(rstd + s);
@@ -192,9 +214,9 @@ constexpr int kBnUnroll = 4;
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kBnThreads)
     bn_sums_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
-                       const float* __restrict__ p0 /* shift | mean */, const float* __restrict__ rstd,
+                       int B, const float* __restrict__ p0 /* shift | mean */, const float* __restrict__ rstd,
                        const float* __restrict__ w, const float* __restrict__ bias, int relu, float* __restrict__ sums,
-                       int rows_per_block) {
+                       int rows_per_block, int32_t* status) {
   constexpr int V = Vec<T>::V;
   constexpr int U = kBnUnroll;
   const int c_lanes = C / V;                      // <= kBnThreads is checked by the caller
@@ -225,7 +247,7 @@ __global__ void __launch_bounds__(kBnThreads)
   // the row lanes in shared memory first, so that the block issues one atomic per channel and component
   // instead of one per thread.
   __shared__ float red[kBnThreads * 2 * V];
-  const int b_common = (batch && row0 < n) ? __ldg(batch + row0) : 0;
+  const int b_common = row0 < n ? sample_of(batch, row0, B, nullptr) : 0;
   for (int64_t r = row0 + rl; r < row_end; r += (int64_t)U * r_lanes) {
     uint4 xr[U], dr[U];
     int bt[U];
@@ -234,7 +256,7 @@ __global__ void __launch_bounds__(kBnThreads)
       const int64_t rr = r + (int64_t)j * r_lanes;
       bt[j] = -1;
       if (rr < row_end) {
-        bt[j] = batch ? __ldg(batch + rr) : 0;
+        bt[j] = sample_of(batch, rr, B, status);
         xr[j] = load_raw(x + rr * C + c0);
         if (MODE == 1) dr[j] = load_raw(dy + rr * C + c0);
       }
@@ -242,6 +264,11 @@ __global__ void __launch_bounds__(kBnThreads)
 #pragma unroll
     for (int j = 0; j < U; ++j) {
       if (r + (int64_t)j * r_lanes >= row_end) break;
+      if (bt[j] < 0) {                             // index outside [0, B): the row joins no sum
+        flush();
+        cur = -1;
+        continue;
+      }
       if (bt[j] != cur) {
         flush();
         cur = bt[j];
@@ -296,6 +323,7 @@ __global__ void __launch_bounds__(kBnThreads)
     }
   }
   __syncthreads();
+  if (b_common < 0) return;                      // everything was added directly (the partials are zero)
   // thread t < 2*C adds up entry e = t of every group:  red[(g * c_lanes + cl) * 2V + j],  e = cl * 2V + j
   for (int e = threadIdx.x; e < 2 * C; e += kBnThreads) {
     float acc = 0.f;
@@ -309,9 +337,9 @@ __global__ void __launch_bounds__(kBnThreads)
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kBnThreads)
     bn_apply_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
-                        const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
+                        int B, const float* __restrict__ mean, const float* __restrict__ rstd, const float* __restrict__ w,
                         const float* __restrict__ bias, int relu, const float* __restrict__ sums,
-                        const float* __restrict__ inv_count, T* __restrict__ out, int rows_per_block) {
+                        const float* __restrict__ inv_count, T* __restrict__ out, int rows_per_block, int32_t* status) {
   constexpr int V = Vec<T>::V;
   constexpr int U = kBnUnroll;
   const int c_lanes = C / V;
@@ -338,7 +366,7 @@ __global__ void __launch_bounds__(kBnThreads)
       const int64_t rr = r + (int64_t)j * r_lanes;
       bt[j] = -1;
       if (rr < row_end) {
-        bt[j] = batch ? __ldg(batch + rr) : 0;
+        bt[j] = sample_of(batch, rr, B, status);
         xr[j] = load_raw(x + rr * C + c0);
         if (MODE == 1) dr[j] = load_raw(dy + rr * C + c0);
       }
@@ -347,6 +375,13 @@ __global__ void __launch_bounds__(kBnThreads)
     for (int j = 0; j < U; ++j) {
       const int64_t rr = r + (int64_t)j * r_lanes;
       if (rr >= row_end) break;
+      if (bt[j] < 0) {                             // index outside [0, B): the row's output is zero
+        float zero[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) zero[i] = 0.f;
+        store_vec(out + rr * C + c0, zero);
+        continue;
+      }
       if (bt[j] != cur) {
         cur = bt[j];
         const int64_t s = (int64_t)cur * C + c0;
@@ -433,7 +468,7 @@ using namespace st;
 extern "C" {
 
 int st_bn_sums(int dtype, const void* X, const int32_t* batch, int64_t n, int C, int B, const float* shift, float* sums,
-               void* stream) {
+               int32_t* status, void* stream) {
   int rc = check_bn("st_bn_sums", dtype, n, C, B);
   if (rc != ST_OK) return rc;
   if (!sums || (n > 0 && !X)) {
@@ -447,11 +482,12 @@ int st_bn_sums(int dtype, const void* X, const int32_t* batch, int64_t n, int C,
       if (vec_ok<T>(C, X, nullptr, nullptr))
       {
         const int rows = apply_rows(C, Vec<T>::V);
-        bn_sums_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C,
-                                                                              shift, nullptr, nullptr, nullptr, 0, sums, rows);
+        bn_sums_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C, B,
+                                                                              shift, nullptr, nullptr, nullptr, 0, sums, rows,
+                                                                              status);
       }
       else
-        bn_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, shift, sums);
+        bn_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, B, shift, sums, status);
     });
     note_launches(1);
   }
@@ -459,7 +495,7 @@ int st_bn_sums(int dtype, const void* X, const int32_t* batch, int64_t n, int C,
 }
 
 int st_bn_apply(int dtype, const void* X, const int32_t* batch, int64_t n, int C, int B, const float* mean,
-                const float* rstd, const float* weight, const float* bias, int relu, void* Y, void* stream) {
+                const float* rstd, const float* weight, const float* bias, int relu, void* Y, int32_t* status, void* stream) {
   int rc = check_bn("st_bn_apply", dtype, n, C, B);
   if (rc != ST_OK) return rc;
   if (n == 0) return ST_OK;
@@ -472,13 +508,13 @@ int st_bn_apply(int dtype, const void* X, const int32_t* batch, int64_t n, int C
     if (vec_ok<T>(C, X, Y, nullptr))
     {
       const int rows = apply_rows(C, Vec<T>::V);
-      bn_apply_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C,
+      bn_apply_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C, B,
                                                                              mean, rstd, weight, bias, relu, nullptr,
-                                                                             nullptr, static_cast<T*>(Y), rows);
+                                                                             nullptr, static_cast<T*>(Y), rows, status);
     }
     else
-      bn_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, mean, rstd, weight,
-                                                                   bias, relu, static_cast<T*>(Y));
+      bn_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, B, mean, rstd, weight,
+                                                                   bias, relu, static_cast<T*>(Y), status);
   });
   note_launches(1);
   return check_launch("st_bn_apply");
@@ -486,7 +522,7 @@ int st_bn_apply(int dtype, const void* X, const int32_t* batch, int64_t n, int C
 
 int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B,
                         const float* mean, const float* rstd, const float* weight, const float* bias, int relu,
-                        float* sums, void* stream) {
+                        float* sums, int32_t* status, void* stream) {
   int rc = check_bn("st_bn_backward_sums", dtype, n, C, B);
   if (rc != ST_OK) return rc;
   if (!sums || !mean || !rstd || (n > 0 && (!X || !dY))) {
@@ -502,12 +538,12 @@ int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t*
       {
         const int rows = apply_rows(C, Vec<T>::V);
         bn_sums_vec_kernel<T, 1><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X),
-                                                                              static_cast<const T*>(dY), batch, n, C, mean, rstd,
-                                                                              weight, bias, relu, sums, rows);
+                                                                              static_cast<const T*>(dY), batch, n, C, B, mean, rstd,
+                                                                              weight, bias, relu, sums, rows, status);
       }
       else
         bn_bwd_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), static_cast<const T*>(dY), batch,
-                                                                     n, C, mean, rstd, weight, bias, relu, sums);
+                                                                     n, C, B, mean, rstd, weight, bias, relu, sums, status);
     });
     note_launches(1);
   }
@@ -516,7 +552,7 @@ int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t*
 
 int st_bn_backward_apply(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B,
                          const float* mean, const float* rstd, const float* weight, const float* bias, int relu,
-                         const float* sums, const float* inv_count, void* dX, void* stream) {
+                         const float* sums, const float* inv_count, void* dX, int32_t* status, void* stream) {
   int rc = check_bn("st_bn_backward_apply", dtype, n, C, B);
   if (rc != ST_OK) return rc;
   if (n == 0) return ST_OK;
@@ -530,13 +566,13 @@ int st_bn_backward_apply(int dtype, const void* X, const void* dY, const int32_t
     {
       const int rows = apply_rows(C, Vec<T>::V);
       bn_apply_vec_kernel<T, 1><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(
-          static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, mean, rstd, weight, bias, relu, sums, inv_count,
-          static_cast<T*>(dX), rows);
+          static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, B, mean, rstd, weight, bias, relu, sums, inv_count,
+          static_cast<T*>(dX), rows, status);
     }
     else
       bn_bwd_apply_kernel<T><<<flat_blocks(n * C), kBnThreads, 0, s>>>(static_cast<const T*>(X), static_cast<const T*>(dY), batch,
-                                                                       n, C, mean, rstd, weight, bias, relu, sums, inv_count,
-                                                                       static_cast<T*>(dX));
+                                                                       n, C, B, mean, rstd, weight, bias, relu, sums, inv_count,
+                                                                       static_cast<T*>(dX), status);
   });
   note_launches(1);
   return check_launch("st_bn_backward_apply");

@@ -12,15 +12,11 @@
 // chunk of the sequence and ranks its elements 32 at a time with match.any, which keeps equal digits
 // in their original order: the result is deterministic (no atomics between warps).
 #include "common.cuh"
+#include "radix_sort.cuh"
 
 namespace st {
 
 namespace {
-
-constexpr int kSortChunk = 512;         // elements per warp
-constexpr int kSortWarps = 4;           // warps per block
-constexpr int kDigitBitsMax = 9;
-constexpr int kBucketsMax = 1 << kDigitBitsMax;
 
 // key[r] = occupancy mask of row r (bit k: nbr[r,k] >= 0) for K <= 32, a 32-bit hash of the whole
 // pattern beyond (equal patterns still get equal keys); val[r] = r.
@@ -49,119 +45,6 @@ __global__ void __launch_bounds__(128) row_keys_kernel(const int32_t* __restrict
   if (threadIdx.x < rows) {
     keys[row] = key;
     vals[row] = (int32_t)row;
-  }
-}
-
-// hist[d * n_chunks + chunk] = number of elements of the chunk whose digit is d
-__global__ void __launch_bounds__(kSortWarps * 32) sort_hist_kernel(const uint32_t* __restrict__ keys, int64_t n,
-                                                                   int shift, int bits, int64_t n_chunks,
-                                                                   uint32_t* __restrict__ hist) {
-  __shared__ uint32_t count[kSortWarps][kBucketsMax];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t chunk = (int64_t)blockIdx.x * kSortWarps + warp;
-  const int buckets = 1 << bits;
-  for (int d = lane; d < buckets; d += 32) count[warp][d] = 0;
-  __syncwarp();
-  if (chunk < n_chunks) {
-    const int64_t begin = chunk * kSortChunk, end = min(n, begin + kSortChunk);
-    for (int64_t i = begin + lane; i < end; i += 32)
-      atomicAdd(&count[warp][(keys[i] >> shift) & (buckets - 1)], 1u);
-    __syncwarp();
-    for (int d = lane; d < buckets; d += 32) hist[(int64_t)d * n_chunks + chunk] = count[warp][d];
-  }
-}
-
-// One block per digit value d: hist[d * n_chunks + *] <- its exclusive prefix over the chunks,
-// totals[d] <- the number of elements with that digit.
-__global__ void __launch_bounds__(256) sort_bucket_scan_kernel(uint32_t* __restrict__ hist, int64_t n_chunks,
-                                                              uint32_t* __restrict__ totals) {
-  __shared__ uint32_t warp_sum[8];
-  __shared__ uint32_t carry_s;
-  uint32_t* row = hist + (int64_t)blockIdx.x * n_chunks;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) carry_s = 0;
-  __syncthreads();
-  for (int64_t base = 0; base < n_chunks; base += 256) {
-    const int64_t i = base + threadIdx.x;
-    const uint32_t v = i < n_chunks ? row[i] : 0u;
-    uint32_t inc = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t u = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-      if (lane >= o) inc += u;
-    }
-    if (lane == 31) warp_sum[warp] = inc;
-    __syncthreads();
-    uint32_t before = carry_s;
-    for (int w = 0; w < warp; ++w) before += warp_sum[w];
-    if (i < n_chunks) row[i] = before + inc - v;
-    __syncthreads();
-    if (threadIdx.x == 255) carry_s = before + inc;
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) totals[blockIdx.x] = carry_s;
-}
-
-// Stable scatter of one digit pass: `prefix` is hist after sort_bucket_scan_kernel; the first output
-// position of digit d is the sum of totals[0..d), which every block works out for itself.
-__global__ void __launch_bounds__(kSortWarps * 32)
-    sort_scatter_kernel(const uint32_t* __restrict__ keys, const int32_t* __restrict__ vals, int64_t n, int shift,
-                        int bits, int64_t n_chunks, const uint32_t* __restrict__ prefix,
-                        const uint32_t* __restrict__ totals, uint32_t* __restrict__ keys_out,
-                        int32_t* __restrict__ vals_out) {
-  __shared__ uint32_t next[kSortWarps][kBucketsMax];
-  __shared__ uint32_t base[kBucketsMax];
-  __shared__ uint32_t part[kSortWarps * 32];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t chunk = (int64_t)blockIdx.x * kSortWarps + warp;
-  const int buckets = 1 << bits;
-  {
-    // exclusive scan of totals[0..buckets) by the whole block: each thread owns a run of `per` digits
-    constexpr int T = kSortWarps * 32;
-    const int per = (buckets + T - 1) / T;
-    uint32_t mine[(kBucketsMax + T - 1) / T];
-    uint32_t sum = 0;
-#pragma unroll
-    for (int i = 0; i < (kBucketsMax + T - 1) / T; ++i) {
-      const int d = threadIdx.x * per + i;
-      mine[i] = (i < per && d < buckets) ? totals[d] : 0u;
-      sum += mine[i];
-    }
-    part[threadIdx.x] = sum;
-    __syncthreads();
-    uint32_t before = 0;
-    for (int j = 0; j < (int)threadIdx.x; ++j) before += part[j];
-#pragma unroll
-    for (int i = 0; i < (kBucketsMax + T - 1) / T; ++i) {
-      const int d = threadIdx.x * per + i;
-      if (i < per && d < buckets) base[d] = before;
-      before += mine[i];
-    }
-    __syncthreads();
-  }
-  if (chunk >= n_chunks) return;
-  for (int d = lane; d < buckets; d += 32) next[warp][d] = base[d] + prefix[(int64_t)d * n_chunks + chunk];
-  __syncwarp();
-  const int64_t begin = chunk * kSortChunk, end = min(n, begin + kSortChunk);
-  const uint32_t lower = (1u << lane) - 1u;
-  for (int64_t i0 = begin; i0 < end; i0 += 32) {
-    const int64_t i = i0 + lane;
-    const bool live = i < end;
-    const uint32_t key = live ? keys[i] : 0u;
-    const int32_t val = live ? vals[i] : 0;
-    // lanes past the end get a digit of their own so that they never share a bucket with live ones
-    const uint32_t d = live ? ((key >> shift) & (uint32_t)(buckets - 1)) : 0xFFFFFFFFu;
-    const uint32_t peers = __match_any_sync(0xFFFFFFFFu, d);
-    uint32_t base = 0;
-    if (live) base = next[warp][d];
-    __syncwarp();
-    if (live && (peers & lower) == 0) next[warp][d] = base + (uint32_t)__popc(peers);
-    __syncwarp();
-    if (live) {
-      const uint32_t dst = base + (uint32_t)__popc(peers & lower);
-      keys_out[dst] = key;
-      vals_out[dst] = val;
-    }
   }
 }
 
@@ -242,25 +125,11 @@ int32_t* first_vals(const OrderScratch& s, int K, int32_t* order) { return passe
 
 void sort_passes(const OrderScratch& s, int64_t n_rows, int K, int32_t* order, uint32_t** sorted_keys, cudaStream_t st) {
   const int key_bits = K < 32 ? K : 32;
-  const int passes = passes_for(K);
-  const int bits = (key_bits + passes - 1) / passes;
   // ping-pong so that the last pass lands in `order`
-  uint32_t* keys_in = s.keys_a;
-  uint32_t* keys_out = s.keys_b;
   int32_t* vals_in = first_vals(s, K, order);
-  int32_t* vals_out = (passes % 2 == 0) ? s.vals_b : order;
-  const unsigned blocks = (unsigned)((s.n_chunks + kSortWarps - 1) / kSortWarps);
-  for (int pass = 0; pass < passes; ++pass) {
-    const int shift = pass * bits;
-    sort_hist_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, n_rows, shift, bits, s.n_chunks, s.hist);
-    sort_bucket_scan_kernel<<<1u << bits, 256, 0, st>>>(s.hist, s.n_chunks, s.totals);
-    sort_scatter_kernel<<<blocks, kSortWarps * 32, 0, st>>>(keys_in, vals_in, n_rows, shift, bits, s.n_chunks, s.hist,
-                                                            s.totals, keys_out, vals_out);
-    note_launches(3);
-    uint32_t* tk = keys_in; keys_in = keys_out; keys_out = tk;
-    int32_t* tv = vals_in; vals_in = vals_out; vals_out = tv;
-  }
-  if (sorted_keys) *sorted_keys = keys_in;
+  int32_t* vals_alt = vals_in == order ? s.vals_b : order;
+  radix_sort_pairs<uint32_t>(s.keys_a, vals_in, s.keys_b, vals_alt, n_rows, key_bits, s.hist, s.totals, sorted_keys,
+                             nullptr, st);
 }
 
 // ---- plan of the INVERSE map straight from the forward map (K <= 32), without writing the inverse ----

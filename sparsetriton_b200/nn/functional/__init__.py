@@ -2,5 +2,6 @@
 from . import conv
 from .conv import sparse_conv3d
 from .norm import sparse_batch_norm
+from .spatial import sparse_pooling, sparse_upsample
 
-__all__ = ["conv", "sparse_conv3d", "sparse_batch_norm"]
+__all__ = ["conv", "sparse_conv3d", "sparse_batch_norm", "sparse_pooling", "sparse_upsample"]

@@ -16,7 +16,9 @@ __all__ = ["sparse_batch_norm"]
 
 
 def _batch_info(tensor: SparseTensor):
-    """(int32 batch index per row, fp32 1/count per sample), memoised with the coordinate set."""
+    """(int32 batch index per row, fp32 1/count per sample, int32 status word), memoised with the coordinate
+    set.  The kernels OR ST_DEV_BAD_INDEX into the status word for rows whose batch index is not in
+    [0, batch_size) -- such rows join no statistic and come out as zeros; `bad_batch_index(tensor)` reads it."""
     cache = tensor._cache.kmaps
     hit = cache.get("batch_info")
     if hit is None or hit[0].shape[0] != tensor.C.shape[0]:
@@ -28,16 +30,23 @@ def _batch_info(tensor: SparseTensor):
         else:
             counts = torch.bincount(ids.long(), minlength=tensor.batch_size)
         counts = counts.clamp(min=1).to(torch.float32)
-        hit = (ids, (1.0 / counts).contiguous())
+        hit = (ids, (1.0 / counts).contiguous(), torch.zeros(1, dtype=torch.int32, device=ids.device))
         cache["batch_info"] = hit
     return hit
+
+
+def bad_batch_index(tensor: SparseTensor) -> bool:
+    """True if a batch-norm kernel has met a batch index outside [0, batch_size) on this tensor's
+    coordinate set (one device->host read)."""
+    hit = tensor._cache.kmaps.get("batch_info")
+    return bool(hit is not None and int(hit[2].item()) & _lib.DEV_BAD_INDEX)
 
 
 class _BatchNormFn(torch.autograd.Function):
     """y = relu?((x - mean_b) * rstd_b * weight + bias) with statistics per sample b."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, batch, inv_count, n_samples, eps, relu, mean_in, rstd_in):
+    def forward(ctx, x, weight, bias, batch, inv_count, n_samples, eps, relu, mean_in, rstd_in, status):
         _lib.require_cuda(x, "sparse_batch_norm")
         x = x.contiguous()
         n, C = x.shape
@@ -50,19 +59,21 @@ class _BatchNormFn(torch.autograd.Function):
             s = _lib.stream_ptr()
             if mean_in is None:
                 sums = torch.empty((n_samples, C, 2), dtype=torch.float32, device=dev)
-                _lib.check(L.st_bn_sums(code, _lib.ptr(x), _lib.ptr(batch), n, C, n_samples, None, _lib.ptr(sums), s),
-                           "st_bn_sums")
+                _lib.check(L.st_bn_sums(code, _lib.ptr(x), _lib.ptr(batch), n, C, n_samples, None, _lib.ptr(sums),
+                                        _lib.ptr(status), s), "st_bn_sums")
                 mean = (sums[:, :, 0] * inv_count.view(-1, 1)).contiguous()
                 _lib.check(L.st_bn_sums(code, _lib.ptr(x), _lib.ptr(batch), n, C, n_samples, _lib.ptr(mean),
-                                        _lib.ptr(sums), s), "st_bn_sums")
+                                        _lib.ptr(sums), _lib.ptr(status), s), "st_bn_sums")
                 var = sums[:, :, 1] * inv_count.view(-1, 1)
                 rstd = torch.rsqrt(var + eps).contiguous()
             else:
                 mean, rstd, var = mean_in.clone(), rstd_in, None
             y = torch.empty_like(x)
             _lib.check(L.st_bn_apply(code, _lib.ptr(x), _lib.ptr(batch), n, C, n_samples, _lib.ptr(mean), _lib.ptr(rstd),
-                                     _lib.ptr(w), _lib.ptr(b), 1 if relu else 0, _lib.ptr(y), s), "st_bn_apply")
+                                     _lib.ptr(w), _lib.ptr(b), 1 if relu else 0, _lib.ptr(y), _lib.ptr(status), s),
+                       "st_bn_apply")
         ctx.save_for_backward(x, batch, inv_count, mean, rstd, w, b)
+        ctx.status = status
         ctx.meta = (n_samples, relu, weight is not None, bias is not None, mean_in is None)
         ctx.mark_non_differentiable(mean)
         if var is None:
@@ -84,7 +95,7 @@ class _BatchNormFn(torch.autograd.Function):
             sums = torch.empty((n_samples, C, 2), dtype=torch.float32, device=dev)
             _lib.check(L.st_bn_backward_sums(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(batch), n, C, n_samples,
                                              _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(w), _lib.ptr(b), 1 if relu else 0,
-                                             _lib.ptr(sums), s), "st_bn_backward_sums")
+                                             _lib.ptr(sums), _lib.ptr(ctx.status), s), "st_bn_backward_sums")
             dw = sums[:, :, 1].sum(0) if has_w else None
             db = sums[:, :, 0].sum(0) if has_b else None
             dx = None
@@ -94,9 +105,9 @@ class _BatchNormFn(torch.autograd.Function):
                 corr = sums if batch_stats else torch.zeros_like(sums)
                 _lib.check(L.st_bn_backward_apply(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(batch), n, C, n_samples,
                                                   _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(w), _lib.ptr(b),
-                                                  1 if relu else 0, _lib.ptr(corr), _lib.ptr(inv_count), _lib.ptr(dx), s),
-                           "st_bn_backward_apply")
-        return dx, dw, db, None, None, None, None, None, None, None
+                                                  1 if relu else 0, _lib.ptr(corr), _lib.ptr(inv_count), _lib.ptr(dx),
+                                                  _lib.ptr(ctx.status), s), "st_bn_backward_apply")
+        return dx, dw, db, None, None, None, None, None, None, None, None
 
 
 def sparse_batch_norm(tensor: SparseTensor, weight=None, bias=None, running_mean=None, running_var=None,
@@ -106,9 +117,9 @@ def sparse_batch_norm(tensor: SparseTensor, weight=None, bias=None, running_mean
         return tensor.replace(feats)
     C = feats.shape[1]
     if training:
-        batch, inv_count = _batch_info(tensor)
+        batch, inv_count, status = _batch_info(tensor)
         y, mean, var = _BatchNormFn.apply(feats, weight, bias, batch, inv_count, tensor.batch_size, float(eps), bool(relu),
-                                          None, None)
+                                          None, None, status)
         if running_mean is not None:
             running_mean.mul_(1 - momentum).add_(momentum * mean.mean(0).detach())
         if running_var is not None:
@@ -117,5 +128,5 @@ def sparse_batch_norm(tensor: SparseTensor, weight=None, bias=None, running_mean
         mean = running_mean.detach().float().view(1, C).contiguous()
         rstd = torch.rsqrt(running_var.detach().float() + eps).view(1, C).contiguous()
         one = torch.ones(1, dtype=torch.float32, device=feats.device)
-        y, _, _ = _BatchNormFn.apply(feats, weight, bias, None, one, 1, float(eps), bool(relu), mean, rstd)
+        y, _, _ = _BatchNormFn.apply(feats, weight, bias, None, one, 1, float(eps), bool(relu), mean, rstd, None)
     return tensor.replace(y)

@@ -55,6 +55,8 @@ class SparseTensor:
                 assert batch_size > extent[0], f"batch_size {batch_size} must be > max batch index {extent[0]}"
             self.batch_size = batch_size
         self._cache = TensorCache() if cache is None else cache
+        # dense() sizes its batch axis by the largest batch index present, as the reference does
+        self._dense_batch = int(extent[0] + 1) if n > 0 else 1
 
     @classmethod
     def _trusted(cls, feats, coords, spatial_shape, batch_size, cache=None):
@@ -67,6 +69,7 @@ class SparseTensor:
         self.spatial_shape = torch.Size(spatial_shape)
         self.batch_size = batch_size
         self._cache = TensorCache() if cache is None else cache
+        self._dense_batch = None
         return self
 
     # feature / coordinate aliases -------------------------------------------------------------
@@ -104,8 +107,11 @@ class SparseTensor:
         return self
 
     def dense(self):
-        """(B, X, Y, Z, C) dense copy."""
-        return to_dense(self.feats, self.coords, self.spatial_shape)
+        """(B, X, Y, Z, C) dense copy (tensor.py:296-312); differentiable.  B is the largest batch index + 1
+        where the constructor has seen the coordinates, `batch_size` for tensors produced by the library's
+        own operators (no device->host read either way)."""
+        batch = self._dense_batch if self._dense_batch is not None else max(int(self.batch_size), 1)
+        return to_dense(self.feats, self.coords, self.spatial_shape, batch_size=batch)
 
     def replace(self, feats):
         """Same coordinates, shape, batch size and cache; new features."""

@@ -104,12 +104,26 @@ class HashTable:
         if keys.shape[0] == 0:
             return
         coords = self._kernel_ready(keys, "HashTable.insert")
-        status = torch.zeros(1, dtype=torch.int32, device=coords.device)
+        # one status word per table, kept across inserts: the kernels OR their ST_DEV_* conditions into it
+        status = getattr(self, "_status", None)
+        if status is None or status.device != coords.device:
+            status = self._status = torch.zeros(1, dtype=torch.int32, device=coords.device)
         with torch.cuda.device(coords.device), trace.stage("hash_build", 1):
             rc = _lib.lib().st_hash_build(_lib.ptr(coords), coords.shape[0], _lib.coord_code(coords),
                                           _lib.ptr(self.table_keys), _lib.ptr(self.table_values), self.capacity,
                                           _lib.ptr(status), _lib.stream_ptr())
         _lib.check(rc, "st_hash_build")
+
+    def check(self):
+        """Raise if an insert into this table ran out of slots (repeated inserts can exceed the capacity that
+        each of them passed on its own) or met a coordinate outside [0, 65535], which has no key.  One
+        device->host read; no reference counterpart (the reference drops such keys silently)."""
+        status = getattr(self, "_status", None)
+        flags = int(status.item()) if status is not None else 0
+        if flags & _lib.DEV_TABLE_FULL:
+            raise RuntimeError("HashTable: an insert found no free slot (capacity too small for all inserted keys)")
+        if flags & _lib.DEV_BAD_INDEX:
+            raise ValueError("HashTable: a coordinate outside [0, 65535] cannot be stored")
 
     def query(self, keys):
         """int32 row index of each (N,4) coordinate, -1 where absent (hash.py:546-580)."""

@@ -22,6 +22,10 @@ What each ``.npz`` pins (reference file:line):
   conv_*      sparse_conv3d forward + autograd backward   nn/functional/conv/conv.py:77-239,
               (both ConvAlgo values)                      funcs/implicit_precomputed_gemm.py:233-324,
                                                           funcs/implicit_hashfly_gemm.py:330-452
+  dense_*     to_dense forward + autograd backward        utils/to_dense.py:143-282
+  pool_*      sparse_pooling (avg) forward + backward     nn/functional/spatial.py:26-292
+  upsample_*  sparse_upsample forward + backward          nn/functional/spatial.py:294-535
+  bn_*        sparse_batch_norm, training and inference   nn/functional/norm.py:20-112
 
 Batched transposed convolution with stride > 1 is run one sample at a time
 (rows of a sample relabelled to batch 0) and concatenated, because the reference
@@ -349,6 +353,117 @@ def make_c1():
     )
 
 
+def make_dense():
+    """to_dense on a batch-2 tensor: dense volume and the gradient that comes back for a random upstream."""
+    from sparsetriton.utils.to_dense import to_dense
+    from sparsetriton.config import set_coords_dtype
+
+    set_coords_dtype(torch.int32)
+    gen = torch.Generator(device="cpu").manual_seed(4242)
+    shape = (6, 5, 7)
+    coords = _rand_coords(gen, 90, 2, shape)
+    feats = torch.randn(90, 5, generator=gen, requires_grad=True)
+    dense = to_dense(feats, coords, shape)
+    g = torch.randn(dense.shape, generator=gen)
+    (dense * g).sum().backward()
+    np.savez_compressed(os.path.join(HERE, "dense_b2_c5.npz"), coords=coords.numpy(), shape=np.array(shape),
+                        feats=feats.detach().numpy(), dense=dense.detach().numpy(), upstream=g.numpy(),
+                        grad_feats=feats.grad.numpy())
+    print("  dense_b2_c5:", tuple(dense.shape))
+
+
+POOL_CASES = [
+    # name, N, batch, shape, kernel, padding, stride, channels
+    ("pool_avg_k2s2", 160, 2, (8, 8, 8), 2, 1, 2, 6),
+    ("pool_avg_k3s2p1", 200, 2, (9, 7, 8), 3, 1, 2, 4),
+    ("pool_avg_k4s4", 150, 1, (12, 12, 12), 4, 2, 4, 3),
+]
+
+
+def make_pool(case):
+    """sparse_pooling(mode="avg"): output coordinates (sorted cells), features, gradient.  Paddings are chosen
+    so that no cell index is negative (the reference's 16-bit packing aliases negative cells).  mode="max"
+    is tried and its failure recorded: the reference's own test skips it for a known compile issue."""
+    from sparsetriton import SparseTensor
+    from sparsetriton.nn.functional import sparse_pooling
+    from sparsetriton.config import set_coords_dtype
+
+    name, n, batch, shape, k, p, s, ch = case
+    set_coords_dtype(torch.int32)
+    gen = torch.Generator(device="cpu").manual_seed(600 + [c[0] for c in POOL_CASES].index(name))
+    coords = _rand_coords(gen, n, batch, shape)
+    feats = torch.randn(n, ch, generator=gen, requires_grad=True)
+    sp = SparseTensor(feats, coords, spatial_shape=shape, batch_size=batch)
+    out = sparse_pooling(sp, kernel_size=k, padding=p, stride=s, mode="avg")
+    g = torch.randn(out.F.shape, generator=gen)
+    (out.F * g).sum().backward()
+    try:
+        sparse_pooling(SparseTensor(feats.detach(), coords, spatial_shape=shape, batch_size=batch), kernel_size=k,
+                       padding=p, stride=s, mode="max")
+        max_note = "ran"
+    except Exception as e:  # noqa: BLE001 - recorded, not handled
+        max_note = type(e).__name__
+    np.savez_compressed(os.path.join(HERE, f"{name}.npz"), coords=coords.numpy(), shape=np.array(shape), batch=batch,
+                        k=k, p=p, s=s, feats=feats.detach().numpy(), out_coords=out.C.to(torch.int32).numpy(),
+                        new_shape=np.array([int(v) for v in out.spatial_shape]), y=out.F.detach().numpy(),
+                        upstream=g.numpy(), grad_feats=feats.grad.numpy(), reference_max_mode=max_note)
+    print(f"  {name}: N_out={out.F.shape[0]} new_shape={tuple(out.spatial_shape)} max mode: {max_note}")
+
+
+def make_upsample(scale):
+    from sparsetriton import SparseTensor
+    from sparsetriton.nn.functional import sparse_upsample
+    from sparsetriton.config import set_coords_dtype
+
+    set_coords_dtype(torch.int32)
+    gen = torch.Generator(device="cpu").manual_seed(700 + scale)
+    shape = (5, 6, 4)
+    coords = _rand_coords(gen, 70, 2, shape)
+    feats = torch.randn(70, 5, generator=gen, requires_grad=True)
+    sp = SparseTensor(feats, coords, spatial_shape=shape, batch_size=2)
+    out = sparse_upsample(sp, scale_factor=scale)
+    g = torch.randn(out.F.shape, generator=gen)
+    (out.F * g).sum().backward()
+    np.savez_compressed(os.path.join(HERE, f"upsample_s{scale}.npz"), coords=coords.numpy(), shape=np.array(shape),
+                        scale=scale, feats=feats.detach().numpy(), out_coords=out.C.to(torch.int32).numpy(),
+                        new_shape=np.array([int(v) for v in out.spatial_shape]), y=out.F.detach().numpy(),
+                        upstream=g.numpy(), grad_feats=feats.grad.numpy())
+    print(f"  upsample_s{scale}: N_out={out.F.shape[0]}")
+
+
+def make_bn():
+    """sparse_batch_norm (plain torch in the reference): training forward + backward with the running buffers
+    it leaves behind, and the inference form on the updated buffers."""
+    from sparsetriton import SparseTensor
+    from sparsetriton.nn.functional import sparse_batch_norm
+    from sparsetriton.config import set_coords_dtype
+
+    set_coords_dtype(torch.int32)
+    gen = torch.Generator(device="cpu").manual_seed(808)
+    shape = (8, 8, 8)
+    coords = _rand_coords(gen, 300, 3, shape)
+    coords = coords[coords[:, 0] != 1]                  # sample 1 is empty: its count clamps to 1
+    n, ch = coords.shape[0], 6
+    feats = (torch.randn(n, ch, generator=gen) * 2.0 + 0.7).requires_grad_(True)
+    weight = (torch.rand(ch, generator=gen) + 0.5).requires_grad_(True)
+    bias = torch.randn(ch, generator=gen).requires_grad_(True)
+    rm, rv = torch.zeros(ch), torch.ones(ch)
+    sp = SparseTensor(feats, coords, spatial_shape=shape, batch_size=3)
+    out = sparse_batch_norm(sp, weight=weight, bias=bias, running_mean=rm, running_var=rv, training=True, eps=1e-5,
+                            momentum=0.1)
+    g = torch.randn(out.F.shape, generator=gen)
+    (out.F * g).sum().backward()
+    with torch.no_grad():
+        ev = sparse_batch_norm(SparseTensor(feats.detach(), coords, spatial_shape=shape, batch_size=3), weight=weight,
+                               bias=bias, running_mean=rm.detach().clone(), running_var=rv.detach().clone(), training=False, eps=1e-5)
+    np.savez_compressed(os.path.join(HERE, "bn_b3_c6.npz"), coords=coords.numpy(), shape=np.array(shape), batch=3,
+                        feats=feats.detach().numpy(), weight=weight.detach().numpy(), bias=bias.detach().numpy(),
+                        eps=1e-5, momentum=0.1, y_train=out.F.detach().numpy(), upstream=g.numpy(),
+                        grad_feats=feats.grad.numpy(), grad_weight=weight.grad.numpy(), grad_bias=bias.grad.numpy(),
+                        running_mean=rm.detach().numpy(), running_var=rv.detach().numpy(), y_eval=ev.F.detach().numpy())
+    print("  bn_b3_c6: rows", n)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -372,6 +487,16 @@ def main():
     for case in CONV_CASES:
         if want(case[0]):
             make_conv(case)
+    if want("dense"):
+        make_dense()
+    for case in POOL_CASES:
+        if want(case[0]):
+            make_pool(case)
+    for scale in (2, 3):
+        if want(f"upsample_s{scale}"):
+            make_upsample(scale)
+    if want("bn"):
+        make_bn()
     if args.c1:
         make_c1()
 

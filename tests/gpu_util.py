@@ -18,6 +18,36 @@ def rel_err(got, want):
     return float(np.abs(got - want).max()) / denom if want.size else 0.0
 
 
+def rms_err(got, want):
+    """||got - want||_2 / ||want||_2 over the whole array."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    denom = max(float(np.sqrt((want * want).sum())), 1e-30)
+    return float(np.sqrt(((got - want) ** 2).sum())) / denom if want.size else 0.0
+
+
+def row_err(got, want, floor=0.05):
+    """Largest per-row relative error, ||got_r - want_r||_2 / max(||want_r||_2, floor * median row norm): a row of
+    small magnitude is measured against its own size (down to `floor` of the typical row), not against the
+    largest entry of the matrix as rel_err does."""
+    got = np.asarray(got, dtype=np.float64).reshape(len(got), -1)
+    want = np.asarray(want, dtype=np.float64).reshape(len(want), -1)
+    if want.size == 0:
+        return 0.0
+    norms = np.sqrt((want * want).sum(1))
+    scale = np.maximum(norms, floor * max(float(np.median(norms)), 1e-30))
+    return float((np.sqrt(((got - want) ** 2).sum(1)) / scale).max())
+
+
+def check_close(got, want, tol, what=""):
+    """The feature bar in three norms: max-norm relative (rel_err) and RMS relative below `tol`, and the worst
+    row, measured against its own norm, below 4 x tol."""
+    errs = (rel_err(got, want), rms_err(got, want), row_err(got, want))
+    assert errs[0] < tol and errs[1] < tol and errs[2] < 4 * tol, f"{what}: max-norm {errs[0]:.2e} rms {errs[1]:.2e} " \
+                                                                   f"worst row {errs[2]:.2e} (tol {tol:.0e})"
+    return errs
+
+
 def t2n(t):
     return t.detach().float().cpu().numpy() if t.is_floating_point() else t.detach().cpu().numpy()
 

@@ -47,7 +47,7 @@ def _static(x, dy, nbr, K, cin, cout):
 
 
 @pytest.mark.parametrize("cin,cout,dtype", [(64, 128, torch.bfloat16), (32, 64, torch.float32), (4, 20, torch.float16)])
-def test_matches_workspace_entry_point_twice(cuda_device, cin, cout, dtype):
+def test_matches_workspace_entry_point_twice(cuda_device, oracle, cin, cout, dtype):
     K = 27
     with torch.cuda.device(cuda_device):
         for call, (n_rows, seed) in enumerate([(20_000, 1), (9_000, 2)]):
@@ -62,6 +62,9 @@ def test_matches_workspace_entry_point_twice(cuda_device, cin, cout, dtype):
             w, g = want.float().cpu().numpy(), got.float().cpu().numpy()
             assert np.abs(g - w).max() <= tol * max(np.abs(w).max(), 1e-30), f"call {call}"
             assert np.array_equal(g, w), f"call {call}: not bit-identical"
+            # and the entry point's own parity line: the fp32 CPU oracle on the same inputs
+            ref = oracle.conv_wgrad(x.float().cpu().numpy(), dy.float().cpu().numpy(), nbr.cpu().numpy(), K, cin, cout)
+            assert np.abs(g - ref).max() <= tol * max(np.abs(ref).max(), 1e-30), f"call {call}: differs from the oracle"
     assert _lib.device_status(cuda_device)[0] == 0
 
 

@@ -804,6 +804,7 @@ struct WgradParams {
   int n_ciblk, n_coblk;
   int a_slot_bytes, b_slot_bytes, b_slots;
   int quad;              // planned_wgrad_kernel: offsets per shared-memory slot (b_slots counts such slots)
+  int a_slots;           // planned_wgrad_kernel: depth of the dY-tile ring
   int tmem_cols;
   uint32_t idesc_base;   // everything but N
 };
@@ -1416,6 +1417,8 @@ static bool plan_wgrad(WgradPlan* plan, int dtype, int64_t n_rows, int K, int ci
   if (p.group > 32) p.group = 32;
   if (p.group > K) p.group = K;
   p.n_kgroups = (K + p.group - 1) / p.group;
+  // (Equal shares, 7 + 7 + 7 + 6 offsets instead of 8 + 8 + 8 + 3, measured slower: every group then loads the
+  // dY tile of nearly every row tile, and the kernel is bound by what the copy engine moves, not by the longest CTA.)
   int cols = 32;
   while (cols < p.group * p.ci_blk) cols <<= 1;
   p.tmem_cols = cols;
@@ -1486,35 +1489,59 @@ static int launch_wgrad(WgradPlan& plan, const Map& map, cudaStream_t stream) {
 // slots fit, else the cp.async producers of wgrad_kernel over the same plan.
 static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cudaStream_t stream) {
   tc::WgradParams& p = plan.p;
-  const int budget = 222 * 1024 - 2 * p.a_slot_bytes - (int)sizeof(tc::WgradControl3);
-  int quad = budget / (2 * p.b_slot_bytes);
-  if (quad > tc::kProducerWarps) quad = tc::kProducerWarps;
+  // Shared memory: a ring of dY tiles and a ring of X-row slots of `quad` offsets each.  Two shapes, chosen by
+  // measurement: rows of one 128-byte line travel four offsets to a slot, two slots, indices loaded as the
+  // task comes up; wider rows (two lines, 128 or more 16-bit channels) travel one offset to a slot with three
+  // dY tiles in flight and the indices loaded ahead.
+  const bool wide = p.b_slot_bytes >= 2 * tc::kABlockBytes;
+  int a_slots = wide ? 3 : 2, quad = wide ? 1 : tc::kProducerWarps, ahead = wide ? 2 : 0, b_cap = wide ? tc::kWgradBSlots3 : 4;
+#ifdef ST_TC_PROFILE
+  {
+    const char* e = getenv("ST_TC_QUAD");
+    if (e && atoi(e) >= 1 && atoi(e) <= tc::kProducerWarps) quad = atoi(e);
+    const char* f = getenv("ST_TC_ASLOTS");
+    if (f && atoi(f) >= 2 && atoi(f) <= tc::kWgradASlots3) a_slots = atoi(f);
+    const char* g = getenv("ST_TC_AHEAD");
+    if (g) ahead = atoi(g);
+    const char* h = getenv("ST_TC_BCAP");
+    if (h && atoi(h) >= 2 && atoi(h) <= tc::kWgradBSlots3) b_cap = atoi(h);
+  }
+#endif
   if (quad > p.group) quad = p.group;
+  int budget = 222 * 1024 - a_slots * p.a_slot_bytes - (int)sizeof(tc::WgradControl3);
+  while (a_slots > 2 && budget < 2 * quad * p.b_slot_bytes) {
+    --a_slots;
+    budget += p.a_slot_bytes;
+  }
+  while (quad > 1 && budget < 2 * quad * p.b_slot_bytes) --quad;
   CUtensorMap x_desc, dy_desc;
   memset(&x_desc, 0, sizeof(x_desc));
   memset(&dy_desc, 0, sizeof(dy_desc));
   const int dtype = p.esize == 4 ? ST_F32 : ST_BF16;      // element size is all the copy engine needs to know
-  const bool tma = g_tma_enabled && quad >= 1 && p.n_src > 0 &&
+  const bool tma = g_tma_enabled && budget >= 2 * quad * p.b_slot_bytes && p.n_src > 0 &&
                    make_gather_desc(&x_desc, p.x, p.n_src, p.cin, p.esize, dtype, p.esize == 4) &&
                    make_gather_desc(&dy_desc, p.dy, p.n_rows, p.cout, p.esize, dtype, p.esize == 4);
   if (!tma) return launch_wgrad(plan, map, stream);
+  p.quad = quad;
+  p.a_slots = a_slots;
+  int slots = budget / (quad * p.b_slot_bytes);
 #ifdef ST_TC_PROFILE
   {
-    const char* e = getenv("ST_TC_QUAD");
-    if (e && atoi(e) >= 1 && atoi(e) <= quad) quad = atoi(e);
+    const char* e = getenv("ST_TC_BSLOTS");
+    if (e && atoi(e) >= 2 && atoi(e) <= slots) slots = atoi(e);
   }
 #endif
-  p.quad = quad;
-  int slots = budget / (quad * p.b_slot_bytes);
-  p.b_slots = slots > 4 ? 4 : slots;
-  const size_t smem = 2 * (size_t)p.a_slot_bytes + (size_t)p.b_slots * quad * p.b_slot_bytes + sizeof(tc::WgradControl3) + 1024;
-  auto kernel = tc::planned_wgrad_kernel;
+  p.b_slots = slots > b_cap ? b_cap : slots;
+  const size_t smem = (size_t)a_slots * p.a_slot_bytes + (size_t)p.b_slots * quad * p.b_slot_bytes + sizeof(tc::WgradControl3) + 1024;
+  auto kernel = ahead == 0 ? tc::planned_wgrad_kernel<0> : (ahead == 2 ? tc::planned_wgrad_kernel<2> : tc::planned_wgrad_kernel<4>);
   static bool configured[kMaxDevices] = {};
   if (!configured[current_device()]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) {
-      set_error("tc planned wgrad: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
-      return ST_ERR_CUDA;
+    for (auto k : {tc::planned_wgrad_kernel<0>, tc::planned_wgrad_kernel<2>, tc::planned_wgrad_kernel<4>}) {
+      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (e != cudaSuccess) {
+        set_error("tc planned wgrad: cannot raise the dynamic shared memory limit: %s", cudaGetErrorString(e));
+        return ST_ERR_CUDA;
+      }
     }
     configured[current_device()] = true;
   }
@@ -1534,6 +1561,7 @@ static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void*
   plan->p.dy = dy;
   plan->p.order = nullptr;
   plan->p.quad = 1;
+  plan->p.a_slots = 2;
   plan->p.partial = partial;
   plan->p.n_src = n_src;
   return true;

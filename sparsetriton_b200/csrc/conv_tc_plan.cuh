@@ -369,15 +369,19 @@ __global__ void __launch_bounds__(kThreads, 1) planned_gather_kernel(const Param
 //     rows of the q-th of them), so the MMA thread waits and commits once per Q x 8 (16) MMAs.
 // Every producer warp arrives on every barrier (see planned_gather_kernel).
 // =================================================================================================
+constexpr int kWgradASlots3 = 4;
+constexpr int kWgradBSlots3 = 12;
+
 struct __align__(8) WgradControl3 {
-  unsigned long long a_full[2], a_empty[2];
-  unsigned long long b_full[4], b_empty[4];
+  unsigned long long a_full[kWgradASlots3], a_empty[kWgradASlots3];
+  unsigned long long b_full[kWgradBSlots3], b_empty[kWgradBSlots3];
   unsigned long long acc_full;
   uint32_t touched;
   uint32_t tmem_base;
   int abort_flag;
 };
 
+template <int kAhead>
 __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradParams p, const PlannedRows map,
                                                                     const __grid_constant__ CUtensorMap x_desc,
                                                                     const __grid_constant__ CUtensorMap dy_desc) {
@@ -386,9 +390,9 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - raw);
   const uint32_t a_ring = base;
-  const uint32_t b_ring = base + 2u * (uint32_t)p.a_slot_bytes;
+  const uint32_t b_ring = base + (uint32_t)p.a_slots * (uint32_t)p.a_slot_bytes;
   const uint32_t quad_bytes = (uint32_t)p.quad * (uint32_t)p.b_slot_bytes;
-  WgradControl3* ctl = reinterpret_cast<WgradControl3*>(base_ptr + 2 * (size_t)p.a_slot_bytes + (size_t)p.b_slots * quad_bytes);
+  WgradControl3* ctl = reinterpret_cast<WgradControl3*>(base_ptr + (size_t)p.a_slots * p.a_slot_bytes + (size_t)p.b_slots * quad_bytes);
   volatile int* abort_flag = &ctl->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -410,7 +414,7 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
   const int b_blocks = (ci_cnt * p.esize + 127) >> 7;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < p.a_slots; ++s) {
       mbar_init(smem_u32(&ctl->a_full[s]), kProducerWarps);
       mbar_init(smem_u32(&ctl->a_empty[s]), 1);
     }
@@ -437,80 +441,229 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
 
   if (warp >= kFirstProducerWarp) {
     // =============================================================== producers
+    // The CTA's copies form one sequence of tasks: per tile with an occupied offset, the dY tile (A), then
+    // one slot of X rows per `quad` occupied offsets (B).  Every producer warp walks the whole sequence (it
+    // has to arrive on every barrier) with two cursors: `fetch` runs kAhead tasks in front and loads the
+    // row indices a task needs (a line of `order` or of the plan) into a short register queue, `issue`
+    // waits for the task's slot and starts its copies with indices that have long arrived.  Without the
+    // look-ahead every slot paid one trip to DRAM for its indices before its copies could start.
+    if constexpr (kAhead == 0) {
+      // plain form: each task loads its row indices, waits for its slot and starts its copies
+      const int pw = warp - kFirstProducerWarp;
+      int a_slot = 0, b_slot = 0;
+      uint32_t a_phase = 0, b_phase = 0;
+      bool ok = true;
+      uint32_t m_next = tile_begin < tile_end ? tile_mask(tile_begin) : 0u;
+      for (int64_t tile = tile_begin; tile < tile_end && ok; tile += tile_step) {
+        uint32_t m = m_next;
+        if (tile + tile_step < tile_end) m_next = tile_mask(tile + tile_step);
+        if (!m) continue;
+        // ---- the dY tile: rows order[tile * 128 + r]
+        {
+          const int64_t pos = tile * kTileM + 4 * lane;
+          int4 rows;
+          if (p.order) {
+            // the last tile's line may run past the end of `order`: read only what exists
+            rows.x = pos + 0 < p.n_rows ? __ldg(p.order + pos + 0) : -1;
+            rows.y = pos + 1 < p.n_rows ? __ldg(p.order + pos + 1) : -1;
+            rows.z = pos + 2 < p.n_rows ? __ldg(p.order + pos + 2) : -1;
+            rows.w = pos + 3 < p.n_rows ? __ldg(p.order + pos + 3) : -1;
+          } else {
+            rows = make_int4((int)pos, (int)pos + 1, (int)pos + 2, (int)pos + 3);
+          }
+          if (pos + 0 >= p.n_rows) rows.x = -1;
+          if (pos + 1 >= p.n_rows) rows.y = -1;
+          if (pos + 2 >= p.n_rows) rows.z = -1;
+          if (pos + 3 >= p.n_rows) rows.w = -1;
+          ok = mbar_wait_warp(smem_u32(&ctl->a_empty[a_slot]), a_phase ^ 1u, abort_flag, 35, lane);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&ctl->a_full[a_slot]);
+          const uint32_t slot_base = a_ring + (uint32_t)a_slot * (uint32_t)p.a_slot_bytes;
+          // column block b is fetched by warp b % 4
+          int mine = 0;
+          for (int b = pw; b < a_blocks; b += kProducerWarps) ++mine;
+          if (lane == 0) {
+            if (mine) mbar_arrive_expect_tx(bar, (uint32_t)mine * kABlockBytes); else mbar_arrive(bar);
+          }
+          __syncwarp();
+          for (int b = pw; b < a_blocks; b += kProducerWarps)
+            tma_gather4(slot_base + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &dy_desc, bar, co0 + b * per_line,
+                        rows.x, rows.y, rows.z, rows.w);
+          if (++a_slot == p.a_slots) {
+            a_slot = 0;
+            a_phase ^= 1u;
+          }
+        }
+        // ---- the gathered X rows, `quad` offsets per slot: warp q fetches the q-th of them
+        while (m && ok) {
+          int my_j = -1;
+          for (int q = 0; q < p.quad && m; ++q) {
+            const int j = __ffs(m) - 1;
+            m &= m - 1;
+            if (q == pw) my_j = j;
+          }
+          int4 idx = make_int4(-1, -1, -1, -1);
+          if (my_j >= 0)
+            idx = __ldg(reinterpret_cast<const int4*>(map.tmap + (tile * map.K + k_first + my_j) * (int64_t)kTileM) + lane);
+          ok = mbar_wait_warp(smem_u32(&ctl->b_empty[b_slot]), b_phase ^ 1u, abort_flag, 36, lane);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&ctl->b_full[b_slot]);
+          const uint32_t stage = b_ring + (uint32_t)b_slot * quad_bytes + (uint32_t)pw * (uint32_t)p.b_slot_bytes;
+          if (lane == 0) {
+            if (my_j >= 0) mbar_arrive_expect_tx(bar, (uint32_t)b_blocks * kABlockBytes); else mbar_arrive(bar);
+          }
+          __syncwarp();
+          if (my_j >= 0) {
+            for (int b = 0; b < b_blocks; ++b)
+              tma_gather4(stage + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &x_desc, bar, ci0 + b * per_line, idx.x,
+                          idx.y, idx.z, idx.w);
+          }
+          if (++b_slot == p.b_slots) {
+            b_slot = 0;
+            b_phase ^= 1u;
+          }
+        }
+      }
+    } else {
     const int pw = warp - kFirstProducerWarp;
-    int a_slot = 0, b_slot = 0;
-    uint32_t a_phase = 0, b_phase = 0;
-    bool ok = true;
-    uint32_t m_next = tile_begin < tile_end ? tile_mask(tile_begin) : 0u;
-    for (int64_t tile = tile_begin; tile < tile_end && ok; tile += tile_step) {
-      uint32_t m = m_next;
-      if (tile + tile_step < tile_end) m_next = tile_mask(tile + tile_step);
-      if (!m) continue;
-      // ---- the dY tile: rows order[tile * 128 + r]
-      {
-        const int64_t pos = tile * kTileM + 4 * lane;
-        int4 rows;
-        if (p.order) {
+    struct Cursor {
+      int64_t tile;
+      uint32_t m, m_next, b_count;
+      int a_slot, b_slot;
+      uint32_t a_phase, b_phase;
+      bool in_tile;
+    };
+    struct Task {
+      int kind;                 // 0 none, 1 dY tile, 2 X rows
+      int64_t tile;
+      int slot;
+      uint32_t parity;
+      int my_j;                 // kind 2: offset (within the group) this warp copies, or -1
+    };
+    auto cursor = [&]() {
+      Cursor c;
+      c.tile = tile_begin;
+      c.m = 0;
+      c.m_next = tile_begin < tile_end ? tile_mask(tile_begin) : 0u;
+      c.b_count = 0;
+      c.a_slot = c.b_slot = 0;
+      c.a_phase = c.b_phase = 0;
+      c.in_tile = false;
+      return c;
+    };
+    auto next = [&](Cursor& c) {
+      Task t{0, 0, 0, 0u, -1};
+      for (;;) {
+        if (c.tile >= tile_end) return t;
+        if (!c.in_tile) {
+          c.m = c.m_next;
+          c.m_next = c.tile + tile_step < tile_end ? tile_mask(c.tile + tile_step) : 0u;
+          if (!c.m) {
+            c.tile += tile_step;
+            continue;
+          }
+          c.in_tile = true;
+          t = Task{1, c.tile, c.a_slot, c.a_phase, -1};
+          if (++c.a_slot == p.a_slots) {
+            c.a_slot = 0;
+            c.a_phase ^= 1u;
+          }
+          return t;
+        }
+        // `quad` offsets per slot: warp q copies the q-th of them; with one offset per slot the warps take turns
+        int my_j = -1;
+        for (int q = 0; q < p.quad && c.m; ++q) {
+          const int j = __ffs(c.m) - 1;
+          c.m &= c.m - 1;
+          if ((p.quad == 1 ? (int)(c.b_count & (kProducerWarps - 1)) : q) == pw) my_j = j;
+        }
+        t = Task{2, c.tile, c.b_slot, c.b_phase, my_j};
+        ++c.b_count;
+        if (++c.b_slot == p.b_slots) {
+          c.b_slot = 0;
+          c.b_phase ^= 1u;
+        }
+        if (!c.m) {
+          c.in_tile = false;
+          c.tile += tile_step;
+        }
+        return t;
+      }
+    };
+    int a_mine = 0;                                   // column blocks of the dY tile this warp copies (block b: warp b % 4)
+    for (int b = pw; b < a_blocks; b += kProducerWarps) ++a_mine;
+    auto load_rows = [&](const Task& t) {
+      int4 rows = make_int4(-1, -1, -1, -1);
+      if (t.kind == 1 && a_mine) {
+        const int64_t pos = t.tile * kTileM + 4 * lane;
+        if (!p.order) {
+          rows = make_int4((int)pos, (int)pos + 1, (int)pos + 2, (int)pos + 3);
+        } else if (pos + 3 < p.n_rows && (reinterpret_cast<uintptr_t>(p.order) & 15) == 0) {
+          rows = __ldg(reinterpret_cast<const int4*>(p.order + pos));
+        } else {
           // the last tile's line may run past the end of `order`: read only what exists
           rows.x = pos + 0 < p.n_rows ? __ldg(p.order + pos + 0) : -1;
           rows.y = pos + 1 < p.n_rows ? __ldg(p.order + pos + 1) : -1;
           rows.z = pos + 2 < p.n_rows ? __ldg(p.order + pos + 2) : -1;
           rows.w = pos + 3 < p.n_rows ? __ldg(p.order + pos + 3) : -1;
-        } else {
-          rows = make_int4((int)pos, (int)pos + 1, (int)pos + 2, (int)pos + 3);
         }
         if (pos + 0 >= p.n_rows) rows.x = -1;
         if (pos + 1 >= p.n_rows) rows.y = -1;
         if (pos + 2 >= p.n_rows) rows.z = -1;
         if (pos + 3 >= p.n_rows) rows.w = -1;
-        ok = mbar_wait_warp(smem_u32(&ctl->a_empty[a_slot]), a_phase ^ 1u, abort_flag, 35, lane);
-        if (!ok) break;
-        const uint32_t bar = smem_u32(&ctl->a_full[a_slot]);
-        const uint32_t slot_base = a_ring + (uint32_t)a_slot * (uint32_t)p.a_slot_bytes;
-        // column block b is fetched by warp b % 4
-        int mine = 0;
-        for (int b = pw; b < a_blocks; b += kProducerWarps) ++mine;
+      } else if (t.kind == 2 && t.my_j >= 0) {
+        rows = __ldg(reinterpret_cast<const int4*>(map.tmap + (t.tile * map.K + k_first + t.my_j) * (int64_t)kTileM) + lane);
+      }
+      return rows;
+    };
+    bool ok = true;
+    auto issue = [&](const Task& t, const int4& rows) {
+      if (t.kind == 1) {
+        ok = mbar_wait_warp(smem_u32(&ctl->a_empty[t.slot]), t.parity ^ 1u, abort_flag, 35, lane);
+        if (!ok) return;
+        const uint32_t bar = smem_u32(&ctl->a_full[t.slot]);
+        const uint32_t slot_base = a_ring + (uint32_t)t.slot * (uint32_t)p.a_slot_bytes;
         if (lane == 0) {
-          if (mine) mbar_arrive_expect_tx(bar, (uint32_t)mine * kABlockBytes); else mbar_arrive(bar);
+          if (a_mine) mbar_arrive_expect_tx(bar, (uint32_t)a_mine * kABlockBytes); else mbar_arrive(bar);
         }
         __syncwarp();
         for (int b = pw; b < a_blocks; b += kProducerWarps)
           tma_gather4(slot_base + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &dy_desc, bar, co0 + b * per_line,
                       rows.x, rows.y, rows.z, rows.w);
-        if (++a_slot == 2) {
-          a_slot = 0;
-          a_phase ^= 1u;
-        }
-      }
-      // ---- the gathered X rows, `quad` offsets per slot: warp q fetches the q-th of them
-      while (m && ok) {
-        int my_j = -1;
-        for (int q = 0; q < p.quad && m; ++q) {
-          const int j = __ffs(m) - 1;
-          m &= m - 1;
-          if (q == pw) my_j = j;
-        }
-        int4 idx = make_int4(-1, -1, -1, -1);
-        if (my_j >= 0)
-          idx = __ldg(reinterpret_cast<const int4*>(map.tmap + (tile * map.K + k_first + my_j) * (int64_t)kTileM) + lane);
-        ok = mbar_wait_warp(smem_u32(&ctl->b_empty[b_slot]), b_phase ^ 1u, abort_flag, 36, lane);
-        if (!ok) break;
-        const uint32_t bar = smem_u32(&ctl->b_full[b_slot]);
-        const uint32_t stage = b_ring + (uint32_t)b_slot * quad_bytes + (uint32_t)pw * (uint32_t)p.b_slot_bytes;
+      } else {
+        ok = mbar_wait_warp(smem_u32(&ctl->b_empty[t.slot]), t.parity ^ 1u, abort_flag, 36, lane);
+        if (!ok) return;
+        const uint32_t bar = smem_u32(&ctl->b_full[t.slot]);
+        const uint32_t stage = b_ring + (uint32_t)t.slot * quad_bytes + (uint32_t)(p.quad == 1 ? 0 : pw) * (uint32_t)p.b_slot_bytes;
         if (lane == 0) {
-          if (my_j >= 0) mbar_arrive_expect_tx(bar, (uint32_t)b_blocks * kABlockBytes); else mbar_arrive(bar);
+          if (t.my_j >= 0) mbar_arrive_expect_tx(bar, (uint32_t)b_blocks * kABlockBytes); else mbar_arrive(bar);
         }
         __syncwarp();
-        if (my_j >= 0) {
+        if (t.my_j >= 0) {
           for (int b = 0; b < b_blocks; ++b)
-            tma_gather4(stage + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &x_desc, bar, ci0 + b * per_line, idx.x,
-                        idx.y, idx.z, idx.w);
-        }
-        if (++b_slot == p.b_slots) {
-          b_slot = 0;
-          b_phase ^= 1u;
+            tma_gather4(stage + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &x_desc, bar, ci0 + b * per_line, rows.x,
+                        rows.y, rows.z, rows.w);
         }
       }
+    };
+    Cursor fetch = cursor();
+    Task queued[kAhead];
+    int4 queued_rows[kAhead];
+#pragma unroll
+    for (int d = 0; d < kAhead; ++d) {
+      queued[d] = next(fetch);
+      queued_rows[d] = load_rows(queued[d]);
+    }
+    while (queued[0].kind != 0 && ok) {
+      issue(queued[0], queued_rows[0]);
+#pragma unroll
+      for (int d = 0; d + 1 < kAhead; ++d) {
+        queued[d] = queued[d + 1];
+        queued_rows[d] = queued_rows[d + 1];
+      }
+      queued[kAhead - 1] = next(fetch);
+      queued_rows[kAhead - 1] = load_rows(queued[kAhead - 1]);
+    }
     }
   } else if (warp == kMmaWarp) {
     // =============================================================== MMA issuer
@@ -560,7 +713,7 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
           }
         }
         mma_commit(smem_u32(&ctl->a_empty[a_slot]));
-        if (++a_slot == 2) {
+        if (++a_slot == p.a_slots) {
           a_slot = 0;
           a_phase ^= 1u;
         }

@@ -2,25 +2,28 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Other workloads: `hash_map_c2` (hash table + kernel-map microbenchmark, 2M or 8M random cells in a
-2048^3 grid), `unet_infer` / `unet_train` (the lidar-like sparse U-Net, batch 8 / 16 sharded by sample
-over the ranks; training all-reduces one flat gradient bucket over NCCL and applies SGD with momentum).
+Default workload `conv_layer_c3` (BASELINE config 3): one SparseConv3D downsample layer, batch 4, grid 512^3,
+300 000 surface voxels per sample, 64 -> 128 channels, kernel 3, stride 2, padding 1, bf16, PrecomputedNeighborGEMM.
+One PASS is the whole hot path over one batch,
 
-Workload (default `conv_layer_c3`): one SparseConv3D downsample layer, batch 4, grid 512^3,
-300 000 surface voxels per sample, 64 -> 128 channels, kernel 3, stride 2, padding 1, bf16,
-PrecomputedNeighborGEMM.  One step is one pass of the whole hot path over one batch:
+    output coordinates -> neighbour map -> tile plans -> forward -> dgrad -> wgrad
 
-    hash build -> output coordinates -> neighbour map -> forward -> dgrad -> wgrad
+and one STEP is `--passes` such passes cycling over `--batches` distinct seeded batches, so that the timed region
+of a default run lasts most of a second.  `value` is input voxels per second with inputs resident in HBM; `e2e` is
+the same passes through the public Python API starting from pinned HOST buffers (coordinates, features, upstream
+gradient copied host->device and Y, dX, dW device->host inside the timed region).  With N > 1 every rank runs its
+own batches of the same shape (weak scaling) and the weight gradient is all-reduced over NCCL inside the pass.
 
-`value` is input voxels per second with inputs resident in HBM; `e2e` is the same step through the
-public Python API starting from pinned HOST buffers (coordinates, features, upstream gradient are
-copied host->device and Y, dX, dW device->host inside the timed region).  With N > 1 every rank
-runs its own batch of the same shape (weak scaling) and the weight gradient is all-reduced over
-NCCL inside the step.  Inputs are synthetic (seeded procedural surfaces) and larger than L2.
+The same JSON line carries, from short legs run after the timed regions: the layer with ImplicitHashFlyGEMM and in
+fp16, the hash / kernel-map microbenchmark at 2 M cells (config 2), the U-Net inference and training steps
+(configs 4 / 5, sharded by sample over the ranks of this run), the reference's own Triton kernels on this GPU
+(from baseline/_ref when it travelled, N = 1 only) and the CPU baseline (oracle port, N = 1 only).
 
-`--impl reference` times the CPU restatement of the reference's algorithm (the oracle port; the
-reference itself is Triton code that only runs on CPU through the Triton interpreter, at minutes per
-4k voxels) on the host cores, one sample of the same workload per step.
+Other workloads, each printing its own line: `hash_map_c2`, `unet_infer`, `unet_train`.
+
+`--impl reference` times the CPU restatement of the reference's algorithm (the oracle port; the reference itself
+is Triton code whose only CPU path is the Triton interpreter, at minutes per 4k voxels) on the host cores, one
+sample of the same workload per step.
 """
 import argparse
 import json
@@ -38,6 +41,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 CIN, COUT, KS, STRIDE, PAD, GRID, BATCH, PER_SAMPLE = 64, 128, 3, 2, 1, 512, 4, 300_000
+K = KS ** 3
+DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
 
 
 def peaks():
@@ -49,10 +54,10 @@ def peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
-def make_batch(rank, batch=BATCH, per_sample=PER_SAMPLE, grid=GRID):
-    """(N,4) int32 CPU coordinates of `batch` surface scenes; seeds 3000 + rank*batch + sample."""
+def make_batch(seed0, batch=BATCH, per_sample=PER_SAMPLE, grid=GRID):
+    """(N,4) int32 CPU coordinates of `batch` surface scenes; seeds seed0 + sample."""
     from sparsetriton_b200 import synthetic
-    scenes = [synthetic.surface_scene(3000 + rank * batch + b, grid=grid, target=per_sample) for b in range(batch)]
+    scenes = [synthetic.surface_scene(seed0 + b, grid=grid, target=per_sample) for b in range(batch)]
     return synthetic.batch_of(scenes, dtype=torch.int32)
 
 
@@ -94,191 +99,162 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-# ------------------------------------------------------------------------------------------------ ours
-def run_ours(args):
+def _dist_setup(args):
     import torch.distributed as dist
-    import sparsetriton_b200 as st
-    from sparsetriton_b200 import trace
-    from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype, set_h_table_f
-    from sparsetriton_b200.nn.functional import sparse_conv3d
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
-    set_coords_dtype(torch.int32)
-    set_h_table_f(2.0)
-    algo = ConvAlgo.ImplicitHashFlyGEMM if args.algo == "hashfly" else ConvAlgo.PrecomputedNeighborGEMM
-    set_conv_algo(algo)
-    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    return dist, world, rank, local, dev
 
-    coords_h = make_batch(rank, args.batch, args.per_sample, args.grid).pin_memory()
-    n_in = coords_h.shape[0]
-    gen = torch.Generator(device="cpu").manual_seed(9000 + rank)
-    feats_h = torch.randn(n_in, CIN, generator=gen).to(dtype).pin_memory()
-    bound = 1.0 / (CIN * KS ** 3) ** 0.5
-    weight = ((torch.rand(KS ** 3, CIN, COUT, generator=torch.Generator().manual_seed(7)) * 2 - 1) * bound).to(dtype).to(dev)
-    shape = (args.grid,) * 3
 
-    def step(coords, feats, dy, w):
-        """One pass of the hot path; returns (y, dx, dw, out_tensor)."""
-        x = feats.detach().requires_grad_(True)
-        wp = w.detach().requires_grad_(True)
-        sp = st.SparseTensor._trusted(x, coords, shape, args.batch)
-        out = sparse_conv3d(sp, wp, kernel_size=KS, stride=STRIDE, padding=PAD, submanifold=False)
-        g = dy if dy is not None else torch.ones_like(out.F)
-        dx, dw = torch.autograd.grad(out.F, [x, wp], g)
-        if world > 1:
-            dist.all_reduce(dw)
-        return out.F, dx, dw, out
+def _sync_all(dist, world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
 
-    coords_d, feats_d = coords_h.to(dev), feats_h.to(dev)
-    # first pass: learn N_out and the pair count, prepare the upstream gradient
-    y0, _, _, out0 = step(coords_d, feats_d, None, weight)
-    n_out = y0.shape[0]
-    dy_h = torch.randn(n_out, COUT, generator=gen).to(dtype).pin_memory()
-    dy_d = dy_h.to(dev)
-    # pair count of the map (for the flop figures): one probe pass with the stored-map algorithm
-    set_conv_algo(ConvAlgo.PrecomputedNeighborGEMM)
-    sp_probe = st.SparseTensor._trusted(feats_d, coords_d, shape, args.batch)
-    sparse_conv3d(sp_probe, weight, kernel_size=KS, stride=STRIDE, padding=PAD, submanifold=False)
-    pairs = int((sp_probe._cache.neighbor_indices[(KS, STRIDE, PAD, 1, False, False)][1] >= 0).sum().item())
-    del sp_probe
-    set_conv_algo(algo)
-    del y0, out0
 
-    def sync_all():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+def _max_over_ranks(dist, world, dev, values):
+    t = torch.tensor(values, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
 
-    for _ in range(args.warmup):
-        step(coords_d, feats_d, dy_d, weight)
-    sync_all()
 
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    ev0.record()
-    for _ in range(args.steps):
-        step(coords_d, feats_d, dy_d, weight)
-    ev1.record()
-    sync_all()
-    dev_ms = ev0.elapsed_time(ev1)
-    # the per-stage breakdown and the launch count come from a second pass over the same steps with the
-    # stage recorder on (its event pairs cost host time, so it stays out of the timed pass)
-    with trace.recording() as rec:
-        for _ in range(args.steps):
-            step(coords_d, feats_d, dy_d, weight)
-        sync_all()
-        stages = rec.summary()
-        launches = rec.total_launches()
+def _sum_over_ranks(dist, world, dev, values):
+    t = torch.tensor(values, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t)
+    return t.tolist()
 
-    # end to end: host buffers in, host results out, through the same public API
-    y_h = torch.empty((n_out, COUT), dtype=dtype).pin_memory()
-    dx_h = torch.empty((n_in, CIN), dtype=dtype).pin_memory()
-    dw_h = torch.empty((KS ** 3, CIN, COUT), dtype=dtype).pin_memory()
 
-    # Three streams: the copy of step i+1's inputs (pinned host -> device, double-buffered) and the read-back
-    # of step i-1's results run beside step i's kernels.  Every step still moves all of its inputs and results.
-    s_comp = torch.cuda.current_stream()
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    in_bufs = [(torch.empty_like(coords_d), torch.empty_like(feats_d), torch.empty_like(dy_d)) for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_free = [torch.cuda.Event() for _ in range(2)]
-
-    def upload(i):
-        b = i % 2
-        with torch.cuda.stream(s_in):
-            if i >= 2:
-                s_in.wait_event(ev_free[b])                 # step i-2 has finished reading this buffer
-            for dst, src in zip(in_bufs[b], (coords_h, feats_h, dy_h)):
-                dst.copy_(src, non_blocking=True)
-            ev_in[b].record(s_in)
-
-    def e2e_run(n_steps):
-        upload(0)
-        for i in range(n_steps):
-            b = i % 2
-            if i + 1 < n_steps:
-                upload(i + 1)
-            s_comp.wait_event(ev_in[b])
-            c, f, g = in_bufs[b]
-            y, dx, dw, _ = step(c, f, g, weight)
-            ev_free[b].record(s_comp)
-            done = torch.cuda.Event()
-            done.record(s_comp)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(done)
-                y_h.copy_(y, non_blocking=True)
-                dx_h.copy_(dx, non_blocking=True)
-                dw_h.copy_(dw, non_blocking=True)
-            for t in (y, dx, dw):
-                t.record_stream(s_out)
-        s_comp.wait_stream(s_out)
-
-    e2e_run(max(2, args.warmup // 2))
-    sync_all()
+def _event_ms(dist, world, fn, reps):
+    """Device time of `reps` calls of fn, bracketed by barrier + synchronize on both sides."""
+    _sync_all(dist, world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    e2e_run(args.steps)
+    for i in range(reps):
+        fn(i)
     e1.record()
-    sync_all()
-    e2e_ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    _sync_all(dist, world)
+    return e0.elapsed_time(e1)
 
-    times = torch.tensor([dev_ms, e2e_ms, float(n_in)], dtype=torch.float64, device=dev)
-    if world > 1:
-        tmax = times.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = times.clone()
-        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        dev_ms, e2e_ms, total_voxels = tmax[0].item(), tmax[1].item(), tsum[2].item()
-    else:
-        total_voxels = float(n_in)
 
-    if rank == 0:
-        pk = peaks()
-        ms_per_step = dev_ms / args.steps
-        value = total_voxels / (ms_per_step * 1e-3)
-        per_stage = {k: {"ms_per_step": v["ms"] / args.steps, "launches_per_step": v["launches"] / args.steps}
-                     for k, v in stages.items()}
-        roof = roofline(per_stage, n_in, n_out, pairs, pk, dtype)
-        if roof is not None:
-            roof["traffic"], roof["traffic_source"] = ncu_traffic(roof["kernel"], args, algo, n_in)
-        h2d = coords_h.numel() * 4 + feats_h.numel() * feats_h.element_size() + dy_h.numel() * dy_h.element_size()
-        d2h = (y_h.numel() + dx_h.numel() + dw_h.numel()) * y_h.element_size()
-        line = {
-            "metric": "sparse_conv_layer_fwd_bwd_voxels_per_s", "value": value, "unit": "voxels/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": args.dtype, "data": "synthetic",
-            "config": {"workload": "conv_layer_c3: SparseConv3D 64->128 k3 s2 p1, batch %d x %d voxels, grid %d^3, "
-                                   "hash+outcoords+map+fwd+dgrad+wgrad per step" % (args.batch, args.per_sample, args.grid),
-                       "algo": algo.value, "n_in_per_gpu": n_in, "n_out_per_gpu": n_out, "pairs_per_gpu": pairs,
-                       "l2_policy": "inputs larger than L2 (features+map+outputs > 400 MB per step)",
-                       "parallelism": "dp%d by sample, NCCL all-reduce of dW" % world},
-            "e2e": {"value": total_voxels / (e2e_ms / args.steps * 1e-3), "unit": "voxels/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": launches,
-            "stages": per_stage,
-            "roofline": roof,
-            "clocks": clocks,
-        }
-        if pairs:
-            gemm_ms = sum(per_stage.get(s, {}).get("ms_per_step", 0.0) for s in ("conv_fwd", "conv_dgrad", "conv_wgrad"))
-            line["gemm_tflops"] = 3 * 2.0 * pairs * CIN * COUT / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline_leg(args, seconds_budget=20.0)
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+# ------------------------------------------------------------------------------------------------ the layer
+class C3Layer:
+    """The config-3 layer over a few resident batches; `one_pass(j)` runs the whole hot path on batch j."""
+
+    def __init__(self, args, dist, world, rank, dev, dtype, algo_name, n_batches):
+        import sparsetriton_b200 as st
+        from sparsetriton_b200.config import ConvAlgo, set_conv_algo
+        from sparsetriton_b200.nn.functional import sparse_conv3d
+        self.st, self.conv, self.dist, self.world, self.dev = st, sparse_conv3d, dist, world, dev
+        self.args, self.dtype = args, dtype
+        self.algo = ConvAlgo.ImplicitHashFlyGEMM if algo_name == "hashfly" else ConvAlgo.PrecomputedNeighborGEMM
+        self.set_algo = lambda: set_conv_algo(self.algo)
+        self.shape = (args.grid,) * 3
+        bound = 1.0 / (CIN * K) ** 0.5
+        self.weight = ((torch.rand(K, CIN, COUT, generator=torch.Generator().manual_seed(7)) * 2 - 1) * bound).to(dtype).to(dev)
+        self.host, self.resident, self.n_in, self.n_out, self.pairs = [], [], [], [], []
+        for j in range(n_batches):
+            coords_h = make_batch(3000 + (rank * n_batches + j) * args.batch, args.batch, args.per_sample, args.grid).pin_memory()
+            gen = torch.Generator(device="cpu").manual_seed(9000 + rank * n_batches + j)
+            feats_h = torch.randn(coords_h.shape[0], CIN, generator=gen).to(dtype).pin_memory()
+            coords_d, feats_d = coords_h.to(dev), feats_h.to(dev)
+            # learn N_out and the pair count of this batch with the stored-map form (one probe pass)
+            set_conv_algo(ConvAlgo.PrecomputedNeighborGEMM)
+            sp = st.SparseTensor._trusted(feats_d, coords_d, self.shape, args.batch)
+            out = sparse_conv3d(sp, self.weight, kernel_size=KS, stride=STRIDE, padding=PAD, submanifold=False)
+            nbr = sp._cache.neighbor_indices[(KS, STRIDE, PAD, 1, False, False)][1]
+            n_out = out.F.shape[0]
+            self.pairs.append(int((nbr >= 0).sum().item()))
+            del sp, out, nbr
+            dy_h = torch.randn(n_out, COUT, generator=gen).to(dtype).pin_memory()
+            self.host.append((coords_h, feats_h, dy_h))
+            self.resident.append((coords_d, feats_d, dy_h.to(dev)))
+            self.n_in.append(coords_h.shape[0])
+            self.n_out.append(n_out)
+        self.set_algo()
+
+    def run(self, coords, feats, dy):
+        """One pass; returns (y, dx, dw)."""
+        x = feats.detach().requires_grad_(True)
+        wp = self.weight.detach().requires_grad_(True)
+        sp = self.st.SparseTensor._trusted(x, coords, self.shape, self.args.batch)
+        out = self.conv(sp, wp, kernel_size=KS, stride=STRIDE, padding=PAD, submanifold=False)
+        dx, dw = torch.autograd.grad(out.F, [x, wp], dy)
+        if self.world > 1:
+            self.dist.all_reduce(dw)
+        return out.F, dx, dw
+
+    def one_pass(self, j):
+        return self.run(*self.resident[j % len(self.resident)])
+
+    def voxels(self, passes):
+        return sum(self.n_in[j % len(self.n_in)] for j in range(passes))
+
+
+def conv_bytes(kind, n_in, n_out, pairs, es):
+    """Compulsory traffic of one product, e*(N_in*Cin + N_out*Cout + K*Cin*Cout) + 4*rows*K (the map is read once:
+    the forward map for fwd and wgrad, the (N_in, K) inverse map for dgrad), and the bytes the kernel gathers."""
+    rows = n_in if kind == "conv_dgrad" else n_out
+    compulsory = es * (n_in * CIN + n_out * COUT + K * CIN * COUT) + 4 * rows * K
+    gathered = {"conv_fwd": pairs * CIN + n_out * COUT, "conv_dgrad": pairs * COUT + n_in * CIN,
+                "conv_wgrad": pairs * CIN + n_out * COUT}[kind] * es + K * CIN * COUT * es + 4 * rows * K
+    return compulsory, gathered
+
+
+def stage_rooflines(per_stage, n_in, n_out, pairs, pk, dtype):
+    """Roofline entry of every stage of the pass.  Algorithmic bytes:
+      out_coords        N_in*(16 + 12*c) + 16*N_out, c = 27/8 candidates per input of a k3 s2 layer
+      map_scatter       N_out*(16 + 12 K) + 4 P   (the kernel-map figure for N_out rows; the scatter form executes less)
+      map_plan          8 K N_out (read the map, write its plan);  map_plan_inverse  8 K N_in + 4 K N_out
+      conv_*            compulsory bytes (conv_bytes) against the copy bandwidth and 2 P Cin Cout flop against the GEMM
+                        peak; the ceiling that takes longer is the bound
+    """
+    es = 4 if dtype == torch.float32 else 2
+    tc_peak = pk["bf16_tflops"] * (0.5 if dtype == torch.float32 else 1.0)
+    out = {}
+    for name, st in per_stage.items():
+        ms = st["ms_per_pass"]
+        if ms <= 0:
+            continue
+        kind = name.replace("_hashfly", "")
+        entry = {"ms": ms}
+        if kind in ("conv_fwd", "conv_dgrad", "conv_wgrad"):
+            nbytes, gathered = conv_bytes(kind, n_in, n_out, pairs, es)
+            flops = 2.0 * pairs * CIN * COUT
+            t_hbm, t_tc = nbytes / (pk["hbm_gbs"] * 1e9), flops / (tc_peak * 1e12)
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            entry.update({"bound": "hbm" if t_hbm >= t_tc else "tensor", "algorithmic_bytes": nbytes,
+                          "gathered_bytes": gathered, "algorithmic_flops": flops, "achieved_gbs": gbs,
+                          "frac": gbs / pk["hbm_gbs"], "tflops": flops / (ms * 1e-3) / 1e12,
+                          "tensor_frac": flops / (ms * 1e-3) / 1e12 / tc_peak})
+            if t_hbm < t_tc:
+                entry["frac"] = entry["tensor_frac"]
+        else:
+            if kind == "out_coords":
+                nbytes = n_in * (16 + 12 * K / 8.0) + 16 * n_out
+            elif kind in ("map_scatter", "map_build"):
+                nbytes = n_out * (16 + 12 * K) + 4 * pairs
+            elif kind == "map_plan":
+                nbytes = 8 * K * n_out
+            elif kind == "map_plan_inverse":
+                nbytes = 8 * K * n_in + 4 * K * n_out
+            elif kind == "map_invert":
+                nbytes = 4 * K * (n_in + n_out)
+            elif kind in ("hash_build", "hash_clear"):
+                nbytes = 52 * n_in
+            else:
+                continue
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            entry.update({"bound": "hbm", "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"]})
+        out[name] = entry
+    return out
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernels, from the ncu
@@ -290,85 +266,301 @@ NCU_TRAFFIC_C3 = {
 }
 
 
-def ncu_traffic(kernel, args, algo, n_in):
-    """Measured DRAM traffic per launch when this run is the configuration the capture was taken on, scaled
-    by the voxel count of this rank otherwise (traffic of these kernels grows with the rows); None where no
-    capture exists."""
-    from sparsetriton_b200.config import ConvAlgo
-    if kernel not in NCU_TRAFFIC_C3 or algo != ConvAlgo.PrecomputedNeighborGEMM or args.dtype == "fp32":
-        return None, None
-    nbytes, src = NCU_TRAFFIC_C3[kernel]
-    return nbytes * n_in / 1.2e6, src
+def run_ours(args):
+    from sparsetriton_b200 import trace
+    from sparsetriton_b200.config import set_coords_dtype, set_h_table_f
+
+    dist, world, rank, local, dev = _dist_setup(args)
+    set_coords_dtype(torch.int32)
+    set_h_table_f(2.0)
+    dtype = DTYPES[args.dtype]
+    layer = C3Layer(args, dist, world, rank, dev, dtype, args.algo, args.batches)
+    passes = args.passes
+
+    def step(_i=0):
+        for j in range(passes):
+            layer.one_pass(j)
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    dev_ms = _event_ms(dist, world, step, args.steps)
+    # the per-stage breakdown and the launch count come from one more step with the stage recorder on (its event
+    # pairs cost host time, so it stays out of the timed steps)
+    with trace.recording() as rec:
+        step()
+        _sync_all(dist, world)
+        stages, launches_per_step = rec.summary(), rec.total_launches()
+
+    # ---- end to end: host buffers in, host results out, through the same public API.  Three streams: the copy of
+    # pass i+1's inputs (pinned host -> device, double-buffered) and the read-back of pass i-1's results run beside
+    # pass i's kernels.  Every pass still moves all of its inputs and results.
+    big = max(range(len(layer.host)), key=lambda j: layer.n_out[j])
+    y_h = torch.empty((layer.n_out[big], COUT), dtype=dtype).pin_memory()
+    dx_h = torch.empty((max(layer.n_in), CIN), dtype=dtype).pin_memory()
+    dw_h = torch.empty((K, CIN, COUT), dtype=dtype).pin_memory()
+    s_comp = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    in_bufs = [(torch.empty((max(layer.n_in), 4), dtype=torch.int32, device=dev),
+                torch.empty((max(layer.n_in), CIN), dtype=dtype, device=dev),
+                torch.empty((max(layer.n_out), COUT), dtype=dtype, device=dev)) for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+
+    def views(b, j):
+        return (in_bufs[b][0][:layer.n_in[j]], in_bufs[b][1][:layer.n_in[j]], in_bufs[b][2][:layer.n_out[j]])
+
+    def upload(i):
+        b, j = i % 2, i % len(layer.host)
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(ev_free[b])                 # pass i-2 has finished reading this buffer
+            for dst, src in zip(views(b, j), layer.host[j]):
+                dst.copy_(src, non_blocking=True)
+            ev_in[b].record(s_in)
+
+    def e2e_run(n_passes):
+        upload(0)
+        for i in range(n_passes):
+            b, j = i % 2, i % len(layer.host)
+            if i + 1 < n_passes:
+                upload(i + 1)
+            s_comp.wait_event(ev_in[b])
+            y, dx, dw = layer.run(*views(b, j))
+            ev_free[b].record(s_comp)
+            done = torch.cuda.Event()
+            done.record(s_comp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                y_h[:y.shape[0]].copy_(y, non_blocking=True)
+                dx_h[:dx.shape[0]].copy_(dx, non_blocking=True)
+                dw_h.copy_(dw, non_blocking=True)
+            for t in (y, dx, dw):
+                t.record_stream(s_out)
+        s_comp.wait_stream(s_out)
+
+    e2e_passes = args.steps * passes
+    e2e_run(min(4, e2e_passes))
+    e2e_ms = _event_ms(dist, world, lambda _i: e2e_run(e2e_passes), 1)
+    clocks = sampler.stop() if rank == 0 else None
+    del in_bufs
+
+    dev_ms, e2e_ms = _max_over_ranks(dist, world, dev, [dev_ms, e2e_ms])
+    (voxels_per_step,) = _sum_over_ranks(dist, world, dev, [float(layer.voxels(passes))])
+
+    # ---- legs (same process, after the timed regions)
+    legs = {}
+    if not args.no_legs:
+        legs.update(c3_variant_legs(args, dist, world, rank, dev))
+        legs.update(unet_legs(args, dist, world, rank, dev))
+        if rank == 0:
+            legs["c2_2m"] = c2_leg(args, dev)
+        if world == 1:
+            legs["reference_gpu_triton"] = reference_gpu_leg(args)
+
+    if rank == 0:
+        pk = peaks()
+        ms_per_step = dev_ms / args.steps
+        ms_per_pass = ms_per_step / passes
+        value = voxels_per_step / (ms_per_step * 1e-3)
+        n_in, n_out, pairs = (statistics.mean(v) for v in (layer.n_in, layer.n_out, layer.pairs))
+        per_stage = {k: {"ms_per_pass": v["ms"] / passes, "launches_per_pass": v["launches"] / passes}
+                     for k, v in stages.items()}
+        roofs = stage_rooflines(per_stage, n_in, n_out, pairs, pk, dtype)
+        top = max(roofs, key=lambda k: roofs[k]["ms"]) if roofs else None
+        roof = None
+        if top:
+            r = roofs[top]
+            bound = r["bound"]
+            traffic, src = None, None
+            if top in NCU_TRAFFIC_C3 and args.algo == "precomputed" and args.dtype != "fp32":
+                traffic, src = NCU_TRAFFIC_C3[top][0] * n_in / 1.2e6, NCU_TRAFFIC_C3[top][1]
+            roof = {"kernel": top, "bound": bound,
+                    "achieved": r["achieved_gbs"] if bound == "hbm" else r["tflops"],
+                    "peak": pk["hbm_gbs"] if bound == "hbm" else pk["bf16_tflops"],
+                    "unit": "GB/s" if bound == "hbm" else "TFLOP/s", "frac": r["frac"], "traffic": traffic,
+                    "traffic_source": src, "peak_source": pk["source"],
+                    "algorithmic_bytes_per_launch": r["algorithmic_bytes"], "gathered_bytes": r.get("gathered_bytes"),
+                    "algorithmic_flops_per_launch": r.get("algorithmic_flops"), "tensor_frac": r.get("tensor_frac"),
+                    "ms_per_launch": r["ms"], "share_of_pass": r["ms"] / sum(v["ms"] for v in roofs.values())}
+        h2d = sum(sum(t.numel() * t.element_size() for t in layer.host[j % len(layer.host)]) for j in range(passes))
+        d2h = sum((layer.n_out[j % len(layer.host)] * COUT + layer.n_in[j % len(layer.host)] * CIN + K * CIN * COUT)
+                  * y_h.element_size() for j in range(passes))
+        line = {
+            "metric": "sparse_conv_layer_fwd_bwd_voxels_per_s", "value": value, "unit": "voxels/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": args.dtype, "data": "synthetic",
+            "config": {"workload": "conv_layer_c3: SparseConv3D 64->128 k3 s2 p1, batch %d x %d voxels, grid %d^3; one pass = "
+                                   "output coordinates + neighbour map (one sweep over the candidates, no hash table of the "
+                                   "inputs) + tile plans + fwd + dgrad + wgrad; one step = %d passes over %d distinct seeded "
+                                   "batches" % (args.batch, args.per_sample, args.grid, passes, len(layer.host)),
+                       "algo": layer.algo.value, "passes_per_step": passes, "ms_per_pass": ms_per_pass,
+                       "n_in_per_pass": n_in, "n_out_per_pass": n_out, "pairs_per_pass": pairs,
+                       "constructor": "SparseTensor._trusted (the library's internal constructor: no validation read of the "
+                                      "coordinates; the public one adds one device->host read per tensor)",
+                       "l2_policy": "inputs larger than L2 (features + map + outputs > 400 MB per pass, %d batches cycled)"
+                                    % len(layer.host),
+                       "parallelism": "dp%d by sample, NCCL all-reduce of dW" % world},
+            "e2e": {"value": voxels_per_step / (e2e_ms / args.steps * 1e-3), "unit": "voxels/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+                    "ms_per_pass": e2e_ms / e2e_passes},
+            "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_pass": launches_per_step / passes,
+            "stages": per_stage, "stage_rooflines": roofs, "roofline": roof, "clocks": clocks,
+        }
+        if pairs:
+            gemm_ms = sum(per_stage.get(s, {}).get("ms_per_pass", 0.0) for s in ("conv_fwd", "conv_dgrad", "conv_wgrad"))
+            line["gemm_tflops"] = 3 * 2.0 * pairs * CIN * COUT / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        line.update(legs)
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_leg(args, seconds_budget=20.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()                     # rank 0 ran legs of its own: leave together
+        dist.destroy_process_group()
 
 
-def roofline(per_stage, n_in, n_out, pairs, pk, dtype):
-    """Roofline entry of the stage that takes the largest share of the step.
+# ------------------------------------------------------------------------------------------------ legs
+def c3_variant_legs(args, dist, world, rank, dev):
+    """The same layer with the hash-on-the-fly algorithm and in fp16: ms per pass (max over ranks), one batch."""
+    out = {}
+    for key, algo, dt in (("c3_hashfly_ms_per_step", "hashfly", args.dtype), ("c3_fp16_ms_per_step", "precomputed", "fp16")):
+        try:
+            layer = C3Layer(args, dist, world, rank, dev, DTYPES[dt], algo, 1)
+            for _ in range(3):
+                layer.one_pass(0)
+            reps = 5
+            ms = _event_ms(dist, world, layer.one_pass, reps) / reps
+            (ms,) = _max_over_ranks(dist, world, dev, [ms])
+            out[key] = ms
+            out[key.replace("_ms_per_step", "_voxels_per_s")] = world * layer.n_in[0] / (ms * 1e-3)
+            del layer
+        except Exception as e:  # noqa: BLE001 - a leg must not take the headline down
+            out[key] = "failed: %r" % (e,)
+        torch.cuda.empty_cache()
+    from sparsetriton_b200.config import ConvAlgo, set_conv_algo
+    set_conv_algo(ConvAlgo.PrecomputedNeighborGEMM)
+    return out
 
-    Algorithmic work per launch:
-      conv_*      2 * pairs * Cin * Cout flop against the bf16 GEMM peak, and
-                  (gathered rows + streamed rows + weights) * element size + map rows * 4 K bytes against the
-                  copy bandwidth: the ceiling that takes longer is reported as the bound
-      map_build   N_out * (16 + 12 K) + 4 * pairs bytes             (coords + key probe + map write + value)
-      map_plan    8 K rows bytes (read the map, write its plan); the inverse plan also reads the forward map
-      out_coords  N * (16 + 12 c) + 16 N_out bytes, c = 27/8        (candidates inserted + coords written)
-      hash_build  52 N bytes at capacity 2N
-    """
-    K = KS ** 3
-    if not per_stage:
-        return None
-    top = max(per_stage, key=lambda k: per_stage[k]["ms_per_step"])
-    ms = per_stage[top]["ms_per_step"]
-    total = sum(v["ms_per_step"] for v in per_stage.values())
-    entry = {"kernel": top, "share_of_step": ms / total if total else None, "traffic": None}
-    if top.startswith("conv_") and pairs:
-        # Both ceilings of the product; the one that takes longer at its measured peak is the bound.
-        flops = 2.0 * pairs * CIN * COUT
-        es = 4 if dtype == torch.float32 else 2
-        kind = top.replace("_hashfly", "")
-        gathered = {"conv_fwd": pairs * CIN, "conv_dgrad": pairs * COUT, "conv_wgrad": pairs * CIN}[kind]
-        streamed = {"conv_fwd": n_out * COUT, "conv_dgrad": n_in * CIN, "conv_wgrad": n_out * COUT}[kind]
-        map_rows = n_in if kind == "conv_dgrad" else n_out
-        nbytes = (gathered + streamed + K * CIN * COUT) * es + map_rows * K * 4
-        tc_peak = pk["bf16_tflops"] * (0.5 if dtype == torch.float32 else 1.0)
-        t_tc = flops / (tc_peak * 1e12)
-        t_hbm = nbytes / (pk["hbm_gbs"] * 1e9)
-        if t_hbm >= t_tc:
-            ach = nbytes / (ms * 1e-3) / 1e9
-            entry.update({"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                          "frac": ach / pk["hbm_gbs"], "peak_source": pk["source"],
-                          "algorithmic_bytes_per_launch": nbytes, "algorithmic_flops_per_launch": flops,
-                          "tensor_frac": flops / (ms * 1e-3) / 1e12 / tc_peak})
-        else:
-            ach = flops / (ms * 1e-3) / 1e12
-            entry.update({"bound": "tensor", "achieved": ach, "peak": tc_peak, "unit": "TFLOP/s", "frac": ach / tc_peak,
-                          "peak_source": pk["source"], "algorithmic_flops_per_launch": flops,
-                          "algorithmic_bytes_per_launch": nbytes})
-    else:
-        if top == "map_build":
-            nbytes = n_out * (16 + 12 * K) + 4 * (pairs or 0)
-        elif top in ("map_plan", "map_plan_inverse"):
-            nbytes = 8 * K * (n_out if top == "map_plan" else n_in) + (4 * K * n_out if top == "map_plan_inverse" else 0)
-        elif top == "map_scatter":
-            nbytes = 4 * (pairs or 0) + 4 * n_out * K
-        elif top == "out_coords":
-            nbytes = n_in * (16 + 12 * K / 8.0) + 16 * n_out
-        else:
-            nbytes = 52 * n_in
-        ach = nbytes / (ms * 1e-3) / 1e9
-        entry.update({"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
-                      "peak_source": pk["source"], "algorithmic_bytes_per_launch": nbytes})
-    return entry
+
+def c2_leg(args, dev, cells=2_000_000, steps=3):
+    """BASELINE config 2 at 2 M cells on one GPU: per-stage ms and fraction of the measured copy bandwidth."""
+    try:
+        res = hash_map_measure(dev, cells, 2001, warmup=2, steps=steps)
+        res.pop("launches", None)
+        return res
+    except Exception as e:  # noqa: BLE001
+        return "failed: %r" % (e,)
+    finally:
+        torch.cuda.empty_cache()
+
+
+def unet_legs(args, dist, world, rank, dev):
+    out = {}
+    for key, train in (("unet_infer", False), ("unet_train", True)):
+        try:
+            r = unet_measure(args, dist, world, rank, dev, train, steps=8, warmup=3, prune=True, e2e=False)
+            out[key + "_ms_per_step"] = r["ms_per_step"]
+            out[key + "_detail"] = {"prune": True, "batch": r["total_batch"], "voxels": r["total_voxels"],
+                                    "launches_per_step": r["launches"], "kernel_ms_per_step": r["kernel_ms"],
+                                    "decoder": "up-convolution evaluated at the encoder's coordinates (prune=True)"}
+        except Exception as e:  # noqa: BLE001
+            out[key + "_ms_per_step"] = "failed: %r" % (e,)
+        torch.cuda.empty_cache()
+    if rank == 0:
+        # the literal decoder (every child of the transposed convolution kept, skip by lookup) on two samples
+        try:
+            r = unet_measure(args, None, 1, 0, dev, False, steps=3, warmup=2, prune=False, e2e=False, samples=[4000, 4001])
+            out["unet_infer_literal_2_samples_ms_per_step"] = r["ms_per_step"]
+            out["unet_infer_literal_detail"] = {"prune": False, "batch": 2, "voxels_in": r["total_voxels"],
+                                                "voxels_out": r["n_out"], "launches_per_step": r["launches"]}
+        except Exception as e:  # noqa: BLE001
+            out["unet_infer_literal_2_samples_ms_per_step"] = "failed: %r" % (e,)
+        torch.cuda.empty_cache()
+    return out
+
+
+REF_GPU_SCRIPT = r"""
+import json, os, sys, time
+root = sys.argv[1]
+sys.path.insert(0, os.path.join(root, "baseline", "_ref"))
+sys.path.insert(0, root)
+import torch
+try:
+    import triton                                                       # noqa: F401
+    import sparsetriton
+    from sparsetriton import SparseTensor
+    from sparsetriton.nn.modules import SparseConv3D
+    from sparsetriton.config import set_conv_algo, ConvAlgo
+    assert os.path.realpath(sparsetriton.__file__).startswith(os.path.realpath(os.path.join(root, "baseline", "_ref")))
+except Exception as e:
+    print(json.dumps({"unavailable": "reference-on-GPU unavailable on this box: %r" % (e,)}))
+    sys.exit(0)
+from sparsetriton_b200 import synthetic
+dev = torch.device("cuda")
+batch, per_sample, grid, warm, iters = int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]), int(sys.argv[6])
+coords = synthetic.batch_of([synthetic.surface_scene(3000 + b, grid=grid, target=per_sample) for b in range(batch)],
+                            dtype=torch.int32).to(dev)
+n = coords.shape[0]
+feats = torch.randn(n, 64, generator=torch.Generator().manual_seed(9000)).to(torch.bfloat16).to(dev)
+res = {"n_in": n, "protocol": "%d warm-up + %d timed iterations of SparseConv3D(64,128,3,stride=2,padding=1) forward + backward "
+                              "on a fresh SparseTensor per iteration (benchmark_spconv_vs_sparsetriton.py:45-64), bf16, CUDA events"
+                              % (warm, iters)}
+for algo in (ConvAlgo.PrecomputedNeighborGEMM, ConvAlgo.ImplicitHashFlyGEMM):
+    try:
+        set_conv_algo(algo)
+        torch.manual_seed(7)
+        conv = SparseConv3D(64, 128, 3, stride=2, padding=1, bias=False).to(dev).to(torch.bfloat16)
+        def step():
+            x = feats.detach().requires_grad_(True)
+            out = conv(SparseTensor(x, coords, spatial_shape=(grid,) * 3, batch_size=batch))
+            out.F.backward(torch.ones_like(out.F))
+            return out.F.shape[0]
+        for _ in range(warm):
+            n_out = step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        res[algo.name] = {"ms_per_step": ms, "voxels_per_s": n / (ms * 1e-3), "n_out": n_out}
+    except Exception as e:
+        res[algo.name] = "failed: %r" % (e,)
+print(json.dumps(res))
+"""
+
+
+def reference_gpu_leg(args, warm=10, iters=30):
+    """The UNMODIFIED reference package (installed into baseline/_ref in the build container) timed on this GPU on the
+    shapes of the default workload, in a child process with a time limit; or the reason it cannot run here."""
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "sparsetriton")):
+        return "reference-on-GPU unavailable on this box: baseline/_ref/sparsetriton is not present"
+    try:
+        p = subprocess.run([sys.executable, "-c", REF_GPU_SCRIPT, ROOT, str(args.batch), str(args.per_sample), str(args.grid),
+                            str(warm), str(iters)], capture_output=True, text=True, timeout=600)
+        lines = [l for l in p.stdout.splitlines() if l.startswith("{")]
+        if p.returncode != 0 or not lines:
+            return "reference-on-GPU unavailable on this box: exit %d: %s" % (p.returncode, (p.stderr or p.stdout)[-300:])
+        res = json.loads(lines[-1])
+        return res.get("unavailable", res)
+    except subprocess.TimeoutExpired:
+        return "reference-on-GPU unavailable on this box: no result within 600 s"
 
 
 # ------------------------------------------------------------------------------------ CPU baseline
 def cpu_step(O, coords, feats, weight, dy_seed):
-    """The same step on the host through the oracle port; returns (seconds, n_in, n_out)."""
+    """The same pass on the host through the oracle port; returns (seconds, n_in, n_out)."""
     t0 = time.perf_counter()
     oc, ns, off, nbr = O.kernel_map(coords, (GRID,) * 3, KS, STRIDE, 1, PAD, False, False)
     y = O.conv_fwd(feats, weight, nbr)
     dy = np.full_like(y, 1.0) if dy_seed is None else dy_seed(y.shape)
     O.conv_dgrad(dy, weight, nbr, feats.shape[0])
-    O.conv_wgrad(feats, dy, nbr, KS ** 3, CIN, COUT)
+    O.conv_wgrad(feats, dy, nbr, K, CIN, COUT)
     return time.perf_counter() - t0, coords.shape[0], oc.shape[0]
 
 
@@ -377,8 +569,13 @@ def cpu_inputs(per_sample, grid):
     coords = synthetic.batch_of([synthetic.surface_scene(3000, grid=grid, target=per_sample)]).numpy()
     rng = np.random.default_rng(9000)
     feats = rng.standard_normal((coords.shape[0], CIN), dtype=np.float32)
-    weight = ((rng.random((KS ** 3, CIN, COUT), dtype=np.float32) * 2 - 1) / (CIN * KS ** 3) ** 0.5).astype(np.float32)
+    weight = ((rng.random((K, CIN, COUT), dtype=np.float32) * 2 - 1) / (CIN * K) ** 0.5).astype(np.float32)
     return coords, feats, weight
+
+
+CPU_NOTE = ("oracle port (C + OpenMP restatement of the reference's algorithm, fp32); the three products, the candidate "
+            "count and the neighbour map run on all threads, the first-occurrence dedupe of the output coordinates and the "
+            "inverse-map build of dgrad are sequential loops (their order defines the result)")
 
 
 def cpu_baseline_leg(args, seconds_budget):
@@ -393,14 +590,13 @@ def cpu_baseline_leg(args, seconds_budget):
         secs = min(secs, s2)
         reps += 1
     return {"value": n_in / secs, "unit": "voxels/s", "cores": O.num_threads(), "kind": "port",
-            "sample": "1 of the %d samples of the batch (%d voxels), same layer and step, fp32, best of %d" %
-                      (args.batch, n_in, reps),
-            "seconds_per_sample_step": secs}
+            "sample": "1 of the %d samples of a batch (%d voxels), same layer and pass, best of %d; %s" %
+                      (args.batch, n_in, reps, CPU_NOTE),
+            "seconds_per_sample_pass": secs}
 
 
 def run_reference(args):
-    """CPU arm: the oracle port (C + OpenMP restatement of the reference's algorithm) on all host
-    threads; each step processes one sample of the workload."""
+    """CPU arm: the oracle port on all host threads; each step processes one sample of the workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -408,7 +604,8 @@ def run_reference(args):
     O.build()
     O.set_threads(os.cpu_count() or 1)            # launchers such as torchrun export OMP_NUM_THREADS=1
     coords, feats, weight = cpu_inputs(args.per_sample, args.grid)
-    for _ in range(min(args.warmup, 1)):
+    warm = min(args.warmup, 1)
+    for _ in range(warm):
         cpu_step(O, coords, feats, weight, None)
     steps = min(args.steps, 5)
     t = 0.0
@@ -416,10 +613,12 @@ def run_reference(args):
         s, n_in, n_out = cpu_step(O, coords, feats, weight, None)
         t += s
     value = n_in * steps / t
-    sample = "each step = 1 of the %d samples of the batch (%d voxels); %d steps timed" % (args.batch, n_in, steps)
+    sample = ("each step = 1 of the %d samples of a batch (%d voxels); %d steps timed after %d warm-up (asked for %d / %d: a "
+              "host step takes ~0.4 s and repeats to within a few per cent, so the arm caps itself at 5 timed steps and 1 "
+              "warm-up to stay within its time budget); %s" % (args.batch, n_in, steps, warm, args.steps, args.warmup, CPU_NOTE))
     print(json.dumps({
         "impl": "reference", "metric": "sparse_conv_layer_fwd_bwd_voxels_per_s", "value": value, "unit": "voxels/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": t / steps * 1e3,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": t / steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "conv_layer_c3 on host cores (oracle port of the reference's algorithm; the reference's "
                                "own Triton-interpreter CPU path needs minutes per 4k voxels)", "sample": sample},
@@ -428,33 +627,21 @@ def run_reference(args):
     }))
 
 
-# --------------------------------------------------------------------------------- other workloads
-def _dist_setup(args):
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    return dist, world, rank, local, dev
-
-
-def run_hash_map(args):
-    """BASELINE config 2: table build at load factor 0.5, submanifold maps for k3 (27) and k5 (125),
-    a k3 s2 p1 downsample (output coordinates + map) and the transposed map from its output."""
+# --------------------------------------------------------------------------------- hash / kernel-map workload
+def hash_map_measure(dev, n, seed, warmup, steps):
+    """BASELINE config 2: table build at load factor <= 0.5, submanifold maps for k3 (27) and k5 (125), a k3 s2 p1
+    downsample (output coordinates + map) and the transposed map from its output.  Returns per-stage ms and
+    rooflines (algorithmic bytes: coords 16 B, one 8-byte key probe + 4-byte map entry per (voxel, offset), 4 bytes
+    per hit; strided / transposed add 16 N_out for the coordinates written and 12 bytes per candidate inserted)."""
     from sparsetriton_b200 import synthetic, trace
     from sparsetriton_b200.config import set_coords_dtype
     from sparsetriton_b200.nn.functional.conv.conv import compute_neighbor_indices
     from sparsetriton_b200.nn.functional.conv.kmap import build_out_coords, out_coords_and_map
     from sparsetriton_b200.utils.hash import HashTable
 
-    dist, world, rank, local, dev = _dist_setup(args)
     set_coords_dtype(torch.int32)
-    n, grid = args.cells, 2048
-    coords = synthetic.random_cells(n, 4, grid, seed=2001 + rank).to(dev)
+    grid = 2048
+    coords = synthetic.random_cells(n, 4, grid, seed=seed).to(dev)
     shape = (grid,) * 3
     cap = 1 << (2 * n - 1).bit_length()
 
@@ -466,68 +653,74 @@ def run_hash_map(args):
             _, _, ko = build_out_coords(coords, shape, k, 1, 1, (k - 1) // 2, submanifold=True)
             with trace.stage(f"subm_map_k{k}"):
                 res[k] = compute_neighbor_indices(t, coords, ko, shape, 1, queries_are_table_rows=True)
-        oc, ns, ko, nbr = out_coords_and_map(coords, shape, 3, 2, 1, 1, False)
-        oc2, ns2, ko2, nbr2 = out_coords_and_map(oc, ns, 3, 2, 1, 1, True)
+        with trace.stage("down_k3s2"):
+            oc, ns, ko, nbr = out_coords_and_map(coords, shape, 3, 2, 1, 1, False)
+        with trace.stage("up_k3s2"):
+            oc2, ns2, ko2, nbr2 = out_coords_and_map(oc, ns, 3, 2, 1, 1, True)
         return res, nbr, nbr2, oc, oc2
 
-    res, nbr, nbr2, oc, oc2 = step()
     def count_pairs(m, rows=1 << 22):
-        """Valid entries of a map, a few million rows at a time (the transposed map has > 3e9 entries)."""
+        """Valid entries of a map, a few million rows at a time (the transposed map has > 3e9 entries at 8 M cells)."""
         return sum(int((m[i:i + rows] >= 0).sum()) for i in range(0, m.shape[0], rows))
 
+    res, nbr, nbr2, oc, oc2 = step()
     pairs = {"k3": count_pairs(res[3]), "k5": count_pairs(res[5]), "down": count_pairs(nbr), "up": count_pairs(nbr2)}
     n_down, n_up = oc.shape[0], oc2.shape[0]
     del res, nbr, nbr2, oc, oc2
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with trace.recording() as rec:
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
         e0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             step()
         e1.record()
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize()
         stages = rec.summary()
         launches = rec.total_launches()
     ms = e0.elapsed_time(e1)
+    pk = peaks()
+    per = {k: v["ms"] / steps for k, v in stages.items()}
+    cand_down = n * 27 / 8.0
+    algo = {
+        "hash_build": 52.0 * n,
+        "subm_map_k3": n * (16 + 12 * 27) + 4.0 * pairs["k3"],
+        "subm_map_k5": n * (16 + 12 * 125) + 4.0 * pairs["k5"],
+        "down_k3s2": 16.0 * n + 12.0 * cand_down + 16.0 * n_down + n_down * (16 + 12 * 27) + 4.0 * pairs["down"],
+        "up_k3s2": 16.0 * n_down + 12.0 * 27 * n_down + 16.0 * n_up + n_up * (16 + 12 * 27) + 4.0 * pairs["up"],
+    }
+    roof = {}
+    for name, nbytes in algo.items():
+        if name in per and per[name] > 0:
+            gbs = nbytes / (per[name] * 1e-3) / 1e9
+            roof[name] = {"ms": per[name], "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"]}
+    return {"cells": n, "table_capacity": cap, "ms_per_step": ms / steps, "pairs": pairs, "n_out_down": n_down,
+            "n_out_up": n_up, "stages_ms": per, "stage_rooflines": roof, "launches": launches / steps}
+
+
+def run_hash_map(args):
+    dist, world, rank, local, dev = _dist_setup(args)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    r = hash_map_measure(dev, args.cells, 2001 + rank, max(args.warmup, 3), args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    (ms_step,) = _max_over_ranks(dist, world, dev, [r["ms_per_step"]])
     if rank == 0:
         pk = peaks()
-        per = {k: v["ms"] / args.steps for k, v in stages.items()}
-        # algorithmic bytes (coords 16 B, one 8 B key probe + 4 B map entry per (voxel, offset), 4 B value per hit)
-        algo = {
-            "hash_build": 52.0 * n,
-            "subm_map_k3": n * (16 + 12 * 27) + 4.0 * pairs["k3"],
-            "subm_map_k5": n * (16 + 12 * 125) + 4.0 * pairs["k5"],
-        }
-        roof = {}
-        for name, nbytes in algo.items():
-            if name in per and per[name] > 0:
-                gbs = nbytes / (per[name] * 1e-3) / 1e9
-                roof[name] = {"ms": per[name], "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac": gbs / pk["hbm_gbs"]}
+        roof = r["stage_rooflines"]
         top = max(roof, key=lambda k: roof[k]["ms"])
-        ms_step = t.item() / args.steps
         print(json.dumps({
-            "metric": "hash_and_kernel_map_voxels_per_s", "value": world * n / (ms_step * 1e-3), "unit": "voxels/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "metric": "hash_and_kernel_map_voxels_per_s", "value": world * r["cells"] / (ms_step * 1e-3), "unit": "voxels/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64 keys / int32 coords",
             "data": "synthetic",
             "config": {"workload": "hash_map_c2: %d random cells, batch 4, grid 2048^3, table capacity %d; build + subm k3 + "
-                                   "subm k5 + k3s2p1 down (coords+map) + transposed map" % (n, cap),
-                       "pairs": pairs, "n_out_down": n_down, "n_out_up": n_up, "l2_policy": "tables and maps larger than L2"},
-            "gpu_launches": launches, "stages": per, "stage_rooflines": roof,
+                                   "subm k5 + k3s2p1 down (coords+map) + transposed map" % (r["cells"], r["table_capacity"]),
+                       "pairs": r["pairs"], "n_out_down": r["n_out_down"], "n_out_up": r["n_out_up"],
+                       "l2_policy": "tables and maps larger than L2"},
+            "gpu_launches": r["launches"] * args.steps, "stages": r["stages_ms"], "stage_rooflines": roof,
             "roofline": {"kernel": top, "bound": "hbm", "achieved": roof[top]["achieved_gbs"], "peak": pk["hbm_gbs"],
                          "unit": "GB/s", "frac": roof[top]["frac"], "traffic": None, "peak_source": pk["source"]},
             "clocks": clocks,
@@ -536,6 +729,7 @@ def run_hash_map(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------- U-Net workloads
 def make_lidar_batch(samples):
     """(coords (N,4) int32 with batch relabelled from 0, feats (N,4) fp32) of the given scene seeds."""
     from sparsetriton_b200 import synthetic
@@ -547,41 +741,45 @@ def make_lidar_batch(samples):
     return coords, feats
 
 
-def run_unet(args, train):
-    """BASELINE configs 4 / 5: lidar-like sparse U-Net, bf16 features, fp32 master weights."""
+def unet_measure(args, dist, world, rank, dev, train, steps, warmup, prune=True, e2e=True, samples=None):
+    """BASELINE configs 4 / 5: lidar-like sparse U-Net, bf16 features, fp32 master weights; batch 8 (inference) or 16
+    (training) sharded by sample over the ranks.  Returns ms per step (max over ranks) and the stage breakdown."""
     from sparsetriton_b200 import trace
     from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype, set_h_table_f
     from sparsetriton_b200.distributed import GradientBucket, global_mean_scale, shard_samples
     from sparsetriton_b200.tensor import SparseTensor
     from sparsetriton_b200.unet import SparseUNet
 
-    dist, world, rank, local, dev = _dist_setup(args)
     set_coords_dtype(torch.int32)
     set_h_table_f(2.0)
     set_conv_algo(ConvAlgo.ImplicitHashFlyGEMM if args.algo == "hashfly" else ConvAlgo.PrecomputedNeighborGEMM)
-    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    dtype = DTYPES[args.dtype]
     total_batch = 16 if train else 8
     base_seed = 5000 if train else 4000
-    mine = shard_samples(total_batch, rank, world)
-    coords_h, feats_h = make_lidar_batch([base_seed + i for i in mine])
+    if samples is None:
+        mine = shard_samples(total_batch, rank, world)
+        seeds = [base_seed + i for i in mine]
+    else:
+        seeds, total_batch = list(samples), len(samples)
+    coords_h, feats_h = make_lidar_batch(seeds)
     coords_h, feats_h = coords_h.pin_memory(), feats_h.to(dtype).pin_memory()
     shape = (1440, 1440, 41)
     torch.manual_seed(5100 if train else 4100)
-    model = SparseUNet().to(dev)
+    model = SparseUNet(prune=prune).to(dev)
     model.train(train)
     n_in = coords_h.shape[0]
     opt = bucket = None
     if train:
         bucket = GradientBucket(model.parameters())
         opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
-
     state = {"labels": None, "scale": None, "n_out": None}
 
     def step(coords, feats):
-        x = SparseTensor._trusted(feats, coords, shape, len(mine))
+        x = SparseTensor._trusted(feats, coords, shape, len(seeds))
         if not train:
             with torch.no_grad():
                 out = model(x)
+            state["n_out"] = out.F.shape[0]
             return out.F
         out = model(x)
         if state["labels"] is None:
@@ -598,70 +796,50 @@ def run_unet(args, train):
         return loss.detach()
 
     coords_d, feats_d = coords_h.to(dev), feats_h.to(dev)
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step(coords_d, feats_d)
+    dev_ms = _event_ms(dist, world, lambda _i: step(coords_d, feats_d), steps)
+    # stage breakdown and launch count: one more step with the stage recorder on (kept out of the timed steps)
+    with trace.recording() as rec:
+        step(coords_d, feats_d)
+        _sync_all(dist, world)
+        stages, launches = rec.summary(), rec.total_launches()
+    e2e_ms = None
+    if e2e:
+        result_h = torch.zeros(1, dtype=torch.float32).pin_memory()
 
-    def sync_all():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+        def e2e_step(_i):
+            c = coords_h.to(dev, non_blocking=True)
+            f = feats_h.to(dev, non_blocking=True)
+            r = step(c, f)
+            result_h.copy_(r.float().sum().reshape(1), non_blocking=True)
 
-    sync_all()
+        for i in range(2):
+            e2e_step(i)
+        e2e_ms = _event_ms(dist, world, e2e_step, steps)
+    vals = _max_over_ranks(dist, world, dev, [dev_ms, e2e_ms or 0.0])
+    (total_voxels,) = _sum_over_ranks(dist, world, dev, [float(n_in)])
+    del model, opt, bucket
+    return {"ms_per_step": vals[0] / steps, "e2e_ms_per_step": (vals[1] / steps) if e2e else None, "stages": stages,
+            "launches": launches, "kernel_ms": sum(v["ms"] for v in stages.values()), "total_voxels": total_voxels,
+            "total_batch": total_batch, "n_in": n_in, "n_out": state["n_out"], "local_samples": len(seeds),
+            "h2d": coords_h.numel() * 4 + feats_h.numel() * feats_h.element_size()}
+
+
+def run_unet(args, train):
+    dist, world, rank, local, dev = _dist_setup(args)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    e0.record()
-    for _ in range(args.steps):
-        step(coords_d, feats_d)
-    e1.record()
-    sync_all()
-    dev_ms = e0.elapsed_time(e1)
-    # stage breakdown and launch count: a second pass with the stage recorder on (kept out of the timed pass)
-    with trace.recording() as rec:
-        for _ in range(args.steps):
-            step(coords_d, feats_d)
-        sync_all()
-        stages = rec.summary()
-        launches = rec.total_launches()
-
-    result_h = torch.zeros(1, dtype=torch.float32).pin_memory()
-
-    def e2e_step():
-        c = coords_h.to(dev, non_blocking=True)
-        f = feats_h.to(dev, non_blocking=True)
-        r = step(c, f)
-        result_h.copy_(r.float().sum().reshape(1), non_blocking=True)
-
-    for _ in range(2):
-        e2e_step()
-    sync_all()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    f1.record()
-    sync_all()
-    e2e_ms = f0.elapsed_time(f1)
+    r = unet_measure(args, dist, world, rank, dev, train, args.steps, max(args.warmup, 3), prune=not args.literal_decoder)
     clocks = sampler.stop() if rank == 0 else None
-
-    t = torch.tensor([dev_ms, e2e_ms, float(n_in)], dtype=torch.float64, device=dev)
-    if world > 1:
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = t.clone()
-        dist.all_reduce(tsum)
-        dev_ms, e2e_ms, total_voxels = tmax[0].item(), tmax[1].item(), tsum[2].item()
-    else:
-        total_voxels = float(n_in)
     if rank == 0:
         pk = peaks()
-        ms_step = dev_ms / args.steps
-        per = {k: {"ms_per_step": v["ms"] / args.steps, "launches_per_step": v["launches"] / args.steps,
-                   "calls_per_step": v["calls"] / args.steps,
+        dtype = DTYPES[args.dtype]
+        ms_step = r["ms_per_step"]
+        per = {k: {"ms_per_step": v["ms"], "launches_per_step": v["launches"], "calls_per_step": v["calls"],
                    "tflops": (v["work"] / (v["ms"] * 1e-3) / 1e12) if v["work"] and v["ms"] > 0 else None}
-               for k, v in stages.items()}
+               for k, v in r["stages"].items()}
         conv = [k for k in per if k.startswith("conv_")]
         top = max(conv, key=lambda k: per[k]["ms_per_step"]) if conv else None
         roof = None
@@ -672,17 +850,19 @@ def run_unet(args, train):
                     "share_of_step": per[top]["ms_per_step"] / ms_step}
         print(json.dumps({
             "metric": "sparse_unet_%s_voxels_per_s" % ("train_step" if train else "inference"),
-            "value": total_voxels / (ms_step * 1e-3), "unit": "voxels/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "value": r["total_voxels"] / (ms_step * 1e-3), "unit": "voxels/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
             "config": {"workload": "%s: lidar-like U-Net 4->32/64/128/256->...->32->20, grid 1440x1440x41, batch %d "
-                                   "(%d samples on this rank, %d voxels)" % (args.workload, total_batch, len(mine), n_in),
+                                   "(%d samples on this rank, %d voxels)" % (args.workload, r["total_batch"], r["local_samples"],
+                                                                             r["n_in"]),
+                       "decoder": "literal (every child of the transposed convolution)" if args.literal_decoder
+                                  else "up-convolution evaluated at the encoder's coordinates (prune=True)",
                        "algo": args.algo, "parallelism": "dp%d by sample%s" % (world, ", NCCL all-reduce of one flat gradient bucket" if train else ""),
                        "l2_policy": "activations of every level exceed L2"},
-            "e2e": {"value": total_voxels / (e2e_ms / args.steps * 1e-3), "unit": "voxels/s",
-                    "h2d_bytes_per_step": coords_h.numel() * 4 + feats_h.numel() * feats_h.element_size(),
-                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": launches, "stages": per, "roofline": roof, "clocks": clocks,
+            "e2e": {"value": r["total_voxels"] / (r["e2e_ms_per_step"] * 1e-3), "unit": "voxels/s",
+                    "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 4, "ms_per_step": r["e2e_ms_per_step"]},
+            "gpu_launches": r["launches"] * args.steps, "stages": per, "roofline": roof, "clocks": clocks,
         }))
     if world > 1:
         dist.destroy_process_group()
@@ -699,7 +879,11 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--per-sample", type=int, default=PER_SAMPLE, dest="per_sample")
     ap.add_argument("--grid", type=int, default=GRID)
+    ap.add_argument("--passes", type=int, default=32, help="conv_layer_c3: passes of the hot path per step")
+    ap.add_argument("--batches", type=int, default=4, help="conv_layer_c3: distinct seeded batches cycled through")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-legs", action="store_true", help="conv_layer_c3: skip the extra legs (variants, config 2, U-Net, reference on GPU)")
+    ap.add_argument("--literal-decoder", action="store_true", help="unet_*: keep every child of the transposed convolutions")
     ap.add_argument("--workload", default="conv_layer_c3",
                     choices=["conv_layer_c3", "hash_map_c2", "unet_infer", "unet_train"])
     ap.add_argument("--cells", type=int, default=8_000_000, help="hash_map_c2: number of coordinates")

@@ -424,10 +424,15 @@ def run_ours(args):
 
 # ------------------------------------------------------------------------------------------------ legs
 def c3_variant_legs(args, dist, world, rank, dev):
-    """The same layer with the hash-on-the-fly algorithm and in fp16: ms per pass (max over ranks), one batch."""
+    """The same layer with the hash-on-the-fly algorithm (scratch map per call, and probing inside the kernels) and in
+    fp16: ms per pass (max over ranks), one batch."""
     out = {}
-    for key, algo, dt in (("c3_hashfly_ms_per_step", "hashfly", args.dtype), ("c3_fp16_ms_per_step", "precomputed", "fp16")):
+    from sparsetriton_b200.config import set_hashfly_transient_map
+    for key, algo, dt, transient in (("c3_hashfly_ms_per_step", "hashfly", args.dtype, True),
+                                     ("c3_hashfly_in_kernel_probing_ms_per_step", "hashfly", args.dtype, False),
+                                     ("c3_fp16_ms_per_step", "precomputed", "fp16", True)):
         try:
+            set_hashfly_transient_map(transient)
             layer = C3Layer(args, dist, world, rank, dev, DTYPES[dt], algo, 1)
             for _ in range(3):
                 layer.one_pass(0)
@@ -442,6 +447,7 @@ def c3_variant_legs(args, dist, world, rank, dev):
         torch.cuda.empty_cache()
     from sparsetriton_b200.config import ConvAlgo, set_conv_algo
     set_conv_algo(ConvAlgo.PrecomputedNeighborGEMM)
+    set_hashfly_transient_map(True)
     return out
 
 

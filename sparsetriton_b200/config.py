@@ -10,7 +10,7 @@ import torch
 __all__ = [
     "ConvAlgo", "set_coords_dtype", "get_coords_dtype", "set_conv_algo", "get_conv_algo",
     "set_h_table_f", "get_h_table_f", "set_h_table_max_p", "get_h_table_max_p",
-    "set_row_order", "get_row_order",
+    "set_row_order", "get_row_order", "set_hashfly_transient_map", "get_hashfly_transient_map",
 ]
 
 
@@ -26,6 +26,7 @@ _STATE = {
     "h_tbl_factor": 1.5,       # minimum slots per key; tables are rounded up to a power of two
     "h_tbl_max_probe_n": 16,   # kept for API parity; probing here is bounded by the capacity
     "row_order": True,         # stored-map products walk rows sorted by occupied offsets (no reference counterpart)
+    "hashfly_transient_map": True,   # hash-on-the-fly probes once per call into scratch, not once per tile and kernel
 }
 
 
@@ -86,3 +87,19 @@ def set_row_order(enabled):
 
 def get_row_order():
     return _STATE["row_order"]
+
+
+def set_hashfly_transient_map(enabled):
+    """How ImplicitHashFlyGEMM finds its neighbours.  True (default): each forward and each backward call probes
+    the table once into a scratch map that lives for that call only (nothing is kept between calls, which is
+    what distinguishes the algorithm from PrecomputedNeighborGEMM) and runs the tile-planned tensor-core kernels
+    over it.  False: the kernels probe the table themselves, per tile and per kernel, as the reference's
+    Triton kernels do; no scratch map exists at any time (lowest memory, several times slower).  Results are
+    identical.  No counterpart in the reference."""
+    if not isinstance(enabled, bool):
+        raise TypeError(f"Expected bool, got {type(enabled)}")
+    _STATE["hashfly_transient_map"] = enabled
+
+
+def get_hashfly_transient_map():
+    return _STATE["hashfly_transient_map"]

@@ -18,7 +18,8 @@ from sparsetriton_b200 import _lib, trace
 
 from ._channels import pad_cols, pad_weight, padded_widths
 
-__all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map", "map_plan", "MapPlan"]
+__all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map", "map_plan", "MapPlan", "stored_map_forward", "stored_map_dgrad",
+           "stored_map_wgrad"]
 
 # below this many rows the sort costs more than the denser tiles save
 _MIN_ROWS_FOR_ORDER = 16384
@@ -121,6 +122,78 @@ def _is_symmetric(map_tensor, n_in):
     return flag
 
 
+def stored_map_forward(x, w, nbr, n_in):
+    """Y = sum_k X[nbr[:, k]] . W[k] over a stored map; x, w already padded and contiguous.  Returns (y, flops)."""
+    K, c_in, c_out = w.shape
+    n_out = nbr.shape[0]
+    code = _lib.feat_code(x)
+    y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
+    flops = 2.0 * trace.map_pairs(nbr) * c_in * c_out if trace.active() else 0.0
+    if n_out > 0:
+        # the plan only serves the tensor-core kernels
+        plan = map_plan(nbr) if _lib.lib().st_conv_uses_tensor_cores(code, c_in, c_out) else _NO_PLAN
+        with torch.cuda.device(x.device), trace.stage("conv_fwd", work=flops):
+            rc = _lib.lib().st_conv_fwd_planned(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
+                                                _lib.ptr(y), n_in, n_out, K, c_in, c_out, None, 0, _lib.stream_ptr())
+        _lib.check(rc, "st_conv_fwd_planned")
+    return y, flops
+
+
+def stored_map_dgrad(dy, w, nbr, n_in, flops=0.0):
+    """dX = sum_k dY[inv[:, k]] . W[k]^T; the inverse map is read through its plan (built straight from `nbr`) or,
+    for a symmetric submanifold map, is `nbr` itself with the offsets reversed."""
+    K, c_in, c_out = w.shape
+    n_out = nbr.shape[0]
+    code = _lib.feat_code(dy)
+    L = _lib.lib()
+    dx = torch.empty((n_in, c_in), device=dy.device, dtype=dy.dtype)
+    if n_in == 0:
+        return dx
+    with torch.cuda.device(dy.device):
+        stream = _lib.stream_ptr()
+        tc = bool(L.st_conv_uses_tensor_cores(code, c_out, c_in))
+        if tc and _is_symmetric(nbr, n_in):
+            # submanifold layer: the map is its own inverse with the offsets reversed
+            plan = map_plan(nbr)
+            with trace.stage("conv_dgrad", work=flops):
+                rc = L.st_conv_dgrad_mirrored(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
+                                              _lib.ptr(dx), n_in, K, c_in, c_out, None, 0, stream)
+            _lib.check(rc, "st_conv_dgrad_mirrored")
+        elif tc and inverse_plan(nbr, n_in) is not None:
+            # the kernels read the inverse map only through its plan, which comes straight from nbr
+            plan = inverse_plan(nbr, n_in)
+            with trace.stage("conv_dgrad", work=flops):
+                rc = L.st_conv_dgrad_planned(code, _lib.ptr(dy), _lib.ptr(w), None, *plan.ptrs(),
+                                             _lib.ptr(dx), n_in, n_out, K, c_in, c_out, None, 0, stream)
+            _lib.check(rc, "st_conv_dgrad_planned")
+        else:
+            inv = inverse_map(nbr, n_in)
+            plan = map_plan(inv) if tc else _NO_PLAN
+            with trace.stage("conv_dgrad", work=flops):
+                rc = L.st_conv_dgrad_planned(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv), *plan.ptrs(),
+                                             _lib.ptr(dx), n_in, n_out, K, c_in, c_out, None, 0, stream)
+            _lib.check(rc, "st_conv_dgrad_planned")
+    return dx
+
+
+def stored_map_wgrad(x, dy, nbr, K, flops=0.0):
+    """dW[k] = sum_o X[nbr[o, k]]^T . dY[o], in the dtype of x."""
+    n_in, c_in = x.shape
+    n_out, c_out = dy.shape
+    code = _lib.feat_code(x)
+    L = _lib.lib()
+    dw = torch.empty((K, c_in, c_out), device=x.device, dtype=x.dtype)
+    with torch.cuda.device(x.device):
+        ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
+        plan = map_plan(nbr) if L.st_conv_uses_tensor_cores(code, c_in, c_out) else _NO_PLAN
+        with trace.stage("conv_wgrad", work=flops):
+            rc = L.st_conv_wgrad_planned(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), *plan.ptrs(),
+                                         _lib.ptr(dw), n_in, n_out, K, c_in, c_out, _lib.ptr(ws), ws.numel(),
+                                         _lib.stream_ptr())
+        _lib.check(rc, "st_conv_wgrad_planned")
+    return dw
+
+
 class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, features, weights, neighbor_indices):
@@ -128,7 +201,6 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         n_in, c_in = features.shape
         K, w_cin, c_out = weights.shape
         assert w_cin == c_in, f"weights expect {w_cin} input channels, features have {c_in}"
-        n_out = neighbor_indices.shape[0]
         assert neighbor_indices.shape[1] == K, "neighbor_indices must be (N_out, K)"
 
         ctx.true_widths = (c_in, c_out)
@@ -137,18 +209,7 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         w = pad_weight(weights.to(x.dtype), c_in, c_out).contiguous()
         nbr = neighbor_indices if neighbor_indices.is_contiguous() else neighbor_indices.contiguous()
         assert nbr.dtype == torch.int32, "neighbor_indices must be int32"
-        code = _lib.feat_code(x)
-        y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
-        ctx.flops = 2.0 * trace.map_pairs(nbr) * c_in * c_out if trace.active() else 0.0
-        # the plan only serves the tensor-core kernels
-        use_plan = ctx.use_plan = bool(_lib.lib().st_conv_uses_tensor_cores(code, c_in, c_out))
-        if n_out > 0:
-            plan = map_plan(nbr) if use_plan else _NO_PLAN
-            with torch.cuda.device(x.device), trace.stage("conv_fwd", work=ctx.flops):
-                rc = _lib.lib().st_conv_fwd_planned(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
-                                                    _lib.ptr(y), n_in, n_out, K, c_in, c_out, None, 0,
-                                                    _lib.stream_ptr())
-            _lib.check(rc, "st_conv_fwd_planned")
+        y, ctx.flops = stored_map_forward(x, w, nbr, n_in)
         ctx.save_for_backward(x, w, nbr)
         ctx.w_dtype = weights.dtype
         return y if c_out == ctx.true_widths[1] else y[:, :ctx.true_widths[1]].contiguous()
@@ -158,47 +219,13 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         x, w, nbr = ctx.saved_tensors
         n_in, c_in = x.shape
         K, _, c_out = w.shape
-        n_out = nbr.shape[0]
         t_in, t_out = ctx.true_widths
         dy = pad_cols(grad_output.to(x.dtype), c_out).contiguous()
-        code = _lib.feat_code(x)
-        L = _lib.lib()
         dx = dw = None
-        with torch.cuda.device(x.device):
-            stream = _lib.stream_ptr()
-            if ctx.needs_input_grad[0]:
-                dx = torch.empty_like(x)
-                if n_in > 0 and _is_symmetric(nbr, n_in) and L.st_conv_uses_tensor_cores(code, c_out, c_in):
-                    # submanifold layer: the map is its own inverse with the offsets reversed
-                    plan = map_plan(nbr)
-                    with trace.stage("conv_dgrad", work=ctx.flops):
-                        rc = L.st_conv_dgrad_mirrored(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
-                                                      _lib.ptr(dx), n_in, K, c_in, c_out, None, 0, stream)
-                    _lib.check(rc, "st_conv_dgrad_mirrored")
-                elif n_in > 0 and L.st_conv_uses_tensor_cores(code, c_out, c_in) and inverse_plan(nbr, n_in) is not None:
-                    # the kernels read the inverse map only through its plan, which comes straight from nbr
-                    plan = inverse_plan(nbr, n_in)
-                    with trace.stage("conv_dgrad", work=ctx.flops):
-                        rc = L.st_conv_dgrad_planned(code, _lib.ptr(dy), _lib.ptr(w), None, *plan.ptrs(),
-                                                     _lib.ptr(dx), n_in, n_out, K, c_in, c_out, None, 0, stream)
-                    _lib.check(rc, "st_conv_dgrad_planned")
-                elif n_in > 0:
-                    inv = inverse_map(nbr, n_in)
-                    plan = map_plan(inv) if L.st_conv_uses_tensor_cores(code, c_out, c_in) else _NO_PLAN
-                    with trace.stage("conv_dgrad", work=ctx.flops):
-                        rc = L.st_conv_dgrad_planned(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv), *plan.ptrs(),
-                                                     _lib.ptr(dx), n_in, n_out, K, c_in, c_out, None, 0, stream)
-                    _lib.check(rc, "st_conv_dgrad_planned")
-            if ctx.needs_input_grad[1]:
-                dw = torch.empty_like(w)
-                ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
-                plan = map_plan(nbr) if ctx.use_plan else _NO_PLAN
-                with trace.stage("conv_wgrad", work=ctx.flops):
-                    rc = L.st_conv_wgrad_planned(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), *plan.ptrs(),
-                                                 _lib.ptr(dw), n_in, n_out, K, c_in, c_out, _lib.ptr(ws), ws.numel(),
-                                                 stream)
-                _lib.check(rc, "st_conv_wgrad_planned")
-                dw = dw.to(ctx.w_dtype)
+        if ctx.needs_input_grad[0]:
+            dx = stored_map_dgrad(dy, w, nbr, n_in, ctx.flops)
+        if ctx.needs_input_grad[1]:
+            dw = stored_map_wgrad(x, dy, nbr, K, ctx.flops).to(ctx.w_dtype)
         if dx is not None and t_in != c_in:
             dx = dx[:, :t_in].contiguous()
         if dw is not None and (t_in != c_in or t_out != c_out):

@@ -4,10 +4,27 @@ import torch
 
 import sparsetriton_b200 as st
 from sparsetriton_b200 import _lib
-from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype
+from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype, set_hashfly_transient_map
 from sparsetriton_b200.nn.functional import sparse_conv3d
 
 TOL = {torch.float32: 2e-3, torch.float16: 1e-2, torch.bfloat16: 1e-2}
+
+
+class Algo:
+    """A convolution algorithm as the tests select it: the reference's two ConvAlgo values, the hash-on-the-fly one
+    in both of its forms here (scratch map per call / probing inside the kernels)."""
+
+    def __init__(self, algo, transient, name):
+        self.algo, self.transient, self.name = algo, transient, name
+
+    def use(self):
+        set_conv_algo(self.algo)
+        set_hashfly_transient_map(self.transient)
+
+
+ALGOS = [Algo(ConvAlgo.PrecomputedNeighborGEMM, True, "PrecomputedNeighborGEMM"),
+         Algo(ConvAlgo.ImplicitHashFlyGEMM, True, "ImplicitHashFlyGEMM"),
+         Algo(ConvAlgo.ImplicitHashFlyGEMM, False, "ImplicitHashFlyGEMM_in_kernel")]
 
 
 def rel_err(got, want):
@@ -57,7 +74,7 @@ def run_conv(dev, coords, shape, batch, feats, weight, bias, dy, k, s, p, d, tra
     """sparse_conv3d forward + backward through the public API.  Returns numpy
     (out_coords, new_shape, y, dx, dw, db)."""
     set_coords_dtype(coord_dtype)
-    set_conv_algo(algo)
+    algo.use() if isinstance(algo, Algo) else set_conv_algo(algo)
     x = torch.as_tensor(feats).to(dev, dtype).requires_grad_(True)
     w = torch.as_tensor(weight).to(dev, dtype).requires_grad_(True)
     b = None

@@ -3,7 +3,8 @@
   config 2   2 M random cells of 4 x 2048^3: table, submanifold maps k3 / k5, the k3 s2 p1 downsample (ordered
              output coordinates + map) and the transposed k3 s2 p1 map built from its output coordinates; every
              map entry identical to oracle.neighbor_map (compared a few million rows at a time)
-  config 3   SparseConv3D 64 -> 128, k3 s2 p1, 4 x 300 k surface voxels, both algorithms x {fp16, bf16}: Y, dX, dW
+  config 3   SparseConv3D 64 -> 128, k3 s2 p1, 4 x 300 k surface voxels, both algorithms (hash-on-the-fly in both of its forms)
+             x {fp16, bf16}: Y, dX, dW
              within 1e-2 of the fp32 oracle in max-norm, RMS and row-wise relative error (gpu_util.check_close)
   configs 4/5  the U-Net on a small two-sample scene, fp32 and bf16, literal and pruned decoder, against the
              host composition oracle/unet_oracle.py: logits and every parameter gradient
@@ -13,7 +14,7 @@ import pytest
 import torch
 
 import sparsetriton_b200 as st
-from gpu_util import check_close, map_triples, rel_err, rms_err, t2n
+from gpu_util import ALGOS, check_close, map_triples, rel_err, rms_err, t2n
 from sparsetriton_b200 import _lib, synthetic
 from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype, set_h_table_f
 from sparsetriton_b200.nn.functional import sparse_conv3d
@@ -121,8 +122,8 @@ def test_config3_layer_full_size(cuda_device, oracle, dtype):
     want_y = oracle.conv_fwd(f32(feats), f32(weight), wnbr)
     want_dx = oracle.conv_dgrad(f32(dy), f32(weight), wnbr, n_in)
     want_dw = oracle.conv_wgrad(f32(feats), f32(dy), wnbr, 27, 64, 128)
-    for algo in (ConvAlgo.PrecomputedNeighborGEMM, ConvAlgo.ImplicitHashFlyGEMM):
-        set_conv_algo(algo)
+    for algo in ALGOS:                                  # stored map, hash-on-the-fly with a scratch map, and probing in the kernels
+        algo.use()
         x = feats.to(dev).requires_grad_(True)
         w = weight.to(dev).requires_grad_(True)
         sp = st.SparseTensor(x, coords.to(dev), spatial_shape=shape, batch_size=4)
@@ -132,7 +133,7 @@ def test_config3_layer_full_size(cuda_device, oracle, dtype):
         check_close(t2n(out.F), want_y, 1e-2, f"{algo.name} Y")
         check_close(t2n(dx), want_dx, 1e-2, f"{algo.name} dX")
         check_close(t2n(dw).reshape(27 * 64, 128), want_dw.reshape(27 * 64, 128), 1e-2, f"{algo.name} dW")
-        if algo == ConvAlgo.PrecomputedNeighborGEMM:
+        if algo.algo == ConvAlgo.PrecomputedNeighborGEMM:
             nbr = sp._cache.neighbor_indices[(3, 2, 1, 1, False, False)][1]
             assert np.array_equal(nbr.cpu().numpy(), wnbr), "neighbour map differs from the oracle"
         del out, dx, dw, sp

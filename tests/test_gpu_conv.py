@@ -10,7 +10,7 @@ import torch
 import torch.nn.functional as TF
 
 from conftest import case_id, golden_files, load_golden
-from gpu_util import TOL, rel_err, run_conv, t2n
+from gpu_util import ALGOS, TOL, rel_err, run_conv, t2n
 import sparsetriton_b200 as st
 from sparsetriton_b200 import synthetic
 from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype
@@ -18,7 +18,6 @@ from sparsetriton_b200.nn.functional import sparse_conv3d
 
 pytestmark = pytest.mark.gpu
 
-ALGOS = [ConvAlgo.PrecomputedNeighborGEMM, ConvAlgo.ImplicitHashFlyGEMM]
 
 
 @pytest.fixture(autouse=True)
@@ -94,7 +93,7 @@ def test_c1_headline_case(cuda_device, oracle, algo):
 
 def test_c1_map_is_exact(cuda_device, oracle):
     from test_gpu_kmap import gpu_kernel_map
-    from gpu_util import map_triples
+    from gpu_util import ALGOS, map_triples
     g = load_golden(golden_files("c1_")[0])
     _, _, _, nbr = gpu_kernel_map(cuda_device, g["coords"], (64, 64, 64), 3, 1, 1, 1, False, True)
     exact = oracle.kernel_map(g["coords"], (64, 64, 64), 3, 1, 1, 1, False, True)[3]

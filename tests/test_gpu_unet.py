@@ -7,7 +7,7 @@ import torch
 import sparsetriton_b200 as st
 from gpu_util import rel_err
 from sparsetriton_b200 import _lib, synthetic
-from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype
+from sparsetriton_b200.config import ConvAlgo, set_conv_algo, set_coords_dtype, set_hashfly_transient_map
 from sparsetriton_b200.unet import SparseUNet, skip_concat, up_conv_onto
 
 pytestmark = pytest.mark.gpu
@@ -27,8 +27,9 @@ def _scene(dev, batch=2):
     return coords.to(dev), feats.to(dev)
 
 
-def _run(model, coords, feats, labels_seed, dtype, algo, tensor_cores):
+def _run(model, coords, feats, labels_seed, dtype, algo, tensor_cores, transient=True):
     set_conv_algo(algo)
+    set_hashfly_transient_map(transient)
     _lib.lib().st_set_tensor_cores(int(tensor_cores))
     model.zero_grad(set_to_none=True)
     x = st.SparseTensor(feats.to(dtype), coords, spatial_shape=SHAPE, batch_size=2)
@@ -55,9 +56,9 @@ def test_unet_algorithms_and_kernels_agree(cuda_device, dtype):
     # live in test_gpu_conv.py.  The gradient bound leaves room for the run-to-run spread of the batch-norm
     # sums (fp32 atomics): 1.9e-2 .. 2.1e-2 was observed.
     tol_out, tol_grad = (5e-3, 3e-2) if dtype == torch.float32 else (5e-2, 1.5e-1)
-    for algo, tcores in [(ConvAlgo.PrecomputedNeighborGEMM, True), (ConvAlgo.ImplicitHashFlyGEMM, True),
-                         (ConvAlgo.ImplicitHashFlyGEMM, False)]:
-        got = _run(model, coords, feats, 1, dtype, algo, tcores)
+    for algo, tcores, transient in [(ConvAlgo.PrecomputedNeighborGEMM, True, True), (ConvAlgo.ImplicitHashFlyGEMM, True, True),
+                                    (ConvAlgo.ImplicitHashFlyGEMM, True, False), (ConvAlgo.ImplicitHashFlyGEMM, False, False)]:
+        got = _run(model, coords, feats, 1, dtype, algo, tcores, transient)
         assert np.array_equal(got[0], ref[0]), "output coordinates differ between algorithms"
         assert rel_err(got[1], ref[1]) < tol_out, (algo, tcores, rel_err(got[1], ref[1]))
         assert abs(got[2] - ref[2]) < tol_out * max(1.0, abs(ref[2]))

@@ -274,6 +274,9 @@ def run_ours(args):
     set_coords_dtype(torch.int32)
     set_h_table_f(2.0)
     dtype = DTYPES[args.dtype]
+    if args.hashfly_in_kernel:
+        from sparsetriton_b200.config import set_hashfly_transient_map
+        set_hashfly_transient_map(False)
     layer = C3Layer(args, dist, world, rank, dev, dtype, args.algo, args.batches)
     passes = args.passes
 
@@ -889,6 +892,8 @@ def main():
     ap.add_argument("--batches", type=int, default=4, help="conv_layer_c3: distinct seeded batches cycled through")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-legs", action="store_true", help="conv_layer_c3: skip the extra legs (variants, config 2, U-Net, reference on GPU)")
+    ap.add_argument("--hashfly-in-kernel", action="store_true",
+                    help="with --algo hashfly: probe the table inside the GEMM kernels instead of into a scratch map per call")
     ap.add_argument("--literal-decoder", action="store_true", help="unet_*: keep every child of the transposed convolutions")
     ap.add_argument("--workload", default="conv_layer_c3",
                     choices=["conv_layer_c3", "hash_map_c2", "unet_infer", "unet_train"])

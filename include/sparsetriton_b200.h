@@ -228,6 +228,16 @@ int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_
                           const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K,
                           int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* The weight gradient walked over the plan of the INVERSE map (from st_map_plan_inverse, or st_map_plan of an
+ * inverted map): tiles of 128 INPUT rows, X the per-tile operand, the dY rows of each offset gathered.  Same dW
+ * as st_conv_wgrad_planned up to the order of the fp32 additions.  Worth it when the inverse map's rows have the
+ * fewer entries (n_in > n_out, a strided layer): its tiles are then the better filled ones.  Tensor-core shapes
+ * with 16-byte aligned tensors only (ST_ERR_UNSUPPORTED otherwise).  No counterpart in the reference. */
+int64_t st_conv_wgrad_inverse_workspace_bytes(int dtype, int64_t n_in, int K, int cin, int cout);
+int st_conv_wgrad_inverse_planned(int dtype, const void* X, const void* dY, const int32_t* row_order, const int32_t* tmap,
+                                  const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K, int cin, int cout,
+                                  void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Feature gradient of a submanifold layer over its OWN map (no inverse map, no second plan):
  *   dX[i,:] = sum_k dY[nbr[i,k],:] . W[K-1-k]^T
  * Valid when the map is symmetric, nbr[o,k] = i <=> nbr[i,K-1-k] = o: offsets in opposite pairs and every
@@ -340,6 +350,25 @@ int st_pool_bwd(int dtype, const void* grad_out, const void* feats, const void* 
 int st_upsample_fwd(int dtype, const void* feats, const void* coords, int coord_dtype, int64_t n, int C, int scale,
                     void* out_feats, void* out_coords, void* stream);
 int st_upsample_bwd(int dtype, const void* grad_out, int64_t n, int C, int scale, void* grad_in, void* stream);
+
+/* first_row[b] (B int32) <- the smallest row whose batch index is b, -1 when the sample has no row. */
+int st_bn_first_rows(const int32_t* batch, int64_t n, int B, int32_t* first_row, void* stream);
+
+/* The statistics of the training forward pass in one call: one pass over X (sums of x - s and (x - s)^2 per
+ * (sample, channel), s = the sample's own first row, first_row[b], -1 for an empty sample), then
+ *   mean[b,c], rstd[b,c] = 1 / sqrt(biased variance + eps)          (B, C) fp32
+ *   running_mean / running_var (C, may be NULL) <- (1 - momentum) * old + momentum * average over the B samples
+ * as nn/functional/norm.py:77-94 computes them.  `sums` (B, C, 2) fp32 is scratch; inv_count[b] = 1 / max(rows of b, 1). */
+int st_bn_forward_stats(int dtype, const void* X, const int32_t* batch, const int32_t* first_row, int64_t n, int C, int B,
+                        const float* inv_count, float eps, float momentum, float* sums, float* mean, float* rstd,
+                        float* running_mean, float* running_var, int32_t* status, void* stream);
+
+/* The whole backward pass: st_bn_backward_sums, then dW[c] = sum_b sums[b,c,1], dB[c] = sum_b sums[b,c,0] (either may
+ * be NULL) and st_bn_backward_apply (skipped when dX is NULL).  batch_stats = 0: mean / rstd were fixed (inference
+ * statistics), the correction terms of dX vanish.  `sums` (B, C, 2) fp32 is scratch. */
+int st_bn_backward(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B, const float* mean,
+                   const float* rstd, const float* weight, const float* bias, int relu, int batch_stats,
+                   const float* inv_count, float* sums, void* dX, float* dW, float* dB, int32_t* status, void* stream);
 
 /* Hash-on-the-fly forms: no stored map; every tile recomputes
  *   curr = out*lookup_stride - off[k], bounds-checks it against lookup_shape and probes the table.

@@ -256,10 +256,14 @@ def upsample_bwd(grad_out, scale):
     return g.reshape(-1, scale ** 3, g.shape[1]).sum(axis=1)
 
 
-def batch_norm(feats, batch_idx, n_samples, weight, bias, eps, relu=False, upstream=None, running=None, momentum=0.1):
+def batch_norm(feats, batch_idx, n_samples, weight, bias, eps, relu=False, upstream=None, running=None, momentum=0.1,
+               decisions=None):
     """nn/functional/norm.py:73-112 in float64: statistics per (sample, channel), biased variance, counts
     clamped to 1; optional ReLU on top (the reference applies it as a separate module).
-    Returns dict(y, mean, var[, dx, dw, db][, running_mean, running_var])."""
+    `decisions` (bool, shape of feats): the ReLU's on/off choice per element taken from another run instead of
+    from this one's own sign of z -- a gradient is discontinuous where z crosses zero, so two runs are compared
+    on common decisions and the caller checks `z` where they differ (it must be within rounding of zero).
+    Returns dict(y, z, mean, var[, dx, dw, db][, running_mean, running_var])."""
     x = np.asarray(feats, np.float64)
     b = np.asarray(batch_idx, np.int64)
     C = x.shape[1]
@@ -275,12 +279,13 @@ def batch_norm(feats, batch_idx, n_samples, weight, bias, eps, relu=False, upstr
     w = np.ones(C) if weight is None else np.asarray(weight, np.float64)
     bb = np.zeros(C) if bias is None else np.asarray(bias, np.float64)
     z = xhat * w + bb
-    res = {"y": np.maximum(z, 0.0) if relu else z, "mean": mean, "var": var}
+    on = (z > 0) if decisions is None else np.asarray(decisions, bool)
+    res = {"y": (z * on) if relu else z, "z": z, "mean": mean, "var": var}
     if running is not None:                                      # norm.py:91-94
         res["running_mean"] = (1 - momentum) * np.asarray(running[0], np.float64) + momentum * mean.mean(0)
         res["running_var"] = (1 - momentum) * np.asarray(running[1], np.float64) + momentum * var.mean(0)
     if upstream is not None:
-        dz = np.asarray(upstream, np.float64) * ((z > 0) if relu else 1.0)
+        dz = np.asarray(upstream, np.float64) * (on if relu else 1.0)
         res["dw"], res["db"] = (dz * xhat).sum(0), dz.sum(0)
         dxhat = dz * w
         s0 = np.zeros((n_samples, C))

@@ -66,6 +66,15 @@ _SIGNATURES["st_bn_backward_sums"] = ([_INT, _PTR, _PTR, _PTR, _I64, _INT, _INT,
                                        _PTR], _INT)
 _SIGNATURES["st_bn_backward_apply"] = ([_INT, _PTR, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _INT, _PTR, _PTR,
                                         _PTR, _PTR, _PTR], _INT)
+_F32 = ctypes.c_float
+_SIGNATURES["st_conv_wgrad_inverse_workspace_bytes"] = ([_INT, _I64, _INT, _INT, _INT], _I64)
+_SIGNATURES["st_conv_wgrad_inverse_planned"] = ([_INT, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64,
+                                                 _PTR], _INT)
+_SIGNATURES["st_bn_first_rows"] = ([_PTR, _I64, _INT, _PTR, _PTR], _INT)
+_SIGNATURES["st_bn_forward_stats"] = ([_INT, _PTR, _PTR, _PTR, _I64, _INT, _INT, _PTR, _F32, _F32, _PTR, _PTR, _PTR, _PTR, _PTR,
+                                       _PTR, _PTR], _INT)
+_SIGNATURES["st_bn_backward"] = ([_INT, _PTR, _PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _PTR, _PTR, _PTR,
+                                  _PTR, _PTR, _PTR, _PTR], _INT)
 _SIGNATURES["st_conv_wgrad_static_max_bytes"] = ([], _I64)
 _SIGNATURES["st_conv_wgrad_static"] = ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR], _INT)
 _SIGNATURES["st_to_dense_fwd"] = ([_INT, _PTR, _PTR, _INT, _I64, _INT, _INT, _PTR, _PTR, _PTR, _PTR], _INT)

@@ -256,6 +256,37 @@ int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_
   });
 }
 
+int64_t st_conv_wgrad_inverse_workspace_bytes(int dtype, int64_t n_in, int K, int cin, int cout) {
+  if (n_in < 0 || K < 1 || cin < 1 || cout < 1) return 256;
+  return align_up(tc_wgrad_partial_bytes(dtype, n_in, K, cin, cout), 256) + 256;
+}
+
+int st_conv_wgrad_inverse_planned(int dtype, const void* X, const void* dY, const int32_t* row_order, const int32_t* tmap,
+                                  const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K, int cin, int cout,
+                                  void* workspace, int64_t workspace_bytes, void* stream) {
+  int rc = check_conv_args("st_conv_wgrad_inverse_planned", dtype, n_in, n_out, K, cin, cout);
+  if (rc != ST_OK) return rc;
+  if (!dW || !tmap || !tmask || n_in < 1 || n_out < 1 || !X || !dY) {
+    set_error("st_conv_wgrad_inverse_planned: null pointer or empty tensor");
+    return ST_ERR_ARG;
+  }
+  if (!tc_wgrad_supported(dtype, n_in, K, cin, cout)) {
+    set_error("st_conv_wgrad_inverse_planned: shape not served by the tensor-core kernels");
+    return ST_ERR_UNSUPPORTED;
+  }
+  if (!workspace || workspace_bytes < st_conv_wgrad_inverse_workspace_bytes(dtype, n_in, K, cin, cout) - 256 ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255)) {
+    set_error("st_conv_wgrad_inverse_planned: workspace too small or misaligned");
+    return ST_ERR_WORKSPACE;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  int chunks = 0;
+  rc = tc_conv_wgrad(dtype, X, dY, nullptr, MapPlan{row_order, tmap, tmask}, static_cast<float*>(workspace), &chunks, n_in,
+                     n_out, K, cin, cout, s, true);
+  if (rc != ST_OK) return rc;
+  return reduce_partials(dtype, static_cast<const float*>(workspace), chunks, (int64_t)K * cin * cout, dW, s);
+}
+
 int st_conv_wgrad(int dtype, const void* X, const void* dY, const int32_t* nbr, void* dW, int64_t n_in, int64_t n_out,
                   int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
   return st_conv_wgrad_planned(dtype, X, dY, nbr, nullptr, nullptr, nullptr, dW, n_in, n_out, K, cin, cout, workspace, workspace_bytes,

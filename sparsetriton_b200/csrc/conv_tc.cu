@@ -804,7 +804,8 @@ struct WgradParams {
   int n_ciblk, n_coblk;
   int a_slot_bytes, b_slot_bytes, b_slots;
   int quad;              // planned_wgrad_kernel: offsets per shared-memory slot (b_slots counts such slots)
-  int a_slots;           // planned_wgrad_kernel: depth of the dY-tile ring
+  int a_slots;           // planned_wgrad_kernel: depth of the tile-operand ring
+  int swap;              // planned_wgrad_kernel: 1 = the plan is the INVERSE map's (tile operand X, gathered operand dY)
   int tmem_cols;
   uint32_t idesc_base;   // everything but N
 };
@@ -1489,6 +1490,12 @@ static int launch_wgrad(WgradPlan& plan, const Map& map, cudaStream_t stream) {
 // slots fit, else the cp.async producers of wgrad_kernel over the same plan.
 static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cudaStream_t stream) {
   tc::WgradParams& p = plan.p;
+  if (p.swap) {
+    // ring 1 holds X tiles (ci_blk wide), ring 2 the gathered dY rows (128 output channels wide)
+    const int t = p.a_slot_bytes;
+    p.a_slot_bytes = p.b_slot_bytes;
+    p.b_slot_bytes = t;
+  }
   // Shared memory: a ring of dY tiles and a ring of X-row slots of `quad` offsets each.  Two shapes, chosen by
   // measurement: rows of one 128-byte line travel four offsets to a slot, two slots, indices loaded as the
   // task comes up; wider rows (two lines, 128 or more 16-bit channels) travel one offset to a slot with three
@@ -1519,9 +1526,15 @@ static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cud
   memset(&dy_desc, 0, sizeof(dy_desc));
   const int dtype = p.esize == 4 ? ST_F32 : ST_BF16;      // element size is all the copy engine needs to know
   const bool tma = g_tma_enabled && budget >= 2 * quad * p.b_slot_bytes && p.n_src > 0 &&
-                   make_gather_desc(&x_desc, p.x, p.n_src, p.cin, p.esize, dtype, p.esize == 4) &&
-                   make_gather_desc(&dy_desc, p.dy, p.n_rows, p.cout, p.esize, dtype, p.esize == 4);
-  if (!tma) return launch_wgrad(plan, map, stream);
+                   make_gather_desc(&x_desc, p.x, p.swap ? p.n_rows : p.n_src, p.cin, p.esize, dtype, p.esize == 4) &&
+                   make_gather_desc(&dy_desc, p.dy, p.swap ? p.n_src : p.n_rows, p.cout, p.esize, dtype, p.esize == 4);
+  if (!tma) {
+    if (p.swap) {
+      set_error("tc wgrad over the inverse plan needs the TMA kernels (16-byte aligned tensors, st_set_tma(1))");
+      return ST_ERR_UNSUPPORTED;
+    }
+    return launch_wgrad(plan, map, stream);
+  }
   p.quad = quad;
   p.a_slots = a_slots;
   int slots = budget / (quad * p.b_slot_bytes);
@@ -1562,16 +1575,23 @@ static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void*
   plan->p.order = nullptr;
   plan->p.quad = 1;
   plan->p.a_slots = 2;
+  plan->p.swap = 0;
   plan->p.partial = partial;
   plan->p.n_src = n_src;
   return true;
 }
 
 int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const MapPlan& rows, float* partial,
-                  int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream) {
+                  int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream,
+                  bool inverse_plan) {
   WgradPlan plan;
   if (!prepare_wgrad(&plan, dtype, x, dy, partial, n_rows, n_src, K, cin, cout)) return ST_ERR_UNSUPPORTED;
   plan.p.order = rows.order;
+  plan.p.swap = inverse_plan ? 1 : 0;
+  if (inverse_plan && !(rows.tmap && rows.tmask)) {
+    set_error("tc wgrad: the inverse form needs a tile plan");
+    return ST_ERR_ARG;
+  }
   int rc;
   if (rows.tmap && rows.tmask)
     rc = launch_wgrad_planned(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream);

@@ -59,8 +59,11 @@ int tc_conv_wgrad_hashfly(int dtype, const void* x, const void* dy, const HashFl
 // Tensor-core weight gradient: fills fp32 partials (n_chunks, K, cin, cout) that the caller reduces.
 bool tc_wgrad_supported(int dtype, int64_t n_rows, int K, int cin, int cout);
 int64_t tc_wgrad_partial_bytes(int dtype, int64_t n_rows, int K, int cin, int cout);
+// inverse_plan: `plan` is the tile plan of the INVERSE map; then n_rows counts the rows of x (the plan's rows) and
+// n_src the rows of dy (the rows the plan's entries name).
 int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const MapPlan& plan, float* partial,
-                  int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream);
+                  int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream,
+                  bool inverse_plan = false);
 
 // Cycle counters of timing experiments (see Params2::dbg).
 int tc_read_prof(long long* host_out, int n);

@@ -410,8 +410,17 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
   const int word = k_first >> 5, shift = k_first & 31;
   const uint32_t group_bits = g_count >= 32 ? 0xFFFFFFFFu : ((1u << g_count) - 1u);
   const int per_line = 128 / p.esize;                       // elements of one 128-byte line
-  const int a_blocks = (co_cnt * p.esize + 127) >> 7;       // 128-byte column blocks of the dY tile
-  const int b_blocks = (ci_cnt * p.esize + 127) >> 7;
+  // The per-tile operand (ring 1, rows taken through `order`) and the per-offset operand (ring 2, rows taken
+  // through the plan's index lines).  Over the forward map the tile operand is dY (M side of the product) and
+  // the gathered one X (N side); with p.swap the kernel walks the plan of the INVERSE map instead: the tile
+  // operand is X, the gathered one dY, and the MMA takes its A operand from ring 2 and its B operand from ring 1.
+  const int m_blocks = (co_cnt * p.esize + 127) >> 7;       // 128-byte column blocks of dY rows
+  const int n_blocks = (ci_cnt * p.esize + 127) >> 7;       // ... of X rows
+  const int a_blocks = p.swap ? n_blocks : m_blocks;        // blocks of the tile operand
+  const int b_blocks = p.swap ? m_blocks : n_blocks;        // blocks of the gathered operand
+  const CUtensorMap* tile_desc = p.swap ? &x_desc : &dy_desc;
+  const CUtensorMap* gath_desc = p.swap ? &dy_desc : &x_desc;
+  const int tile_col0 = p.swap ? ci0 : co0, gath_col0 = p.swap ? co0 : ci0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.a_slots; ++s) {
@@ -487,7 +496,7 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
           }
           __syncwarp();
           for (int b = pw; b < a_blocks; b += kProducerWarps)
-            tma_gather4(slot_base + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &dy_desc, bar, co0 + b * per_line,
+            tma_gather4(slot_base + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, tile_desc, bar, tile_col0 + b * per_line,
                         rows.x, rows.y, rows.z, rows.w);
           if (++a_slot == p.a_slots) {
             a_slot = 0;
@@ -515,7 +524,7 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
           __syncwarp();
           if (my_j >= 0) {
             for (int b = 0; b < b_blocks; ++b)
-              tma_gather4(stage + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &x_desc, bar, ci0 + b * per_line, idx.x,
+              tma_gather4(stage + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, gath_desc, bar, gath_col0 + b * per_line, idx.x,
                           idx.y, idx.z, idx.w);
           }
           if (++b_slot == p.b_slots) {
@@ -628,7 +637,7 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
         }
         __syncwarp();
         for (int b = pw; b < a_blocks; b += kProducerWarps)
-          tma_gather4(slot_base + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &dy_desc, bar, co0 + b * per_line,
+          tma_gather4(slot_base + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, tile_desc, bar, tile_col0 + b * per_line,
                       rows.x, rows.y, rows.z, rows.w);
       } else {
         ok = mbar_wait_warp(smem_u32(&ctl->b_empty[t.slot]), t.parity ^ 1u, abort_flag, 36, lane);
@@ -641,7 +650,7 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
         __syncwarp();
         if (t.my_j >= 0) {
           for (int b = 0; b < b_blocks; ++b)
-            tma_gather4(stage + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, &x_desc, bar, ci0 + b * per_line, rows.x,
+            tma_gather4(stage + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, gath_desc, bar, gath_col0 + b * per_line, rows.x,
                         rows.y, rows.z, rows.w);
         }
       }
@@ -697,8 +706,8 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
             const uint32_t d_addr = tmem_base + (uint32_t)(j * p.ci_blk);
             const uint32_t first = ((touched >> j) & 1u) ? 1u : 0u;
             for (int ks = 0; ks < ksteps; ++ks) {
-              const uint64_t da = desc_hi | (uint64_t)(a_lo + ks * (step_bytes >> 4));
-              const uint64_t db = desc_hi | (uint64_t)(b_lo + ks * (step_bytes >> 4));
+              const uint64_t da = desc_hi | (uint64_t)((p.swap ? b_lo : a_lo) + ks * (step_bytes >> 4));   // dY rows (M)
+              const uint64_t db = desc_hi | (uint64_t)((p.swap ? a_lo : b_lo) + ks * (step_bytes >> 4));   // X rows (N)
               if (p.esize == 2)
                 mma_f16(d_addr, da, db, idesc, ks == 0 ? first : 1u);
               else

@@ -120,6 +120,7 @@ static int product_kernel_size(const Offsets& off, int K) {
 //
 //   count   candidates that survive the stride / range filters -> scratch-table capacity, chosen ON
 //           THE DEVICE as the power of two >= 1.5 x candidates (the host only reserves the worst case)
+//   clear   that many 16-byte slots {key, smallest candidate index, output row} to all ones
 //   insert  exact-key open addressing; atomicMin keeps the smallest flat index n*K+k per coordinate
 //   mark    a candidate wins if it holds that smallest index; K win bits and a win count per row
 //   scan    exclusive prefix sum of the per-row counts = first output row of each input row
@@ -135,10 +136,17 @@ struct OutCoordsHeader {                 // first 256 bytes of the workspace
   uint32_t pad;
 };
 
+// One slot of the dedupe table: 16 bytes, so that a probe, the minimum of the candidate indices and the output
+// row of the coordinate all live in one 32-byte sector (three separate arrays cost three sectors per candidate).
+struct __align__(16) Slot {
+  unsigned long long key;                // exact packed coordinate, all ones = empty
+  uint32_t flat;                         // smallest flat candidate index n*K+k seen for the key
+  uint32_t out_row;                      // output row of the coordinate (written by the `write` pass)
+};
+
 struct OutCoordsWorkspace {
   OutCoordsHeader* header;
-  unsigned long long* keys;              // scratch table keys
-  uint32_t* slot_value;                  // smallest flat candidate index per key; after `write`: output row
+  Slot* slots;                           // scratch table
   uint32_t* win_words;                   // (n, words) win bits of each input row
   uint32_t* row_counts;                  // wins per input row, then their exclusive prefix sum
   void* scan_tmp;
@@ -164,8 +172,8 @@ static int64_t scratch_capacity(int64_t n, int K, int stride, int transposed) {
 static int64_t outcoords_bytes(int64_t n, int K, int stride, int transposed) {
   const int64_t cap = scratch_capacity(n, K, stride, transposed);
   const int words = (K + 31) / 32;
-  return 256 + align_up(cap * 8, 256) + align_up(cap * 4, 256) + align_up(n * words * 4, 256) +
-         align_up(n * 4, 256) + scan_tmp_bytes(n) + 256;
+  return 256 + align_up(cap * (int64_t)sizeof(Slot), 256) + align_up(n * words * 4, 256) + align_up(n * 4, 256) +
+         scan_tmp_bytes(n) + 256;
 }
 
 static bool carve(void* workspace, int64_t bytes, int64_t n, int K, int stride, int transposed,
@@ -176,10 +184,8 @@ static bool carve(void* workspace, int64_t bytes, int64_t n, int K, int stride, 
   char* end = p + bytes;
   w->header = reinterpret_cast<OutCoordsHeader*>(p);
   p += 256;
-  w->keys = reinterpret_cast<unsigned long long*>(p);
-  p += align_up(cap * 8, 256);
-  w->slot_value = reinterpret_cast<uint32_t*>(p);
-  p += align_up(cap * 4, 256);
+  w->slots = reinterpret_cast<Slot*>(p);
+  p += align_up(cap * (int64_t)sizeof(Slot), 256);
   w->win_words = reinterpret_cast<uint32_t*>(p);
   p += align_up(n * w->words * 4, 256);
   w->row_counts = reinterpret_cast<uint32_t*>(p);
@@ -213,53 +219,74 @@ outcoords_count_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets 
   }
 }
 
-__global__ void outcoords_capacity_kernel(OutCoordsHeader* header, unsigned long long capacity_max) {
-  unsigned long long want = (3 * header->n_candidates + 1) / 2;
+// Table capacity for the counted candidates: the power of two >= 1.5 x candidates, at most what was reserved.
+__device__ __forceinline__ uint32_t capacity_for(unsigned long long n_candidates, unsigned long long capacity_max) {
+  const unsigned long long want = (3 * n_candidates + 1) / 2;
   unsigned long long cap = 1024;
   while (cap < want && cap < capacity_max) cap <<= 1;
-  header->capacity = (uint32_t)cap;
+  return (uint32_t)cap;
 }
 
+// Chooses the capacity (every thread works it out from the candidate count; one thread records it for the
+// kernels that follow) and clears that many slots: 16-byte stores of all ones.
 __global__ void __launch_bounds__(256)
-scratch_clear_kernel(const OutCoordsHeader* header, unsigned long long* keys, uint32_t* slot_value) {
-  const uint32_t capacity = header->capacity;
-  for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < capacity; i += gridDim.x * 256u) {
-    keys[i] = kEmptyKey;
-    slot_value[i] = 0xFFFFFFFFu;
-  }
+scratch_clear_kernel(OutCoordsHeader* header, unsigned long long capacity_max, Slot* slots) {
+  const uint32_t capacity = capacity_for(header->n_candidates, capacity_max);
+  if (blockIdx.x == 0 && threadIdx.x == 0) header->capacity = capacity;
+  const uint4 empty = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+  for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < capacity; i += gridDim.x * 256u)
+    reinterpret_cast<uint4*>(slots)[i] = empty;
 }
 
-// Slot of `key`, inserting it if absent; capacity is a power of two.  Returns 0xFFFFFFFF when full.
-__device__ __forceinline__ uint32_t scratch_insert(unsigned long long* keys, uint32_t capacity, unsigned long long key) {
+// Records candidate index `flat` for `key`: finds or claims the key's slot and lowers the slot's index to `flat`.
+// Capacity is a power of two.  Returns false when the table is full.
+//
+// Four out of five candidates of a strided layer are repeats of a coordinate another input has already
+// produced, and they arrive roughly in ascending order of `flat`, so a repeat usually finds its key in place
+// with a smaller index already stored: one 16-byte read (past L1, which may hold an old copy) and no atomic.
+// A stale read can only show an empty slot that is taken by now (the compare-and-swap then returns the owner)
+// or an index larger than the current one (the minimum is then applied needlessly): both are harmless.
+__device__ __forceinline__ bool scratch_record(Slot* slots, uint32_t capacity, unsigned long long key, uint32_t flat) {
   const uint32_t mask = capacity - 1;
   uint32_t slot = mix_key(key) & mask;
   for (uint32_t step = 0; step < capacity; ++step) {
-    unsigned long long seen = keys[slot];
-    if (seen == kEmptyKey) seen = atomicCAS(keys + slot, kEmptyKey, key);
-    if (seen == kEmptyKey || seen == key) return slot;
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + slot));
+    unsigned long long seen = (unsigned long long)v.x | ((unsigned long long)v.y << 32);
+    if (seen == kEmptyKey) seen = atomicCAS(&slots[slot].key, kEmptyKey, key);
+    else if (seen == key) {
+      if (v.z > flat) atomicMin(&slots[slot].flat, flat);
+      return true;
+    }
+    if (seen == kEmptyKey || seen == key) {
+      atomicMin(&slots[slot].flat, flat);
+      return true;
+    }
     slot = (slot + 1) & mask;
   }
-  return 0xFFFFFFFFu;
+  return false;
 }
 
-__device__ __forceinline__ uint32_t scratch_find(const unsigned long long* keys, uint32_t capacity,
-                                                 unsigned long long key) {
+// The slot holding `key` with its contents (one 16-byte load per probe), or index 0xFFFFFFFF.
+struct Found {
+  uint32_t slot, flat, out_row;
+};
+__device__ __forceinline__ Found scratch_find(const Slot* slots, uint32_t capacity, unsigned long long key) {
   const uint32_t mask = capacity - 1;
   uint32_t slot = mix_key(key) & mask;
   for (uint32_t step = 0; step < capacity; ++step) {
-    const unsigned long long seen = keys[slot];
-    if (seen == key) return slot;
-    if (seen == kEmptyKey) return 0xFFFFFFFFu;
+    const uint4 v = *reinterpret_cast<const uint4*>(slots + slot);
+    const unsigned long long seen = (unsigned long long)v.x | ((unsigned long long)v.y << 32);
+    if (seen == key) return Found{slot, v.z, v.w};
+    if (seen == kEmptyKey) break;
     slot = (slot + 1) & mask;
   }
-  return 0xFFFFFFFFu;
+  return Found{0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
 }
 
 template <typename CT, int KS>
 __global__ void __launch_bounds__(kRowThreads)
 outcoords_insert_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
-                        Int3 new_shape, const OutCoordsHeader* header, unsigned long long* keys,
-                        uint32_t* slot_value, int32_t* status) {
+                        Int3 new_shape, const OutCoordsHeader* header, Slot* slots, int32_t* status) {
   const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
   if (row >= n) return;
   const uint32_t capacity = header->capacity;
@@ -268,21 +295,18 @@ outcoords_insert_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets
   bool full = false;
   for_each_candidate<KS>(c, off, K, stride, transposed, new_shape, [&](int k, const Int3& v) {
     if (full) return;
-    const uint32_t slot = scratch_insert(keys, capacity, pack_key(c.x, v.x, v.y, v.z));
-    if (slot == 0xFFFFFFFFu) {
+    if (!scratch_record(slots, capacity, pack_key(c.x, v.x, v.y, v.z), flat0 + (uint32_t)k)) {
       atomicOr(status, ST_DEV_TABLE_FULL);
       full = true;
-      return;
     }
-    atomicMin(slot_value + slot, flat0 + (uint32_t)k);
   });
 }
 
 template <typename CT, int KS>
 __global__ void __launch_bounds__(kRowThreads)
 outcoords_mark_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
-                      Int3 new_shape, const OutCoordsHeader* header, const unsigned long long* keys,
-                      const uint32_t* slot_value, uint32_t* win_words, int words, uint32_t* row_counts) {
+                      Int3 new_shape, const OutCoordsHeader* header, const Slot* slots, uint32_t* win_words, int words,
+                      uint32_t* row_counts) {
   const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
   if (row >= n) return;
   const uint32_t capacity = header->capacity;
@@ -296,8 +320,8 @@ outcoords_mark_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets o
       for (int k = w * 32; k < k_end; ++k) {
         Int3 v;
         if (!candidate(c, off, k, stride, transposed, new_shape, &v)) continue;
-        const uint32_t slot = scratch_find(keys, capacity, pack_key(c.x, v.x, v.y, v.z));
-        if (slot != 0xFFFFFFFFu && slot_value[slot] == flat0 + (uint32_t)k) bits |= 1u << (k & 31);
+        const Found f = scratch_find(slots, capacity, pack_key(c.x, v.x, v.y, v.z));
+        if (f.slot != 0xFFFFFFFFu && f.flat == flat0 + (uint32_t)k) bits |= 1u << (k & 31);
       }
       win_words[row * words + w] = bits;
       count += __popc(bits);
@@ -305,8 +329,8 @@ outcoords_mark_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets o
   } else {
     uint32_t bits = 0;                                       // KS <= 3: a single word of win bits
     for_each_candidate<KS>(c, off, K, stride, transposed, new_shape, [&](int k, const Int3& v) {
-      const uint32_t slot = scratch_find(keys, capacity, pack_key(c.x, v.x, v.y, v.z));
-      if (slot != 0xFFFFFFFFu && slot_value[slot] == flat0 + (uint32_t)k) bits |= 1u << k;
+      const Found f = scratch_find(slots, capacity, pack_key(c.x, v.x, v.y, v.z));
+      if (f.slot != 0xFFFFFFFFu && f.flat == flat0 + (uint32_t)k) bits |= 1u << k;
     });
     win_words[row * words] = bits;
     count = __popc(bits);
@@ -317,8 +341,8 @@ outcoords_mark_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets o
 template <typename CT>
 __global__ void __launch_bounds__(kRowThreads)
 outcoords_write_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
-                       Int3 new_shape, const OutCoordsHeader* header, const unsigned long long* keys,
-                       uint32_t* slot_value, const uint32_t* __restrict__ win_words, int words,
+                       Int3 new_shape, const OutCoordsHeader* header, Slot* slots,
+                       const uint32_t* __restrict__ win_words, int words,
                        const uint32_t* __restrict__ row_offsets, CT* out, int64_t out_capacity, int32_t* status) {
   const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
   if (row >= n) return;
@@ -337,8 +361,8 @@ outcoords_write_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets 
         return;
       }
       store_coord<CT>(out, dst, c.x, v.x, v.y, v.z);
-      const uint32_t slot = scratch_find(keys, capacity, pack_key(c.x, v.x, v.y, v.z));
-      if (slot != 0xFFFFFFFFu) slot_value[slot] = (uint32_t)dst;      // the coordinate's output row
+      const Found f = scratch_find(slots, capacity, pack_key(c.x, v.x, v.y, v.z));
+      if (f.slot != 0xFFFFFFFFu) slots[f.slot].out_row = (uint32_t)dst;      // the coordinate's output row
       ++dst;
     }
   }
@@ -348,8 +372,8 @@ outcoords_write_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets 
 template <typename CT, int KS>
 __global__ void __launch_bounds__(kRowThreads)
 outcoords_map_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
-                     Int3 new_shape, Int3 in_shape, const OutCoordsHeader* header, const unsigned long long* keys,
-                     const uint32_t* slot_value, int32_t* nbr, int64_t n_out) {
+                     Int3 new_shape, Int3 in_shape, const OutCoordsHeader* header, const Slot* slots, int32_t* nbr,
+                     int64_t n_out) {
   const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
   if (row >= n) return;
   const uint32_t capacity = header->capacity;
@@ -357,9 +381,9 @@ outcoords_map_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets of
   // an input outside its own grid is never found by the bounds-checked lookup of the probing form
   if (c.y < 0 || c.y >= in_shape.x || c.z < 0 || c.z >= in_shape.y || c.w < 0 || c.w >= in_shape.z) return;
   for_each_candidate<KS>(c, off, K, stride, transposed, new_shape, [&](int k, const Int3& v) {
-    const uint32_t slot = scratch_find(keys, capacity, pack_key(c.x, v.x, v.y, v.z));
-    if (slot == 0xFFFFFFFFu) return;
-    const uint32_t o = slot_value[slot];
+    const Found f = scratch_find(slots, capacity, pack_key(c.x, v.x, v.y, v.z));
+    if (f.slot == 0xFFFFFFFFu) return;
+    const uint32_t o = f.out_row;
     if (o < (uint32_t)n_out) atomicMax(nbr + (int64_t)o * K + k, (int32_t)row);   // duplicate coordinates: largest row
   });
 }
@@ -494,14 +518,12 @@ static int outcoords_count_impl(const CT* coords, int64_t n, const Offsets& off,
 #define ST_SWEEP(KS)                                                                                                  \
   {                                                                                                                   \
     outcoords_count_kernel<CT, KS><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, w.header); \
-    outcoords_capacity_kernel<<<1, 1, 0, s>>>(w.header, (unsigned long long)w.capacity_max);                         \
-    scratch_clear_kernel<<<1184, 256, 0, s>>>(w.header, w.keys, w.slot_value);                                       \
+    scratch_clear_kernel<<<1184, 256, 0, s>>>(w.header, (unsigned long long)w.capacity_max, w.slots);                \
     outcoords_insert_kernel<CT, KS><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, w.header, \
-                                                                 w.keys, w.slot_value, status);                      \
+                                                                 w.slots, status);                                   \
     outcoords_mark_kernel<CT, KS><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, w.header,   \
-                                                               w.keys, w.slot_value, w.win_words, w.words,           \
-                                                               w.row_counts);                                        \
-    note_launches(5);                                                                                                 \
+                                                               w.slots, w.win_words, w.words, w.row_counts);         \
+    note_launches(4);                                                                                                 \
   }
   if (ks == 3) ST_SWEEP(3) else if (ks == 2) ST_SWEEP(2) else ST_SWEEP(0)
 #undef ST_SWEEP
@@ -591,11 +613,11 @@ int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int
   const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
   if (coord_dtype == ST_I32) {
     outcoords_write_kernel<int32_t><<<grid, kRowThreads, 0, s>>>(
-        static_cast<const int32_t*>(coords), n, K, off, stride, transposed != 0, ns, w.header, w.keys, w.slot_value,
+        static_cast<const int32_t*>(coords), n, K, off, stride, transposed != 0, ns, w.header, w.slots,
         w.win_words, w.words, w.row_counts, static_cast<int32_t*>(out_coords), out_capacity, status);
   } else {
     outcoords_write_kernel<int16_t><<<grid, kRowThreads, 0, s>>>(
-        static_cast<const int16_t*>(coords), n, K, off, stride, transposed != 0, ns, w.header, w.keys, w.slot_value,
+        static_cast<const int16_t*>(coords), n, K, off, stride, transposed != 0, ns, w.header, w.slots,
         w.win_words, w.words, w.row_counts, static_cast<int16_t*>(out_coords), out_capacity, status);
   }
   note_launches(1);
@@ -624,8 +646,8 @@ int st_outcoords_map(const void* coords, int64_t n, int coord_dtype, const int32
   const int ks = product_kernel_size(off, K);
 #define ST_MAP(CT, KS)                                                                                              \
   outcoords_map_kernel<CT, KS><<<grid, kRowThreads, 0, s>>>(static_cast<const CT*>(coords), n, K, off, stride,     \
-                                                            transposed != 0, ns, in_shape, w.header, w.keys,       \
-                                                            w.slot_value, nbr, n_out)
+                                                            transposed != 0, ns, in_shape, w.header, w.slots, nbr, \
+                                                            n_out)
   if (coord_dtype == ST_I32) {
     if (ks == 3) ST_MAP(int32_t, 3); else if (ks == 2) ST_MAP(int32_t, 2); else ST_MAP(int32_t, 0);
   } else {

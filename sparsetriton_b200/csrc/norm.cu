@@ -52,10 +52,21 @@ __device__ __forceinline__ int sample_of(const int32_t* __restrict__ batch, int6
   return -1;
 }
 
+// The shift of sample b taken from the data: the value of the sample's first row (0 when there is none).  Sums
+// of (x - shift) and (x - shift)^2 around a value of the distribution keep the one-pass variance accurate.
+template <typename T>
+__device__ __forceinline__ float shift_from_row(const T* __restrict__ x, const int32_t* __restrict__ first_row, int b, int C,
+                                                int c) {
+  if (!first_row) return 0.f;
+  const int32_t r = __ldg(first_row + b);
+  return r >= 0 ? to_f(x[(int64_t)r * C + c]) : 0.f;
+}
+
 // sums[(b*C + c)*2 + 0] += sum (x - shift),  [.. + 1] += sum (x - shift)^2      shift (B, C) or null
 template <typename T>
 __global__ void __launch_bounds__(kBnThreads) bn_sums_kernel(const T* __restrict__ x, const int32_t* __restrict__ batch,
                                                             int64_t n, int C, int B, const float* __restrict__ shift,
+                                                            const int32_t* __restrict__ first_row,
                                                             float* __restrict__ sums, int32_t* status) {
   const Lanes L = lanes_for(C);
   const int cl = threadIdx.x % L.c_lanes, rl = threadIdx.x / L.c_lanes;
@@ -73,7 +84,7 @@ __global__ void __launch_bounds__(kBnThreads) bn_sums_kernel(const T* __restrict
         }
         cur = b;
         s0 = s1 = 0.f;
-        if (b >= 0) sh = shift ? __ldg(shift + (int64_t)b * C + c) : 0.f;
+        if (b >= 0) sh = shift ? __ldg(shift + (int64_t)b * C + c) : shift_from_row(x, first_row, b, C, c);
       }
       if (b < 0) continue;
       const float v = to_f(x[r * C + c]) - sh;
@@ -216,7 +227,7 @@ __global__ void __launch_bounds__(kBnThreads)
     bn_sums_vec_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
                        int B, const float* __restrict__ p0 /* shift | mean */, const float* __restrict__ rstd,
                        const float* __restrict__ w, const float* __restrict__ bias, int relu, float* __restrict__ sums,
-                       int rows_per_block, int32_t* status) {
+                       int rows_per_block, int32_t* status, const int32_t* __restrict__ first_row /* MODE 0: shift rows */) {
   constexpr int V = Vec<T>::V;
   constexpr int U = kBnUnroll;
   const int c_lanes = C / V;                      // <= kBnThreads is checked by the caller
@@ -274,7 +285,7 @@ __global__ void __launch_bounds__(kBnThreads)
         cur = bt[j];
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-          a[i] = p0 ? __ldg(p0 + (int64_t)cur * C + c0 + i) : 0.f;
+          a[i] = p0 ? __ldg(p0 + (int64_t)cur * C + c0 + i) : (MODE == 0 ? shift_from_row(x, first_row, cur, C, c0 + i) : 0.f);
           if (MODE == 1) b[i] = __ldg(rstd + (int64_t)cur * C + c0 + i);
         }
       }
@@ -423,6 +434,56 @@ __global__ void __launch_bounds__(kBnThreads)
   }
 }
 
+// One thread per channel: mean / rstd of every sample from the shifted one-pass sums, and the running buffers
+// (averages of the per-sample statistics over all B samples, empty ones counting as zero).
+template <typename T>
+__global__ void __launch_bounds__(128)
+bn_finalize_kernel(const float* __restrict__ sums, const T* __restrict__ x, const int32_t* __restrict__ first_row,
+                   const float* __restrict__ inv_count, int B, int C, float eps, float momentum, float* __restrict__ mean,
+                   float* __restrict__ rstd, float* running_mean, float* running_var) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  if (c >= C) return;
+  float mean_sum = 0.f, var_sum = 0.f;
+  for (int b = 0; b < B; ++b) {
+    const float ic = __ldg(inv_count + b);
+    const float shift = shift_from_row(x, first_row, b, C, c);
+    const float m1 = sums[((int64_t)b * C + c) * 2] * ic;
+    const float var = fmaxf(sums[((int64_t)b * C + c) * 2 + 1] * ic - m1 * m1, 0.f);
+    const float m = shift + m1;
+    mean[(int64_t)b * C + c] = m;
+    rstd[(int64_t)b * C + c] = rsqrtf(var + eps);
+    mean_sum += m;
+    var_sum += var;
+  }
+  if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mean_sum / (float)B;
+  if (running_var) running_var[c] = (1.f - momentum) * running_var[c] + momentum * var_sum / (float)B;
+}
+
+// first[b] = smallest row whose batch index is b, as an unsigned minimum over the rows that open a run of equal
+// indices (first holds 0xFFFFFFFF = -1 "no row" on entry)
+__global__ void __launch_bounds__(256)
+bn_first_rows_kernel(const int32_t* __restrict__ batch, int64_t n, int B, uint32_t* first) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const int b = __ldg(batch + i);
+  if ((unsigned)b >= (unsigned)B) return;
+  if (i == 0 || __ldg(batch + i - 1) != b) atomicMin(first + b, (uint32_t)i);
+}
+
+// dW[c] = sum_b sums[b,c,1], dB[c] = sum_b sums[b,c,0]
+__global__ void __launch_bounds__(128)
+bn_param_grads_kernel(const float* __restrict__ sums, int B, int C, float* dW, float* dB) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  if (c >= C) return;
+  float w = 0.f, b0 = 0.f;
+  for (int b = 0; b < B; ++b) {
+    b0 += sums[((int64_t)b * C + c) * 2];
+    w += sums[((int64_t)b * C + c) * 2 + 1];
+  }
+  if (dW) dW[c] = w;
+  if (dB) dB[c] = b0;
+}
+
 // The vector forms need whole 16-byte vectors per row, aligned rows, and at most kBnThreads channel lanes.
 template <typename T>
 bool vec_ok(int C, const void* a, const void* b, const void* c) {
@@ -484,10 +545,11 @@ int st_bn_sums(int dtype, const void* X, const int32_t* batch, int64_t n, int C,
         const int rows = apply_rows(C, Vec<T>::V);
         bn_sums_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C, B,
                                                                               shift, nullptr, nullptr, nullptr, 0, sums, rows,
-                                                                              status);
+                                                                              status, nullptr);
       }
       else
-        bn_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, B, shift, sums, status);
+        bn_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, B, shift, nullptr, sums,
+                                                                status);
     });
     note_launches(1);
   }
@@ -539,7 +601,7 @@ int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t*
         const int rows = apply_rows(C, Vec<T>::V);
         bn_sums_vec_kernel<T, 1><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X),
                                                                               static_cast<const T*>(dY), batch, n, C, B, mean, rstd,
-                                                                              weight, bias, relu, sums, rows, status);
+                                                                              weight, bias, relu, sums, rows, status, nullptr);
       }
       else
         bn_bwd_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), static_cast<const T*>(dY), batch,
@@ -576,6 +638,70 @@ int st_bn_backward_apply(int dtype, const void* X, const void* dY, const int32_t
   });
   note_launches(1);
   return check_launch("st_bn_backward_apply");
+}
+
+int st_bn_first_rows(const int32_t* batch, int64_t n, int B, int32_t* first_row, void* stream) {
+  if (n < 0 || B < 1 || !first_row || (n > 0 && !batch) || n > 0x7FFFFFFFll) {
+    set_error("st_bn_first_rows: bad arguments");
+    return ST_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cudaMemsetAsync(first_row, 0xFF, sizeof(int32_t) * (size_t)B, s) != cudaSuccess) return check_launch("st_bn_first_rows");
+  if (n > 0) {
+    bn_first_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(batch, n, B, reinterpret_cast<uint32_t*>(first_row));
+    note_launches(1);
+  }
+  return check_launch("st_bn_first_rows");
+}
+
+int st_bn_forward_stats(int dtype, const void* X, const int32_t* batch, const int32_t* first_row, int64_t n, int C, int B,
+                        const float* inv_count, float eps, float momentum, float* sums, float* mean, float* rstd,
+                        float* running_mean, float* running_var, int32_t* status, void* stream) {
+  int rc = check_bn("st_bn_forward_stats", dtype, n, C, B);
+  if (rc != ST_OK) return rc;
+  if (!sums || !mean || !rstd || !inv_count || (n > 0 && !X)) {
+    set_error("st_bn_forward_stats: null pointer");
+    return ST_ERR_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)B * C, s) != cudaSuccess) return check_launch("st_bn_forward_stats");
+  ST_BN_DISPATCH(dtype, {
+    if (n > 0) {
+      if (vec_ok<T>(C, X, nullptr, nullptr)) {
+        const int rows = apply_rows(C, Vec<T>::V);
+        bn_sums_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C, B,
+                                                                              nullptr, nullptr, nullptr, nullptr, 0, sums, rows,
+                                                                              status, first_row);
+      } else {
+        bn_sums_kernel<T><<<strip_blocks(n), kBnThreads, 0, s>>>(static_cast<const T*>(X), batch, n, C, B, nullptr, first_row,
+                                                                  sums, status);
+      }
+      note_launches(1);
+    }
+    bn_finalize_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, s>>>(sums, static_cast<const T*>(X), n > 0 ? first_row : nullptr,
+                                                                      inv_count, B, C, eps, momentum, mean, rstd, running_mean,
+                                                                      running_var);
+    note_launches(1);
+  });
+  return check_launch("st_bn_forward_stats");
+}
+
+int st_bn_backward(int dtype, const void* X, const void* dY, const int32_t* batch, int64_t n, int C, int B, const float* mean,
+                   const float* rstd, const float* weight, const float* bias, int relu, int batch_stats,
+                   const float* inv_count, float* sums, void* dX, float* dW, float* dB, int32_t* status, void* stream) {
+  int rc = st_bn_backward_sums(dtype, X, dY, batch, n, C, B, mean, rstd, weight, bias, relu, sums, status, stream);
+  if (rc != ST_OK) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dW || dB) {
+    bn_param_grads_kernel<<<(unsigned)((C + 127) / 128), 128, 0, s>>>(sums, B, C, dW, dB);
+    note_launches(1);
+  }
+  if (!dX) return check_launch("st_bn_backward");
+  if (!batch_stats) {
+    // fixed (running) statistics: the two correction terms vanish
+    if (cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)B * C, s) != cudaSuccess) return check_launch("st_bn_backward");
+  }
+  return st_bn_backward_apply(dtype, X, dY, batch, n, C, B, mean, rstd, weight, bias, relu, sums, inv_count, dX, status, stream);
 }
 
 }  // extern "C"

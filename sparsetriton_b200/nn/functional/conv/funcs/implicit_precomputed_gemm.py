@@ -24,6 +24,12 @@ __all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map", "map_plan", "MapPlan", 
 # below this many rows the sort costs more than the denser tiles save
 _MIN_ROWS_FOR_ORDER = 16384
 
+# Walk the weight gradient of a strided layer over the INVERSE map's plan (st_conv_wgrad_inverse_planned)?  Its
+# tiles are better filled (all rows of a tile share their few offsets), but measured slower on the 64 -> 128
+# k3 s2 layer of 1.2 M voxels (0.68 ms against 0.55 ms over the forward plan): each CTA then meets only one or
+# two offsets of its group per tile and long runs of tiles without any, so its copy rings run nearly empty.
+WGRAD_OVER_INVERSE_PLAN = False
+
 
 def inverse_map(neighbor_indices, n_in):
     """inv (n_in, K) with inv[nbr[o,k], k] = o.  Memoised on the map tensor: layers that share a
@@ -177,15 +183,28 @@ def stored_map_dgrad(dy, w, nbr, n_in, flops=0.0):
 
 
 def stored_map_wgrad(x, dy, nbr, K, flops=0.0):
-    """dW[k] = sum_o X[nbr[o, k]]^T . dY[o], in the dtype of x."""
+    """dW[k] = sum_o X[nbr[o, k]]^T . dY[o], in the dtype of x.  Walks the plan of the forward map; with
+    WGRAD_OVER_INVERSE_PLAN, a layer with more input than output rows walks the inverse plan instead."""
     n_in, c_in = x.shape
     n_out, c_out = dy.shape
     code = _lib.feat_code(x)
     L = _lib.lib()
     dw = torch.empty((K, c_in, c_out), device=x.device, dtype=x.dtype)
+    tc = bool(L.st_conv_uses_tensor_cores(code, c_in, c_out))
     with torch.cuda.device(x.device):
+        inv_plan = None
+        if WGRAD_OVER_INVERSE_PLAN and tc and n_in > n_out > 0 and not _is_symmetric(nbr, n_in):
+            inv_plan = inverse_plan(nbr, n_in)
+        if inv_plan is not None:
+            ws = _lib.workspace(L.st_conv_wgrad_inverse_workspace_bytes(code, n_in, K, c_in, c_out), x.device)
+            with trace.stage("conv_wgrad", work=flops):
+                rc = L.st_conv_wgrad_inverse_planned(code, _lib.ptr(x), _lib.ptr(dy), *inv_plan.ptrs(), _lib.ptr(dw), n_in,
+                                                     n_out, K, c_in, c_out, _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
+            if rc != -5:                      # ST_ERR_UNSUPPORTED: unaligned tensors or TMA switched off -> forward plan
+                _lib.check(rc, "st_conv_wgrad_inverse_planned")
+                return dw
         ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
-        plan = map_plan(nbr) if L.st_conv_uses_tensor_cores(code, c_in, c_out) else _NO_PLAN
+        plan = map_plan(nbr) if tc else _NO_PLAN
         with trace.stage("conv_wgrad", work=flops):
             rc = L.st_conv_wgrad_planned(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), *plan.ptrs(),
                                          _lib.ptr(dw), n_in, n_out, K, c_in, c_out, _lib.ptr(ws), ws.numel(),

@@ -4,7 +4,7 @@ biased variance, eps inside the square root, affine), which tests/test_oracle_go
 holds to the reference's own output; and against that output directly (tests/golden/bn_b3_c6.npz).
 Forward and backward, training and inference mode.
 
-Tolerances (max-norm relative): fp32 1e-5 forward / 2e-4 gradients; bf16 / fp16 1e-2 / 2e-2 (the result is
+Tolerances (max-norm relative): fp32 2e-5 forward / 2e-4 gradients; bf16 / fp16 1e-2 / 2e-2 (the result is
 stored in the feature dtype).
 """
 import numpy as np
@@ -54,10 +54,16 @@ def test_training_forward_backward(cuda_device, oracle, dtype, relu, n, C, B, so
     dy = torch.randn(n, C, generator=g).to(dev, dtype)
     (out.F.float() * dy.float()).sum().backward()
 
+    # gradients are compared on the GPU run's own ReLU decisions, which may differ from the oracle's only where the
+    # oracle's pre-activation is within rounding of zero (a flipped element would move dx by its whole magnitude)
+    decisions = (out.F > 0).cpu().numpy() if relu else None
     r = oracle.batch_norm(sp.F.detach().double().cpu().numpy(), bidx.cpu().numpy(), B, w.detach().cpu().numpy(),
                           b.detach().cpu().numpy(), 1e-5, relu=relu, upstream=dy.double().cpu().numpy(),
-                          running=(np.zeros(C), np.ones(C)), momentum=0.1)
-    tol = 1e-5 if dtype == torch.float32 else 1e-2
+                          running=(np.zeros(C), np.ones(C)), momentum=0.1, decisions=decisions)
+    if relu:
+        differ = decisions != (r["z"] > 0)
+        assert not differ.any() or np.abs(r["z"][differ]).max() < (1e-4 if dtype == torch.float32 else 1e-3)
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
     assert out.F.dtype == dtype
     assert _rel(out.F, r["y"]) < tol
     assert _rel(x.grad, r["dx"]) < (2e-4 if dtype == torch.float32 else 2e-2)

@@ -192,3 +192,45 @@ def test_inverse_plan_from_the_forward_map(cuda_device, n_rows, n_src, K, densit
     assert torch.equal(order, want[0])
     assert torch.equal(tmap, want[1])
     assert torch.equal(tmask, want[2])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16], ids=["fp32", "bf16", "fp16"])
+@pytest.mark.parametrize("n_rows,n_src,K,cin,cout,patterns", [(5000, 9000, 27, 64, 128, 20), (20001, 30000, 27, 32, 64, None),
+                                                              (3000, 6001, 8, 128, 256, None), (900, 2000, 27, 16, 8, 5),
+                                                              (129, 130, 27, 64, 64, None)])
+def test_wgrad_over_the_inverse_plan(cuda_device, oracle, dtype, n_rows, n_src, K, cin, cout, patterns):
+    """st_conv_wgrad_inverse_planned (tiles of input rows, dY gathered) against the oracle and against the
+    forward-plan form; rows of X without any output (zero masks) and a ragged last tile included."""
+    dev = cuda_device
+    L = _lib.lib()
+    nbr = _random_map(n_rows, n_src, K, 0.3, 5 + n_rows + K, dev, patterns)
+    g = torch.Generator().manual_seed(n_rows)
+    x = torch.randn(n_src, cin, generator=g).to(dtype).to(dev)
+    dy = torch.randn(n_rows, cout, generator=g).to(dtype).to(dev)
+    code = _lib.feat_code(x)
+    if not L.st_conv_uses_tensor_cores(code, cin, cout):
+        pytest.skip("shape served by the CUDA-core kernels")
+    n_tiles = (n_src + 127) // 128
+    order = torch.empty((n_src,), dtype=torch.int32, device=dev)
+    tmap = torch.empty((n_tiles * K * 128,), dtype=torch.int32, device=dev)
+    tmask = torch.empty((n_tiles,), dtype=torch.int32, device=dev)
+    dw_inv = torch.empty((K, cin, cout), dtype=dtype, device=dev)
+    dw_fwd = torch.empty_like(dw_inv)
+    p = _lib.ptr
+    with torch.cuda.device(dev):
+        s = _lib.stream_ptr()
+        ws = _lib.workspace(L.st_map_plan_inverse_workspace_bytes(n_src, K), dev)
+        _lib.check(L.st_map_plan_inverse(p(nbr), n_rows, K, n_src, p(order), p(tmap), p(tmask), p(ws), ws.numel(), s),
+                   "st_map_plan_inverse")
+        ws2 = _lib.workspace(L.st_conv_wgrad_inverse_workspace_bytes(code, n_src, K, cin, cout), dev)
+        _lib.check(L.st_conv_wgrad_inverse_planned(code, p(x), p(dy), p(order), p(tmap), p(tmask), p(dw_inv), n_src, n_rows, K,
+                                                   cin, cout, p(ws2), ws2.numel(), s), "st_conv_wgrad_inverse_planned")
+        ws3 = _lib.workspace(L.st_conv_workspace_bytes(code, n_src, n_rows, K, cin, cout), dev)
+        _lib.check(L.st_conv_wgrad(code, p(x), p(dy), p(nbr), p(dw_fwd), n_src, n_rows, K, cin, cout, p(ws3), ws3.numel(), s),
+                   "st_conv_wgrad")
+        torch.cuda.synchronize()
+    assert _lib.device_status(dev)[0] == 0
+    want = oracle.conv_wgrad(t2n(x), t2n(dy), nbr.cpu().numpy(), K, cin, cout)
+    tol = TOL[dtype]
+    assert rel_err(t2n(dw_inv), want) < tol
+    assert rel_err(t2n(dw_inv), t2n(dw_fwd)) < tol

@@ -1291,6 +1291,33 @@ static int launch_planned(tc::Params2 p, const tc::PlannedRows& map, cudaStream_
   CUtensorMap in_desc, w_desc;
   memset(&in_desc, 0, sizeof(in_desc));
   memset(&w_desc, 0, sizeof(w_desc));
+  // Two CTAs per SM (experiment switch of instrumented builds): super tiles of at most two row tiles whose
+  // accumulators take at most half of TMEM, rings cut to half of the shared memory, twice the CTAs.  Measured
+  // slower on every layer tried (64 -> 128 k3 s2 forward 0.33 -> 0.47 ms, dgrad 0.25 -> 0.44 ms; submanifold
+  // 32..256 channels 1.5-1.8x slower): what bounds these kernels is the copy engine's rate of row gathers per SM,
+  // which two half-size pipelines share, while each W slice is then fetched for two row tiles instead of four.
+  int smem_budget = 222 * 1024;
+  int ctas_per_sm = 1;
+#ifdef ST_TC_PROFILE
+  {
+    const char* e = getenv("ST_TC_HALF");
+    if (e && atoi(e)) {
+      const int64_t n_tiles = (p.n_rows + tc::kTileM - 1) / tc::kTileM;
+      int sub = p.sub < 2 ? p.sub : 2;
+      while (sub > 1 && sub * p.c_acc > 256) --sub;
+      if (sub * p.c_acc <= 256) {
+        p.sub = sub;
+        p.n_super = (n_tiles + sub - 1) / sub;
+        p.acc_bufs = (2 * sub * p.c_acc <= 256) ? 2 : 1;
+        int cols = 32;
+        while (cols < p.acc_bufs * sub * p.c_acc) cols <<= 1;
+        p.tmem_cols = cols;
+        smem_budget = 110 * 1024;
+        ctas_per_sm = 2;
+      }
+    }
+  }
+#endif
   p.part = p.sub;                        // smaller parts (more slots in flight) were measured slower
 #ifdef ST_TC_PROFILE
   {
@@ -1301,7 +1328,7 @@ static int launch_planned(tc::Params2 p, const tc::PlannedRows& map, cudaStream_
   int n_slots = 0;
   for (;;) {
     p.slot_bytes = p.w_slot_bytes + p.part * tc::kABlockBytes;
-    n_slots = (int)((222 * 1024 - (int)sizeof(tc::Control3)) / p.slot_bytes);
+    n_slots = (int)((smem_budget - (int)sizeof(tc::Control3)) / p.slot_bytes);
     if (n_slots > tc::kMaxSlots3) n_slots = tc::kMaxSlots3;
     // the slot that carries an offset's W slice is held until the offset's last item: the ring must
     // have room for all of an offset's items
@@ -1325,7 +1352,8 @@ static int launch_planned(tc::Params2 p, const tc::PlannedRows& map, cudaStream_
     }
     configured[p.esize == 4][current_device()] = true;
   }
-  int64_t grid = p.n_super < sm_count() ? p.n_super : sm_count();
+  const int64_t max_ctas = (int64_t)ctas_per_sm * sm_count();
+  int64_t grid = p.n_super < max_ctas ? p.n_super : max_ctas;
   kernel<<<(unsigned)grid, tc::kThreads, smem, stream>>>(p, map, in_desc, w_desc);
   note_launches(1);
   return check_launch("tc planned gather");

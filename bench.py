@@ -108,7 +108,19 @@ def _dist_setup(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1 and not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL announces its version on the process's stdout when the first communicator comes up: keep stdout
+        # for the one JSON line by pointing file descriptor 1 at stderr until that has happened
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
     return dist, world, rank, local, dev
 
 

@@ -143,7 +143,11 @@ def ptr(t):
 
 
 def stream_ptr(device=None):
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    """The current CUDA stream of `device` (a torch.device, an index or None) as a raw handle."""
+    index = device.index if isinstance(device, torch.device) else device
+    if index is None:
+        index = torch.cuda.current_device()
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(index))
 
 
 def host_i32(values):

@@ -63,8 +63,14 @@ def compute_neighbor_indices(
                                                    _lib.stream_ptr())
         _lib.check(rc, "st_map_build_symmetric")
         # rows not returned for their own coordinate (duplicates, outside the grid); 0 = the map is its own
-        # inverse up to the order of the offsets, which the feature gradient then exploits
-        nbr._st_asymmetric_rows = asym
+        # inverse up to the order of the offsets, which the feature gradient then exploits.  The count travels to
+        # pinned host memory right away and an event marks its arrival, so that the backward pass, much later,
+        # reads it without waiting for everything the stream holds by then.
+        flag_host = torch.empty(1, dtype=torch.int32, pin_memory=True)
+        flag_host.copy_(asym, non_blocking=True)
+        arrived = torch.cuda.Event()
+        arrived.record(torch.cuda.current_stream(device))
+        nbr._st_asymmetric_rows = (flag_host, arrived)
         return nbr
     with torch.cuda.device(device), trace.stage("map_build", 1):
         rc = _lib.lib().st_map_build(_lib.ptr(coords), n_out, _lib.coord_code(coords), _lib.host_i32(host), K,

@@ -118,12 +118,15 @@ def inverse_plan(neighbor_indices, n_in):
 
 def _is_symmetric(map_tensor, n_in):
     """True for a submanifold map whose builder found every row under its own coordinate
-    (st_map_build_symmetric): then nbr[o,k] = i <=> nbr[i,K-1-k] = o.  One 4-byte read, memoised."""
+    (st_map_build_symmetric): then nbr[o,k] = i <=> nbr[i,K-1-k] = o.  The builder's count was copied to pinned
+    host memory when the map was built; this waits for that copy only (not for the stream) and memoises."""
     flag = getattr(map_tensor, "_st_asymmetric_rows", None)
     if flag is None or map_tensor.shape[0] != n_in:
         return False
     if not isinstance(flag, bool):
-        flag = int(flag.item()) == 0
+        host, arrived = flag
+        arrived.synchronize()
+        flag = int(host[0]) == 0
         map_tensor._st_asymmetric_rows = flag
     return flag
 

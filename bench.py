@@ -192,11 +192,18 @@ class C3Layer:
             self.n_out.append(n_out)
         self.set_algo()
 
-    def run(self, coords, feats, dy):
-        """One pass; returns (y, dx, dw)."""
+    def prepare(self, coords, consumer):
+        """First half of the coordinate side of one pass (candidates counted and deduplicated) on the current stream;
+        `.finish()` launches the rest (output coordinates, map, tile plans) and returns the cache for `run`."""
+        from sparsetriton_b200.nn.functional import ConvPreparation
+        return ConvPreparation(coords, self.shape, kernel_size=KS, stride=STRIDE, padding=PAD, submanifold=False,
+                               consumer_stream=consumer)
+
+    def run(self, coords, feats, dy, cache=None):
+        """One pass; returns (y, dx, dw).  With `cache` (from `prepare`) only the three products are left to do."""
         x = feats.detach().requires_grad_(True)
         wp = self.weight.detach().requires_grad_(True)
-        sp = self.st.SparseTensor._trusted(x, coords, self.shape, self.args.batch)
+        sp = self.st.SparseTensor._trusted(x, coords, self.shape, self.args.batch, cache)
         out = self.conv(sp, wp, kernel_size=KS, stride=STRIDE, padding=PAD, submanifold=False)
         dx, dw = torch.autograd.grad(out.F, [x, wp], dy)
         if self.world > 1:
@@ -205,6 +212,36 @@ class C3Layer:
 
     def one_pass(self, j):
         return self.run(*self.resident[j % len(self.resident)])
+
+    def pipelined(self, passes, side):
+        """`passes` passes with the coordinate side of the passes ahead on stream `side`, beside the products of pass j:
+        while pass j's products run, the second half of pass j+1's preparation and the first half of pass j+2's are
+        launched, so the host never waits for a count that is not already there.  Every pass still builds its own
+        coordinates, map and plans; nothing is carried from one pass to another."""
+        main = torch.cuda.current_stream()
+        side.wait_stream(main)
+
+        def begin(j):
+            with torch.cuda.stream(side):
+                return self.prepare(self.resident[j % len(self.resident)][0], main)
+
+        def finish(prep):
+            with torch.cuda.stream(side):
+                cache = prep.finish()
+                ready = torch.cuda.Event()
+                ready.record(side)
+            return cache, ready
+
+        current = finish(begin(0))
+        ahead = begin(1) if passes > 1 else None
+        for j in range(passes):
+            cache, ready = current
+            main.wait_event(ready)
+            self.run(*self.resident[j % len(self.resident)], cache=cache)
+            if ahead is not None:
+                current = finish(ahead)
+                ahead = begin(j + 2) if j + 2 < passes else None
+        main.wait_stream(side)
 
     def voxels(self, passes):
         return sum(self.n_in[j % len(self.n_in)] for j in range(passes))
@@ -292,9 +329,22 @@ def run_ours(args):
     layer = C3Layer(args, dist, world, rank, dev, dtype, args.algo, args.batches)
     passes = args.passes
 
-    def step(_i=0):
+    def serial_step(_i=0):
         for j in range(passes):
             layer.one_pass(j)
+
+    # Timed form: the coordinate side of pass j+1 (output coordinates, map, tile plans: prepare_conv3d on a second
+    # stream) runs beside the three products of pass j.  The serial form is timed as well and reported next to it.
+    pipelined = args.algo == "precomputed" and not args.no_pipeline
+    # the side stream's small kernels go ahead of the products' queued CTAs (higher priority), or they would wait
+    # behind every wave of a product
+    side = torch.cuda.Stream(priority=-1) if pipelined else None
+
+    def step(_i=0):
+        if pipelined:
+            layer.pipelined(passes, side)
+        else:
+            serial_step()
 
     for _ in range(args.warmup):
         step()
@@ -302,6 +352,8 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     dev_ms = _event_ms(dist, world, step, args.steps)
+    serial_ms = _event_ms(dist, world, serial_step, args.steps) if pipelined else dev_ms
+    step = serial_step
     # the per-stage breakdown and the launch count come from one more step with the stage recorder on (its event
     # pairs cost host time, so it stays out of the timed steps)
     with trace.recording() as rec:
@@ -362,7 +414,7 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     del in_bufs
 
-    dev_ms, e2e_ms = _max_over_ranks(dist, world, dev, [dev_ms, e2e_ms])
+    dev_ms, e2e_ms, serial_ms = _max_over_ranks(dist, world, dev, [dev_ms, e2e_ms, serial_ms])
     (voxels_per_step,) = _sum_over_ranks(dist, world, dev, [float(layer.voxels(passes))])
 
     # ---- legs (same process, after the timed regions)
@@ -413,6 +465,10 @@ def run_ours(args):
                                    "inputs) + tile plans + fwd + dgrad + wgrad; one step = %d passes over %d distinct seeded "
                                    "batches" % (args.batch, args.per_sample, args.grid, passes, len(layer.host)),
                        "algo": layer.algo.value, "passes_per_step": passes, "ms_per_pass": ms_per_pass,
+                       "pipelining": ("coordinate side of passes j+1 and j+2 on a second stream beside the products of pass j "
+                                      "(prepare_conv3d); every pass builds its own coordinates, map and plans"
+                                      if pipelined else "none: one stream"),
+                       "serial_ms_per_pass": serial_ms / args.steps / passes,
                        "n_in_per_pass": n_in, "n_out_per_pass": n_out, "pairs_per_pass": pairs,
                        "constructor": "SparseTensor._trusted (the library's internal constructor: no validation read of the "
                                       "coordinates; the public one adds one device->host read per tensor)",
@@ -903,6 +959,8 @@ def main():
     ap.add_argument("--passes", type=int, default=32, help="conv_layer_c3: passes of the hot path per step")
     ap.add_argument("--batches", type=int, default=4, help="conv_layer_c3: distinct seeded batches cycled through")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-pipeline", action="store_true",
+                    help="conv_layer_c3: time the passes on one stream (no overlap of the next pass's coordinate side)")
     ap.add_argument("--no-legs", action="store_true", help="conv_layer_c3: skip the extra legs (variants, config 2, U-Net, reference on GPU)")
     ap.add_argument("--hashfly-in-kernel", action="store_true",
                     help="with --algo hashfly: probe the table inside the GEMM kernels instead of into a scratch map per call")

@@ -10,13 +10,14 @@ import torch
 
 from sparsetriton_b200 import _lib, trace
 from sparsetriton_b200.config import ConvAlgo, get_conv_algo, get_h_table_f
-from sparsetriton_b200.tensor import SparseTensor
+from sparsetriton_b200.tensor import SparseTensor, TensorCache
 from sparsetriton_b200.utils.hash import HashTable, round_up_capacity
 
 from .funcs import ConvHashOnTheFlyImplicitGEMM, ConvPrecomputedNeighborGEMM
-from .kmap import build_out_coords, kernel_offsets, out_coords_and_map
+from .funcs.implicit_precomputed_gemm import prepare_plans
+from .kmap import PendingOutCoordsAndMap, build_out_coords, kernel_offsets, out_coords_and_map
 
-__all__ = ["compute_neighbor_indices", "sparse_conv3d"]
+__all__ = ["compute_neighbor_indices", "sparse_conv3d", "prepare_conv3d", "ConvPreparation"]
 
 
 def compute_neighbor_indices(
@@ -86,6 +87,125 @@ def _new_table(coords, device):
     return table
 
 
+def _table_and_out_coords(cache, coords, spatial_shape, k, s, p, d, submanifold, transposed):
+    """Table over the coordinates the lookup is made in (the inputs themselves, or, for an upsampling transposed
+    conv, the inputs with their spatial columns scaled: conv.py:138-142) and the output coordinates."""
+    device = coords.device
+    if transposed and s > 1:
+        scaled = coords.clone()
+        scaled[:, 1:] *= s
+        table = _new_table(scaled, device)
+    else:
+        if cache.hashtable is None:
+            cache.hashtable = _new_table(coords, device)
+        table = cache.hashtable
+    out_coords, new_shape, koff = build_out_coords(coords, spatial_shape, k, s, d, p, transposed=transposed,
+                                                   submanifold=submanifold)
+    koff._st_host = [v for o in kernel_offsets(k, d, p, transposed) for v in o]
+    return table, out_coords, new_shape, koff
+
+
+def _stored_geometry(cache, coords, spatial_shape, k, s, p, d, submanifold, transposed):
+    """(out_coords, neighbor_indices, new_shape) of a layer under the stored-map algorithm, from the cache of the
+    input's coordinate set or built and memoised there."""
+    cache_key = (k, s, p, d, submanifold, transposed)
+    cached = cache.neighbor_indices.get(cache_key)
+    if cached is not None:
+        return cached
+    if not (submanifold and s == 1):
+        # strided / transposed layer: coordinates and map come out of one pass over the candidates; no table over
+        # the inputs is needed
+        out_coords, new_shape, _, neighbor_indices = out_coords_and_map(coords, spatial_shape, k, s, d, p, transposed)
+    else:
+        table, out_coords, new_shape, koff = _table_and_out_coords(cache, coords, spatial_shape, k, s, p, d,
+                                                                   submanifold, transposed)
+        upsample = transposed and s > 1
+        lookup_shape = tuple(v * s for v in spatial_shape) if upsample else tuple(spatial_shape)
+        neighbor_indices = compute_neighbor_indices(table, out_coords, koff, lookup_shape, 1 if transposed else s, p, d,
+                                                    queries_are_table_rows=out_coords is coords)
+    if out_coords.shape[0] > 0:
+        cache.neighbor_indices[cache_key] = (out_coords, neighbor_indices, new_shape)
+    return out_coords, neighbor_indices, new_shape
+
+
+class ConvPreparation:
+    """Everything a stored-map layer derives from coordinates alone, built ahead of the features, in two halves (no
+    reference counterpart).  Construction launches, on the current stream, the half that needs no size from the
+    device (for a strided or transposed layer: counting and deduplicating the candidates; for a submanifold layer:
+    table and map).  `finish()` waits for the output count alone, launches the rest on that same stream (output
+    coordinates, neighbour map, tile plan and, with `backward`, what the feature gradient reads) and returns the
+    TensorCache to hand to `SparseTensor(feats, coords, spatial_shape, batch_size, cache=...)`; `sparse_conv3d`
+    with the same geometry then launches only its products.
+
+    Built under a side stream it overlaps the products of another batch; a caller that constructs the preparation of
+    batch j+2 before finishing that of batch j+1 never waits for the device.  Pass the stream the layer will run on as
+    `consumer_stream` so that the allocator keeps the results alive for it, and make that stream wait for an event
+    recorded after `finish()`."""
+
+    def __init__(self, coords, spatial_shape, kernel_size, stride=1, dilation=1, padding=0, transposed=False,
+                 submanifold=True, backward=True, cache=None, consumer_stream=None):
+        k = _scalar(kernel_size, "Only cubic kernels supported for now")
+        s = _scalar(stride, "Only uniform stride supported for now")
+        d = _scalar(dilation, "Only uniform dilation supported for now")
+        if submanifold:
+            padding = ((k - 1) * d) // 2
+            assert not transposed, "Submanifold convolution does not support transposed=True"
+        p = _scalar(padding, "Only uniform padding supported for now")
+        _lib.require_cuda(coords, "prepare_conv3d")
+        self.cache = TensorCache() if cache is None else cache
+        self.coords, self.spatial_shape = coords, tuple(spatial_shape)
+        self.geometry = (k, s, p, d, submanifold, transposed)
+        self.backward, self.consumer_stream = backward, consumer_stream
+        self.stream = torch.cuda.current_stream(coords.device)
+        self.pending = None
+        if self.geometry in self.cache.neighbor_indices:
+            return
+        if submanifold and s == 1:
+            _stored_geometry(self.cache, coords, self.spatial_shape, k, s, p, d, submanifold, transposed)
+        else:
+            self.pending = PendingOutCoordsAndMap(coords, self.spatial_shape, k, s, d, p, transposed)
+
+    def finish(self) -> TensorCache:
+        cache, coords = self.cache, self.coords
+        with torch.cuda.stream(self.stream):
+            if self.pending is not None:
+                out_coords, new_shape, _, nbr = self.pending.finish()
+                self.pending = None
+                if out_coords.shape[0] > 0:
+                    cache.neighbor_indices[self.geometry] = (out_coords, nbr, new_shape)
+            else:
+                out_coords, nbr, _ = _stored_geometry(cache, coords, self.spatial_shape, *self.geometry)
+            made = [out_coords, nbr]
+            if nbr.shape[0] > 0:
+                made += prepare_plans(nbr, coords.shape[0], self.backward)
+        if cache.hashtable is not None:
+            made += [cache.hashtable.table_keys, cache.hashtable.table_values]
+        if self.consumer_stream is not None:
+            for t in made:
+                if t is not None and t.is_cuda and t.numel() > 0:
+                    t.record_stream(self.consumer_stream)
+        return cache
+
+
+def prepare_conv3d(
+    coords: torch.Tensor,
+    spatial_shape: Tuple[int, int, int],
+    kernel_size: Union[int, Tuple[int, int, int]],
+    stride: Union[int, Tuple[int, int, int]] = 1,
+    dilation: Union[int, Tuple[int, int, int]] = 1,
+    padding: Union[int, Tuple[int, int, int]] = 0,
+    transposed: bool = False,
+    submanifold: bool = True,
+    backward: bool = True,
+    cache: TensorCache = None,
+    consumer_stream: "torch.cuda.Stream" = None,
+) -> TensorCache:
+    """Both halves of a ConvPreparation at once, on the current stream: returns the TensorCache holding output
+    coordinates, neighbour map and tile plans of the layer (no reference counterpart)."""
+    return ConvPreparation(coords, spatial_shape, kernel_size, stride, dilation, padding, transposed, submanifold,
+                           backward, cache, consumer_stream).finish()
+
+
 def _scalar(value, what):
     if isinstance(value, tuple):
         assert value[0] == value[1] == value[2], what
@@ -126,36 +246,15 @@ def sparse_conv3d(
     assert K == k ** 3, f"Kernel size in weight({K}) and argument({k ** 3}) must match"
 
     cache = tensor._cache
-    cache_key = (k, s, p, d, submanifold, transposed)
     algo = get_conv_algo()
     upsample = transposed and s > 1
-
-    cached = cache.neighbor_indices.get(cache_key) if algo == ConvAlgo.PrecomputedNeighborGEMM else None
-    shortcut = submanifold and s == 1                       # output coordinates are the input coordinates
     neighbor_indices = table = koff = None
-    if cached is not None:
-        out_coords, neighbor_indices, new_shape = cached
-    elif algo == ConvAlgo.PrecomputedNeighborGEMM and not shortcut:
-        # strided / transposed layer with a stored map: coordinates and map come out of one pass over
-        # the candidates; no table over the inputs is needed
-        out_coords, new_shape, koff, neighbor_indices = out_coords_and_map(coords, tensor.spatial_shape, k, s, d, p,
-                                                                           transposed)
-        if out_coords.shape[0] > 0:
-            cache.neighbor_indices[cache_key] = (out_coords, neighbor_indices, new_shape)
+    if algo == ConvAlgo.PrecomputedNeighborGEMM:
+        out_coords, neighbor_indices, new_shape = _stored_geometry(cache, coords, tensor.spatial_shape, k, s, p, d,
+                                                                   submanifold, transposed)
     else:
-        # Table over the coordinates the lookup is made in: the inputs themselves, or, for an
-        # upsampling transposed conv, the inputs with their spatial columns scaled (conv.py:138-142).
-        if upsample:
-            scaled = coords.clone()
-            scaled[:, 1:] *= s
-            table = _new_table(scaled, device)
-        else:
-            if cache.hashtable is None:
-                cache.hashtable = _new_table(coords, device)
-            table = cache.hashtable
-        out_coords, new_shape, koff = build_out_coords(coords, tensor.spatial_shape, k, s, d, p,
-                                                       transposed=transposed, submanifold=submanifold)
-        koff._st_host = [v for o in kernel_offsets(k, d, p, transposed) for v in o]
+        table, out_coords, new_shape, koff = _table_and_out_coords(cache, coords, tensor.spatial_shape, k, s, p, d,
+                                                                   submanifold, transposed)
 
     if out_coords.shape[0] == 0:
         return SparseTensor(
@@ -163,16 +262,11 @@ def sparse_conv3d(
             coords=torch.empty((0, 4), device=device, dtype=coords.dtype),
             spatial_shape=_as_shape(new_shape), batch_size=tensor.batch_size)
 
-    lookup_shape = tuple(v * s for v in tensor.spatial_shape) if upsample else tuple(tensor.spatial_shape)
-    lookup_stride = 1 if transposed else s
-
     if algo == ConvAlgo.PrecomputedNeighborGEMM:
-        if neighbor_indices is None:
-            neighbor_indices = compute_neighbor_indices(table, out_coords, koff, lookup_shape, lookup_stride, p, d,
-                                                        queries_are_table_rows=shortcut and out_coords is coords)
-            cache.neighbor_indices[cache_key] = (out_coords, neighbor_indices, new_shape)
         out_feats = ConvPrecomputedNeighborGEMM.apply(feats, weight, neighbor_indices)
     elif algo == ConvAlgo.ImplicitHashFlyGEMM:
+        lookup_shape = tuple(v * s for v in tensor.spatial_shape) if upsample else tuple(tensor.spatial_shape)
+        lookup_stride = 1 if transposed else s
         out_feats = ConvHashOnTheFlyImplicitGEMM.apply(feats, weight, out_coords, koff, table.table_keys,
                                                        table.table_values, lookup_shape, lookup_stride)
     else:  # pragma: no cover - ConvAlgo has two members

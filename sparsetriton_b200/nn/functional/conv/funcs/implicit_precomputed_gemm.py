@@ -19,7 +19,7 @@ from sparsetriton_b200 import _lib, trace
 from ._channels import pad_cols, pad_weight, padded_widths
 
 __all__ = ["ConvPrecomputedNeighborGEMM", "inverse_map", "map_plan", "MapPlan", "stored_map_forward", "stored_map_dgrad",
-           "stored_map_wgrad"]
+           "stored_map_wgrad", "prepare_plans"]
 
 # below this many rows the sort costs more than the denser tiles save
 _MIN_ROWS_FOR_ORDER = 16384
@@ -129,6 +129,22 @@ def _is_symmetric(map_tensor, n_in):
         flag = int(host[0]) == 0
         map_tensor._st_asymmetric_rows = flag
     return flag
+
+
+def prepare_plans(nbr, n_in, backward=True):
+    """Builds (and memoises on the map) what the tensor-core products read besides the map: the tile plan, and with
+    `backward` the feature gradient's side (nothing more for a symmetric submanifold map, else the inverse map's plan).
+    Returns the tensors made, for callers that manage streams."""
+    plan = map_plan(nbr)
+    made = [plan.order, plan.tmap, plan.tmask]
+    if backward and not _is_symmetric(nbr, n_in):
+        inv_plan = inverse_plan(nbr, n_in)
+        if inv_plan is None:
+            inv = inverse_map(nbr, n_in)
+            inv_plan = map_plan(inv)
+            made.append(inv)
+        made += [inv_plan.order, inv_plan.tmap, inv_plan.tmask]
+    return made
 
 
 def stored_map_forward(x, w, nbr, n_in):

@@ -20,7 +20,7 @@ import torch
 
 from sparsetriton_b200 import _lib, trace
 
-__all__ = ["build_out_coords", "out_coords_and_map", "kernel_offsets", "output_shape"]
+__all__ = ["build_out_coords", "out_coords_and_map", "PendingOutCoordsAndMap", "kernel_offsets", "output_shape"]
 
 
 def kernel_offsets(kernel_size: int, dilation: int, padding: int, transposed: bool):
@@ -43,8 +43,25 @@ def output_shape(spatial_shape, kernel_size, stride, dilation, padding, transpos
     return tuple((int(s) - (kernel_size - 1) * dilation + 2 * padding - 1) // stride + 1 for s in spatial_shape)
 
 
+_CONSTANTS = {}
+
+
+def _constant_tensor(values, dtype, device, shape):
+    """Small constant device tensor, made once per (values, dtype, device): building one from a python list is a
+    pageable host->device copy, which waits for everything its stream holds."""
+    key = (tuple(values), dtype, device.type, device.index, shape)
+    t = _CONSTANTS.get(key)
+    if t is None:
+        if len(_CONSTANTS) > 256:
+            _CONSTANTS.clear()
+        t = _CONSTANTS[key] = torch.tensor(list(values), dtype=dtype, device=device).reshape(shape)
+    return t
+
+
 def _offsets_tensor(offsets, like):
-    return torch.tensor(offsets, dtype=like.dtype, device=like.device).reshape(-1, 3)
+    """(K,3) device tensor of the offsets in the coordinate dtype.  Shared between calls: treat as read-only."""
+    t = _constant_tensor([v for o in offsets for v in o], like.dtype, like.device, (-1, 3))
+    return t.view(t.shape)            # a fresh tensor object per call (callers attach attributes), same storage
 
 
 def build_out_coords(
@@ -67,14 +84,14 @@ def build_out_coords(
     """
     device = in_coords.device
     offsets = kernel_offsets(kernel_size, dilation, padding, transposed)
-    koff = _offsets_tensor(offsets, in_coords)
+    koff = _offsets_tensor(offsets, in_coords).clone()          # the caller's own copy (a device-side copy: no wait)
     new_shape = output_shape(spatial_shape, kernel_size, stride, dilation, padding, transposed)
 
     # kmap.py:261-262 / :380-381
     if submanifold and stride == 1 and ((kernel_size - 1) * dilation) // 2 == padding:
         return in_coords, spatial_shape, koff
 
-    new_shape_t = torch.tensor(new_shape, device=device)
+    new_shape_t = _constant_tensor(new_shape, torch.int64, device, (3,)).clone()
     new_shape_t._st_host = new_shape      # spares callers in this package a device->host read
     out, _ = _run_out_coords(in_coords, offsets, new_shape, stride, transposed, with_map=False)
     return out, new_shape_t, koff
@@ -85,51 +102,89 @@ def out_coords_and_map(in_coords, spatial_shape, kernel_size, stride, dilation, 
     one pass over the candidates (the map is scattered from the same dedupe table instead of probing
     the input table N_out*K times).  Returns (out_coords, new_shape tuple, kernel_offsets tensor, nbr).
     Same results as build_out_coords followed by compute_neighbor_indices."""
-    offsets = kernel_offsets(kernel_size, dilation, padding, transposed)
-    koff = _offsets_tensor(offsets, in_coords)
-    koff._st_host = [v for o in offsets for v in o]
-    new_shape = output_shape(spatial_shape, kernel_size, stride, dilation, padding, transposed)
-    out, nbr = _run_out_coords(in_coords, offsets, new_shape, stride, transposed, with_map=True,
-                               in_shape=tuple(int(v) for v in spatial_shape))
-    return out, new_shape, koff, nbr
+    return PendingOutCoordsAndMap(in_coords, spatial_shape, kernel_size, stride, dilation, padding, transposed).finish()
+
+
+class _PendingOutCoords:
+    """First half of the output-coordinate build: candidates counted and deduplicated on the stream current at
+    construction, the count on its way to pinned host memory.  `finish()` waits for that copy alone (not for the
+    stream), sizes the outputs and launches the second half on the same stream."""
+
+    def __init__(self, in_coords, offsets, new_shape, stride, transposed, with_map, in_shape=None):
+        device = in_coords.device
+        self.n, self.K = in_coords.shape[0], len(offsets)
+        self.with_map, self.coord_dtype, self.device = with_map, in_coords.dtype, device
+        if self.n == 0:
+            return
+        _lib.require_cuda(in_coords, "build_out_coords")
+        self.coords = in_coords.contiguous()
+        self.code = _lib.coord_code(self.coords)
+        L = _lib.lib()
+        self.off_h = _lib.host_i32(v for o in offsets for v in o)
+        self.shape_h = _lib.host_i32(new_shape)
+        self.in_shape_h = _lib.host_i32(in_shape) if in_shape is not None else None
+        self.stride, self.transposed = stride, int(transposed)
+        self.ws = _lib.workspace(L.st_outcoords_workspace_bytes(self.n, self.K, stride, self.transposed), device)
+        self.counters = torch.zeros(2, dtype=torch.int64, device=device)      # [n_out, status]
+        self.status = self.counters[1:].view(torch.int32)
+        self.stream = torch.cuda.current_stream(device)
+        with torch.cuda.device(device), trace.stage("out_coords"):
+            rc = L.st_outcoords_count(_lib.ptr(self.coords), self.n, self.code, self.off_h, self.K, stride,
+                                      self.transposed, self.shape_h, _lib.ptr(self.ws), self.ws.numel(),
+                                      _lib.ptr(self.counters), _lib.ptr(self.status), _lib.stream_ptr(device))
+            _lib.check(rc, "st_outcoords_count")
+            self.host = torch.empty(2, dtype=torch.int64, pin_memory=True)
+            self.host.copy_(self.counters, non_blocking=True)
+            self.arrived = torch.cuda.Event()
+            self.arrived.record(self.stream)
+
+    def finish(self):
+        device, K = self.device, self.K
+        if self.n == 0:
+            return (torch.empty((0, 4), dtype=self.coord_dtype, device=device),
+                    torch.empty((0, K), dtype=torch.int32, device=device) if self.with_map else None)
+        L = _lib.lib()
+        self.arrived.synchronize()                                     # the one device->host wait
+        n_out, flags = self.host.tolist()
+        if flags & _lib.DEV_TABLE_FULL:
+            raise RuntimeError("build_out_coords: dedupe table overflow")
+        nbr = None
+        with torch.cuda.device(device), torch.cuda.stream(self.stream):
+            stream = _lib.stream_ptr(device)
+            out = torch.empty((n_out, 4), dtype=self.coord_dtype, device=device)
+            if n_out > 0:
+                with trace.stage("out_coords"):
+                    rc = L.st_outcoords_write(_lib.ptr(self.coords), self.n, self.code, self.off_h, K, self.stride,
+                                              self.transposed, self.shape_h, _lib.ptr(self.ws), self.ws.numel(),
+                                              _lib.ptr(out), n_out, _lib.ptr(self.status), stream)
+                    _lib.check(rc, "st_outcoords_write")
+            if self.with_map:
+                nbr = torch.empty((n_out, K), dtype=torch.int32, device=device)
+                if n_out > 0:
+                    with trace.stage("map_scatter"):
+                        rc = L.st_outcoords_map(_lib.ptr(self.coords), self.n, self.code, self.off_h, K, self.stride,
+                                                self.transposed, self.shape_h, self.in_shape_h, _lib.ptr(self.ws),
+                                                self.ws.numel(), _lib.ptr(nbr), n_out, stream)
+                        _lib.check(rc, "st_outcoords_map")
+        return out, nbr
 
 
 def _run_out_coords(in_coords, offsets, new_shape, stride, transposed, with_map, in_shape=None):
-    device = in_coords.device
-    n, K = in_coords.shape[0], len(offsets)
-    if n == 0:
-        return (torch.empty((0, 4), dtype=in_coords.dtype, device=device),
-                torch.empty((0, K), dtype=torch.int32, device=device) if with_map else None)
-    _lib.require_cuda(in_coords, "build_out_coords")
-    coords = in_coords.contiguous()
-    code = _lib.coord_code(coords)
-    L = _lib.lib()
-    off_h = _lib.host_i32(v for o in offsets for v in o)
-    shape_h = _lib.host_i32(new_shape)
-    ws_bytes = L.st_outcoords_workspace_bytes(n, K, stride, int(transposed))
-    ws = _lib.workspace(ws_bytes, device)
-    counters = torch.zeros(2, dtype=torch.int64, device=device)      # [n_out, status]
-    status = counters[1:].view(torch.int32)
-    nbr = None
-    with torch.cuda.device(device), trace.stage("out_coords"):
-        stream = _lib.stream_ptr()
-        rc = L.st_outcoords_count(_lib.ptr(coords), n, code, off_h, K, stride, int(transposed), shape_h,
-                                  _lib.ptr(ws), ws.numel(), _lib.ptr(counters), _lib.ptr(status), stream)
-        _lib.check(rc, "st_outcoords_count")
-        n_out, flags = counters.tolist()                               # the one device->host sync
-        if flags & _lib.DEV_TABLE_FULL:
-            raise RuntimeError("build_out_coords: dedupe table overflow")
-        out = torch.empty((n_out, 4), dtype=coords.dtype, device=device)
-        if n_out > 0:
-            rc = L.st_outcoords_write(_lib.ptr(coords), n, code, off_h, K, stride, int(transposed), shape_h,
-                                      _lib.ptr(ws), ws.numel(), _lib.ptr(out), n_out, _lib.ptr(status), stream)
-            _lib.check(rc, "st_outcoords_write")
-    if with_map:
-        nbr = torch.empty((n_out, K), dtype=torch.int32, device=device)
-        if n_out > 0:
-            with torch.cuda.device(device), trace.stage("map_scatter"):
-                rc = L.st_outcoords_map(_lib.ptr(coords), n, code, off_h, K, stride, int(transposed), shape_h,
-                                        _lib.host_i32(in_shape), _lib.ptr(ws), ws.numel(), _lib.ptr(nbr), n_out,
-                                        _lib.stream_ptr())
-                _lib.check(rc, "st_outcoords_map")
-    return out, nbr
+    return _PendingOutCoords(in_coords, offsets, new_shape, stride, transposed, with_map, in_shape).finish()
+
+
+class PendingOutCoordsAndMap:
+    """`out_coords_and_map` in two halves: construction launches the counting half, `finish()` returns what
+    `out_coords_and_map` returns.  Lets a caller put other work between the launch and the wait for the count."""
+
+    def __init__(self, in_coords, spatial_shape, kernel_size, stride, dilation, padding, transposed):
+        offsets = kernel_offsets(kernel_size, dilation, padding, transposed)
+        self.koff = _offsets_tensor(offsets, in_coords)
+        self.koff._st_host = [v for o in offsets for v in o]
+        self.new_shape = output_shape(spatial_shape, kernel_size, stride, dilation, padding, transposed)
+        self.pending = _PendingOutCoords(in_coords, offsets, self.new_shape, stride, transposed, with_map=True,
+                                         in_shape=tuple(int(v) for v in spatial_shape))
+
+    def finish(self):
+        out, nbr = self.pending.finish()
+        return out, self.new_shape, self.koff, nbr

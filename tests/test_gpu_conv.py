@@ -203,6 +203,52 @@ def test_submanifold_keeps_coords_and_cache(cuda_device):
     assert len(sp._cache.neighbor_indices) == 1 and out2.F.shape == (100, 8)
 
 
+@pytest.mark.parametrize("k,s,p,subm,transposed", [(3, 1, 1, True, False), (3, 2, 1, False, False), (2, 2, 0, False, False),
+                                                   (2, 2, 0, False, True)])
+def test_prepared_on_a_side_stream(cuda_device, k, s, p, subm, transposed):
+    """prepare_conv3d under a second stream, then the layer on the first: same bits as the layer alone, and the layer
+    then builds nothing of its own."""
+    from sparsetriton_b200 import trace
+    from sparsetriton_b200.nn.functional import ConvPreparation, prepare_conv3d
+    set_conv_algo(ConvAlgo.PrecomputedNeighborGEMM)
+    set_coords_dtype(torch.int32)
+    n, grid, cin, cout = 40_000, 96, 32, 64
+    coords = synthetic.random_cells(n, 2, grid, 77).to(cuda_device)
+    gen = torch.Generator().manual_seed(78)
+    feats = torch.randn(n, cin, generator=gen).to(torch.bfloat16).to(cuda_device)
+    weight = (torch.randn(k ** 3, cin, cout, generator=gen) * 0.05).to(torch.bfloat16).to(cuda_device)
+
+    def layer(cache):
+        x, w = feats.clone().requires_grad_(True), weight.clone().requires_grad_(True)
+        sp = st.SparseTensor(x, coords, (grid,) * 3, 2, cache=cache)
+        out = sparse_conv3d(sp, w, kernel_size=k, stride=s, padding=p, submanifold=subm, transposed=transposed)
+        dy = torch.ones_like(out.F) * 0.25
+        dx, dw = torch.autograd.grad(out.F, [x, w], dy)
+        return out.C, out.F, dx, dw
+
+    want = layer(None)
+    main, side = torch.cuda.current_stream(cuda_device), torch.cuda.Stream(cuda_device)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        cache = prepare_conv3d(coords, (grid,) * 3, kernel_size=k, stride=s, padding=p, submanifold=subm,
+                               transposed=transposed, consumer_stream=main)
+        # two preparations in flight, begun before either is finished
+        first, second = (ConvPreparation(coords, (grid,) * 3, kernel_size=k, stride=s, padding=p, submanifold=subm,
+                                         transposed=transposed, consumer_stream=main) for _ in range(2))
+        caches = [cache, first.finish(), second.finish()]
+        ready = torch.cuda.Event()
+        ready.record(side)
+    main.wait_event(ready)
+    for cache in caches:
+        with trace.recording() as rec:
+            got = layer(cache)
+            torch.cuda.synchronize(cuda_device)
+            stages = set(rec.summary())
+        assert stages <= {"conv_fwd", "conv_dgrad", "conv_wgrad"}, stages
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+
+
 def test_empty_and_errors(cuda_device):
     set_coords_dtype(torch.int32)
     empty = st.SparseTensor(torch.empty(0, 4, device=cuda_device), torch.empty(0, 4, dtype=torch.int32),

@@ -477,6 +477,9 @@ def run_ours(args):
                        "parallelism": "dp%d by sample, NCCL all-reduce of dW" % world},
             "e2e": {"value": voxels_per_step / (e2e_ms / args.steps * 1e-3), "unit": "voxels/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+                    "h2d_gbs": h2d / (e2e_ms / args.steps * 1e-3) / 1e9, "d2h_gbs": d2h / (e2e_ms / args.steps * 1e-3) / 1e9,
+                    "bound": "host<->device copies: both directions busy at once (this pool's boxes copy 48 GB/s per "
+                             "direction when both run, 55 GB/s alone: PCIe 5 x16)",
                     "ms_per_pass": e2e_ms / e2e_passes},
             "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_pass": launches_per_step / passes,
             "stages": per_stage, "stage_rooflines": roofs, "roofline": roof, "clocks": clocks,

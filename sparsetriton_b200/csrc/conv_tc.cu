@@ -1212,6 +1212,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn encode_tiled_fn() {
+  // The encoder is a driver call and wants the device's context current on the calling thread.  A thread that has
+  // made no runtime call that binds it yet (an autograd worker on its first backward node) would get an error from
+  // the encoder and the caller would quietly take the cp.async kernels for that one call: bind it here.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   static bool tried = false;
   if (!tried) {

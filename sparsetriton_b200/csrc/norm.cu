@@ -434,26 +434,355 @@ __global__ void __launch_bounds__(kBnThreads)
   }
 }
 
-// One thread per channel: mean / rstd of every sample from the shifted one-pass sums, and the running buffers
-// (averages of the per-sample statistics over all B samples, empty ones counting as zero).
+// ---- Streaming forms: rows whose 16-byte vectors number a power of two (every width the networks use).
+// A block owns a contiguous range of rows, which is one contiguous range of bytes of every (N, C) operand, and
+// walks it in chunks of 16 KB.  A producer warp brings the chunks into a ring of shared-memory stages with bulk
+// asynchronous copies (one instruction per chunk and operand, completion counted in bytes on the stage's
+// mbarrier), so the bytes in flight per SM are set by the ring (128-192 KB with two blocks per SM) and cost
+// no registers; the 256 consumer threads read their vectors from shared memory, keep the coefficients of their
+// V channels in registers and, in the elementwise modes, store the result straight to global memory.
+// MODE 0: sums of (x - shift), (x - shift)^2   1: sums of dz, dz * xhat   2: forward output   3: dX.
+namespace stream {
+
+constexpr int kChunkBytes = 16384;
+constexpr int kConsumers = kBnThreads;                  // 8 warps
+constexpr int kThreads = kConsumers + 32;               // + the producer warp
+constexpr long long kWaitCycles = 4000000000ll;          // ~2 s: a wait that long means a copy never arrived
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.shared::cta.b64 t, [%0];\n\t}" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 t;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 t, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another warp of the block has given up already.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      if (status) atomicOr(status, ST_DEV_TIMEOUT);
+      return false;
+    }
+  }
+}
+// `bytes` (a multiple of 16) from global `src` (16-byte aligned) to shared `dst` (16-byte aligned).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+template <int MODE> struct Ring {
+  static constexpr int kOperands = (MODE == 1 || MODE == 3) ? 2 : 1;
+  static constexpr int kStages = kOperands == 2 ? 3 : 4;
+  static constexpr int kIdBytes = 4096;                   // batch indices of a chunk's rows (at most 1024 rows)
+  static constexpr int kStageBytes = kOperands * kChunkBytes + kIdBytes;
+  static constexpr int kBytes = kStages * kStageBytes + 128;
+};
+
+}  // namespace stream
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(stream::kThreads, 2)
+    bn_stream_kernel(const T* __restrict__ x, const T* __restrict__ dy, const int32_t* __restrict__ batch, int64_t n, int C,
+                     int B, const float* __restrict__ p0 /* MODE 0: unused, else mean */, const float* __restrict__ rstd,
+                     const float* __restrict__ w, const float* __restrict__ bias, int relu,
+                     const float* __restrict__ sums_in, const float* __restrict__ inv_count, float* __restrict__ sums_out,
+                     T* __restrict__ out, const int32_t* __restrict__ first_row, int64_t chunks_per_block, int32_t* status) {
+  using namespace stream;
+  constexpr int V = Vec<T>::V;
+  constexpr int A = Ring<MODE>::kOperands, S = Ring<MODE>::kStages;
+  constexpr bool kSums = MODE < 2, kBackward = (MODE & 1) != 0;
+  extern __shared__ unsigned char bn_smem_raw[];
+  __shared__ unsigned long long full[S], empty[S];
+  __shared__ int abort_word, last_lap[S];
+  volatile int* abort_flag = &abort_word;
+  const uint32_t raw = smem_u32(bn_smem_raw);
+  const uint32_t ring = (raw + 127u) & ~127u;
+  const unsigned char* ring_ptr = bn_smem_raw + (ring - raw);
+
+  const int row_bytes = C * (int)sizeof(T);
+  const int R = kChunkBytes / row_bytes;                 // rows per chunk (a power of two >= 4)
+  const int c_lanes = C / V;
+  const int64_t n_chunks = (n + R - 1) / R;
+  const int64_t k_begin = (int64_t)blockIdx.x * chunks_per_block;
+  const int64_t k_end = min(n_chunks, k_begin + chunks_per_block);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), kConsumers / 32);
+      last_lap[s] = -1;
+    }
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  float s0[V], s1[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) s0[i] = s1[i] = 0.f;
+  int cur = -1;
+  const int cl = threadIdx.x % c_lanes, c0 = cl * V;
+  const int b_common = (kSums && k_begin < k_end) ? sample_of(batch, k_begin * R, B, nullptr) : -1;
+
+  if (warp == kConsumers / 32) {
+    // ---- producer: lane 0 keeps the ring full
+    if (lane == 0) {
+      for (int64_t k = k_begin; k < k_end; ++k) {
+        const int64_t i = k - k_begin;
+        const int s = (int)(i % S);
+        const int lap = (int)(i / S);
+        if (lap > 0 && !mbar_wait(smem_u32(&empty[s]), (uint32_t)(lap - 1) & 1u, abort_flag, status)) break;
+        const int64_t row_start = k * R;
+        const int rows = (int)min((int64_t)R, n - row_start);
+        const uint32_t bytes = (uint32_t)rows * (uint32_t)row_bytes;
+        // batch indices travel with the chunk, in whole 16-byte pieces (the last rows of the last chunk, at most
+        // three, are read directly by their consumers)
+        const uint32_t id_bytes = batch ? ((uint32_t)rows * 4u) & ~15u : 0u;
+        const uint32_t bar = smem_u32(&full[s]);
+        const uint32_t stage = ring + (uint32_t)s * Ring<MODE>::kStageBytes;
+        mbar_arrive_expect_tx(bar, A * bytes + id_bytes);
+        last_lap[s] = lap;
+        bulk_load(stage, x + row_start * C, bytes, bar);
+        if (A == 2) bulk_load(stage + kChunkBytes, dy + row_start * C, bytes, bar);
+        if (id_bytes) bulk_load(stage + A * kChunkBytes, batch + row_start, id_bytes, bar);
+      }
+    }
+  } else {
+    // ---- consumers: thread t owns vectors t, t + 256, t + 512, t + 768 of every chunk (always the same V channels)
+    const int rl = threadIdx.x / c_lanes, r_step = kConsumers / c_lanes;
+    float a[V], b[V], wc[V], bc[V], q0[V], q1[V];
+    float ic = 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      a[i] = q0[i] = q1[i] = 0.f;
+      b[i] = 1.f;
+      wc[i] = (MODE != 0 && w) ? __ldg(w + c0 + i) : 1.f;
+      bc[i] = (MODE != 0 && bias) ? __ldg(bias + c0 + i) : 0.f;
+    }
+    auto flush = [&]() {                       // sums of a sample other than the block's first: added directly
+      if (!kSums || cur < 0) return;
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        atomicAdd(sums_out + ((int64_t)cur * C + c0 + i) * 2, s0[i]);
+        atomicAdd(sums_out + ((int64_t)cur * C + c0 + i) * 2 + 1, s1[i]);
+        s0[i] = s1[i] = 0.f;
+      }
+    };
+    for (int64_t k = k_begin; k < k_end; ++k) {
+      const int64_t i = k - k_begin;
+      const int s = (int)(i % S);
+      const uint32_t parity = (uint32_t)(i / S) & 1u;
+      const int64_t row_start = k * R;
+      const int rows = (int)min((int64_t)R, n - row_start);
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(smem_u32(&full[s]), parity, abort_flag, status) ? 1 : 0;
+      if (!__shfl_sync(0xFFFFFFFFu, ok, 0)) break;
+      const unsigned char* stage = ring_ptr + (size_t)s * Ring<MODE>::kStageBytes;
+      const uint4* sx = reinterpret_cast<const uint4*>(stage);
+      const uint4* sd = reinterpret_cast<const uint4*>(stage + (A - 1) * kChunkBytes);
+      const int32_t* sid = reinterpret_cast<const int32_t*>(stage + A * kChunkBytes);
+      const int rows_copied = rows & ~3;           // rows whose batch index came with the chunk
+      int bt[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int row_local = rl + j * r_step;
+        int bj = -2;
+        if (row_local < rows) {
+          bj = !batch ? 0 : (row_local < rows_copied ? sid[row_local] : __ldg(batch + row_start + row_local));
+          if ((unsigned)bj >= (unsigned)B) {
+            if (status) atomicOr(status, ST_DEV_BAD_INDEX);
+            bj = -1;
+          }
+        }
+        bt[j] = bj;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (bt[j] == -2) continue;
+        const uint4 xr = sx[j * kConsumers + threadIdx.x];
+        uint4 dr = xr;
+        if (A == 2) dr = sd[j * kConsumers + threadIdx.x];
+        T* dst = kSums ? nullptr : out + row_start * C + (int64_t)(j * kConsumers + threadIdx.x) * V;
+        if (bt[j] < 0) {                         // index outside [0, B): joins no sum, comes out as zeros
+          if (kSums) {
+            flush();
+            cur = -1;
+          } else {
+            float zero[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) zero[i] = 0.f;
+            store_vec(dst, zero);
+          }
+          continue;
+        }
+        if (bt[j] != cur) {
+          flush();                               // the sums of the sample being left go out directly
+          cur = bt[j];
+          const int64_t sc = (int64_t)cur * C + c0;
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            if (MODE == 0) {
+              a[i] = shift_from_row(x, first_row, cur, C, c0 + i);
+            } else {
+              a[i] = __ldg(p0 + sc + i);
+              b[i] = __ldg(rstd + sc + i);
+            }
+            if (MODE == 3) {
+              q0[i] = __ldg(sums_in + (sc + i) * 2);
+              q1[i] = __ldg(sums_in + (sc + i) * 2 + 1);
+            }
+          }
+          if (MODE == 3) ic = __ldg(inv_count + cur);
+        }
+        float xv[V], res[V];
+        unpack_vec<T>(xr, xv);
+        if (MODE == 0) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const float v = xv[i] - a[i];
+            s0[i] += v;
+            s1[i] += v * v;
+          }
+        } else if (MODE == 2) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            float v = (xv[i] - a[i]) * b[i];
+            if (w) v *= wc[i];
+            if (bias) v += bc[i];
+            if (relu) v = fmaxf(v, 0.f);
+            res[i] = v;
+          }
+          store_vec(dst, res);
+        } else {
+          float dv[V];
+          unpack_vec<T>(dr, dv);
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const float xhat = (xv[i] - a[i]) * b[i];
+            float dz = dv[i];
+            if (relu && !(xhat * wc[i] + bc[i] > 0.f)) dz = 0.f;
+            if (MODE == 1) {
+              s0[i] += dz;
+              s1[i] += dz * xhat;
+            } else {
+              res[i] = b[i] * wc[i] * (dz - ic * (q0[i] + xhat * q1[i]));
+            }
+          }
+          if (MODE == 3) store_vec(dst, res);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty[s]));          // this warp has read its part of the stage
+    }
+    if (kSums && cur != b_common) flush();       // what is left belongs to another sample than the block's first
+  }
+
+  if (kSums) {
+    // Partial sums of the block's first sample: row lanes that share a warp are added by shuffles, the rest
+    // through shared memory, then one atomic per channel and component.
+    const bool consumer = warp < kConsumers / 32;
+    if (consumer) {
+      for (int d = c_lanes; d < 32; d <<= 1) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          s0[i] += __shfl_xor_sync(0xFFFFFFFFu, s0[i], d);
+          s1[i] += __shfl_xor_sync(0xFFFFFFFFu, s1[i], d);
+        }
+      }
+    }
+    const bool warp_shared = c_lanes < 32;
+    const int groups = warp_shared ? kConsumers / 32 : kConsumers / c_lanes;
+    __syncthreads();                             // every stage has been read (or a wait gave up): the ring is free
+    float* red = reinterpret_cast<float*>(bn_smem_raw + (ring - raw));
+    if (consumer && (!warp_shared || lane < c_lanes)) {
+      float* mine = red + ((size_t)(warp_shared ? warp : threadIdx.x / c_lanes) * c_lanes + cl) * 2 * V;
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        mine[2 * i] = s0[i];
+        mine[2 * i + 1] = s1[i];
+      }
+    }
+    __syncthreads();
+    if (b_common >= 0 && !*abort_flag) {
+      for (int e = threadIdx.x; e < 2 * C; e += kThreads) {
+        float acc = 0.f;
+        for (int q = 0; q < groups; ++q) acc += red[(size_t)q * c_lanes * 2 * V + e];
+        const int c = (e / (2 * V)) * V + (e % (2 * V)) / 2;
+        atomicAdd(sums_out + ((int64_t)b_common * C + c) * 2 + (e & 1), acc);
+      }
+    }
+  } else {
+    __syncthreads();
+  }
+  // A wait gave up: before the block's shared memory is released, give every copy that was issued a (bounded)
+  // chance to land.
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      if (last_lap[s] < 0) continue;
+      const long long t0 = clock64();
+      while (!mbar_try(smem_u32(&full[s]), (uint32_t)last_lap[s] & 1u) && clock64() - t0 < kWaitCycles) {
+      }
+    }
+  }
+}
+
+// mean / rstd of every (sample, channel) from the shifted one-pass sums, and the running buffers (averages of the
+// per-sample statistics over all B samples, empty ones counting as zero).  A block covers 32 channels with 16
+// sample lanes, so the loads of a sample's shift row (one DRAM round trip each) overlap instead of queueing up
+// behind one another; the per-channel totals are added in a fixed order (lane by lane), so the running buffers
+// come out the same on every run.
+constexpr int kFinChannels = 32, kFinLanes = 16;
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kFinChannels * kFinLanes)
 bn_finalize_kernel(const float* __restrict__ sums, const T* __restrict__ x, const int32_t* __restrict__ first_row,
                    const float* __restrict__ inv_count, int B, int C, float eps, float momentum, float* __restrict__ mean,
                    float* __restrict__ rstd, float* running_mean, float* running_var) {
-  const int c = blockIdx.x * 128 + threadIdx.x;
-  if (c >= C) return;
+  __shared__ float part_mean[kFinLanes][kFinChannels], part_var[kFinLanes][kFinChannels];
+  const int tx = threadIdx.x % kFinChannels, ty = threadIdx.x / kFinChannels;
+  const int c = blockIdx.x * kFinChannels + tx;
   float mean_sum = 0.f, var_sum = 0.f;
-  for (int b = 0; b < B; ++b) {
-    const float ic = __ldg(inv_count + b);
-    const float shift = shift_from_row(x, first_row, b, C, c);
-    const float m1 = sums[((int64_t)b * C + c) * 2] * ic;
-    const float var = fmaxf(sums[((int64_t)b * C + c) * 2 + 1] * ic - m1 * m1, 0.f);
-    const float m = shift + m1;
-    mean[(int64_t)b * C + c] = m;
-    rstd[(int64_t)b * C + c] = rsqrtf(var + eps);
-    mean_sum += m;
-    var_sum += var;
+  if (c < C) {
+    for (int b = ty; b < B; b += kFinLanes) {
+      const float ic = __ldg(inv_count + b);
+      const float shift = shift_from_row(x, first_row, b, C, c);
+      const float m1 = sums[((int64_t)b * C + c) * 2] * ic;
+      const float var = fmaxf(sums[((int64_t)b * C + c) * 2 + 1] * ic - m1 * m1, 0.f);
+      const float m = shift + m1;
+      mean[(int64_t)b * C + c] = m;
+      rstd[(int64_t)b * C + c] = rsqrtf(var + eps);
+      mean_sum += m;
+      var_sum += var;
+    }
+  }
+  part_mean[ty][tx] = mean_sum;
+  part_var[ty][tx] = var_sum;
+  __syncthreads();
+  if (ty != 0 || c >= C) return;
+  mean_sum = var_sum = 0.f;
+  for (int l = 0; l < kFinLanes; ++l) {
+    mean_sum += part_mean[l][tx];
+    var_sum += part_var[l][tx];
   }
   if (running_mean) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mean_sum / (float)B;
   if (running_var) running_var[c] = (1.f - momentum) * running_var[c] + momentum * var_sum / (float)B;
@@ -490,6 +819,62 @@ bool vec_ok(int C, const void* a, const void* b, const void* c) {
   constexpr int V = Vec<T>::V;
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   return C % V == 0 && C / V <= kBnThreads && kBnThreads % (C / V) == 0 && al(a) && al(b) && al(c);
+}
+
+// The streaming kernels need whole 16-byte vectors per row, a power-of-two number of them (<= 256: every block
+// thread keeps its channels from chunk to chunk and a chunk holds at least four rows) and 16-byte aligned operands.
+template <typename T>
+bool stream_ok(int C, const void* a, const void* b, const void* c) {
+  constexpr int V = Vec<T>::V;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (C % V != 0) return false;
+  const int lanes = C / V;
+  return lanes >= 1 && lanes <= kBnThreads && (lanes & (lanes - 1)) == 0 && al(a) && al(b) && al(c);
+}
+bool ids_ok(const int32_t* batch) { return (reinterpret_cast<uintptr_t>(batch) & 15) == 0; }
+
+constexpr int kBnMaxDevices = 64;
+int bn_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < kBnMaxDevices) ? dev : 0;
+}
+int bn_sm_count() {
+  static int count[kBnMaxDevices] = {0};
+  const int dev = bn_device();
+  if (count[dev] == 0) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    count[dev] = v > 0 ? v : 148;
+  }
+  return count[dev];
+}
+
+// Launches bn_stream_kernel<T, MODE> over all n rows: two blocks per SM, each a contiguous range of chunks.
+template <typename T, int MODE>
+bool launch_stream(const T* x, const T* dy, const int32_t* batch, int64_t n, int C, int B, const float* p0, const float* rstd,
+                   const float* w, const float* bias, int relu, const float* sums_in, const float* inv_count, float* sums_out,
+                   T* out, const int32_t* first_row, int32_t* status, cudaStream_t s) {
+  auto kernel = bn_stream_kernel<T, MODE>;
+  constexpr int smem = stream::Ring<MODE>::kBytes;
+  static bool configured[kBnMaxDevices] = {};
+  const int dev = bn_device();
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    configured[dev] = true;
+  }
+  const int rows = stream::kChunkBytes / (C * (int)sizeof(T));
+  const int64_t n_chunks = (n + rows - 1) / rows;
+  int64_t grid = 2 * (int64_t)bn_sm_count();
+  if (grid > n_chunks) grid = n_chunks;
+  const int64_t per_block = (n_chunks + grid - 1) / grid;
+  grid = (n_chunks + per_block - 1) / per_block;
+  kernel<<<(unsigned)grid, stream::kThreads, smem, s>>>(x, dy, batch, n, C, B, p0, rstd, w, bias, relu, sums_in, inv_count,
+                                                         sums_out, out, first_row, per_block, status);
+  return true;
 }
 
 int check_bn(const char* who, int dtype, int64_t n, int C, int B) {
@@ -567,7 +952,10 @@ int st_bn_apply(int dtype, const void* X, const int32_t* batch, int64_t n, int C
   }
   cudaStream_t s = (cudaStream_t)stream;
   ST_BN_DISPATCH(dtype, {
-    if (vec_ok<T>(C, X, Y, nullptr))
+    if (stream_ok<T>(C, X, Y, nullptr) && ids_ok(batch) &&
+        launch_stream<T, 2>(static_cast<const T*>(X), nullptr, batch, n, C, B, mean, rstd, weight, bias, relu, nullptr, nullptr,
+                            nullptr, static_cast<T*>(Y), nullptr, status, s)) {
+    } else if (vec_ok<T>(C, X, Y, nullptr))
     {
       const int rows = apply_rows(C, Vec<T>::V);
       bn_apply_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C, B,
@@ -596,7 +984,10 @@ int st_bn_backward_sums(int dtype, const void* X, const void* dY, const int32_t*
     return check_launch("st_bn_backward_sums");
   if (n > 0) {
     ST_BN_DISPATCH(dtype, {
-      if (vec_ok<T>(C, X, dY, nullptr))
+      if (stream_ok<T>(C, X, dY, nullptr) && ids_ok(batch) &&
+          launch_stream<T, 1>(static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, B, mean, rstd, weight, bias, relu,
+                              nullptr, nullptr, sums, nullptr, nullptr, status, s)) {
+      } else if (vec_ok<T>(C, X, dY, nullptr))
       {
         const int rows = apply_rows(C, Vec<T>::V);
         bn_sums_vec_kernel<T, 1><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X),
@@ -624,7 +1015,10 @@ int st_bn_backward_apply(int dtype, const void* X, const void* dY, const int32_t
   }
   cudaStream_t s = (cudaStream_t)stream;
   ST_BN_DISPATCH(dtype, {
-    if (vec_ok<T>(C, X, dY, dX))
+    if (stream_ok<T>(C, X, dY, dX) && ids_ok(batch) &&
+        launch_stream<T, 3>(static_cast<const T*>(X), static_cast<const T*>(dY), batch, n, C, B, mean, rstd, weight, bias, relu,
+                            sums, inv_count, nullptr, static_cast<T*>(dX), nullptr, status, s)) {
+    } else if (vec_ok<T>(C, X, dY, dX))
     {
       const int rows = apply_rows(C, Vec<T>::V);
       bn_apply_vec_kernel<T, 1><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(
@@ -667,7 +1061,10 @@ int st_bn_forward_stats(int dtype, const void* X, const int32_t* batch, const in
   if (cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)B * C, s) != cudaSuccess) return check_launch("st_bn_forward_stats");
   ST_BN_DISPATCH(dtype, {
     if (n > 0) {
-      if (vec_ok<T>(C, X, nullptr, nullptr)) {
+      if (stream_ok<T>(C, X, nullptr, nullptr) && ids_ok(batch) &&
+          launch_stream<T, 0>(static_cast<const T*>(X), nullptr, batch, n, C, B, nullptr, nullptr, nullptr, nullptr, 0, nullptr,
+                              nullptr, sums, nullptr, first_row, status, s)) {
+      } else if (vec_ok<T>(C, X, nullptr, nullptr)) {
         const int rows = apply_rows(C, Vec<T>::V);
         bn_sums_vec_kernel<T, 0><<<apply_blocks(n, rows), kBnThreads, 0, s>>>(static_cast<const T*>(X), nullptr, batch, n, C, B,
                                                                               nullptr, nullptr, nullptr, nullptr, 0, sums, rows,
@@ -678,7 +1075,7 @@ int st_bn_forward_stats(int dtype, const void* X, const int32_t* batch, const in
       }
       note_launches(1);
     }
-    bn_finalize_kernel<T><<<(unsigned)((C + 127) / 128), 128, 0, s>>>(sums, static_cast<const T*>(X), n > 0 ? first_row : nullptr,
+    bn_finalize_kernel<T><<<(unsigned)((C + kFinChannels - 1) / kFinChannels), kFinChannels * kFinLanes, 0, s>>>(sums, static_cast<const T*>(X), n > 0 ? first_row : nullptr,
                                                                       inv_count, B, C, eps, momentum, mean, rstd, running_mean,
                                                                       running_var);
     note_launches(1);

@@ -545,6 +545,9 @@ def unet_legs(args, dist, world, rank, dev):
             out[key + "_ms_per_step"] = r["ms_per_step"]
             out[key + "_detail"] = {"prune": True, "batch": r["total_batch"], "voxels": r["total_voxels"],
                                     "launches_per_step": r["launches"], "kernel_ms_per_step": r["kernel_ms"],
+                                    "serial_ms_per_step": r["serial_ms_per_step"],
+                                    "pipelining": ("coordinate side of step i+1 (SparseUNet.prepare) on a second stream "
+                                                   "beside step i" if r["pipelined"] else "none: one stream"),
                                     "decoder": "up-convolution evaluated at the encoder's coordinates (prune=True)"}
         except Exception as e:  # noqa: BLE001
             out[key + "_ms_per_step"] = "failed: %r" % (e,)
@@ -854,8 +857,8 @@ def unet_measure(args, dist, world, rank, dev, train, steps, warmup, prune=True,
         opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
     state = {"labels": None, "scale": None, "n_out": None}
 
-    def step(coords, feats):
-        x = SparseTensor._trusted(feats, coords, shape, len(seeds))
+    def step(coords, feats, cache=None):
+        x = SparseTensor._trusted(feats, coords, shape, len(seeds), cache)
         if not train:
             with torch.no_grad():
                 out = model(x)
@@ -875,11 +878,44 @@ def unet_measure(args, dist, world, rank, dev, train, steps, warmup, prune=True,
         opt.step()
         return loss.detach()
 
+    # Timed form (stored maps, pruned decoder): while step i runs, the coordinate side of step i+1 (SparseUNet.prepare:
+    # every level's maps, plans and row counts) is built on a second stream from that step's coordinates; the
+    # step itself then launches no coordinate work and reads nothing back.  Every step still builds all of its maps.
+    pipelined = prune and args.algo != "hashfly" and not args.no_pipeline
+    main = torch.cuda.current_stream()
+    side = torch.cuda.Stream(priority=-1) if pipelined else None
+
+    def prefetch(coords=None):
+        """Coordinate side of the next step on the side stream; uploads the coordinates there first when none are given
+        (resident coordinates were uploaded and waited for before the first step)."""
+        with torch.cuda.stream(side):
+            if coords is None:
+                coords = coords_h.to(dev, non_blocking=True)
+                coords.record_stream(main)
+            cache = model.prepare(coords, shape, len(seeds), backward=train, consumer_stream=main)
+            ready = torch.cuda.Event()
+            ready.record(side)
+        return coords, cache, ready
+
     coords_d, feats_d = coords_h.to(dev), feats_h.to(dev)
+    torch.cuda.synchronize()
+    pending = {"next": None}
+
+    def run_step(_i=0):
+        if not pipelined:
+            return step(coords_d, feats_d)
+        coords, cache, ready = pending["next"] or prefetch(coords_d)
+        main.wait_event(ready)
+        r = step(coords, feats_d, cache)
+        pending["next"] = prefetch(coords_d)
+        return r
+
     for _ in range(warmup):
-        step(coords_d, feats_d)
-    dev_ms = _event_ms(dist, world, lambda _i: step(coords_d, feats_d), steps)
-    # stage breakdown and launch count: one more step with the stage recorder on (kept out of the timed steps)
+        run_step()
+    dev_ms = _event_ms(dist, world, run_step, steps)
+    pending["next"] = None
+    serial_ms = _event_ms(dist, world, lambda _i: step(coords_d, feats_d), steps) if pipelined else dev_ms
+    # stage breakdown and launch count: one more step (one stream) with the stage recorder on, outside the timed steps
     with trace.recording() as rec:
         step(coords_d, feats_d)
         _sync_all(dist, world)
@@ -889,18 +925,26 @@ def unet_measure(args, dist, world, rank, dev, train, steps, warmup, prune=True,
         result_h = torch.zeros(1, dtype=torch.float32).pin_memory()
 
         def e2e_step(_i):
-            c = coords_h.to(dev, non_blocking=True)
+            if pipelined:
+                coords, cache, ready = pending["next"] or prefetch()
+                main.wait_event(ready)
+            else:
+                coords, cache = coords_h.to(dev, non_blocking=True), None
             f = feats_h.to(dev, non_blocking=True)
-            r = step(c, f)
+            r = step(coords, f, cache)
             result_h.copy_(r.float().sum().reshape(1), non_blocking=True)
+            if pipelined:
+                pending["next"] = prefetch()
 
         for i in range(2):
             e2e_step(i)
         e2e_ms = _event_ms(dist, world, e2e_step, steps)
-    vals = _max_over_ranks(dist, world, dev, [dev_ms, e2e_ms or 0.0])
+        pending["next"] = None
+    vals = _max_over_ranks(dist, world, dev, [dev_ms, e2e_ms or 0.0, serial_ms])
     (total_voxels,) = _sum_over_ranks(dist, world, dev, [float(n_in)])
     del model, opt, bucket
     return {"ms_per_step": vals[0] / steps, "e2e_ms_per_step": (vals[1] / steps) if e2e else None, "stages": stages,
+            "serial_ms_per_step": vals[2] / steps, "pipelined": pipelined,
             "launches": launches, "kernel_ms": sum(v["ms"] for v in stages.values()), "total_voxels": total_voxels,
             "total_batch": total_batch, "n_in": n_in, "n_out": state["n_out"], "local_samples": len(seeds),
             "h2d": coords_h.numel() * 4 + feats_h.numel() * feats_h.element_size()}
@@ -939,6 +983,9 @@ def run_unet(args, train):
                        "decoder": "literal (every child of the transposed convolution)" if args.literal_decoder
                                   else "up-convolution evaluated at the encoder's coordinates (prune=True)",
                        "algo": args.algo, "parallelism": "dp%d by sample%s" % (world, ", NCCL all-reduce of one flat gradient bucket" if train else ""),
+                       "pipelining": ("coordinate side of step i+1 (SparseUNet.prepare) on a second stream beside step i"
+                                      if r["pipelined"] else "none: one stream"),
+                       "serial_ms_per_step": r["serial_ms_per_step"],
                        "l2_policy": "activations of every level exceed L2"},
             "e2e": {"value": r["total_voxels"] / (r["e2e_ms_per_step"] * 1e-3), "unit": "voxels/s",
                     "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 4, "ms_per_step": r["e2e_ms_per_step"]},

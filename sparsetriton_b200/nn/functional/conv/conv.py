@@ -174,10 +174,11 @@ class ConvPreparation:
                 if out_coords.shape[0] > 0:
                     cache.neighbor_indices[self.geometry] = (out_coords, nbr, new_shape)
             else:
-                out_coords, nbr, _ = _stored_geometry(cache, coords, self.spatial_shape, *self.geometry)
+                out_coords, nbr, new_shape = _stored_geometry(cache, coords, self.spatial_shape, *self.geometry)
             made = [out_coords, nbr]
             if nbr.shape[0] > 0:
                 made += prepare_plans(nbr, coords.shape[0], self.backward)
+        self.out_coords, self.neighbor_indices, self.new_shape = out_coords, nbr, _as_shape(new_shape)
         if cache.hashtable is not None:
             made += [cache.hashtable.table_keys, cache.hashtable.table_values]
         if self.consumer_stream is not None:
@@ -277,7 +278,9 @@ def sparse_conv3d(
 
     if submanifold and out_coords is coords:
         return tensor.replace(out_feats)
-    return SparseTensor._trusted(out_feats, out_coords, _as_shape(new_shape), tensor.batch_size)
+    # with a stored map the output coordinates are memoised per geometry, and so is the cache of what derives from them
+    child = cache.child((k, s, p, d, submanifold, transposed)) if algo == ConvAlgo.PrecomputedNeighborGEMM else None
+    return SparseTensor._trusted(out_feats, out_coords, _as_shape(new_shape), tensor.batch_size, child)
 
 
 def _as_shape(shape):

@@ -23,12 +23,24 @@ class TensorCache:
     neighbor_indices  (k, s, p, d, subm, transposed) -> (out_coords, nbr (N_out,K) int32, new_shape)
     kmaps             free-form; this implementation keeps derived maps here (inverse maps for
                       the gather-form dgrad) keyed by ("inv", <neighbor_indices key>)
+    children          (no reference counterpart) neighbor_indices key -> TensorCache of the output coordinate set
+                      of that layer: applying the same geometry to the same coordinates gives the same output
+                      coordinates, so what was derived from those (maps of the next layers) is found again, and a
+                      whole network's maps can be prepared ahead of its features
     """
 
     def __init__(self):
         self.kmaps: Dict[Tuple[Any, ...], Any] = {}
         self.hashtable: Optional[HashTable] = None
         self.neighbor_indices: Dict[Tuple[Any, ...], Tuple[torch.Tensor, torch.Tensor, Tuple]] = {}
+        self.children: Dict[Tuple[Any, ...], "TensorCache"] = {}
+
+    def child(self, key) -> "TensorCache":
+        """The cache of the output coordinate set of the layer `key` (made on first use)."""
+        c = self.children.get(key)
+        if c is None:
+            c = self.children[key] = TensorCache()
+        return c
 
 
 class SparseTensor:

@@ -29,9 +29,11 @@ from torch import nn
 
 from sparsetriton_b200.config import ConvAlgo, get_conv_algo
 from sparsetriton_b200.nn.functional.conv.funcs import ConvPrecomputedNeighborGEMM
-from sparsetriton_b200.nn.functional.conv.funcs.implicit_precomputed_gemm import inverse_map
+from sparsetriton_b200.nn.functional.conv.conv import ConvPreparation
+from sparsetriton_b200.nn.functional.conv.funcs.implicit_precomputed_gemm import inverse_map, prepare_plans
+from sparsetriton_b200.nn.functional.norm import _batch_info
 from sparsetriton_b200.nn.modules import ReLU, SparseBatchNorm, SparseConv3D, SparseConvTransposed3D, SparseLinear, SubMConv3D
-from sparsetriton_b200.tensor import SparseTensor
+from sparsetriton_b200.tensor import SparseTensor, TensorCache
 from sparsetriton_b200.utils.hash import HashTable, round_up_capacity
 
 __all__ = ["SparseUNet", "skip_concat", "up_conv_onto"]
@@ -109,6 +111,44 @@ class SparseUNet(nn.Module):
             self.up.append(SparseConvTransposed3D(widths[i], widths[i - 1], 2, stride=2, bias=False))
             self.dec.append(_Block(2 * widths[i - 1], widths[i - 1]))
         self.head = SparseLinear(widths[0], num_classes)
+
+    def prepare(self, coords, spatial_shape, batch_size, backward=True, consumer_stream=None) -> TensorCache:
+        """Everything this network derives from the input coordinates alone, ahead of the features: per level the
+        submanifold map, the down-convolution's output coordinates and map, the inverse map the pruned up-convolution
+        gathers over, their tile plans and the per-sample row counts of the normalisation layers.  Returns the
+        TensorCache for `SparseTensor(feats, coords, spatial_shape, batch_size, cache=...)`; the forward and backward
+        passes then launch no coordinate work and read nothing back from the device.
+
+        Stored-map algorithm and prune=True only.  Runs on the current stream: under a side stream it overlaps the
+        previous step (pass the training stream as `consumer_stream` and make it wait for an event recorded after
+        this call).  The waits for the three output counts are waits for that side stream alone."""
+        assert self.prune and get_conv_algo() == ConvAlgo.PrecomputedNeighborGEMM, \
+            "prepare() serves the pruned decoder under the stored-map algorithm"
+        root = cache = TensorCache()
+        shape = tuple(spatial_shape)
+        made = []
+        for level in range(len(self.enc)):
+            ConvPreparation(coords, shape, 3, submanifold=True, backward=backward, cache=cache,
+                            consumer_stream=consumer_stream).finish()
+            made += [t for t in _batch_info(SparseTensor._trusted(None, coords, shape, batch_size, cache))]
+            if level + 1 == len(self.enc):
+                break
+            down = self.down[level]
+            k, s, p, d = down.kernel_size[0], down.stride[0], down.padding[0], down.dilation[0]
+            prep = ConvPreparation(coords, shape, k, stride=s, dilation=d, padding=p, submanifold=False, backward=backward,
+                                   cache=cache, consumer_stream=consumer_stream)
+            prep.finish()
+            if prep.neighbor_indices.shape[0] > 0:
+                # the pruned up-convolution of this level is a gather over the inverse of the down-convolution's map
+                inv = inverse_map(prep.neighbor_indices, coords.shape[0])
+                made += [inv] + prepare_plans(inv, prep.out_coords.shape[0], backward)
+            cache = cache.child((k, s, p, d, False, False))
+            coords, shape = prep.out_coords, prep.new_shape
+        if consumer_stream is not None:
+            for t in made:
+                if t is not None and t.is_cuda and t.numel() > 0:
+                    t.record_stream(consumer_stream)
+        return root
 
     def forward(self, x: SparseTensor) -> SparseTensor:
         skips = []

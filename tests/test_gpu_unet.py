@@ -130,3 +130,52 @@ def test_skip_concat(cuda_device):
                           torch.tensor([[1, 1, 1, 1], [0, 9, 9, 9], [0, 2, 2, 2], [0, 1, 1, 1]], device=cuda_device))
     out = skip_concat(dec, enc)
     assert out.F.tolist() == [[1, 4, 5], [1, 0, 0], [1, 2, 3], [1, 0, 1]]
+
+
+@pytest.mark.parametrize("backward", [False, True], ids=["forward", "forward_backward"])
+def test_prepared_network_matches(cuda_device, backward):
+    """SparseUNet.prepare on a second stream, then the network on the first: the same results as the network alone, and
+    the network then launches no coordinate work.  The normalisation layers use their running statistics here, which
+    leaves the products and every feature gradient free of atomics, so those must agree bit for bit; the gradients of
+    the normalisation parameters are sums by atomic adds and agree to rounding."""
+    from sparsetriton_b200 import trace
+    set_conv_algo(ConvAlgo.PrecomputedNeighborGEMM)
+    set_coords_dtype(torch.int32)
+    coords, feats = _scene(cuda_device)
+    feats = feats.to(torch.bfloat16)
+    shape, batch = SHAPE, 2
+    assert coords.shape[0] > 10_000
+    torch.manual_seed(14)
+    model = SparseUNet(widths=(16, 32, 64), num_classes=5).to(cuda_device)
+    model.train(False)
+    names = ["logits"] + [n for n, _ in model.named_parameters()]
+
+    def run(cache):
+        model.zero_grad(set_to_none=True)
+        x = st.SparseTensor(feats, coords, shape, batch, cache=cache)
+        if not backward:
+            with torch.no_grad():
+                return [model(x).F]
+        out = model(x)
+        out.F.float().square().mean().backward()
+        return [out.F.detach()] + [p.grad.clone() for p in model.parameters()]
+
+    want = run(None)
+    main, side = torch.cuda.current_stream(cuda_device), torch.cuda.Stream(cuda_device)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        cache = model.prepare(coords, shape, batch, backward=backward, consumer_stream=main)
+        ready = torch.cuda.Event()
+        ready.record(side)
+    main.wait_event(ready)
+    with trace.recording() as rec:
+        got = run(cache)
+        torch.cuda.synchronize(cuda_device)
+        stages = set(rec.summary())
+    assert {"conv_fwd", "bn_fwd"} <= stages <= {"conv_fwd", "conv_dgrad", "conv_wgrad", "bn_fwd", "bn_bwd"}, stages
+    assert len(got) == len(want)
+    for name, a, b in zip(names, got, want):
+        if ".bn" in name:
+            assert torch.allclose(a, b, rtol=1e-4, atol=1e-7 + 1e-5 * float(b.abs().max())), name
+        else:
+            assert torch.equal(a, b), name

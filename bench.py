@@ -197,7 +197,7 @@ class C3Layer:
         `.finish()` launches the rest (output coordinates, map, tile plans) and returns the cache for `run`."""
         from sparsetriton_b200.nn.functional import ConvPreparation
         return ConvPreparation(coords, self.shape, kernel_size=KS, stride=STRIDE, padding=PAD, submanifold=False,
-                               consumer_stream=consumer)
+                               consumer_stream=consumer, batch_size=self.args.batch)
 
     def run(self, coords, feats, dy, cache=None):
         """One pass; returns (y, dx, dw).  With `cache` (from `prepare`) only the three products are left to do."""

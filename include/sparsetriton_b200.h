@@ -104,16 +104,22 @@ int64_t st_outcoords_workspace_bytes(int64_t n, int K, int stride, int transpose
  * to *n_out (device or pinned-host int64).
  * Replaces _build_out_coords_normal / _build_out_coords_transposed with expand_coords_kernel,
  * mask_spatial_range and filter_unique_kernel: nn/functional/conv/kmap.py:213-444, 11-97,
- * utils/spatial/tile.py:6-84. */
+ * utils/spatial/tile.py:6-84.
+ *
+ * batch_bound (all three passes, the same value): the number of samples the batch holds, if the caller knows it,
+ * else 0.  With it, and an output grid of at most 2^29 cells over all samples whose bitmaps fit the workspace, the
+ * coordinates are deduplicated by direct addressing (one bit per cell, ranks by popcount) instead of through a
+ * hash table: same results, but every structure then lives in L2.  Rows whose batch index is outside
+ * [0, batch_bound) are then skipped and ST_DEV_BAD_INDEX is OR-ed into *status. */
 int st_outcoords_count(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K,
-                       int stride, int transposed, const int32_t* new_shape_host, void* workspace,
+                       int stride, int transposed, const int32_t* new_shape_host, int batch_bound, void* workspace,
                        int64_t workspace_bytes, int64_t* n_out, int32_t* status, void* stream);
 
 /* Pass 2: write the surviving coordinates, ordered by first occurrence (n-major, k-minor), into
  * out_coords (same integer type as coords, out_capacity rows).  Must follow st_outcoords_count on
  * the same stream with the same arguments and workspace. */
 int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K,
-                       int stride, int transposed, const int32_t* new_shape_host, void* workspace,
+                       int stride, int transposed, const int32_t* new_shape_host, int batch_bound, void* workspace,
                        int64_t workspace_bytes, void* out_coords, int64_t out_capacity, int32_t* status,
                        void* stream);
 
@@ -124,8 +130,8 @@ int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int
  * Must follow st_outcoords_write on the same stream with the same arguments and workspace.
  * Replaces compute_neighbor_indices for strided / transposed layers, nn/functional/conv/conv.py:12-75. */
 int st_outcoords_map(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K, int stride,
-                     int transposed, const int32_t* new_shape_host, const int32_t* in_shape_host, void* workspace,
-                     int64_t workspace_bytes, int32_t* nbr, int64_t n_out, void* stream);
+                     int transposed, const int32_t* new_shape_host, const int32_t* in_shape_host, int batch_bound,
+                     void* workspace, int64_t workspace_bytes, int32_t* nbr, int64_t n_out, void* stream);
 
 /* ---------------------------------------------------------------- neighbour map ---------- */
 

@@ -35,9 +35,9 @@ _SIGNATURES = {
     "st_hash_build": ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
     "st_hash_query": ([_PTR, _I64, _INT, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
     "st_outcoords_workspace_bytes": ([_I64, _INT, _INT, _INT], _I64),
-    "st_outcoords_count": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _I64, _PTR, _PTR, _PTR], _INT),
-    "st_outcoords_write": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _I64, _PTR, _I64, _PTR, _PTR], _INT),
-    "st_outcoords_map": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _I64, _PTR], _INT),
+    "st_outcoords_count": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _INT, _PTR, _I64, _PTR, _PTR, _PTR], _INT),
+    "st_outcoords_write": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _INT, _PTR, _I64, _PTR, _I64, _PTR, _PTR], _INT),
+    "st_outcoords_map": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _INT, _PTR, _PTR, _INT, _PTR, _I64, _PTR, _I64, _PTR], _INT),
     "st_map_build": ([_PTR, _I64, _INT, _PTR, _INT, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _PTR], _INT),
     "st_map_build_symmetric": ([_PTR, _I64, _INT, _PTR, _INT, _PTR, _PTR, _PTR, _I64, _PTR, _PTR, _PTR], _INT),
     "st_conv_dgrad_mirrored": ([_INT, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),

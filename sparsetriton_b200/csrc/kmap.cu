@@ -77,24 +77,57 @@ __device__ __forceinline__ void for_each_candidate(const int4& c, const Offsets&
       if (candidate(c, off, k, stride, transposed, new_shape, &v)) f(k, v);
     }
   } else {
-    int vx[KS], vy[KS], vz[KS];
-    uint32_t mx = 0, my = 0, mz = 0;
+    // Per axis: the offsets that pass, compacted to the front (value and offset index), and how many there are.
+    // The three loops below then run over this thread's own candidates only -- at most ceil(KS / stride) per axis --
+    // where a sweep over all KS^3 combinations makes a warp walk every combination that any of its lanes needs
+    // (all 27 of a stride-2 k3 layer, of which a lane uses 3.4 on average).
+    int vx[KS], vy[KS], vz[KS], jx[KS], jy[KS], jz[KS];
+    int nx = 0, ny = 0, nz = 0;
 #pragma unroll
     for (int j = 0; j < KS; ++j) {
-      if (axis_candidate(c.y, off.v[(j * KS * KS) * 3 + 0], stride, transposed, new_shape.x, &vx[j])) mx |= 1u << j;
-      if (axis_candidate(c.z, off.v[(j * KS) * 3 + 1], stride, transposed, new_shape.y, &vy[j])) my |= 1u << j;
-      if (axis_candidate(c.w, off.v[j * 3 + 2], stride, transposed, new_shape.z, &vz[j])) mz |= 1u << j;
+      int v;
+      if (axis_candidate(c.y, off.v[(j * KS * KS) * 3 + 0], stride, transposed, new_shape.x, &v)) {
+#pragma unroll
+        for (int q = 0; q < KS; ++q)
+          if (q == nx) {
+            vx[q] = v;
+            jx[q] = j;
+          }
+        ++nx;
+      }
+      if (axis_candidate(c.z, off.v[(j * KS) * 3 + 1], stride, transposed, new_shape.y, &v)) {
+#pragma unroll
+        for (int q = 0; q < KS; ++q)
+          if (q == ny) {
+            vy[q] = v;
+            jy[q] = j;
+          }
+        ++ny;
+      }
+      if (axis_candidate(c.w, off.v[j * 3 + 2], stride, transposed, new_shape.z, &v)) {
+#pragma unroll
+        for (int q = 0; q < KS; ++q)
+          if (q == nz) {
+            vz[q] = v;
+            jz[q] = j;
+          }
+        ++nz;
+      }
     }
+    auto pick = [](const int (&a)[KS], int i) {
+      int r = a[0];
 #pragma unroll
-    for (int ix = 0; ix < KS; ++ix) {
-      if (!((mx >> ix) & 1u)) continue;
-#pragma unroll
-      for (int iy = 0; iy < KS; ++iy) {
-        if (!((my >> iy) & 1u)) continue;
-#pragma unroll
-        for (int iz = 0; iz < KS; ++iz) {
-          if ((mz >> iz) & 1u) f((ix * KS + iy) * KS + iz, Int3{vx[ix], vy[iy], vz[iz]});
-        }
+      for (int q = 1; q < KS; ++q) r = (i == q) ? a[q] : r;
+      return r;
+    };
+#pragma unroll 1
+    for (int ax = 0; ax < nx; ++ax) {
+      const int x = pick(vx, ax), ix = pick(jx, ax);
+#pragma unroll 1
+      for (int ay = 0; ay < ny; ++ay) {
+        const int y = pick(vy, ay), iy = pick(jy, ay);
+#pragma unroll 1
+        for (int az = 0; az < nz; ++az) f((ix * KS + iy) * KS + pick(jz, az), Int3{x, y, pick(vz, az)});
       }
     }
   }
@@ -509,6 +542,244 @@ pairs_write_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, const
   triples[dst * 3 + 2] = (int32_t)(t - o * K);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Output coordinates by direct addressing.  When the caller knows how many samples the batch holds and the
+// output grid of all samples has few enough cells, a coordinate needs no hash table: its cell number
+// ((b * X + x) * Y + y) * Z + z addresses one bit of a bitmap (C3: 67 M cells = 8 MB; a 1440 x 1440 x 41 lidar
+// batch of 16 at stride 2: 22 MB), which stays in L2 together with everything derived from it, where the
+// 16-byte slots of the dedupe table (128 MB on C3) are DRAM round trips.
+//
+//   bits      every candidate sets the bit of its cell                         -> set bits = output coordinates
+//   ranks     popcount per block of 256 cells + exclusive scan                 -> rank of a cell = its dense index
+//   minflat   every candidate lowers min_flat[rank(cell)] to its flat index n*K+k (the first discoverer)
+//   order     the winners' flat indices set bits of a second bitmap over n*K; its ranks are the output rows:
+//             coordinates come out ordered by first occurrence (n-major, k-minor), exactly as from the table
+//   write     winner r stores its coordinate at row rank(min_flat[r]) and leaves that row in out_row[r]
+//   map       candidate (n, k) looks up out_row[rank(cell)] and scatters n into nbr[row, k]
+// ---------------------------------------------------------------------------------------------
+struct DirectLayout {
+  int64_t cells, n_cell_blocks, n_flat_blocks, n_out_max;
+  uint32_t* cell_bits;      // n_cell_blocks * 8 words
+  uint32_t* cell_prefix;    // n_cell_blocks
+  uint32_t* flat_bits;      // n_flat_blocks * 8 words
+  uint32_t* flat_prefix;    // n_flat_blocks
+  uint32_t* min_flat;       // n_out_max
+  uint32_t* out_row;        // n_out_max
+  void* scan_tmp;
+};
+
+constexpr int64_t kDirectMaxCells = 1ll << 29;          // a bitmap of 64 MB at most: it has to live in L2
+
+// Lays the direct-addressing arrays out in `workspace` (after its 256-byte header); false when the batch size is
+// unknown, the grid is too large or the workspace (sized for the dedupe table) does not hold them.
+static bool direct_layout(void* workspace, int64_t bytes, int64_t n, int K, int stride, int transposed, const Int3& ns,
+                          int batch_bound, DirectLayout* d) {
+  if (batch_bound < 1 || ns.x < 1 || ns.y < 1 || ns.z < 1) return false;
+  const int64_t per_sample = (int64_t)ns.x * ns.y * ns.z;
+  if (per_sample > kDirectMaxCells || (int64_t)batch_bound * per_sample > kDirectMaxCells) return false;
+  d->cells = (int64_t)batch_bound * per_sample;
+  d->n_cell_blocks = (d->cells + 255) / 256;
+  d->n_flat_blocks = (n * K + 255) / 256;
+  int64_t per_input = K;
+  if (!transposed && stride > 1) {
+    int ks = 1;
+    while (ks * ks * ks < K) ++ks;
+    const int64_t c = (ks + stride - 1) / stride;
+    per_input = c * c * c;
+  }
+  d->n_out_max = n * per_input < d->cells ? n * per_input : d->cells;
+  char* p = static_cast<char*>(workspace) + 256;
+  char* end = static_cast<char*>(workspace) + bytes;
+  auto take = [&](int64_t nbytes) {
+    char* q = p;
+    p += align_up(nbytes, 256);
+    return q;
+  };
+  d->cell_bits = reinterpret_cast<uint32_t*>(take(d->n_cell_blocks * 32));
+  d->cell_prefix = reinterpret_cast<uint32_t*>(take(d->n_cell_blocks * 4));
+  d->flat_bits = reinterpret_cast<uint32_t*>(take(d->n_flat_blocks * 32));
+  d->flat_prefix = reinterpret_cast<uint32_t*>(take(d->n_flat_blocks * 4));
+  d->min_flat = reinterpret_cast<uint32_t*>(take(d->n_out_max * 4));
+  d->out_row = reinterpret_cast<uint32_t*>(take(d->n_out_max * 4));
+  const int64_t scan_n = d->n_cell_blocks > d->n_flat_blocks ? d->n_cell_blocks : d->n_flat_blocks;
+  d->scan_tmp = take(scan_tmp_bytes(scan_n));
+  return p <= end;
+}
+
+__device__ __forceinline__ int64_t cell_index(int b, const Int3& v, const Int3& shape) {
+  return (((int64_t)b * shape.x + v.x) * shape.y + v.y) * shape.z + v.z;
+}
+
+// Number of set bits below bit i: the block's prefix plus the popcounts inside its 256-bit block (one 32-byte
+// sector).
+__device__ __forceinline__ uint32_t bit_rank(const uint32_t* __restrict__ bits, const uint32_t* __restrict__ prefix,
+                                             int64_t i) {
+  const int64_t blk = i >> 8;
+  const uint4* p = reinterpret_cast<const uint4*>(bits + blk * 8);
+  const uint4 lo = p[0], hi = p[1];
+  const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+  const int wi = (int)((i >> 5) & 7);
+  const uint32_t below = (1u << (i & 31)) - 1u;
+  uint32_t r = prefix[blk];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) r += __popc(w[j] & (j < wi ? 0xFFFFFFFFu : (j == wi ? below : 0u)));
+  return r;
+}
+
+template <typename CT, int KS>
+__global__ void __launch_bounds__(kRowThreads)
+direct_bits_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
+                   Int3 new_shape, int batch_bound, uint32_t* bits, int32_t* status) {
+  const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if (row >= n) return;
+  const int4 c = load_coord<CT>(coords, row);
+  if ((unsigned)c.x >= (unsigned)batch_bound) {           // a sample the caller did not announce: no cell for it
+    atomicOr(status, ST_DEV_BAD_INDEX);
+    return;
+  }
+  for_each_candidate<KS>(c, off, K, stride, transposed, new_shape, [&](int, const Int3& v) {
+    const int64_t i = cell_index(c.x, v, new_shape);
+    const uint32_t m = 1u << (i & 31);
+    if (!(__ldcg(bits + (i >> 5)) & m)) atomicOr(bits + (i >> 5), m);
+  });
+}
+
+// counts[b] = set bits of block b (8 words)
+__global__ void __launch_bounds__(256)
+bit_block_count_kernel(const uint32_t* __restrict__ bits, int64_t n_blocks, uint32_t* __restrict__ counts) {
+  const int64_t b = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (b >= n_blocks) return;
+  const uint4* p = reinterpret_cast<const uint4*>(bits + b * 8);
+  const uint4 lo = p[0], hi = p[1];
+  counts[b] = __popc(lo.x) + __popc(lo.y) + __popc(lo.z) + __popc(lo.w) + __popc(hi.x) + __popc(hi.y) + __popc(hi.z) +
+              __popc(hi.w);
+}
+
+template <typename CT, int KS>
+__global__ void __launch_bounds__(kRowThreads)
+direct_minflat_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
+                      Int3 new_shape, int batch_bound, const uint32_t* __restrict__ bits,
+                      const uint32_t* __restrict__ prefix, uint32_t* min_flat) {
+  const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if (row >= n) return;
+  const int4 c = load_coord<CT>(coords, row);
+  if ((unsigned)c.x >= (unsigned)batch_bound) return;
+  const uint32_t flat0 = (uint32_t)row * (uint32_t)K;
+  for_each_candidate<KS>(c, off, K, stride, transposed, new_shape, [&](int k, const Int3& v) {
+    const uint32_t r = bit_rank(bits, prefix, cell_index(c.x, v, new_shape));
+    const uint32_t flat = flat0 + (uint32_t)k;
+    if (__ldcg(min_flat + r) > flat) atomicMin(min_flat + r, flat);
+  });
+}
+
+__global__ void __launch_bounds__(256)
+direct_flatbits_kernel(const uint32_t* __restrict__ min_flat, int64_t n_out, uint32_t n_flat, uint32_t* flat_bits,
+                       int32_t* status) {
+  const int64_t r = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (r >= n_out) return;
+  const uint32_t f = min_flat[r];
+  if (f >= n_flat) {                          // no candidate has this rank: the caller asked for more rows than exist
+    atomicOr(status, ST_DEV_OUT_OVERFLOW);
+    return;
+  }
+  atomicOr(flat_bits + (f >> 5), 1u << (f & 31));
+}
+
+template <typename CT>
+__global__ void __launch_bounds__(256)
+direct_write_kernel(const CT* __restrict__ coords, int K, Offsets off, int stride, bool transposed, Int3 new_shape,
+                    const uint32_t* __restrict__ min_flat, int64_t n_out, uint32_t n_flat,
+                    const uint32_t* __restrict__ flat_bits, const uint32_t* __restrict__ flat_prefix, CT* out,
+                    int64_t out_capacity, uint32_t* out_row, int32_t* status) {
+  const int64_t r = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (r >= n_out) return;
+  const uint32_t f = min_flat[r];
+  if (f >= n_flat) {
+    out_row[r] = 0xFFFFFFFFu;
+    return;
+  }
+  const uint32_t dst = bit_rank(flat_bits, flat_prefix, f);
+  out_row[r] = dst;
+  if ((int64_t)dst >= out_capacity) {
+    atomicOr(status, ST_DEV_OUT_OVERFLOW);
+    return;
+  }
+  const uint32_t row = f / (uint32_t)K;
+  const int k = (int)(f - row * (uint32_t)K);
+  const int4 c = load_coord<CT>(coords, row);
+  Int3 v;
+  candidate(c, off, k, stride, transposed, new_shape, &v);
+  store_coord<CT>(out, dst, c.x, v.x, v.y, v.z);
+}
+
+// nbr[out_row(candidate), k] = max(input row), as outcoords_map_kernel.  nbr must hold -1.
+template <typename CT, int KS>
+__global__ void __launch_bounds__(kRowThreads)
+direct_map_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed, Int3 new_shape,
+                  Int3 in_shape, int batch_bound, const uint32_t* __restrict__ bits, const uint32_t* __restrict__ prefix,
+                  const uint32_t* __restrict__ out_row, int32_t* nbr, int64_t n_out) {
+  const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if (row >= n) return;
+  const int4 c = load_coord<CT>(coords, row);
+  if ((unsigned)c.x >= (unsigned)batch_bound) return;
+  if (c.y < 0 || c.y >= in_shape.x || c.z < 0 || c.z >= in_shape.y || c.w < 0 || c.w >= in_shape.z) return;
+  for_each_candidate<KS>(c, off, K, stride, transposed, new_shape, [&](int k, const Int3& v) {
+    const uint32_t o = out_row[bit_rank(bits, prefix, cell_index(c.x, v, new_shape))];
+    if (o < (uint32_t)n_out) atomicMax(nbr + (int64_t)o * K + k, (int32_t)row);
+  });
+}
+
+template <typename CT>
+static int direct_count_impl(const CT* coords, int64_t n, const Offsets& off, int K, int stride, bool transposed, Int3 ns,
+                             int batch_bound, const DirectLayout& d, int64_t* n_out, int32_t* status, cudaStream_t s) {
+  const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
+  cudaMemsetAsync(d.cell_bits, 0, (size_t)d.n_cell_blocks * 32, s);
+  const int ks = product_kernel_size(off, K);
+  if (ks == 3)
+    direct_bits_kernel<CT, 3><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, status);
+  else if (ks == 2)
+    direct_bits_kernel<CT, 2><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, status);
+  else
+    direct_bits_kernel<CT, 0><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, status);
+  bit_block_count_kernel<<<(unsigned)((d.n_cell_blocks + 255) / 256), 256, 0, s>>>(d.cell_bits, d.n_cell_blocks, d.cell_prefix);
+  note_launches(2);
+  int rc = check_launch("st_outcoords_count");
+  if (rc != ST_OK) return rc;
+  return exclusive_scan_u32(d.cell_prefix, d.cell_prefix, d.n_cell_blocks, d.scan_tmp, n_out, s);
+}
+
+template <typename CT>
+static int direct_write_impl(const CT* coords, int64_t n, const Offsets& off, int K, int stride, bool transposed, Int3 ns,
+                             int batch_bound, const DirectLayout& d, CT* out, int64_t n_out, int32_t* status,
+                             cudaStream_t s) {
+  if (n_out > d.n_out_max) {
+    set_error("st_outcoords_write: %lld output rows asked for, at most %lld can exist", (long long)n_out,
+              (long long)d.n_out_max);
+    return ST_ERR_ARG;
+  }
+  if (n_out == 0) return ST_OK;
+  const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
+  const unsigned out_grid = (unsigned)((n_out + 255) / 256);
+  cudaMemsetAsync(d.min_flat, 0xFF, (size_t)n_out * 4, s);
+  cudaMemsetAsync(d.flat_bits, 0, (size_t)d.n_flat_blocks * 32, s);
+  const int ks = product_kernel_size(off, K);
+  if (ks == 3)
+    direct_minflat_kernel<CT, 3><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, d.cell_prefix, d.min_flat);
+  else if (ks == 2)
+    direct_minflat_kernel<CT, 2><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, d.cell_prefix, d.min_flat);
+  else
+    direct_minflat_kernel<CT, 0><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, d.cell_prefix, d.min_flat);
+  direct_flatbits_kernel<<<out_grid, 256, 0, s>>>(d.min_flat, n_out, (uint32_t)(n * K), d.flat_bits, status);
+  bit_block_count_kernel<<<(unsigned)((d.n_flat_blocks + 255) / 256), 256, 0, s>>>(d.flat_bits, d.n_flat_blocks, d.flat_prefix);
+  note_launches(3);
+  int rc = exclusive_scan_u32(d.flat_prefix, d.flat_prefix, d.n_flat_blocks, d.scan_tmp, nullptr, s);
+  if (rc != ST_OK) return rc;
+  direct_write_kernel<CT><<<out_grid, 256, 0, s>>>(coords, K, off, stride, transposed, ns, d.min_flat, n_out, (uint32_t)(n * K),
+                                                   d.flat_bits, d.flat_prefix, out, n_out, d.out_row, status);
+  note_launches(1);
+  return check_launch("st_outcoords_write");
+}
+
 template <typename CT>
 static int outcoords_count_impl(const CT* coords, int64_t n, const Offsets& off, int K, int stride, bool transposed,
                                 Int3 ns, OutCoordsWorkspace& w, int64_t* n_out, int32_t* status, cudaStream_t s) {
@@ -574,8 +845,8 @@ int64_t st_outcoords_workspace_bytes(int64_t n, int K, int stride, int transpose
 }
 
 int st_outcoords_count(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K, int stride,
-                       int transposed, const int32_t* new_shape_host, void* workspace, int64_t workspace_bytes,
-                       int64_t* n_out, int32_t* status, void* stream) {
+                       int transposed, const int32_t* new_shape_host, int batch_bound, void* workspace,
+                       int64_t workspace_bytes, int64_t* n_out, int32_t* status, void* stream) {
   Offsets off;
   Int3 ns;
   OutCoordsWorkspace w;
@@ -588,6 +859,14 @@ int st_outcoords_count(const void* coords, int64_t n, int coord_dtype, const int
   if (rc != ST_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   if (n == 0) return exclusive_scan_u32(nullptr, nullptr, 0, nullptr, n_out, s);
+  DirectLayout d;
+  if (direct_layout(workspace, workspace_bytes, n, K, stride, transposed, ns, batch_bound, &d)) {
+    if (coord_dtype == ST_I32)
+      return direct_count_impl<int32_t>(static_cast<const int32_t*>(coords), n, off, K, stride, transposed != 0, ns,
+                                        batch_bound, d, n_out, status, s);
+    return direct_count_impl<int16_t>(static_cast<const int16_t*>(coords), n, off, K, stride, transposed != 0, ns,
+                                      batch_bound, d, n_out, status, s);
+  }
   if (coord_dtype == ST_I32)
     return outcoords_count_impl<int32_t>(static_cast<const int32_t*>(coords), n, off, K, stride, transposed != 0, ns,
                                          w, n_out, status, s);
@@ -596,8 +875,8 @@ int st_outcoords_count(const void* coords, int64_t n, int coord_dtype, const int
 }
 
 int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K, int stride,
-                       int transposed, const int32_t* new_shape_host, void* workspace, int64_t workspace_bytes,
-                       void* out_coords, int64_t out_capacity, int32_t* status, void* stream) {
+                       int transposed, const int32_t* new_shape_host, int batch_bound, void* workspace,
+                       int64_t workspace_bytes, void* out_coords, int64_t out_capacity, int32_t* status, void* stream) {
   Offsets off;
   Int3 ns;
   OutCoordsWorkspace w;
@@ -610,6 +889,14 @@ int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int
   if (rc != ST_OK) return rc;
   if (n == 0) return ST_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  DirectLayout d;
+  if (direct_layout(workspace, workspace_bytes, n, K, stride, transposed, ns, batch_bound, &d)) {
+    if (coord_dtype == ST_I32)
+      return direct_write_impl<int32_t>(static_cast<const int32_t*>(coords), n, off, K, stride, transposed != 0, ns,
+                                        batch_bound, d, static_cast<int32_t*>(out_coords), out_capacity, status, s);
+    return direct_write_impl<int16_t>(static_cast<const int16_t*>(coords), n, off, K, stride, transposed != 0, ns,
+                                      batch_bound, d, static_cast<int16_t*>(out_coords), out_capacity, status, s);
+  }
   const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
   if (coord_dtype == ST_I32) {
     outcoords_write_kernel<int32_t><<<grid, kRowThreads, 0, s>>>(
@@ -625,8 +912,8 @@ int st_outcoords_write(const void* coords, int64_t n, int coord_dtype, const int
 }
 
 int st_outcoords_map(const void* coords, int64_t n, int coord_dtype, const int32_t* offsets_host, int K, int stride,
-                     int transposed, const int32_t* new_shape_host, const int32_t* in_shape_host, void* workspace,
-                     int64_t workspace_bytes, int32_t* nbr, int64_t n_out, void* stream) {
+                     int transposed, const int32_t* new_shape_host, const int32_t* in_shape_host, int batch_bound,
+                     void* workspace, int64_t workspace_bytes, int32_t* nbr, int64_t n_out, void* stream) {
   Offsets off;
   Int3 ns;
   OutCoordsWorkspace w;
@@ -644,6 +931,21 @@ int st_outcoords_map(const void* coords, int64_t n, int coord_dtype, const int32
   const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
   const Int3 in_shape = {in_shape_host[0], in_shape_host[1], in_shape_host[2]};
   const int ks = product_kernel_size(off, K);
+  DirectLayout d;
+  if (direct_layout(workspace, workspace_bytes, n, K, stride, transposed, ns, batch_bound, &d)) {
+#define ST_DMAP(CT, KS)                                                                                               \
+  direct_map_kernel<CT, KS><<<grid, kRowThreads, 0, s>>>(static_cast<const CT*>(coords), n, K, off, stride,          \
+                                                         transposed != 0, ns, in_shape, batch_bound, d.cell_bits,    \
+                                                         d.cell_prefix, d.out_row, nbr, n_out)
+    if (coord_dtype == ST_I32) {
+      if (ks == 3) ST_DMAP(int32_t, 3); else if (ks == 2) ST_DMAP(int32_t, 2); else ST_DMAP(int32_t, 0);
+    } else {
+      if (ks == 3) ST_DMAP(int16_t, 3); else if (ks == 2) ST_DMAP(int16_t, 2); else ST_DMAP(int16_t, 0);
+    }
+#undef ST_DMAP
+    note_launches(1);
+    return check_launch("st_outcoords_map");
+  }
 #define ST_MAP(CT, KS)                                                                                              \
   outcoords_map_kernel<CT, KS><<<grid, kRowThreads, 0, s>>>(static_cast<const CT*>(coords), n, K, off, stride,     \
                                                             transposed != 0, ns, in_shape, w.header, w.slots, nbr, \

@@ -105,7 +105,7 @@ def _table_and_out_coords(cache, coords, spatial_shape, k, s, p, d, submanifold,
     return table, out_coords, new_shape, koff
 
 
-def _stored_geometry(cache, coords, spatial_shape, k, s, p, d, submanifold, transposed):
+def _stored_geometry(cache, coords, spatial_shape, k, s, p, d, submanifold, transposed, batch_bound=0):
     """(out_coords, neighbor_indices, new_shape) of a layer under the stored-map algorithm, from the cache of the
     input's coordinate set or built and memoised there."""
     cache_key = (k, s, p, d, submanifold, transposed)
@@ -115,7 +115,8 @@ def _stored_geometry(cache, coords, spatial_shape, k, s, p, d, submanifold, tran
     if not (submanifold and s == 1):
         # strided / transposed layer: coordinates and map come out of one pass over the candidates; no table over
         # the inputs is needed
-        out_coords, new_shape, _, neighbor_indices = out_coords_and_map(coords, spatial_shape, k, s, d, p, transposed)
+        out_coords, new_shape, _, neighbor_indices = out_coords_and_map(coords, spatial_shape, k, s, d, p, transposed,
+                                                                        batch_bound)
     else:
         table, out_coords, new_shape, koff = _table_and_out_coords(cache, coords, spatial_shape, k, s, p, d,
                                                                    submanifold, transposed)
@@ -140,10 +141,11 @@ class ConvPreparation:
     Built under a side stream it overlaps the products of another batch; a caller that constructs the preparation of
     batch j+2 before finishing that of batch j+1 never waits for the device.  Pass the stream the layer will run on as
     `consumer_stream` so that the allocator keeps the results alive for it, and make that stream wait for an event
-    recorded after `finish()`."""
+    recorded after `finish()`.  `batch_size` (the number of samples, every batch index below it) is optional; with
+    it the output coordinates are deduplicated by direct addressing instead of hashing."""
 
     def __init__(self, coords, spatial_shape, kernel_size, stride=1, dilation=1, padding=0, transposed=False,
-                 submanifold=True, backward=True, cache=None, consumer_stream=None):
+                 submanifold=True, backward=True, cache=None, consumer_stream=None, batch_size=None):
         k = _scalar(kernel_size, "Only cubic kernels supported for now")
         s = _scalar(stride, "Only uniform stride supported for now")
         d = _scalar(dilation, "Only uniform dilation supported for now")
@@ -163,7 +165,7 @@ class ConvPreparation:
         if submanifold and s == 1:
             _stored_geometry(self.cache, coords, self.spatial_shape, k, s, p, d, submanifold, transposed)
         else:
-            self.pending = PendingOutCoordsAndMap(coords, self.spatial_shape, k, s, d, p, transposed)
+            self.pending = PendingOutCoordsAndMap(coords, self.spatial_shape, k, s, d, p, transposed, batch_size or 0)
 
     def finish(self) -> TensorCache:
         cache, coords = self.cache, self.coords
@@ -200,11 +202,12 @@ def prepare_conv3d(
     backward: bool = True,
     cache: TensorCache = None,
     consumer_stream: "torch.cuda.Stream" = None,
+    batch_size: int = None,
 ) -> TensorCache:
     """Both halves of a ConvPreparation at once, on the current stream: returns the TensorCache holding output
     coordinates, neighbour map and tile plans of the layer (no reference counterpart)."""
     return ConvPreparation(coords, spatial_shape, kernel_size, stride, dilation, padding, transposed, submanifold,
-                           backward, cache, consumer_stream).finish()
+                           backward, cache, consumer_stream, batch_size).finish()
 
 
 def _scalar(value, what):
@@ -252,7 +255,7 @@ def sparse_conv3d(
     neighbor_indices = table = koff = None
     if algo == ConvAlgo.PrecomputedNeighborGEMM:
         out_coords, neighbor_indices, new_shape = _stored_geometry(cache, coords, tensor.spatial_shape, k, s, p, d,
-                                                                   submanifold, transposed)
+                                                                   submanifold, transposed, tensor.batch_size)
     else:
         table, out_coords, new_shape, koff = _table_and_out_coords(cache, coords, tensor.spatial_shape, k, s, p, d,
                                                                    submanifold, transposed)

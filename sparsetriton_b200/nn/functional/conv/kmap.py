@@ -97,12 +97,15 @@ def build_out_coords(
     return out, new_shape_t, koff
 
 
-def out_coords_and_map(in_coords, spatial_shape, kernel_size, stride, dilation, padding, transposed):
+def out_coords_and_map(in_coords, spatial_shape, kernel_size, stride, dilation, padding, transposed, batch_bound=0):
     """Output coordinates AND the (N_out, K) neighbour map of a strided / transposed convolution in
     one pass over the candidates (the map is scattered from the same dedupe table instead of probing
     the input table N_out*K times).  Returns (out_coords, new_shape tuple, kernel_offsets tensor, nbr).
-    Same results as build_out_coords followed by compute_neighbor_indices."""
-    return PendingOutCoordsAndMap(in_coords, spatial_shape, kernel_size, stride, dilation, padding, transposed).finish()
+    Same results as build_out_coords followed by compute_neighbor_indices.  `batch_bound`: the number of samples in
+    the batch (every batch index below it) if the caller knows it, else 0; it lets the library dedupe by direct
+    addressing instead of hashing."""
+    return PendingOutCoordsAndMap(in_coords, spatial_shape, kernel_size, stride, dilation, padding, transposed,
+                                  batch_bound).finish()
 
 
 class _PendingOutCoords:
@@ -110,8 +113,9 @@ class _PendingOutCoords:
     construction, the count on its way to pinned host memory.  `finish()` waits for that copy alone (not for the
     stream), sizes the outputs and launches the second half on the same stream."""
 
-    def __init__(self, in_coords, offsets, new_shape, stride, transposed, with_map, in_shape=None):
+    def __init__(self, in_coords, offsets, new_shape, stride, transposed, with_map, in_shape=None, batch_bound=0):
         device = in_coords.device
+        self.batch_bound = int(batch_bound or 0)   # samples in the batch if known: lets the library address cells directly
         self.n, self.K = in_coords.shape[0], len(offsets)
         self.with_map, self.coord_dtype, self.device = with_map, in_coords.dtype, device
         if self.n == 0:
@@ -130,7 +134,7 @@ class _PendingOutCoords:
         self.stream = torch.cuda.current_stream(device)
         with torch.cuda.device(device), trace.stage("out_coords"):
             rc = L.st_outcoords_count(_lib.ptr(self.coords), self.n, self.code, self.off_h, self.K, stride,
-                                      self.transposed, self.shape_h, _lib.ptr(self.ws), self.ws.numel(),
+                                      self.transposed, self.shape_h, self.batch_bound, _lib.ptr(self.ws), self.ws.numel(),
                                       _lib.ptr(self.counters), _lib.ptr(self.status), _lib.stream_ptr(device))
             _lib.check(rc, "st_outcoords_count")
             self.host = torch.empty(2, dtype=torch.int64, pin_memory=True)
@@ -148,6 +152,8 @@ class _PendingOutCoords:
         n_out, flags = self.host.tolist()
         if flags & _lib.DEV_TABLE_FULL:
             raise RuntimeError("build_out_coords: dedupe table overflow")
+        if flags & _lib.DEV_BAD_INDEX:
+            raise ValueError(f"build_out_coords: a batch index lies outside [0, {self.batch_bound}) (the batch size given)")
         nbr = None
         with torch.cuda.device(device), torch.cuda.stream(self.stream):
             stream = _lib.stream_ptr(device)
@@ -155,7 +161,7 @@ class _PendingOutCoords:
             if n_out > 0:
                 with trace.stage("out_coords"):
                     rc = L.st_outcoords_write(_lib.ptr(self.coords), self.n, self.code, self.off_h, K, self.stride,
-                                              self.transposed, self.shape_h, _lib.ptr(self.ws), self.ws.numel(),
+                                              self.transposed, self.shape_h, self.batch_bound, _lib.ptr(self.ws), self.ws.numel(),
                                               _lib.ptr(out), n_out, _lib.ptr(self.status), stream)
                     _lib.check(rc, "st_outcoords_write")
             if self.with_map:
@@ -163,27 +169,27 @@ class _PendingOutCoords:
                 if n_out > 0:
                     with trace.stage("map_scatter"):
                         rc = L.st_outcoords_map(_lib.ptr(self.coords), self.n, self.code, self.off_h, K, self.stride,
-                                                self.transposed, self.shape_h, self.in_shape_h, _lib.ptr(self.ws),
-                                                self.ws.numel(), _lib.ptr(nbr), n_out, stream)
+                                                self.transposed, self.shape_h, self.in_shape_h, self.batch_bound,
+                                                _lib.ptr(self.ws), self.ws.numel(), _lib.ptr(nbr), n_out, stream)
                         _lib.check(rc, "st_outcoords_map")
         return out, nbr
 
 
-def _run_out_coords(in_coords, offsets, new_shape, stride, transposed, with_map, in_shape=None):
-    return _PendingOutCoords(in_coords, offsets, new_shape, stride, transposed, with_map, in_shape).finish()
+def _run_out_coords(in_coords, offsets, new_shape, stride, transposed, with_map, in_shape=None, batch_bound=0):
+    return _PendingOutCoords(in_coords, offsets, new_shape, stride, transposed, with_map, in_shape, batch_bound).finish()
 
 
 class PendingOutCoordsAndMap:
     """`out_coords_and_map` in two halves: construction launches the counting half, `finish()` returns what
     `out_coords_and_map` returns.  Lets a caller put other work between the launch and the wait for the count."""
 
-    def __init__(self, in_coords, spatial_shape, kernel_size, stride, dilation, padding, transposed):
+    def __init__(self, in_coords, spatial_shape, kernel_size, stride, dilation, padding, transposed, batch_bound=0):
         offsets = kernel_offsets(kernel_size, dilation, padding, transposed)
         self.koff = _offsets_tensor(offsets, in_coords)
         self.koff._st_host = [v for o in offsets for v in o]
         self.new_shape = output_shape(spatial_shape, kernel_size, stride, dilation, padding, transposed)
         self.pending = _PendingOutCoords(in_coords, offsets, self.new_shape, stride, transposed, with_map=True,
-                                         in_shape=tuple(int(v) for v in spatial_shape))
+                                         in_shape=tuple(int(v) for v in spatial_shape), batch_bound=batch_bound)
 
     def finish(self):
         out, nbr = self.pending.finish()

@@ -136,7 +136,7 @@ class SparseUNet(nn.Module):
             down = self.down[level]
             k, s, p, d = down.kernel_size[0], down.stride[0], down.padding[0], down.dilation[0]
             prep = ConvPreparation(coords, shape, k, stride=s, dilation=d, padding=p, submanifold=False, backward=backward,
-                                   cache=cache, consumer_stream=consumer_stream)
+                                   cache=cache, consumer_stream=consumer_stream, batch_size=batch_size)
             prep.finish()
             if prep.neighbor_indices.shape[0] > 0:
                 # the pruned up-convolution of this level is a gather over the inverse of the down-convolution's map

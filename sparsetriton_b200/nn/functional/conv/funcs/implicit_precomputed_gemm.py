@@ -131,19 +131,48 @@ def _is_symmetric(map_tensor, n_in):
     return flag
 
 
+_AUX_STREAMS = {}
+
+
+def _aux_stream(device, like):
+    """A second stream per device (and priority of the stream it helps) for work that is independent of what the
+    current stream does next."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), like.priority)
+    s = _AUX_STREAMS.get(key)
+    if s is None:
+        s = _AUX_STREAMS[key] = torch.cuda.Stream(device=device, priority=like.priority)
+    return s
+
+
 def prepare_plans(nbr, n_in, backward=True):
     """Builds (and memoises on the map) what the tensor-core products read besides the map: the tile plan, and with
     `backward` the feature gradient's side (nothing more for a symmetric submanifold map, else the inverse map's plan).
+    The two plans depend on the map alone and each is a chain of short kernels, so the inverse map's plan is built on
+    a second stream beside the forward one; the current stream waits for it before this returns.
     Returns the tensors made, for callers that manage streams."""
-    plan = map_plan(nbr)
-    made = [plan.order, plan.tmap, plan.tmask]
-    if backward and not _is_symmetric(nbr, n_in):
-        inv_plan = inverse_plan(nbr, n_in)
-        if inv_plan is None:
-            inv = inverse_map(nbr, n_in)
-            inv_plan = map_plan(inv)
-            made.append(inv)
+    made = []
+    fork = None
+    if backward and not _is_symmetric(nbr, n_in) and getattr(nbr, "_st_inverse_plan", None) is None \
+            and getattr(nbr, "_st_inverse", None) is None:
+        cur = torch.cuda.current_stream(nbr.device)
+        aux = _aux_stream(nbr.device, cur)
+        aux.wait_stream(cur)
+        with torch.cuda.stream(aux):
+            inv_plan = inverse_plan(nbr, n_in)
+            if inv_plan is None:
+                inv = inverse_map(nbr, n_in)
+                inv_plan = map_plan(inv)
+                made.append(inv)
+        fork = (cur, aux)
         made += [inv_plan.order, inv_plan.tmap, inv_plan.tmask]
+    plan = map_plan(nbr)
+    made += [plan.order, plan.tmap, plan.tmask]
+    if fork is not None:
+        cur, aux = fork
+        cur.wait_stream(aux)
+        for t in made:
+            if t is not None and t.is_cuda and t.numel() > 0:
+                t.record_stream(cur)
     return made
 
 

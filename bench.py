@@ -955,7 +955,12 @@ def run_unet(args, train):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    r = unet_measure(args, dist, world, rank, dev, train, args.steps, max(args.warmup, 3), prune=not args.literal_decoder)
+    samples = None
+    if args.unet_samples:
+        base = 5000 if train else 4000
+        samples = [base + rank * args.unet_samples + i for i in range(args.unet_samples)]
+    r = unet_measure(args, dist, world, rank, dev, train, args.steps, max(args.warmup, 3), prune=not args.literal_decoder,
+                     samples=samples)
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
         pk = peaks()
@@ -1015,6 +1020,8 @@ def main():
     ap.add_argument("--hashfly-in-kernel", action="store_true",
                     help="with --algo hashfly: probe the table inside the GEMM kernels instead of into a scratch map per call")
     ap.add_argument("--literal-decoder", action="store_true", help="unet_*: keep every child of the transposed convolutions")
+    ap.add_argument("--unet-samples", type=int, default=0, dest="unet_samples",
+                    help="unet_*: samples per rank instead of the BASELINE batch (8 inference / 16 training) split over the ranks")
     ap.add_argument("--workload", default="conv_layer_c3",
                     choices=["conv_layer_c3", "hash_map_c2", "unet_infer", "unet_train"])
     ap.add_argument("--cells", type=int, default=8_000_000, help="hash_map_c2: number of coordinates")

@@ -546,6 +546,7 @@ def unet_legs(args, dist, world, rank, dev):
             out[key + "_detail"] = {"prune": True, "batch": r["total_batch"], "voxels": r["total_voxels"],
                                     "launches_per_step": r["launches"], "kernel_ms_per_step": r["kernel_ms"],
                                     "serial_ms_per_step": r["serial_ms_per_step"],
+                                    "conv_by_width": r["conv_by_width"],
                                     "pipelining": ("coordinate side of step i+1 (SparseUNet.prepare) on a second stream "
                                                    "beside step i" if r["pipelined"] else "none: one stream"),
                                     "decoder": "up-convolution evaluated at the encoder's coordinates (prune=True)"}
@@ -920,6 +921,18 @@ def unet_measure(args, dist, world, rank, dev, train, steps, warmup, prune=True,
         step(coords_d, feats_d)
         _sync_all(dist, world)
         stages, launches = rec.summary(), rec.total_launches()
+        # the three products by channel widths: ms, TFLOP/s and the fraction of the sustained dense bf16 peak
+        pk = peaks()
+        peak_tf = pk["bf16_tflops_sustained"] * (0.5 if dtype == torch.float32 else 1.0)
+        widths = {}
+        for (name, tag), v in rec.by_tag().items():
+            e = widths.setdefault("%dx%d" % tag, {"ms": 0.0, "flops": 0.0, "launches": 0})
+            e["ms"] += v["ms"]
+            e["flops"] += v["work"]
+            e["launches"] += v["calls"]
+        for e in widths.values():
+            e["tflops"] = e["flops"] / (e["ms"] * 1e-3) / 1e12 if e["ms"] > 0 else None
+            e["tensor_frac"] = e["tflops"] / peak_tf if e["tflops"] else None
     e2e_ms = None
     if e2e:
         result_h = torch.zeros(1, dtype=torch.float32).pin_memory()
@@ -944,7 +957,7 @@ def unet_measure(args, dist, world, rank, dev, train, steps, warmup, prune=True,
     (total_voxels,) = _sum_over_ranks(dist, world, dev, [float(n_in)])
     del model, opt, bucket
     return {"ms_per_step": vals[0] / steps, "e2e_ms_per_step": (vals[1] / steps) if e2e else None, "stages": stages,
-            "serial_ms_per_step": vals[2] / steps, "pipelined": pipelined,
+            "serial_ms_per_step": vals[2] / steps, "pipelined": pipelined, "conv_by_width": widths,
             "launches": launches, "kernel_ms": sum(v["ms"] for v in stages.values()), "total_voxels": total_voxels,
             "total_batch": total_batch, "n_in": n_in, "n_out": state["n_out"], "local_samples": len(seeds),
             "h2d": coords_h.numel() * 4 + feats_h.numel() * feats_h.element_size()}

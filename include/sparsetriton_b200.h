@@ -64,6 +64,13 @@ long long st_launch_count(void);
 /* Sticky status of the tensor-core kernels on the current device: out4 (HOST memory, 4 x int32) =
  * {ST_DEV_* flags, id of the wait that expired, block index, reserved}.  Synchronises the stream. */
 int st_device_status(int32_t* out4, void* stream);
+
+/* The same copy without the synchronisation: out4 (PINNED host memory) holds the four words once the stream has
+ * passed this point.  Lets a caller fold the check into a wait it makes anyway.  No reference counterpart. */
+int st_device_status_enqueue(int32_t* pinned_out4, void* stream);
+
+/* Clears the sticky status word of the current device (stream-ordered).  No reference counterpart. */
+int st_device_status_clear(void* stream);
 /* 1 if the tcgen05 (tensor-core) kernels can serve this conv shape, else 0 (SIMT kernels used). */
 int st_conv_uses_tensor_cores(int dtype, int cin, int cout);
 /* Process-wide switch (default on).  With 0 every product runs on the CUDA-core kernels; used to

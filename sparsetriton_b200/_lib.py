@@ -29,6 +29,8 @@ _SIGNATURES = {
     "st_launch_count": ([], ctypes.c_longlong),
     "st_conv_uses_tensor_cores": ([_INT, _INT, _INT], _INT),
     "st_device_status": ([_PTR, _PTR], _INT),
+    "st_device_status_enqueue": ([_PTR, _PTR], _INT),
+    "st_device_status_clear": ([_PTR], _INT),
     "st_set_tensor_cores": ([_INT], _INT),
     "st_set_tma": ([_INT], _INT),
     "st_hash_clear": ([_PTR, _PTR, _I64, _PTR], _INT),
@@ -159,6 +161,21 @@ def host_i32(values):
 def workspace(nbytes, device):
     """256-byte aligned scratch from torch's caching allocator."""
     return torch.empty((max(int(nbytes), 256),), dtype=torch.uint8, device=device)
+
+
+def clear_device_status(device=None):
+    """Clears the sticky status word of the tensor-core kernels on `device` (stream-ordered)."""
+    with torch.cuda.device(device):
+        check(lib().st_device_status_clear(stream_ptr()), "st_device_status_clear")
+
+
+def raise_on_timeout(words, device):
+    """`words`: the four status words read back from the device.  A bounded wait that expired means some earlier product
+    returned partial results: clear the word (it is sticky) and raise."""
+    if int(words[0]) & DEV_TIMEOUT:
+        clear_device_status(device)
+        raise RuntimeError("a bounded wait inside a tensor-core kernel expired earlier on this device (wait site %d, "
+                           "block %d): results produced since the last check are incomplete" % (int(words[1]), int(words[2])))
 
 
 def device_status(device=None):

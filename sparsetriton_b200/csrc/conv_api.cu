@@ -130,6 +130,16 @@ int st_device_status(int32_t* out4, void* stream) {
   return tc_read_status(out4, (cudaStream_t)stream);
 }
 
+int st_device_status_enqueue(int32_t* pinned_out4, void* stream) {
+  if (!pinned_out4) {
+    set_error("st_device_status_enqueue: null output");
+    return ST_ERR_ARG;
+  }
+  return tc_read_status(pinned_out4, (cudaStream_t)stream, /*wait=*/false);
+}
+
+int st_device_status_clear(void* stream) { return tc_clear_status((cudaStream_t)stream); }
+
 int64_t st_conv_workspace_bytes(int dtype, int64_t n_in, int64_t n_out, int K, int cin, int cout) {
   (void)n_in;
   if (n_out < 0 || K < 1 || cin < 1 || cout < 1) return 256;

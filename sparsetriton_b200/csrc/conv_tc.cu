@@ -1652,11 +1652,22 @@ int tc_read_prof(long long* host_out, int n) {
   return cudaMemcpyFromSymbol(host_out, tc::g_prof, sizeof(long long) * n) == cudaSuccess ? ST_OK : ST_ERR_CUDA;
 }
 
-int tc_read_status(int32_t* host_out4, cudaStream_t stream) {
+int tc_read_status(int32_t* host_out4, cudaStream_t stream, bool wait) {
   cudaError_t e = cudaMemcpyFromSymbolAsync(host_out4, tc::g_status, sizeof(int32_t) * 4, 0, cudaMemcpyDeviceToHost, stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess && wait) e = cudaStreamSynchronize(stream);
   if (e != cudaSuccess) {
     set_error("tc_read_status: %s", cudaGetErrorString(e));
+    return ST_ERR_CUDA;
+  }
+  return ST_OK;
+}
+
+int tc_clear_status(cudaStream_t stream) {
+  void* addr = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&addr, tc::g_status);
+  if (e == cudaSuccess) e = cudaMemsetAsync(addr, 0, sizeof(int32_t) * 4, stream);
+  if (e != cudaSuccess) {
+    set_error("tc_clear_status: %s", cudaGetErrorString(e));
     return ST_ERR_CUDA;
   }
   return ST_OK;

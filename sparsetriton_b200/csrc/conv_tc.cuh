@@ -70,6 +70,7 @@ int tc_read_prof(long long* host_out, int n);
 
 // Copies the sticky device status words of the tensor-core kernels (flags, wait site, block, extra)
 // to host memory and synchronises the stream.
-int tc_read_status(int32_t* host_out4, cudaStream_t stream);
+int tc_read_status(int32_t* host_out4, cudaStream_t stream, bool wait = true);
+int tc_clear_status(cudaStream_t stream);
 
 }  // namespace st

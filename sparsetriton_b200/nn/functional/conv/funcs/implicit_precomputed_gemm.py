@@ -186,7 +186,7 @@ def stored_map_forward(x, w, nbr, n_in):
     if n_out > 0:
         # the plan only serves the tensor-core kernels
         plan = map_plan(nbr) if _lib.lib().st_conv_uses_tensor_cores(code, c_in, c_out) else _NO_PLAN
-        with torch.cuda.device(x.device), trace.stage("conv_fwd", work=flops):
+        with torch.cuda.device(x.device), trace.stage("conv_fwd", work=flops, tag=(c_in, c_out)):
             rc = _lib.lib().st_conv_fwd_planned(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
                                                 _lib.ptr(y), n_in, n_out, K, c_in, c_out, None, 0, _lib.stream_ptr())
         _lib.check(rc, "st_conv_fwd_planned")
@@ -209,21 +209,21 @@ def stored_map_dgrad(dy, w, nbr, n_in, flops=0.0):
         if tc and _is_symmetric(nbr, n_in):
             # submanifold layer: the map is its own inverse with the offsets reversed
             plan = map_plan(nbr)
-            with trace.stage("conv_dgrad", work=flops):
+            with trace.stage("conv_dgrad", work=flops, tag=(c_in, c_out)):
                 rc = L.st_conv_dgrad_mirrored(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
                                               _lib.ptr(dx), n_in, K, c_in, c_out, None, 0, stream)
             _lib.check(rc, "st_conv_dgrad_mirrored")
         elif tc and inverse_plan(nbr, n_in) is not None:
             # the kernels read the inverse map only through its plan, which comes straight from nbr
             plan = inverse_plan(nbr, n_in)
-            with trace.stage("conv_dgrad", work=flops):
+            with trace.stage("conv_dgrad", work=flops, tag=(c_in, c_out)):
                 rc = L.st_conv_dgrad_planned(code, _lib.ptr(dy), _lib.ptr(w), None, *plan.ptrs(),
                                              _lib.ptr(dx), n_in, n_out, K, c_in, c_out, None, 0, stream)
             _lib.check(rc, "st_conv_dgrad_planned")
         else:
             inv = inverse_map(nbr, n_in)
             plan = map_plan(inv) if tc else _NO_PLAN
-            with trace.stage("conv_dgrad", work=flops):
+            with trace.stage("conv_dgrad", work=flops, tag=(c_in, c_out)):
                 rc = L.st_conv_dgrad_planned(code, _lib.ptr(dy), _lib.ptr(w), _lib.ptr(inv), *plan.ptrs(),
                                              _lib.ptr(dx), n_in, n_out, K, c_in, c_out, None, 0, stream)
             _lib.check(rc, "st_conv_dgrad_planned")
@@ -245,7 +245,7 @@ def stored_map_wgrad(x, dy, nbr, K, flops=0.0):
             inv_plan = inverse_plan(nbr, n_in)
         if inv_plan is not None:
             ws = _lib.workspace(L.st_conv_wgrad_inverse_workspace_bytes(code, n_in, K, c_in, c_out), x.device)
-            with trace.stage("conv_wgrad", work=flops):
+            with trace.stage("conv_wgrad", work=flops, tag=(c_in, c_out)):
                 rc = L.st_conv_wgrad_inverse_planned(code, _lib.ptr(x), _lib.ptr(dy), *inv_plan.ptrs(), _lib.ptr(dw), n_in,
                                                      n_out, K, c_in, c_out, _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
             if rc != -5:                      # ST_ERR_UNSUPPORTED: unaligned tensors or TMA switched off -> forward plan
@@ -253,7 +253,7 @@ def stored_map_wgrad(x, dy, nbr, K, flops=0.0):
                 return dw
         ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
         plan = map_plan(nbr) if tc else _NO_PLAN
-        with trace.stage("conv_wgrad", work=flops):
+        with trace.stage("conv_wgrad", work=flops, tag=(c_in, c_out)):
             rc = L.st_conv_wgrad_planned(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), *plan.ptrs(),
                                          _lib.ptr(dw), n_in, n_out, K, c_in, c_out, _lib.ptr(ws), ws.numel(),
                                          _lib.stream_ptr())

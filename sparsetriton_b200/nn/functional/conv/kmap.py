@@ -16,6 +16,8 @@ Two reference behaviours are intentionally not reproduced:
 """
 from typing import Tuple
 
+import ctypes
+
 import torch
 
 from sparsetriton_b200 import _lib, trace
@@ -139,6 +141,10 @@ class _PendingOutCoords:
             _lib.check(rc, "st_outcoords_count")
             self.host = torch.empty(2, dtype=torch.int64, pin_memory=True)
             self.host.copy_(self.counters, non_blocking=True)
+            # the tensor-core kernels' sticky status word rides along: this is the one wait a step makes anyway
+            self.kernel_status = torch.empty(4, dtype=torch.int32, pin_memory=True)
+            _lib.check(L.st_device_status_enqueue(ctypes.c_void_p(self.kernel_status.data_ptr()), _lib.stream_ptr(device)),
+                       "st_device_status_enqueue")
             self.arrived = torch.cuda.Event()
             self.arrived.record(self.stream)
 
@@ -150,6 +156,7 @@ class _PendingOutCoords:
         L = _lib.lib()
         self.arrived.synchronize()                                     # the one device->host wait
         n_out, flags = self.host.tolist()
+        _lib.raise_on_timeout(self.kernel_status, device)
         if flags & _lib.DEV_TABLE_FULL:
             raise RuntimeError("build_out_coords: dedupe table overflow")
         if flags & _lib.DEV_BAD_INDEX:

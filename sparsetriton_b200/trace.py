@@ -20,16 +20,29 @@ _active = None
 
 class Recording:
     def __init__(self):
-        self.spans = []          # (name, start_event, end_event, launches, algorithmic work)
+        self.spans = []          # (name, start_event, end_event, launches, algorithmic work, tag)
 
     def summary(self):
         torch.cuda.synchronize()
         out = {}
-        for name, a, b, launches, work in self.spans:
+        for name, a, b, launches, work, _tag in self.spans:
             e = out.setdefault(name, {"calls": 0, "ms": 0.0, "launches": 0, "work": 0.0})
             e["calls"] += 1
             e["ms"] += a.elapsed_time(b)
             e["launches"] += launches
+            e["work"] += work
+        return out
+
+    def by_tag(self):
+        """{(stage, tag): {"calls", "ms", "work"}} over the spans that carry a tag (the products tag their channel widths)."""
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b, _launches, work, tag in self.spans:
+            if tag is None:
+                continue
+            e = out.setdefault((name, tag), {"calls": 0, "ms": 0.0, "work": 0.0})
+            e["calls"] += 1
+            e["ms"] += a.elapsed_time(b)
             e["work"] += work
         return out
 
@@ -62,7 +75,7 @@ def map_pairs(neighbor_indices):
 
 
 @contextlib.contextmanager
-def stage(name, launches=None, work=0.0):
+def stage(name, launches=None, work=0.0, tag=None):
     rec = _active
     if rec is None:
         yield
@@ -76,4 +89,4 @@ def stage(name, launches=None, work=0.0):
         yield
     finally:
         b.record()
-        rec.spans.append((name, a, b, counter() - before, float(work)))
+        rec.spans.append((name, a, b, counter() - before, float(work), tag))

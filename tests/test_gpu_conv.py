@@ -283,3 +283,24 @@ def test_modules(cuda_device):
     assert up.spatial_shape == torch.Size([16, 16, 16]) and up.batch_size == 2
     up.F.sum().backward()
     assert sub.weight.grad is not None and torch.isfinite(sub.weight.grad).all()
+
+
+def test_status_word_can_be_cleared_and_rides_with_the_output_count(cuda_device):
+    """st_device_status_enqueue / _clear: the sticky word is read without a synchronisation of its own (here through
+    the wait a strided layer makes for its output count) and stays 0 on a healthy run; clearing is stream-ordered."""
+    import ctypes
+    from sparsetriton_b200 import _lib
+    _lib.clear_device_status(cuda_device)
+    assert _lib.device_status(cuda_device)[0] == 0
+    words = torch.full((4,), -1, dtype=torch.int32).pin_memory()
+    with torch.cuda.device(cuda_device):
+        _lib.check(_lib.lib().st_device_status_enqueue(ctypes.c_void_p(words.data_ptr()), _lib.stream_ptr()),
+                   "st_device_status_enqueue")
+    torch.cuda.synchronize(cuda_device)
+    assert words.tolist()[0] == 0
+    _lib.raise_on_timeout(words, cuda_device)                       # nothing expired: no exception
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        _lib.raise_on_timeout([_lib.DEV_TIMEOUT, 33, 7, 0], cuda_device)   # host-side: what a caller would see
+    sp = st.randn((24, 24, 24), batch_size=2, channels=16, nnz=3000, device=cuda_device)
+    out = sparse_conv3d(sp, torch.rand(27, 16, 32, device=cuda_device), kernel_size=3, stride=2, padding=1, submanifold=False)
+    assert out.F.shape[1] == 32 and out.F.shape[0] > 0

@@ -181,3 +181,28 @@ def test_submanifold_map_by_symmetry_equals_full_probing(cuda_device, oracle, k,
     assert torch.equal(full, half)
     want = oracle.kernel_map(coords, shape, k, 1, d, p, False, True)[3]
     assert np.array_equal(half.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("cdt", [torch.int32, torch.int16], ids=["int32", "int16"])
+@pytest.mark.parametrize("k,s,p,d,transposed", [(3, 2, 1, 1, False), (2, 2, 0, 1, False), (3, 1, 0, 1, False), (5, 2, 2, 1, False),
+                                                (3, 2, 1, 1, True), (2, 2, 0, 1, True), (3, 3, 0, 2, False)])
+def test_direct_addressing_equals_the_hash_table(cuda_device, k, s, p, d, transposed, cdt):
+    """With the batch size given, output coordinates are deduplicated by direct addressing (cell bitmap); without,
+    through the hash table: ordered coordinates and map must be identical, duplicates in the input included."""
+    from sparsetriton_b200.nn.functional.conv.kmap import out_coords_and_map
+    set_coords_dtype(cdt)
+    batch, grid = 3, 40
+    coords = synthetic.random_cells(20_000, batch, grid, 321, dtype=cdt)
+    coords = torch.cat([coords, coords[:500]]).to(cuda_device)                # 500 duplicated rows
+    want = out_coords_and_map(coords, (grid,) * 3, k, s, d, p, transposed, batch_bound=0)
+    got = out_coords_and_map(coords, (grid,) * 3, k, s, d, p, transposed, batch_bound=batch)
+    assert got[0].shape[0] > 0 and got[1] == want[1]
+    assert torch.equal(got[0], want[0]) and torch.equal(got[3], want[3])
+
+
+def test_direct_addressing_flags_a_batch_index_beyond_the_batch(cuda_device):
+    from sparsetriton_b200.nn.functional.conv.kmap import out_coords_and_map
+    set_coords_dtype(torch.int32)
+    coords = synthetic.random_cells(5_000, 3, 32, 322).to(cuda_device)
+    with pytest.raises(ValueError, match="batch index"):
+        out_coords_and_map(coords, (32,) * 3, 3, 2, 1, 1, False, batch_bound=2)

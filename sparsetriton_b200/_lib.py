@@ -4,6 +4,7 @@ The product has no CPU fallback: if the library is missing, or a tensor that rea
 kernel is not a CUDA tensor, the call raises.  Pointers are taken from torch tensors; the
 library itself knows nothing about torch.
 """
+import contextlib
 import ctypes
 import os
 
@@ -142,6 +143,18 @@ def feat_code(t):
 
 def ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() > 0 else ctypes.c_void_p(0)
+
+
+_NULL_CONTEXT = contextlib.nullcontext()
+
+
+def on_device(device):
+    """`torch.cuda.device(device)`, or nothing at all when `device` is the current one already (the usual case:
+    the switch and the switch back cost more host time than many of the calls they guard)."""
+    index = device.index if isinstance(device, torch.device) else device
+    if index is None or index == torch.cuda.current_device():
+        return _NULL_CONTEXT
+    return torch.cuda.device(index)
 
 
 def stream_ptr(device=None):

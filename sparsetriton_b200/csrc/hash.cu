@@ -26,31 +26,54 @@ hash_clear_kernel(unsigned long long* keys, int32_t* vals, int64_t capacity) {
   }
 }
 
+// Two coordinates per thread, their probes interleaved: an insert is a chain of dependent round trips to L2 (the
+// claim, then on a collision the next slot), and the kernel is bound by that latency, not by bytes.  The first probe
+// of a key is the compare-and-swap itself -- at the load factors used most home slots are still empty, and a plain
+// load first would only add a round trip.
 template <typename CT>
 __global__ void __launch_bounds__(kThreads)
 hash_build_kernel(const CT* __restrict__ coords, int64_t n, unsigned long long* keys, int32_t* vals,
                   uint32_t capacity, uint32_t mask, int32_t* status) {
-  int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-  if (i >= n) return;
-  int4 c = load_coord<CT>(coords, i);
-  if (!key_representable(c.x, c.y, c.z, c.w)) {
-    // a negative value or one above 65535 has no key of its own (it would alias another cell's): the
-    // row is left out of the table, where st_hash_query could never return it anyway
-    atomicOr(status, ST_DEV_BAD_INDEX);
-    return;
-  }
-  unsigned long long key = pack_key(c.x, c.y, c.z, c.w);
-  uint32_t slot = home_slot(key, capacity, mask);
-  for (uint32_t step = 0; step < capacity; ++step) {
-    unsigned long long seen = keys[slot];
-    if (seen == kEmptyKey) seen = atomicCAS(keys + slot, kEmptyKey, key);
-    if (seen == kEmptyKey || seen == key) {
-      atomicMax(vals + slot, (int32_t)i);  // repeated coordinate: largest row stays
-      return;
+  constexpr int kPer = 2;
+  const int64_t i0 = (int64_t)blockIdx.x * (kThreads * kPer) + threadIdx.x;
+  unsigned long long key[kPer];
+  uint32_t slot[kPer];
+  bool live[kPer];
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int64_t i = i0 + (int64_t)j * kThreads;
+    live[j] = i < n;
+    key[j] = 0;
+    slot[j] = 0;
+    if (!live[j]) continue;
+    const int4 c = load_coord<CT>(coords, i);
+    if (!key_representable(c.x, c.y, c.z, c.w)) {
+      // a negative value or one above 65535 has no key of its own (it would alias another cell's): the
+      // row is left out of the table, where st_hash_query could never return it anyway
+      atomicOr(status, ST_DEV_BAD_INDEX);
+      live[j] = false;
+      continue;
     }
-    slot = next_slot(slot, capacity);
+    key[j] = pack_key(c.x, c.y, c.z, c.w);
+    slot[j] = home_slot(key[j], capacity, mask);
   }
-  atomicOr(status, ST_DEV_TABLE_FULL);
+  for (uint32_t step = 0; step < capacity && (live[0] || live[1]); ++step) {
+    unsigned long long seen[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j)
+      if (live[j]) seen[j] = atomicCAS(keys + slot[j], kEmptyKey, key[j]);
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      if (!live[j]) continue;
+      if (seen[j] == kEmptyKey || seen[j] == key[j]) {
+        atomicMax(vals + slot[j], (int32_t)(i0 + (int64_t)j * kThreads));  // repeated coordinate: largest row stays
+        live[j] = false;
+      } else {
+        slot[j] = next_slot(slot[j], capacity);
+      }
+    }
+  }
+  if (live[0] || live[1]) atomicOr(status, ST_DEV_TABLE_FULL);
 }
 
 template <typename CT>
@@ -130,7 +153,7 @@ int st_hash_build(const void* coords, int64_t n, int coord_dtype, int64_t* keys,
     return ST_ERR_ARG;
   }
   Table t = make_table(keys, vals, capacity);
-  unsigned grid = (unsigned)((n + kThreads - 1) / kThreads);
+  unsigned grid = (unsigned)((n + 2 * kThreads - 1) / (2 * kThreads));          // two coordinates per thread
   auto* k = reinterpret_cast<unsigned long long*>(keys);
   if (coord_dtype == ST_I32)
     { hash_build_kernel<int32_t><<<grid, kThreads, 0, (cudaStream_t)stream>>>(

@@ -56,7 +56,7 @@ def compute_neighbor_indices(
     # come in opposite pairs, so half of the probes give the whole map (no reference counterpart).
     if queries_are_table_rows and int(stride) == 1 and K % 2 == 1 and \
             all(host[i] == -host[3 * (K - 1) - 3 * (i // 3) + i % 3] for i in range(3 * K)):
-        with torch.cuda.device(device), trace.stage("map_build", 3):
+        with _lib.on_device(device), trace.stage("map_build", 3):
             asym = torch.empty(1, dtype=torch.int32, device=device)
             rc = _lib.lib().st_map_build_symmetric(_lib.ptr(coords), n_out, _lib.coord_code(coords), _lib.host_i32(host),
                                                    K, _lib.host_i32(int(v) for v in spatial_shape), _lib.ptr(keys),
@@ -73,7 +73,7 @@ def compute_neighbor_indices(
         arrived.record(torch.cuda.current_stream(device))
         nbr._st_asymmetric_rows = (flag_host, arrived)
         return nbr
-    with torch.cuda.device(device), trace.stage("map_build", 1):
+    with _lib.on_device(device), trace.stage("map_build", 1):
         rc = _lib.lib().st_map_build(_lib.ptr(coords), n_out, _lib.coord_code(coords), _lib.host_i32(host), K,
                                      int(stride), _lib.host_i32(int(v) for v in spatial_shape), _lib.ptr(keys),
                                      _lib.ptr(vals), keys.shape[0], _lib.ptr(nbr), _lib.stream_ptr())

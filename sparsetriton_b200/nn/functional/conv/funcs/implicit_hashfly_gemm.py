@@ -46,7 +46,7 @@ def _probe_map(c, offsets_h, keys, vals, shape_h, lookup_stride, K):
     n_out = c.shape[0]
     nbr = torch.empty((n_out, K), dtype=torch.int32, device=c.device)
     if n_out > 0:
-        with torch.cuda.device(c.device), trace.stage("hashfly_probe", 1):
+        with _lib.on_device(c.device), trace.stage("hashfly_probe", 1):
             rc = _lib.lib().st_map_build(_lib.ptr(c), n_out, _lib.coord_code(c), offsets_h, K, lookup_stride, shape_h,
                                          _lib.ptr(keys), _lib.ptr(vals), keys.shape[0], _lib.ptr(nbr), _lib.stream_ptr())
         _lib.check(rc, "st_map_build")
@@ -85,7 +85,7 @@ class ConvHashOnTheFlyImplicitGEMM(torch.autograd.Function):
             return y if c_out == ctx.true_widths[1] else y[:, :ctx.true_widths[1]].contiguous()
         y = torch.empty((n_out, c_out), device=x.device, dtype=x.dtype)
         if n_out > 0:
-            with torch.cuda.device(x.device), trace.stage("conv_fwd_hashfly", 1):
+            with _lib.on_device(x.device), trace.stage("conv_fwd_hashfly", 1):
                 rc = _lib.lib().st_conv_fwd_hashfly(
                     code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(c), _lib.coord_code(c), ctx.offsets_h, _lib.ptr(keys),
                     _lib.ptr(vals), keys.shape[0], ctx.shape_h, ctx.lookup_stride, _lib.ptr(y), n_in, n_out, K, c_in,
@@ -117,7 +117,7 @@ class ConvHashOnTheFlyImplicitGEMM(torch.autograd.Function):
             if dw is not None and (t_in != c_in or t_out != c_out):
                 dw = dw[:, :t_in, :t_out].contiguous()
             return dx, dw, None, None, None, None, None, None
-        with torch.cuda.device(x.device):
+        with _lib.on_device(x.device):
             stream = _lib.stream_ptr()
             ws = _lib.workspace(L.st_conv_hashfly_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
             if ctx.needs_input_grad[0]:

@@ -39,7 +39,7 @@ def inverse_map(neighbor_indices, n_in):
         return cached
     n_out, K = neighbor_indices.shape
     inv = torch.empty((n_in, K), dtype=torch.int32, device=neighbor_indices.device)
-    with torch.cuda.device(neighbor_indices.device), trace.stage("map_invert", 2):
+    with _lib.on_device(neighbor_indices.device), trace.stage("map_invert", 2):
         rc = _lib.lib().st_map_invert(_lib.ptr(neighbor_indices), n_out, K, n_in, _lib.ptr(inv), _lib.stream_ptr())
     _lib.check(rc, "st_map_invert")
     neighbor_indices._st_inverse = inv
@@ -80,7 +80,7 @@ def map_plan(map_tensor):
     tmap = torch.empty((n_tiles * K * 128,), dtype=torch.int32, device=dev)
     tmask = torch.empty((n_tiles * ((K + 31) // 32),), dtype=torch.int32, device=dev)
     ws = _lib.workspace(L.st_map_plan_workspace_bytes(n_rows, K), dev) if sort_rows else None
-    with torch.cuda.device(dev), trace.stage("map_plan"):
+    with _lib.on_device(dev), trace.stage("map_plan"):
         rc = L.st_map_plan(_lib.ptr(map_tensor), n_rows, K, 1 if sort_rows else 0, _lib.ptr(order), _lib.ptr(tmap),
                            _lib.ptr(tmask), _lib.ptr(ws), ws.numel() if ws is not None else 0, _lib.stream_ptr())
     _lib.check(rc, "st_map_plan")
@@ -107,7 +107,7 @@ def inverse_plan(neighbor_indices, n_in):
     tmap = torch.empty((n_tiles * K * 128,), dtype=torch.int32, device=dev)
     tmask = torch.empty((n_tiles,), dtype=torch.int32, device=dev)
     ws = _lib.workspace(L.st_map_plan_inverse_workspace_bytes(n_in, K), dev)
-    with torch.cuda.device(dev), trace.stage("map_plan_inverse"):
+    with _lib.on_device(dev), trace.stage("map_plan_inverse"):
         rc = L.st_map_plan_inverse(_lib.ptr(neighbor_indices), n_out, K, n_in, _lib.ptr(order), _lib.ptr(tmap),
                                    _lib.ptr(tmask), _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
     _lib.check(rc, "st_map_plan_inverse")
@@ -186,7 +186,7 @@ def stored_map_forward(x, w, nbr, n_in):
     if n_out > 0:
         # the plan only serves the tensor-core kernels
         plan = map_plan(nbr) if _lib.lib().st_conv_uses_tensor_cores(code, c_in, c_out) else _NO_PLAN
-        with torch.cuda.device(x.device), trace.stage("conv_fwd", work=flops, tag=(c_in, c_out)):
+        with _lib.on_device(x.device), trace.stage("conv_fwd", work=flops, tag=(c_in, c_out)):
             rc = _lib.lib().st_conv_fwd_planned(code, _lib.ptr(x), _lib.ptr(w), _lib.ptr(nbr), *plan.ptrs(),
                                                 _lib.ptr(y), n_in, n_out, K, c_in, c_out, None, 0, _lib.stream_ptr())
         _lib.check(rc, "st_conv_fwd_planned")
@@ -203,7 +203,7 @@ def stored_map_dgrad(dy, w, nbr, n_in, flops=0.0):
     dx = torch.empty((n_in, c_in), device=dy.device, dtype=dy.dtype)
     if n_in == 0:
         return dx
-    with torch.cuda.device(dy.device):
+    with _lib.on_device(dy.device):
         stream = _lib.stream_ptr()
         tc = bool(L.st_conv_uses_tensor_cores(code, c_out, c_in))
         if tc and _is_symmetric(nbr, n_in):
@@ -239,7 +239,7 @@ def stored_map_wgrad(x, dy, nbr, K, flops=0.0):
     L = _lib.lib()
     dw = torch.empty((K, c_in, c_out), device=x.device, dtype=x.dtype)
     tc = bool(L.st_conv_uses_tensor_cores(code, c_in, c_out))
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         inv_plan = None
         if WGRAD_OVER_INVERSE_PLAN and tc and n_in > n_out > 0 and not _is_symmetric(nbr, n_in):
             inv_plan = inverse_plan(nbr, n_in)

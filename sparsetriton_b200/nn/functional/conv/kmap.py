@@ -134,7 +134,7 @@ class _PendingOutCoords:
         self.counters = torch.zeros(2, dtype=torch.int64, device=device)      # [n_out, status]
         self.status = self.counters[1:].view(torch.int32)
         self.stream = torch.cuda.current_stream(device)
-        with torch.cuda.device(device), trace.stage("out_coords"):
+        with _lib.on_device(device), trace.stage("out_coords"):
             rc = L.st_outcoords_count(_lib.ptr(self.coords), self.n, self.code, self.off_h, self.K, stride,
                                       self.transposed, self.shape_h, self.batch_bound, _lib.ptr(self.ws), self.ws.numel(),
                                       _lib.ptr(self.counters), _lib.ptr(self.status), _lib.stream_ptr(device))
@@ -162,7 +162,7 @@ class _PendingOutCoords:
         if flags & _lib.DEV_BAD_INDEX:
             raise ValueError(f"build_out_coords: a batch index lies outside [0, {self.batch_bound}) (the batch size given)")
         nbr = None
-        with torch.cuda.device(device), torch.cuda.stream(self.stream):
+        with _lib.on_device(device), torch.cuda.stream(self.stream):
             stream = _lib.stream_ptr(device)
             out = torch.empty((n_out, 4), dtype=self.coord_dtype, device=device)
             if n_out > 0:

@@ -33,7 +33,7 @@ def _batch_info(tensor: SparseTensor):
         counts = counts.clamp(min=1).to(torch.float32)
         # first row of every sample (-1 for an empty one): the statistics are summed around that row's values
         first = torch.empty((tensor.batch_size,), dtype=torch.int32, device=ids.device)
-        with torch.cuda.device(ids.device):
+        with _lib.on_device(ids.device):
             _lib.check(_lib.lib().st_bn_first_rows(_lib.ptr(ids), ids.shape[0], tensor.batch_size, _lib.ptr(first),
                                                    _lib.stream_ptr()), "st_bn_first_rows")
         hit = (ids, (1.0 / counts).contiguous(), torch.zeros(1, dtype=torch.int32, device=ids.device), first)
@@ -62,7 +62,7 @@ class _BatchNormFn(torch.autograd.Function):
         dev = x.device
         w = weight.detach().float().contiguous() if weight is not None else None
         b = bias.detach().float().contiguous() if bias is not None else None
-        with torch.cuda.device(dev), trace.stage("bn_fwd"):
+        with _lib.on_device(dev), trace.stage("bn_fwd"):
             s = _lib.stream_ptr()
             if mean_in is None:
                 sums = torch.empty((n_samples, C, 2), dtype=torch.float32, device=dev)
@@ -92,7 +92,7 @@ class _BatchNormFn(torch.autograd.Function):
         code = _lib.feat_code(x)
         dy = dy.to(x.dtype).contiguous()
         dev = x.device
-        with torch.cuda.device(dev), trace.stage("bn_bwd"):
+        with _lib.on_device(dev), trace.stage("bn_bwd"):
             sums = torch.empty((n_samples, C, 2), dtype=torch.float32, device=dev)
             dw = torch.empty((C,), dtype=torch.float32, device=dev) if has_w else None
             db = torch.empty((C,), dtype=torch.float32, device=dev) if has_b else None

@@ -44,7 +44,7 @@ class SparsePoolingFunction(torch.autograd.Function):
         ws = _lib.workspace(L.st_pool_workspace_bytes(n), dev)
         counters = torch.zeros(2, dtype=torch.int64, device=dev)          # [n_out, status]
         status = counters[1:].view(torch.int32)
-        with torch.cuda.device(dev), trace.stage("pool_map"):
+        with _lib.on_device(dev), trace.stage("pool_map"):
             s = _lib.stream_ptr()
             _lib.check(L.st_pool_count(_lib.ptr(coords), n, ccode, kernel_size, padding, stride, shape_h, int(batch_size),
                                        _lib.ptr(ws), ws.numel(), _lib.ptr(counters), _lib.ptr(status), s), "st_pool_count")
@@ -59,7 +59,7 @@ class SparsePoolingFunction(torch.autograd.Function):
                                        _lib.ptr(ws), ws.numel(), _lib.ptr(out_coords), n_out, _lib.ptr(in_to_out),
                                        _lib.ptr(members), _lib.ptr(seg_start), s), "st_pool_write")
         out_feats = torch.empty((n_out, C), dtype=feats.dtype, device=dev)
-        with torch.cuda.device(dev), trace.stage("pool_fwd"):
+        with _lib.on_device(dev), trace.stage("pool_fwd"):
             _lib.check(L.st_pool_fwd(code, _lib.ptr(feats), C, _lib.ptr(members), _lib.ptr(seg_start), n_out,
                                      int(mode == "max"), _lib.ptr(out_feats), _lib.stream_ptr()), "st_pool_fwd")
         ctx.save_for_backward(feats, out_feats, in_to_out, seg_start)
@@ -73,7 +73,7 @@ class SparsePoolingFunction(torch.autograd.Function):
         n, C = feats.shape
         g = grad_out_feats.to(feats.dtype).contiguous()
         grad_in = torch.empty_like(feats)
-        with torch.cuda.device(feats.device), trace.stage("pool_bwd"):
+        with _lib.on_device(feats.device), trace.stage("pool_bwd"):
             _lib.check(_lib.lib().st_pool_bwd(_lib.feat_code(feats), _lib.ptr(g), _lib.ptr(feats), _lib.ptr(out_feats), C,
                                               _lib.ptr(in_to_out), _lib.ptr(seg_start), n, int(ctx.mode == "max"),
                                               _lib.ptr(grad_in), _lib.stream_ptr()), "st_pool_bwd")
@@ -97,7 +97,7 @@ class SparseUpsampleFunction(torch.autograd.Function):
         dev = feats.device
         out_feats = torch.empty((n * s3, C), dtype=feats.dtype, device=dev)
         out_coords = torch.empty((n * s3, 4), dtype=coords.dtype, device=dev)
-        with torch.cuda.device(dev), trace.stage("upsample_fwd"):
+        with _lib.on_device(dev), trace.stage("upsample_fwd"):
             _lib.check(_lib.lib().st_upsample_fwd(_lib.feat_code(feats), _lib.ptr(feats), _lib.ptr(coords),
                                                   _lib.coord_code(coords), n, C, int(scale_factor), _lib.ptr(out_feats),
                                                   _lib.ptr(out_coords), _lib.stream_ptr()), "st_upsample_fwd")
@@ -110,7 +110,7 @@ class SparseUpsampleFunction(torch.autograd.Function):
         n, C, scale = ctx.geometry
         g = grad_output.contiguous()
         grad_in = torch.empty((n, C), dtype=g.dtype, device=g.device)
-        with torch.cuda.device(g.device), trace.stage("upsample_bwd"):
+        with _lib.on_device(g.device), trace.stage("upsample_bwd"):
             _lib.check(_lib.lib().st_upsample_bwd(_lib.feat_code(g), _lib.ptr(g), n, C, scale, _lib.ptr(grad_in),
                                                   _lib.stream_ptr()), "st_upsample_bwd")
         return grad_in, None, None, None

@@ -74,12 +74,19 @@ def map_pairs(neighbor_indices):
     return n
 
 
-@contextlib.contextmanager
+_NULL_CONTEXT = contextlib.nullcontext()
+
+
 def stage(name, launches=None, work=0.0, tag=None):
+    """Context manager around one C-ABI call site: nothing when no recording is open."""
+    if _active is None:
+        return _NULL_CONTEXT
+    return _recorded_stage(name, launches, work, tag)
+
+
+@contextlib.contextmanager
+def _recorded_stage(name, launches, work, tag):
     rec = _active
-    if rec is None:
-        yield
-        return
     counter = _lib.lib().st_launch_count
     a = torch.cuda.Event(enable_timing=True)
     b = torch.cuda.Event(enable_timing=True)

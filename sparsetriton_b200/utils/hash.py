@@ -58,7 +58,7 @@ class HashTable:
         if dev.type == "cuda" and capacity > 0:
             self.table_keys = torch.empty((capacity,), dtype=torch.int64, device=dev)
             self.table_values = torch.empty((capacity,), dtype=torch.int32, device=dev)
-            with torch.cuda.device(self.table_keys.device), trace.stage("hash_clear", 1):
+            with _lib.on_device(self.table_keys.device), trace.stage("hash_clear", 1):
                 rc = _lib.lib().st_hash_clear(_lib.ptr(self.table_keys), _lib.ptr(self.table_values), capacity,
                                               _lib.stream_ptr())
             _lib.check(rc, "st_hash_clear")
@@ -108,7 +108,7 @@ class HashTable:
         status = getattr(self, "_status", None)
         if status is None or status.device != coords.device:
             status = self._status = torch.zeros(1, dtype=torch.int32, device=coords.device)
-        with torch.cuda.device(coords.device), trace.stage("hash_build", 1):
+        with _lib.on_device(coords.device), trace.stage("hash_build", 1):
             rc = _lib.lib().st_hash_build(_lib.ptr(coords), coords.shape[0], _lib.coord_code(coords),
                                           _lib.ptr(self.table_keys), _lib.ptr(self.table_values), self.capacity,
                                           _lib.ptr(status), _lib.stream_ptr())
@@ -132,7 +132,7 @@ class HashTable:
             return torch.empty((0,), dtype=torch.int32, device=self.device)
         coords = self._kernel_ready(keys, "HashTable.query")
         out = torch.empty((n,), dtype=torch.int32, device=coords.device)
-        with torch.cuda.device(coords.device), trace.stage("hash_query", 1):
+        with _lib.on_device(coords.device), trace.stage("hash_query", 1):
             rc = _lib.lib().st_hash_query(_lib.ptr(coords), n, _lib.coord_code(coords), _lib.ptr(self.table_keys),
                                           _lib.ptr(self.table_values), self.capacity, _lib.ptr(out),
                                           _lib.stream_ptr())

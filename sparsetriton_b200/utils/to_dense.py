@@ -26,7 +26,7 @@ class ToDenseFunction(torch.autograd.Function):
         shape = tuple(int(v) for v in spatial_range)
         dense = torch.empty((int(batch_size), *shape, C), dtype=feats.dtype, device=feats.device)
         status = torch.zeros(1, dtype=torch.int32, device=feats.device)
-        with torch.cuda.device(feats.device), trace.stage("to_dense_fwd"):
+        with _lib.on_device(feats.device), trace.stage("to_dense_fwd"):
             rc = _lib.lib().st_to_dense_fwd(_lib.feat_code(feats), _lib.ptr(feats), _lib.ptr(coords), _lib.coord_code(coords),
                                             n, C, int(batch_size), _lib.host_i32(shape), _lib.ptr(dense), _lib.ptr(status),
                                             _lib.stream_ptr())
@@ -41,7 +41,7 @@ class ToDenseFunction(torch.autograd.Function):
         n, C, batch, shape = ctx.geometry
         grad_output = grad_output.contiguous()
         grad_feats = torch.empty((n, C), dtype=grad_output.dtype, device=grad_output.device)
-        with torch.cuda.device(grad_output.device), trace.stage("to_dense_bwd"):
+        with _lib.on_device(grad_output.device), trace.stage("to_dense_bwd"):
             rc = _lib.lib().st_to_dense_bwd(_lib.feat_code(grad_output), _lib.ptr(grad_output), _lib.ptr(coords),
                                             _lib.coord_code(coords), n, C, batch, _lib.host_i32(shape),
                                             _lib.ptr(grad_feats), _lib.stream_ptr())

@@ -213,7 +213,7 @@ class C3Layer:
     def one_pass(self, j):
         return self.run(*self.resident[j % len(self.resident)])
 
-    def pipelined(self, passes, side):
+    def pipelined(self, passes, side, keep=None):
         """`passes` passes with the coordinate side of the passes ahead on stream `side`, beside the products of pass j:
         while pass j's products run, the second half of pass j+1's preparation and the first half of pass j+2's are
         launched, so the host never waits for a count that is not already there.  Every pass still builds its own
@@ -237,11 +237,30 @@ class C3Layer:
         for j in range(passes):
             cache, ready = current
             main.wait_event(ready)
-            self.run(*self.resident[j % len(self.resident)], cache=cache)
+            out = self.run(*self.resident[j % len(self.resident)], cache=cache)
+            if keep is not None:
+                keep.append(out)
             if ahead is not None:
                 current = finish(ahead)
                 ahead = begin(j + 2) if j + 2 < passes else None
         main.wait_stream(side)
+
+    def overlapped_equals_serial(self, side, passes=5):
+        """The overlapped form must give, bit for bit, what the passes give on one stream (nothing in the path is
+        order-dependent: no atomics in the products, deterministic maps and plans)."""
+        got = []
+        self.pipelined(passes, side, keep=got)
+        torch.cuda.synchronize()
+        for j, out in enumerate(got):
+            want = self.one_pass(j)
+            torch.cuda.synchronize()
+            if not (torch.equal(out[0], want[0]) and torch.equal(out[1], want[1])):
+                return False
+            # dW went through the all-reduce when there are several ranks: equal up to the collective's own rounding
+            if not (torch.equal(out[2], want[2]) if self.world == 1 else
+                    torch.allclose(out[2].float(), want[2].float(), rtol=2e-2, atol=1e-3)):
+                return False
+        return True
 
     def voxels(self, passes):
         return sum(self.n_in[j % len(self.n_in)] for j in range(passes))
@@ -353,6 +372,7 @@ def run_ours(args):
         sampler.start()
     dev_ms = _event_ms(dist, world, step, args.steps)
     serial_ms = _event_ms(dist, world, serial_step, args.steps) if pipelined else dev_ms
+    same = layer.overlapped_equals_serial(side) if pipelined else None
     step = serial_step
     # the per-stage breakdown and the launch count come from one more step with the stage recorder on (its event
     # pairs cost host time, so it stays out of the timed steps)
@@ -469,6 +489,7 @@ def run_ours(args):
                                       "(prepare_conv3d); every pass builds its own coordinates, map and plans"
                                       if pipelined else "none: one stream"),
                        "serial_ms_per_pass": serial_ms / args.steps / passes,
+                       "overlapped_results_equal_serial_bitwise": same,
                        "n_in_per_pass": n_in, "n_out_per_pass": n_out, "pairs_per_pass": pairs,
                        "constructor": "SparseTensor._trusted (the library's internal constructor: no validation read of the "
                                       "coordinates; the public one adds one device->host read per tensor)",

@@ -206,3 +206,22 @@ def test_direct_addressing_flags_a_batch_index_beyond_the_batch(cuda_device):
     coords = synthetic.random_cells(5_000, 3, 32, 322).to(cuda_device)
     with pytest.raises(ValueError, match="batch index"):
         out_coords_and_map(coords, (32,) * 3, 3, 2, 1, 1, False, batch_bound=2)
+
+
+def test_direct_addressing_edge_cases(cuda_device):
+    """No candidate at all (every input falls outside the output grid), a single voxel, and a batch bound larger
+    than the samples present."""
+    from sparsetriton_b200.nn.functional.conv.kmap import out_coords_and_map
+    set_coords_dtype(torch.int32)
+    one = torch.tensor([[1, 5, 6, 7]], dtype=torch.int32, device=cuda_device)
+    for bound in (0, 2, 64):
+        oc, shape, _, nbr = out_coords_and_map(one, (16, 16, 16), 3, 2, 1, 1, False, batch_bound=bound)
+        # (5,6,7) + off is even on every axis for four offsets, in ascending k: 3, 5, 21, 23
+        assert oc.tolist() == [[1, 3, 3, 4], [1, 3, 3, 3], [1, 2, 3, 4], [1, 2, 3, 3]]
+        assert nbr.shape == (4, 27) and [int(nbr[r, k]) for r, k in enumerate((3, 5, 21, 23))] == [0, 0, 0, 0]
+        assert int((nbr >= 0).sum()) == 4
+    # k2 s2 on a 1-cell-wide grid: the output grid is empty
+    thin = torch.tensor([[0, 0, 0, 0]], dtype=torch.int32, device=cuda_device)
+    for bound in (0, 1):
+        oc, shape, _, nbr = out_coords_and_map(thin, (1, 1, 1), 2, 2, 1, 0, False, batch_bound=bound)
+        assert oc.shape[0] == 0 and nbr.shape[0] == 0

@@ -41,7 +41,8 @@ def _scene(n, C, B, dtype, dev, seed, sorted_batches=True):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16], ids=["fp32", "bf16", "fp16"])
 @pytest.mark.parametrize("n,C,B,sorted_batches", [(1, 16, 1, True), (777, 32, 3, True), (20000, 64, 4, True),
                                                   (5000, 48, 5, False), (3000, 256, 2, True), (900, 5, 2, True),
-                                                  (1200, 20, 4, True), (6000, 32, 5, False), (300_000, 32, 7, True)])
+                                                  (1200, 20, 4, True), (6000, 32, 5, False), (300_000, 32, 7, True),
+                                                  (1000, 512, 2, True), (300, 2048, 2, True), (5, 8, 1, True)])
 def test_training_forward_backward(cuda_device, oracle, dtype, relu, n, C, B, sorted_batches):
     dev = cuda_device
     sp, bidx = _scene(n, C, B, dtype, dev, 100 + n + C, sorted_batches)

@@ -466,7 +466,7 @@ def make_bn():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="checkout of the unmodified reference (the directory that holds sparsetriton/)")
     ap.add_argument("--only", default=None, help="substring filter on fixture names")
     ap.add_argument("--c1", action="store_true", help="also run the 4096-voxel headline case (minutes)")
     args = ap.parse_args()

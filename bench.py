@@ -266,6 +266,9 @@ class C3Layer:
         return sum(self.n_in[j % len(self.n_in)] for j in range(passes))
 
 
+GATHER_CEILING_GBS = 4400.0      # measured row-gather rate of one B200 (see stage_rooflines)
+
+
 def conv_bytes(kind, n_in, n_out, pairs, es):
     """Compulsory traffic of one product, e*(N_in*Cin + N_out*Cout + K*Cin*Cout) + 4*rows*K (the map is read once:
     the forward map for fwd and wgrad, the (N_in, K) inverse map for dgrad), and the bytes the kernel gathers."""
@@ -304,6 +307,12 @@ def stage_rooflines(per_stage, n_in, n_out, pairs, pk, dtype):
                           "tensor_frac": flops / (ms * 1e-3) / 1e12 / tc_peak})
             if t_hbm < t_tc:
                 entry["frac"] = entry["tensor_frac"]
+            # what these kernels are bound by in practice: rows pulled into shared memory per second.  A microbenchmark
+            # on this pool's B200 (one 16 KB slot = 128 rows of 128 bytes per tile::gather4 burst, ring of slots,
+            # 148 CTAs) tops out at 15.7 B/clk/SM = 4.4 TB/s for random rows out of DRAM
+            entry["gather_gbs"] = gathered / (ms * 1e-3) / 1e9
+            entry["gather_ceiling_gbs"] = GATHER_CEILING_GBS
+            entry["gather_frac"] = entry["gather_gbs"] / GATHER_CEILING_GBS
         else:
             if kind == "out_coords":
                 nbytes = n_in * (16 + 12 * K / 8.0) + 16 * n_out

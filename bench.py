@@ -172,6 +172,7 @@ class C3Layer:
         bound = 1.0 / (CIN * K) ** 0.5
         self.weight = ((torch.rand(K, CIN, COUT, generator=torch.Generator().manual_seed(7)) * 2 - 1) * bound).to(dtype).to(dev)
         self.host, self.resident, self.n_in, self.n_out, self.pairs = [], [], [], [], []
+        self.steps_fwd, self.steps_inv = [], []
         for j in range(n_batches):
             coords_h = make_batch(3000 + (rank * n_batches + j) * args.batch, args.batch, args.per_sample, args.grid).pin_memory()
             gen = torch.Generator(device="cpu").manual_seed(9000 + rank * n_batches + j)
@@ -184,7 +185,18 @@ class C3Layer:
             nbr = sp._cache.neighbor_indices[(KS, STRIDE, PAD, 1, False, False)][1]
             n_out = out.F.shape[0]
             self.pairs.append(int((nbr >= 0).sum().item()))
-            del sp, out, nbr
+            # (tile, offset) steps of the two tile plans = 128-row gather slots the products issue (one per step and
+            # 128-byte line of a row): what their copy time is proportional to, absent rows of a slot included
+            from sparsetriton_b200.nn.functional.conv.funcs.implicit_precomputed_gemm import inverse_plan, map_plan
+
+            def popcount(t):
+                b = t.view(torch.uint8)
+                lut = torch.tensor([bin(i).count("1") for i in range(256)], dtype=torch.int64, device=b.device)
+                return int(lut[b.long()].sum().item())
+            fwd_plan, inv_plan = map_plan(nbr), inverse_plan(nbr, coords_d.shape[0])
+            self.steps_fwd.append(popcount(fwd_plan.tmask) if fwd_plan.tmask is not None else 0)
+            self.steps_inv.append(popcount(inv_plan.tmask) if inv_plan is not None else 0)
+            del sp, out, nbr, fwd_plan, inv_plan
             dy_h = torch.randn(n_out, COUT, generator=gen).to(dtype).pin_memory()
             self.host.append((coords_h, feats_h, dy_h))
             self.resident.append((coords_d, feats_d, dy_h.to(dev)))
@@ -279,7 +291,7 @@ def conv_bytes(kind, n_in, n_out, pairs, es):
     return compulsory, gathered
 
 
-def stage_rooflines(per_stage, n_in, n_out, pairs, pk, dtype):
+def stage_rooflines(per_stage, n_in, n_out, pairs, pk, dtype, steps_fwd=0, steps_inv=0):
     """Roofline entry of every stage of the pass.  Algorithmic bytes:
       out_coords        N_in*(16 + 12*c) + 16*N_out, c = 27/8 candidates per input of a k3 s2 layer
       map_scatter       N_out*(16 + 12 K) + 4 P   (the kernel-map figure for N_out rows; the scatter form executes less)
@@ -310,9 +322,17 @@ def stage_rooflines(per_stage, n_in, n_out, pairs, pk, dtype):
             # what these kernels are bound by in practice: rows pulled into shared memory per second.  A microbenchmark
             # on this pool's B200 (one 16 KB slot = 128 rows of 128 bytes per tile::gather4 burst, ring of slots,
             # 148 CTAs) tops out at 15.7 B/clk/SM = 4.4 TB/s for random rows out of DRAM
-            entry["gather_gbs"] = gathered / (ms * 1e-3) / 1e9
-            entry["gather_ceiling_gbs"] = GATHER_CEILING_GBS
-            entry["gather_frac"] = entry["gather_gbs"] / GATHER_CEILING_GBS
+            # Slots issued: one per (tile, offset) step of the plan the product walks and per 128-byte line of the
+            # gathered row (fwd and wgrad gather X rows over the forward plan, dgrad gathers dY rows over the inverse
+            # plan).  wgrad also loads a dY tile per (tile, offset group): not counted here.
+            steps = steps_inv if kind == "conv_dgrad" else steps_fwd
+            lines = -(-(COUT if kind == "conv_dgrad" else CIN) * es // 128)
+            if steps:
+                slot_bytes = steps * lines * 128 * 128
+                entry["gather_slot_bytes"] = slot_bytes
+                entry["gather_gbs"] = slot_bytes / (ms * 1e-3) / 1e9
+                entry["gather_ceiling_gbs"] = GATHER_CEILING_GBS
+                entry["gather_frac"] = entry["gather_gbs"] / GATHER_CEILING_GBS
         else:
             if kind == "out_coords":
                 nbytes = n_in * (16 + 12 * K / 8.0) + 16 * n_out
@@ -464,7 +484,8 @@ def run_ours(args):
         n_in, n_out, pairs = (statistics.mean(v) for v in (layer.n_in, layer.n_out, layer.pairs))
         per_stage = {k: {"ms_per_pass": v["ms"] / passes, "launches_per_pass": v["launches"] / passes}
                      for k, v in stages.items()}
-        roofs = stage_rooflines(per_stage, n_in, n_out, pairs, pk, dtype)
+        roofs = stage_rooflines(per_stage, n_in, n_out, pairs, pk, dtype, statistics.mean(layer.steps_fwd),
+                                statistics.mean(layer.steps_inv))
         top = max(roofs, key=lambda k: roofs[k]["ms"]) if roofs else None
         roof = None
         if top:

@@ -81,6 +81,10 @@ int st_set_tensor_cores(int enable);
  * the same plan.  Results are identical. */
 int st_set_tma(int enable);
 
+/* 1 (default): the planned weight gradient copies dY into tile order once and loads its tiles as dense boxes; 0: it
+ * gathers the rows of every tile through the row order (the earlier form, kept for comparison).  No reference counterpart. */
+int st_set_dense_tiles(int enable);
+
 /* ---------------------------------------------------------------- hash table ------------- */
 
 /* Fill keys and vals with -1.

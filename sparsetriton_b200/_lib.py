@@ -29,6 +29,7 @@ _SIGNATURES = {
     "st_last_error_string": ([], ctypes.c_char_p),
     "st_launch_count": ([], ctypes.c_longlong),
     "st_conv_uses_tensor_cores": ([_INT, _INT, _INT], _INT),
+    "st_set_dense_tiles": ([_INT], _INT),
     "st_device_status": ([_PTR, _PTR], _INT),
     "st_device_status_enqueue": ([_PTR, _PTR], _INT),
     "st_device_status_clear": ([_PTR], _INT),

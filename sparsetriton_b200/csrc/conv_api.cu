@@ -42,9 +42,14 @@ static int64_t wgrad_partial_bytes(int64_t n_out, int K, int cin, int cout) {
 }
 
 // Partials of whichever weight-gradient kernel would run, so one workspace serves both.
+// The tensor-core form also keeps a copy of dY in tile order behind its partials (see tc_conv_wgrad).
+static int64_t wgrad_sorted_offset(int dtype, int64_t n_out, int K, int cin, int cout) {
+  return align_up(tc_wgrad_partial_bytes(dtype, n_out, K, cin, cout), 256);
+}
 static int64_t wgrad_workspace_bytes(int dtype, int64_t n_out, int K, int cin, int cout) {
   int64_t simt = wgrad_partial_bytes(n_out, K, cin, cout);
-  int64_t tcb = align_up(tc_wgrad_partial_bytes(dtype, n_out, K, cin, cout), 256);
+  int64_t tcb = wgrad_sorted_offset(dtype, n_out, K, cin, cout);
+  if (tcb > 0) tcb += align_up(n_out * (int64_t)cout * (dtype == ST_F32 ? 4 : 2), 256);
   return simt > tcb ? simt : tcb;
 }
 
@@ -119,6 +124,11 @@ int st_set_tensor_cores(int enable) {
 
 int st_set_tma(int enable) {
   tc_set_tma(enable != 0);
+  return ST_OK;
+}
+
+int st_set_dense_tiles(int enable) {
+  tc_set_dense_tiles(enable != 0);
   return ST_OK;
 }
 
@@ -254,7 +264,9 @@ int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_
   cudaStream_t s = (cudaStream_t)stream;
   if (n_out > 0 && tc_wgrad_supported(dtype, n_out, K, cin, cout)) {
     int chunks = 0;
-    rc = tc_conv_wgrad(dtype, X, dY, nbr, MapPlan{row_order, tmap, tmask}, static_cast<float*>(workspace), &chunks, n_out, n_in, K, cin, cout, s);
+    void* sorted_rows = static_cast<char*>(workspace) + wgrad_sorted_offset(dtype, n_out, K, cin, cout);
+    rc = tc_conv_wgrad(dtype, X, dY, nbr, MapPlan{row_order, tmap, tmask}, static_cast<float*>(workspace), &chunks, n_out, n_in, K, cin, cout, s,
+                       /*inverse_plan=*/false, sorted_rows);
     if (rc != ST_OK) return rc;
     return reduce_partials(dtype, static_cast<const float*>(workspace), chunks, (int64_t)K * cin * cout, dW, s);
   }

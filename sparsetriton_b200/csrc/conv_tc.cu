@@ -806,6 +806,8 @@ struct WgradParams {
   int quad;              // planned_wgrad_kernel: offsets per shared-memory slot (b_slots counts such slots)
   int a_slots;           // planned_wgrad_kernel: depth of the tile-operand ring
   int swap;              // planned_wgrad_kernel: 1 = the plan is the INVERSE map's (tile operand X, gathered operand dY)
+  int dense_tiles;       // planned_wgrad_kernel: 1 = the tile operand's rows lie in tile order (a copy permuted by `order`,
+                         // or no `order` at all): a tile is one 2-D box per column block instead of 32 row gathers
   int tmem_cols;
   uint32_t idesc_base;   // everything but N
 };
@@ -1117,6 +1119,9 @@ void tc_set_enabled(bool on) { g_tc_enabled = on; }
 static bool g_tma_enabled = true;
 
 void tc_set_tma(bool on) { g_tma_enabled = on; }
+
+static bool g_dense_tiles = true;
+void tc_set_dense_tiles(bool on) { g_dense_tiles = on; }
 
 bool tc_supported(int dtype, int c_red, int c_acc) {
   if (!g_tc_enabled) return false;
@@ -1522,9 +1527,22 @@ static int launch_wgrad(WgradPlan& plan, const Map& map, cudaStream_t stream) {
   return check_launch("tc wgrad");
 }
 
+// dst[r] = src[order[r]] for rows of `vecs` 16-byte pieces: the tile operand of the weight gradient in the order
+// the kernel walks it, so that a tile of 128 rows is a dense box.
+__global__ void __launch_bounds__(256)
+permute_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ order, int64_t n_rows, int vecs,
+                    uint4* __restrict__ dst) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n_rows * vecs) return;
+  const int64_t r = i / vecs;
+  const int v = (int)(i - r * vecs);
+  dst[i] = __ldg(src + (int64_t)__ldg(order + r) * vecs + v);
+}
+
 // Tile-plan form: the TMA-fed kernel when both tensors can be described to the copy engine and two
-// slots fit, else the cp.async producers of wgrad_kernel over the same plan.
-static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cudaStream_t stream) {
+// slots fit, else the cp.async producers of wgrad_kernel over the same plan.  `sorted_rows`: scratch for a copy of
+// the tile operand in tile order (n_rows x cout elements), or null.
+static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cudaStream_t stream, void* sorted_rows) {
   tc::WgradParams& p = plan.p;
   if (p.swap) {
     // ring 1 holds X tiles (ci_blk wide), ring 2 the gathered dY rows (128 output channels wide)
@@ -1557,13 +1575,30 @@ static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cud
     budget += p.a_slot_bytes;
   }
   while (quad > 1 && budget < 2 * quad * p.b_slot_bytes) --quad;
-  CUtensorMap x_desc, dy_desc;
+  CUtensorMap x_desc, dy_desc, tile_box_desc;
   memset(&x_desc, 0, sizeof(x_desc));
   memset(&dy_desc, 0, sizeof(dy_desc));
+  memset(&tile_box_desc, 0, sizeof(tile_box_desc));
   const int dtype = p.esize == 4 ? ST_F32 : ST_BF16;      // element size is all the copy engine needs to know
   const bool tma = g_tma_enabled && budget >= 2 * quad * p.b_slot_bytes && p.n_src > 0 &&
                    make_gather_desc(&x_desc, p.x, p.swap ? p.n_rows : p.n_src, p.cin, p.esize, dtype, p.esize == 4) &&
                    make_gather_desc(&dy_desc, p.dy, p.swap ? p.n_src : p.n_rows, p.cout, p.esize, dtype, p.esize == 4);
+  // The dY tile of a step is 128 rows picked through `order`: 32 row gathers per 128-byte column block, and every
+  // offset group (and input-channel block) of a row chunk fetches it again.  With the rows copied into tile order once
+  // (one streaming pass) a tile is a dense box, which the copy engine moves 2.3x faster.
+  p.dense_tiles = 0;
+  if (tma && !p.swap && g_dense_tiles && (p.order == nullptr || sorted_rows != nullptr) && (p.cout * p.esize) % 16 == 0) {
+    const void* tiles = p.dy;
+    if (p.order) {
+      const int vecs = p.cout * p.esize / 16;
+      const int64_t total = p.n_rows * vecs;
+      permute_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+          static_cast<const uint4*>(p.dy), p.order, p.n_rows, vecs, static_cast<uint4*>(sorted_rows));
+      note_launches(1);
+      tiles = sorted_rows;
+    }
+    if (make_weight_desc(&tile_box_desc, tiles, p.n_rows, p.cout, p.esize, dtype, tc::kTileM, p.esize == 4)) p.dense_tiles = 1;
+  }
   if (!tma) {
     if (p.swap) {
       set_error("tc wgrad over the inverse plan needs the TMA kernels (16-byte aligned tensors, st_set_tma(1))");
@@ -1595,7 +1630,7 @@ static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cud
     configured[current_device()] = true;
   }
   dim3 grid((unsigned)plan.n_chunks, (unsigned)p.n_kgroups, (unsigned)(p.n_coblk * p.n_ciblk));
-  kernel<<<grid, tc::kThreads, smem, stream>>>(p, map, x_desc, dy_desc);
+  kernel<<<grid, tc::kThreads, smem, stream>>>(p, map, x_desc, dy_desc, tile_box_desc);
   note_launches(1);
   return check_launch("tc planned wgrad");
 }
@@ -1612,6 +1647,7 @@ static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void*
   plan->p.quad = 1;
   plan->p.a_slots = 2;
   plan->p.swap = 0;
+  plan->p.dense_tiles = 0;
   plan->p.partial = partial;
   plan->p.n_src = n_src;
   return true;
@@ -1619,7 +1655,7 @@ static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void*
 
 int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const MapPlan& rows, float* partial,
                   int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream,
-                  bool inverse_plan) {
+                  bool inverse_plan, void* sorted_rows) {
   WgradPlan plan;
   if (!prepare_wgrad(&plan, dtype, x, dy, partial, n_rows, n_src, K, cin, cout)) return ST_ERR_UNSUPPORTED;
   plan.p.order = rows.order;
@@ -1630,7 +1666,7 @@ int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, 
   }
   int rc;
   if (rows.tmap && rows.tmask)
-    rc = launch_wgrad_planned(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream);
+    rc = launch_wgrad_planned(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream, sorted_rows);
   else
     rc = launch_wgrad(plan, tc::StoredRows{map, K}, stream);
   *n_chunks_out = plan.n_chunks;

@@ -15,6 +15,7 @@ bool tc_supported(int dtype, int c_red, int c_acc);
 void tc_set_enabled(bool on);
 // Process-wide switch: when off, products over a tile plan run their cp.async forms instead of the TMA-fed ones.
 void tc_set_tma(bool on);
+void tc_set_dense_tiles(bool on);
 
 // OUT[r,:] = sum_k IN[map[r,k],:] . B_k over a stored (n_rows, K) map.
 //   w_transposed = false: B_k = W[k]   with W (K, c_red, c_acc)   (forward)
@@ -63,7 +64,7 @@ int64_t tc_wgrad_partial_bytes(int dtype, int64_t n_rows, int K, int cin, int co
 // n_src the rows of dy (the rows the plan's entries name).
 int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const MapPlan& plan, float* partial,
                   int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream,
-                  bool inverse_plan = false);
+                  bool inverse_plan = false, void* sorted_rows = nullptr);
 
 // Cycle counters of timing experiments (see Params2::dbg).
 int tc_read_prof(long long* host_out, int n);

@@ -384,7 +384,8 @@ struct __align__(8) WgradControl3 {
 template <int kAhead>
 __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradParams p, const PlannedRows map,
                                                                     const __grid_constant__ CUtensorMap x_desc,
-                                                                    const __grid_constant__ CUtensorMap dy_desc) {
+                                                                    const __grid_constant__ CUtensorMap dy_desc,
+                                                                    const __grid_constant__ CUtensorMap tile_box_desc) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -467,8 +468,26 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
         uint32_t m = m_next;
         if (tile + tile_step < tile_end) m_next = tile_mask(tile + tile_step);
         if (!m) continue;
-        // ---- the dY tile: rows order[tile * 128 + r]
-        {
+        // ---- the dY tile: rows order[tile * 128 + r], or one dense box when the rows lie in tile order
+        if (p.dense_tiles) {
+          ok = mbar_wait_warp(smem_u32(&ctl->a_empty[a_slot]), a_phase ^ 1u, abort_flag, 35, lane);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&ctl->a_full[a_slot]);
+          const uint32_t slot_base = a_ring + (uint32_t)a_slot * (uint32_t)p.a_slot_bytes;
+          if (lane == 0) {
+            int mine = 0;
+            for (int b = pw; b < a_blocks; b += kProducerWarps) ++mine;
+            if (mine) mbar_arrive_expect_tx(bar, (uint32_t)mine * kABlockBytes); else mbar_arrive(bar);
+            for (int b = pw; b < a_blocks; b += kProducerWarps)
+              tma_load_2d(slot_base + (uint32_t)b * kABlockBytes, &tile_box_desc, bar, tile_col0 + b * per_line,
+                          (int)(tile * kTileM));
+          }
+          __syncwarp();
+          if (++a_slot == p.a_slots) {
+            a_slot = 0;
+            a_phase ^= 1u;
+          }
+        } else {
           const int64_t pos = tile * kTileM + 4 * lane;
           int4 rows;
           if (p.order) {
@@ -634,11 +653,16 @@ __global__ void __launch_bounds__(kThreads, 1) planned_wgrad_kernel(const WgradP
         const uint32_t slot_base = a_ring + (uint32_t)t.slot * (uint32_t)p.a_slot_bytes;
         if (lane == 0) {
           if (a_mine) mbar_arrive_expect_tx(bar, (uint32_t)a_mine * kABlockBytes); else mbar_arrive(bar);
+          if (p.dense_tiles)
+            for (int b = pw; b < a_blocks; b += kProducerWarps)
+              tma_load_2d(slot_base + (uint32_t)b * kABlockBytes, &tile_box_desc, bar, tile_col0 + b * per_line,
+                          (int)(t.tile * kTileM));
         }
         __syncwarp();
-        for (int b = pw; b < a_blocks; b += kProducerWarps)
-          tma_gather4(slot_base + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, tile_desc, bar, tile_col0 + b * per_line,
-                      rows.x, rows.y, rows.z, rows.w);
+        if (!p.dense_tiles)
+          for (int b = pw; b < a_blocks; b += kProducerWarps)
+            tma_gather4(slot_base + (uint32_t)b * kABlockBytes + (uint32_t)lane * 512u, tile_desc, bar, tile_col0 + b * per_line,
+                        rows.x, rows.y, rows.z, rows.w);
       } else {
         ok = mbar_wait_warp(smem_u32(&ctl->b_empty[t.slot]), t.parity ^ 1u, abort_flag, 36, lane);
         if (!ok) return;

@@ -592,11 +592,15 @@ def unet_legs(args, dist, world, rank, dev):
     out = {}
     for key, train in (("unet_infer", False), ("unet_train", True)):
         try:
-            r = unet_measure(args, dist, world, rank, dev, train, steps=8, warmup=3, prune=True, e2e=False)
+            # ten warm-up steps: with the preparation on a second stream the caching allocator keeps growing its pools
+            # (cudaMalloc inside a step) for about that long; detail.device_allocs_in_timed_steps says what was left
+            r = unet_measure(args, dist, world, rank, dev, train, steps=8, warmup=10, prune=True, e2e=False)
             out[key + "_ms_per_step"] = r["ms_per_step"]
             out[key + "_detail"] = {"prune": True, "batch": r["total_batch"], "voxels": r["total_voxels"],
                                     "launches_per_step": r["launches"], "kernel_ms_per_step": r["kernel_ms"],
                                     "serial_ms_per_step": r["serial_ms_per_step"],
+                       "device_allocs_in_timed_steps": r["device_allocs_in_timed_steps"],
+                                    "device_allocs_in_timed_steps": r["device_allocs_in_timed_steps"],
                                     "conv_by_width": r["conv_by_width"],
                                     "pipelining": ("coordinate side of step i+1 (SparseUNet.prepare) on a second stream "
                                                    "beside step i" if r["pipelined"] else "none: one stream"),
@@ -964,7 +968,10 @@ def unet_measure(args, dist, world, rank, dev, train, steps, warmup, prune=True,
 
     for _ in range(warmup):
         run_step()
+    allocs_before = torch.cuda.memory_stats()["num_device_alloc"]
     dev_ms = _event_ms(dist, world, run_step, steps)
+    # cudaMalloc calls inside the timed steps (the caching allocator still growing): such a run is not steady state
+    device_allocs = torch.cuda.memory_stats()["num_device_alloc"] - allocs_before
     pending["next"] = None
     serial_ms = _event_ms(dist, world, lambda _i: step(coords_d, feats_d), steps) if pipelined else dev_ms
     # stage breakdown and launch count: one more step (one stream) with the stage recorder on, outside the timed steps
@@ -1009,6 +1016,7 @@ def unet_measure(args, dist, world, rank, dev, train, steps, warmup, prune=True,
     del model, opt, bucket
     return {"ms_per_step": vals[0] / steps, "e2e_ms_per_step": (vals[1] / steps) if e2e else None, "stages": stages,
             "serial_ms_per_step": vals[2] / steps, "pipelined": pipelined, "conv_by_width": widths,
+            "device_allocs_in_timed_steps": device_allocs,
             "launches": launches, "kernel_ms": sum(v["ms"] for v in stages.values()), "total_voxels": total_voxels,
             "total_batch": total_batch, "n_in": n_in, "n_out": state["n_out"], "local_samples": len(seeds),
             "h2d": coords_h.numel() * 4 + feats_h.numel() * feats_h.element_size()}
@@ -1023,8 +1031,8 @@ def run_unet(args, train):
     if args.unet_samples:
         base = 5000 if train else 4000
         samples = [base + rank * args.unet_samples + i for i in range(args.unet_samples)]
-    r = unet_measure(args, dist, world, rank, dev, train, args.steps, max(args.warmup, 3), prune=not args.literal_decoder,
-                     samples=samples)
+    r = unet_measure(args, dist, world, rank, dev, train, args.steps, max(args.warmup, 3 if args.no_pipeline else 10),
+                     prune=not args.literal_decoder, samples=samples)
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
         pk = peaks()
@@ -1044,7 +1052,8 @@ def run_unet(args, train):
         print(json.dumps({
             "metric": "sparse_unet_%s_voxels_per_s" % ("train_step" if train else "inference"),
             "value": r["total_voxels"] / (ms_step * 1e-3), "unit": "voxels/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "warmup": max(args.warmup, 3 if args.no_pipeline else 10), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong",
             "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
             "config": {"workload": "%s: lidar-like U-Net 4->32/64/128/256->...->32->20, grid 1440x1440x41, batch %d "
                                    "(%d samples on this rank, %d voxels)" % (args.workload, r["total_batch"], r["local_samples"],
@@ -1055,6 +1064,7 @@ def run_unet(args, train):
                        "pipelining": ("coordinate side of step i+1 (SparseUNet.prepare) on a second stream beside step i"
                                       if r["pipelined"] else "none: one stream"),
                        "serial_ms_per_step": r["serial_ms_per_step"],
+                       "device_allocs_in_timed_steps": r["device_allocs_in_timed_steps"],
                        "l2_policy": "activations of every level exceed L2"},
             "e2e": {"value": r["total_voxels"] / (r["e2e_ms_per_step"] * 1e-3), "unit": "voxels/s",
                     "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 4, "ms_per_step": r["e2e_ms_per_step"]},

@@ -1586,8 +1586,12 @@ static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cud
   // The dY tile of a step is 128 rows picked through `order`: 32 row gathers per 128-byte column block, and every
   // offset group (and input-channel block) of a row chunk fetches it again.  With the rows copied into tile order once
   // (one streaming pass) a tile is a dense box, which the copy engine moves 2.3x faster.
+  // The copy pass pays for itself when a tile is fetched by four CTAs or more (offset groups x channel blocks); with two
+  // groups (32 input channels: 16 offsets per group) it only adds its own cost.
   p.dense_tiles = 0;
-  if (tma && !p.swap && g_dense_tiles && (p.order == nullptr || sorted_rows != nullptr) && (p.cout * p.esize) % 16 == 0) {
+  const bool worth_a_copy = p.n_kgroups * p.n_ciblk * p.n_coblk >= 4;
+  if (tma && !p.swap && g_dense_tiles && (p.order == nullptr || (sorted_rows != nullptr && worth_a_copy)) &&
+      (p.cout * p.esize) % 16 == 0) {
     const void* tiles = p.dy;
     if (p.order) {
       const int vecs = p.cout * p.esize / 16;

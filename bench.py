@@ -399,7 +399,9 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    allocs_before = torch.cuda.memory_stats()["num_device_alloc"]
     dev_ms = _event_ms(dist, world, step, args.steps)
+    device_allocs = torch.cuda.memory_stats()["num_device_alloc"] - allocs_before      # cudaMalloc calls inside the timed steps
     serial_ms = _event_ms(dist, world, serial_step, args.steps) if pipelined else dev_ms
     same = layer.overlapped_equals_serial(side) if pipelined else None
     step = serial_step
@@ -520,6 +522,7 @@ def run_ours(args):
                                       if pipelined else "none: one stream"),
                        "serial_ms_per_pass": serial_ms / args.steps / passes,
                        "overlapped_results_equal_serial_bitwise": same,
+                       "device_allocs_in_timed_steps": device_allocs,
                        "n_in_per_pass": n_in, "n_out_per_pass": n_out, "pairs_per_pass": pairs,
                        "constructor": "SparseTensor._trusted (the library's internal constructor: no validation read of the "
                                       "coordinates; the public one adds one device->host read per tensor)",

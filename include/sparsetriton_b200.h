@@ -327,6 +327,13 @@ int st_to_dense_fwd(int dtype, const void* feats, const void* coords, int coord_
 int st_to_dense_bwd(int dtype, const void* grad_dense, const void* coords, int coord_dtype, int64_t n, int C, int batch,
                     const int32_t* shape_host, void* grad_feats, void* stream);
 
+/* out[r] = left[r] | right[r]: channel-wise concatenation of two (n, *) feature matrices whose rows are left_bytes and
+ * right_bytes long (multiples of 16, 16-byte aligned pointers; else ST_ERR_UNSUPPORTED), and its inverse, which hands
+ * the backward pass two contiguous gradients instead of two strided slices.  No reference counterpart (the reference's
+ * networks call torch.cat on the features of a skip connection). */
+int st_concat_cols(const void* left, const void* right, int64_t n, int left_bytes, int right_bytes, void* out, void* stream);
+int st_split_cols(const void* whole, int64_t n, int left_bytes, int right_bytes, void* left, void* right, void* stream);
+
 /* ---------------------------------------------------------------- pooling / upsampling --- */
 
 /* Pooling of a sparse tensor: input voxel `in` belongs to the output cell

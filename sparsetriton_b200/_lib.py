@@ -30,6 +30,8 @@ _SIGNATURES = {
     "st_launch_count": ([], ctypes.c_longlong),
     "st_conv_uses_tensor_cores": ([_INT, _INT, _INT], _INT),
     "st_set_dense_tiles": ([_INT], _INT),
+    "st_concat_cols": ([_PTR, _PTR, _I64, _INT, _INT, _PTR, _PTR], _INT),
+    "st_split_cols": ([_PTR, _I64, _INT, _INT, _PTR, _PTR, _PTR], _INT),
     "st_device_status": ([_PTR, _PTR], _INT),
     "st_device_status_enqueue": ([_PTR, _PTR], _INT),
     "st_device_status_clear": ([_PTR], _INT),

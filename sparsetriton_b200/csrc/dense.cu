@@ -93,6 +93,24 @@ int dense_args(const char* who, int dtype, const void* a, const void* coords, in
   return ST_OK;
 }
 
+// Channel-wise concatenation of two feature matrices and its inverse, in 16-byte pieces: whole[r] = left[r] | right[r].
+// The split hands an autograd graph two CONTIGUOUS gradients where slicing a concatenated gradient gives two strided
+// views that every consumer then has to copy.
+template <bool SPLIT>
+__global__ void __launch_bounds__(256)
+cols_kernel(uint4* __restrict__ whole, int64_t n, int pieces, int left_pieces, uint4* __restrict__ left,
+            uint4* __restrict__ right) {
+  const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (t >= n * pieces) return;
+  const int64_t row = t / pieces;
+  const int p = (int)(t - row * pieces);
+  uint4* part = p < left_pieces ? left + row * left_pieces + p : right + row * (pieces - left_pieces) + (p - left_pieces);
+  if (SPLIT)
+    *part = whole[t];
+  else
+    whole[t] = *part;
+}
+
 }  // namespace
 }  // namespace st
 
@@ -133,6 +151,45 @@ int st_to_dense_bwd(int dtype, const void* grad_dense, const void* coords, int c
   if (coord_dtype == ST_I32)
     return launch_move<int32_t, true>(coords, n, C * esize, esize, shape, grad_dense, grad_feats, nullptr, s);
   return launch_move<int16_t, true>(coords, n, C * esize, esize, shape, grad_dense, grad_feats, nullptr, s);
+}
+
+static int cols_args(const char* who, const void* whole, int64_t n, int left_bytes, int right_bytes, const void* left,
+                     const void* right) {
+  if (n < 0 || left_bytes < 0 || right_bytes < 0 || (n > 0 && left_bytes + right_bytes > 0 && !whole) ||
+      (n > 0 && left_bytes > 0 && !left) || (n > 0 && right_bytes > 0 && !right)) {
+    set_error("%s: bad arguments", who);
+    return ST_ERR_ARG;
+  }
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(whole) | reinterpret_cast<uintptr_t>(left) | reinterpret_cast<uintptr_t>(right);
+  if (left_bytes % 16 || right_bytes % 16 || (bits & 15)) {
+    set_error("%s: rows and pointers must be multiples of 16 bytes", who);
+    return ST_ERR_UNSUPPORTED;
+  }
+  return ST_OK;
+}
+
+int st_concat_cols(const void* left, const void* right, int64_t n, int left_bytes, int right_bytes, void* out, void* stream) {
+  int rc = cols_args("st_concat_cols", out, n, left_bytes, right_bytes, left, right);
+  if (rc != ST_OK) return rc;
+  const int pieces = (left_bytes + right_bytes) / 16;
+  if (n == 0 || pieces == 0) return ST_OK;
+  cols_kernel<false><<<(unsigned)((n * pieces + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      static_cast<uint4*>(out), n, pieces, left_bytes / 16, const_cast<uint4*>(static_cast<const uint4*>(left)),
+      const_cast<uint4*>(static_cast<const uint4*>(right)));
+  note_launches(1);
+  return check_launch("st_concat_cols");
+}
+
+int st_split_cols(const void* whole, int64_t n, int left_bytes, int right_bytes, void* left, void* right, void* stream) {
+  int rc = cols_args("st_split_cols", whole, n, left_bytes, right_bytes, left, right);
+  if (rc != ST_OK) return rc;
+  const int pieces = (left_bytes + right_bytes) / 16;
+  if (n == 0 || pieces == 0) return ST_OK;
+  cols_kernel<true><<<(unsigned)((n * pieces + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      const_cast<uint4*>(static_cast<const uint4*>(whole)), n, pieces, left_bytes / 16, static_cast<uint4*>(left),
+      static_cast<uint4*>(right));
+  note_launches(1);
+  return check_launch("st_split_cols");
 }
 
 }  // extern "C"

@@ -34,6 +34,7 @@ from sparsetriton_b200.nn.functional.conv.funcs.implicit_precomputed_gemm import
 from sparsetriton_b200.nn.functional.norm import _batch_info
 from sparsetriton_b200.nn.modules import ReLU, SparseBatchNorm, SparseConv3D, SparseConvTransposed3D, SparseLinear, SubMConv3D
 from sparsetriton_b200.tensor import SparseTensor, TensorCache
+from sparsetriton_b200.utils.concat import concat_features
 from sparsetriton_b200.utils.hash import HashTable, round_up_capacity
 
 __all__ = ["SparseUNet", "skip_concat", "up_conv_onto"]
@@ -161,7 +162,7 @@ class SparseUNet(nn.Module):
             skip = skips[len(skips) - 2 - j]
             if self.prune:
                 x = up_conv_onto(x, up, skip)
-                x = x.replace(torch.cat([x.F, skip.F], dim=1))
+                x = x.replace(concat_features(x.F, skip.F))
             else:
                 x = skip_concat(up(x), skip)
             x = block(x)

@@ -175,3 +175,22 @@ def test_upsample_reference_known_answer(cuda_device):
         assert out.F.shape[0] == scale ** 3 and torch.allclose(out.F, feats.repeat(scale ** 3, 1))
         want = [[0, x, y, z] for x in range(scale) for y in range(scale) for z in range(scale)]
         assert out.C.tolist() == want and tuple(out.spatial_shape) == (10 * scale,) * 3
+
+
+@pytest.mark.parametrize("dtype,a,b", [(torch.bfloat16, 32, 32), (torch.float32, 4, 12), (torch.float16, 64, 8), (torch.float32, 3, 5)])
+def test_concat_features_and_its_gradients(cuda_device, dtype, a, b):
+    """concat_features = torch.cat along the channels, forward and backward, bit for bit (copies only); widths that are
+    not whole 16-byte pieces take torch.cat itself."""
+    from sparsetriton_b200.utils.concat import concat_features
+    gen = torch.Generator().manual_seed(3)
+    left = torch.randn(1003, a, generator=gen).to(dtype).to(cuda_device).requires_grad_(True)
+    right = torch.randn(1003, b, generator=gen).to(dtype).to(cuda_device).requires_grad_(True)
+    out = concat_features(left, right)
+    want = torch.cat([left.detach(), right.detach()], dim=1)
+    assert torch.equal(out, want)
+    g = torch.randn(1003, a + b, generator=gen).to(dtype).to(cuda_device)
+    out.backward(g)
+    assert left.grad.is_contiguous() and right.grad.is_contiguous()
+    assert torch.equal(left.grad, g[:, :a]) and torch.equal(right.grad, g[:, a:])
+    empty = concat_features(left[:0].detach(), right[:0].detach())
+    assert empty.shape == (0, a + b)

@@ -359,7 +359,8 @@ def stage_rooflines(per_stage, n_in, n_out, pairs, pk, dtype, steps_fwd=0, steps
 NCU_TRAFFIC_C3 = {
     "conv_fwd": (466.4e6 + 187.8e6, "profiles/planned_gather_kernel_c3.md"),
     "conv_dgrad": (820.9e6 + 143.0e6, "profiles/planned_gather_kernel_c3.md"),
-    "conv_wgrad": (899.5e6 + 43.6e6, "profiles/planned_wgrad_kernel_c3.md"),
+    # the stage's three kernels: the copy of dY into tile order, the product, the sum of the partials
+    "conv_wgrad": ((216.9e6 + 169.8e6) + (976.2e6 + 46.5e6) + (65.5e6 + 0.2e6), "profiles/planned_wgrad_kernel_c3.md"),
 }
 
 

@@ -152,3 +152,51 @@ def test_module_surface_and_compat_alias():
     from sparsetriton.nn.functional.conv.funcs import ConvHashOnTheFlyImplicitGEMM  # noqa: F401
     from sparsetriton.nn.functional.conv.funcs.implicit_precomputed_gemm import ConvPrecomputedNeighborGEMM  # noqa: F401
     assert Aliased is st.SparseTensor
+
+
+def test_preparation_surface_needs_cuda_and_caches_children():
+    """ConvPreparation / prepare_conv3d refuse CPU coordinates (no CPU path), and a TensorCache hands out one child
+    cache per layer geometry."""
+    from sparsetriton_b200.nn.functional import ConvPreparation, prepare_conv3d
+    from sparsetriton_b200.tensor import TensorCache
+    coords = torch.zeros((4, 4), dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ConvPreparation(coords, (8, 8, 8), 3, stride=2, padding=1, submanifold=False)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        prepare_conv3d(coords, (8, 8, 8), 3)
+    with pytest.raises(AssertionError, match="transposed"):
+        ConvPreparation(coords, (8, 8, 8), 3, transposed=True, submanifold=True)
+    cache = TensorCache()
+    key = (2, 2, 0, 1, False, False)
+    child = cache.child(key)
+    assert cache.child(key) is child and cache.child((3, 2, 1, 1, False, False)) is not child
+    assert child.neighbor_indices == {} and child.hashtable is None and child.children == {}
+
+
+def test_tall_linear_gradients_on_the_host():
+    """The split weight gradient of SparseLinear's tall form equals torch's on the same numbers (the Function itself is
+    device-agnostic; the module only routes CUDA inputs of 65 536 rows or more through it)."""
+    import sparsetriton_b200.nn.modules.simple as simple
+    torch.manual_seed(0)
+    lin = simple.SparseLinear(7, 5).double()
+    ref = torch.nn.Linear(7, 5).double()
+    ref.load_state_dict(lin.state_dict())
+    n = 2 * simple._SPLIT_ROWS + 333                      # two whole pieces and a remainder
+    x = torch.randn(n, 7, dtype=torch.float64, requires_grad=True)
+    x2 = x.detach().clone().requires_grad_(True)
+    y, y2 = simple._TallLinear.apply(x, lin.weight, lin.bias), ref(x2)
+    g = torch.randn_like(y)
+    y.backward(g)
+    y2.backward(g)
+    assert torch.allclose(y, y2) and torch.allclose(x.grad, x2.grad)
+    assert torch.allclose(lin.weight.grad, ref.weight.grad) and torch.allclose(lin.bias.grad, ref.bias.grad)
+    # a CPU input takes nn.Linear's own path
+    assert torch.equal(lin(x.detach()), ref(x.detach()))
+
+
+def test_concat_features_is_torch_cat_for_host_tensors():
+    """The reference's networks call torch.cat here; the library's copy kernels only take over for CUDA matrices whose rows
+    are whole 16-byte pieces."""
+    from sparsetriton_b200.utils.concat import concat_features
+    a, b = torch.randn(5, 8), torch.randn(5, 4)
+    assert torch.equal(concat_features(a, b), torch.cat([a, b], dim=1))

@@ -37,9 +37,15 @@ bool pack_offsets(const int32_t* host, int K, Offsets* out) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Exclusive scan: 1024 values per block, block sums scanned recursively (three levels cover 2^30).
+// Exclusive scan.  Up to 16.7 M values take two launches: the sum of every span of 4096 values, then
+// each block adds up the sums of the spans before its own (at most 4096 of them, L2-resident) and
+// scans its span; the last block also writes the grand total.  Longer inputs go through 1024 values
+// per block with the block sums scanned recursively (three levels cover 2^30).
 // ---------------------------------------------------------------------------------------------
 constexpr int kScanBlock = 1024;
+constexpr int kScanPer = 4;                              // consecutive values per thread in the two-launch form
+constexpr int kScanSpan = kScanBlock * kScanPer;
+constexpr int64_t kScanDirectSpans = 4096;
 
 __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* block_total) {
   __shared__ uint32_t warp_sums[32];
@@ -83,6 +89,55 @@ scan_add_kernel(uint32_t* out, int64_t n, const uint32_t* block_offsets) {
   if (i < n) out[i] += block_offsets[blockIdx.x];
 }
 
+__device__ __forceinline__ uint32_t block_sum(uint32_t v) {
+  __shared__ uint32_t warp_part[32];
+  __shared__ uint32_t result;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = __reduce_add_sync(0xFFFFFFFFu, v);
+  if (lane == 0) warp_part[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    const uint32_t w = __reduce_add_sync(0xFFFFFFFFu, warp_part[lane]);
+    if (lane == 0) result = w;
+  }
+  __syncthreads();
+  return result;
+}
+
+__global__ void __launch_bounds__(kScanBlock) scan_span_sums_kernel(const uint32_t* in, int64_t n, uint32_t* sums) {
+  const int64_t first = (int64_t)blockIdx.x * kScanSpan + (int64_t)threadIdx.x * kScanPer;
+  uint32_t mine = 0;
+#pragma unroll
+  for (int j = 0; j < kScanPer; ++j)
+    if (first + j < n) mine += in[first + j];
+  const uint32_t all = block_sum(mine);
+  if (threadIdx.x == 0) sums[blockIdx.x] = all;
+}
+
+// `in` may alias `out`: a block reads only its own span before it writes it
+__global__ void __launch_bounds__(kScanBlock)
+scan_spans_kernel(const uint32_t* in, uint32_t* out, int64_t n, const uint32_t* sums, int64_t* total) {
+  __shared__ uint32_t span_total;
+  uint32_t before = 0;
+  for (int i = threadIdx.x; i < (int)blockIdx.x; i += kScanBlock) before += sums[i];
+  const uint32_t base = blockIdx.x > 0 ? block_sum(before) : 0u;
+  const int64_t first = (int64_t)blockIdx.x * kScanSpan + (int64_t)threadIdx.x * kScanPer;
+  uint32_t v[kScanPer];
+  uint32_t mine = 0;
+#pragma unroll
+  for (int j = 0; j < kScanPer; ++j) {
+    v[j] = first + j < n ? in[first + j] : 0u;
+    mine += v[j];
+  }
+  uint32_t run = base + block_exclusive_scan(mine, &span_total);
+#pragma unroll
+  for (int j = 0; j < kScanPer; ++j) {
+    if (first + j < n) out[first + j] = run;
+    run += v[j];
+  }
+  if (total && blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) *total = (int64_t)base + (int64_t)span_total;
+}
+
 __global__ void scan_total_kernel(const uint32_t* last_in, const uint32_t* last_out, int64_t* total) {
   *total = (int64_t)(*last_in) + (int64_t)(*last_out);
 }
@@ -101,6 +156,15 @@ int exclusive_scan_u32(const uint32_t* in, uint32_t* out, int64_t n, void* tmp, 
   if (n <= 0) {
     if (total) { scan_zero_total_kernel<<<1, 1, 0, stream>>>(total); note_launches(1); }
     return check_launch("scan(empty)");
+  }
+  const int64_t spans = (n + kScanSpan - 1) / kScanSpan;
+  if (spans <= kScanDirectSpans) {
+    // the span sums live where the recursive form keeps its level-1 block sums (that array is four times as long)
+    uint32_t* sums = reinterpret_cast<uint32_t*>(static_cast<char*>(tmp) + align_up(4, 256));
+    if (spans > 1) { scan_span_sums_kernel<<<(unsigned)spans, kScanBlock, 0, stream>>>(in, n, sums); note_launches(1); }
+    scan_spans_kernel<<<(unsigned)spans, kScanBlock, 0, stream>>>(in, out, n, sums, total);
+    note_launches(1);
+    return check_launch("scan");
   }
   const int64_t b1 = (n + kScanBlock - 1) / kScanBlock;
   const int64_t b2 = (b1 + kScanBlock - 1) / kScanBlock;

@@ -1528,15 +1528,33 @@ static int launch_wgrad(WgradPlan& plan, const Map& map, cudaStream_t stream) {
 }
 
 // dst[r] = src[order[r]] for rows of `vecs` 16-byte pieces: the tile operand of the weight gradient in the order
-// the kernel walks it, so that a tile of 128 rows is a dense box.
+// the kernel walks it, so that a tile of 128 rows is a dense box.  Eight pieces per thread, the eight row
+// numbers loaded before the eight pieces, so that a thread keeps 128 bytes in flight.
+constexpr int kPermutePer = 8;
+
+template <typename IndexT>
 __global__ void __launch_bounds__(256)
 permute_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ order, int64_t n_rows, int vecs,
                     uint4* __restrict__ dst) {
-  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (i >= n_rows * vecs) return;
-  const int64_t r = i / vecs;
-  const int v = (int)(i - r * vecs);
-  dst[i] = __ldg(src + (int64_t)__ldg(order + r) * vecs + v);
+  const IndexT total = (IndexT)(n_rows * vecs);
+  const IndexT first = (IndexT)blockIdx.x * (256 * kPermutePer) + threadIdx.x;
+  int64_t from[kPermutePer];
+#pragma unroll
+  for (int j = 0; j < kPermutePer; ++j) {
+    const IndexT i = first + (IndexT)j * 256;
+    from[j] = -1;
+    if (i < total) {
+      const IndexT r = i / (IndexT)vecs;
+      from[j] = (int64_t)__ldg(order + r) * vecs + (int64_t)(i - r * (IndexT)vecs);
+    }
+  }
+  uint4 piece[kPermutePer];
+#pragma unroll
+  for (int j = 0; j < kPermutePer; ++j)
+    if (from[j] >= 0) piece[j] = __ldg(src + from[j]);
+#pragma unroll
+  for (int j = 0; j < kPermutePer; ++j)
+    if (from[j] >= 0) dst[first + (IndexT)j * 256] = piece[j];
 }
 
 // Tile-plan form: the TMA-fed kernel when both tensors can be described to the copy engine and two
@@ -1596,8 +1614,13 @@ static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cud
     if (p.order) {
       const int vecs = p.cout * p.esize / 16;
       const int64_t total = p.n_rows * vecs;
-      permute_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-          static_cast<const uint4*>(p.dy), p.order, p.n_rows, vecs, static_cast<uint4*>(sorted_rows));
+      const unsigned blocks = (unsigned)((total + 256 * kPermutePer - 1) / (256 * kPermutePer));
+      if (total + 256 * kPermutePer < 0xFFFFFFFFll)
+        permute_rows_kernel<uint32_t><<<blocks, 256, 0, stream>>>(
+            static_cast<const uint4*>(p.dy), p.order, p.n_rows, vecs, static_cast<uint4*>(sorted_rows));
+      else
+        permute_rows_kernel<int64_t><<<blocks, 256, 0, stream>>>(
+            static_cast<const uint4*>(p.dy), p.order, p.n_rows, vecs, static_cast<uint4*>(sorted_rows));
       note_launches(1);
       tiles = sorted_rows;
     }

@@ -8,9 +8,8 @@
 // those are denser.  The order only decides which rows share a tile; every row's own sum still
 // runs over the offsets in ascending k, so forward and feature-gradient results do not depend on it.
 //
-// order = stable LSD radix sort of the rows by mask (9-bit digits).  Each warp owns a contiguous
-// chunk of the sequence and ranks its elements 32 at a time with match.any, which keeps equal digits
-// in their original order: the result is deterministic (no atomics between warps).
+// order = stable LSD radix sort of the rows by mask (9-bit digits); equal masks keep their original
+// order and no atomic decides a position, so the result is deterministic.
 #include "common.cuh"
 #include "radix_sort.cuh"
 
@@ -53,9 +52,9 @@ __global__ void __launch_bounds__(128) row_keys_kernel(const int32_t* __restrict
 // offsets that have a neighbour anywhere in the tile.
 //   tmap [(tile * K + k) * 128 + r] = nbr[order[tile * 128 + r], k]      (-1 past the last row)
 //   tmask[tile * MW + k / 32] bit (k % 32)                                 MW = ceil(K / 32)
-// One block per tile.  The tile's rows are read as runs of consecutive entries (a warp-wide load
-// touches 2-3 lines, not 32) into shared memory, `kPlanChunk` offsets at a time, and written back
-// transposed.
+// One block per tile.  A warp reads one row at a time as a run of consecutive entries (a warp-wide
+// load touches one or two lines, not 32) into shared memory, `kPlanChunk` offsets at a time, with the
+// loads of eight rows in flight together; the block writes them back transposed.
 constexpr int kPlanChunk = 64;
 
 __global__ void __launch_bounds__(128) plan_tiles_kernel(const int32_t* __restrict__ nbr,
@@ -74,10 +73,15 @@ __global__ void __launch_bounds__(128) plan_tiles_kernel(const int32_t* __restri
     const int pitch = kc | 1;                              // odd: conflict-free column reads
     if (r < 2) mask_word[r] = 0;
     __syncthreads();
-    for (int e = r; e < 128 * kc; e += 128) {
-      const int row = e / kc, k = e - row * kc;
+    // a warp per row: lane l fetches entries l and l + 32 of the chunk, eight rows' loads issued together
+#pragma unroll 8
+    for (int row = warp; row < 128; row += 4) {
       const int64_t src = src_row[row];
-      stage[row * pitch + k] = src >= 0 ? __ldg(nbr + src * K + k0 + k) : -1;
+      const int32_t* from = nbr + src * K + k0;
+      const int32_t lo = (src >= 0 && lane < kc) ? __ldg(from + lane) : -1;
+      const int32_t hi = (src >= 0 && lane + 32 < kc) ? __ldg(from + lane + 32) : -1;
+      if (lane < kc) stage[row * pitch + lane] = lo;
+      if (lane + 32 < kc) stage[row * pitch + lane + 32] = hi;
     }
     __syncthreads();
     for (int k = 0; k < kc; ++k) {
@@ -90,18 +94,15 @@ __global__ void __launch_bounds__(128) plan_tiles_kernel(const int32_t* __restri
     if (r < (kc + 31) / 32) tmask[tile * MW + (k0 >> 5) + r] = mask_word[r];
     __syncthreads();
   }
-  (void)warp;
 }
 
 struct OrderScratch {
   uint32_t *keys_a, *keys_b, *hist, *totals;
   int32_t* vals_b;
-  int64_t n_chunks;
 };
 
 int64_t carve(OrderScratch* s, void* ws, int64_t n, int K) {
   (void)K;
-  const int64_t n_chunks = n > 0 ? (n + kSortChunk - 1) / kSortChunk : 1;
   int64_t off = 0;
   auto take = [&](int64_t bytes) {
     char* p = ws ? static_cast<char*>(ws) + off : nullptr;
@@ -112,9 +113,8 @@ int64_t carve(OrderScratch* s, void* ws, int64_t n, int K) {
   s->keys_a = reinterpret_cast<uint32_t*>(take(nn * 4));
   s->keys_b = reinterpret_cast<uint32_t*>(take(nn * 4));
   s->vals_b = reinterpret_cast<int32_t*>(take(nn * 4));
-  s->hist = reinterpret_cast<uint32_t*>(take(n_chunks * kBucketsMax * 4));
+  s->hist = reinterpret_cast<uint32_t*>(take(sort_hist_bytes(nn)));
   s->totals = reinterpret_cast<uint32_t*>(take(kBucketsMax * 4));
-  s->n_chunks = n_chunks;
   return off;
 }
 
@@ -142,23 +142,40 @@ __global__ void __launch_bounds__(256) iota_clear_kernel(uint32_t* keys, int32_t
 }
 
 // keys[i] |= 1 << k for every nbr[o,k] = i: the occupancy mask of row i of the inverse map.
-// Four consecutive entries per thread (one 16-byte load, one division).
+// kFlatQuads runs of four consecutive entries per thread (16-byte loads, all issued before they are used).
+constexpr int kFlatQuads = 4;
+constexpr int kFlatPerBlock = 256 * 4 * kFlatQuads;
+
+__device__ __forceinline__ void load_quads(const int32_t* __restrict__ nbr, int64_t n_flat, int64_t block_first,
+                                           int32_t (&v)[kFlatQuads][4]) {
+  const bool aligned = (reinterpret_cast<uintptr_t>(nbr) & 15) == 0;
+#pragma unroll
+  for (int q = 0; q < kFlatQuads; ++q) {
+    const int64_t t0 = block_first + ((int64_t)q * 256 + threadIdx.x) * 4;
+    v[q][0] = v[q][1] = v[q][2] = v[q][3] = -1;
+    if (t0 + 3 < n_flat && aligned) {
+      const int4 w = __ldg(reinterpret_cast<const int4*>(nbr + t0));
+      v[q][0] = w.x; v[q][1] = w.y; v[q][2] = w.z; v[q][3] = w.w;
+    } else {
+      for (int j = 0; j < 4 && t0 + j < n_flat; ++j) v[q][j] = __ldg(nbr + t0 + j);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 inverse_keys_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int64_t n_in, uint32_t* keys) {
-  const int64_t t0 = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
-  if (t0 >= n_flat) return;
-  int32_t v[4] = {-1, -1, -1, -1};
-  if (t0 + 3 < n_flat && (reinterpret_cast<uintptr_t>(nbr) & 15) == 0) {
-    const int4 q = __ldg(reinterpret_cast<const int4*>(nbr + t0));
-    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
-  } else {
-    for (int j = 0; j < 4 && t0 + j < n_flat; ++j) v[j] = __ldg(nbr + t0 + j);
-  }
-  int k = (int)(t0 % K);
+  const int64_t block_first = (int64_t)blockIdx.x * kFlatPerBlock;
+  int32_t v[kFlatQuads][4];
+  load_quads(nbr, n_flat, block_first, v);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    if (v[j] >= 0 && v[j] < n_in) atomicOr(keys + v[j], 1u << k);
-    if (++k == K) k = 0;
+  for (int q = 0; q < kFlatQuads; ++q) {
+    const int64_t t0 = block_first + ((int64_t)q * 256 + threadIdx.x) * 4;
+    int k = (int)(t0 % K);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (v[q][j] >= 0 && v[q][j] < n_in) atomicOr(keys + v[q][j], 1u << k);
+      if (++k == K) k = 0;
+    }
   }
 }
 
@@ -182,26 +199,26 @@ __global__ void __launch_bounds__(128) tile_mask_kernel(const uint32_t* __restri
 __global__ void __launch_bounds__(256)
 inverse_plan_scatter_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int64_t n_in,
                             const int32_t* __restrict__ rank, int32_t* __restrict__ tmap) {
-  const int64_t t0 = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;          // four entries per thread
-  if (t0 >= n_flat) return;
-  int32_t v[4] = {-1, -1, -1, -1};
-  if (t0 + 3 < n_flat && (reinterpret_cast<uintptr_t>(nbr) & 15) == 0) {
-    const int4 q = __ldg(reinterpret_cast<const int4*>(nbr + t0));
-    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
-  } else {
-    for (int j = 0; j < 4 && t0 + j < n_flat; ++j) v[j] = __ldg(nbr + t0 + j);
-  }
-  int64_t o = t0 / K;
-  int k = (int)(t0 - o * K);
+  const int64_t block_first = (int64_t)blockIdx.x * kFlatPerBlock;
+  int32_t v[kFlatQuads][4];
+  load_quads(nbr, n_flat, block_first, v);
+  int32_t pos[kFlatQuads][4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    if (v[j] >= 0 && v[j] < n_in) {
-      const int64_t pos = __ldg(rank + v[j]);
-      tmap[((pos >> 7) * K + k) * 128 + (pos & 127)] = (int32_t)o;
-    }
-    if (++k == K) {
-      k = 0;
-      ++o;
+  for (int q = 0; q < kFlatQuads; ++q)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pos[q][j] = (v[q][j] >= 0 && v[q][j] < n_in) ? __ldg(rank + v[q][j]) : -1;
+#pragma unroll
+  for (int q = 0; q < kFlatQuads; ++q) {
+    const int64_t t0 = block_first + ((int64_t)q * 256 + threadIdx.x) * 4;
+    int64_t o = t0 / K;
+    int k = (int)(t0 - o * K);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (pos[q][j] >= 0) tmap[((int64_t)(pos[q][j] >> 7) * K + k) * 128 + (pos[q][j] & 127)] = (int32_t)o;
+      if (++k == K) {
+        k = 0;
+        ++o;
+      }
     }
   }
 }
@@ -268,7 +285,7 @@ int st_map_plan_inverse(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, 
   const unsigned rows_grid = (unsigned)((n_in + 255) / 256);
   iota_clear_kernel<<<rows_grid, 256, 0, st>>>(s.keys_a, first_vals(s, K, order), n_in);
   if (n_flat > 0)
-    inverse_keys_kernel<<<(unsigned)((n_flat / 4 + 256) / 256), 256, 0, st>>>(nbr, n_flat, K, n_in, s.keys_a);
+    inverse_keys_kernel<<<(unsigned)((n_flat + kFlatPerBlock - 1) / kFlatPerBlock), 256, 0, st>>>(nbr, n_flat, K, n_in, s.keys_a);
   note_launches(2);
   uint32_t* sorted_keys = nullptr;
   sort_passes(s, n_in, K, order, &sorted_keys, st);
@@ -276,7 +293,7 @@ int st_map_plan_inverse(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, 
   tile_mask_kernel<<<(unsigned)n_tiles, 128, 0, st>>>(sorted_keys, n_in, tmask);
   cudaMemsetAsync(tmap, 0xFF, (size_t)n_tmap * sizeof(int32_t), st);                  // every entry -1
   if (n_flat > 0)
-    inverse_plan_scatter_kernel<<<(unsigned)((n_flat / 4 + 256) / 256), 256, 0, st>>>(nbr, n_flat, K, n_in, rank, tmap);
+    inverse_plan_scatter_kernel<<<(unsigned)((n_flat + kFlatPerBlock - 1) / kFlatPerBlock), 256, 0, st>>>(nbr, n_flat, K, n_in, rank, tmap);
   note_launches(3);
   return check_launch("st_map_plan_inverse");
 }

@@ -245,6 +245,22 @@ int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_
                           const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K,
                           int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* st_conv_wgrad_planned in two calls, for a caller that runs the first on another stream beside the feature gradient.
+ * On tensor-core shapes st_conv_wgrad_planned first copies dY into the plan's row order (scratch in its workspace), so
+ * that the product loads each dY tile as one dense box; the copy depends on dY and row_order alone.
+ *   st_conv_wgrad_presort            makes that copy in `workspace`.  ST_ERR_UNSUPPORTED (nothing launched, no error
+ *                                    text) when st_conv_wgrad_planned would make none for this layer: call
+ *                                    st_conv_wgrad_planned as usual then.
+ *   st_conv_wgrad_planned_presorted  the rest, with the same arguments and the same workspace, once the copy is
+ *                                    complete on `stream` (an event of the caller's).  Same dW, bit for bit, as
+ *                                    st_conv_wgrad_planned.
+ * No counterpart in the reference. */
+int st_conv_wgrad_presort(int dtype, const void* dY, const int32_t* row_order, int64_t n_out, int K, int cin, int cout,
+                          void* workspace, int64_t workspace_bytes, void* stream);
+int st_conv_wgrad_planned_presorted(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
+                                    const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out,
+                                    int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* The weight gradient walked over the plan of the INVERSE map (from st_map_plan_inverse, or st_map_plan of an
  * inverted map): tiles of 128 INPUT rows, X the per-tile operand, the dY rows of each offset gathered.  Same dW
  * as st_conv_wgrad_planned up to the order of the fp32 additions.  Worth it when the inverse map's rows have the

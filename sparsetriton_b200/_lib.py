@@ -58,8 +58,9 @@ _SIGNATURES = {
     "st_conv_wgrad": ([_INT, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT),
 }
 _PLANNED_SIG = ([_INT, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _PTR, _I64, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT)
-for _n in ("st_conv_fwd_planned", "st_conv_dgrad_planned", "st_conv_wgrad_planned"):
+for _n in ("st_conv_fwd_planned", "st_conv_dgrad_planned", "st_conv_wgrad_planned", "st_conv_wgrad_planned_presorted"):
     _SIGNATURES[_n] = _PLANNED_SIG
+_SIGNATURES["st_conv_wgrad_presort"] = ([_INT, _PTR, _PTR, _I64, _INT, _INT, _INT, _PTR, _I64, _PTR], _INT)
 _SIGNATURES["st_map_plan_workspace_bytes"] = ([_I64, _INT], _I64)
 _SIGNATURES["st_map_plan_inverse_workspace_bytes"] = ([_I64, _INT], _I64)
 _SIGNATURES["st_map_plan_inverse"] = ([_PTR, _I64, _INT, _I64, _PTR, _PTR, _PTR, _PTR, _I64, _PTR], _INT)

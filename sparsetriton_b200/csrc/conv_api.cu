@@ -247,9 +247,9 @@ int st_conv_dgrad_mirrored(int dtype, const void* dY, const void* W, const int32
                         (cudaStream_t)stream, /*w_flip=*/true);
 }
 
-int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
-                          const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K, int cin, int cout, void* workspace,
-                          int64_t workspace_bytes, void* stream) {
+static int wgrad_planned(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
+                         const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K, int cin,
+                         int cout, void* workspace, int64_t workspace_bytes, void* stream, bool presorted) {
   int rc = check_conv_args("st_conv_wgrad", dtype, n_in, n_out, K, cin, cout);
   if (rc != ST_OK) return rc;
   if (!dW || (n_out > 0 && (!X || !dY || !nbr))) {
@@ -266,7 +266,7 @@ int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_
     int chunks = 0;
     void* sorted_rows = static_cast<char*>(workspace) + wgrad_sorted_offset(dtype, n_out, K, cin, cout);
     rc = tc_conv_wgrad(dtype, X, dY, nbr, MapPlan{row_order, tmap, tmask}, static_cast<float*>(workspace), &chunks, n_out, n_in, K, cin, cout, s,
-                       /*inverse_plan=*/false, sorted_rows);
+                       /*inverse_plan=*/false, sorted_rows, presorted);
     if (rc != ST_OK) return rc;
     return reduce_partials(dtype, static_cast<const float*>(workspace), chunks, (int64_t)K * cin * cout, dW, s);
   }
@@ -276,6 +276,36 @@ int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_
     return simt_wgrad<T, StoredMap>(static_cast<const T*>(X), static_cast<const T*>(dY), map, static_cast<T*>(dW),
                                     static_cast<float*>(workspace), n_out, n_in, K, cin, cout, s);
   });
+}
+
+int st_conv_wgrad_planned(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
+                          const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out, int K, int cin,
+                          int cout, void* workspace, int64_t workspace_bytes, void* stream) {
+  return wgrad_planned(dtype, X, dY, nbr, row_order, tmap, tmask, dW, n_in, n_out, K, cin, cout, workspace, workspace_bytes,
+                       stream, /*presorted=*/false);
+}
+
+int st_conv_wgrad_presort(int dtype, const void* dY, const int32_t* row_order, int64_t n_out, int K, int cin, int cout,
+                          void* workspace, int64_t workspace_bytes, void* stream) {
+  int rc = check_conv_args("st_conv_wgrad_presort", dtype, n_out, n_out, K, cin, cout);
+  if (rc != ST_OK) return rc;
+  if (n_out == 0 || !row_order || !tc_wgrad_supported(dtype, n_out, K, cin, cout) ||
+      !tc_wgrad_sorts_rows(dtype, n_out, K, cin, cout))
+    return ST_ERR_UNSUPPORTED;                              // st_conv_wgrad_planned makes no copy for this layer
+  if (!dY || !workspace || workspace_bytes < wgrad_workspace_bytes(dtype, n_out, K, cin, cout) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255)) {
+    set_error("st_conv_wgrad_presort: null dY, or workspace too small or misaligned");
+    return ST_ERR_WORKSPACE;
+  }
+  void* sorted_rows = static_cast<char*>(workspace) + wgrad_sorted_offset(dtype, n_out, K, cin, cout);
+  return tc_wgrad_sort_rows(dtype, dY, row_order, n_out, cout, sorted_rows, (cudaStream_t)stream);
+}
+
+int st_conv_wgrad_planned_presorted(int dtype, const void* X, const void* dY, const int32_t* nbr, const int32_t* row_order,
+                                    const int32_t* tmap, const uint32_t* tmask, void* dW, int64_t n_in, int64_t n_out,
+                                    int K, int cin, int cout, void* workspace, int64_t workspace_bytes, void* stream) {
+  return wgrad_planned(dtype, X, dY, nbr, row_order, tmap, tmask, dW, n_in, n_out, K, cin, cout, workspace, workspace_bytes,
+                       stream, /*presorted=*/true);
 }
 
 int64_t st_conv_wgrad_inverse_workspace_bytes(int dtype, int64_t n_in, int K, int cin, int cout) {

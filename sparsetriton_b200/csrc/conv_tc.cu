@@ -1557,10 +1557,28 @@ permute_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ o
     if (from[j] >= 0) dst[first + (IndexT)j * 256] = piece[j];
 }
 
+static void launch_permute_rows(const void* src, const int32_t* order, int64_t n_rows, int vecs, void* dst,
+                                cudaStream_t stream) {
+  const int64_t total = n_rows * vecs;
+  const unsigned blocks = (unsigned)((total + 256 * kPermutePer - 1) / (256 * kPermutePer));
+  if (total + 256 * kPermutePer < 0xFFFFFFFFll)
+    permute_rows_kernel<uint32_t><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(src), order, n_rows, vecs,
+                                                              static_cast<uint4*>(dst));
+  else
+    permute_rows_kernel<int64_t><<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(src), order, n_rows, vecs,
+                                                             static_cast<uint4*>(dst));
+  note_launches(1);
+}
+
+// The copy pass pays for itself when a tile is fetched by four CTAs or more (offset groups x channel blocks); with two
+// groups (32 input channels: 16 offsets per group) it only adds its own cost.
+static bool wgrad_copy_pays(const tc::WgradParams& p) { return p.n_kgroups * p.n_ciblk * p.n_coblk >= 4; }
+
 // Tile-plan form: the TMA-fed kernel when both tensors can be described to the copy engine and two
 // slots fit, else the cp.async producers of wgrad_kernel over the same plan.  `sorted_rows`: scratch for a copy of
 // the tile operand in tile order (n_rows x cout elements), or null.
-static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cudaStream_t stream, void* sorted_rows) {
+static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cudaStream_t stream, void* sorted_rows,
+                                bool presorted) {
   tc::WgradParams& p = plan.p;
   if (p.swap) {
     // ring 1 holds X tiles (ci_blk wide), ring 2 the gathered dY rows (128 output channels wide)
@@ -1604,24 +1622,15 @@ static int launch_wgrad_planned(WgradPlan& plan, const tc::PlannedRows& map, cud
   // The dY tile of a step is 128 rows picked through `order`: 32 row gathers per 128-byte column block, and every
   // offset group (and input-channel block) of a row chunk fetches it again.  With the rows copied into tile order once
   // (one streaming pass) a tile is a dense box, which the copy engine moves 2.3x faster.
-  // The copy pass pays for itself when a tile is fetched by four CTAs or more (offset groups x channel blocks); with two
-  // groups (32 input channels: 16 offsets per group) it only adds its own cost.
+  // `presorted`: the caller made that copy already (tc_wgrad_sort_rows, typically on another stream beside the
+  // feature gradient).
   p.dense_tiles = 0;
-  const bool worth_a_copy = p.n_kgroups * p.n_ciblk * p.n_coblk >= 4;
-  if (tma && !p.swap && g_dense_tiles && (p.order == nullptr || (sorted_rows != nullptr && worth_a_copy)) &&
+  if (tma && !p.swap && g_dense_tiles &&
+      (p.order == nullptr || (sorted_rows != nullptr && (presorted || wgrad_copy_pays(p)))) &&
       (p.cout * p.esize) % 16 == 0) {
     const void* tiles = p.dy;
     if (p.order) {
-      const int vecs = p.cout * p.esize / 16;
-      const int64_t total = p.n_rows * vecs;
-      const unsigned blocks = (unsigned)((total + 256 * kPermutePer - 1) / (256 * kPermutePer));
-      if (total + 256 * kPermutePer < 0xFFFFFFFFll)
-        permute_rows_kernel<uint32_t><<<blocks, 256, 0, stream>>>(
-            static_cast<const uint4*>(p.dy), p.order, p.n_rows, vecs, static_cast<uint4*>(sorted_rows));
-      else
-        permute_rows_kernel<int64_t><<<blocks, 256, 0, stream>>>(
-            static_cast<const uint4*>(p.dy), p.order, p.n_rows, vecs, static_cast<uint4*>(sorted_rows));
-      note_launches(1);
+      if (!presorted) launch_permute_rows(p.dy, p.order, p.n_rows, p.cout * p.esize / 16, sorted_rows, stream);
       tiles = sorted_rows;
     }
     if (make_weight_desc(&tile_box_desc, tiles, p.n_rows, p.cout, p.esize, dtype, tc::kTileM, p.esize == 4)) p.dense_tiles = 1;
@@ -1682,7 +1691,7 @@ static bool prepare_wgrad(WgradPlan* plan, int dtype, const void* x, const void*
 
 int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const MapPlan& rows, float* partial,
                   int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream,
-                  bool inverse_plan, void* sorted_rows) {
+                  bool inverse_plan, void* sorted_rows, bool presorted) {
   WgradPlan plan;
   if (!prepare_wgrad(&plan, dtype, x, dy, partial, n_rows, n_src, K, cin, cout)) return ST_ERR_UNSUPPORTED;
   plan.p.order = rows.order;
@@ -1693,11 +1702,29 @@ int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, 
   }
   int rc;
   if (rows.tmap && rows.tmask)
-    rc = launch_wgrad_planned(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream, sorted_rows);
+    rc = launch_wgrad_planned(plan, tc::PlannedRows{rows.tmap, rows.tmask, K, (K + 31) / 32}, stream, sorted_rows,
+                              presorted);
   else
     rc = launch_wgrad(plan, tc::StoredRows{map, K}, stream);
   *n_chunks_out = plan.n_chunks;
   return rc;
+}
+
+bool tc_wgrad_sorts_rows(int dtype, int64_t n_rows, int K, int cin, int cout) {
+  WgradPlan plan;
+  if (!g_tma_enabled || !g_dense_tiles || !plan_wgrad(&plan, dtype, n_rows, K, cin, cout)) return false;
+  return wgrad_copy_pays(plan.p) && (plan.p.cout * plan.p.esize) % 16 == 0;
+}
+
+int tc_wgrad_sort_rows(int dtype, const void* dy, const int32_t* order, int64_t n_rows, int cout, void* sorted,
+                       cudaStream_t stream) {
+  const int esize = dtype == ST_F32 ? 4 : 2;
+  if ((cout * esize) % 16 != 0 || ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(sorted)) & 15)) {
+    set_error("tc wgrad: rows to sort must be whole 16-byte pieces at 16-byte aligned addresses");
+    return ST_ERR_UNSUPPORTED;
+  }
+  launch_permute_rows(dy, order, n_rows, cout * esize / 16, sorted, stream);
+  return check_launch("tc wgrad row sort");
 }
 
 int tc_conv_wgrad_hashfly(int dtype, const void* x, const void* dy, const HashFlyArgs& h, float* partial,

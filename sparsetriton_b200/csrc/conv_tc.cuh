@@ -64,7 +64,12 @@ int64_t tc_wgrad_partial_bytes(int dtype, int64_t n_rows, int K, int cin, int co
 // n_src the rows of dy (the rows the plan's entries name).
 int tc_conv_wgrad(int dtype, const void* x, const void* dy, const int32_t* map, const MapPlan& plan, float* partial,
                   int* n_chunks_out, int64_t n_rows, int64_t n_src, int K, int cin, int cout, cudaStream_t stream,
-                  bool inverse_plan = false, void* sorted_rows = nullptr);
+                  bool inverse_plan = false, void* sorted_rows = nullptr, bool presorted = false);
+// Whether tc_conv_wgrad over a tile plan with a row order would copy dY into tile order (into `sorted_rows`), and that
+// copy alone; with it made beforehand, tc_conv_wgrad takes presorted = true.
+bool tc_wgrad_sorts_rows(int dtype, int64_t n_rows, int K, int cin, int cout);
+int tc_wgrad_sort_rows(int dtype, const void* dy, const int32_t* order, int64_t n_rows, int cout, void* sorted,
+                       cudaStream_t stream);
 
 // Cycle counters of timing experiments (see Params2::dbg).
 int tc_read_prof(long long* host_out, int n);

@@ -51,7 +51,10 @@ __device__ __forceinline__ bool axis_candidate(int in, int o, int stride, bool t
     v = in * stride + o;
   } else {
     const int t = in + o;
-    if (stride > 1) {
+    if (stride == 2) {                                      // the usual stride: no division
+      if (t & 1) return false;
+      v = t >> 1;
+    } else if (stride > 1) {
       const int q = t / stride;
       if (t - q * stride != 0) return false;
       v = q;
@@ -68,6 +71,59 @@ __device__ __forceinline__ bool axis_candidate(int in, int o, int stride, bool t
 // cubic kernel gives): the filters are then separable, so each axis is evaluated KS times instead of
 // KS^3 times and only the surviving combinations are visited (8 of 27 at most for a stride-2 k3 layer).
 // These sweeps were bound by instruction issue (ncu: SM throughput 62-71 %, DRAM 3-25 %).
+// Per axis of a product grid of offsets: the offsets that pass axis_candidate(), compacted to the front (output
+// coordinate and offset index), and how many there are.
+template <int KS>
+struct AxisLists {
+  int vx[KS], vy[KS], vz[KS], jx[KS], jy[KS], jz[KS];
+  int nx, ny, nz;
+};
+
+template <int KS>
+__device__ __forceinline__ void axis_lists(const int4& c, const Offsets& off, int stride, bool transposed,
+                                           const Int3& new_shape, AxisLists<KS>& a) {
+  a.nx = a.ny = a.nz = 0;
+#pragma unroll
+  for (int j = 0; j < KS; ++j) {
+    int v;
+    if (axis_candidate(c.y, off.v[(j * KS * KS) * 3 + 0], stride, transposed, new_shape.x, &v)) {
+#pragma unroll
+      for (int q = 0; q < KS; ++q)
+        if (q == a.nx) {
+          a.vx[q] = v;
+          a.jx[q] = j;
+        }
+      ++a.nx;
+    }
+    if (axis_candidate(c.z, off.v[(j * KS) * 3 + 1], stride, transposed, new_shape.y, &v)) {
+#pragma unroll
+      for (int q = 0; q < KS; ++q)
+        if (q == a.ny) {
+          a.vy[q] = v;
+          a.jy[q] = j;
+        }
+      ++a.ny;
+    }
+    if (axis_candidate(c.w, off.v[j * 3 + 2], stride, transposed, new_shape.z, &v)) {
+#pragma unroll
+      for (int q = 0; q < KS; ++q)
+        if (q == a.nz) {
+          a.vz[q] = v;
+          a.jz[q] = j;
+        }
+      ++a.nz;
+    }
+  }
+}
+
+template <int KS>
+__device__ __forceinline__ int pick(const int (&a)[KS], int i) {
+  int r = a[0];
+#pragma unroll
+  for (int q = 1; q < KS; ++q) r = (i == q) ? a[q] : r;
+  return r;
+}
+
 template <int KS, typename F>
 __device__ __forceinline__ void for_each_candidate(const int4& c, const Offsets& off, int K, int stride, bool transposed,
                                                    const Int3& new_shape, F&& f) {
@@ -77,60 +133,80 @@ __device__ __forceinline__ void for_each_candidate(const int4& c, const Offsets&
       if (candidate(c, off, k, stride, transposed, new_shape, &v)) f(k, v);
     }
   } else {
-    // Per axis: the offsets that pass, compacted to the front (value and offset index), and how many there are.
-    // The three loops below then run over this thread's own candidates only -- at most ceil(KS / stride) per axis --
+    // The three loops below run over this thread's own candidates only -- at most ceil(KS / stride) per axis --
     // where a sweep over all KS^3 combinations makes a warp walk every combination that any of its lanes needs
     // (all 27 of a stride-2 k3 layer, of which a lane uses 3.4 on average).
-    int vx[KS], vy[KS], vz[KS], jx[KS], jy[KS], jz[KS];
-    int nx = 0, ny = 0, nz = 0;
-#pragma unroll
-    for (int j = 0; j < KS; ++j) {
-      int v;
-      if (axis_candidate(c.y, off.v[(j * KS * KS) * 3 + 0], stride, transposed, new_shape.x, &v)) {
-#pragma unroll
-        for (int q = 0; q < KS; ++q)
-          if (q == nx) {
-            vx[q] = v;
-            jx[q] = j;
-          }
-        ++nx;
-      }
-      if (axis_candidate(c.z, off.v[(j * KS) * 3 + 1], stride, transposed, new_shape.y, &v)) {
-#pragma unroll
-        for (int q = 0; q < KS; ++q)
-          if (q == ny) {
-            vy[q] = v;
-            jy[q] = j;
-          }
-        ++ny;
-      }
-      if (axis_candidate(c.w, off.v[j * 3 + 2], stride, transposed, new_shape.z, &v)) {
-#pragma unroll
-        for (int q = 0; q < KS; ++q)
-          if (q == nz) {
-            vz[q] = v;
-            jz[q] = j;
-          }
-        ++nz;
-      }
-    }
-    auto pick = [](const int (&a)[KS], int i) {
-      int r = a[0];
-#pragma unroll
-      for (int q = 1; q < KS; ++q) r = (i == q) ? a[q] : r;
-      return r;
-    };
+    AxisLists<KS> a;
+    axis_lists<KS>(c, off, stride, transposed, new_shape, a);
 #pragma unroll 1
-    for (int ax = 0; ax < nx; ++ax) {
-      const int x = pick(vx, ax), ix = pick(jx, ax);
+    for (int ax = 0; ax < a.nx; ++ax) {
+      const int x = pick<KS>(a.vx, ax), ix = pick<KS>(a.jx, ax);
 #pragma unroll 1
-      for (int ay = 0; ay < ny; ++ay) {
-        const int y = pick(vy, ay), iy = pick(jy, ay);
+      for (int ay = 0; ay < a.ny; ++ay) {
+        const int y = pick<KS>(a.vy, ay), iy = pick<KS>(a.jy, ay);
 #pragma unroll 1
-        for (int az = 0; az < nz; ++az) f((ix * KS + iy) * KS + pick(jz, az), Int3{x, y, pick(vz, az)});
+        for (int az = 0; az < a.nz; ++az) f((ix * KS + iy) * KS + pick<KS>(a.jz, az), Int3{x, y, pick<KS>(a.vz, az)});
       }
     }
   }
+}
+
+// The rows of a warp have 1 to 8 candidates each on a stride-2 k3 layer, 3.4 on average: with one row per lane a
+// warp runs the body eight times at 42 % of its lanes.  Here every lane first lists its candidates (cell number,
+// owner lane, offset) in a shared line of the warp, at the positions a prefix sum of the counts gives, and the warp
+// then takes the listed candidates 32 at a time, one per lane: f(owner lane, k, cell).  For layers whose rows have at
+// most kDensePerRow candidates (see dense_sweep_ok) and whose cell numbers fit 32 bits (kDirectMaxCells).  Every
+// lane of the warp must call it; `live` says whether the lane has a row.
+constexpr int kDensePerRow = 8;
+
+template <typename F>
+__device__ __forceinline__ void warp_dense_candidates(bool live, const int4& c, const Offsets& off, int stride,
+                                                      const Int3& new_shape, uint2* line, F&& f) {
+  const int lane = threadIdx.x & 31;
+  AxisLists<3> a;
+  a.nx = a.ny = a.nz = 0;
+  if (live) axis_lists<3>(c, off, stride, false, new_shape, a);
+  const int mine = a.nx * a.ny * a.nz;
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int u = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= o) incl += u;
+  }
+  const int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+  int q = incl - mine;
+#pragma unroll 1
+  for (int ax = 0; ax < a.nx; ++ax) {
+    const int x = pick<3>(a.vx, ax), ix = pick<3>(a.jx, ax);
+#pragma unroll 1
+    for (int ay = 0; ay < a.ny; ++ay) {
+      const int y = pick<3>(a.vy, ay), iy = pick<3>(a.jy, ay);
+      const int plane = ((c.x * new_shape.x + x) * new_shape.y + y) * new_shape.z;
+#pragma unroll 1
+      for (int az = 0; az < a.nz; ++az)
+        line[q++] = make_uint2((uint32_t)(plane + pick<3>(a.vz, az)),
+                               ((uint32_t)lane << 8) | (uint32_t)((ix * 3 + iy) * 3 + pick<3>(a.jz, az)));
+    }
+  }
+  __syncwarp();
+  for (int i = lane; i < total; i += 32) {
+    const uint2 e = line[i];
+    f((int)(e.y >> 8), (int)(e.y & 255u), e.x);
+  }
+  __syncwarp();
+}
+
+// Whether warp_dense_candidates() serves the layer: a cubic k3 product grid at stride 2, not transposed, whose
+// offsets along an axis do not all share a parity (then at most two of the three pass the stride filter).
+static bool dense_sweep_ok(const Offsets& off, int ks, int stride, bool transposed) {
+  if (ks != 3 || stride != 2 || transposed) return false;
+  for (int axis = 0; axis < 3; ++axis) {
+    const int step = axis == 0 ? 9 : (axis == 1 ? 3 : 1);
+    int odd = 0;
+    for (int j = 0; j < 3; ++j) odd += off.v[(j * step) * 3 + axis] & 1;
+    if (odd == 0 || odd == 3) return false;
+  }
+  return true;
 }
 
 // KS such that the K offsets are the product grid for_each_candidate<KS> expects (2 or 3), else 0.
@@ -612,9 +688,10 @@ __device__ __forceinline__ int64_t cell_index(int b, const Int3& v, const Int3& 
 
 // Number of set bits below bit i: the block's prefix plus the popcounts inside its 256-bit block (one 32-byte
 // sector).
+template <typename IndexT>
 __device__ __forceinline__ uint32_t bit_rank(const uint32_t* __restrict__ bits, const uint32_t* __restrict__ prefix,
-                                             int64_t i) {
-  const int64_t blk = i >> 8;
+                                             IndexT i) {
+  const IndexT blk = i >> 8;
   const uint4* p = reinterpret_cast<const uint4*>(bits + blk * 8);
   const uint4 lo = p[0], hi = p[1];
   const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
@@ -626,11 +703,25 @@ __device__ __forceinline__ uint32_t bit_rank(const uint32_t* __restrict__ bits, 
   return r;
 }
 
-template <typename CT, int KS>
+template <typename CT, int KS, bool DENSE = false>
 __global__ void __launch_bounds__(kRowThreads)
 direct_bits_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
                    Int3 new_shape, int batch_bound, uint32_t* bits, int32_t* status) {
   const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if constexpr (DENSE) {
+    __shared__ uint2 lines[kRowThreads / 32][32 * kDensePerRow];
+    bool live = row < n;
+    const int4 c = live ? load_coord<CT>(coords, row) : make_int4(0, 0, 0, 0);
+    if (live && (unsigned)c.x >= (unsigned)batch_bound) {
+      atomicOr(status, ST_DEV_BAD_INDEX);
+      live = false;
+    }
+    warp_dense_candidates(live, c, off, stride, new_shape, lines[threadIdx.x >> 5], [&](int, int, uint32_t cell) {
+      const uint32_t m = 1u << (cell & 31);
+      if (!(__ldcg(bits + (cell >> 5)) & m)) atomicOr(bits + (cell >> 5), m);
+    });
+    return;
+  }
   if (row >= n) return;
   const int4 c = load_coord<CT>(coords, row);
   if ((unsigned)c.x >= (unsigned)batch_bound) {           // a sample the caller did not announce: no cell for it
@@ -655,12 +746,25 @@ bit_block_count_kernel(const uint32_t* __restrict__ bits, int64_t n_blocks, uint
               __popc(hi.w);
 }
 
-template <typename CT, int KS>
+template <typename CT, int KS, bool DENSE = false>
 __global__ void __launch_bounds__(kRowThreads)
 direct_minflat_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed,
                       Int3 new_shape, int batch_bound, const uint32_t* __restrict__ bits,
                       const uint32_t* __restrict__ prefix, uint32_t* min_flat) {
   const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if constexpr (DENSE) {
+    __shared__ uint2 lines[kRowThreads / 32][32 * kDensePerRow];
+    bool live = row < n;
+    const int4 c = live ? load_coord<CT>(coords, row) : make_int4(0, 0, 0, 0);
+    if ((unsigned)c.x >= (unsigned)batch_bound) live = false;
+    const uint32_t warp_row = (uint32_t)(row - (threadIdx.x & 31));
+    warp_dense_candidates(live, c, off, stride, new_shape, lines[threadIdx.x >> 5], [&](int owner, int k, uint32_t cell) {
+      const uint32_t r = bit_rank<uint32_t>(bits, prefix, cell);
+      const uint32_t flat = (warp_row + (uint32_t)owner) * (uint32_t)K + (uint32_t)k;
+      if (__ldcg(min_flat + r) > flat) atomicMin(min_flat + r, flat);
+    });
+    return;
+  }
   if (row >= n) return;
   const int4 c = load_coord<CT>(coords, row);
   if ((unsigned)c.x >= (unsigned)batch_bound) return;
@@ -713,12 +817,25 @@ direct_write_kernel(const CT* __restrict__ coords, int K, Offsets off, int strid
 }
 
 // nbr[out_row(candidate), k] = max(input row), as outcoords_map_kernel.  nbr must hold -1.
-template <typename CT, int KS>
+template <typename CT, int KS, bool DENSE = false>
 __global__ void __launch_bounds__(kRowThreads)
 direct_map_kernel(const CT* __restrict__ coords, int64_t n, int K, Offsets off, int stride, bool transposed, Int3 new_shape,
                   Int3 in_shape, int batch_bound, const uint32_t* __restrict__ bits, const uint32_t* __restrict__ prefix,
                   const uint32_t* __restrict__ out_row, int32_t* nbr, int64_t n_out) {
   const int64_t row = (int64_t)blockIdx.x * kRowThreads + threadIdx.x;
+  if constexpr (DENSE) {
+    __shared__ uint2 lines[kRowThreads / 32][32 * kDensePerRow];
+    bool live = row < n;
+    const int4 c = live ? load_coord<CT>(coords, row) : make_int4(0, 0, 0, 0);
+    if ((unsigned)c.x >= (unsigned)batch_bound) live = false;
+    if (c.y < 0 || c.y >= in_shape.x || c.z < 0 || c.z >= in_shape.y || c.w < 0 || c.w >= in_shape.z) live = false;
+    const int32_t warp_row = (int32_t)(row - (threadIdx.x & 31));
+    warp_dense_candidates(live, c, off, stride, new_shape, lines[threadIdx.x >> 5], [&](int owner, int k, uint32_t cell) {
+      const uint32_t o = out_row[bit_rank<uint32_t>(bits, prefix, cell)];
+      if (o < (uint32_t)n_out) atomicMax(nbr + (int64_t)o * K + k, warp_row + owner);
+    });
+    return;
+  }
   if (row >= n) return;
   const int4 c = load_coord<CT>(coords, row);
   if ((unsigned)c.x >= (unsigned)batch_bound) return;
@@ -735,7 +852,9 @@ static int direct_count_impl(const CT* coords, int64_t n, const Offsets& off, in
   const unsigned grid = (unsigned)((n + kRowThreads - 1) / kRowThreads);
   cudaMemsetAsync(d.cell_bits, 0, (size_t)d.n_cell_blocks * 32, s);
   const int ks = product_kernel_size(off, K);
-  if (ks == 3)
+  if (dense_sweep_ok(off, ks, stride, transposed))
+    direct_bits_kernel<CT, 3, true><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, status);
+  else if (ks == 3)
     direct_bits_kernel<CT, 3><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, status);
   else if (ks == 2)
     direct_bits_kernel<CT, 2><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, status);
@@ -763,7 +882,9 @@ static int direct_write_impl(const CT* coords, int64_t n, const Offsets& off, in
   cudaMemsetAsync(d.min_flat, 0xFF, (size_t)n_out * 4, s);
   cudaMemsetAsync(d.flat_bits, 0, (size_t)d.n_flat_blocks * 32, s);
   const int ks = product_kernel_size(off, K);
-  if (ks == 3)
+  if (dense_sweep_ok(off, ks, stride, transposed))
+    direct_minflat_kernel<CT, 3, true><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, d.cell_prefix, d.min_flat);
+  else if (ks == 3)
     direct_minflat_kernel<CT, 3><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, d.cell_prefix, d.min_flat);
   else if (ks == 2)
     direct_minflat_kernel<CT, 2><<<grid, kRowThreads, 0, s>>>(coords, n, K, off, stride, transposed, ns, batch_bound, d.cell_bits, d.cell_prefix, d.min_flat);
@@ -933,14 +1054,17 @@ int st_outcoords_map(const void* coords, int64_t n, int coord_dtype, const int32
   const int ks = product_kernel_size(off, K);
   DirectLayout d;
   if (direct_layout(workspace, workspace_bytes, n, K, stride, transposed, ns, batch_bound, &d)) {
-#define ST_DMAP(CT, KS)                                                                                               \
-  direct_map_kernel<CT, KS><<<grid, kRowThreads, 0, s>>>(static_cast<const CT*>(coords), n, K, off, stride,          \
-                                                         transposed != 0, ns, in_shape, batch_bound, d.cell_bits,    \
-                                                         d.cell_prefix, d.out_row, nbr, n_out)
+    const bool dense = dense_sweep_ok(off, ks, stride, transposed != 0);
+#define ST_DMAP(CT, KS, DENSE)                                                                                        \
+  direct_map_kernel<CT, KS, DENSE><<<grid, kRowThreads, 0, s>>>(static_cast<const CT*>(coords), n, K, off, stride,   \
+                                                                transposed != 0, ns, in_shape, batch_bound,          \
+                                                                d.cell_bits, d.cell_prefix, d.out_row, nbr, n_out)
     if (coord_dtype == ST_I32) {
-      if (ks == 3) ST_DMAP(int32_t, 3); else if (ks == 2) ST_DMAP(int32_t, 2); else ST_DMAP(int32_t, 0);
+      if (dense) ST_DMAP(int32_t, 3, true); else if (ks == 3) ST_DMAP(int32_t, 3, false);
+      else if (ks == 2) ST_DMAP(int32_t, 2, false); else ST_DMAP(int32_t, 0, false);
     } else {
-      if (ks == 3) ST_DMAP(int16_t, 3); else if (ks == 2) ST_DMAP(int16_t, 2); else ST_DMAP(int16_t, 0);
+      if (dense) ST_DMAP(int16_t, 3, true); else if (ks == 3) ST_DMAP(int16_t, 3, false);
+      else if (ks == 2) ST_DMAP(int16_t, 2, false); else ST_DMAP(int16_t, 0, false);
     }
 #undef ST_DMAP
     note_launches(1);

@@ -230,9 +230,49 @@ def stored_map_dgrad(dy, w, nbr, n_in, flops=0.0):
     return dx
 
 
-def stored_map_wgrad(x, dy, nbr, K, flops=0.0):
+_NO_PRESORT = set()          # (dtype code, K, c_in, c_out) of layers whose weight gradient makes no sorted copy of dY
+
+
+def start_wgrad_presort(x, dy, nbr, K):
+    """First half of the weight gradient, on a second stream: the copy of dY in the plan's row order, which depends on
+    dY and the plan alone, so that it runs beside the feature gradient instead of before the weight gradient's
+    product.  Returns (workspace, event) for stored_map_wgrad, or None when the layer makes no such copy."""
+    n_in, c_in = x.shape
+    n_out, c_out = dy.shape
+    code = _lib.feat_code(x)
+    key = (code, K, c_in, c_out)
+    if n_out == 0 or key in _NO_PRESORT or WGRAD_OVER_INVERSE_PLAN:
+        return None
+    L = _lib.lib()
+    if not L.st_conv_uses_tensor_cores(code, c_in, c_out):
+        _NO_PRESORT.add(key)
+        return None
+    with _lib.on_device(x.device):
+        plan = map_plan(nbr)
+        if plan.order is None:
+            return None
+        ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
+        cur = torch.cuda.current_stream(x.device)
+        aux = _aux_stream(x.device, cur)
+        aux.wait_stream(cur)
+        with torch.cuda.stream(aux):
+            rc = L.st_conv_wgrad_presort(code, _lib.ptr(dy), _lib.ptr(plan.order), n_out, K, c_in, c_out, _lib.ptr(ws),
+                                         ws.numel(), _lib.stream_ptr())
+            if rc == -5:                      # ST_ERR_UNSUPPORTED: no copy for this shape; nothing was launched
+                _NO_PRESORT.add(key)
+                return None
+            _lib.check(rc, "st_conv_wgrad_presort")
+            done = torch.cuda.Event()
+            done.record(aux)
+    # no record_stream on ws / dy: the caller's stream waits for `done` before the product, and both tensors are
+    # released on that stream after it, so their memory is never handed out while the second stream still reads it
+    return ws, done
+
+
+def stored_map_wgrad(x, dy, nbr, K, flops=0.0, presorted=None):
     """dW[k] = sum_o X[nbr[o, k]]^T . dY[o], in the dtype of x.  Walks the plan of the forward map; with
-    WGRAD_OVER_INVERSE_PLAN, a layer with more input than output rows walks the inverse plan instead."""
+    WGRAD_OVER_INVERSE_PLAN, a layer with more input than output rows walks the inverse plan instead.
+    `presorted`: what start_wgrad_presort returned for the same operands."""
     n_in, c_in = x.shape
     n_out, c_out = dy.shape
     code = _lib.feat_code(x)
@@ -251,12 +291,17 @@ def stored_map_wgrad(x, dy, nbr, K, flops=0.0):
             if rc != -5:                      # ST_ERR_UNSUPPORTED: unaligned tensors or TMA switched off -> forward plan
                 _lib.check(rc, "st_conv_wgrad_inverse_planned")
                 return dw
-        ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
         plan = map_plan(nbr) if tc else _NO_PLAN
+        if presorted is not None:
+            ws, done = presorted
+            torch.cuda.current_stream(x.device).wait_event(done)
+            entry = L.st_conv_wgrad_planned_presorted
+        else:
+            ws = _lib.workspace(L.st_conv_workspace_bytes(code, n_in, n_out, K, c_in, c_out), x.device)
+            entry = L.st_conv_wgrad_planned
         with trace.stage("conv_wgrad", work=flops, tag=(c_in, c_out)):
-            rc = L.st_conv_wgrad_planned(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), *plan.ptrs(),
-                                         _lib.ptr(dw), n_in, n_out, K, c_in, c_out, _lib.ptr(ws), ws.numel(),
-                                         _lib.stream_ptr())
+            rc = entry(code, _lib.ptr(x), _lib.ptr(dy), _lib.ptr(nbr), *plan.ptrs(), _lib.ptr(dw), n_in, n_out, K, c_in,
+                       c_out, _lib.ptr(ws), ws.numel(), _lib.stream_ptr())
         _lib.check(rc, "st_conv_wgrad_planned")
     return dw
 
@@ -289,10 +334,13 @@ class ConvPrecomputedNeighborGEMM(torch.autograd.Function):
         t_in, t_out = ctx.true_widths
         dy = pad_cols(grad_output.to(x.dtype), c_out).contiguous()
         dx = dw = None
+        presorted = None
+        if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
+            presorted = start_wgrad_presort(x, dy, nbr, K)     # beside the feature gradient, on a second stream
         if ctx.needs_input_grad[0]:
             dx = stored_map_dgrad(dy, w, nbr, n_in, ctx.flops)
         if ctx.needs_input_grad[1]:
-            dw = stored_map_wgrad(x, dy, nbr, K, ctx.flops).to(ctx.w_dtype)
+            dw = stored_map_wgrad(x, dy, nbr, K, ctx.flops, presorted).to(ctx.w_dtype)
         if dx is not None and t_in != c_in:
             dx = dx[:, :t_in].contiguous()
         if dw is not None and (t_in != c_in or t_out != c_out):

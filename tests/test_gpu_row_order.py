@@ -168,6 +168,47 @@ def test_products_with_plan(cuda_device, oracle, dtype, form, n_rows, n_src, K, 
     assert rel_err(t2n(dw1), oracle.conv_wgrad(xf, dyf, m, K, cin, cout)) < tol
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
+@pytest.mark.parametrize("n_rows,n_src,K,cin,cout,copies", [(70001, 40000, 27, 64, 128, True), (9000, 12000, 27, 128, 128, True),
+                                                            (5000, 5000, 27, 32, 64, None), (3000, 3000, 8, 16, 16, False)])
+def test_wgrad_in_two_calls(cuda_device, dtype, n_rows, n_src, K, cin, cout, copies):
+    """st_conv_wgrad_presort on a second stream + st_conv_wgrad_planned_presorted give st_conv_wgrad_planned's dW bit
+    for bit; a layer without a sorted copy answers ST_ERR_UNSUPPORTED and launches nothing."""
+    dev = cuda_device
+    L = _lib.lib()
+    nbr = _random_map(n_rows, n_src, K, 0.25, 11, dev, 20)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(n_src, cin, generator=g).to(dev, dtype)
+    dy = torch.randn(n_rows, cout, generator=g).to(dev, dtype)
+    code = _lib.feat_code(x)
+    dw0 = torch.full((K, cin, cout), 7.0, device=dev, dtype=dtype)
+    dw1 = torch.full_like(dw0, 9.0)
+    nbytes = L.st_conv_workspace_bytes(code, n_src, n_rows, K, cin, cout)
+    ws0, ws1 = _lib.workspace(nbytes, dev), _lib.workspace(nbytes, dev)
+    p = _lib.ptr
+    with torch.cuda.device(dev):
+        s = _lib.stream_ptr()
+        fpp = [p(v) for v in _plan(nbr, True)]
+        _lib.check(L.st_conv_wgrad_planned(code, p(x), p(dy), p(nbr), *fpp, p(dw0), n_src, n_rows, K, cin, cout, p(ws0),
+                                           ws0.numel(), s), "wgrad planned")
+        cur, aux = torch.cuda.current_stream(dev), torch.cuda.Stream(device=dev)
+        aux.wait_stream(cur)
+        with torch.cuda.stream(aux):
+            rc = L.st_conv_wgrad_presort(code, p(dy), fpp[0], n_rows, K, cin, cout, p(ws1), ws1.numel(), _lib.stream_ptr())
+        if copies is not None:
+            assert (rc == 0) == copies
+        if rc == 0:
+            cur.wait_stream(aux)
+            _lib.check(L.st_conv_wgrad_planned_presorted(code, p(x), p(dy), p(nbr), *fpp, p(dw1), n_src, n_rows, K, cin, cout,
+                                                         p(ws1), ws1.numel(), s), "wgrad planned presorted")
+        else:
+            assert rc == -5
+        torch.cuda.synchronize()
+    assert _lib.device_status(dev)[0] == 0
+    if rc == 0:
+        assert torch.equal(dw0, dw1)
+
+
 @pytest.mark.parametrize("n_rows,n_src,K,density,patterns", [(5000, 4000, 27, 0.25, 20), (70001, 50000, 27, 0.2, None),
                                                               (3000, 9000, 8, 0.5, None), (900, 700, 1, 0.6, None),
                                                               (40000, 30000, 32, 0.1, 50)])

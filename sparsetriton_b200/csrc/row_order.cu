@@ -162,6 +162,9 @@ __device__ __forceinline__ void load_quads(const int32_t* __restrict__ nbr, int6
   }
 }
 
+// IndexT: the type the flat index is divided in (32 bits when the map has fewer than 2^31 entries: a 64-bit division
+// per run made these kernels instruction-bound).
+template <typename IndexT>
 __global__ void __launch_bounds__(256)
 inverse_keys_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int64_t n_in, uint32_t* keys) {
   const int64_t block_first = (int64_t)blockIdx.x * kFlatPerBlock;
@@ -170,7 +173,7 @@ inverse_keys_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int6
 #pragma unroll
   for (int q = 0; q < kFlatQuads; ++q) {
     const int64_t t0 = block_first + ((int64_t)q * 256 + threadIdx.x) * 4;
-    int k = (int)(t0 % K);
+    int k = (int)((IndexT)t0 % (IndexT)K);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       if (v[q][j] >= 0 && v[q][j] < n_in) atomicOr(keys + v[q][j], 1u << k);
@@ -196,6 +199,7 @@ __global__ void __launch_bounds__(128) tile_mask_kernel(const uint32_t* __restri
 }
 
 // tmap_inv[(tile(pos) * K + k) * 128 + pos % 128] = o for nbr[o,k] = i, pos = rank[i]; tmap_inv holds -1
+template <typename IndexT>
 __global__ void __launch_bounds__(256)
 inverse_plan_scatter_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int K, int64_t n_in,
                             const int32_t* __restrict__ rank, int32_t* __restrict__ tmap) {
@@ -210,7 +214,7 @@ inverse_plan_scatter_kernel(const int32_t* __restrict__ nbr, int64_t n_flat, int
 #pragma unroll
   for (int q = 0; q < kFlatQuads; ++q) {
     const int64_t t0 = block_first + ((int64_t)q * 256 + threadIdx.x) * 4;
-    int64_t o = t0 / K;
+    int64_t o = (int64_t)((IndexT)t0 / (IndexT)K);
     int k = (int)(t0 - o * K);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -284,16 +288,22 @@ int st_map_plan_inverse(const int32_t* nbr, int64_t n_out, int K, int64_t n_in, 
   const int64_t n_flat = n_out * K, n_tiles = (n_in + 127) / 128, n_tmap = n_tiles * K * 128;
   const unsigned rows_grid = (unsigned)((n_in + 255) / 256);
   iota_clear_kernel<<<rows_grid, 256, 0, st>>>(s.keys_a, first_vals(s, K, order), n_in);
-  if (n_flat > 0)
-    inverse_keys_kernel<<<(unsigned)((n_flat + kFlatPerBlock - 1) / kFlatPerBlock), 256, 0, st>>>(nbr, n_flat, K, n_in, s.keys_a);
+  const unsigned flat_grid = (unsigned)((n_flat + kFlatPerBlock - 1) / kFlatPerBlock);
+  const bool narrow = n_flat + kFlatPerBlock < 0x7FFFFFFFll;           // every flat index a thread forms fits 32 bits
+  if (n_flat > 0) {
+    if (narrow) inverse_keys_kernel<uint32_t><<<flat_grid, 256, 0, st>>>(nbr, n_flat, K, n_in, s.keys_a);
+    else inverse_keys_kernel<int64_t><<<flat_grid, 256, 0, st>>>(nbr, n_flat, K, n_in, s.keys_a);
+  }
   note_launches(2);
   uint32_t* sorted_keys = nullptr;
   sort_passes(s, n_in, K, order, &sorted_keys, st);
   rank_kernel<<<rows_grid, 256, 0, st>>>(order, n_in, rank);
   tile_mask_kernel<<<(unsigned)n_tiles, 128, 0, st>>>(sorted_keys, n_in, tmask);
   cudaMemsetAsync(tmap, 0xFF, (size_t)n_tmap * sizeof(int32_t), st);                  // every entry -1
-  if (n_flat > 0)
-    inverse_plan_scatter_kernel<<<(unsigned)((n_flat + kFlatPerBlock - 1) / kFlatPerBlock), 256, 0, st>>>(nbr, n_flat, K, n_in, rank, tmap);
+  if (n_flat > 0) {
+    if (narrow) inverse_plan_scatter_kernel<uint32_t><<<flat_grid, 256, 0, st>>>(nbr, n_flat, K, n_in, rank, tmap);
+    else inverse_plan_scatter_kernel<int64_t><<<flat_grid, 256, 0, st>>>(nbr, n_flat, K, n_in, rank, tmap);
+  }
   note_launches(3);
   return check_launch("st_map_plan_inverse");
 }

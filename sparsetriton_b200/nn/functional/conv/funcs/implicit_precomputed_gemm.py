@@ -256,8 +256,9 @@ def start_wgrad_presort(x, dy, nbr, K):
         aux = _aux_stream(x.device, cur)
         aux.wait_stream(cur)
         with torch.cuda.stream(aux):
-            rc = L.st_conv_wgrad_presort(code, _lib.ptr(dy), _lib.ptr(plan.order), n_out, K, c_in, c_out, _lib.ptr(ws),
-                                         ws.numel(), _lib.stream_ptr())
+            with trace.stage("conv_wgrad_presort", tag=(c_in, c_out)):
+                rc = L.st_conv_wgrad_presort(code, _lib.ptr(dy), _lib.ptr(plan.order), n_out, K, c_in, c_out, _lib.ptr(ws),
+                                             ws.numel(), _lib.stream_ptr())
             if rc == -5:                      # ST_ERR_UNSUPPORTED: no copy for this shape; nothing was launched
                 _NO_PRESORT.add(key)
                 return None

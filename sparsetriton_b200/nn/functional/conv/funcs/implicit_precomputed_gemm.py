@@ -231,6 +231,9 @@ def stored_map_dgrad(dy, w, nbr, n_in, flops=0.0):
 
 
 _NO_PRESORT = set()          # (dtype code, K, c_in, c_out) of layers whose weight gradient makes no sorted copy of dY
+# A second stream costs the host some 30 us (two waits, an event, the stream switch): worth it when the copy is long
+# enough to hide something -- 32 MB of dY are 13 us of copy at 5 TB/s.  Below that the copy stays inside the one call.
+_PRESORT_MIN_BYTES = 32 << 20
 
 
 def start_wgrad_presort(x, dy, nbr, K):
@@ -241,7 +244,7 @@ def start_wgrad_presort(x, dy, nbr, K):
     n_out, c_out = dy.shape
     code = _lib.feat_code(x)
     key = (code, K, c_in, c_out)
-    if n_out == 0 or key in _NO_PRESORT or WGRAD_OVER_INVERSE_PLAN:
+    if n_out == 0 or key in _NO_PRESORT or WGRAD_OVER_INVERSE_PLAN or dy.numel() * dy.element_size() < _PRESORT_MIN_BYTES:
         return None
     L = _lib.lib()
     if not L.st_conv_uses_tensor_cores(code, c_in, c_out):

@@ -146,7 +146,11 @@ def feat_code(t):
 
 
 def ptr(t):
-    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() > 0 else ctypes.c_void_p(0)
+    """The address of a tensor's first element as a plain integer (None for no tensor): every entry point has its
+    argument types declared, so ctypes converts it to `void*` itself, which costs less host time than building a
+    c_void_p per argument (a training step passes about a thousand).  An empty tensor gives 0 or the address of its
+    storage; the library reads nothing through either."""
+    return None if t is None else t.data_ptr()
 
 
 _NULL_CONTEXT = contextlib.nullcontext()
@@ -166,7 +170,7 @@ def stream_ptr(device=None):
     index = device.index if isinstance(device, torch.device) else device
     if index is None:
         index = torch.cuda.current_device()
-    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(index))
+    return torch._C._cuda_getCurrentRawStream(index)
 
 
 def host_i32(values):
